@@ -1,0 +1,194 @@
+/*
+ * sb200.h — C ABI of libsarek_b200.so, the B200 (sm_100a) backend for Sarek's
+ * dense-GEMM and fused element-wise map path.
+ *
+ * Every entry point takes plain integers, pointers and sizes so that an OCaml
+ * `ctypes-foreign` binding (the style of sarek-cuda/Cuda_bindings.ml:39-87)
+ * can bind it with `Foreign.foreign`.  Each function returns an int status:
+ * 0 on success, a positive CUDA error code (cudaError_t numbering) when a CUDA
+ * call failed, or a negative SB200_ERR_* for errors detected by the library.
+ * sb200_last_error_string() describes the last failure on the calling thread.
+ *
+ * Device pointers are uint64_t (the `device_ptr : nativeint` of
+ * spoc/framework/Framework_sig.ml Memory); streams, events and kernels are
+ * opaque uint64_t handles; stream 0 is the device's default stream.
+ */
+#ifndef SB200_H
+#define SB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SB200_API __attribute__((visibility("default")))
+
+/* ---- status codes ----------------------------------------------------- */
+#define SB200_OK 0
+#define SB200_ERR_INVALID_VALUE (-1)   /* bad argument (null, negative, overflow) */
+#define SB200_ERR_INVALID_HANDLE (-2)  /* unknown stream/event/kernel/buffer */
+#define SB200_ERR_UNSUPPORTED (-3)     /* IR is not a kernel this backend runs:
+                                          the Backend_error.Unsupported_construct
+                                          of spoc/framework/Backend_error.ml:21-67 */
+#define SB200_ERR_PARSE (-4)           /* malformed IR text */
+#define SB200_ERR_ARGS (-5)            /* argument list does not match the kernel */
+#define SB200_ERR_BOUNDS (-6)          /* launch would index past a vector's length */
+#define SB200_ERR_TIMEOUT (-7)         /* a bounded device-side wait expired */
+#define SB200_ERR_NO_DEVICE (-8)       /* no sm_100 device / CUDA unavailable */
+#define SB200_ERR_TOO_LARGE (-9)       /* size beyond a stated maximum */
+#define SB200_ERR_ALIGNMENT (-10)      /* pointer or leading dimension misaligned */
+
+/* ---- numeric mode of the GEMM ------------------------------------------ */
+#define SB200_MODE_3XTF32 3 /* split accumulation, fp32-grade accuracy (default) */
+#define SB200_MODE_TF32 1   /* operands rounded to TF32 once, one MMA per k-step */
+
+/* ---- epilogue activation ------------------------------------------------ */
+#define SB200_ACT_NONE 0
+#define SB200_ACT_RELU 1 /* if x > 0 then x else 0 */
+
+/* ---- kernel kinds reported by sb200_kernel_kind ----------------------- */
+#define SB200_KIND_MAP 1          /* element-wise map (vector_add, triad, fused chains) */
+#define SB200_KIND_GEMM_NAIVE 2   /* the matrix_mul IR shape */
+#define SB200_KIND_GEMM_TILED 3   /* the matrix_mul_tiled IR shape */
+
+/* ---- argument tags for sb200_kernel_launch ---------------------------- */
+/* One entry per value the caller's run_source receives, in order: a vector
+ * arrives as SB200_ARG_BUFFER followed by SB200_ARG_I32 (its length), scalars
+ * as themselves (sarek/sarek/Execute.ml:197-216). */
+#define SB200_ARG_BUFFER 0
+#define SB200_ARG_I32 1
+#define SB200_ARG_I64 2
+#define SB200_ARG_F32 3
+#define SB200_ARG_F64 4
+
+typedef struct sb200_arg {
+  int32_t tag;
+  int32_t reserved;
+  union {
+    uint64_t buffer; /* device pointer */
+    int32_t i32;
+    int64_t i64;
+    float f32;
+    double f64;
+  } v;
+} sb200_arg;
+
+typedef struct sb200_device_info {
+  char name[256];
+  uint64_t total_mem;
+  int32_t cc_major, cc_minor;
+  int32_t sm_count;
+  int32_t max_threads_per_block;
+  int32_t max_shared_per_block; /* opt-in maximum, bytes */
+  int32_t warp_size;
+  int32_t clock_khz;
+  int32_t l2_bytes;
+} sb200_device_info;
+
+/* ---- library / device: replaces cuInit, cuDeviceGetCount, cuDeviceGet*,
+ *      cuCtxSetCurrent, cuCtxSynchronize (sarek-cuda/Cuda_bindings.ml:90-170,
+ *      sarek-cuda/Cuda_api.ml:35-176) ------------------------------------ */
+SB200_API int sb200_init(void);
+SB200_API int sb200_version(void);
+SB200_API const char *sb200_last_error_string(void);
+SB200_API int sb200_device_count(int *count);
+SB200_API int sb200_device_get_info(int dev, sb200_device_info *out);
+SB200_API int sb200_device_set_current(int dev);
+SB200_API int sb200_device_synchronize(int dev);
+
+/* ---- memory: replaces cuMemAlloc/cuMemFree/cuMemcpyHtoD/DtoH/DtoD and the
+ *      unused async variants (Cuda_bindings.ml:172-258, Cuda_api.ml:191-243).
+ *      sb200_mem_free is idempotent (a GC finaliser may free twice,
+ *      sarek/core/Gpu_memory.ml:151-178) and waits for the device to go idle. */
+SB200_API int sb200_mem_alloc(int dev, uint64_t bytes, uint64_t *dptr);
+SB200_API int sb200_mem_free(int dev, uint64_t dptr);
+SB200_API int sb200_mem_size(int dev, uint64_t dptr, uint64_t *bytes);
+SB200_API int sb200_memset32(int dev, uint64_t dptr, uint32_t value, uint64_t count, uint64_t stream);
+SB200_API int sb200_memcpy_htod(int dev, uint64_t dst, const void *src, uint64_t bytes);
+SB200_API int sb200_memcpy_dtoh(int dev, void *dst, uint64_t src, uint64_t bytes);
+SB200_API int sb200_memcpy_dtod(int dev, uint64_t dst, uint64_t src, uint64_t bytes);
+SB200_API int sb200_memcpy_htod_async(int dev, uint64_t dst, const void *src, uint64_t bytes, uint64_t stream);
+SB200_API int sb200_memcpy_dtoh_async(int dev, void *dst, uint64_t src, uint64_t bytes, uint64_t stream);
+/* pinned host staging for the transfer path (sarek/core/Transfer.ml:229-322) */
+SB200_API int sb200_host_alloc(uint64_t bytes, void **ptr);
+SB200_API int sb200_host_free(void *ptr);
+
+/* ---- streams and events: replaces the cuStream and cuEvent families
+ *      (Cuda_bindings.ml:260-330, Cuda_api.ml:245-311) ------------------- */
+SB200_API int sb200_stream_create(int dev, uint64_t *stream);
+SB200_API int sb200_stream_destroy(int dev, uint64_t stream);
+SB200_API int sb200_stream_synchronize(int dev, uint64_t stream);
+/* adopt a cudaStream_t created elsewhere (e.g. by the host framework) */
+SB200_API int sb200_stream_wrap(int dev, uint64_t native_stream, uint64_t *stream);
+SB200_API int sb200_event_create(int dev, uint64_t *event);
+SB200_API int sb200_event_destroy(int dev, uint64_t event);
+SB200_API int sb200_event_record(int dev, uint64_t event, uint64_t stream);
+SB200_API int sb200_event_synchronize(int dev, uint64_t event);
+SB200_API int sb200_event_elapsed_ms(int dev, uint64_t start, uint64_t stop, float *ms);
+
+/* ---- kernels: replaces generate_source + NVRTC + cuModuleLoadDataEx +
+ *      cuLaunchKernel (sarek-cuda/Sarek_ir_cuda.ml:871-929,
+ *      sarek-cuda/Cuda_api.ml:315-487, sarek-cuda/Cuda_plugin.ml:174-210).
+ *      `ir_text` is the S-expression rendering of a Sarek_ir_types.kernel
+ *      (spoc/ir/Sarek_ir_types.ml:230-245).  Compilation recognises the
+ *      kernel as a GEMM (naive or tiled shape, with optional fused epilogue)
+ *      or an element-wise map; anything else is SB200_ERR_UNSUPPORTED — there
+ *      is no fallback path. */
+SB200_API int sb200_kernel_compile(int dev, const char *ir_text, const char *name, uint64_t *kernel);
+SB200_API int sb200_kernel_destroy(uint64_t kernel);
+SB200_API int sb200_kernel_kind(uint64_t kernel, int *kind);
+/* human-readable summary of what was recognised (for SAREK_DEBUG=kernel) */
+SB200_API int sb200_kernel_describe(uint64_t kernel, char *buf, int buflen);
+SB200_API int sb200_kernel_launch(uint64_t kernel, const sb200_arg *args, int nargs,
+                                  const uint32_t grid[3], const uint32_t block[3],
+                                  uint32_t shared_mem, uint64_t stream);
+
+/* ---- IR fusion: the host-side rewrite of sarek/sarek/Sarek_fusion.ml
+ *      (can_fuse :401-431, fuse :459-547, fuse_pipeline :570-598) on IR text.
+ *      Results are written to `out` (NUL-terminated, at most outlen bytes). */
+SB200_API int sb200_ir_can_fuse(const char *producer, const char *consumer, const char *intermediate, int *result);
+SB200_API int sb200_ir_fuse(const char *producer, const char *consumer, const char *intermediate, char *out, int outlen);
+SB200_API int sb200_ir_fuse_pipeline(const char *const *kernels, int count, char *out, int outlen, char *eliminated, int elimlen);
+
+/* ---- direct operators (what a recognised kernel launch dispatches to) ---
+ * D[M x N] = act(alpha * A[M x K] . B[K x N] + beta * C[M x N] + bias[N]),
+ * all row-major float32 with leading dimensions in elements; C and bias may
+ * be 0.  D may alias C.  Replaces the matrix_mul / matrix_mul_tiled kernels
+ * (benchmarks/bench_matrix_mul.ml:55-73, bench_matrix_mul_tiled.ml:55-94). */
+SB200_API int sb200_gemm_f32(int dev, uint64_t stream, int mode,
+                             int64_t M, int64_t N, int64_t K,
+                             uint64_t A, int64_t lda, uint64_t B, int64_t ldb,
+                             uint64_t D, int64_t ldd,
+                             float alpha, uint64_t C, int64_t ldc, float beta,
+                             uint64_t bias, int act);
+/* bytes of library-owned scratch the call above needs for these sizes */
+SB200_API int sb200_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, uint64_t *bytes);
+
+/* c = a + b  (benchmarks/bench_vector_add.ml:47-55) */
+SB200_API int sb200_vector_add_f32(int dev, uint64_t stream, uint64_t c, uint64_t a, uint64_t b, int64_t n);
+/* a = b + c * scalar  (benchmarks/bench_stream_triad.ml:22-31) */
+SB200_API int sb200_stream_triad_f32(int dev, uint64_t stream, uint64_t a, uint64_t b, uint64_t c, float scalar, int64_t n);
+/* fused chain a = b + scalar*c ; d = a*a + b in one pass; a_out may be 0 when
+ * the intermediate is eliminated (sarek/sarek/Sarek_fusion.ml:490-499). */
+SB200_API int sb200_chain_triad_square_f32(int dev, uint64_t stream, uint64_t d, uint64_t a_out, uint64_t b, uint64_t c, float scalar, int64_t n);
+
+/* default numeric mode for GEMM kernels launched through sb200_kernel_launch
+ * (also read once from the environment variable SAREK_B200_MODE=3xtf32|tf32) */
+SB200_API int sb200_set_mode(int mode);
+SB200_API int sb200_get_mode(int *mode);
+
+/* seeded synthetic data written on the device: kind 0 U[-1,1), 1 U[-0.1,0.1),
+ * 2 N(0,sigma); element i of the stream is a pure function of (seed, stream_id,
+ * first + i). */
+SB200_API int sb200_fill_f32(int dev, uint64_t stream, uint64_t dptr, int64_t n,
+                             uint64_t seed, uint64_t stream_id, int kind, double sigma, int64_t first);
+
+/* number of kernels this library has launched on this thread's behalf since
+ * load (monotonic; used by benchmarks to report launch counts) */
+SB200_API int sb200_launch_count(uint64_t *count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SB200_H */

@@ -1,0 +1,367 @@
+// gemm_tcgen05.cuh — fp32 GEMM for sm_100a on tcgen05 tensor cores.
+//
+//   D[M x N] = act(alpha * A[M x K] . B[K x N] + beta * C + bias[col])
+//
+// replaces the matrix_mul and matrix_mul_tiled kernels of the reference
+// (benchmarks/bench_matrix_mul.ml:55-73, benchmarks/bench_matrix_mul_tiled.ml:55-94),
+// with the epilogue fused into the accumulator read-out so the product never
+// makes a round trip through HBM.
+//
+// Two stages:
+//  1. operand preparation (prep_a_kernel / prep_b_kernel): A and B are split
+//     into TF32-exact panels  hi = rna_tf32(x),  lo = rna_tf32(x - hi)  (lo only
+//     in 3xTF32 mode).  B is transposed on the way so both panels are K-major,
+//     and K is zero-padded to a multiple of 32 so every TMA box starts on a
+//     128-byte boundary whatever K is.
+//  2. gemm_tf32_kernel: a persistent, warp-specialised kernel, one block per
+//     SM.  Warp 0 streams 128x32 (A) and 256x32 (B) fp32 tiles into a ring of
+//     shared-memory stages with TMA (128-byte swizzle, no cluster forms);
+//     warp 1 issues tcgen05.mma kind::tf32 128x256x8 into one of two 256-column
+//     fp32 accumulators in tensor memory; warps 2-5 read the finished
+//     accumulator back with tcgen05.ld, apply the epilogue and store D while
+//     the MMA warp already works on the next tile.
+//     3xTF32 mode issues  lo*hi + hi*lo + hi*hi  per k-step into the same
+//     accumulator (the lo*lo term, ~2^-22 relative, is dropped).
+//
+// Work per launch: 2*M*N*K useful flops (3x that in MMA flops in 3xTF32
+// mode); the bound is the tensor pipe.
+#pragma once
+#include "ptx_sm100.cuh"
+
+namespace sb200 {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BN = 256;
+constexpr int GEMM_BK = 32;      // floats per k-block = one 128-byte swizzle row
+constexpr int GEMM_UMMA_K = 8;   // floats per tcgen05.mma kind::tf32 (32 bytes)
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_GROUP_M = 16;  // tile rasterisation: bands of 16 row tiles
+constexpr uint32_t GEMM_A_BYTES = GEMM_BM * GEMM_BK * 4;  // 16 KiB
+constexpr uint32_t GEMM_B_BYTES = GEMM_BN * GEMM_BK * 4;  // 32 KiB
+constexpr uint32_t GEMM_TMEM_COLS = 512;                  // two 256-column accumulators
+constexpr uint32_t GEMM_EPI_BUF_BYTES = 4 * 32 * 33 * 4;  // per-warp 32x33 transpose tiles
+constexpr uint32_t GEMM_CTRL_BYTES = 256;
+
+template <int MODE>
+struct GemmCfg {
+  static constexpr int kOperands = (MODE == 3) ? 2 : 1;  // hi (+ lo)
+  static constexpr int kStages = (MODE == 3) ? 2 : 4;
+  static constexpr uint32_t kStageBytes = kOperands * (GEMM_A_BYTES + GEMM_B_BYTES);
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + GEMM_EPI_BUF_BYTES + GEMM_CTRL_BYTES + 1024;
+};
+
+struct GemmParams {
+  int M, N;
+  int num_k_blocks;  // padded K / 32
+  int tiles_m, tiles_n;
+  float* D;
+  long long ldd;
+  const float* C;  // may be null
+  long long ldc;
+  const float* bias;  // may be null
+  float alpha, beta;
+  int act;      // 0 none, 1 relu
+  int* status;  // device word, set non-zero when a bounded wait expired
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int band_tiles = GEMM_GROUP_M * tiles_n;
+  const int band = tile / band_tiles;
+  const int within = tile - band * band_tiles;
+  const int first_m = band * GEMM_GROUP_M;
+  const int band_m = min(GEMM_GROUP_M, tiles_m - first_m);
+  tm = first_m + within % band_m;
+  tn = within / band_m;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_b_hi,
+                 const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
+                 const GemmParams p) {
+  using Cfg = GemmCfg<MODE>;
+  constexpr int STAGES = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment is what the 128-byte swizzle pattern is anchored to
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_base = smem;
+  float* epi_buf = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes + GEMM_EPI_BUF_BYTES);
+  // bars[0..STAGES) full, [STAGES..2*STAGES) empty, then tmem_full[2], tmem_empty[2]
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;
+  uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a_hi);
+    tma_prefetch_desc(&map_b_hi);
+    if (MODE == 3) {
+      tma_prefetch_desc(&map_a_lo);
+      tma_prefetch_desc(&map_b_lo);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), GEMM_TMEM_COLS);
+    tmem_relinquish();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * GEMM_BM, n0 = tn * GEMM_BN;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
+            atomicCAS(p.status, 0, 0x100 | stage);
+            ok = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(&full_bar[stage]);
+          uint8_t* sp = stage_base + stage * Cfg::kStageBytes;
+          mbar_arrive_expect_tx(bar, Cfg::kStageBytes);
+          tma_load_2d(smem_u32(sp), &map_a_hi, bar, kb * GEMM_BK, m0);
+          tma_load_2d(smem_u32(sp + GEMM_A_BYTES), &map_b_hi, bar, kb * GEMM_BK, n0);
+          if (MODE == 3) {
+            tma_load_2d(smem_u32(sp + GEMM_A_BYTES + GEMM_B_BYTES), &map_a_lo, bar, kb * GEMM_BK, m0);
+            tma_load_2d(smem_u32(sp + 2 * GEMM_A_BYTES + GEMM_B_BYTES), &map_b_lo, bar, kb * GEMM_BK, n0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Give loads that are still in flight a bounded chance to land before
+        // the block retires: a stage whose load was issued completes its
+        // full barrier regardless of the consumer.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(GEMM_BM, GEMM_BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        const int acc = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        if (!mbar_wait_bounded(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) {
+          atomicCAS(p.status, 0, 0x200 | acc);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * GEMM_BN;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!mbar_wait_bounded(smem_u32(&full_bar[stage]), phase, abort_flag)) {
+            atomicCAS(p.status, 0, 0x300 | stage);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa_hi = smem_u32(stage_base + stage * Cfg::kStageBytes);
+          const uint32_t sb_hi = sa_hi + GEMM_A_BYTES;
+          const uint32_t sa_lo = sb_hi + GEMM_B_BYTES;
+          const uint32_t sb_lo = sa_lo + GEMM_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
+            const uint32_t koff = k * GEMM_UMMA_K * 4;  // 32 bytes along K inside the swizzle row
+            const uint64_t da_hi = umma_desc_k_sw128(sa_hi + koff);
+            const uint64_t db_hi = umma_desc_k_sw128(sb_hi + koff);
+            const uint32_t first = (kb | k) ? 1u : 0u;
+            if (MODE == 3) {
+              const uint64_t da_lo = umma_desc_k_sw128(sa_lo + koff);
+              const uint64_t db_lo = umma_desc_k_sw128(sb_lo + koff);
+              umma_tf32(tmem_d, da_lo, db_hi, idesc, first);
+              umma_tf32(tmem_d, da_hi, db_lo, idesc, 1u);
+              umma_tf32(tmem_d, da_hi, db_hi, idesc, 1u);
+            } else {
+              umma_tf32(tmem_d, da_hi, db_hi, idesc, first);
+            }
+          }
+          umma_commit(smem_u32(&empty_bar[stage]));  // stage is free once these MMAs retire
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(smem_u32(&tmem_full_bar[acc]));
+      }
+    }
+    __syncwarp();
+  } else {
+    // --------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, 32*quarter+32)
+    float* tbuf = epi_buf + (warp - 2) * (32 * 33);
+    int local_tile = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      const int acc = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int row0 = tm * GEMM_BM + quarter * 32;
+      const int n0 = tn * GEMM_BN;
+      if (!mbar_wait_bounded(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag)) {
+        if (lane == 0) atomicCAS(p.status, 0, 0x400 | acc);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int rows_here = min(32, p.M - row0);  // may be <= 0 for a ragged last tile
+#pragma unroll 1
+      for (int chunk = 0; chunk < GEMM_BN / 32; ++chunk) {
+        const int col = n0 + chunk * 32 + lane;
+        if (n0 + chunk * 32 >= p.N) break;  // warp-uniform
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * GEMM_BN + chunk * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) tbuf[lane * 33 + j] = __uint_as_float(v[j]);
+        __syncwarp();
+        if (col < p.N) {
+          const float bias_v = p.bias ? p.bias[col] : 0.0f;
+          for (int rr = 0; rr < rows_here; ++rr) {
+            const long long row = row0 + rr;
+            float x = p.alpha * tbuf[rr * 33 + lane];
+            if (p.C) x = fmaf(p.beta, p.C[row * p.ldc + col], x);
+            x += bias_v;
+            if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
+            p.D[row * p.ldd + col] = x;
+          }
+        }
+        __syncwarp();
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+    }
+    __syncwarp();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, GEMM_TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------
+// Operand preparation
+// ------------------------------------------------------------------------
+
+// A[M x K] (row stride lda) -> hi[M x Kp] (and lo[M x Kp]), Kp = K rounded up
+// to 32, columns K..Kp zero.  One thread per 4 consecutive k.
+template <int MODE>
+__global__ void prep_a_kernel(const float* __restrict__ A, long long lda, float* __restrict__ hi,
+                              float* __restrict__ lo, int M, int K, int Kp, int vec_ok) {
+  const long long quads_per_row = Kp >> 2;
+  const long long total = static_cast<long long>(M) * quads_per_row;
+  for (long long q = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; q < total;
+       q += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = q / quads_per_row;
+    const int k = static_cast<int>(q - row * quads_per_row) << 2;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* src = A + row * lda + k;
+    if (vec_ok && k + 3 < K) {
+      x = *reinterpret_cast<const float4*>(src);
+    } else {
+      if (k < K) x.x = src[0];
+      if (k + 1 < K) x.y = src[1];
+      if (k + 2 < K) x.z = src[2];
+      if (k + 3 < K) x.w = src[3];
+    }
+    float4 h = make_float4(tf32_rna(x.x), tf32_rna(x.y), tf32_rna(x.z), tf32_rna(x.w));
+    *reinterpret_cast<float4*>(hi + row * Kp + k) = h;
+    if (MODE == 3) {
+      float4 l = make_float4(tf32_rna(x.x - h.x), tf32_rna(x.y - h.y), tf32_rna(x.z - h.z), tf32_rna(x.w - h.w));
+      *reinterpret_cast<float4*>(lo + row * Kp + k) = l;
+    }
+  }
+}
+
+// B[K x N] (row stride ldb) -> hi[N x Kp] (and lo[N x Kp]): 32x32 tiles
+// transposed through shared memory; block (32, 8); 1-D grid over
+// (Kp/32) * ceil(N/32) tiles.
+template <int MODE>
+__global__ void prep_b_kernel(const float* __restrict__ B, long long ldb, float* __restrict__ hi,
+                              float* __restrict__ lo, int K, int N, int Kp) {
+  __shared__ float tile[32][33];
+  const long long k_tiles = Kp >> 5;
+  const long long n_tiles = (N + 31) >> 5;
+  const long long total = k_tiles * n_tiles;
+  for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+    // n varies fastest so consecutive blocks read consecutive 128-byte runs of a B row
+    const long long kt = t / n_tiles;
+    const int n0 = static_cast<int>(t - kt * n_tiles) << 5;
+    const int k0 = static_cast<int>(kt) << 5;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      const int k = k0 + threadIdx.y + j, n = n0 + threadIdx.x;
+      tile[threadIdx.y + j][threadIdx.x] = (k < K && n < N) ? B[static_cast<long long>(k) * ldb + n] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      const int n = n0 + threadIdx.y + j, k = k0 + threadIdx.x;
+      if (n < N) {
+        const float x = tile[threadIdx.x][threadIdx.y + j];
+        const float h = tf32_rna(x);
+        hi[static_cast<long long>(n) * Kp + k] = h;
+        if (MODE == 3) lo[static_cast<long long>(n) * Kp + k] = tf32_rna(x - h);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Degenerate product (K == 0): D = act(beta*C + bias).
+__global__ void gemm_k0_kernel(GemmParams p) {
+  const long long total = static_cast<long long>(p.M) * p.N;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / p.N;
+    const int col = static_cast<int>(i - row * p.N);
+    float x = 0.0f;
+    if (p.C) x = fmaf(p.beta, p.C[row * p.ldc + col], x);
+    if (p.bias) x += p.bias[col];
+    if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
+    p.D[row * p.ldd + col] = x;
+  }
+}
+
+}  // namespace sb200

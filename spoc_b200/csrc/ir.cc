@@ -1,0 +1,918 @@
+// ir.cc — parser for the S-expression form of Sarek kernel IR and the
+// structural recogniser that maps a kernel onto this backend's operators.
+// The shapes matched are the ones the reference's PPX lowers the benchmark
+// kernels to (sarek/ppx/Sarek_lower_ir.ml:274-526,577-702).
+#include "ir.hpp"
+
+#include <cmath>
+#include <cstdlib>
+#include <functional>
+#include <map>
+#include <set>
+#include <sstream>
+
+#include "../../include/sb200.h"
+
+namespace sb200 {
+
+// ------------------------------------------------------------------ parser
+namespace {
+struct Parser {
+  const std::string& t;
+  size_t i = 0;
+  std::string err;
+  explicit Parser(const std::string& text) : t(text) {}
+  void skip() {
+    while (i < t.size()) {
+      if (isspace(static_cast<unsigned char>(t[i]))) {
+        ++i;
+      } else if (t[i] == ';') {
+        while (i < t.size() && t[i] != '\n') ++i;
+      } else {
+        break;
+      }
+    }
+  }
+  bool parse(Sx* out, int depth) {
+    skip();
+    if (i >= t.size()) {
+      err = "unexpected end of IR text";
+      return false;
+    }
+    if (depth > 512) {
+      err = "IR nesting deeper than 512";
+      return false;
+    }
+    if (t[i] == '(') {
+      ++i;
+      out->atom = false;
+      for (;;) {
+        skip();
+        if (i >= t.size()) {
+          err = "unbalanced '(' in IR text";
+          return false;
+        }
+        if (t[i] == ')') {
+          ++i;
+          return true;
+        }
+        Sx kid;
+        if (!parse(&kid, depth + 1)) return false;
+        out->kids.push_back(std::move(kid));
+      }
+    }
+    if (t[i] == ')') {
+      err = "unexpected ')' in IR text";
+      return false;
+    }
+    out->atom = true;
+    if (t[i] == '"') {
+      size_t j = i + 1;
+      std::string s;
+      while (j < t.size() && t[j] != '"') {
+        if (t[j] == '\\' && j + 1 < t.size()) ++j;
+        s.push_back(t[j++]);
+      }
+      if (j >= t.size()) {
+        err = "unterminated string in IR text";
+        return false;
+      }
+      out->s = s;
+      i = j + 1;
+      return true;
+    }
+    size_t j = i;
+    while (j < t.size() && !isspace(static_cast<unsigned char>(t[j])) && t[j] != '(' && t[j] != ')') ++j;
+    out->s = t.substr(i, j - i);
+    i = j;
+    return true;
+  }
+};
+}  // namespace
+
+bool sx_parse(const std::string& text, Sx* out, std::string* err) {
+  Parser p(text);
+  Sx x;
+  if (!p.parse(&x, 0)) {
+    if (err) *err = p.err;
+    return false;
+  }
+  p.skip();
+  if (p.i != text.size()) {
+    if (err) *err = "trailing characters after the kernel form";
+    return false;
+  }
+  *out = std::move(x);
+  return true;
+}
+
+std::string sx_print(const Sx& x) {
+  if (x.atom) {
+    bool plain = !x.s.empty();
+    for (char c : x.s)
+      if (isspace(static_cast<unsigned char>(c)) || c == '(' || c == ')' || c == '"' || c == ';') plain = false;
+    if (plain) return x.s;
+    std::string o = "\"";
+    for (char c : x.s) {
+      if (c == '"' || c == '\\') o.push_back('\\');
+      o.push_back(c);
+    }
+    return o + "\"";
+  }
+  std::string o = "(";
+  for (size_t i = 0; i < x.kids.size(); ++i) {
+    if (i) o.push_back(' ');
+    o += sx_print(x.kids[i]);
+  }
+  return o + ")";
+}
+
+bool sx_equal(const Sx& a, const Sx& b) {
+  if (a.atom != b.atom) return false;
+  if (a.atom) return a.s == b.s;
+  if (a.kids.size() != b.kids.size()) return false;
+  for (size_t i = 0; i < a.kids.size(); ++i)
+    if (!sx_equal(a.kids[i], b.kids[i])) return false;
+  return true;
+}
+
+// --------------------------------------------------------------- recogniser
+namespace {
+
+using Env = std::map<std::string, Sx>;  // var id -> inlined defining expression
+
+// Replace every (evar NAME ID) whose ID is let-bound by its definition.
+Sx inline_expr(const Sx& e, const Env& env) {
+  if (e.atom) return e;
+  if (e.is("evar") && e.size() >= 3) {
+    auto it = env.find(e[2].s);
+    if (it != env.end()) return it->second;
+    return e;
+  }
+  Sx o;
+  o.kids.reserve(e.kids.size());
+  for (const Sx& k : e.kids) o.kids.push_back(inline_expr(k, env));
+  return o;
+}
+
+bool is_binop(const Sx& e, const char* op, const Sx** l, const Sx** r) {
+  if (!e.is("binop") || e.size() != 4 || !e[1].atom || e[1].s != op) return false;
+  *l = &e[2];
+  *r = &e[3];
+  return true;
+}
+
+// Commutative binop: calls f(l, r) and f(r, l) until one succeeds.
+bool is_comm(const Sx& e, const char* op, const std::function<bool(const Sx&, const Sx&)>& f) {
+  const Sx *l, *r;
+  if (!is_binop(e, op, &l, &r)) return false;
+  return f(*l, *r) || f(*r, *l);
+}
+
+bool is_intrinsic(const Sx& e, const char* name) {
+  return e.is("intrinsic") && e.size() >= 3 && e[2].atom && e[2].s == name;
+}
+
+bool contains_intrinsic(const Sx& e, const char* name) {
+  if (e.atom) return false;
+  if (is_intrinsic(e, name)) return true;
+  for (const Sx& k : e.kids)
+    if (contains_intrinsic(k, name)) return true;
+  return false;
+}
+
+// global x index: global_thread_id / global_idx_x, or thread_idx_x + block_dim_x*block_idx_x
+bool is_global_x(const Sx& e) {
+  if (is_intrinsic(e, "global_thread_id") || is_intrinsic(e, "global_idx_x")) return true;
+  return is_comm(e, "add", [](const Sx& a, const Sx& b) {
+    return is_intrinsic(a, "thread_idx_x") && is_comm(b, "mul", [](const Sx& c, const Sx& d) {
+             return is_intrinsic(c, "block_dim_x") && is_intrinsic(d, "block_idx_x");
+           });
+  });
+}
+bool is_global_y(const Sx& e) {
+  if (is_intrinsic(e, "global_idx_y")) return true;
+  return is_comm(e, "add", [](const Sx& a, const Sx& b) {
+    return is_intrinsic(a, "thread_idx_y") && is_comm(b, "mul", [](const Sx& c, const Sx& d) {
+             return is_intrinsic(c, "block_dim_y") && is_intrinsic(d, "block_idx_y");
+           });
+  });
+}
+
+struct Ctx {
+  KernelPlan* plan;
+  std::string why;  // first reason a match failed, for the error message
+  int param_index(const std::string& name) const {
+    for (size_t i = 0; i < plan->params.size(); ++i)
+      if (plan->params[i].name == name) return static_cast<int>(i);
+    return -1;
+  }
+  // (evar NAME ID) naming a scalar parameter of element type elt (or any when elt == nullptr)
+  int scalar_param(const Sx& e, const char* elt) const {
+    if (!e.is("evar") || e.size() < 3) return -1;
+    for (size_t i = 0; i < plan->params.size(); ++i) {
+      const ParamInfo& p = plan->params[i];
+      if (!p.is_vec && p.name == e[1].s && std::to_string(p.id) == e[2].s && (!elt || p.elt == elt))
+        return static_cast<int>(i);
+    }
+    return -1;
+  }
+  int vec_param(const std::string& name, const char* elt) const {
+    int i = param_index(name);
+    if (i < 0 || !plan->params[i].is_vec) return -1;
+    if (elt && plan->params[i].elt != elt) return -1;
+    return i;
+  }
+  // (read ARR IDX) of a float32 vector parameter
+  bool is_read(const Sx& e, int* param, const Sx** idx) const {
+    if (!e.is("read") || e.size() != 3 || !e[1].atom) return false;
+    int p = vec_param(e[1].s, "f32");
+    if (p < 0) return false;
+    *param = p;
+    *idx = &e[2];
+    return true;
+  }
+  bool is_coef(const Sx& e, Coef* c) const {
+    if (e.is("const") && e.size() == 3 && (e[1].s == "f32" || e[1].s == "f64")) {
+      c->param = -1;
+      c->value = strtod(e[2].s.c_str(), nullptr);
+      return true;
+    }
+    int p = scalar_param(e, "f32");
+    if (p >= 0) {
+      c->param = p;
+      return true;
+    }
+    return false;
+  }
+};
+
+bool is_const_i32(const Sx& e, long long v) {
+  return e.is("const") && e.size() == 3 && (e[1].s == "i32" || e[1].s == "i64") && atoll(e[2].s.c_str()) == v;
+}
+bool is_const_f_zero(const Sx& e) {
+  return e.is("const") && e.size() == 3 && (e[1].s == "f32" || e[1].s == "f64") && strtod(e[2].s.c_str(), nullptr) == 0.0;
+}
+
+// Peel lets / blocks / single-statement seqs / pragmas / else-less ifs off the
+// front of a body.  Shared-array lets are recorded, not inlined.
+struct Peeled {
+  Env env;
+  std::set<std::string> shared;
+  std::vector<Sx> guards;
+  const Sx* core = nullptr;
+};
+
+bool is_shared_let(const Sx& s) {
+  return s.is("let") && s.size() == 6 && s[4].is("arraycreate");
+}
+
+void peel(const Sx& stmt, Peeled* p, bool through_guards) {
+  const Sx* s = &stmt;
+  for (;;) {
+    if (s->is("let") && s->size() == 6) {
+      if (is_shared_let(*s)) {
+        p->shared.insert((*s)[1].s);
+      } else {
+        p->env[(*s)[2].s] = inline_expr((*s)[4], p->env);
+      }
+      s = &(*s)[5];
+    } else if (s->is("block") && s->size() == 2) {
+      s = &(*s)[1];
+    } else if (s->is("pragma") && s->size() == 3) {
+      s = &(*s)[2];
+    } else if (s->is("seq")) {
+      const Sx* only = nullptr;
+      int count = 0;
+      for (size_t i = 1; i < s->size(); ++i)
+        if (!(*s)[i].is("empty")) {
+          only = &(*s)[i];
+          ++count;
+        }
+      if (count != 1) break;
+      s = only;
+    } else if (through_guards && s->is("sif") && s->size() == 3) {
+      p->guards.push_back(inline_expr((*s)[1], p->env));
+      s = &(*s)[2];
+    } else {
+      break;
+    }
+  }
+  p->core = s;
+}
+
+std::vector<const Sx*> seq_items(const Sx& s) {
+  std::vector<const Sx*> v;
+  if (s.is("seq")) {
+    for (size_t i = 1; i < s.size(); ++i) {
+      if (s[i].is("empty")) continue;
+      if (s[i].is("seq")) {
+        for (const Sx* k : seq_items(s[i])) v.push_back(k);
+      } else {
+        v.push_back(&s[i]);
+      }
+    }
+  } else if (!s.is("empty")) {
+    v.push_back(&s);
+  }
+  return v;
+}
+
+// ------------------------------------------------------------------- maps
+
+// Substitute reads of arrays written earlier in the same straight-line body.
+Sx subst_reads(const Sx& e, const std::map<std::string, Sx>& written, const Sx& idx) {
+  if (e.atom) return e;
+  if (e.is("read") && e.size() == 3 && e[1].atom) {
+    auto it = written.find(e[1].s);
+    if (it != written.end() && sx_equal(e[2], idx)) return it->second;
+  }
+  Sx o;
+  for (const Sx& k : e.kids) o.kids.push_back(subst_reads(k, written, idx));
+  return o;
+}
+
+struct Triad {
+  int b, c;
+  Coef s;
+};
+
+bool match_triad(const Ctx& cx, const Sx& e, const Sx& idx, Triad* t) {
+  return is_comm(e, "add", [&](const Sx& l, const Sx& r) {
+    const Sx* i0;
+    int b;
+    if (!cx.is_read(l, &b, &i0) || !sx_equal(*i0, idx)) return false;
+    return is_comm(r, "mul", [&](const Sx& m0, const Sx& m1) {
+      const Sx* i1;
+      int c;
+      Coef s;
+      if (!cx.is_read(m0, &c, &i1) || !sx_equal(*i1, idx) || !cx.is_coef(m1, &s)) return false;
+      t->b = b;
+      t->c = c;
+      t->s = s;
+      return true;
+    });
+  });
+}
+
+bool match_map(Ctx& cx, const Sx& body) {
+  KernelPlan& plan = *cx.plan;
+  Peeled pl;
+  peel(body, &pl, true);
+  if (!pl.shared.empty()) {
+    cx.why = "uses shared arrays";
+    return false;
+  }
+  std::vector<const Sx*> items = seq_items(*pl.core);
+  if (items.empty() || items.size() > 2) {
+    cx.why = "body is not one or two element stores";
+    return false;
+  }
+  MapPlan mp;
+  Sx idx;
+  bool have_idx = false;
+  std::map<std::string, Sx> written;
+  std::vector<std::pair<int, Sx>> stores;  // (out param, inlined+substituted rhs)
+  for (const Sx* it : items) {
+    if (!it->is("assign") || it->size() != 3 || !(*it)[1].is("elem") || (*it)[1].size() != 3) {
+      cx.why = "statement is not an array element store";
+      return false;
+    }
+    const Sx& lv = (*it)[1];
+    Sx this_idx = inline_expr(lv[2], pl.env);
+    if (!have_idx) {
+      idx = this_idx;
+      have_idx = true;
+    } else if (!sx_equal(idx, this_idx)) {
+      cx.why = "stores use different indices";
+      return false;
+    }
+    int out = cx.vec_param(lv[1].s, "f32");
+    if (out < 0) {
+      cx.why = "store target is not a float32 vector parameter";
+      return false;
+    }
+    Sx rhs = subst_reads(inline_expr((*it)[2], pl.env), written, idx);
+    written[lv[1].s] = rhs;
+    stores.emplace_back(out, rhs);
+  }
+  if (is_global_x(idx)) {
+    mp.index_kind = IDX_GLOBAL;
+  } else if (is_intrinsic(idx, "thread_idx_x")) {
+    mp.index_kind = IDX_THREAD_X;
+  } else {
+    cx.why = "element index is not the global or block-local x thread index";
+    return false;
+  }
+  if (pl.guards.size() > 1) {
+    cx.why = "more than one guard";
+    return false;
+  }
+  if (pl.guards.size() == 1) {
+    const Sx *l, *r;
+    if (!is_binop(pl.guards[0], "lt", &l, &r) || !sx_equal(*l, idx) || (mp.n_param = cx.scalar_param(*r, "i32")) < 0) {
+      cx.why = "guard is not `index < n` with n an int32 parameter";
+      return false;
+    }
+  }
+  // classify the final store (and the optional kept intermediate)
+  const Sx& rhs = stores.back().second;
+  mp.out0 = stores.back().first;
+  Triad t;
+  bool ok = false;
+  // vector_add
+  ok = is_comm(rhs, "add", [&](const Sx& l, const Sx& r) {
+    const Sx *i0, *i1;
+    int a, b;
+    if (!cx.is_read(l, &a, &i0) || !cx.is_read(r, &b, &i1)) return false;
+    if (!sx_equal(*i0, idx) || !sx_equal(*i1, idx)) return false;
+    mp.op = OP_VECADD;
+    mp.in0 = a;
+    mp.in1 = b;
+    return true;
+  });
+  if (ok && stores.size() == 2) ok = false;
+  if (!ok && stores.size() == 1 && match_triad(cx, rhs, idx, &t)) {
+    mp.op = OP_TRIAD;
+    mp.in0 = t.b;
+    mp.in1 = t.c;
+    mp.scalar = t.s;
+    ok = true;
+  }
+  if (!ok) {
+    // d = T*T + b with T = b + c*s
+    ok = is_comm(rhs, "add", [&](const Sx& l, const Sx& r) {
+      const Sx *m0, *m1, *i0;
+      int b;
+      if (!is_binop(l, "mul", &m0, &m1) || !sx_equal(*m0, *m1)) return false;
+      if (!match_triad(cx, *m0, idx, &t)) return false;
+      if (!cx.is_read(r, &b, &i0) || !sx_equal(*i0, idx) || b != t.b) return false;
+      mp.op = OP_CHAIN;
+      mp.in0 = t.b;
+      mp.in1 = t.c;
+      mp.scalar = t.s;
+      return true;
+    });
+    if (ok && stores.size() == 2) {
+      Triad t2;
+      if (match_triad(cx, stores[0].second, idx, &t2) && t2.b == t.b && t2.c == t.c && t2.s.param == t.s.param &&
+          t2.s.value == t.s.value) {
+        mp.op = OP_CHAIN_KEEP;
+        mp.out1 = stores[0].first;
+      } else {
+        ok = false;
+      }
+    }
+  }
+  if (!ok) {
+    cx.why = "element expression is not one of: a+b, b+c*s, (b+c*s)^2+b";
+    return false;
+  }
+  if (mp.out0 == mp.out1) {
+    cx.why = "both stores target the same vector";
+    return false;
+  }
+  plan.kind = KIND_MAP;
+  plan.map = mp;
+  static const char* names[] = {"vector_add", "stream_triad", "triad_square_chain", "triad_square_chain(keep)"};
+  plan.description = std::string("map:") + names[mp.op] + (mp.n_param >= 0 ? " guarded" : " unguarded") +
+                     (mp.index_kind == IDX_GLOBAL ? " idx=global_x" : " idx=thread_idx_x");
+  return true;
+}
+
+// ------------------------------------------------------------------- GEMM
+
+// relu wrapper: (if (binop gt X (const f32 0)) X (const f32 0))
+const Sx* strip_relu(const Sx& e, int* act) {
+  *act = 0;
+  if (e.is("if") && e.size() == 4) {
+    const Sx *l, *r;
+    if (is_binop(e[1], "gt", &l, &r) && is_const_f_zero(*r) && sx_equal(*l, e[2]) && is_const_f_zero(e[3])) {
+      *act = 1;
+      return &e[2];
+    }
+  }
+  return &e;
+}
+
+void flatten_add(const Sx& e, std::vector<const Sx*>* terms) {
+  const Sx *l, *r;
+  if (is_binop(e, "add", &l, &r)) {
+    flatten_add(*l, terms);
+    flatten_add(*r, terms);
+  } else {
+    terms->push_back(&e);
+  }
+}
+
+// EPI(acc) = act(alpha*acc + beta*C[row*n+col] + bias[col]); every read index
+// is compared after let-inlining.
+bool match_epilogue(Ctx& cx, const Sx& e_in, const std::string& acc_id, const Sx& out_idx, const Sx& col, GemmPlan* g) {
+  int act;
+  const Sx* e = strip_relu(e_in, &act);
+  g->act = act;
+  g->alpha.param = -1;
+  g->alpha.value = 1.0;
+  g->beta.param = -1;
+  g->beta.value = 0.0;
+  std::vector<const Sx*> terms;
+  flatten_add(*e, &terms);
+  bool have_acc = false;
+  auto is_acc = [&](const Sx& x) { return x.is("evar") && x.size() >= 3 && x[2].s == acc_id; };
+  for (const Sx* t : terms) {
+    const Sx* idx;
+    int prm;
+    Coef cf;
+    if (is_acc(*t)) {
+      if (have_acc) return false;
+      have_acc = true;
+    } else if (is_comm(*t, "mul", [&](const Sx& a, const Sx& b) { return cx.is_coef(a, &cf) && is_acc(b); })) {
+      if (have_acc) return false;
+      have_acc = true;
+      g->alpha = cf;
+    } else if (cx.is_read(*t, &prm, &idx)) {
+      if (sx_equal(*idx, out_idx) && g->c < 0) {
+        g->c = prm;
+        g->beta.param = -1;
+        g->beta.value = 1.0;
+      } else if (sx_equal(*idx, col) && g->bias < 0) {
+        g->bias = prm;
+      } else {
+        return false;
+      }
+    } else if (is_comm(*t, "mul", [&](const Sx& a, const Sx& b) {
+                 return cx.is_coef(a, &cf) && cx.is_read(b, &prm, &idx) && sx_equal(*idx, out_idx);
+               })) {
+      if (g->c >= 0) return false;
+      g->c = prm;
+      g->beta = cf;
+    } else {
+      return false;
+    }
+  }
+  return have_acc;
+}
+
+bool match_guard_mn(Ctx& cx, const Sx& guard, const Sx& row, const Sx& col, GemmPlan* g) {
+  return is_comm(guard, "and", [&](const Sx& a, const Sx& b) {
+    const Sx *l, *r;
+    if (!is_binop(a, "lt", &l, &r) || !sx_equal(*l, row)) return false;
+    int m = cx.scalar_param(*r, "i32");
+    if (!is_binop(b, "lt", &l, &r) || !sx_equal(*l, col)) return false;
+    int n = cx.scalar_param(*r, "i32");
+    if (m < 0 || n < 0) return false;
+    g->m = m;
+    g->n = n;
+    return true;
+  });
+}
+
+// acc := acc + X*Y ; returns X and Y (not inlined)
+bool match_accumulate(const Sx& s, std::string* acc_id, const Sx** x, const Sx** y) {
+  if (!s.is("assign") || s.size() != 3 || !s[1].is("lvar") || s[1].size() < 3) return false;
+  const std::string id = s[1][2].s;
+  const Sx& rhs = s[2];
+  bool ok = is_comm(rhs, "add", [&](const Sx& a, const Sx& b) {
+    const Sx *m0, *m1;
+    if (!a.is("evar") || a.size() < 3 || a[2].s != id) return false;
+    if (!is_binop(b, "mul", &m0, &m1)) return false;
+    *x = m0;
+    *y = m1;
+    return true;
+  });
+  if (ok) *acc_id = id;
+  return ok;
+}
+
+// upper bound `k - 1` of an inclusive upto loop starting at 0
+bool loop_0_to_km1(const Sx& f, const Env& env, Sx* k_expr) {
+  if (!f.is("for") || f.size() != 7 || f[5].s != "upto") return false;
+  if (!is_const_i32(inline_expr(f[3], env), 0)) return false;
+  Sx hi = inline_expr(f[4], env);
+  const Sx *l, *r;
+  if (!is_binop(hi, "sub", &l, &r) || !is_const_i32(*r, 1)) return false;
+  *k_expr = *l;
+  return true;
+}
+
+bool match_gemm_naive(Ctx& cx, const Sx& body) {
+  KernelPlan& plan = *cx.plan;
+  Peeled pl;
+  peel(body, &pl, true);
+  if (!pl.shared.empty() || pl.guards.size() != 1) return false;
+  const Sx& core = *pl.core;
+  if (!core.is("letmut") || core.size() != 6 || !is_const_f_zero(inline_expr(core[4], pl.env))) return false;
+  const std::string acc_id = core[2].s;
+  std::vector<const Sx*> items = seq_items(core[5]);
+  if (items.size() != 2) return false;
+  const Sx& loop = *items[0];
+  Sx k_expr;
+  if (!loop_0_to_km1(loop, pl.env, &k_expr)) return false;
+  GemmPlan g;
+  g.k = cx.scalar_param(k_expr, "i32");
+  if (g.k < 0) return false;
+  const std::string loop_id = loop[2].s;
+  Peeled lp;
+  lp.env = pl.env;
+  peel(loop[6], &lp, false);
+  std::string aid;
+  const Sx *x, *y;
+  if (!match_accumulate(*lp.core, &aid, &x, &y) || aid != acc_id) return false;
+  Sx xa = inline_expr(*x, lp.env), yb = inline_expr(*y, lp.env);
+  const Sx *ia, *ib;
+  if (!cx.is_read(xa, &g.a, &ia) || !cx.is_read(yb, &g.b, &ib)) return false;
+  auto is_loop_var = [&](const Sx& e) { return e.is("evar") && e.size() >= 3 && e[2].s == loop_id; };
+  // A index: row*k + i ; B index: i*n + col
+  Sx row, col;
+  int kk = -1, nn = -1;
+  bool ok_a = is_comm(*ia, "add", [&](const Sx& p, const Sx& q) {
+    return is_loop_var(q) && is_comm(p, "mul", [&](const Sx& r, const Sx& s) {
+             int kp = cx.scalar_param(s, "i32");
+             if (kp < 0) return false;
+             kk = kp;
+             row = r;
+             return true;
+           });
+  });
+  bool ok_b = is_comm(*ib, "add", [&](const Sx& p, const Sx& q) {
+    return is_comm(p, "mul", [&](const Sx& r, const Sx& s) {
+             int np = cx.scalar_param(s, "i32");
+             if (!is_loop_var(r) || np < 0) return false;
+             nn = np;
+             col = q;
+             return true;
+           });
+  });
+  if (!ok_a || !ok_b || kk != g.k) {
+    cx.why = "operand indices are not a[row*k+i] and b[i*n+col]";
+    return false;
+  }
+  // row = tid / n, col = tid mod n
+  const Sx *l, *r;
+  if (!is_binop(row, "div", &l, &r) || !is_global_x(*l) || cx.scalar_param(*r, "i32") != nn) return false;
+  if (!is_binop(col, "mod", &l, &r) || !is_global_x(*l) || cx.scalar_param(*r, "i32") != nn) return false;
+  if (!match_guard_mn(cx, pl.guards[0], row, col, &g) || g.n != nn) {
+    cx.why = "guard is not row < m && col < n";
+    return false;
+  }
+  // final store d[row*n+col] <- EPI(acc)
+  const Sx& st = *items[1];
+  if (!st.is("assign") || st.size() != 3 || !st[1].is("elem")) return false;
+  g.d = cx.vec_param(st[1][1].s, "f32");
+  Sx out_idx = inline_expr(st[1][2], pl.env);
+  bool ok_o = is_comm(out_idx, "add", [&](const Sx& p, const Sx& q) {
+    return sx_equal(q, col) && is_comm(p, "mul", [&](const Sx& rr, const Sx& ss) {
+             return sx_equal(rr, row) && cx.scalar_param(ss, "i32") == nn;
+           });
+  });
+  if (g.d < 0 || !ok_o) {
+    cx.why = "result is not stored at d[row*n+col]";
+    return false;
+  }
+  if (!match_epilogue(cx, inline_expr(st[2], pl.env), acc_id, out_idx, col, &g)) {
+    cx.why = "stored expression is not act(alpha*sum + beta*c[row*n+col] + bias[col])";
+    return false;
+  }
+  plan.kind = KIND_GEMM_NAIVE;
+  plan.gemm = g;
+  return true;
+}
+
+// Walk every statement under `s`, carrying the let environment.
+void walk(const Sx& s, Env env, const std::function<void(const Sx&, const Env&)>& f) {
+  if (s.atom) return;
+  f(s, env);
+  if (s.is("let") && s.size() == 6) {
+    if (!is_shared_let(s)) env[s[2].s] = inline_expr(s[4], env);
+    walk(s[5], env, f);
+  } else if (s.is("letmut") && s.size() == 6) {
+    walk(s[5], env, f);
+  } else if (s.is("seq")) {
+    for (size_t i = 1; i < s.size(); ++i) walk(s[i], env, f);
+  } else if (s.is("sif")) {
+    for (size_t i = 2; i < s.size(); ++i) walk(s[i], env, f);
+  } else if (s.is("for") && s.size() == 7) {
+    walk(s[6], env, f);
+  } else if (s.is("block") && s.size() == 2) {
+    walk(s[1], env, f);
+  } else if (s.is("pragma") && s.size() == 3) {
+    walk(s[2], env, f);
+  } else if (s.is("while") && s.size() == 3) {
+    walk(s[2], env, f);
+  }
+}
+
+bool match_gemm_tiled(Ctx& cx, const Sx& body) {
+  KernelPlan& plan = *cx.plan;
+  Peeled pl;
+  peel(body, &pl, false);
+  if (pl.shared.size() != 2) return false;
+  const Sx& core = *pl.core;
+  if (!core.is("letmut") || core.size() != 6 || !is_const_f_zero(inline_expr(core[4], pl.env))) return false;
+  const std::string acc_id = core[2].s;
+  std::vector<const Sx*> items = seq_items(core[5]);
+  if (items.size() != 2 || !items[0]->is("for")) return false;
+  GemmPlan g;
+  // facts gathered from the k-tile loop
+  std::string tile_a, tile_b;
+  int barriers = 0;
+  long long tile = 0;
+  struct Load {
+    std::string tile;
+    int param;
+    Sx idx;
+  };
+  std::vector<Load> loads;
+  bool bad = false;
+  walk(*items[0], pl.env, [&](const Sx& s, const Env& env) {
+    if (s.is("barrier")) ++barriers;
+    std::string aid;
+    const Sx *x, *y;
+    if (match_accumulate(s, &aid, &x, &y) && aid == acc_id) {
+      if (x->is("read") && y->is("read") && pl.shared.count((*x)[1].s) && pl.shared.count((*y)[1].s)) {
+        tile_a = (*x)[1].s;
+        tile_b = (*y)[1].s;
+      } else {
+        bad = true;
+      }
+    }
+    if (s.is("for") && s.size() == 7 && &s != items[0]) {
+      Sx hi = inline_expr(s[4], env);
+      const Sx *l, *r;
+      if (is_binop(hi, "sub", &l, &r) && l->is("const") && is_const_i32(*r, 1)) tile = atoll((*l)[2].s.c_str());
+    }
+    if (s.is("assign") && s.size() == 3 && s[1].is("elem") && pl.shared.count(s[1][1].s)) {
+      Sx rhs = inline_expr(s[2], env);
+      int prm;
+      const Sx* idx;
+      if (cx.is_read(rhs, &prm, &idx)) {
+        loads.push_back({s[1][1].s, prm, *idx});
+      } else if (!is_const_f_zero(rhs)) {
+        bad = true;
+      }
+    }
+  });
+  if (bad || tile_a.empty() || tile_a == tile_b || barriers < 2 || tile <= 0 || loads.size() != 2) {
+    cx.why = "k-tile loop is not load A tile / load B tile / accumulate with barriers";
+    return false;
+  }
+  // final guarded store
+  Peeled fin;
+  fin.env = pl.env;
+  peel(*items[1], &fin, true);
+  if (fin.guards.size() != 1 || !fin.core->is("assign") || !(*fin.core)[1].is("elem")) return false;
+  const Sx& st = *fin.core;
+  g.d = cx.vec_param(st[1][1].s, "f32");
+  Sx out_idx = inline_expr(st[1][2], fin.env);
+  Sx row, col;
+  int nn = -1;
+  bool ok_o = is_comm(out_idx, "add", [&](const Sx& p, const Sx& q) {
+    return is_comm(p, "mul", [&](const Sx& rr, const Sx& ss) {
+      int np = cx.scalar_param(ss, "i32");
+      if (np < 0) return false;
+      nn = np;
+      row = rr;
+      col = q;
+      return true;
+    });
+  });
+  if (g.d < 0 || !ok_o || !is_global_y(row) || !is_global_x(col)) {
+    cx.why = "result is not stored at c[row*n+col] with row/col the global y/x indices";
+    return false;
+  }
+  if (!match_guard_mn(cx, fin.guards[0], row, col, &g) || g.n != nn) return false;
+  for (const Load& ld : loads) {
+    if (ld.tile == tile_a) {
+      // a[row*k + a_col]
+      int kk = -1;
+      bool ok = is_comm(ld.idx, "add", [&](const Sx& p, const Sx&) {
+        return is_comm(p, "mul", [&](const Sx& rr, const Sx& ss) {
+          kk = cx.scalar_param(ss, "i32");
+          return sx_equal(rr, row) && kk >= 0;
+        });
+      });
+      if (!ok) return false;
+      g.a = ld.param;
+      g.k = kk;
+    } else if (ld.tile == tile_b) {
+      // b[b_row*n + col]
+      bool ok = is_comm(ld.idx, "add", [&](const Sx& p, const Sx& q) {
+        return sx_equal(q, col) && is_comm(p, "mul", [&](const Sx&, const Sx& ss) {
+                 return cx.scalar_param(ss, "i32") == nn;
+               });
+      });
+      if (!ok) return false;
+      g.b = ld.param;
+    }
+  }
+  if (g.a < 0 || g.b < 0 || g.k < 0) return false;
+  if (!match_epilogue(cx, inline_expr(st[2], fin.env), acc_id, out_idx, col, &g)) {
+    cx.why = "stored expression is not act(alpha*sum + beta*c[row*n+col] + bias[col])";
+    return false;
+  }
+  g.tile = static_cast<int>(tile);
+  plan.kind = KIND_GEMM_TILED;
+  plan.gemm = g;
+  return true;
+}
+
+std::string describe_gemm(const KernelPlan& p) {
+  const GemmPlan& g = p.gemm;
+  std::ostringstream o;
+  o << (p.kind == KIND_GEMM_TILED ? "gemm:tiled" : "gemm:naive") << " A=" << p.params[g.a].name
+    << " B=" << p.params[g.b].name << " D=" << p.params[g.d].name << " m=" << p.params[g.m].name
+    << " n=" << p.params[g.n].name << " k=" << p.params[g.k].name;
+  if (g.alpha.param >= 0)
+    o << " alpha=" << p.params[g.alpha.param].name;
+  else if (g.alpha.value != 1.0)
+    o << " alpha=" << g.alpha.value;
+  if (g.c >= 0) {
+    o << " C=" << p.params[g.c].name << " beta=";
+    if (g.beta.param >= 0)
+      o << p.params[g.beta.param].name;
+    else
+      o << g.beta.value;
+  }
+  if (g.bias >= 0) o << " bias=" << p.params[g.bias].name;
+  if (g.act == 1) o << " act=relu";
+  if (g.tile) o << " tile=" << g.tile;
+  return o.str();
+}
+
+bool has_unsupported_stmt(const Sx& s, std::string* what) {
+  if (s.atom) return false;
+  if (s.is("while") || s.is("return") || s.is("match") || s.is("native")) {
+    *what = s[0].s;
+    return true;
+  }
+  for (const Sx& k : s.kids)
+    if (has_unsupported_stmt(k, what)) return true;
+  return false;
+}
+
+}  // namespace
+
+bool parse_kernel_form(const std::string& text, Sx* root, KernelPlan* plan, const Sx** body, std::string* err) {
+  if (!sx_parse(text, root, err)) return false;
+  if (!root->is("kernel") || root->size() != 4 || !(*root)[1].atom || !(*root)[2].is("params") || !(*root)[3].is("body") ||
+      (*root)[3].size() != 2) {
+    *err = "expected (kernel NAME (params ...) (body STMT))";
+    return false;
+  }
+  plan->name = (*root)[1].s;
+  plan->params.clear();
+  const Sx& ps = (*root)[2];
+  for (size_t i = 1; i < ps.size(); ++i) {
+    const Sx& p = ps[i];
+    if (!(p.is("vec") || p.is("scalar")) || p.size() != 4 || !p[1].atom || !p[2].atom) {
+      *err = "malformed parameter: " + sx_print(p);
+      return false;
+    }
+    ParamInfo pi;
+    pi.name = p[1].s;
+    pi.id = atoi(p[2].s.c_str());
+    pi.is_vec = p.is("vec");
+    pi.elt = p[3].atom ? p[3].s : sx_print(p[3]);
+    plan->params.push_back(pi);
+  }
+  *body = &(*root)[3][1];
+  return true;
+}
+
+int ir_compile(const std::string& text, KernelPlan* plan, std::string* err) {
+  Sx root;
+  const Sx* body = nullptr;
+  std::string perr;
+  if (!parse_kernel_form(text, &root, plan, &body, &perr)) {
+    if (err) *err = perr;
+    return SB200_ERR_PARSE;
+  }
+  std::string what;
+  if (has_unsupported_stmt(*body, &what)) {
+    if (err) *err = "unsupported construct in kernel '" + plan->name + "': " + what;
+    return SB200_ERR_UNSUPPORTED;
+  }
+  Ctx cx{plan, ""};
+  std::string reasons;
+  if (match_map(cx, *body)) return 0;
+  reasons += "map: " + cx.why;
+  cx.why.clear();
+  if (match_gemm_naive(cx, *body)) {
+    plan->description = describe_gemm(*plan);
+    return 0;
+  }
+  reasons += "; naive gemm: " + (cx.why.empty() ? std::string("shape mismatch") : cx.why);
+  cx.why.clear();
+  if (match_gemm_tiled(cx, *body)) {
+    plan->description = describe_gemm(*plan);
+    return 0;
+  }
+  reasons += "; tiled gemm: " + (cx.why.empty() ? std::string("shape mismatch") : cx.why);
+  if (err)
+    *err = "unsupported construct in kernel '" + plan->name +
+           "': body is neither a GEMM nor a supported element-wise map (" + reasons + ")";
+  plan->kind = 0;
+  return SB200_ERR_UNSUPPORTED;
+}
+
+}  // namespace sb200

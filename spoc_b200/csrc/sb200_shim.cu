@@ -1,0 +1,961 @@
+// sb200_shim.cu — the C ABI of libsarek_b200.so (see include/sb200.h).
+//
+// Host side of the B200 backend: device/memory/stream/event plumbing in the
+// shape of sarek-cuda/Cuda_api.ml, kernel "compilation" (IR recognition) and
+// launch in the shape of sarek-cuda/Cuda_plugin.ml:174-210, and the direct
+// GEMM / map operators the recognised kernels dispatch to.  There is no CPU
+// execution path in this library: every operator launches CUDA kernels or
+// returns an error.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <atomic>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+#include "../../include/sb200.h"
+#include "gemm_tcgen05.cuh"
+#include "ir.hpp"
+#include "map_fused.cuh"
+
+using namespace sb200;
+
+namespace {
+
+constexpr int kMaxDevices = 16;
+constexpr int kVersion = 100;
+
+thread_local std::string g_err;
+std::atomic<uint64_t> g_launches{0};
+std::atomic<int> g_mode{0};  // 0 = not yet read from the environment
+
+int fail(int code, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  // clear the sticky-less error state so the next call starts clean
+  cudaGetLastError();
+  return fail(static_cast<int>(e), "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+}
+
+#define CU_TRY(call)                                      \
+  do {                                                    \
+    cudaError_t e__ = (call);                             \
+    if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
+  } while (0)
+
+bool debug_kernel() {
+  static int v = -1;
+  if (v < 0) {
+    const char* s = getenv("SAREK_DEBUG");
+    v = (s && (strstr(s, "kernel") || strstr(s, "all"))) ? 1 : 0;
+  }
+  return v == 1;
+}
+
+struct DeviceState {
+  std::mutex mu;
+  bool ready = false;
+  int sm_count = 0;
+  int cc_major = 0;
+  void* workspace = nullptr;
+  size_t workspace_bytes = 0;
+  int* status = nullptr;  // device word written by kernels whose bounded waits expire
+  std::unordered_map<uint64_t, uint64_t> allocs;
+};
+DeviceState g_dev[kMaxDevices];
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+std::once_flag g_encode_once;
+
+int device_ready(int dev, DeviceState** out) {
+  if (dev < 0 || dev >= kMaxDevices) return fail(SB200_ERR_INVALID_VALUE, "device index %d out of range", dev);
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    return fail(SB200_ERR_NO_DEVICE, "no CUDA device available (%s)", e == cudaSuccess ? "count is 0" : cudaGetErrorString(e));
+  }
+  if (dev >= count) return fail(SB200_ERR_INVALID_VALUE, "device index %d but only %d device(s)", dev, count);
+  DeviceState& d = g_dev[dev];
+  CU_TRY(cudaSetDevice(dev));
+  std::lock_guard<std::mutex> lock(d.mu);
+  if (!d.ready) {
+    cudaDeviceProp prop;
+    CU_TRY(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10)
+      return fail(SB200_ERR_NO_DEVICE, "device %d is sm_%d%d; this library carries sm_100a code only", dev, prop.major,
+                  prop.minor);
+    d.sm_count = prop.multiProcessorCount;
+    d.cc_major = prop.major;
+    CU_TRY(cudaMalloc(&d.status, sizeof(int)));
+    CU_TRY(cudaMemset(d.status, 0, sizeof(int)));
+    d.ready = true;
+  }
+  *out = &d;
+  return SB200_OK;
+}
+
+int check_status_word(DeviceState& d) {
+  int h = 0;
+  CU_TRY(cudaMemcpy(&h, d.status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (h != 0) {
+    cudaMemset(d.status, 0, sizeof(int));
+    return fail(SB200_ERR_TIMEOUT, "a bounded device-side wait expired in the GEMM pipeline (site 0x%x)", h);
+  }
+  return SB200_OK;
+}
+
+inline cudaStream_t as_stream(uint64_t s) { return reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(s)); }
+inline cudaEvent_t as_event(uint64_t e) { return reinterpret_cast<cudaEvent_t>(static_cast<uintptr_t>(e)); }
+template <class T>
+inline T* as_ptr(uint64_t p) {
+  return reinterpret_cast<T*>(static_cast<uintptr_t>(p));
+}
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+int launch_check(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, what);
+  count_launch();
+  return SB200_OK;
+}
+
+int current_mode() {
+  int m = g_mode.load();
+  if (m == 0) {
+    const char* s = getenv("SAREK_B200_MODE");
+    m = (s && (!strcmp(s, "tf32") || !strcmp(s, "TF32"))) ? SB200_MODE_TF32 : SB200_MODE_3XTF32;
+    g_mode.store(m);
+  }
+  return m;
+}
+
+// --------------------------------------------------------------- map host
+template <class Op>
+int launch_map2(DeviceState& d, cudaStream_t st, const float* in0, const float* in1, float* out0, float* out1, float s,
+                long long n) {
+  if (n <= 0) return SB200_OK;
+  const uintptr_t a0 = reinterpret_cast<uintptr_t>(in0), a1 = reinterpret_cast<uintptr_t>(in1),
+                  a2 = reinterpret_cast<uintptr_t>(out0),
+                  a3 = Op::kOutputs == 2 ? reinterpret_cast<uintptr_t>(out1) : a2;
+  const uintptr_t mis = a0 & 15;
+  const bool same = (a1 & 15) == mis && (a2 & 15) == mis && (a3 & 15) == mis && (mis & 3) == 0;
+  long long head = 0, nvec = 0;
+  if (same) {
+    head = mis ? static_cast<long long>((16 - mis) >> 2) : 0;
+    if (head > n) head = n;
+    nvec = (n - head) >> 2;
+  }
+  const long long body_end = head + nvec * 4;
+  if (head > 0) {
+    map2_scalar_kernel<Op><<<1, MAP_THREADS, 0, st>>>(in0, in1, out0, out1, s, 0, head);
+    int rc = launch_check("map head");
+    if (rc) return rc;
+  }
+  if (nvec > 0) {
+    const long long chunk = static_cast<long long>(MAP_THREADS) * MAP_UNROLL;
+    const long long nchunks = (nvec + chunk - 1) / chunk;
+    long long grid = nchunks;
+    const long long cap = static_cast<long long>(d.sm_count) * 32;
+    if (grid > cap) grid = cap;
+    map2_vec_kernel<Op><<<static_cast<unsigned>(grid), MAP_THREADS, 0, st>>>(
+        reinterpret_cast<const float4*>(in0 + head), reinterpret_cast<const float4*>(in1 + head),
+        reinterpret_cast<float4*>(out0 + head), Op::kOutputs == 2 ? reinterpret_cast<float4*>(out1 + head) : nullptr, s,
+        nvec);
+    int rc = launch_check("map body");
+    if (rc) return rc;
+  }
+  if (body_end < n) {
+    const long long rem = n - body_end;
+    long long grid = (rem + MAP_THREADS - 1) / MAP_THREADS;
+    const long long cap = static_cast<long long>(d.sm_count) * 16;
+    if (grid > cap) grid = cap;
+    map2_scalar_kernel<Op><<<static_cast<unsigned>(grid), MAP_THREADS, 0, st>>>(in0, in1, out0, out1, s, body_end, n);
+    int rc = launch_check("map tail");
+    if (rc) return rc;
+  }
+  return SB200_OK;
+}
+
+int run_map(DeviceState& d, cudaStream_t st, int op, uint64_t out0, uint64_t out1, uint64_t in0, uint64_t in1, float s,
+            long long n) {
+  if (n < 0) return fail(SB200_ERR_INVALID_VALUE, "negative element count %lld", n);
+  if (n == 0) return SB200_OK;
+  if (!out0 || !in0 || !in1) return fail(SB200_ERR_INVALID_VALUE, "null device pointer passed to a map operator");
+  if ((out0 | out1 | in0 | in1) & 3) return fail(SB200_ERR_ALIGNMENT, "float32 vectors must be 4-byte aligned");
+  const float* p0 = as_ptr<const float>(in0);
+  const float* p1 = as_ptr<const float>(in1);
+  float* q0 = as_ptr<float>(out0);
+  float* q1 = as_ptr<float>(out1);
+  switch (op) {
+    case OP_VECADD: return launch_map2<VecAddOp>(d, st, p0, p1, q0, nullptr, s, n);
+    case OP_TRIAD: return launch_map2<TriadOp>(d, st, p0, p1, q0, nullptr, s, n);
+    case OP_CHAIN: return launch_map2<ChainOp>(d, st, p0, p1, q0, nullptr, s, n);
+    case OP_CHAIN_KEEP:
+      if (!out1) return fail(SB200_ERR_INVALID_VALUE, "null intermediate vector");
+      return launch_map2<ChainKeepOp>(d, st, p0, p1, q0, q1, s, n);
+  }
+  return fail(SB200_ERR_INVALID_VALUE, "unknown map operator %d", op);
+}
+
+// -------------------------------------------------------------- GEMM host
+inline long long round_up(long long x, long long m) { return (x + m - 1) / m * m; }
+
+int ensure_workspace(DeviceState& d, size_t bytes) {
+  if (bytes <= d.workspace_bytes) return SB200_OK;
+  if (d.workspace) {
+    CU_TRY(cudaDeviceSynchronize());
+    CU_TRY(cudaFree(d.workspace));
+    d.workspace = nullptr;
+    d.workspace_bytes = 0;
+  }
+  CU_TRY(cudaMalloc(&d.workspace, bytes));
+  d.workspace_bytes = bytes;
+  return SB200_OK;
+}
+
+int encode_panel_map(CUtensorMap* map, const float* base, long long kp, long long rows, int box_rows) {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    cudaGetLastError();
+  });
+  if (!g_encode_tiled) return fail(SB200_ERR_NO_DEVICE, "driver does not export cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(kp), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(kp) * 4};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(GEMM_BK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(SB200_ERR_INVALID_VALUE, "cuTensorMapEncodeTiled failed with CUresult %d (kp=%lld rows=%lld)", (int)r, kp,
+                rows);
+  return SB200_OK;
+}
+
+size_t gemm_workspace_need(int mode, long long M, long long N, long long K) {
+  const long long kp = round_up(K, GEMM_BK);
+  const size_t ops = mode == SB200_MODE_3XTF32 ? 2 : 1;
+  const size_t a = round_up(M * kp * 4, 1024), b = round_up(N * kp * 4, 1024);
+  return ops * (a + b);
+}
+
+template <int MODE>
+int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, long long K, const float* A,
+                     long long lda, const float* B, long long ldb, const GemmParams& gp_in) {
+  using Cfg = GemmCfg<MODE>;
+  static std::once_flag attr_once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_tf32_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(Cfg::kSmemBytes));
+  });
+  // the attribute is per device; set it again when several devices are in use
+  cudaError_t ae = cudaFuncSetAttribute(gemm_tf32_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(Cfg::kSmemBytes));
+  if (ae != cudaSuccess) return cuda_fail(ae, "cudaFuncSetAttribute(max dynamic shared memory)");
+  (void)attr_err;
+
+  const long long kp = round_up(K, GEMM_BK);
+  const size_t a_bytes = round_up(M * kp * 4, 1024), b_bytes = round_up(N * kp * 4, 1024);
+  int rc = ensure_workspace(d, gemm_workspace_need(MODE == 3 ? SB200_MODE_3XTF32 : SB200_MODE_TF32, M, N, K));
+  if (rc) return rc;
+  uint8_t* ws = static_cast<uint8_t*>(d.workspace);
+  float* a_hi = reinterpret_cast<float*>(ws);
+  float* b_hi = reinterpret_cast<float*>(ws + a_bytes);
+  float* a_lo = MODE == 3 ? reinterpret_cast<float*>(ws + a_bytes + b_bytes) : a_hi;
+  float* b_lo = MODE == 3 ? reinterpret_cast<float*>(ws + 2 * a_bytes + b_bytes) : b_hi;
+
+  {
+    const long long quads = M * (kp >> 2);
+    long long grid = (quads + 255) / 256;
+    const long long cap = static_cast<long long>(d.sm_count) * 16;
+    if (grid > cap) grid = cap;
+    const int vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0) ? 1 : 0;
+    prep_a_kernel<MODE><<<static_cast<unsigned>(grid), 256, 0, st>>>(A, lda, a_hi, a_lo, static_cast<int>(M),
+                                                                      static_cast<int>(K), static_cast<int>(kp), vec_ok);
+    rc = launch_check("prep_a_kernel");
+    if (rc) return rc;
+  }
+  {
+    const long long tiles = (kp >> 5) * ((N + 31) >> 5);
+    long long grid = tiles;
+    const long long cap = static_cast<long long>(d.sm_count) * 32;
+    if (grid > cap) grid = cap;
+    prep_b_kernel<MODE><<<static_cast<unsigned>(grid), dim3(32, 8), 0, st>>>(B, ldb, b_hi, b_lo, static_cast<int>(K),
+                                                                               static_cast<int>(N), static_cast<int>(kp));
+    rc = launch_check("prep_b_kernel");
+    if (rc) return rc;
+  }
+
+  CUtensorMap ma_hi, mb_hi, ma_lo, mb_lo;
+  if ((rc = encode_panel_map(&ma_hi, a_hi, kp, M, GEMM_BM))) return rc;
+  if ((rc = encode_panel_map(&mb_hi, b_hi, kp, N, GEMM_BN))) return rc;
+  if ((rc = encode_panel_map(&ma_lo, a_lo, kp, M, GEMM_BM))) return rc;
+  if ((rc = encode_panel_map(&mb_lo, b_lo, kp, N, GEMM_BN))) return rc;
+
+  GemmParams gp = gp_in;
+  gp.num_k_blocks = static_cast<int>(kp / GEMM_BK);
+  gp.tiles_m = static_cast<int>((M + GEMM_BM - 1) / GEMM_BM);
+  gp.tiles_n = static_cast<int>((N + GEMM_BN - 1) / GEMM_BN);
+  gp.status = d.status;
+  const long long tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n;
+  const unsigned grid = static_cast<unsigned>(tiles < d.sm_count ? tiles : d.sm_count);
+  gemm_tf32_kernel<MODE><<<grid, GEMM_THREADS, Cfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo, mb_lo, gp);
+  return launch_check("gemm_tf32_kernel");
+}
+
+int run_gemm(DeviceState& d, cudaStream_t st, int mode, long long M, long long N, long long K, uint64_t A, long long lda,
+             uint64_t B, long long ldb, uint64_t D, long long ldd, float alpha, uint64_t C, long long ldc, float beta,
+             uint64_t bias, int act) {
+  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  if (M < 0 || N < 0 || K < 0) return fail(SB200_ERR_INVALID_VALUE, "negative GEMM dimension (M=%lld N=%lld K=%lld)", M, N, K);
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL - 64)
+    return fail(SB200_ERR_TOO_LARGE, "GEMM dimension beyond 2^31-1 (M=%lld N=%lld K=%lld)", M, N, K);
+  if (act != SB200_ACT_NONE && act != SB200_ACT_RELU) return fail(SB200_ERR_INVALID_VALUE, "unknown activation %d", act);
+  if (M == 0 || N == 0) return SB200_OK;
+  if (!D || (K > 0 && (!A || !B))) return fail(SB200_ERR_INVALID_VALUE, "null device pointer passed to GEMM");
+  if ((K > 0 && lda < K) || (K > 0 && ldb < N) || ldd < N || (C && ldc < N))
+    return fail(SB200_ERR_INVALID_VALUE, "leading dimension smaller than the row length (lda=%lld ldb=%lld ldc=%lld ldd=%lld)",
+                lda, ldb, ldc, ldd);
+  if ((A | B | C | D | bias) & 3) return fail(SB200_ERR_ALIGNMENT, "float32 matrices must be 4-byte aligned");
+  GemmParams gp;
+  memset(&gp, 0, sizeof gp);
+  gp.M = static_cast<int>(M);
+  gp.N = static_cast<int>(N);
+  gp.D = as_ptr<float>(D);
+  gp.ldd = ldd;
+  gp.C = as_ptr<const float>(C);
+  gp.ldc = ldc;
+  gp.bias = as_ptr<const float>(bias);
+  gp.alpha = alpha;
+  gp.beta = beta;
+  gp.act = act;
+  if (K == 0) {
+    const long long total = M * N;
+    long long grid = (total + 255) / 256;
+    const long long cap = static_cast<long long>(d.sm_count) * 16;
+    if (grid > cap) grid = cap;
+    gemm_k0_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(gp);
+    return launch_check("gemm_k0_kernel");
+  }
+  if (mode == SB200_MODE_3XTF32)
+    return launch_gemm_mode<3>(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
+  return launch_gemm_mode<1>(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
+}
+
+// ---------------------------------------------------------- kernel objects
+struct KernelObj {
+  int dev;
+  KernelPlan plan;
+};
+std::mutex g_kernels_mu;
+std::unordered_set<KernelObj*> g_kernels;
+
+KernelObj* find_kernel(uint64_t h) {
+  KernelObj* k = reinterpret_cast<KernelObj*>(static_cast<uintptr_t>(h));
+  std::lock_guard<std::mutex> lock(g_kernels_mu);
+  return g_kernels.count(k) ? k : nullptr;
+}
+
+struct Slot {
+  bool is_vec = false;
+  uint64_t ptr = 0;
+  long long len = 0;
+  double f = 0.0;
+  long long i = 0;
+};
+
+int bind_args(const KernelPlan& plan, const sb200_arg* args, int nargs, std::vector<Slot>* slots) {
+  slots->assign(plan.params.size(), Slot());
+  int a = 0;
+  for (size_t p = 0; p < plan.params.size(); ++p) {
+    const ParamInfo& pi = plan.params[p];
+    Slot& s = (*slots)[p];
+    if (pi.is_vec) {
+      if (a + 1 >= nargs || args[a].tag != SB200_ARG_BUFFER || args[a + 1].tag != SB200_ARG_I32)
+        return fail(SB200_ERR_ARGS, "kernel '%s': parameter %zu (%s) expects a buffer followed by its int32 length",
+                    plan.name.c_str(), p, pi.name.c_str());
+      s.is_vec = true;
+      s.ptr = args[a].v.buffer;
+      s.len = args[a + 1].v.i32;
+      if (s.len < 0) return fail(SB200_ERR_ARGS, "kernel '%s': negative length for vector %s", plan.name.c_str(), pi.name.c_str());
+      a += 2;
+    } else {
+      if (a >= nargs) return fail(SB200_ERR_ARGS, "kernel '%s': too few arguments (%d)", plan.name.c_str(), nargs);
+      const sb200_arg& x = args[a++];
+      const bool is_float = pi.elt == "f32" || pi.elt == "f64";
+      switch (x.tag) {
+        case SB200_ARG_I32: s.i = x.v.i32; s.f = static_cast<double>(x.v.i32); break;
+        case SB200_ARG_I64: s.i = x.v.i64; s.f = static_cast<double>(x.v.i64); break;
+        case SB200_ARG_F32: s.f = x.v.f32; s.i = static_cast<long long>(x.v.f32); break;
+        case SB200_ARG_F64: s.f = x.v.f64; s.i = static_cast<long long>(x.v.f64); break;
+        default:
+          return fail(SB200_ERR_ARGS, "kernel '%s': scalar parameter %s received a buffer", plan.name.c_str(), pi.name.c_str());
+      }
+      if (is_float != (x.tag == SB200_ARG_F32 || x.tag == SB200_ARG_F64))
+        return fail(SB200_ERR_ARGS, "kernel '%s': scalar parameter %s has type %s but the argument tag is %d", plan.name.c_str(),
+                    pi.name.c_str(), pi.elt.c_str(), x.tag);
+    }
+  }
+  if (a != nargs) return fail(SB200_ERR_ARGS, "kernel '%s': %d arguments passed, %d consumed", plan.name.c_str(), nargs, a);
+  return SB200_OK;
+}
+
+float coef_value(const Coef& c, const std::vector<Slot>& slots) {
+  return static_cast<float>(c.param >= 0 ? slots[c.param].f : c.value);
+}
+
+int launch_map_kernel(DeviceState& d, const KernelPlan& plan, const std::vector<Slot>& s, const uint32_t grid[3],
+                      const uint32_t block[3], cudaStream_t st) {
+  const MapPlan& m = plan.map;
+  // which element indices the reference launch would touch
+  long long covered = m.index_kind == IDX_GLOBAL ? static_cast<long long>(grid[0]) * block[0] : block[0];
+  long long n = covered;
+  if (m.n_param >= 0) {
+    if (s[m.n_param].i < n) n = s[m.n_param].i;
+    if (n < 0) n = 0;
+  }
+  const int vecs[4] = {m.out0, m.out1, m.in0, m.in1};
+  for (int v : vecs)
+    if (v >= 0 && s[v].len < n)
+      return fail(SB200_ERR_BOUNDS, "kernel '%s': launch covers %lld elements but vector %s holds %lld", plan.name.c_str(), n,
+                  plan.params[v].name.c_str(), s[v].len);
+  return run_map(d, st, m.op, s[m.out0].ptr, m.out1 >= 0 ? s[m.out1].ptr : 0, s[m.in0].ptr, s[m.in1].ptr,
+                 coef_value(m.scalar, s), n);
+}
+
+int launch_gemm_kernel(DeviceState& d, const KernelPlan& plan, const std::vector<Slot>& s, const uint32_t grid[3],
+                       const uint32_t block[3], cudaStream_t st) {
+  const GemmPlan& g = plan.gemm;
+  const long long M = s[g.m].i, N = s[g.n].i, K = s[g.k].i;
+  if (M < 0 || N < 0 || K < 0) return fail(SB200_ERR_ARGS, "kernel '%s': negative m, n or k", plan.name.c_str());
+  auto need = [&](int v, long long elems) -> int {
+    if (v >= 0 && s[v].len < elems)
+      return fail(SB200_ERR_BOUNDS, "kernel '%s': vector %s holds %lld elements, the launch needs %lld", plan.name.c_str(),
+                  plan.params[v].name.c_str(), s[v].len, elems);
+    return SB200_OK;
+  };
+  int rc;
+  if ((rc = need(g.a, M * K)) || (rc = need(g.b, K * N)) || (rc = need(g.d, M * N)) || (rc = need(g.c, M * N)) ||
+      (rc = need(g.bias, N)))
+    return rc;
+  const float alpha = coef_value(g.alpha, s), beta = g.c >= 0 ? coef_value(g.beta, s) : 0.0f;
+  const uint64_t A = s[g.a].ptr, B = s[g.b].ptr, D = s[g.d].ptr, C = g.c >= 0 ? s[g.c].ptr : 0,
+                 bias = g.bias >= 0 ? s[g.bias].ptr : 0;
+  const int mode = current_mode();
+  if (plan.kind == KIND_GEMM_TILED) {
+    if (static_cast<long long>(block[0]) != g.tile || static_cast<long long>(block[1]) != g.tile)
+      return fail(SB200_ERR_ARGS, "kernel '%s': block is %ux%u but the kernel's tiles are %dx%d", plan.name.c_str(), block[0],
+                  block[1], g.tile, g.tile);
+    // the reference launch computes rows < gy*by and columns < gx*bx only
+    long long Me = static_cast<long long>(grid[1]) * block[1], Ne = static_cast<long long>(grid[0]) * block[0];
+    if (Me > M) Me = M;
+    if (Ne > N) Ne = N;
+    return run_gemm(d, st, mode, Me, Ne, K, A, K, B, N, D, N, alpha, C, N, beta, bias, g.act);
+  }
+  // naive shape: thread tid computes element tid of the row-major result
+  long long covered = static_cast<long long>(grid[0]) * block[0];
+  if (covered > M * N) covered = M * N;
+  if (N == 0) return SB200_OK;
+  const long long full_rows = covered / N, rest = covered - full_rows * N;
+  rc = run_gemm(d, st, mode, full_rows, N, K, A, K, B, N, D, N, alpha, C, N, beta, bias, g.act);
+  if (rc || rest == 0) return rc;
+  const uint64_t off_a = static_cast<uint64_t>(full_rows) * K * 4, off_d = static_cast<uint64_t>(full_rows) * N * 4;
+  return run_gemm(d, st, mode, 1, rest, K, A + off_a, K, B, N, D + off_d, N, alpha, C ? C + off_d : 0, N, beta, bias, g.act);
+}
+
+}  // namespace
+
+// =========================================================================
+// C ABI
+// =========================================================================
+extern "C" {
+
+int sb200_init(void) {
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(SB200_ERR_NO_DEVICE, "CUDA is not available: %s", cudaGetErrorString(e));
+  }
+  if (count == 0) return fail(SB200_ERR_NO_DEVICE, "no CUDA device");
+  return SB200_OK;
+}
+
+int sb200_version(void) { return kVersion; }
+
+const char* sb200_last_error_string(void) { return g_err.c_str(); }
+
+int sb200_device_count(int* count) {
+  if (!count) return fail(SB200_ERR_INVALID_VALUE, "null count pointer");
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    *count = 0;
+    return SB200_OK;  // no driver / no device: zero devices, like Cuda_api.is_available () = false
+  }
+  int usable = 0;
+  for (int i = 0; i < n && i < kMaxDevices; ++i) {
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, i) == cudaSuccess && major == 10) usable = i + 1;
+  }
+  *count = usable;
+  return SB200_OK;
+}
+
+int sb200_device_get_info(int dev, sb200_device_info* out) {
+  if (!out) return fail(SB200_ERR_INVALID_VALUE, "null info pointer");
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  cudaDeviceProp p;
+  CU_TRY(cudaGetDeviceProperties(&p, dev));
+  memset(out, 0, sizeof *out);
+  snprintf(out->name, sizeof out->name, "%s", p.name);
+  out->total_mem = p.totalGlobalMem;
+  out->cc_major = p.major;
+  out->cc_minor = p.minor;
+  out->sm_count = p.multiProcessorCount;
+  out->max_threads_per_block = p.maxThreadsPerBlock;
+  out->max_shared_per_block = static_cast<int32_t>(p.sharedMemPerBlockOptin);
+  out->warp_size = p.warpSize;
+  int khz = 0;
+  cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev);
+  out->clock_khz = khz;
+  out->l2_bytes = p.l2CacheSize;
+  return SB200_OK;
+}
+
+int sb200_device_set_current(int dev) {
+  DeviceState* d;
+  return device_ready(dev, &d);
+}
+
+int sb200_device_synchronize(int dev) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  CU_TRY(cudaDeviceSynchronize());
+  return check_status_word(*d);
+}
+
+int sb200_mem_alloc(int dev, uint64_t bytes, uint64_t* dptr) {
+  if (!dptr) return fail(SB200_ERR_INVALID_VALUE, "null dptr pointer");
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  void* p = nullptr;
+  CU_TRY(cudaMalloc(&p, bytes ? bytes : 1));
+  *dptr = reinterpret_cast<uintptr_t>(p);
+  std::lock_guard<std::mutex> lock(d->mu);
+  d->allocs[*dptr] = bytes;
+  return SB200_OK;
+}
+
+int sb200_mem_free(int dev, uint64_t dptr) {
+  if (!dptr) return SB200_OK;
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  {
+    std::lock_guard<std::mutex> lock(d->mu);
+    auto it = d->allocs.find(dptr);
+    if (it == d->allocs.end()) return SB200_OK;  // already freed (or never ours): idempotent
+    d->allocs.erase(it);
+  }
+  CU_TRY(cudaFree(as_ptr<void>(dptr)));  // cudaFree waits for work that may still use the buffer
+  return SB200_OK;
+}
+
+int sb200_mem_size(int dev, uint64_t dptr, uint64_t* bytes) {
+  if (!bytes) return fail(SB200_ERR_INVALID_VALUE, "null bytes pointer");
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  std::lock_guard<std::mutex> lock(d->mu);
+  auto it = d->allocs.find(dptr);
+  if (it == d->allocs.end()) return fail(SB200_ERR_INVALID_HANDLE, "unknown device buffer");
+  *bytes = it->second;
+  return SB200_OK;
+}
+
+int sb200_memset32(int dev, uint64_t dptr, uint32_t value, uint64_t count, uint64_t stream) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (count == 0) return SB200_OK;
+  if (!dptr || (dptr & 3)) return fail(SB200_ERR_INVALID_VALUE, "memset32 needs a 4-byte aligned device pointer");
+  if (value == 0) {
+    CU_TRY(cudaMemsetAsync(as_ptr<void>(dptr), 0, count * 4, as_stream(stream)));
+    return SB200_OK;
+  }
+  // cuMemsetD32 equivalent through the runtime's 2-D memset is byte-wise only; use the driver entry
+  typedef CUresult (*MemsetFn)(CUdeviceptr, unsigned int, size_t, CUstream);
+  static MemsetFn fn = nullptr;
+  if (!fn) {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemsetD32Async", &f, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<MemsetFn>(f);
+  }
+  if (!fn) return fail(SB200_ERR_NO_DEVICE, "driver does not export cuMemsetD32Async");
+  CUresult r = fn(static_cast<CUdeviceptr>(dptr), value, count, reinterpret_cast<CUstream>(as_stream(stream)));
+  if (r != CUDA_SUCCESS) return fail(static_cast<int>(r), "cuMemsetD32Async failed with CUresult %d", (int)r);
+  return SB200_OK;
+}
+
+int sb200_memcpy_htod(int dev, uint64_t dst, const void* src, uint64_t bytes) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (bytes == 0) return SB200_OK;
+  if (!dst || !src) return fail(SB200_ERR_INVALID_VALUE, "null pointer passed to memcpy_htod");
+  CU_TRY(cudaMemcpy(as_ptr<void>(dst), src, bytes, cudaMemcpyHostToDevice));
+  return SB200_OK;
+}
+
+int sb200_memcpy_dtoh(int dev, void* dst, uint64_t src, uint64_t bytes) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (bytes == 0) return SB200_OK;
+  if (!dst || !src) return fail(SB200_ERR_INVALID_VALUE, "null pointer passed to memcpy_dtoh");
+  CU_TRY(cudaMemcpy(dst, as_ptr<void>(src), bytes, cudaMemcpyDeviceToHost));
+  return check_status_word(*d);
+}
+
+int sb200_memcpy_dtod(int dev, uint64_t dst, uint64_t src, uint64_t bytes) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (bytes == 0) return SB200_OK;
+  if (!dst || !src) return fail(SB200_ERR_INVALID_VALUE, "null pointer passed to memcpy_dtod");
+  CU_TRY(cudaMemcpy(as_ptr<void>(dst), as_ptr<void>(src), bytes, cudaMemcpyDeviceToDevice));
+  return SB200_OK;
+}
+
+int sb200_memcpy_htod_async(int dev, uint64_t dst, const void* src, uint64_t bytes, uint64_t stream) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (bytes == 0) return SB200_OK;
+  if (!dst || !src) return fail(SB200_ERR_INVALID_VALUE, "null pointer passed to memcpy_htod_async");
+  CU_TRY(cudaMemcpyAsync(as_ptr<void>(dst), src, bytes, cudaMemcpyHostToDevice, as_stream(stream)));
+  return SB200_OK;
+}
+
+int sb200_memcpy_dtoh_async(int dev, void* dst, uint64_t src, uint64_t bytes, uint64_t stream) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (bytes == 0) return SB200_OK;
+  if (!dst || !src) return fail(SB200_ERR_INVALID_VALUE, "null pointer passed to memcpy_dtoh_async");
+  CU_TRY(cudaMemcpyAsync(dst, as_ptr<void>(src), bytes, cudaMemcpyDeviceToHost, as_stream(stream)));
+  return SB200_OK;
+}
+
+int sb200_host_alloc(uint64_t bytes, void** ptr) {
+  if (!ptr) return fail(SB200_ERR_INVALID_VALUE, "null ptr pointer");
+  CU_TRY(cudaMallocHost(ptr, bytes ? bytes : 1));
+  return SB200_OK;
+}
+
+int sb200_host_free(void* ptr) {
+  if (!ptr) return SB200_OK;
+  CU_TRY(cudaFreeHost(ptr));
+  return SB200_OK;
+}
+
+int sb200_stream_create(int dev, uint64_t* stream) {
+  if (!stream) return fail(SB200_ERR_INVALID_VALUE, "null stream pointer");
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  cudaStream_t s;
+  CU_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  *stream = reinterpret_cast<uintptr_t>(s);
+  return SB200_OK;
+}
+
+int sb200_stream_destroy(int dev, uint64_t stream) {
+  if (!stream) return SB200_OK;
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  CU_TRY(cudaStreamDestroy(as_stream(stream)));
+  return SB200_OK;
+}
+
+int sb200_stream_synchronize(int dev, uint64_t stream) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  CU_TRY(cudaStreamSynchronize(as_stream(stream)));
+  return check_status_word(*d);
+}
+
+int sb200_stream_wrap(int dev, uint64_t native_stream, uint64_t* stream) {
+  if (!stream) return fail(SB200_ERR_INVALID_VALUE, "null stream pointer");
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  *stream = native_stream;
+  return SB200_OK;
+}
+
+int sb200_event_create(int dev, uint64_t* event) {
+  if (!event) return fail(SB200_ERR_INVALID_VALUE, "null event pointer");
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  cudaEvent_t e;
+  CU_TRY(cudaEventCreate(&e));
+  *event = reinterpret_cast<uintptr_t>(e);
+  return SB200_OK;
+}
+
+int sb200_event_destroy(int dev, uint64_t event) {
+  if (!event) return SB200_OK;
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  CU_TRY(cudaEventDestroy(as_event(event)));
+  return SB200_OK;
+}
+
+int sb200_event_record(int dev, uint64_t event, uint64_t stream) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (!event) return fail(SB200_ERR_INVALID_HANDLE, "null event");
+  CU_TRY(cudaEventRecord(as_event(event), as_stream(stream)));
+  return SB200_OK;
+}
+
+int sb200_event_synchronize(int dev, uint64_t event) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (!event) return fail(SB200_ERR_INVALID_HANDLE, "null event");
+  CU_TRY(cudaEventSynchronize(as_event(event)));
+  return SB200_OK;
+}
+
+int sb200_event_elapsed_ms(int dev, uint64_t start, uint64_t stop, float* ms) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (!start || !stop || !ms) return fail(SB200_ERR_INVALID_HANDLE, "null event or result pointer");
+  CU_TRY(cudaEventElapsedTime(ms, as_event(start), as_event(stop)));
+  return SB200_OK;
+}
+
+int sb200_kernel_compile(int dev, const char* ir_text, const char* name, uint64_t* kernel) {
+  if (!ir_text || !kernel) return fail(SB200_ERR_INVALID_VALUE, "null IR text or kernel pointer");
+  if (dev < 0 || dev >= kMaxDevices) return fail(SB200_ERR_INVALID_VALUE, "device index %d out of range", dev);
+  KernelObj* k = new KernelObj;
+  k->dev = dev;
+  std::string err;
+  int rc = ir_compile(ir_text, &k->plan, &err);
+  if (rc) {
+    delete k;
+    return fail(rc, "%s", err.c_str());
+  }
+  if (name && *name && k->plan.name != name && debug_kernel())
+    fprintf(stderr, "[sarek-b200] kernel name '%s' requested, IR names it '%s'\n", name, k->plan.name.c_str());
+  if (debug_kernel()) fprintf(stderr, "[sarek-b200] compiled %s -> %s\n", k->plan.name.c_str(), k->plan.description.c_str());
+  {
+    std::lock_guard<std::mutex> lock(g_kernels_mu);
+    g_kernels.insert(k);
+  }
+  *kernel = reinterpret_cast<uintptr_t>(k);
+  return SB200_OK;
+}
+
+int sb200_kernel_destroy(uint64_t kernel) {
+  KernelObj* k = reinterpret_cast<KernelObj*>(static_cast<uintptr_t>(kernel));
+  {
+    std::lock_guard<std::mutex> lock(g_kernels_mu);
+    if (!g_kernels.erase(k)) return SB200_OK;
+  }
+  delete k;
+  return SB200_OK;
+}
+
+int sb200_kernel_kind(uint64_t kernel, int* kind) {
+  KernelObj* k = find_kernel(kernel);
+  if (!k || !kind) return fail(SB200_ERR_INVALID_HANDLE, "unknown kernel handle");
+  *kind = k->plan.kind;
+  return SB200_OK;
+}
+
+int sb200_kernel_describe(uint64_t kernel, char* buf, int buflen) {
+  KernelObj* k = find_kernel(kernel);
+  if (!k || !buf || buflen <= 0) return fail(SB200_ERR_INVALID_HANDLE, "unknown kernel handle");
+  snprintf(buf, static_cast<size_t>(buflen), "%s", k->plan.description.c_str());
+  return SB200_OK;
+}
+
+int sb200_kernel_launch(uint64_t kernel, const sb200_arg* args, int nargs, const uint32_t grid[3], const uint32_t block[3],
+                        uint32_t shared_mem, uint64_t stream) {
+  (void)shared_mem;  // forwarded by the caller even when arrays are static; our kernels size their own
+  KernelObj* k = find_kernel(kernel);
+  if (!k) return fail(SB200_ERR_INVALID_HANDLE, "unknown kernel handle");
+  if ((!args && nargs > 0) || nargs < 0 || !grid || !block) return fail(SB200_ERR_INVALID_VALUE, "null argument list or dims");
+  for (int i = 0; i < 3; ++i)
+    if (grid[i] == 0 || block[i] == 0) return fail(SB200_ERR_INVALID_VALUE, "grid and block dimensions must be positive");
+  std::vector<Slot> slots;
+  int rc = bind_args(k->plan, args, nargs, &slots);
+  if (rc) return rc;
+  DeviceState* d;
+  rc = device_ready(k->dev, &d);
+  if (rc) return rc;
+  if (debug_kernel())
+    fprintf(stderr, "[sarek-b200] launch %s grid=(%u,%u,%u) block=(%u,%u,%u)\n", k->plan.description.c_str(), grid[0], grid[1],
+            grid[2], block[0], block[1], block[2]);
+  if (k->plan.kind == KIND_MAP) return launch_map_kernel(*d, k->plan, slots, grid, block, as_stream(stream));
+  return launch_gemm_kernel(*d, k->plan, slots, grid, block, as_stream(stream));
+}
+
+static int copy_out(const std::string& s, char* out, int outlen) {
+  if (!out || outlen <= 0) return fail(SB200_ERR_INVALID_VALUE, "null output buffer");
+  if (static_cast<int>(s.size()) + 1 > outlen)
+    return fail(SB200_ERR_TOO_LARGE, "output buffer of %d bytes is too small for %zu bytes", outlen, s.size() + 1);
+  memcpy(out, s.c_str(), s.size() + 1);
+  return SB200_OK;
+}
+
+int sb200_ir_can_fuse(const char* producer, const char* consumer, const char* intermediate, int* result) {
+  if (!producer || !consumer || !intermediate || !result) return fail(SB200_ERR_INVALID_VALUE, "null argument");
+  bool ok = false;
+  std::string err;
+  int rc = ir_can_fuse(producer, consumer, intermediate, &ok, &err);
+  if (rc) return fail(rc, "%s", err.c_str());
+  *result = ok ? 1 : 0;
+  return SB200_OK;
+}
+
+int sb200_ir_fuse(const char* producer, const char* consumer, const char* intermediate, char* out, int outlen) {
+  if (!producer || !consumer || !intermediate) return fail(SB200_ERR_INVALID_VALUE, "null argument");
+  std::string text, err;
+  int rc = ir_fuse(producer, consumer, intermediate, &text, &err);
+  if (rc) return fail(rc, "%s", err.c_str());
+  return copy_out(text, out, outlen);
+}
+
+int sb200_ir_fuse_pipeline(const char* const* kernels, int count, char* out, int outlen, char* eliminated, int elimlen) {
+  if (!kernels || count <= 0) return fail(SB200_ERR_INVALID_VALUE, "empty kernel list");
+  std::vector<std::string> ks;
+  for (int i = 0; i < count; ++i) {
+    if (!kernels[i]) return fail(SB200_ERR_INVALID_VALUE, "null kernel text");
+    ks.push_back(kernels[i]);
+  }
+  std::string text, err;
+  std::vector<std::string> elim;
+  int rc = ir_fuse_pipeline(ks, &text, &elim, &err);
+  if (rc) return fail(rc, "%s", err.c_str());
+  std::string joined;
+  for (size_t i = 0; i < elim.size(); ++i) joined += (i ? "," : "") + elim[i];
+  if (eliminated && elimlen > 0 && (rc = copy_out(joined, eliminated, elimlen))) return rc;
+  return copy_out(text, out, outlen);
+}
+
+int sb200_gemm_f32(int dev, uint64_t stream, int mode, int64_t M, int64_t N, int64_t K, uint64_t A, int64_t lda, uint64_t B,
+                   int64_t ldb, uint64_t D, int64_t ldd, float alpha, uint64_t C, int64_t ldc, float beta, uint64_t bias,
+                   int act) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  return run_gemm(*d, as_stream(stream), mode, M, N, K, A, lda, B, ldb, D, ldd, alpha, C, ldc, beta, bias, act);
+}
+
+int sb200_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, uint64_t* bytes) {
+  if (!bytes || M < 0 || N < 0 || K < 0) return fail(SB200_ERR_INVALID_VALUE, "bad argument");
+  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  *bytes = (M == 0 || N == 0 || K == 0) ? 0 : gemm_workspace_need(mode, M, N, K);
+  return SB200_OK;
+}
+
+int sb200_vector_add_f32(int dev, uint64_t stream, uint64_t c, uint64_t a, uint64_t b, int64_t n) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  return run_map(*d, as_stream(stream), OP_VECADD, c, 0, a, b, 0.0f, n);
+}
+
+int sb200_stream_triad_f32(int dev, uint64_t stream, uint64_t a, uint64_t b, uint64_t c, float scalar, int64_t n) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  return run_map(*d, as_stream(stream), OP_TRIAD, a, 0, b, c, scalar, n);
+}
+
+int sb200_chain_triad_square_f32(int dev, uint64_t stream, uint64_t dd, uint64_t a_out, uint64_t b, uint64_t c, float scalar,
+                                 int64_t n) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  return run_map(*d, as_stream(stream), a_out ? OP_CHAIN_KEEP : OP_CHAIN, dd, a_out, b, c, scalar, n);
+}
+
+int sb200_set_mode(int mode) {
+  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  g_mode.store(mode);
+  return SB200_OK;
+}
+
+int sb200_get_mode(int* mode) {
+  if (!mode) return fail(SB200_ERR_INVALID_VALUE, "null mode pointer");
+  *mode = current_mode();
+  return SB200_OK;
+}
+
+int sb200_fill_f32(int dev, uint64_t stream, uint64_t dptr, int64_t n, uint64_t seed, uint64_t stream_id, int kind, double sigma,
+                   int64_t first) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (n < 0 || kind < 0 || kind > 2) return fail(SB200_ERR_INVALID_VALUE, "bad fill arguments");
+  if (n == 0) return SB200_OK;
+  if (!dptr || (dptr & 3)) return fail(SB200_ERR_INVALID_VALUE, "fill needs a 4-byte aligned device pointer");
+  long long grid = (n + 255) / 256;
+  const long long cap = static_cast<long long>(d->sm_count) * 16;
+  if (grid > cap) grid = cap;
+  fill_kernel<<<static_cast<unsigned>(grid), 256, 0, as_stream(stream)>>>(as_ptr<float>(dptr), n, seed, stream_id, kind, sigma,
+                                                                          first);
+  return launch_check("fill_kernel");
+}
+
+int sb200_launch_count(uint64_t* count) {
+  if (!count) return fail(SB200_ERR_INVALID_VALUE, "null count pointer");
+  *count = g_launches.load();
+  return SB200_OK;
+}
+
+}  // extern "C"

