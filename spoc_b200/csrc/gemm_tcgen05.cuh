@@ -235,7 +235,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       const int row0 = tm * GEMM_BM + quarter * 32;
       const int n0 = tn * GEMM_BN;
-      if (!mbar_wait_bounded(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag)) {
+      // every lane waits; the warp then agrees on the outcome so that the
+      // warp-collective tensor-memory loads below are never partly skipped
+      const bool landed = mbar_wait_bounded(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag);
+      if (!__all_sync(0xffffffffu, landed)) {
         if (lane == 0) atomicCAS(p.status, 0, 0x400 | acc);
         ok = false;
         break;
