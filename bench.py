@@ -1,0 +1,426 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 backend's hot path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload (N = 1): fp32 GEMM with fused epilogue D = max(0, 1.5 A.B + 0.5 C + bias[col]),
+M = N = K = 8192, row-major float32, seeded uniform inputs, in 3xTF32 mode (the
+fp32-grade mode).  One step = one call of the operator: two operand-preparation
+kernels plus the tcgen05 kernel.  All four matrices are 256 MiB, larger than the
+126 MB L2, so no flush is needed between steps.  At N > 1 every rank owns an
+8192-row block of A/C/D (weak scaling), B is replicated with an NCCL broadcast
+before the timed region, and there is no collective inside it.
+
+The JSON line also carries the TF32-mode figure and the fused-map chain
+(a = b + 3c ; d = a*a + b over 2^28 floats) with their own rooflines.
+
+`--impl reference` times the CPU restatement of the reference's Native backend
+(oracle/native_oracle.c, the naive matrix_mul kernel with the same epilogue) on
+the host cores, on a bounded row slab of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M = N = K = 8192
+SEED = 20260101
+MAP_N = 1 << 28
+METRIC = "fp32_gemm_fused_epilogue_8192cubed"
+WORKLOAD = "gemm M=N=K=8192 fp32, D=max(0,1.5*A.B+0.5*C+bias[col]), 3xTF32 split accumulation"
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # "under load" = samples in the upper half of the observed power range
+        thr = (max(power) + min(power)) / 2 if power else 0
+        loaded = [c for c, p in zip(sm, power) if p >= thr] or sm
+        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power) if power else None}
+
+
+# --------------------------------------------------------------------------- reference arm
+def oracle_lib():
+    from tests import oracle_lib as O  # the checker doubles as the timed CPU baseline
+    return O
+
+
+def cpu_slab_rate(workers: int, target_s: float):
+    """Times the Native-semantics naive kernel with the fused epilogue on the first
+    `rows` rows of the 8192^3 problem; returns (tflops, seconds, rows)."""
+    import numpy as np
+    O = oracle_lib()
+    lib = O.load()
+    a = O.fill(64 * K, SEED, 1)          # rows of A that the slab can touch (<= 64)
+    b = O.fill(K * N, SEED, 2)
+    c = O.fill(64 * N, SEED, 3)
+    bias = O.fill(N, SEED, 4, kind=1)
+    out = np.empty(64 * N, dtype=np.float32)
+
+    def run(ids: int) -> float:
+        t0 = time.perf_counter()
+        lib.so_par_matmul_naive(a, b, out, 64, N, K, 0, ids, 1.5, 0.5, c.ctypes.data_as(C.c_void_p),
+                                bias.ctypes.data_as(C.c_void_p), 1, 1, workers)
+        return time.perf_counter() - t0
+
+    calib_ids = 256 * workers
+    t = run(calib_ids)
+    ids = int(min(64 * N, max(calib_ids, calib_ids * target_s / max(t, 1e-6))))
+    ids = max(256, ids // 256 * 256)
+    return (lambda: run(ids)), ids
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    workers = max(1, (os.cpu_count() or 2) - 1)
+    step, ids = cpu_slab_rate(workers, target_s=2.0)
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    flops = 2.0 * K * ids * args.steps
+    value = flops / dt / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f64 accumulate, f32 store", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "l2": "inputs larger than any cache"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": workers, "kind": "port",
+                         "sample": f"first {ids} output elements ({ids / N:.2f} rows) of the 8192^3 problem per step; "
+                                   "C restatement of Sarek Native (no OCaml toolchain here), faster than the real OCaml "
+                                   "backend because it has none of its per-element boxing"},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- B200 arm
+def run_b200(args, rank: int, local_rank: int, world: int) -> None:
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from spoc_b200 import Backend, _lib as L
+    from spoc_b200.build import build_library
+    from spoc_b200.plugin import _check
+
+    if not os.path.exists(L.LIB_PATH):
+        build_library()
+    lib = L.load()  # raises when the CUDA library is missing: there is no fallback
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    backend = Backend()
+    backend.Device.init()
+    dev = backend.Device.get(local_rank)
+    backend.Device.set_current(dev)
+    tdev = torch.device("cuda", local_rank)
+    stream = torch.cuda.current_stream().cuda_stream
+    peaks = load_peaks()
+
+    def fill(t, sid, kind, first=0):
+        _check(lib.sb200_fill_f32(dev.id, stream, t.data_ptr(), t.numel(), SEED, sid, kind, 1.0, first))
+
+    A = torch.empty(M * K, dtype=torch.float32, device=tdev)
+    B = torch.empty(K * N, dtype=torch.float32, device=tdev)
+    Cm = torch.empty(M * N, dtype=torch.float32, device=tdev)
+    D = torch.empty(M * N, dtype=torch.float32, device=tdev)
+    bias = torch.empty(N, dtype=torch.float32, device=tdev)
+    fill(A, 1, 0, first=rank * M * K)   # rank r owns rows [r*M, (r+1)*M) of the global A and C
+    fill(Cm, 3, 0, first=rank * M * N)
+    fill(bias, 4, 1)
+    bcast_ms = None
+    if world > 1:
+        if rank == 0:
+            fill(B, 2, 0)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dist.broadcast(B, src=0)          # B replicated over NVLink into each GPU's own HBM
+        e1.record()
+        torch.cuda.synchronize()
+        bcast_ms = e0.elapsed_time(e1)
+    else:
+        fill(B, 2, 0)
+    torch.cuda.synchronize()
+
+    def gemm(mode):
+        _check(lib.sb200_gemm_f32(dev.id, stream, mode, M, N, K, A.data_ptr(), K, B.data_ptr(), N, D.data_ptr(), N,
+                                  1.5, Cm.data_ptr(), N, 0.5, bias.data_ptr(), L.ACT_RELU))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=tdev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn, steps, warmup, profile=False):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        barrier()
+        if profile:
+            backend.profile_gemm_read(dev)
+            backend.enable_profiling()
+        l0 = backend.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        launches = backend.launch_count() - l0
+        prof = None
+        if profile:
+            backend.disable_profiling()
+            prof = backend.profile_gemm_read(dev)
+        return max_over_ranks(e0.elapsed_time(e1)), launches, prof
+
+    flops_step = 2.0 * M * N * K
+    # ---- headline: 3xTF32 ------------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, launches, prof = timed(lambda: gemm(L.MODE_3XTF32), args.steps, args.warmup, profile=True)
+    clocks = sampler.stop() if rank == 0 else None
+    _check(lib.sb200_device_synchronize(dev.id))  # also surfaces a device-side timeout flag
+    ms_step = ms / args.steps
+    value = world * flops_step / (ms_step * 1e-3) / 1e12
+    tf32_peak = peaks["bf16_tflops"] / 2.0
+    main_ms = prof["main_ms"] / max(prof["calls"], 1)
+    prep_ms = prof["prep_ms"] / max(prof["calls"], 1)
+    achieved = flops_step / (main_ms * 1e-3) / 1e12
+    roofline = {
+        "bound": "tensor", "kernel": "gemm_tf32_kernel<3>", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
+        "frac": achieved / tf32_peak, "traffic": None,
+        "peak_source": f"{peaks['source']}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 = dense TF32",
+        "mma_frac": 3.0 * achieved / tf32_peak,
+        "kernel_ms": main_ms, "prep_ms": prep_ms,
+        "note": "achieved counts the algorithmic 2*M*N*K flops; 3xTF32 issues 3 MMAs per k-step, mma_frac is the tensor-pipe share",
+    }
+
+    # ---- TF32 mode ----------------------------------------------------------------------
+    s2 = max(3, min(args.steps, 10))
+    ms2, _, prof2 = timed(lambda: gemm(L.MODE_TF32), s2, 3, profile=True)
+    main2 = prof2["main_ms"] / max(prof2["calls"], 1)
+    tf32_mode = {
+        "value": world * flops_step / (ms2 / s2 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms2 / s2,
+        "roofline": {"bound": "tensor", "kernel": "gemm_tf32_kernel<1>", "achieved": flops_step / (main2 * 1e-3) / 1e12,
+                     "peak": tf32_peak, "unit": "TFLOP/s", "frac": flops_step / (main2 * 1e-3) / 1e12 / tf32_peak,
+                     "kernel_ms": main2, "prep_ms": prof2["prep_ms"] / max(prof2["calls"], 1)},
+    }
+
+    # ---- e2e: host buffers, copies inside the timed region ---------------------------------
+    hA = torch.empty(M * K, dtype=torch.float32).pin_memory()
+    hB = torch.empty(K * N, dtype=torch.float32).pin_memory()
+    hC = torch.empty(M * N, dtype=torch.float32).pin_memory()
+    hbias = torch.empty(N, dtype=torch.float32).pin_memory()
+    hD = torch.empty(M * N, dtype=torch.float32).pin_memory()
+    for h, d in ((hA, A), (hB, B), (hC, Cm), (hbias, bias)):
+        h.copy_(d)
+    torch.cuda.synchronize()
+
+    def e2e_step():
+        for h, d in ((hA, A), (hB, B), (hC, Cm), (hbias, bias)):
+            _check(lib.sb200_memcpy_htod_async(dev.id, d.data_ptr(), h.data_ptr(), h.numel() * 4, stream))
+        gemm(L.MODE_3XTF32)
+        _check(lib.sb200_memcpy_dtoh_async(dev.id, hD.data_ptr(), D.data_ptr(), hD.numel() * 4, stream))
+        _check(lib.sb200_stream_synchronize(dev.id, stream))
+
+    s3 = max(3, min(args.steps, 10))
+    ms3, _, _ = timed(e2e_step, s3, 2)
+    e2e = {"value": world * flops_step / (ms3 / s3 * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "h2d_bytes_per_step": 4 * (M * K + K * N + M * N + N), "d2h_bytes_per_step": 4 * M * N,
+           "ms_per_step": ms3 / s3}
+    del hA, hB, hC, hD
+
+    # ---- fused-map chain (HBM bound) ---------------------------------------------------------
+    fused_map = None
+    if world == 1:
+        del A, Cm
+        b = torch.empty(MAP_N, dtype=torch.float32, device=tdev)
+        c = torch.empty(MAP_N, dtype=torch.float32, device=tdev)
+        d = torch.empty(MAP_N, dtype=torch.float32, device=tdev)
+        fill(b, 2, 0)
+        fill(c, 3, 0)
+        s4 = max(5, min(args.steps, 20))
+        ms4, l4, _ = timed(lambda: _check(lib.sb200_chain_triad_square_f32(dev.id, stream, d.data_ptr(), 0, b.data_ptr(),
+                                                                         c.data_ptr(), 3.0, MAP_N)), s4, 3)
+        gbs = 12.0 * MAP_N / (ms4 / s4 * 1e-3) / 1e9
+        fused_map = {"workload": "a=b+3c; d=a*a+b fused, N=2^28 float32, intermediate eliminated", "value": gbs,
+                     "unit": "GB/s", "ms_per_step": ms4 / s4, "launches_per_step": l4 / s4,
+                     "roofline": {"bound": "hbm", "kernel": "map2_vec_kernel<ChainOp>", "achieved": gbs,
+                                  "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                                  "traffic": None, "peak_source": f"{peaks['source']} copy bandwidth",
+                                  "frac_of_nominal_8TBs": gbs / 8000.0}}
+
+    # ---- CPU baseline (rank 0, N = 1 only) -----------------------------------------------------
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        workers = max(1, (os.cpu_count() or 2) - 1)
+        step, ids = cpu_slab_rate(workers, target_s=12.0)
+        dt = step()
+        cpu_baseline = {"value": 2.0 * K * ids / dt / 1e12, "unit": "TFLOP/s", "cores": workers, "kind": "port",
+                        "sample": f"first {ids} output elements ({ids / N:.2f} rows) of the same 8192^3 problem, "
+                                  f"{dt:.1f} s; C restatement of Sarek Native's naive kernel with the epilogue"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32x3 (f32 in/out)",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "rows_per_gpu": M, "l2": "inputs larger than L2 (4 x 256 MiB per GPU)",
+                       "sharding": "row blocks of A/C/D per rank, B replicated by NCCL broadcast before the timed region"},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "tf32_mode": tf32_mode, "fused_map": fused_map, "b_broadcast_ms": bcast_ms,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_case(args) -> None:
+    """A small single-operator run for profiler captures: one warm-up call and two
+    measured calls of one operator on inputs larger than L2 but well under a GB."""
+    import torch
+
+    from spoc_b200 import Backend, _lib as L
+    from spoc_b200.plugin import _check
+    lib = L.load()
+    backend = Backend()
+    backend.Device.init()
+    dev = backend.Device.get(0)
+    backend.Device.set_current(dev)
+    torch.cuda.set_device(0)
+    tdev = torch.device("cuda", 0)
+    stream = torch.cuda.current_stream().cuda_stream
+    S = args.size
+    if args.case in ("gemm3", "gemm1"):
+        mode = L.MODE_3XTF32 if args.case == "gemm3" else L.MODE_TF32
+        bufs = [torch.empty(S * S, dtype=torch.float32, device=tdev) for _ in range(4)]
+        bias = torch.empty(S, dtype=torch.float32, device=tdev)
+        for i, t in enumerate(bufs[:3]):
+            _check(lib.sb200_fill_f32(dev.id, stream, t.data_ptr(), t.numel(), SEED, i + 1, 0, 1.0, 0))
+        _check(lib.sb200_fill_f32(dev.id, stream, bias.data_ptr(), S, SEED, 4, 1, 1.0, 0))
+        fn = lambda: _check(lib.sb200_gemm_f32(dev.id, stream, mode, S, S, S, bufs[0].data_ptr(), S, bufs[1].data_ptr(), S,
+                                               bufs[3].data_ptr(), S, 1.5, bufs[2].data_ptr(), S, 0.5, bias.data_ptr(), 1))
+        work, unit = 2.0 * S ** 3 / 1e12, "TFLOP/s"
+    else:
+        n = S * S
+        bufs = [torch.empty(n, dtype=torch.float32, device=tdev) for _ in range(3)]
+        for i, t in enumerate(bufs[:2]):
+            _check(lib.sb200_fill_f32(dev.id, stream, t.data_ptr(), n, SEED, i + 2, 0, 1.0, 0))
+        fn = lambda: _check(lib.sb200_chain_triad_square_f32(dev.id, stream, bufs[2].data_ptr(), 0, bufs[0].data_ptr(),
+                                                             bufs[1].data_ptr(), 3.0, n))
+        work, unit = 12.0 * n / 1e9, "GB/s"
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    _check(lib.sb200_device_synchronize(dev.id))
+    ms = e0.elapsed_time(e1) / 2
+    print(json.dumps({"case": args.case, "size": S, "ms_per_call": ms, "rate": work / (ms * 1e-3), "unit": unit}), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default=None, choices=["gemm3", "gemm1", "map"],
+                    help="profiler-sized single-operator run (square size --size; map uses size^2 elements)")
+    ap.add_argument("--size", type=int, default=4096)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_b200(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -184,6 +184,16 @@ SB200_API int sb200_get_mode(int *mode);
 SB200_API int sb200_fill_f32(int dev, uint64_t stream, uint64_t dptr, int64_t n,
                              uint64_t seed, uint64_t stream_id, int kind, double sigma, int64_t first);
 
+/* kernel profiling: the enable_profiling / disable_profiling members of
+ * Framework_sig.BACKEND (spoc/framework/Framework_sig.ml:280-282;
+ * sarek-cuda/Cuda_plugin_base.ml:294-300).  While enabled, every GEMM call
+ * records CUDA events on its launch stream around the operand-preparation
+ * kernels and around the tensor-core kernel; sb200_profile_gemm_read waits for
+ * the recorded calls, returns their count and summed durations and clears the
+ * record. */
+SB200_API int sb200_enable_profiling(int on);
+SB200_API int sb200_profile_gemm_read(int dev, uint64_t *calls, double *prep_ms, double *main_ms);
+
 /* number of kernels this library has launched on this thread's behalf since
  * load (monotonic; used by benchmarks to report launch counts) */
 SB200_API int sb200_launch_count(uint64_t *count);

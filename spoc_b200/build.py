@@ -19,7 +19,7 @@ HEADERS = ["gemm_tcgen05.cuh", "map_fused.cuh", "ptx_sm100.cuh", "ir.hpp",
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared", "-cudart", "shared",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared", "-cudart", "static",
 ]
 
 

@@ -77,8 +77,14 @@ struct DeviceState {
   size_t workspace_bytes = 0;
   int* status = nullptr;  // device word written by kernels whose bounded waits expire
   std::unordered_map<uint64_t, uint64_t> allocs;
+  // kernel profiling (enable_profiling): event triples recorded around the GEMM stages
+  struct ProfRec {
+    cudaEvent_t e0, e1, e2;
+  };
+  std::vector<ProfRec> prof;
 };
 DeviceState g_dev[kMaxDevices];
+std::atomic<int> g_profiling{0};
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -284,6 +290,14 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   const size_t a_bytes = round_up(M * kp * 4, 1024), b_bytes = round_up(N * kp * 4, 1024);
   int rc = ensure_workspace(d, gemm_workspace_need(MODE == 3 ? SB200_MODE_3XTF32 : SB200_MODE_TF32, M, N, K));
   if (rc) return rc;
+  const bool prof = g_profiling.load() != 0;
+  DeviceState::ProfRec rec{nullptr, nullptr, nullptr};
+  if (prof) {
+    CU_TRY(cudaEventCreate(&rec.e0));
+    CU_TRY(cudaEventCreate(&rec.e1));
+    CU_TRY(cudaEventCreate(&rec.e2));
+    CU_TRY(cudaEventRecord(rec.e0, st));
+  }
   uint8_t* ws = static_cast<uint8_t*>(d.workspace);
   float* a_hi = reinterpret_cast<float*>(ws);
   float* b_hi = reinterpret_cast<float*>(ws + a_bytes);
@@ -325,8 +339,15 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   gp.status = d.status;
   const long long tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n;
   const unsigned grid = static_cast<unsigned>(tiles < d.sm_count ? tiles : d.sm_count);
+  if (prof) CU_TRY(cudaEventRecord(rec.e1, st));
   gemm_tf32_kernel<MODE><<<grid, GEMM_THREADS, Cfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo, mb_lo, gp);
-  return launch_check("gemm_tf32_kernel");
+  rc = launch_check("gemm_tf32_kernel");
+  if (prof) {
+    CU_TRY(cudaEventRecord(rec.e2, st));
+    std::lock_guard<std::mutex> lock(d.mu);
+    d.prof.push_back(rec);
+  }
+  return rc;
 }
 
 int run_gemm(DeviceState& d, cudaStream_t st, int mode, long long M, long long N, long long K, uint64_t A, long long lda,
@@ -950,6 +971,39 @@ int sb200_fill_f32(int dev, uint64_t stream, uint64_t dptr, int64_t n, uint64_t 
   fill_kernel<<<static_cast<unsigned>(grid), 256, 0, as_stream(stream)>>>(as_ptr<float>(dptr), n, seed, stream_id, kind, sigma,
                                                                           first);
   return launch_check("fill_kernel");
+}
+
+int sb200_enable_profiling(int on) {
+  g_profiling.store(on ? 1 : 0);
+  return SB200_OK;
+}
+
+int sb200_profile_gemm_read(int dev, uint64_t* calls, double* prep_ms, double* main_ms) {
+  if (!calls || !prep_ms || !main_ms) return fail(SB200_ERR_INVALID_VALUE, "null result pointer");
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  std::vector<DeviceState::ProfRec> recs;
+  {
+    std::lock_guard<std::mutex> lock(d->mu);
+    recs.swap(d->prof);
+  }
+  *calls = recs.size();
+  *prep_ms = 0.0;
+  *main_ms = 0.0;
+  for (auto& r : recs) {
+    float a = 0.f, b = 0.f;
+    cudaError_t e = cudaEventSynchronize(r.e2);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&a, r.e0, r.e1);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&b, r.e1, r.e2);
+    cudaEventDestroy(r.e0);
+    cudaEventDestroy(r.e1);
+    cudaEventDestroy(r.e2);
+    if (e != cudaSuccess) return cuda_fail(e, "reading GEMM profile events");
+    *prep_ms += a;
+    *main_ms += b;
+  }
+  return SB200_OK;
 }
 
 int sb200_launch_count(uint64_t* count) {

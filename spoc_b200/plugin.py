@@ -367,6 +367,17 @@ class Backend:
         """IR -> source text.  The IR already is its own source language here."""
         return ir
 
+    def enable_profiling(self) -> None:
+        _check(L.load().sb200_enable_profiling(1))
+
+    def disable_profiling(self) -> None:
+        _check(L.load().sb200_enable_profiling(0))
+
+    def profile_gemm_read(self, d: _Device.T) -> dict:
+        n, a, b = C.c_uint64(0), C.c_double(0), C.c_double(0)
+        _check(L.load().sb200_profile_gemm_read(d.id, C.byref(n), C.byref(a), C.byref(b)))
+        return {"calls": n.value, "prep_ms": a.value, "main_ms": b.value}
+
     def execute_direct(self, *a, **k):
         raise BackendError(L.ERR_UNSUPPORTED, "execute_direct: B200 is a JIT-model backend")
 
