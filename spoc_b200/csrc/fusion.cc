@@ -1,8 +1,478 @@
-// fusion.cc — placeholder, replaced below
-#include "ir.hpp"
+// fusion.cc — vertical fusion of element-wise kernels on IR text.
+//
+// Restates the behaviour of the reference's host-side fusion pass
+// (sarek/sarek/Sarek_fusion.ml) on the S-expression form of the IR:
+//   expr_equal            :32-46     structural equality, variables by id
+//   collect_reads/writes  :170-262   (array, index) pairs, newest first
+//   analyze_pattern       :296-322   OneToOne / Stencil offsets / Gather
+//   find_write_expr       :360-378   gives up inside if / for / while
+//   can_fuse              :401-431
+//   fuse                  :459-547   substitute, drop the intermediate,
+//                                    append producer parameters, "<name>_fused"
+//   fuse_pipeline         :570-598   greedy left to right
+//   should_fuse           :1068-1098 Fuse / DontFuse / MaybeFuse with reason
+//   auto_fuse_pipeline    :1133-1165
+// Reduction and stencil fusion (:667-1030) are not part of this backend's
+// path; a consumer that reads the intermediate more than once is classified
+// as a stencil here exactly as in the reference, so can_fuse refuses it while
+// a direct fuse still rewrites every read that uses the matching index.
+#include <algorithm>
+#include <set>
+
 #include "../../include/sb200.h"
+#include "ir.hpp"
+
 namespace sb200 {
-int ir_can_fuse(const std::string&, const std::string&, const std::string&, bool*, std::string* err) { *err = "not implemented"; return SB200_ERR_UNSUPPORTED; }
-int ir_fuse(const std::string&, const std::string&, const std::string&, std::string*, std::string* err) { *err = "not implemented"; return SB200_ERR_UNSUPPORTED; }
-int ir_fuse_pipeline(const std::vector<std::string>&, std::string*, std::vector<std::string>*, std::string* err) { *err = "not implemented"; return SB200_ERR_UNSUPPORTED; }
+
+bool parse_kernel_form(const std::string& text, Sx* root, KernelPlan* plan, const Sx** body, std::string* err);
+
+namespace {
+
+struct Kernel {
+  Sx root;  // (kernel NAME (params ...) (body STMT))
+  std::string name() const { return root[1].s; }
+  const Sx& params() const { return root[2]; }
+  const Sx& body() const { return root[3][1]; }
+};
+
+bool load_kernel(const std::string& text, Kernel* k, std::string* err) {
+  KernelPlan plan;
+  const Sx* body;
+  return parse_kernel_form(text, &k->root, &plan, &body, err);
 }
+
+// structural equality with variables compared by id only; forms the
+// reference's expr_equal does not know (if, cast, ...) never compare equal
+bool expr_equal(const Sx& a, const Sx& b) {
+  if (a.atom || b.atom || a.kids.empty() || b.kids.empty() || !a[0].atom || !b[0].atom || a[0].s != b[0].s) return false;
+  const std::string& h = a[0].s;
+  if (h == "const") return a.size() == 3 && b.size() == 3 && a[1].s == b[1].s && a[2].s == b[2].s;
+  if (h == "evar") return a.size() >= 3 && b.size() >= 3 && a[2].s == b[2].s;
+  if (h == "binop") return a.size() == 4 && b.size() == 4 && a[1].s == b[1].s && expr_equal(a[2], b[2]) && expr_equal(a[3], b[3]);
+  if (h == "unop") return a.size() == 3 && b.size() == 3 && a[1].s == b[1].s && expr_equal(a[2], b[2]);
+  if (h == "read") return a.size() == 3 && b.size() == 3 && a[1].s == b[1].s && expr_equal(a[2], b[2]);
+  if (h == "intrinsic") {
+    if (a.size() != b.size() || a.size() < 3 || !sx_equal(a[1], b[1]) || a[2].s != b[2].s) return false;
+    for (size_t i = 3; i < a.size(); ++i)
+      if (!expr_equal(a[i], b[i])) return false;
+    return true;
+  }
+  return false;
+}
+
+using Access = std::pair<std::string, Sx>;  // (array, index)
+using AccessList = std::vector<Access>;     // front = most recently found (the reference conses)
+
+void push_front(AccessList* l, Access a) { l->insert(l->begin(), std::move(a)); }
+
+void reads_expr(const Sx& e, AccessList* acc) {
+  if (e.atom || e.kids.empty()) return;
+  const std::string& h = e[0].s;
+  if (h == "read" && e.size() == 3) {
+    // (arr, idx) :: collect idx  — the read itself ends up in front of its index's reads
+    reads_expr(e[2], acc);
+    push_front(acc, {e[1].s, e[2]});
+  } else if (h == "binop" && e.size() == 4) {
+    reads_expr(e[2], acc);
+    reads_expr(e[3], acc);
+  } else if (h == "unop" && e.size() == 3) {
+    reads_expr(e[2], acc);
+  } else if (h == "intrinsic") {
+    for (size_t i = 3; i < e.size(); ++i) reads_expr(e[i], acc);
+  } else if (h == "cast" && e.size() == 3) {
+    reads_expr(e[2], acc);
+  } else if (h == "if" && e.size() == 4) {
+    reads_expr(e[1], acc);
+    reads_expr(e[2], acc);
+    reads_expr(e[3], acc);
+  }
+}
+
+void reads_stmt(const Sx& s, AccessList* acc) {
+  if (s.atom || s.kids.empty()) return;
+  const std::string& h = s[0].s;
+  if (h == "assign" && s.size() == 3) {
+    if (s[1].is("elem") && s[1].size() == 3) reads_expr(s[1][2], acc);
+    reads_expr(s[2], acc);
+  } else if (h == "seq") {
+    for (size_t i = 1; i < s.size(); ++i) reads_stmt(s[i], acc);
+  } else if (h == "sif") {
+    reads_expr(s[1], acc);
+    for (size_t i = 2; i < s.size(); ++i) reads_stmt(s[i], acc);
+  } else if (h == "while" && s.size() == 3) {
+    reads_expr(s[1], acc);
+    reads_stmt(s[2], acc);
+  } else if (h == "for" && s.size() == 7) {
+    reads_expr(s[3], acc);
+    reads_expr(s[4], acc);
+    reads_stmt(s[6], acc);
+  } else if ((h == "return" || h == "expr") && s.size() == 2) {
+    reads_expr(s[1], acc);
+  } else if ((h == "let" || h == "letmut") && s.size() == 6) {
+    reads_expr(s[4], acc);
+    reads_stmt(s[5], acc);
+  } else if (h == "pragma" && s.size() == 3) {
+    reads_stmt(s[2], acc);
+  } else if (h == "block" && s.size() == 2) {
+    reads_stmt(s[1], acc);
+  }
+}
+
+void writes_stmt(const Sx& s, AccessList* acc) {
+  if (s.atom || s.kids.empty()) return;
+  const std::string& h = s[0].s;
+  if (h == "assign" && s.size() == 3) {
+    if (s[1].is("elem") && s[1].size() == 3) push_front(acc, {s[1][1].s, s[1][2]});
+  } else if (h == "seq") {
+    for (size_t i = 1; i < s.size(); ++i) writes_stmt(s[i], acc);
+  } else if (h == "sif") {
+    for (size_t i = 2; i < s.size(); ++i) writes_stmt(s[i], acc);
+  } else if (h == "while" && s.size() == 3) {
+    writes_stmt(s[2], acc);
+  } else if (h == "for" && s.size() == 7) {
+    writes_stmt(s[6], acc);
+  } else if ((h == "let" || h == "letmut") && s.size() == 6) {
+    writes_stmt(s[5], acc);
+  } else if (h == "pragma" && s.size() == 3) {
+    writes_stmt(s[2], acc);
+  } else if (h == "block" && s.size() == 2) {
+    writes_stmt(s[1], acc);
+  }
+}
+
+bool has_barrier(const Sx& s) {
+  if (s.atom) return false;
+  if (s.is("barrier") || s.is("warpbarrier")) return true;
+  for (const Sx& k : s.kids)
+    if (has_barrier(k)) return true;
+  return false;
+}
+
+enum PatternKind { P_ONE_TO_ONE, P_STENCIL, P_GATHER, P_UNKNOWN };
+struct Pattern {
+  PatternKind kind = P_UNKNOWN;
+  Sx index;                  // OneToOne
+  std::vector<int> offsets;  // Stencil
+};
+
+bool const_i32(const Sx& e, int* v) {
+  if (e.is("const") && e.size() == 3 && e[1].s == "i32") {
+    *v = atoi(e[2].s.c_str());
+    return true;
+  }
+  return false;
+}
+
+// idx = base + const | base - const | const + base
+bool extract_offset(const Sx& idx, Sx* base, int* off) {
+  if (!idx.is("binop") || idx.size() != 4) return false;
+  int n;
+  if (idx[1].s == "add" && const_i32(idx[3], &n)) {
+    *base = idx[2];
+    *off = n;
+    return true;
+  }
+  if (idx[1].s == "sub" && const_i32(idx[3], &n)) {
+    *base = idx[2];
+    *off = -n;
+    return true;
+  }
+  if (idx[1].s == "add" && const_i32(idx[2], &n)) {
+    *base = idx[3];
+    *off = n;
+    return true;
+  }
+  return false;
+}
+
+Pattern analyze_pattern(const AccessList& all, const std::string& arr) {
+  std::vector<const Sx*> idxs;
+  for (const Access& a : all)
+    if (a.first == arr) idxs.push_back(&a.second);
+  Pattern p;
+  if (idxs.empty()) return p;
+  if (idxs.size() == 1) {
+    p.kind = P_ONE_TO_ONE;
+    p.index = *idxs[0];
+    return p;
+  }
+  std::vector<std::pair<Sx, int>> ob;
+  for (const Sx* i : idxs) {
+    Sx base;
+    int off;
+    if (extract_offset(*i, &base, &off))
+      ob.emplace_back(base, off);
+    else if (i->is("evar") || i->is("intrinsic"))
+      ob.emplace_back(*i, 0);
+  }
+  if (ob.size() != idxs.size()) {
+    p.kind = P_GATHER;
+    return p;
+  }
+  for (size_t i = 1; i < ob.size(); ++i)
+    if (!expr_equal(ob[i].first, ob[0].first)) {
+      p.kind = P_GATHER;
+      return p;
+    }
+  std::set<int> offs;
+  for (auto& x : ob) offs.insert(x.second);
+  p.kind = P_STENCIL;
+  p.offsets.assign(offs.begin(), offs.end());
+  return p;
+}
+
+struct Info {
+  AccessList reads, writes;
+  bool barriers = false;
+  std::vector<std::string> read_arrays, write_arrays;  // sorted, unique
+};
+
+Info analyze(const Kernel& k) {
+  Info in;
+  reads_stmt(k.body(), &in.reads);
+  writes_stmt(k.body(), &in.writes);
+  in.barriers = has_barrier(k.body());
+  std::set<std::string> r, w;
+  for (auto& a : in.reads) r.insert(a.first);
+  for (auto& a : in.writes) w.insert(a.first);
+  in.read_arrays.assign(r.begin(), r.end());
+  in.write_arrays.assign(w.begin(), w.end());
+  return in;
+}
+
+bool contains(const std::vector<std::string>& v, const std::string& s) { return std::find(v.begin(), v.end(), s) != v.end(); }
+
+bool can_fuse_k(const Kernel& prod, const Kernel& cons, const std::string& inter) {
+  Info pi = analyze(prod), ci = analyze(cons);
+  if (!contains(pi.write_arrays, inter) || !contains(ci.read_arrays, inter)) return false;
+  if (analyze_pattern(pi.writes, inter).kind != P_ONE_TO_ONE) return false;
+  if (analyze_pattern(ci.reads, inter).kind != P_ONE_TO_ONE) return false;
+  return !pi.barriers && !ci.barriers;
+}
+
+// the expression stored to arr[idx]; nullptr inside conditionals and loops
+const Sx* find_write_expr(const Sx& s, const std::string& arr, const Sx& idx) {
+  if (s.atom || s.kids.empty()) return nullptr;
+  const std::string& h = s[0].s;
+  if (h == "assign" && s.size() == 3) {
+    if (s[1].is("elem") && s[1].size() == 3 && s[1][1].s == arr && expr_equal(s[1][2], idx)) return &s[2];
+    return nullptr;
+  }
+  if (h == "seq") {
+    for (size_t i = 1; i < s.size(); ++i)
+      if (const Sx* e = find_write_expr(s[i], arr, idx)) return e;
+    return nullptr;
+  }
+  if ((h == "let" || h == "letmut") && s.size() == 6) return find_write_expr(s[5], arr, idx);
+  if (h == "pragma" && s.size() == 3) return find_write_expr(s[2], arr, idx);
+  if (h == "block" && s.size() == 2) return find_write_expr(s[1], arr, idx);
+  return nullptr;
+}
+
+Sx subst_expr(const Sx& e, const std::string& arr, const Sx& idx, const Sx& repl) {
+  if (e.atom) return e;
+  if (e.is("read") && e.size() == 3) {
+    if (e[1].s == arr && expr_equal(e[2], idx)) return repl;
+    return Sx::L({e[0], e[1], subst_expr(e[2], arr, idx, repl)});
+  }
+  if (e.is("evar") || e.is("const") || e.is("arraylen")) return e;
+  Sx o;
+  for (const Sx& k : e.kids) o.kids.push_back(k.atom ? k : subst_expr(k, arr, idx, repl));
+  return o;
+}
+
+Sx subst_stmt(const Sx& s, const std::string& arr, const Sx& idx, const Sx& repl) {
+  if (s.atom || s.kids.empty()) return s;
+  const std::string& h = s[0].s;
+  if (h == "assign" && s.size() == 3) {
+    Sx lv = s[1];
+    if (lv.is("elem") && lv.size() == 3) lv = Sx::L({lv[0], lv[1], subst_expr(lv[2], arr, idx, repl)});
+    return Sx::L({s[0], lv, subst_expr(s[2], arr, idx, repl)});
+  }
+  if (h == "seq" || h == "block" || h == "pragma") {
+    Sx o;
+    for (size_t i = 0; i < s.size(); ++i) o.kids.push_back((i == 0 || s[i].atom || (h == "pragma" && i == 1)) ? s[i] : subst_stmt(s[i], arr, idx, repl));
+    return o;
+  }
+  if (h == "sif") {
+    Sx o = Sx::L({s[0], subst_expr(s[1], arr, idx, repl)});
+    for (size_t i = 2; i < s.size(); ++i) o.kids.push_back(subst_stmt(s[i], arr, idx, repl));
+    return o;
+  }
+  if (h == "while" && s.size() == 3) return Sx::L({s[0], subst_expr(s[1], arr, idx, repl), subst_stmt(s[2], arr, idx, repl)});
+  if (h == "for" && s.size() == 7)
+    return Sx::L({s[0], s[1], s[2], subst_expr(s[3], arr, idx, repl), subst_expr(s[4], arr, idx, repl), s[5],
+                  subst_stmt(s[6], arr, idx, repl)});
+  if ((h == "let" || h == "letmut") && s.size() == 6)
+    return Sx::L({s[0], s[1], s[2], s[3], subst_expr(s[4], arr, idx, repl), subst_stmt(s[5], arr, idx, repl)});
+  if ((h == "return" || h == "expr") && s.size() == 2) return Sx::L({s[0], subst_expr(s[1], arr, idx, repl)});
+  return s;
+}
+
+Kernel fuse_k(const Kernel& prod, const Kernel& cons, const std::string& inter) {
+  AccessList cr;
+  reads_stmt(cons.body(), &cr);
+  const Sx* inter_idx = nullptr;
+  for (const Access& a : cr)
+    if (a.first == inter) {
+      inter_idx = &a.second;
+      break;
+    }
+  if (!inter_idx) return cons;
+  const Sx* repl = find_write_expr(prod.body(), inter, *inter_idx);
+  if (!repl) return cons;
+  Sx body = subst_stmt(cons.body(), inter, *inter_idx, *repl);
+  Sx params = Sx::L({Sx::A("params")});
+  std::set<std::string> names;
+  for (size_t i = 1; i < cons.params().size(); ++i) {
+    const Sx& p = cons.params()[i];
+    if (p[1].s == inter) continue;
+    params.kids.push_back(p);
+    names.insert(p[1].s);
+  }
+  for (size_t i = 1; i < prod.params().size(); ++i) {
+    const Sx& p = prod.params()[i];
+    if (p[1].s == inter || names.count(p[1].s)) continue;
+    params.kids.push_back(p);
+  }
+  Kernel out;
+  out.root = Sx::L({Sx::A("kernel"), Sx::A(cons.name() + "_fused"), params, Sx::L({Sx::A("body"), body})});
+  return out;
+}
+
+struct Hint {
+  const char* decision;
+  const char* reason;
+};
+
+Hint should_fuse_k(const Kernel& prod, const Kernel& cons, const std::string& inter) {
+  Info pi = analyze(prod), ci = analyze(cons);
+  if (pi.barriers || ci.barriers) return {"DontFuse", "Barrier prevents fusion"};
+  const bool pw = contains(pi.write_arrays, inter), cr = contains(ci.read_arrays, inter);
+  Pattern w = analyze_pattern(pi.writes, inter), r = analyze_pattern(ci.reads, inter);
+  if (pw && cr && w.kind == P_ONE_TO_ONE) {
+    if (r.kind == P_ONE_TO_ONE) return {"Fuse", "Element-wise producer/consumer"};
+    if (r.kind == P_STENCIL)
+      return r.offsets.size() <= 3 ? Hint{"MaybeFuse", "Small stencil - profile to decide"}
+                                   : Hint{"DontFuse", "Large stencil radius - keep separate"};
+    if (r.kind == P_GATHER) return {"DontFuse", "Gather pattern - keep separate"};
+  }
+  return {"MaybeFuse", "Unknown pattern - profile to decide"};
+}
+
+std::vector<std::string> candidates(const Info& cur, const Info& next) {
+  std::vector<std::string> out;
+  for (const std::string& a : cur.write_arrays)
+    if (contains(next.read_arrays, a)) out.push_back(a);
+  return out;
+}
+
+}  // namespace
+
+int ir_can_fuse(const std::string& producer, const std::string& consumer, const std::string& inter, bool* ok,
+                std::string* err) {
+  Kernel p, c;
+  if (!load_kernel(producer, &p, err) || !load_kernel(consumer, &c, err)) return SB200_ERR_PARSE;
+  *ok = can_fuse_k(p, c, inter);
+  return SB200_OK;
+}
+
+int ir_fuse(const std::string& producer, const std::string& consumer, const std::string& inter, std::string* out,
+            std::string* err) {
+  Kernel p, c;
+  if (!load_kernel(producer, &p, err) || !load_kernel(consumer, &c, err)) return SB200_ERR_PARSE;
+  *out = sx_print(fuse_k(p, c, inter).root);
+  return SB200_OK;
+}
+
+int ir_fuse_pipeline(const std::vector<std::string>& kernels, std::string* out, std::vector<std::string>* eliminated,
+                     std::string* err) {
+  if (kernels.empty()) {
+    *err = "fuse_pipeline: empty pipeline";
+    return SB200_ERR_INVALID_VALUE;
+  }
+  std::vector<Kernel> ks(kernels.size());
+  for (size_t i = 0; i < kernels.size(); ++i)
+    if (!load_kernel(kernels[i], &ks[i], err)) return SB200_ERR_PARSE;
+  Kernel cur = ks[0];
+  eliminated->clear();
+  for (size_t i = 1; i < ks.size(); ++i) {
+    std::vector<std::string> c = candidates(analyze(cur), analyze(ks[i]));
+    if (!c.empty() && can_fuse_k(cur, ks[i], c[0])) {
+      cur = fuse_k(cur, ks[i], c[0]);
+      eliminated->insert(eliminated->begin(), c[0]);  // the reference conses: newest first
+    } else {
+      cur = ks[i];
+    }
+  }
+  *out = sx_print(cur.root);
+  return SB200_OK;
+}
+
+int ir_should_fuse(const std::string& producer, const std::string& consumer, const std::string& inter,
+                   std::string* decision, std::string* reason, std::string* err) {
+  Kernel p, c;
+  if (!load_kernel(producer, &p, err) || !load_kernel(consumer, &c, err)) return SB200_ERR_PARSE;
+  Hint h = should_fuse_k(p, c, inter);
+  *decision = h.decision;
+  *reason = h.reason;
+  return SB200_OK;
+}
+
+int ir_auto_fuse_pipeline(const std::vector<std::string>& kernels, std::string* out, std::vector<std::string>* eliminated,
+                          std::vector<std::string>* skipped, std::string* err) {
+  if (kernels.empty()) {
+    *err = "auto_fuse_pipeline: empty pipeline";
+    return SB200_ERR_INVALID_VALUE;
+  }
+  std::vector<Kernel> ks(kernels.size());
+  for (size_t i = 0; i < kernels.size(); ++i)
+    if (!load_kernel(kernels[i], &ks[i], err)) return SB200_ERR_PARSE;
+  Kernel cur = ks[0];
+  eliminated->clear();
+  skipped->clear();
+  for (size_t i = 1; i < ks.size(); ++i) {
+    std::vector<std::string> c = candidates(analyze(cur), analyze(ks[i]));
+    if (c.empty()) {
+      cur = ks[i];
+      continue;
+    }
+    Hint h = should_fuse_k(cur, ks[i], c[0]);
+    if (std::string(h.decision) == "Fuse" && can_fuse_k(cur, ks[i], c[0])) {
+      cur = fuse_k(cur, ks[i], c[0]);
+      eliminated->insert(eliminated->begin(), c[0]);
+    } else {
+      skipped->insert(skipped->begin(), h.reason);
+      cur = ks[i];
+    }
+  }
+  *out = sx_print(cur.root);
+  return SB200_OK;
+}
+
+// One line per array: "read|write NAME one_to_one|stencil[o1,o2]|gather|unknown", then "barriers yes|no".
+int ir_analyze(const std::string& kernel, std::string* report, std::string* err) {
+  Kernel k;
+  if (!load_kernel(kernel, &k, err)) return SB200_ERR_PARSE;
+  Info in = analyze(k);
+  auto fmt = [](const Pattern& p) {
+    switch (p.kind) {
+      case P_ONE_TO_ONE: return std::string("one_to_one");
+      case P_GATHER: return std::string("gather");
+      case P_STENCIL: {
+        std::string s = "stencil[";
+        for (size_t i = 0; i < p.offsets.size(); ++i) s += (i ? "," : "") + std::to_string(p.offsets[i]);
+        return s + "]";
+      }
+      default: return std::string("unknown");
+    }
+  };
+  std::string r;
+  for (auto& a : in.read_arrays) r += "read " + a + " " + fmt(analyze_pattern(in.reads, a)) + "\n";
+  for (auto& a : in.write_arrays) r += "write " + a + " " + fmt(analyze_pattern(in.writes, a)) + "\n";
+  r += std::string("barriers ") + (in.barriers ? "yes" : "no") + "\n";
+  *report = r;
+  return SB200_OK;
+}
+
+}  // namespace sb200
