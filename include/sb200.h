@@ -162,7 +162,26 @@ SB200_API int sb200_gemm_f32(int dev, uint64_t stream, int mode,
                              uint64_t D, int64_t ldd,
                              float alpha, uint64_t C, int64_t ldc, float beta,
                              uint64_t bias, int act);
-/* bytes of library-owned scratch the call above needs for these sizes */
+/* Same operator and arguments as sb200_gemm_f32, for callers that must not
+ * allocate device memory: a host framework whose caching allocator already owns
+ * all of the GPU's memory (any further cudaMalloc fails), or a caller that
+ * cannot take the device-wide synchronisation of cudaMalloc/cudaFree while its
+ * other streams are busy.  This entry point has no counterpart in the
+ * reference.  It allocates nothing: the TF32 operand panels live in a fixed
+ * 32 MiB device array inside the library image (held by every GPU that loads
+ * the library, until exit).  Sizes whose panels do not fit, (M+N)*roundup(K,32)*4
+ * bytes (x2 in 3xTF32 mode), return SB200_ERR_TOO_LARGE.  All calls on a device
+ * share the array and it keeps the last call's contents (each call rewrites
+ * all it reads); calls that overlap on the GPU race on it.  The first call on a
+ * device looks up the array's address and should come before any stream
+ * capture.  The call returns after its kernels have finished. */
+SB200_API int sb200_gemm_f32_noalloc(int dev, uint64_t stream, int mode,
+                                     int64_t M, int64_t N, int64_t K,
+                                     uint64_t A, int64_t lda, uint64_t B, int64_t ldb,
+                                     uint64_t D, int64_t ldd,
+                                     float alpha, uint64_t C, int64_t ldc, float beta,
+                                     uint64_t bias, int act);
+/* bytes of library-owned scratch sb200_gemm_f32 needs for these sizes */
 SB200_API int sb200_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, uint64_t *bytes);
 
 /* c = a + b  (benchmarks/bench_vector_add.ml:47-55) */

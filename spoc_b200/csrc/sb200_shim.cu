@@ -1013,3 +1013,192 @@ int sb200_launch_count(uint64_t* count) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// GEMM for callers that must not allocate device memory
+// ---------------------------------------------------------------------------
+// sb200_gemm_f32 keeps its TF32 operand panels in a grow-only workspace that it
+// obtains with cudaMalloc (and releases with cudaFree when it has to grow).
+// Two kinds of caller cannot live with that.  A host framework whose own
+// caching allocator already holds all of the GPU's memory makes every further
+// cudaMalloc fail.  And a caller that keeps other streams busy, or that calls
+// from a latency-critical loop, cannot afford the device-wide synchronisation
+// that cudaMalloc / cudaFree imply.  The variant below computes the same
+// result with the same kernels, but its panels live in a fixed array that is
+// part of the library image, so the call allocates nothing at all: no
+// cudaMalloc, no cudaFree, no pinned host memory, no CUDA events.
+//
+// Price and rules:
+//  * Every GPU on which the library is loaded carries the array (32 MiB) from
+//    load to exit.
+//  * Problem sizes are limited by it: the panels need
+//    (M + N) * roundup(K, 32) * 4 bytes, twice that in 3xTF32 mode (each part
+//    rounded up to 1 KiB); larger problems are refused with SB200_ERR_TOO_LARGE.
+//    1024^3 in 3xTF32 mode and 1448^3 in TF32 mode fit.
+//  * All calls on a device share the one array and it keeps whatever the last
+//    call left in it.  Nothing in it has to start at zero: each call rewrites
+//    every panel element it later reads, including the zero padding of K.
+//    For the same reason two calls that overlap on the GPU (different streams,
+//    or different host threads) race on the panels; serialise them.
+//  * The first call on each device looks up the array's device address.  Make
+//    that first call before any stream capture begins.
+//  * The call returns after its kernels have finished (it waits on `stream`),
+//    so that a device-side wait that ran out of time is reported by the call
+//    that suffered it, as SB200_ERR_TIMEOUT.
+namespace {
+
+constexpr size_t kNoAllocScratchBytes = size_t(32) << 20;
+
+// In host code these two names are only stand-ins for the device objects; the
+// addresses kernels may use come from cudaGetSymbolAddress (noalloc_setup).
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+static __device__ int g_noalloc_status;
+
+struct NoAllocDevice {
+  bool ready = false;
+  unsigned char* scratch = nullptr;  // device address of g_noalloc_scratch on this device
+  int* status = nullptr;             // device address of g_noalloc_status on this device
+  int sm_count = 0;
+};
+NoAllocDevice g_noalloc[kMaxDevices];
+std::mutex g_noalloc_mu;
+
+// Once per device, with that device current.
+int noalloc_setup(int dev, NoAllocDevice** out) {
+  if (dev < 0 || dev >= kMaxDevices) return fail(SB200_ERR_INVALID_VALUE, "device index %d out of range", dev);
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    return fail(SB200_ERR_NO_DEVICE, "no CUDA device available");
+  }
+  if (dev >= count) return fail(SB200_ERR_INVALID_VALUE, "device index %d but only %d device(s)", dev, count);
+  CU_TRY(cudaSetDevice(dev));
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  NoAllocDevice& nd = g_noalloc[dev];
+  if (!nd.ready) {
+    int major = 0, sms = 0;
+    CU_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    CU_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (major != 10) return fail(SB200_ERR_NO_DEVICE, "device %d is not sm_100; this library carries sm_100a code only", dev);
+    void* p = nullptr;
+    CU_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    nd.scratch = static_cast<unsigned char*>(p);
+    CU_TRY(cudaGetSymbolAddress(&p, g_noalloc_status));
+    nd.status = static_cast<int*>(p);
+    CU_TRY(cudaMemset(nd.status, 0, sizeof(int)));
+    nd.sm_count = sms;
+    nd.ready = true;
+  }
+  *out = &nd;
+  return SB200_OK;
+}
+
+template <int MODE>
+int launch_gemm_fixed_scratch(const NoAllocDevice& nd, cudaStream_t st, long long M, long long N, long long K, const float* A,
+                              long long lda, const float* B, long long ldb, GemmParams gp) {
+  using Cfg = GemmCfg<MODE>;
+  CU_TRY(cudaFuncSetAttribute(gemm_tf32_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(Cfg::kSmemBytes)));
+  const long long kp = round_up(K, GEMM_BK);
+  const size_t a_bytes = round_up(M * kp * 4, 1024), b_bytes = round_up(N * kp * 4, 1024);
+  float* a_hi = reinterpret_cast<float*>(nd.scratch);
+  float* b_hi = reinterpret_cast<float*>(nd.scratch + a_bytes);
+  float* a_lo = MODE == 3 ? reinterpret_cast<float*>(nd.scratch + a_bytes + b_bytes) : a_hi;
+  float* b_lo = MODE == 3 ? reinterpret_cast<float*>(nd.scratch + 2 * a_bytes + b_bytes) : b_hi;
+  int rc;
+  {
+    long long grid = (M * (kp >> 2) + 255) / 256;
+    const long long cap = static_cast<long long>(nd.sm_count) * 16;
+    if (grid > cap) grid = cap;
+    const int vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0) ? 1 : 0;
+    prep_a_kernel<MODE><<<static_cast<unsigned>(grid), 256, 0, st>>>(A, lda, a_hi, a_lo, static_cast<int>(M),
+                                                                      static_cast<int>(K), static_cast<int>(kp), vec_ok);
+    if ((rc = launch_check("prep_a_kernel"))) return rc;
+  }
+  {
+    long long grid = (kp >> 5) * ((N + 31) >> 5);
+    const long long cap = static_cast<long long>(nd.sm_count) * 32;
+    if (grid > cap) grid = cap;
+    prep_b_kernel<MODE><<<static_cast<unsigned>(grid), dim3(32, 8), 0, st>>>(B, ldb, b_hi, b_lo, static_cast<int>(K),
+                                                                               static_cast<int>(N), static_cast<int>(kp));
+    if ((rc = launch_check("prep_b_kernel"))) return rc;
+  }
+  CUtensorMap ma_hi, mb_hi, ma_lo, mb_lo;
+  if ((rc = encode_panel_map(&ma_hi, a_hi, kp, M, GEMM_BM))) return rc;
+  if ((rc = encode_panel_map(&mb_hi, b_hi, kp, N, GEMM_BN))) return rc;
+  if ((rc = encode_panel_map(&ma_lo, a_lo, kp, M, GEMM_BM))) return rc;
+  if ((rc = encode_panel_map(&mb_lo, b_lo, kp, N, GEMM_BN))) return rc;
+  gp.num_k_blocks = static_cast<int>(kp / GEMM_BK);
+  gp.tiles_m = static_cast<int>((M + GEMM_BM - 1) / GEMM_BM);
+  gp.tiles_n = static_cast<int>((N + GEMM_BN - 1) / GEMM_BN);
+  gp.status = nd.status;
+  const long long tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n;
+  const unsigned grid = static_cast<unsigned>(tiles < nd.sm_count ? tiles : nd.sm_count);
+  gemm_tf32_kernel<MODE><<<grid, GEMM_THREADS, Cfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo, mb_lo, gp);
+  return launch_check("gemm_tf32_kernel");
+}
+
+}  // namespace
+
+extern "C" int sb200_gemm_f32_noalloc(int dev, uint64_t stream, int mode, int64_t M, int64_t N, int64_t K, uint64_t A,
+                                      int64_t lda, uint64_t B, int64_t ldb, uint64_t D, int64_t ldd, float alpha, uint64_t C,
+                                      int64_t ldc, float beta, uint64_t bias, int act) {
+  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  if (M < 0 || N < 0 || K < 0) return fail(SB200_ERR_INVALID_VALUE, "negative GEMM dimension (M=%lld N=%lld K=%lld)",
+                                           (long long)M, (long long)N, (long long)K);
+  if (act != SB200_ACT_NONE && act != SB200_ACT_RELU) return fail(SB200_ERR_INVALID_VALUE, "unknown activation %d", act);
+  if (M > 0 && N > 0 && K > 0) {
+    if (M > (1 << 24) || N > (1 << 24) || K > (1 << 24))
+      return fail(SB200_ERR_TOO_LARGE, "GEMM dimension beyond the fixed scratch (M=%lld N=%lld K=%lld)", (long long)M,
+                  (long long)N, (long long)K);
+    const size_t need = gemm_workspace_need(mode, M, N, K);
+    if (need > kNoAllocScratchBytes)
+      return fail(SB200_ERR_TOO_LARGE,
+                  "this problem needs %zu bytes of operand panels but the allocation-free entry point has a fixed %zu-byte "
+                  "scratch; use sb200_gemm_f32 or a smaller problem",
+                  need, kNoAllocScratchBytes);
+  }
+  if (M == 0 || N == 0) return SB200_OK;
+  if (!D || (K > 0 && (!A || !B))) return fail(SB200_ERR_INVALID_VALUE, "null device pointer passed to GEMM");
+  if ((K > 0 && lda < K) || (K > 0 && ldb < N) || ldd < N || (C && ldc < N))
+    return fail(SB200_ERR_INVALID_VALUE, "leading dimension smaller than the row length");
+  if ((A | B | C | D | bias) & 3) return fail(SB200_ERR_ALIGNMENT, "float32 matrices must be 4-byte aligned");
+  NoAllocDevice* nd;
+  int rc = noalloc_setup(dev, &nd);
+  if (rc) return rc;
+  cudaStream_t st = as_stream(stream);
+  GemmParams gp;
+  memset(&gp, 0, sizeof gp);
+  gp.M = static_cast<int>(M);
+  gp.N = static_cast<int>(N);
+  gp.D = as_ptr<float>(D);
+  gp.ldd = ldd;
+  gp.C = as_ptr<const float>(C);
+  gp.ldc = ldc;
+  gp.bias = as_ptr<const float>(bias);
+  gp.alpha = alpha;
+  gp.beta = beta;
+  gp.act = act;
+  gp.status = nd->status;
+  if (K == 0) {
+    long long grid = (M * N + 255) / 256;
+    const long long cap = static_cast<long long>(nd->sm_count) * 16;
+    if (grid > cap) grid = cap;
+    gemm_k0_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(gp);
+    rc = launch_check("gemm_k0_kernel");
+  } else if (mode == SB200_MODE_3XTF32) {
+    rc = launch_gemm_fixed_scratch<3>(*nd, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
+  } else {
+    rc = launch_gemm_fixed_scratch<1>(*nd, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
+  }
+  if (rc) return rc;
+  CU_TRY(cudaStreamSynchronize(st));
+  int flag = 0;
+  CU_TRY(cudaMemcpy(&flag, nd->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (flag != 0) {
+    CU_TRY(cudaMemset(nd->status, 0, sizeof(int)));
+    return fail(SB200_ERR_TIMEOUT, "a bounded device-side wait expired in the GEMM pipeline (site 0x%x)", flag);
+  }
+  return SB200_OK;
+}
