@@ -150,6 +150,15 @@ SB200_API int sb200_kernel_launch(uint64_t kernel, const sb200_arg *args, int na
 SB200_API int sb200_ir_can_fuse(const char *producer, const char *consumer, const char *intermediate, int *result);
 SB200_API int sb200_ir_fuse(const char *producer, const char *consumer, const char *intermediate, char *out, int outlen);
 SB200_API int sb200_ir_fuse_pipeline(const char *const *kernels, int count, char *out, int outlen, char *eliminated, int elimlen);
+/* should_fuse (Sarek_fusion.ml:1068-1098): decision is "Fuse", "DontFuse" or "MaybeFuse" */
+SB200_API int sb200_ir_should_fuse(const char *producer, const char *consumer, const char *intermediate,
+                                   char *decision, int declen, char *reason, int reasonlen);
+/* auto_fuse_pipeline (Sarek_fusion.ml:1133-1165): eliminated arrays comma-separated, skipped reasons one per line */
+SB200_API int sb200_ir_auto_fuse_pipeline(const char *const *kernels, int count, char *out, int outlen,
+                                          char *eliminated, int elimlen, char *skipped, int skiplen);
+/* analyze (Sarek_fusion.ml:340-354): one line per array "read|write NAME one_to_one|stencil[..]|gather|unknown",
+ * then "barriers yes|no" */
+SB200_API int sb200_ir_analyze(const char *kernel, char *out, int outlen);
 
 /* ---- direct operators (what a recognised kernel launch dispatches to) ---
  * D[M x N] = act(alpha * A[M x K] . B[K x N] + beta * C[M x N] + bias[N]),

@@ -76,6 +76,9 @@ SIGNATURES = {
     "sb200_ir_can_fuse": ([C.c_char_p, C.c_char_p, C.c_char_p, p(i32)], i32),
     "sb200_ir_fuse": ([C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, i32], i32),
     "sb200_ir_fuse_pipeline": ([p(C.c_char_p), i32, C.c_char_p, i32, C.c_char_p, i32], i32),
+    "sb200_ir_should_fuse": ([C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, i32, C.c_char_p, i32], i32),
+    "sb200_ir_auto_fuse_pipeline": ([p(C.c_char_p), i32, C.c_char_p, i32, C.c_char_p, i32, C.c_char_p, i32], i32),
+    "sb200_ir_analyze": ([C.c_char_p, C.c_char_p, i32], i32),
     "sb200_gemm_f32": ([i32, u64, i32, i64, i64, i64, u64, i64, u64, i64, u64, i64, f32, u64, i64, f32, u64, i32], i32),
     "sb200_gemm_f32_noalloc": ([i32, u64, i32, i64, i64, i64, u64, i64, u64, i64, u64, i64, f32, u64, i64, f32, u64, i32], i32),
     "sb200_gemm_workspace_bytes": ([i32, i64, i64, i64, p(u64)], i32),

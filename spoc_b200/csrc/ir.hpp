@@ -101,5 +101,10 @@ int ir_fuse(const std::string& producer, const std::string& consumer, const std:
             std::string* err);
 int ir_fuse_pipeline(const std::vector<std::string>& kernels, std::string* out, std::vector<std::string>* eliminated,
                      std::string* err);
+int ir_should_fuse(const std::string& producer, const std::string& consumer, const std::string& inter,
+                   std::string* decision, std::string* reason, std::string* err);
+int ir_auto_fuse_pipeline(const std::vector<std::string>& kernels, std::string* out, std::vector<std::string>* eliminated,
+                          std::vector<std::string>* skipped, std::string* err);
+int ir_analyze(const std::string& kernel, std::string* report, std::string* err);
 
 }  // namespace sb200

@@ -907,6 +907,44 @@ int sb200_ir_fuse_pipeline(const char* const* kernels, int count, char* out, int
   return copy_out(text, out, outlen);
 }
 
+int sb200_ir_should_fuse(const char* producer, const char* consumer, const char* intermediate, char* decision, int declen,
+                         char* reason, int reasonlen) {
+  if (!producer || !consumer || !intermediate) return fail(SB200_ERR_INVALID_VALUE, "null argument");
+  std::string d, r, err;
+  int rc = ir_should_fuse(producer, consumer, intermediate, &d, &r, &err);
+  if (rc) return fail(rc, "%s", err.c_str());
+  if ((rc = copy_out(d, decision, declen))) return rc;
+  return copy_out(r, reason, reasonlen);
+}
+
+int sb200_ir_auto_fuse_pipeline(const char* const* kernels, int count, char* out, int outlen, char* eliminated, int elimlen,
+                                char* skipped, int skiplen) {
+  if (!kernels || count <= 0) return fail(SB200_ERR_INVALID_VALUE, "empty kernel list");
+  std::vector<std::string> ks;
+  for (int i = 0; i < count; ++i) {
+    if (!kernels[i]) return fail(SB200_ERR_INVALID_VALUE, "null kernel text");
+    ks.push_back(kernels[i]);
+  }
+  std::string text, err;
+  std::vector<std::string> elim, skip;
+  int rc = ir_auto_fuse_pipeline(ks, &text, &elim, &skip, &err);
+  if (rc) return fail(rc, "%s", err.c_str());
+  std::string je, js;
+  for (size_t i = 0; i < elim.size(); ++i) je += (i ? "," : "") + elim[i];
+  for (size_t i = 0; i < skip.size(); ++i) js += (i ? "\n" : "") + skip[i];
+  if (eliminated && elimlen > 0 && (rc = copy_out(je, eliminated, elimlen))) return rc;
+  if (skipped && skiplen > 0 && (rc = copy_out(js, skipped, skiplen))) return rc;
+  return copy_out(text, out, outlen);
+}
+
+int sb200_ir_analyze(const char* kernel, char* out, int outlen) {
+  if (!kernel) return fail(SB200_ERR_INVALID_VALUE, "null argument");
+  std::string rep, err;
+  int rc = ir_analyze(kernel, &rep, &err);
+  if (rc) return fail(rc, "%s", err.c_str());
+  return copy_out(rep, out, outlen);
+}
+
 int sb200_gemm_f32(int dev, uint64_t stream, int mode, int64_t M, int64_t N, int64_t K, uint64_t A, int64_t lda, uint64_t B,
                    int64_t ldb, uint64_t D, int64_t ldd, float alpha, uint64_t C, int64_t ldc, float beta, uint64_t bias,
                    int act) {

@@ -1,0 +1,126 @@
+"""The fusion pass on IR text against the behaviour the reference's own tests pin
+(sarek/tests/unit/test_fusion.ml, sarek/tests/e2e/test_fusion_api.ml)."""
+import pytest
+
+from spoc_b200 import fusion as F
+from spoc_b200 import sarek_ir as S
+
+TX = ("intrinsic", ("Gpu",), "thread_idx_x")
+
+
+def kern(name, body, params=()):
+    return S.sx(("kernel", name, ("params",) + tuple(params), ("body", body)))
+
+
+def c_i32(v):
+    return ("const", "i32", v)
+
+
+def scale(name, dst, src, op, k):
+    return kern(name, ("assign", ("elem", dst, TX), ("binop", op, ("read", src, TX), c_i32(k))),
+                [("vec", dst, 1, "i32"), ("vec", src, 2, "i32")])
+
+
+PRODUCER = scale("producer", "temp", "input", "mul", 2)
+CONSUMER = scale("consumer", "output", "temp", "add", 1)
+
+
+def test_analyze_one_to_one():          # test_fusion.ml:21-46
+    info = F.analyze(scale("scale", "output", "input", "mul", 2))
+    assert info["reads"] == {"input": "one_to_one"} and info["writes"] == {"output": "one_to_one"}
+    assert not info["has_barriers"]
+
+
+def test_analyze_with_barrier():        # test_fusion.ml:49-76
+    body = ("seq", ("assign", ("elem", "shared", TX), ("read", "input", TX)), ("barrier",),
+            ("assign", ("elem", "output", TX), ("read", "shared", TX)))
+    assert F.analyze(kern("with_barrier", body))["has_barriers"]
+
+
+def test_can_fuse_compatible_and_barrier():   # test_fusion.ml:79-156
+    assert F.can_fuse(PRODUCER, CONSUMER, "temp")
+    with_barrier = kern("producer", ("seq", ("assign", ("elem", "temp", TX), ("read", "input", TX)), ("barrier",)))
+    assert not F.can_fuse(with_barrier, CONSUMER, "temp")
+    assert not F.can_fuse(PRODUCER, CONSUMER, "other")
+
+
+def test_fuse_simple():                 # test_fusion.ml:159-202
+    fused = F.fuse(PRODUCER, CONSUMER, "temp")
+    assert fused.startswith("(kernel consumer_fused ")
+    info = F.analyze(fused)
+    assert "temp" not in info["reads"] and "input" in info["reads"] and "output" in info["writes"]
+    # the intermediate leaves the parameter list, the producer's input joins it
+    assert "(vec temp" not in fused and "(vec input" in fused
+    # output[i] = (input[i] * 2) + 1
+    assert "(binop add (binop mul (read input" in fused
+
+
+def test_fuse_pipeline_eliminates_both_intermediates():   # test_fusion.ml:205-267, test_fusion_api.ml:52-81
+    k1, k2, k3 = scale("k1", "a", "input", "mul", 2), scale("k2", "b", "a", "add", 1), scale("k3", "output", "b", "mul", 3)
+    fused, eliminated = F.fuse_pipeline([k1, k2, k3])
+    assert set(eliminated) == {"a", "b"} and eliminated == ["b", "a"]   # newest first, like the reference's cons
+    info = F.analyze(fused)
+    assert "input" in info["reads"] and "output" in info["writes"] and "a" not in info["reads"] and "b" not in info["reads"]
+    assert fused.startswith("(kernel k3_fused ")   # consumer name + "_fused" at each step: k2_fused, then k3_fused
+    single, none = F.fuse_pipeline([k1])
+    assert none == [] and single.startswith("(kernel k1 ")
+
+
+def test_fuse_leaves_consumer_alone_when_write_is_conditional():   # find_write_expr, Sarek_fusion.ml:360-378
+    guarded = kern("producer", ("sif", ("binop", "lt", TX, c_i32(10)), ("assign", ("elem", "temp", TX), ("read", "input", TX))))
+    out = F.fuse(guarded, CONSUMER, "temp")
+    assert out.startswith("(kernel consumer ") and "(read temp" in out
+
+
+def stencil_consumer(offsets):
+    e = None
+    for o in offsets:
+        idx = TX if o == 0 else ("binop", "add" if o > 0 else "sub", TX, c_i32(abs(o)))
+        r = ("read", "temp", idx)
+        e = r if e is None else ("binop", "add", e, r)
+    return kern("consumer", ("assign", ("elem", "output", TX), e))
+
+
+def test_should_fuse_decisions():       # test_fusion.ml:712-833
+    assert F.should_fuse(PRODUCER, CONSUMER, "temp")[0] == "Fuse"
+    with_barrier = kern("producer", ("seq", ("assign", ("elem", "temp", TX), ("read", "input", TX)), ("barrier",)))
+    assert F.should_fuse(with_barrier, CONSUMER, "temp") == ("DontFuse", "Barrier prevents fusion")
+    assert F.should_fuse(PRODUCER, stencil_consumer([-1, 0, 1]), "temp")[0] == "MaybeFuse"
+    assert F.should_fuse(PRODUCER, stencil_consumer([-2, -1, 0, 1, 2]), "temp")[0] == "DontFuse"
+    gather = kern("consumer", ("assign", ("elem", "output", TX),
+                               ("binop", "add", ("read", "temp", ("read", "index", TX)), ("read", "temp", TX))))
+    assert F.should_fuse(PRODUCER, gather, "temp") == ("DontFuse", "Gather pattern - keep separate")
+    assert F.analyze(stencil_consumer([-1, 0, 1]))["reads"]["temp"] == "stencil[-1,0,1]"
+
+
+def test_auto_fuse_pipeline():          # test_fusion.ml:836-943
+    k1, k2, k3 = scale("k1", "a", "input", "mul", 2), scale("k2", "b", "a", "add", 1), scale("k3", "output", "b", "mul", 3)
+    fused, eliminated, skipped = F.auto_fuse_pipeline([k1, k2, k3])
+    assert set(eliminated) == {"a", "b"} and skipped == []
+    k_st = kern("k2", ("assign", ("elem", "output", TX),
+                       ("binop", "add", ("read", "temp", ("binop", "sub", TX, c_i32(1))),
+                        ("read", "temp", ("binop", "add", TX, c_i32(1))))))
+    _, eliminated, skipped = F.auto_fuse_pipeline([PRODUCER, k_st])
+    assert eliminated == [] and len(skipped) == 1
+
+
+def test_config2_chain_behaves_like_the_reference():
+    """a = b + 3c ; d = a*a + b: the consumer reads `a` twice, which the reference classifies as a
+    stencil with offsets [0] (Sarek_fusion.ml:301-322): can_fuse is false, should_fuse says MaybeFuse,
+    fuse_pipeline skips it, and a direct fuse rewrites both reads."""
+    p, c = S.triad_producer_ir(3.0), S.square_add_consumer_ir()
+    assert F.analyze(c)["reads"]["a"] == "stencil[0]"
+    assert not F.can_fuse(p, c, "a")
+    assert F.should_fuse(p, c, "a")[0] == "MaybeFuse"
+    assert F.fuse_pipeline([p, c])[1] == []
+    fused = F.fuse(p, c, "a")
+    assert "(read a" not in fused and "(vec a" not in fused and fused.startswith("(kernel square_add_fused ")
+    assert fused == S.chain_fused_ir(3.0)
+
+
+def test_errors():
+    from spoc_b200 import BackendError
+    with pytest.raises(BackendError):
+        F.fuse("(kernel", CONSUMER, "temp")
+    with pytest.raises(BackendError):
+        F.fuse_pipeline([])

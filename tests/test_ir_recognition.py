@@ -1,0 +1,152 @@
+"""IR text -> operator recognition, argument binding and the C ABI's behaviour without a GPU."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from spoc_b200 import Backend, BackendError, UnsupportedConstruct, dims1d, sarek_ir as S
+from spoc_b200 import _lib as L
+
+EPI = dict(alpha=1.5, beta=0.5, c="c", bias="bias", relu=True)
+
+
+def compile_(ir):
+    b = Backend()
+    return b.Kernel.compile(b.Device.T(0, "none", 0, (10, 0), 148, 0, 0), name="sarek_kern", source=ir)
+
+
+@pytest.mark.parametrize("ir,kind,needle", [
+    (S.vector_add_ir(), L.KIND_MAP, "map:vector_add guarded idx=global_x"),
+    (S.stream_triad_ir(), L.KIND_MAP, "map:stream_triad guarded"),
+    (S.chain_fused_ir(), L.KIND_MAP, "map:triad_square_chain unguarded"),
+    (S.triad_producer_ir(index="thread_idx_x"), L.KIND_MAP, "idx=thread_idx_x"),
+    (S.matmul_naive_ir(), L.KIND_GEMM_NAIVE, "gemm:naive A=a B=b D=c m=m n=n k=k"),
+    (S.matmul_tiled_ir(), L.KIND_GEMM_TILED, "gemm:tiled A=a B=b D=c m=m n=n k=k tile=16"),
+    (S.matmul_naive_ir(epilogue=EPI), L.KIND_GEMM_NAIVE, "alpha=1.5 C=c beta=0.5 bias=bias act=relu"),
+    (S.matmul_tiled_ir(epilogue=EPI), L.KIND_GEMM_TILED, "D=d m=m n=n k=k alpha=1.5 C=c beta=0.5 bias=bias act=relu tile=16"),
+    (S.matmul_tiled_ir(epilogue=dict(bias="bias")), L.KIND_GEMM_TILED, "bias=bias tile=16"),
+])
+def test_reference_kernels_are_recognised(ir, kind, needle):
+    k = compile_(ir)
+    assert k.kind == kind
+    assert needle in k.describe()
+
+
+def test_commuted_operands_and_expanded_thread_id_are_recognised():
+    b = S.Builder()
+    p = b.params([("vec", "a", "f32"), ("vec", "b", "f32"), ("vec", "c", "f32"), ("scalar", "s", "f32"), ("scalar", "n", "i32")])
+    tid = b.binop("add", b.binop("mul", b.intr("block_idx_x"), b.intr("block_dim_x")), b.intr("thread_idx_x"))
+    body = b.let("i", "i32", tid, lambda: ("sif", b.binop("lt", b.evar("i"), b.evar("n")),
+                 ("assign", ("elem", "a", b.evar("i")),
+                  b.binop("add", b.binop("mul", b.evar("s"), b.read("c", b.evar("i"))), b.read("b", b.evar("i"))))))
+    k = compile_(S.sx(("kernel", "t", p, ("body", body))))
+    assert "map:stream_triad guarded idx=global_x" in k.describe()
+
+
+@pytest.mark.parametrize("ir,why", [
+    (S.square_add_consumer_ir(), "element expression"),          # a*a+b alone: not one of the compiled shapes
+    ("(kernel k (params (vec a 1 f32)) (body (while (const bool true) (empty))))", "while"),
+    ("(kernel k (params (vec a 1 i32) (vec b 2 i32)) (body (assign (elem a (intrinsic (Gpu) thread_idx_x)) (read b (intrinsic (Gpu) thread_idx_x)))))", "float32"),
+])
+def test_unrecognised_kernels_raise_unsupported_construct(ir, why):
+    with pytest.raises(UnsupportedConstruct) as e:
+        compile_(ir)
+    assert e.value.code == L.ERR_UNSUPPORTED and why in e.value.message
+
+
+@pytest.mark.parametrize("text", ["", "(kernel", "(kernel k (params) (body (empty))) trailing", "(notakernel)", "(kernel k (params (vec a)) (body (empty)))"])
+def test_malformed_ir_is_a_parse_error(text):
+    with pytest.raises(BackendError) as e:
+        compile_(text)
+    assert e.value.code == L.ERR_PARSE
+
+
+def test_argument_binding_errors_are_reported_before_any_device_work():
+    b = Backend()
+    k = compile_(S.stream_triad_ir())
+    buf = b.Memory.Buffer(0, 4096, 16, 4)
+
+    def launch(build):
+        ka = b.Kernel.create_args()
+        build(ka)
+        b.Kernel.launch(k, args=ka, grid=dims1d(1), block=dims1d(32))
+
+    def good_prefix(ka):
+        for _ in range(3):
+            b.Kernel.set_arg_buffer(ka, 0, buf)
+            b.Kernel.set_arg_int32(ka, 0, 16)
+
+    with pytest.raises(BackendError) as e:   # too few
+        launch(good_prefix)
+    assert e.value.code == L.ERR_ARGS
+
+    def wrong_scalar(ka):
+        good_prefix(ka)
+        b.Kernel.set_arg_int32(ka, 0, 3)     # scalar is float32
+        b.Kernel.set_arg_int32(ka, 0, 16)
+    with pytest.raises(BackendError) as e:
+        launch(wrong_scalar)
+    assert e.value.code == L.ERR_ARGS
+
+    def missing_length(ka):
+        b.Kernel.set_arg_buffer(ka, 0, buf)
+        b.Kernel.set_arg_buffer(ka, 0, buf)
+    with pytest.raises(BackendError) as e:
+        launch(missing_length)
+    assert e.value.code == L.ERR_ARGS
+
+    def too_many(ka):
+        good_prefix(ka)
+        b.Kernel.set_arg_float32(ka, 0, 3.0)
+        b.Kernel.set_arg_int32(ka, 0, 16)
+        b.Kernel.set_arg_int32(ka, 0, 16)
+    with pytest.raises(BackendError) as e:
+        launch(too_many)
+    assert e.value.code == L.ERR_ARGS
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(os.path.dirname(L.HERE), "include", "sb200.h")).read()
+    declared = set(re.findall(r"SB200_API\s+(?:const\s+)?\w+\s*\*?\s*(sb200_\w+)\s*\(", header))
+    assert len(declared) >= 45
+    lib = L.load()
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in sb200.h but not exported"
+    assert declared == set(L.SIGNATURES), declared ^ set(L.SIGNATURES)
+    assert lib.sb200_version() == 100
+
+
+def test_no_gpu_means_errors_not_fallbacks():
+    """Without a device the library reports it; nothing computes on the CPU."""
+    b = Backend()
+    if b.Device.count() > 0:
+        pytest.skip("a GPU is present")
+    lib = L.load()
+    assert not b.is_available()
+    assert lib.sb200_init() == L.ERR_NO_DEVICE
+    assert lib.sb200_vector_add_f32(0, 0, 16, 16, 16, 4) == L.ERR_NO_DEVICE
+    assert lib.sb200_gemm_f32(0, 0, 3, 4, 4, 4, 16, 4, 16, 4, 16, 4, 1.0, 0, 0, 0.0, 0, 0) == L.ERR_NO_DEVICE
+    assert lib.sb200_gemm_f32_noalloc(0, 0, 3, 4, 4, 4, 16, 4, 16, 4, 16, 4, 1.0, 0, 0, 0.0, 0, 0) == L.ERR_NO_DEVICE
+    p = C.c_uint64(0)
+    assert lib.sb200_mem_alloc(0, 64, C.byref(p)) == L.ERR_NO_DEVICE
+    assert b"CUDA" in lib.sb200_last_error_string() or b"device" in lib.sb200_last_error_string()
+    n = C.c_uint64(0)
+    assert lib.sb200_gemm_workspace_bytes(3, 8192, 8192, 8192, C.byref(n)) == 0 and n.value == 4 * 8192 * 8192 * 4
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(L, "_lib", None)
+    monkeypatch.setattr(L, "LIB_PATH", str(tmp_path / "libsarek_b200.so"))
+    with pytest.raises(L.LibraryMissing):
+        L.load()
+
+
+def test_mode_setting():
+    b = Backend()
+    b.set_mode(L.MODE_TF32)
+    assert b.get_mode() == L.MODE_TF32
+    b.set_mode(L.MODE_3XTF32)
+    assert b.get_mode() == L.MODE_3XTF32
+    with pytest.raises(BackendError):
+        b.set_mode(2)
