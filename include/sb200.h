@@ -205,6 +205,11 @@ SB200_API int sb200_chain_triad_square_f32(int dev, uint64_t stream, uint64_t d,
  * (also read once from the environment variable SAREK_B200_MODE=3xtf32|tf32) */
 SB200_API int sb200_set_mode(int mode);
 SB200_API int sb200_get_mode(int *mode);
+/* which tensor-core kernel sb200_gemm_f32 launches: 0 = automatic (CTA pairs on
+ * 256x256 tiles when M > 128, else single-CTA 128x256 tiles), 1 = always
+ * single-CTA tiles, 2 = always CTA pairs.  Also SAREK_B200_GEMM=single|pair.
+ * Results of the two kernels agree to the last bit. */
+SB200_API int sb200_set_gemm_variant(int variant);
 
 /* seeded synthetic data written on the device: kind 0 U[-1,1), 1 U[-0.1,0.1),
  * 2 N(0,sigma); element i of the stream is a pure function of (seed, stream_id,

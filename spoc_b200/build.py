@@ -14,7 +14,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsarek_b200.so")
 
 SOURCES = ["sb200_shim.cu", "ir.cc", "fusion.cc"]
-HEADERS = ["gemm_tcgen05.cuh", "map_fused.cuh", "ptx_sm100.cuh", "ir.hpp",
+HEADERS = ["gemm_tcgen05.cuh", "gemm_tcgen05_pair.cuh", "map_fused.cuh", "ptx_sm100.cuh", "ir.hpp",
            os.path.join("..", "..", "include", "sb200.h")]
 
 NVCC_FLAGS = [

@@ -1,0 +1,270 @@
+// gemm_tcgen05_pair.cuh — the fp32 GEMM on CTA pairs (tcgen05 cta_group::2).
+//
+// Same operator, operand panels and epilogue as gemm_tcgen05.cuh; what changes
+// is the tile: two thread blocks on neighbouring SMs form a cluster and compute
+// one 256x256 tile of D together.  Each block owns 128 rows of the tile (its
+// own 128x32 A tile and its own 128x256 fp32 accumulator in tensor memory) and
+// loads only half of the B tile (128 of its 256 N-rows); the MMA unit reads the
+// other half from the peer's shared memory.  Per block and k-block that is
+// 32 KiB of TMA traffic instead of 48 KiB for the same 512 MMA cycles, so the
+// shared-memory ring holds 6 stages instead of 4 (TF32 mode; 3 instead of 2 in
+// 3xTF32 mode): less L2 bandwidth and 5/6 of 192 KiB in flight per SM.
+//
+// Roles per block: warp 0 lane 0 loads this block's A tile and B half with TMA
+// (completion counted on the leader's `full` barrier); warp 1 lane 0 of the
+// leader block (cluster rank 0) issues the 256x256x8 MMAs for both blocks and
+// commits to the `empty` and `tmem_full` barriers of both; warps 2-5 of both
+// blocks run the epilogue on their own accumulator rows and hand the
+// accumulator back by arriving on the leader's `tmem_empty` barrier.
+// No cluster-multicast load is used anywhere.
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace sb200 {
+
+constexpr int PAIR_BM = 256;        // tile rows (128 per block)
+constexpr int PAIR_BN = 256;        // tile columns
+constexpr int PAIR_GROUP_M = 8;     // rasterisation: bands of 8 row tiles
+constexpr uint32_t PAIR_A_BYTES = 128 * GEMM_BK * 4;  // this block's A rows: 16 KiB
+constexpr uint32_t PAIR_B_BYTES = 128 * GEMM_BK * 4;  // this block's half of B: 16 KiB
+
+template <int MODE>
+struct PairCfg {
+  static constexpr int kOperands = (MODE == 3) ? 2 : 1;
+  static constexpr int kStages = (MODE == 3) ? 3 : 6;
+  static constexpr uint32_t kStageBytes = kOperands * (PAIR_A_BYTES + PAIR_B_BYTES);
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + GEMM_EPI_BUF_BYTES + GEMM_CTRL_BYTES + 1024;
+};
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int band_tiles = PAIR_GROUP_M * tiles_n;
+  const int band = tile / band_tiles;
+  const int within = tile - band * band_tiles;
+  const int first_m = band * PAIR_GROUP_M;
+  const int band_m = min(PAIR_GROUP_M, tiles_m - first_m);
+  tm = first_m + within % band_m;
+  tn = within / band_m;
+}
+
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_b_hi,
+                 const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
+                 const GemmParams p) {
+  using Cfg = PairCfg<MODE>;
+  constexpr int STAGES = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_base = smem;
+  float* epi_buf = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes + GEMM_EPI_BUF_BYTES);
+  uint64_t* full_bar = bars;                        // used in the leader only
+  uint64_t* empty_bar = bars + STAGES;              // one set per block
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;      // one set per block
+  uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2; // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const uint32_t peer = rank ^ 1u;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 8);  // four epilogue warps in each of the two blocks
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a_hi);
+    tma_prefetch_desc(&map_b_hi);
+    if (MODE == 3) {
+      tma_prefetch_desc(&map_a_lo);
+      tma_prefetch_desc(&map_b_lo);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), GEMM_TMEM_COLS);
+    tmem_relinquish_pair();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  // both blocks' barriers exist before any signal crosses between them
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        int tm, tn;
+        pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * PAIR_BM + static_cast<int>(rank) * 128;  // this block's rows of A
+        const int n0 = tn * PAIR_BN + static_cast<int>(rank) * 128;  // this block's half of B's N-rows
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
+            atomicCAS(p.status, 0, 0x1100 | (rank << 4) | stage);
+            ok = false;
+            break;
+          }
+          // the leader arms its barrier with the bytes of both blocks
+          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * Cfg::kStageBytes);
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          uint8_t* sp = stage_base + stage * Cfg::kStageBytes;
+          tma_load_2d_pair(smem_u32(sp), &map_a_hi, bar, kb * GEMM_BK, m0);
+          tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES), &map_b_hi, bar, kb * GEMM_BK, n0);
+          if (MODE == 3) {
+            tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES + PAIR_B_BYTES), &map_a_lo, bar, kb * GEMM_BK, m0);
+            tma_load_2d_pair(smem_u32(sp + 2 * PAIR_A_BYTES + PAIR_B_BYTES), &map_b_lo, bar, kb * GEMM_BK, n0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------- MMA issuer (leader block)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(PAIR_BM, PAIR_BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local_tile = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
+        const int acc = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        if (!mbar_wait_bounded(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) {
+          atomicCAS(p.status, 0, 0x1200 | acc);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * PAIR_BN;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!mbar_wait_bounded(smem_u32(&full_bar[stage]), phase, abort_flag)) {
+            atomicCAS(p.status, 0, 0x1300 | stage);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa_hi = smem_u32(stage_base + stage * Cfg::kStageBytes);
+          const uint32_t sb_hi = sa_hi + PAIR_A_BYTES;
+          const uint32_t sa_lo = sb_hi + PAIR_B_BYTES;
+          const uint32_t sb_lo = sa_lo + PAIR_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
+            const uint32_t koff = k * GEMM_UMMA_K * 4;
+            const uint64_t da_hi = umma_desc_k_sw128(sa_hi + koff);
+            const uint64_t db_hi = umma_desc_k_sw128(sb_hi + koff);
+            const uint32_t accumulate = (kb | k) ? 1u : 0u;
+            if (MODE == 3) {
+              const uint64_t da_lo = umma_desc_k_sw128(sa_lo + koff);
+              const uint64_t db_lo = umma_desc_k_sw128(sb_lo + koff);
+              umma_tf32_pair(tmem_d, da_lo, db_hi, idesc, accumulate);
+              umma_tf32_pair(tmem_d, da_hi, db_lo, idesc, 1u);
+              umma_tf32_pair(tmem_d, da_hi, db_hi, idesc, 1u);
+            } else {
+              umma_tf32_pair(tmem_d, da_hi, db_hi, idesc, accumulate);
+            }
+          }
+          // the stage is free in both blocks once these MMAs retire
+          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 0));
+          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) {
+          umma_commit_pair(map_to_cta(smem_u32(&tmem_full_bar[acc]), 0));
+          umma_commit_pair(map_to_cta(smem_u32(&tmem_full_bar[acc]), 1));
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // --------------------------------------------------------- epilogue
+    const int quarter = warp & 3;
+    float* tbuf = epi_buf + (warp - 2) * (32 * 33);
+    int local_tile = 0;
+    bool ok = true;
+    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
+      const int acc = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      int tm, tn;
+      pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int row0 = tm * PAIR_BM + static_cast<int>(rank) * 128 + quarter * 32;
+      const int n0 = tn * PAIR_BN;
+      const bool landed = mbar_wait_bounded(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag);
+      if (!__all_sync(0xffffffffu, landed)) {
+        if (lane == 0) atomicCAS(p.status, 0, 0x1400 | (rank << 4) | acc);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int rows_here = min(32, p.M - row0);
+#pragma unroll 1
+      for (int chunk = 0; chunk < PAIR_BN / 32; ++chunk) {
+        const int col = n0 + chunk * 32 + lane;
+        if (n0 + chunk * 32 >= p.N) break;  // warp-uniform
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * PAIR_BN + chunk * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) tbuf[lane * 33 + j] = __uint_as_float(v[j]);
+        __syncwarp();
+        if (col < p.N) {
+          const float bias_v = p.bias ? p.bias[col] : 0.0f;
+          for (int rr = 0; rr < rows_here; ++rr) {
+            const long long row = row0 + rr;
+            float x = p.alpha * tbuf[rr * 33 + lane];
+            if (p.C) x = fmaf(p.beta, p.C[row * p.ldc + col], x);
+            x += bias_v;
+            if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
+            p.D[row * p.ldd + col] = x;
+          }
+        }
+        __syncwarp();
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
+    }
+    __syncwarp();
+  }
+
+  // Neither block may retire, or free tensor memory, while its peer can still
+  // signal its barriers, read its shared memory or write its accumulators.
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, GEMM_TMEM_COLS);
+  }
+  (void)peer;
+}
+
+}  // namespace sb200

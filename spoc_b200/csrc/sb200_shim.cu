@@ -23,6 +23,7 @@
 
 #include "../../include/sb200.h"
 #include "gemm_tcgen05.cuh"
+#include "gemm_tcgen05_pair.cuh"
 #include "ir.hpp"
 #include "map_fused.cuh"
 
@@ -85,6 +86,7 @@ struct DeviceState {
 };
 DeviceState g_dev[kMaxDevices];
 std::atomic<int> g_profiling{0};
+std::atomic<int> g_gemm_variant{-1};  // -1 = not yet read from the environment; 0 auto, 1 single-CTA tiles, 2 CTA pairs
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -326,22 +328,65 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
     if (rc) return rc;
   }
 
+  int variant = g_gemm_variant.load();
+  if (variant < 0) {
+    const char* e = getenv("SAREK_B200_GEMM");
+    variant = (e && !strcmp(e, "single")) ? 1 : (e && !strcmp(e, "pair")) ? 2 : 0;
+    g_gemm_variant.store(variant);
+  }
+  // CTA pairs work on 256-row tiles; a problem with at most 128 rows would leave the second block idle
+  const bool pair = variant == 2 || (variant == 0 && M > GEMM_BM);
+
   CUtensorMap ma_hi, mb_hi, ma_lo, mb_lo;
+  const int b_box_rows = pair ? 128 : GEMM_BN;
   if ((rc = encode_panel_map(&ma_hi, a_hi, kp, M, GEMM_BM))) return rc;
-  if ((rc = encode_panel_map(&mb_hi, b_hi, kp, N, GEMM_BN))) return rc;
+  if ((rc = encode_panel_map(&mb_hi, b_hi, kp, N, b_box_rows))) return rc;
   if ((rc = encode_panel_map(&ma_lo, a_lo, kp, M, GEMM_BM))) return rc;
-  if ((rc = encode_panel_map(&mb_lo, b_lo, kp, N, GEMM_BN))) return rc;
+  if ((rc = encode_panel_map(&mb_lo, b_lo, kp, N, b_box_rows))) return rc;
 
   GemmParams gp = gp_in;
   gp.num_k_blocks = static_cast<int>(kp / GEMM_BK);
-  gp.tiles_m = static_cast<int>((M + GEMM_BM - 1) / GEMM_BM);
-  gp.tiles_n = static_cast<int>((N + GEMM_BN - 1) / GEMM_BN);
   gp.status = d.status;
-  const long long tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n;
-  const unsigned grid = static_cast<unsigned>(tiles < d.sm_count ? tiles : d.sm_count);
   if (prof) CU_TRY(cudaEventRecord(rec.e1, st));
-  gemm_tf32_kernel<MODE><<<grid, GEMM_THREADS, Cfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo, mb_lo, gp);
-  rc = launch_check("gemm_tf32_kernel");
+  if (pair) {
+    using PCfg = PairCfg<MODE>;
+    CU_TRY(cudaFuncSetAttribute(gemm_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                static_cast<int>(PCfg::kSmemBytes)));
+    gp.tiles_m = static_cast<int>((M + PAIR_BM - 1) / PAIR_BM);
+    gp.tiles_n = static_cast<int>((N + PAIR_BN - 1) / PAIR_BN);
+    // how many 2-block clusters can be resident at once with this much shared memory
+    int max_clusters = 0;
+    {
+      cudaLaunchConfig_t cfg;
+      memset(&cfg, 0, sizeof cfg);
+      cfg.gridDim = dim3(static_cast<unsigned>(d.sm_count & ~1), 1, 1);
+      cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+      cfg.dynamicSmemBytes = PCfg::kSmemBytes;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      if (cudaOccupancyMaxActiveClusters(&max_clusters, gemm_pair_kernel<MODE>, &cfg) != cudaSuccess || max_clusters <= 0) {
+        cudaGetLastError();
+        max_clusters = d.sm_count / 2;
+      }
+    }
+    const long long tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n;
+    const long long pairs = tiles < max_clusters ? tiles : max_clusters;
+    gemm_pair_kernel<MODE><<<static_cast<unsigned>(2 * pairs), GEMM_THREADS, PCfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo, mb_lo,
+                                                                                                    gp);
+    rc = launch_check("gemm_pair_kernel");
+  } else {
+    gp.tiles_m = static_cast<int>((M + GEMM_BM - 1) / GEMM_BM);
+    gp.tiles_n = static_cast<int>((N + GEMM_BN - 1) / GEMM_BN);
+    const long long tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n;
+    const unsigned grid = static_cast<unsigned>(tiles < d.sm_count ? tiles : d.sm_count);
+    gemm_tf32_kernel<MODE><<<grid, GEMM_THREADS, Cfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo, mb_lo, gp);
+    rc = launch_check("gemm_tf32_kernel");
+  }
   if (prof) {
     CU_TRY(cudaEventRecord(rec.e2, st));
     std::lock_guard<std::mutex> lock(d.mu);
@@ -986,6 +1031,12 @@ int sb200_chain_triad_square_f32(int dev, uint64_t stream, uint64_t dd, uint64_t
 int sb200_set_mode(int mode) {
   if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   g_mode.store(mode);
+  return SB200_OK;
+}
+
+int sb200_set_gemm_variant(int variant) {
+  if (variant < 0 || variant > 2) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM variant %d (0 auto, 1 single, 2 pair)", variant);
+  g_gemm_variant.store(variant);
   return SB200_OK;
 }
 

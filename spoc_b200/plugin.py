@@ -413,6 +413,10 @@ class Backend:
         _check(L.load().sb200_get_mode(C.byref(m)))
         return m.value
 
+    def set_gemm_variant(self, variant: int) -> None:
+        """0 automatic, 1 single-CTA tiles, 2 CTA pairs."""
+        _check(L.load().sb200_set_gemm_variant(variant))
+
     def launch_count(self) -> int:
         n = C.c_uint64(0)
         _check(L.load().sb200_launch_count(C.byref(n)))

@@ -17,6 +17,14 @@ from tests.gpu_util import CANARY, Dev, dev_from, gemm
 pytestmark = pytest.mark.gpu
 
 MODES = [L.MODE_3XTF32, L.MODE_TF32]
+VARIANTS = [1, 2]  # 1 = single-CTA 128x256 tiles, 2 = CTA pairs on 256x256 tiles
+
+
+@pytest.fixture(params=VARIANTS, ids=["single", "pair"])
+def variant(request, backend):
+    backend.set_gemm_variant(request.param)
+    yield request.param
+    backend.set_gemm_variant(0)
 
 
 def tol(mode, K):
@@ -32,7 +40,7 @@ SHAPES = [(1, 1, 1), (5, 7, 3), (16, 16, 16), (128, 256, 32), (128, 256, 64), (1
 
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("shape", SHAPES)
-def test_plain_product_matches_oracle(backend, device, mode, shape):
+def test_plain_product_matches_oracle(backend, device, mode, shape, variant):
     M, N, K = shape
     a, b = O.fill(M * K, 1, 1), O.fill(K * N, 1, 2)
     A, B, D = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * N)
@@ -48,19 +56,19 @@ def test_plain_product_matches_oracle(backend, device, mode, shape):
 
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("shape", [(130, 260, 96), (256, 256, 256), (77, 513, 200)])
-@pytest.mark.parametrize("variant", ["full", "beta_only", "bias_only", "relu_only", "alias"])
-def test_fused_epilogue_matches_oracle(backend, device, mode, shape, variant):
+@pytest.mark.parametrize("epi", ["full", "beta_only", "bias_only", "relu_only", "alias"])
+def test_fused_epilogue_matches_oracle(backend, device, mode, shape, epi, variant):
     M, N, K = shape
     a, b, c = O.fill(M * K, 2, 1), O.fill(K * N, 2, 2), O.fill(M * N, 2, 3)
     bias = O.fill(N, 2, 4, kind=1)
-    use_c = variant in ("full", "beta_only", "alias")
-    use_bias = variant in ("full", "bias_only", "alias")
-    act = 1 if variant in ("full", "relu_only", "alias") else 0
-    alpha, beta = (1.5, 0.5) if variant in ("full", "alias") else (1.0, 0.25 if use_c else 0.0)
+    use_c = epi in ("full", "beta_only", "alias")
+    use_bias = epi in ("full", "bias_only", "alias")
+    act = 1 if epi in ("full", "relu_only", "alias") else 0
+    alpha, beta = (1.5, 0.5) if epi in ("full", "alias") else (1.0, 0.25 if use_c else 0.0)
     A, B = dev_from(backend, device, a), dev_from(backend, device, b)
     Cd = dev_from(backend, device, c) if use_c else None
     Bi = dev_from(backend, device, bias) if use_bias else None
-    D = Cd if variant == "alias" else Dev(backend, device, M * N)
+    D = Cd if epi == "alias" else Dev(backend, device, M * N)
     try:
         gemm(backend, device, mode, M, N, K, A, B, D, alpha=alpha, C_=Cd, beta=beta, bias=Bi, act=act)
         got = D.download().reshape(M, N)
@@ -72,7 +80,7 @@ def test_fused_epilogue_matches_oracle(backend, device, mode, shape, variant):
 
 
 @pytest.mark.parametrize("mode", MODES)
-def test_small_integer_operands_are_bit_exact(backend, device, mode):
+def test_small_integer_operands_are_bit_exact(backend, device, mode, variant):
     """Operands in {-4..4}: every product and partial sum is exact in TF32 and fp32, so the GPU
     result must equal the oracle bit for bit whatever the summation order."""
     M, N, K = 384, 768, 544
@@ -86,6 +94,24 @@ def test_small_integer_operands_are_bit_exact(backend, device, mode):
         assert np.array_equal(D.download().reshape(M, N), ref)
     finally:
         for x in (A, B, D):
+            x.free()
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_single_and_pair_kernels_agree_bit_for_bit(backend, device, mode):
+    """Both kernels sum k ascending into one fp32 accumulator per element, so they must agree exactly."""
+    M, N, K = 700, 900, 1000
+    a, b = O.fill(M * K, 8, 1), O.fill(K * N, 8, 2)
+    A, B, D1, D2 = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * N), Dev(backend, device, M * N)
+    try:
+        backend.set_gemm_variant(1)
+        gemm(backend, device, mode, M, N, K, A, B, D1)
+        backend.set_gemm_variant(2)
+        gemm(backend, device, mode, M, N, K, A, B, D2)
+        assert np.array_equal(D1.download(), D2.download())
+    finally:
+        backend.set_gemm_variant(0)
+        for x in (A, B, D1, D2):
             x.free()
 
 
@@ -213,7 +239,7 @@ def test_epilogue_ir(backend, device, shape_kind, mode):
 
 
 @pytest.mark.parametrize("mode", MODES)
-def test_config_1024_cubed_full_compare(backend, device, mode):
+def test_config_1024_cubed_full_compare(backend, device, mode, variant):
     """M=N=K=1024, A and B uniform [-1,1) from seed, C zero-initialised: every element."""
     M = N = K = 1024
     a, b = O.fill(M * K, 20260101, 1), O.fill(K * N, 20260101, 2)
