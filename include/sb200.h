@@ -190,6 +190,17 @@ SB200_API int sb200_gemm_f32_noalloc(int dev, uint64_t stream, int mode,
                                      uint64_t D, int64_t ldd,
                                      float alpha, uint64_t C, int64_t ldc, float beta,
                                      uint64_t bias, int act);
+/* The same operator on HOST operands (pinned memory for full overlap; pageable
+ * memory works but serialises the copies).  Replaces the reference's sequence
+ * Transfer.to_device of every argument, launch, Transfer.to_cpu of the result
+ * (sarek/core/Transfer.ml:229-322, sarek/sarek/Execute.ml:520-543) with one call
+ * in which host-to-device copies, the GEMM of the row blocks that have arrived
+ * and device-to-host copies of finished blocks overlap.  Returns when D is
+ * complete in host memory. */
+SB200_API int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int64_t K,
+                                  const float *A, int64_t lda, const float *B, int64_t ldb,
+                                  float *D, int64_t ldd, float alpha, const float *C, int64_t ldc,
+                                  float beta, const float *bias, int act);
 /* bytes of library-owned scratch sb200_gemm_f32 needs for these sizes */
 SB200_API int sb200_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, uint64_t *bytes);
 

@@ -81,6 +81,8 @@ SIGNATURES = {
     "sb200_ir_analyze": ([C.c_char_p, C.c_char_p, i32], i32),
     "sb200_gemm_f32": ([i32, u64, i32, i64, i64, i64, u64, i64, u64, i64, u64, i64, f32, u64, i64, f32, u64, i32], i32),
     "sb200_gemm_f32_noalloc": ([i32, u64, i32, i64, i64, i64, u64, i64, u64, i64, u64, i64, f32, u64, i64, f32, u64, i32], i32),
+    "sb200_gemm_f32_host": ([i32, i32, i64, i64, i64, C.c_void_p, i64, C.c_void_p, i64, C.c_void_p, i64, f32, C.c_void_p, i64, f32,
+                             C.c_void_p, i32], i32),
     "sb200_gemm_workspace_bytes": ([i32, i64, i64, i64, p(u64)], i32),
     "sb200_vector_add_f32": ([i32, u64, u64, u64, u64, i64], i32),
     "sb200_stream_triad_f32": ([i32, u64, u64, u64, u64, f32, i64], i32),

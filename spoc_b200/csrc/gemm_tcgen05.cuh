@@ -257,13 +257,33 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         __syncwarp();
         if (col < p.N) {
           const float bias_v = p.bias ? p.bias[col] : 0.0f;
-          for (int rr = 0; rr < rows_here; ++rr) {
-            const long long row = row0 + rr;
-            float x = p.alpha * tbuf[rr * 33 + lane];
-            if (p.C) x = fmaf(p.beta, p.C[row * p.ldc + col], x);
-            x += bias_v;
-            if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
-            p.D[row * p.ldd + col] = x;
+          if (rows_here >= 32) {
+            // full 32-row slab: issue all 32 loads of C before the first use so that
+            // their latencies overlap instead of adding up
+            float cv[32];
+            if (p.C) {
+              const float* cp = p.C + static_cast<long long>(row0) * p.ldc + col;
+#pragma unroll
+              for (int rr = 0; rr < 32; ++rr) cv[rr] = cp[rr * p.ldc];
+            }
+            float* dp = p.D + static_cast<long long>(row0) * p.ldd + col;
+#pragma unroll
+            for (int rr = 0; rr < 32; ++rr) {
+              float x = p.alpha * tbuf[rr * 33 + lane];
+              if (p.C) x = fmaf(p.beta, cv[rr], x);
+              x += bias_v;
+              if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
+              dp[rr * p.ldd] = x;
+            }
+          } else {
+            for (int rr = 0; rr < rows_here; ++rr) {
+              const long long row = row0 + rr;
+              float x = p.alpha * tbuf[rr * 33 + lane];
+              if (p.C) x = fmaf(p.beta, p.C[row * p.ldc + col], x);
+              x += bias_v;
+              if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
+              p.D[row * p.ldd + col] = x;
+            }
           }
         }
         __syncwarp();

@@ -5,6 +5,7 @@
 #include "ir.hpp"
 
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <functional>
 #include <map>
@@ -480,6 +481,333 @@ bool match_map(Ctx& cx, const Sx& body) {
   return true;
 }
 
+// ------------------------------------------------------- generic map codegen
+// Emits the element function of an arbitrary straight-line element-wise map.
+// Arithmetic follows the Native backend exactly: loads widen to double, every
+// operation is a separately rounded double operation (no contraction), literals
+// are doubles, one rounding to float32 at each store, and a later read of a
+// vector stored earlier in the same body sees the rounded value.
+struct GenCtx {
+  const Ctx* cx;
+  const Sx* idx;
+  GenericMap* gm;
+  std::map<std::string, std::string> stored;  // array name -> temp holding its rounded value
+  std::string why;
+  int input_slot(int param) {
+    for (size_t i = 0; i < gm->inputs.size(); ++i)
+      if (gm->inputs[i] == param) return static_cast<int>(i);
+    gm->inputs.push_back(param);
+    return static_cast<int>(gm->inputs.size()) - 1;
+  }
+  int scalar_slot(int param) {
+    for (size_t i = 0; i < gm->scalars.size(); ++i)
+      if (gm->scalars[i] == param) return static_cast<int>(i);
+    gm->scalars.push_back(param);
+    return static_cast<int>(gm->scalars.size()) - 1;
+  }
+};
+
+bool gen_int(GenCtx& g, const Sx& e, std::string* out);
+
+bool gen_float(GenCtx& g, const Sx& e, std::string* out) {
+  const Ctx& cx = *g.cx;
+  if (e.is("const") && e.size() == 3 && (e[1].s == "f32" || e[1].s == "f64")) {
+    char buf[64];
+    snprintf(buf, sizeof buf, "%.17g", strtod(e[2].s.c_str(), nullptr));
+    std::string t = buf;
+    if (t.find_first_of(".eEn") == std::string::npos) t += ".0";
+    *out = "(" + t + ")";
+    return true;
+  }
+  if (e.is("evar")) {
+    int p = cx.scalar_param(e, nullptr);
+    if (p < 0) {
+      g.why = "variable " + (e.size() > 1 ? e[1].s : std::string("?")) + " is not a scalar parameter";
+      return false;
+    }
+    const std::string& elt = cx.plan->params[p].elt;
+    if (elt != "f32" && elt != "f64") {
+      g.why = "integer parameter used as a float value";
+      return false;
+    }
+    *out = "s" + std::to_string(g.scalar_slot(p));
+    return true;
+  }
+  if (e.is("read") && e.size() == 3 && e[1].atom) {
+    if (!sx_equal(e[2], *g.idx)) {
+      g.why = "vector " + e[1].s + " is read at an index other than the element index";
+      return false;
+    }
+    auto it = g.stored.find(e[1].s);
+    if (it != g.stored.end()) {
+      *out = "((double)" + it->second + ")";
+      return true;
+    }
+    int p = cx.vec_param(e[1].s, "f32");
+    if (p < 0) {
+      g.why = "read of " + e[1].s + ", which is not a float32 vector parameter";
+      return false;
+    }
+    *out = "X" + std::to_string(g.input_slot(p));
+    return true;
+  }
+  if (e.is("binop") && e.size() == 4) {
+    static const std::map<std::string, const char*> ar = {{"add", "__dadd_rn"}, {"sub", "__dsub_rn"}, {"mul", "__dmul_rn"}, {"div", "__ddiv_rn"}};
+    auto it = ar.find(e[1].s);
+    if (it == ar.end()) {
+      g.why = "operator " + e[1].s + " in a float expression";
+      return false;
+    }
+    std::string a, b;
+    if (!gen_float(g, e[2], &a) || !gen_float(g, e[3], &b)) return false;
+    *out = std::string(it->second) + "(" + a + ", " + b + ")";
+    return true;
+  }
+  if (e.is("unop") && e.size() == 3 && e[1].s == "neg") {
+    std::string a;
+    if (!gen_float(g, e[2], &a)) return false;
+    *out = "(-" + a + ")";
+    return true;
+  }
+  if (e.is("if") && e.size() == 4) {
+    std::string c, a, b;
+    std::function<bool(const Sx&, std::string*)> cond = [&](const Sx& x, std::string* o) -> bool {
+      if (x.is("const") && x.size() == 3 && x[1].s == "bool") {
+        *o = x[2].s == "true" ? "true" : "false";
+        return true;
+      }
+      if (x.is("unop") && x.size() == 3 && x[1].s == "not") {
+        std::string i;
+        if (!cond(x[2], &i)) return false;
+        *o = "(!" + i + ")";
+        return true;
+      }
+      if (x.is("binop") && x.size() == 4) {
+        static const std::map<std::string, const char*> cmp = {{"lt", "<"}, {"le", "<="}, {"gt", ">"}, {"ge", ">="}, {"eq", "=="}, {"ne", "!="}};
+        auto it = cmp.find(x[1].s);
+        std::string l, r;
+        if (it != cmp.end()) {
+          if (gen_float(g, x[2], &l) && gen_float(g, x[3], &r)) {
+            *o = "(" + l + " " + it->second + " " + r + ")";
+            return true;
+          }
+          return false;
+        }
+        if (x[1].s == "and" || x[1].s == "or") {
+          if (!cond(x[2], &l) || !cond(x[3], &r)) return false;
+          *o = "(" + l + (x[1].s == "and" ? " && " : " || ") + r + ")";
+          return true;
+        }
+      }
+      g.why = "unsupported condition";
+      return false;
+    };
+    if (!cond(e[1], &c) || !gen_float(g, e[2], &a) || !gen_float(g, e[3], &b)) return false;
+    *out = "(" + c + " ? " + a + " : " + b + ")";
+    return true;
+  }
+  if (e.is("intrinsic") && e.size() >= 3) {
+    static const std::map<std::string, const char*> un = {
+        {"sin", "sin"}, {"cos", "cos"}, {"tan", "tan"}, {"asin", "asin"}, {"acos", "acos"}, {"atan", "atan"},
+        {"sinh", "sinh"}, {"cosh", "cosh"}, {"tanh", "tanh"}, {"exp", "exp"}, {"log", "log"}, {"log10", "log10"},
+        {"sqrt", "sqrt"}, {"ceil", "ceil"}, {"floor", "floor"}, {"expm1", "expm1"}, {"log1p", "log1p"}, {"abs_float", "fabs"}};
+    static const std::map<std::string, const char*> bin = {{"pow", "pow"}, {"atan2", "atan2"}, {"hypot", "hypot"}, {"copysign", "copysign"},
+                                                            {"add", "__dadd_rn"}, {"minus", "__dsub_rn"}, {"mul", "__dmul_rn"}, {"div", "__ddiv_rn"},
+                                                            {"add_float32", "__dadd_rn"}, {"sub_float32", "__dsub_rn"},
+                                                            {"mul_float32", "__dmul_rn"}, {"div_float32", "__ddiv_rn"}};
+    const std::string& name = e[2].s;
+    if (un.count(name) && e.size() == 4) {
+      std::string a;
+      if (!gen_float(g, e[3], &a)) return false;
+      *out = std::string(un.at(name)) + "(" + a + ")";
+      return true;
+    }
+    if (name == "rsqrt" && e.size() == 4) {
+      std::string a;
+      if (!gen_float(g, e[3], &a)) return false;
+      *out = "__ddiv_rn(1.0, sqrt(" + a + "))";
+      return true;
+    }
+    if (bin.count(name) && e.size() == 5) {
+      std::string a, b;
+      if (!gen_float(g, e[3], &a) || !gen_float(g, e[4], &b)) return false;
+      *out = std::string(bin.at(name)) + "(" + a + ", " + b + ")";
+      return true;
+    }
+    if ((name == "of_int" || name == "float" || name == "float_of_int") && e.size() == 4) {
+      std::string a;
+      if (!gen_int(g, e[3], &a)) return false;
+      *out = "((double)" + a + ")";
+      return true;
+    }
+    g.why = "intrinsic " + name + " is not supported in element-wise maps";
+    return false;
+  }
+  if (e.is("cast") && e.size() == 3 && (e[1].s == "f32" || e[1].s == "f64")) return gen_float(g, e[2], out);
+  g.why = "unsupported expression form " + (e.atom ? e.s : (e.kids.empty() ? std::string("()") : e[0].s));
+  return false;
+}
+
+bool gen_int(GenCtx& g, const Sx& e, std::string* out) {
+  if (e.is("const") && e.size() == 3 && (e[1].s == "i32" || e[1].s == "i64")) {
+    *out = "((long long)" + std::to_string(atoll(e[2].s.c_str())) + "ll)";
+    return true;
+  }
+  if (e.is("evar")) {
+    int p = g.cx->scalar_param(e, nullptr);
+    if (p >= 0 && (g.cx->plan->params[p].elt == "i32" || g.cx->plan->params[p].elt == "i64")) {
+      *out = "s" + std::to_string(g.scalar_slot(p));
+      return true;
+    }
+  }
+  if (e.is("binop") && e.size() == 4 && (e[1].s == "add" || e[1].s == "sub" || e[1].s == "mul")) {
+    std::string a, b;
+    if (!gen_int(g, e[2], &a) || !gen_int(g, e[3], &b)) return false;
+    // int32 arithmetic wraps, as in the Native backend
+    *out = "((long long)(int)(" + a + (e[1].s == "add" ? " + " : e[1].s == "sub" ? " - " : " * ") + b + "))";
+    return true;
+  }
+  g.why = "unsupported integer expression";
+  return false;
+}
+
+std::string generic_map_source(const KernelPlan& plan, const GenericMap& gm, const std::vector<std::string>& store_exprs) {
+  const size_t ni = gm.inputs.size(), no = gm.outputs.size(), ns = gm.scalars.size();
+  auto scalar_type = [&](size_t i) {
+    const std::string& elt = plan.params[gm.scalars[i]].elt;
+    return (elt == "f32" || elt == "f64") ? "double" : "long long";
+  };
+  std::ostringstream o;
+  o << "// generated for kernel '" << plan.name << "'\n";
+  o << "__device__ __forceinline__ void sb200_elem(";
+  for (size_t i = 0; i < ni; ++i) o << "float x" << i << ", ";
+  for (size_t i = 0; i < ns; ++i) o << scalar_type(i) << " s" << i << ", ";
+  for (size_t i = 0; i < no; ++i) o << "float& y" << i << (i + 1 < no ? ", " : "");
+  o << ") {\n";
+  for (size_t i = 0; i < ni; ++i) o << "  const double X" << i << " = (double)x" << i << ";\n";
+  for (size_t i = 0; i < no; ++i) o << "  const float t" << i << " = (float)(" << store_exprs[i] << ");\n  y" << i << " = t" << i << ";\n";
+  o << "}\n";
+  // vector kernel: 2 x 128-bit per operand per thread per iteration
+  o << "extern \"C\" __global__ void __launch_bounds__(256) sb200_map_vec(";
+  for (size_t i = 0; i < ni; ++i) o << "const float4* __restrict__ in" << i << ", ";
+  for (size_t i = 0; i < no; ++i) o << "float4* __restrict__ out" << i << ", ";
+  for (size_t i = 0; i < ns; ++i) o << scalar_type(i) << " s" << i << ", ";
+  o << "long long nvec) {\n";
+  o << "  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {\n";
+  for (size_t i = 0; i < ni; ++i) o << "    const float4 a" << i << " = in" << i << "[v];\n";
+  for (size_t i = 0; i < no; ++i) o << "    float4 r" << i << ";\n";
+  for (const char* c : {"x", "y", "z", "w"}) {
+    o << "    sb200_elem(";
+    for (size_t i = 0; i < ni; ++i) o << "a" << i << "." << c << ", ";
+    for (size_t i = 0; i < ns; ++i) o << "s" << i << ", ";
+    for (size_t i = 0; i < no; ++i) o << "r" << i << "." << c << (i + 1 < no ? ", " : "");
+    o << ");\n";
+  }
+  for (size_t i = 0; i < no; ++i) o << "    out" << i << "[v] = r" << i << ";\n";
+  o << "  }\n}\n";
+  o << "extern \"C\" __global__ void __launch_bounds__(256) sb200_map_scalar(";
+  for (size_t i = 0; i < ni; ++i) o << "const float* __restrict__ in" << i << ", ";
+  for (size_t i = 0; i < no; ++i) o << "float* __restrict__ out" << i << ", ";
+  for (size_t i = 0; i < ns; ++i) o << scalar_type(i) << " s" << i << ", ";
+  o << "long long first, long long n) {\n";
+  o << "  for (long long e = first + blockIdx.x * (long long)blockDim.x + threadIdx.x; e < n; e += (long long)gridDim.x * blockDim.x) {\n";
+  for (size_t i = 0; i < no; ++i) o << "    float r" << i << ";\n";
+  o << "    sb200_elem(";
+  for (size_t i = 0; i < ni; ++i) o << "in" << i << "[e], ";
+  for (size_t i = 0; i < ns; ++i) o << "s" << i << ", ";
+  for (size_t i = 0; i < no; ++i) o << "r" << i << (i + 1 < no ? ", " : "");
+  o << ");\n";
+  for (size_t i = 0; i < no; ++i) o << "    out" << i << "[e] = r" << i << ";\n";
+  o << "  }\n}\n";
+  return o.str();
+}
+
+bool match_map_generic(Ctx& cx, const Sx& body) {
+  KernelPlan& plan = *cx.plan;
+  Peeled pl;
+  peel(body, &pl, true);
+  if (!pl.shared.empty()) {
+    cx.why = "uses shared arrays";
+    return false;
+  }
+  std::vector<const Sx*> items = seq_items(*pl.core);
+  if (items.empty() || items.size() > 8) {
+    cx.why = "body is not one to eight element stores";
+    return false;
+  }
+  MapPlan mp;
+  GenericMap gm;
+  Sx idx;
+  bool have_idx = false;
+  for (const Sx* it : items) {
+    if (!it->is("assign") || it->size() != 3 || !(*it)[1].is("elem") || (*it)[1].size() != 3) {
+      cx.why = "statement is not an array element store";
+      return false;
+    }
+    Sx this_idx = inline_expr((*it)[1][2], pl.env);
+    if (!have_idx) {
+      idx = this_idx;
+      have_idx = true;
+    } else if (!sx_equal(idx, this_idx)) {
+      cx.why = "stores use different indices";
+      return false;
+    }
+  }
+  if (is_global_x(idx)) {
+    mp.index_kind = IDX_GLOBAL;
+  } else if (is_intrinsic(idx, "thread_idx_x")) {
+    mp.index_kind = IDX_THREAD_X;
+  } else {
+    cx.why = "element index is not the global or block-local x thread index";
+    return false;
+  }
+  if (pl.guards.size() > 1) {
+    cx.why = "more than one guard";
+    return false;
+  }
+  if (pl.guards.size() == 1) {
+    const Sx *l, *r;
+    if (!is_binop(pl.guards[0], "lt", &l, &r) || !sx_equal(*l, idx) || (mp.n_param = cx.scalar_param(*r, "i32")) < 0) {
+      cx.why = "guard is not `index < n` with n an int32 parameter";
+      return false;
+    }
+  }
+  GenCtx g{&cx, &idx, &gm, {}, ""};
+  std::vector<std::string> exprs;
+  for (const Sx* it : items) {
+    const std::string& arr = (*it)[1][1].s;
+    int out = cx.vec_param(arr, "f32");
+    if (out < 0) {
+      cx.why = "store target " + arr + " is not a float32 vector parameter";
+      return false;
+    }
+    for (int prev : gm.outputs)
+      if (prev == out) {
+        cx.why = "vector " + arr + " is stored twice";
+        return false;
+      }
+    std::string code;
+    if (!gen_float(g, inline_expr((*it)[2], pl.env), &code)) {
+      cx.why = g.why;
+      return false;
+    }
+    exprs.push_back(code);
+    g.stored[arr] = "t" + std::to_string(gm.outputs.size());
+    gm.outputs.push_back(out);
+  }
+  // an input that is also an output is read before it is written by the same thread: allowed
+  gm.source = generic_map_source(plan, gm, exprs);
+  mp.op = OP_GENERIC;
+  mp.out0 = gm.outputs[0];
+  plan.kind = KIND_MAP;
+  plan.map = mp;
+  plan.generic = gm;
+  plan.description = "map:generic(jit) inputs=" + std::to_string(gm.inputs.size()) + " outputs=" + std::to_string(gm.outputs.size()) +
+                     " scalars=" + std::to_string(gm.scalars.size()) + (mp.n_param >= 0 ? " guarded" : " unguarded") +
+                     (mp.index_kind == IDX_GLOBAL ? " idx=global_x" : " idx=thread_idx_x");
+  return true;
+}
+
 // ------------------------------------------------------------------- GEMM
 
 // relu wrapper: (if (binop gt X (const f32 0)) X (const f32 0))
@@ -908,6 +1236,9 @@ int ir_compile(const std::string& text, KernelPlan* plan, std::string* err) {
     return 0;
   }
   reasons += "; tiled gemm: " + (cx.why.empty() ? std::string("shape mismatch") : cx.why);
+  cx.why.clear();
+  if (match_map_generic(cx, *body)) return 0;
+  reasons += "; generic map: " + cx.why;
   if (err)
     *err = "unsupported construct in kernel '" + plan->name +
            "': body is neither a GEMM nor a supported element-wise map (" + reasons + ")";

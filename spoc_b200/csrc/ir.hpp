@@ -59,7 +59,7 @@ struct Coef {
   double value = 0.0;
 };
 
-enum { OP_VECADD = 0, OP_TRIAD = 1, OP_CHAIN = 2, OP_CHAIN_KEEP = 3 };
+enum { OP_VECADD = 0, OP_TRIAD = 1, OP_CHAIN = 2, OP_CHAIN_KEEP = 3, OP_GENERIC = 4 };
 enum { IDX_GLOBAL = 0, IDX_THREAD_X = 1 };
 enum { KIND_MAP = 1, KIND_GEMM_NAIVE = 2, KIND_GEMM_TILED = 3 };
 
@@ -69,6 +69,15 @@ struct MapPlan {
   Coef scalar;
   int n_param = -1;  // guard `idx < n`; -1 when the body is unguarded
   int index_kind = IDX_GLOBAL;
+};
+
+// An element-wise map that is none of the ahead-of-time shapes: the expression is
+// emitted as CUDA source into the vectorised map skeleton and compiled at run time.
+struct GenericMap {
+  std::vector<int> inputs;   // float32 vector params read at the element index
+  std::vector<int> outputs;  // float32 vector params stored, in store order
+  std::vector<int> scalars;  // scalar params used by the expression (passed as double / long long)
+  std::string source;        // complete CUDA translation unit (kernels sb200_map_vec, sb200_map_scalar)
 };
 
 struct GemmPlan {
@@ -87,6 +96,7 @@ struct KernelPlan {
   std::vector<ParamInfo> params;
   int kind = 0;
   MapPlan map;
+  GenericMap generic;  // when map.op == OP_GENERIC
   GemmPlan gemm;
   std::string description;
 };

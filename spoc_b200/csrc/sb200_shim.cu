@@ -14,6 +14,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <atomic>
 #include <mutex>
 #include <string>
@@ -26,6 +27,7 @@
 #include "gemm_tcgen05_pair.cuh"
 #include "ir.hpp"
 #include "map_fused.cuh"
+#include "map_jit.hpp"
 
 using namespace sb200;
 
@@ -83,6 +85,10 @@ struct DeviceState {
     cudaEvent_t e0, e1, e2;
   };
   std::vector<ProfRec> prof;
+  // host-operand GEMM (sb200_gemm_f32_host): device mirrors of the operands and three streams
+  void* host_stage = nullptr;
+  size_t host_stage_bytes = 0;
+  cudaStream_t pipe_in = nullptr, pipe_compute = nullptr, pipe_out = nullptr;
 };
 DeviceState g_dev[kMaxDevices];
 std::atomic<int> g_profiling{0};
@@ -274,7 +280,11 @@ size_t gemm_workspace_need(int mode, long long M, long long N, long long K) {
 
 template <int MODE>
 int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, long long K, const float* A,
-                     long long lda, const float* B, long long ldb, const GemmParams& gp_in) {
+                     long long lda, const float* B, long long ldb, const GemmParams& gp_in, long long panel_rows_a = 0,
+                     bool b_panels_ready = false) {
+  // panel_rows_a: rows the A panels are laid out for (>= M); callers that run several row blocks
+  // against one prepared B pass the largest block so that the B panels keep their place.
+  if (panel_rows_a < M) panel_rows_a = M;
   using Cfg = GemmCfg<MODE>;
   static std::once_flag attr_once;
   static cudaError_t attr_err = cudaSuccess;
@@ -289,8 +299,8 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   (void)attr_err;
 
   const long long kp = round_up(K, GEMM_BK);
-  const size_t a_bytes = round_up(M * kp * 4, 1024), b_bytes = round_up(N * kp * 4, 1024);
-  int rc = ensure_workspace(d, gemm_workspace_need(MODE == 3 ? SB200_MODE_3XTF32 : SB200_MODE_TF32, M, N, K));
+  const size_t a_bytes = round_up(panel_rows_a * kp * 4, 1024), b_bytes = round_up(N * kp * 4, 1024);
+  int rc = ensure_workspace(d, gemm_workspace_need(MODE == 3 ? SB200_MODE_3XTF32 : SB200_MODE_TF32, panel_rows_a, N, K));
   if (rc) return rc;
   const bool prof = g_profiling.load() != 0;
   DeviceState::ProfRec rec{nullptr, nullptr, nullptr};
@@ -300,11 +310,13 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
     CU_TRY(cudaEventCreate(&rec.e2));
     CU_TRY(cudaEventRecord(rec.e0, st));
   }
+  // workspace layout: B panels first (their size does not depend on M), then the A panels
   uint8_t* ws = static_cast<uint8_t*>(d.workspace);
-  float* a_hi = reinterpret_cast<float*>(ws);
-  float* b_hi = reinterpret_cast<float*>(ws + a_bytes);
-  float* a_lo = MODE == 3 ? reinterpret_cast<float*>(ws + a_bytes + b_bytes) : a_hi;
-  float* b_lo = MODE == 3 ? reinterpret_cast<float*>(ws + 2 * a_bytes + b_bytes) : b_hi;
+  constexpr size_t kOps = MODE == 3 ? 2 : 1;
+  float* b_hi = reinterpret_cast<float*>(ws);
+  float* b_lo = MODE == 3 ? reinterpret_cast<float*>(ws + b_bytes) : b_hi;
+  float* a_hi = reinterpret_cast<float*>(ws + kOps * b_bytes);
+  float* a_lo = MODE == 3 ? reinterpret_cast<float*>(ws + kOps * b_bytes + a_bytes) : a_hi;
 
   {
     const long long quads = M * (kp >> 2);
@@ -317,7 +329,7 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
     rc = launch_check("prep_a_kernel");
     if (rc) return rc;
   }
-  {
+  if (!b_panels_ready) {
     const long long tiles = (kp >> 5) * ((N + 31) >> 5);
     long long grid = tiles;
     const long long cap = static_cast<long long>(d.sm_count) * 32;
@@ -438,6 +450,9 @@ int run_gemm(DeviceState& d, cudaStream_t st, int mode, long long M, long long N
 struct KernelObj {
   int dev;
   KernelPlan plan;
+  std::string cubin;          // generic maps: compiled at sb200_kernel_compile (needs no GPU)
+  JitModule jit[kMaxDevices]; // loaded on first launch per device
+  std::mutex mu;
 };
 std::mutex g_kernels_mu;
 std::unordered_set<KernelObj*> g_kernels;
@@ -496,8 +511,85 @@ float coef_value(const Coef& c, const std::vector<Slot>& slots) {
   return static_cast<float>(c.param >= 0 ? slots[c.param].f : c.value);
 }
 
-int launch_map_kernel(DeviceState& d, const KernelPlan& plan, const std::vector<Slot>& s, const uint32_t grid[3],
+int launch_generic_map(DeviceState& d, KernelObj& k, const std::vector<Slot>& s, long long n, cudaStream_t st) {
+  const GenericMap& gm = k.plan.generic;
+  JitModule* jm = &k.jit[k.dev];
+  {
+    std::lock_guard<std::mutex> lock(k.mu);
+    if (!jm->module) {
+      std::string err;
+      int rc = jit_load(k.cubin, jm, &err);
+      if (rc) return fail(rc, "kernel '%s': %s", k.plan.name.c_str(), err.c_str());
+    }
+  }
+  if (n <= 0) return SB200_OK;
+  const size_t ni = gm.inputs.size(), no = gm.outputs.size(), ns = gm.scalars.size();
+  std::vector<uint64_t> ptrs;
+  for (int p : gm.inputs) ptrs.push_back(s[p].ptr);
+  for (int p : gm.outputs) ptrs.push_back(s[p].ptr);
+  uintptr_t mis = ptrs[0] & 15;
+  bool same = (mis & 3) == 0;
+  for (uint64_t p : ptrs) {
+    if (!p) return fail(SB200_ERR_INVALID_VALUE, "kernel '%s': null device pointer", k.plan.name.c_str());
+    if (p & 3) return fail(SB200_ERR_ALIGNMENT, "float32 vectors must be 4-byte aligned");
+    if ((p & 15) != mis) same = false;
+  }
+  long long head = 0, nvec = 0;
+  if (same) {
+    head = mis ? static_cast<long long>((16 - mis) >> 2) : 0;
+    if (head > n) head = n;
+    nvec = (n - head) >> 2;
+  }
+  const long long body_end = head + nvec * 4;
+  std::vector<double> sd(ns);
+  std::vector<long long> si(ns);
+  auto scalar_arg = [&](size_t i) -> void* {
+    const std::string& elt = k.plan.params[gm.scalars[i]].elt;
+    if (elt == "f32" || elt == "f64") {
+      sd[i] = s[gm.scalars[i]].f;
+      return &sd[i];
+    }
+    si[i] = s[gm.scalars[i]].i;
+    return &si[i];
+  };
+  std::string err;
+  auto run_scalar = [&](long long first, long long last) -> int {
+    std::vector<void*> args;
+    for (size_t i = 0; i < ni + no; ++i) args.push_back(&ptrs[i]);
+    for (size_t i = 0; i < ns; ++i) args.push_back(scalar_arg(i));
+    args.push_back(&first);
+    args.push_back(&last);
+    long long grid = (last - first + 255) / 256;
+    const long long cap = static_cast<long long>(d.sm_count) * 16;
+    if (grid > cap) grid = cap;
+    int rc = jit_launch(jm->scalar_fn, static_cast<unsigned>(grid), 256, st, args.data(), &err);
+    if (rc) return fail(rc, "kernel '%s': %s", k.plan.name.c_str(), err.c_str());
+    count_launch();
+    return SB200_OK;
+  };
+  int rc;
+  if (head > 0 && (rc = run_scalar(0, head))) return rc;
+  if (nvec > 0) {
+    std::vector<uint64_t> vp(ptrs);
+    for (auto& p : vp) p += static_cast<uint64_t>(head) * 4;
+    std::vector<void*> args;
+    for (size_t i = 0; i < ni + no; ++i) args.push_back(&vp[i]);
+    for (size_t i = 0; i < ns; ++i) args.push_back(scalar_arg(i));
+    args.push_back(&nvec);
+    long long grid = (nvec + 255) / 256;
+    const long long cap = static_cast<long long>(d.sm_count) * 8;
+    if (grid > cap) grid = cap;
+    rc = jit_launch(jm->vec_fn, static_cast<unsigned>(grid), 256, st, args.data(), &err);
+    if (rc) return fail(rc, "kernel '%s': %s", k.plan.name.c_str(), err.c_str());
+    count_launch();
+  }
+  if (body_end < n && (rc = run_scalar(body_end, n))) return rc;
+  return SB200_OK;
+}
+
+int launch_map_kernel(DeviceState& d, KernelObj& kobj, const std::vector<Slot>& s, const uint32_t grid[3],
                       const uint32_t block[3], cudaStream_t st) {
+  const KernelPlan& plan = kobj.plan;
   const MapPlan& m = plan.map;
   // which element indices the reference launch would touch
   long long covered = m.index_kind == IDX_GLOBAL ? static_cast<long long>(grid[0]) * block[0] : block[0];
@@ -506,11 +598,16 @@ int launch_map_kernel(DeviceState& d, const KernelPlan& plan, const std::vector<
     if (s[m.n_param].i < n) n = s[m.n_param].i;
     if (n < 0) n = 0;
   }
-  const int vecs[4] = {m.out0, m.out1, m.in0, m.in1};
+  std::vector<int> vecs = {m.out0, m.out1, m.in0, m.in1};
+  if (m.op == OP_GENERIC) {
+    vecs = plan.generic.inputs;
+    vecs.insert(vecs.end(), plan.generic.outputs.begin(), plan.generic.outputs.end());
+  }
   for (int v : vecs)
     if (v >= 0 && s[v].len < n)
       return fail(SB200_ERR_BOUNDS, "kernel '%s': launch covers %lld elements but vector %s holds %lld", plan.name.c_str(), n,
                   plan.params[v].name.c_str(), s[v].len);
+  if (m.op == OP_GENERIC) return launch_generic_map(d, kobj, s, n, st);
   return run_map(d, st, m.op, s[m.out0].ptr, m.out1 >= 0 ? s[m.out1].ptr : 0, s[m.in0].ptr, s[m.in1].ptr,
                  coef_value(m.scalar, s), n);
 }
@@ -853,6 +950,13 @@ int sb200_kernel_compile(int dev, const char* ir_text, const char* name, uint64_
     delete k;
     return fail(rc, "%s", err.c_str());
   }
+  if (k->plan.kind == KIND_MAP && k->plan.map.op == OP_GENERIC) {
+    rc = jit_compile_cubin(k->plan.generic.source, k->plan.name, &k->cubin, &err);
+    if (rc) {
+      delete k;
+      return fail(rc, "%s", err.c_str());
+    }
+  }
   if (name && *name && k->plan.name != name && debug_kernel())
     fprintf(stderr, "[sarek-b200] kernel name '%s' requested, IR names it '%s'\n", name, k->plan.name.c_str());
   if (debug_kernel()) fprintf(stderr, "[sarek-b200] compiled %s -> %s\n", k->plan.name.c_str(), k->plan.description.c_str());
@@ -870,6 +974,8 @@ int sb200_kernel_destroy(uint64_t kernel) {
     std::lock_guard<std::mutex> lock(g_kernels_mu);
     if (!g_kernels.erase(k)) return SB200_OK;
   }
+  for (int i = 0; i < kMaxDevices; ++i)
+    if (k->jit[i].module && cudaSetDevice(i) == cudaSuccess) jit_unload(&k->jit[i]);
   delete k;
   return SB200_OK;
 }
@@ -905,7 +1011,7 @@ int sb200_kernel_launch(uint64_t kernel, const sb200_arg* args, int nargs, const
   if (debug_kernel())
     fprintf(stderr, "[sarek-b200] launch %s grid=(%u,%u,%u) block=(%u,%u,%u)\n", k->plan.description.c_str(), grid[0], grid[1],
             grid[2], block[0], block[1], block[2]);
-  if (k->plan.kind == KIND_MAP) return launch_map_kernel(*d, k->plan, slots, grid, block, as_stream(stream));
+  if (k->plan.kind == KIND_MAP) return launch_map_kernel(*d, *k, slots, grid, block, as_stream(stream));
   return launch_gemm_kernel(*d, k->plan, slots, grid, block, as_stream(stream));
 }
 
@@ -1290,4 +1396,145 @@ extern "C" int sb200_gemm_f32_noalloc(int dev, uint64_t stream, int mode, int64_
     return fail(SB200_ERR_TIMEOUT, "a bounded device-side wait expired in the GEMM pipeline (site 0x%x)", flag);
   }
   return SB200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// GEMM on host operands, transfers pipelined with compute
+// ---------------------------------------------------------------------------
+// The reference moves whole vectors with synchronous copies before and after a
+// launch (sarek/core/Transfer.ml:229-322: to_device, kernel, to_cpu).  Here the
+// same end-to-end operation is one call that overlaps the three phases: B and
+// the bias go first; A and C then stream in by row blocks on one stream while
+// a second stream runs the GEMM of the blocks that have arrived and a third
+// copies finished blocks of D back (PCIe carries both directions at once).
+// B's panels are prepared once and reused by every row block.
+extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                                   const float* B, int64_t ldb, float* D, int64_t ldd, float alpha, const float* C,
+                                   int64_t ldc, float beta, const float* bias, int act) {
+  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  if (M < 0 || N < 0 || K < 0) return fail(SB200_ERR_INVALID_VALUE, "negative GEMM dimension");
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL - 64) return fail(SB200_ERR_TOO_LARGE, "GEMM dimension beyond 2^31-1");
+  if (act != SB200_ACT_NONE && act != SB200_ACT_RELU) return fail(SB200_ERR_INVALID_VALUE, "unknown activation %d", act);
+  if (M == 0 || N == 0) return SB200_OK;
+  if (!D || (K > 0 && (!A || !B))) return fail(SB200_ERR_INVALID_VALUE, "null host pointer passed to GEMM");
+  if ((K > 0 && lda < K) || (K > 0 && ldb < N) || ldd < N || (C && ldc < N))
+    return fail(SB200_ERR_INVALID_VALUE, "leading dimension smaller than the row length");
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (!d->pipe_in) {
+    CU_TRY(cudaStreamCreateWithFlags(&d->pipe_in, cudaStreamNonBlocking));
+    CU_TRY(cudaStreamCreateWithFlags(&d->pipe_compute, cudaStreamNonBlocking));
+    CU_TRY(cudaStreamCreateWithFlags(&d->pipe_out, cudaStreamNonBlocking));
+  }
+  // device mirrors, packed: A[M x K], B[K x N], C[M x N] (if any), D[M x N], bias[N]
+  auto al = [](size_t b) { return (b + 255) / 256 * 256; };
+  const size_t szA = al(size_t(M) * K * 4), szB = al(size_t(K) * N * 4), szC = C ? al(size_t(M) * N * 4) : 0,
+               szD = al(size_t(M) * N * 4), szBias = bias ? al(size_t(N) * 4) : 0;
+  const size_t need = szA + szB + szC + szD + szBias + 256;
+  if (need > d->host_stage_bytes) {
+    if (d->host_stage) {
+      CU_TRY(cudaDeviceSynchronize());
+      CU_TRY(cudaFree(d->host_stage));
+      d->host_stage = nullptr;
+      d->host_stage_bytes = 0;
+    }
+    CU_TRY(cudaMalloc(&d->host_stage, need));
+    d->host_stage_bytes = need;
+  }
+  uint8_t* base = static_cast<uint8_t*>(d->host_stage);
+  float* dA = reinterpret_cast<float*>(base);
+  float* dB = reinterpret_cast<float*>(base + szA);
+  float* dC = C ? reinterpret_cast<float*>(base + szA + szB) : nullptr;
+  float* dD = reinterpret_cast<float*>(base + szA + szB + szC);
+  float* dBias = bias ? reinterpret_cast<float*>(base + szA + szB + szC + szD) : nullptr;
+
+  // row blocks: about eight, multiples of 256 rows so that block edges are tile edges
+  long long block_rows = (M + 7) / 8;
+  block_rows = (block_rows + 255) / 256 * 256;
+  if (block_rows > M) block_rows = M;
+  const int nblocks = static_cast<int>((M + block_rows - 1) / block_rows);
+
+  std::vector<cudaEvent_t> ev_in(nblocks), ev_done(nblocks);
+  cudaEvent_t ev_b = nullptr;
+  auto cleanup = [&]() {
+    if (ev_b) cudaEventDestroy(ev_b);
+    for (auto e : ev_in) if (e) cudaEventDestroy(e);
+    for (auto e : ev_done) if (e) cudaEventDestroy(e);
+  };
+  for (auto& e : ev_in) e = nullptr;
+  for (auto& e : ev_done) e = nullptr;
+#define PIPE_TRY(call)                          \
+  do {                                          \
+    cudaError_t e__ = (call);                   \
+    if (e__ != cudaSuccess) {                   \
+      cudaDeviceSynchronize();                  \
+      cleanup();                                \
+      return cuda_fail(e__, #call);             \
+    }                                           \
+  } while (0)
+  PIPE_TRY(cudaEventCreateWithFlags(&ev_b, cudaEventDisableTiming));
+  for (int i = 0; i < nblocks; ++i) {
+    PIPE_TRY(cudaEventCreateWithFlags(&ev_in[i], cudaEventDisableTiming));
+    PIPE_TRY(cudaEventCreateWithFlags(&ev_done[i], cudaEventDisableTiming));
+  }
+  // inbound stream: B and bias first, then the row blocks of A and C
+  if (K > 0) PIPE_TRY(cudaMemcpy2DAsync(dB, size_t(N) * 4, B, size_t(ldb) * 4, size_t(N) * 4, size_t(K), cudaMemcpyHostToDevice, d->pipe_in));
+  if (bias) PIPE_TRY(cudaMemcpyAsync(dBias, bias, size_t(N) * 4, cudaMemcpyHostToDevice, d->pipe_in));
+  PIPE_TRY(cudaEventRecord(ev_b, d->pipe_in));
+  for (int i = 0; i < nblocks; ++i) {
+    const long long r0 = i * block_rows, rows = std::min<long long>(block_rows, M - r0);
+    if (K > 0)
+      PIPE_TRY(cudaMemcpy2DAsync(dA + r0 * K, size_t(K) * 4, A + r0 * lda, size_t(lda) * 4, size_t(K) * 4, size_t(rows),
+                                 cudaMemcpyHostToDevice, d->pipe_in));
+    if (C)
+      PIPE_TRY(cudaMemcpy2DAsync(dC + r0 * N, size_t(N) * 4, C + r0 * ldc, size_t(ldc) * 4, size_t(N) * 4, size_t(rows),
+                                 cudaMemcpyHostToDevice, d->pipe_in));
+    PIPE_TRY(cudaEventRecord(ev_in[i], d->pipe_in));
+  }
+  // compute stream: one GEMM per row block, B's panels prepared by the first
+  PIPE_TRY(cudaStreamWaitEvent(d->pipe_compute, ev_b, 0));
+  for (int i = 0; i < nblocks && rc == SB200_OK; ++i) {
+    const long long r0 = i * block_rows, rows = std::min<long long>(block_rows, M - r0);
+    PIPE_TRY(cudaStreamWaitEvent(d->pipe_compute, ev_in[i], 0));
+    GemmParams gp;
+    memset(&gp, 0, sizeof gp);
+    gp.M = static_cast<int>(rows);
+    gp.N = static_cast<int>(N);
+    gp.D = dD + r0 * N;
+    gp.ldd = N;
+    gp.C = dC ? dC + r0 * N : nullptr;
+    gp.ldc = N;
+    gp.bias = dBias;
+    gp.alpha = alpha;
+    gp.beta = beta;
+    gp.act = act;
+    if (K == 0) {
+      long long grid = (rows * N + 255) / 256;
+      const long long cap = static_cast<long long>(d->sm_count) * 16;
+      if (grid > cap) grid = cap;
+      gemm_k0_kernel<<<static_cast<unsigned>(grid), 256, 0, d->pipe_compute>>>(gp);
+      rc = launch_check("gemm_k0_kernel");
+    } else if (mode == SB200_MODE_3XTF32) {
+      rc = launch_gemm_mode<3>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);
+    } else {
+      rc = launch_gemm_mode<1>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);
+    }
+    if (rc == SB200_OK) PIPE_TRY(cudaEventRecord(ev_done[i], d->pipe_compute));
+    // outbound stream: the finished block of D
+    if (rc == SB200_OK) {
+      PIPE_TRY(cudaStreamWaitEvent(d->pipe_out, ev_done[i], 0));
+      PIPE_TRY(cudaMemcpy2DAsync(D + r0 * ldd, size_t(ldd) * 4, dD + r0 * N, size_t(N) * 4, size_t(N) * 4, size_t(rows),
+                                 cudaMemcpyDeviceToHost, d->pipe_out));
+    }
+  }
+  cudaError_t e1 = cudaStreamSynchronize(d->pipe_in), e2 = cudaStreamSynchronize(d->pipe_compute),
+              e3 = cudaStreamSynchronize(d->pipe_out);
+  cleanup();
+#undef PIPE_TRY
+  if (rc) return rc;
+  if (e1 != cudaSuccess) return cuda_fail(e1, "inbound copies");
+  if (e2 != cudaSuccess) return cuda_fail(e2, "GEMM row blocks");
+  if (e3 != cudaSuccess) return cuda_fail(e3, "outbound copies");
+  return check_status_word(*d);
 }

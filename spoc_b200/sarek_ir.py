@@ -16,7 +16,7 @@ from typing import Iterable, Sequence
 
 __all__ = [
     "sx", "Builder", "vector_add_ir", "stream_triad_ir", "matmul_naive_ir", "matmul_tiled_ir",
-    "triad_producer_ir", "square_add_consumer_ir", "chain_fused_ir",
+    "triad_producer_ir", "square_add_consumer_ir", "chain_fused_ir", "generic_example_ir",
 ]
 
 
@@ -261,3 +261,24 @@ def chain_fused_ir(scalar: float = 3.0, index: str = "global_thread_id") -> str:
     t = b.binop("add", b.read("b", idx), b.binop("mul", b.c_f32(scalar), b.read("c", idx)))
     body = ("assign", ("elem", "d", idx), b.binop("add", b.binop("mul", t, t), b.read("b", idx)))
     return _kernel("square_add_fused", p, body)
+
+
+def generic_example_ir() -> str:
+    """A map outside the ahead-of-time shapes, with two stores and a math intrinsic:
+         u.(i) <- x.(i) /. (y.(i) +. 2.5) -. sqrt (abs_float (z.(i) *. s))
+         v.(i) <- if u.(i) > 0.0 then u.(i) *. x.(i) else -. y.(i)
+    guarded by i < n.  The second store reads the value the first one stored."""
+    b = Builder()
+    p = b.params([("vec", "u", "f32"), ("vec", "v", "f32"), ("vec", "x", "f32"), ("vec", "y", "f32"), ("vec", "z", "f32"),
+                  ("scalar", "s", "f32"), ("scalar", "n", "i32")])
+
+    def body():
+        i = b.evar("i")
+        e1 = b.binop("sub", b.binop("div", b.read("x", i), b.binop("add", b.read("y", i), b.c_f32(2.5))),
+                     ("intrinsic", ("Float32",), "sqrt",
+                      ("intrinsic", ("Float32",), "abs_float", b.binop("mul", b.read("z", i), b.evar("s")))))
+        e2 = ("if", b.binop("gt", b.read("u", i), b.c_f32(0.0)), b.binop("mul", b.read("u", i), b.read("x", i)),
+              ("unop", "neg", b.read("y", i)))
+        return ("sif", b.binop("lt", i, b.evar("n")), ("seq", ("assign", ("elem", "u", i), e1), ("assign", ("elem", "v", i), e2)))
+
+    return _kernel("generic_example", p, b.let("i", "i32", b.intr("global_thread_id"), body))

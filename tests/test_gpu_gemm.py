@@ -115,6 +115,48 @@ def test_single_and_pair_kernels_agree_bit_for_bit(backend, device, mode):
             x.free()
 
 
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("pinned", [False, True])
+def test_host_operand_gemm_matches_device_path(backend, device, mode, pinned):
+    """sb200_gemm_f32_host: copies in, row-block GEMMs and copies out overlapped; the result must be
+    the device path's, bit for bit (row blocks are multiples of the tile height)."""
+    import ctypes as C
+    lib = L.load()
+    M, N, K, lda, ldd = 1000, 700, 300, 304, 712
+    a, b, c = O.fill(M * lda, 21, 1), O.fill(K * N, 21, 2), O.fill(M * N, 21, 3)
+    bias = O.fill(N, 21, 4, kind=1)
+    host_ptrs = []
+    if pinned:
+        def pin(arr):
+            p = C.c_void_p()
+            assert lib.sb200_host_alloc(arr.nbytes, C.byref(p)) == 0
+            host_ptrs.append(p)
+            C.memmove(p, arr.ctypes.data, arr.nbytes)
+            return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(arr.size,))
+        a, b, c, bias = pin(a), pin(b), pin(c), pin(bias)
+        d_host = pin(np.full(M * ldd, CANARY, np.float32))
+    else:
+        d_host = np.full(M * ldd, CANARY, np.float32)
+    ptr = lambda x: x.ctypes.data_as(C.c_void_p)
+    try:
+        rc = lib.sb200_gemm_f32_host(device.id, mode, M, N, K, ptr(a), lda, ptr(b), N, ptr(d_host), ldd, 1.5, ptr(c), N, 0.5,
+                                     ptr(bias), 1)
+        assert rc == 0, lib.sb200_last_error_string()
+        got = d_host.reshape(M, ldd)
+        assert np.all(got[:, N:] == CANARY)
+        a2 = np.ascontiguousarray(np.asarray(a).reshape(M, lda)[:, :K]).ravel()
+        A, B, Cd, Bi, D = (dev_from(backend, device, x) for x in (a2, np.asarray(b), np.asarray(c), np.asarray(bias), np.zeros(M * N, np.float32)))
+        gemm(backend, device, mode, M, N, K, A, B, D, alpha=1.5, C_=Cd, beta=0.5, bias=Bi, act=1)
+        assert np.array_equal(got[:, :N], D.download().reshape(M, N))
+        ref = O.gemm(a2, np.asarray(b), M, N, K, 1.5, 0.5, np.asarray(c), np.asarray(bias), 1)
+        assert O.gemm_rel_error(got[:, :N], ref) <= tol(mode, K) * 1.5 * math.sqrt(2)
+        for x in (A, B, Cd, Bi, D):
+            x.free()
+    finally:
+        for p in host_ptrs:
+            lib.sb200_host_free(p)
+
+
 def test_leading_dimensions_and_submatrices(backend, device):
     M, N, K, lda, ldb, ldd = 70, 90, 50, 64, 100, 128
     a, b = O.fill(M * lda, 3, 1), O.fill(K * ldb, 3, 2)

@@ -188,3 +188,37 @@ def test_full_size_chain_properties(backend, device, oracle):
     finally:
         for x in bufs:
             backend.Memory.free(x)
+
+
+@pytest.mark.parametrize("n", [1, 5, 1000, 65537])
+def test_generated_map_kernel_is_bit_exact_against_native_semantics(backend, device, n):
+    """A map that is none of the ahead-of-time shapes is compiled at run time; it evaluates in double and
+    rounds once per store like the Native backend, so it must match a float64 evaluation bit for bit."""
+    rng = np.random.default_rng(n)
+    x, y, z = (rng.standard_normal(n).astype(np.float32) for _ in range(3))
+    vu, vv = Vector(backend, np.full(n, CANARY, np.float32)), Vector(backend, np.full(n, CANARY, np.float32))
+    vx, vy, vz = Vector(backend, x.copy()), Vector(backend, y.copy()), Vector(backend, z.copy())
+    s = 0.75
+    before = backend.launch_count()
+    run_vectors(backend, device=device, ir=sarek_ir.generic_example_ir(), args=[vu, vv, vx, vy, vz, ("float32", s), ("int32", n)],
+                block=dims1d(256), grid=dims1d((n + 255) // 256))
+    assert backend.launch_count() > before
+    X, Y, Z = x.astype(np.float64), y.astype(np.float64), z.astype(np.float64)
+    u = (X / (Y + 2.5) - np.sqrt(np.abs(Z * s))).astype(np.float32)
+    U = u.astype(np.float64)
+    v = np.where(U > 0.0, U * X, -Y).astype(np.float32)
+    assert np.array_equal(vu.to_array(), u)
+    assert np.array_equal(vv.to_array(), v)
+    for t in (vu, vv, vx, vy, vz):
+        t.free()
+
+
+def test_unfused_consumer_runs_through_the_generated_path(backend, device):
+    n = 4096
+    a, b = O.fill(n, 31, 1), O.fill(n, 31, 2)
+    vd, va, vb = Vector.create(backend, n), Vector(backend, a.copy()), Vector(backend, b.copy())
+    run_vectors(backend, device=device, ir=sarek_ir.square_add_consumer_ir(), args=[vd, va, vb], block=dims1d(256), grid=dims1d(n // 256))
+    want = (a.astype(np.float64) * a.astype(np.float64) + b.astype(np.float64)).astype(np.float32)
+    assert np.array_equal(vd.to_array(), want)
+    for t in (vd, va, vb):
+        t.free()

@@ -33,6 +33,13 @@ def test_reference_kernels_are_recognised(ir, kind, needle):
     assert needle in k.describe()
 
 
+def test_other_elementwise_expressions_take_the_generated_kernel_path():
+    k = compile_(S.square_add_consumer_ir())       # d = a*a + b: none of the ahead-of-time shapes
+    assert k.kind == L.KIND_MAP and "map:generic(jit) inputs=2 outputs=1" in k.describe()
+    k = compile_(S.generic_example_ir())
+    assert "map:generic(jit) inputs=3 outputs=2 scalars=1 guarded" in k.describe()
+
+
 def test_commuted_operands_and_expanded_thread_id_are_recognised():
     b = S.Builder()
     p = b.params([("vec", "a", "f32"), ("vec", "b", "f32"), ("vec", "c", "f32"), ("scalar", "s", "f32"), ("scalar", "n", "i32")])
@@ -45,7 +52,8 @@ def test_commuted_operands_and_expanded_thread_id_are_recognised():
 
 
 @pytest.mark.parametrize("ir,why", [
-    (S.square_add_consumer_ir(), "element expression"),          # a*a+b alone: not one of the compiled shapes
+    ("(kernel k (params (vec a 1 f32) (vec b 2 f32)) (body (assign (elem a (intrinsic (Gpu) thread_idx_x)) "
+     "(read b (binop add (intrinsic (Gpu) thread_idx_x) (const i32 1))))))", "other than the element index"),   # stencil read
     ("(kernel k (params (vec a 1 f32)) (body (while (const bool true) (empty))))", "while"),
     ("(kernel k (params (vec a 1 i32) (vec b 2 i32)) (body (assign (elem a (intrinsic (Gpu) thread_idx_x)) (read b (intrinsic (Gpu) thread_idx_x)))))", "float32"),
 ])
