@@ -192,8 +192,11 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     Cm = torch.empty(M * N, dtype=torch.float32, device=tdev)
     D = torch.empty(M * N, dtype=torch.float32, device=tdev)
     bias = torch.empty(N, dtype=torch.float32, device=tdev)
-    fill(A, 1, 0, first=rank * M * K)   # rank r owns rows [r*M, (r+1)*M) of the global A and C
-    fill(Cm, 3, 0, first=rank * M * N)
+    from spoc_b200.sharding import row_block
+    first_row, rows = row_block(M * world, world, rank)   # weak scaling: the global problem has M*world rows
+    assert rows == M
+    fill(A, 1, 0, first=first_row * K)   # this rank's row block of the global A and C
+    fill(Cm, 3, 0, first=first_row * N)
     fill(bias, 4, 1)
     bcast_ms = None
     if world > 1:

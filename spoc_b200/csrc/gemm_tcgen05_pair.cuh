@@ -16,7 +16,7 @@
 // commits to the `empty` and `tmem_full` barriers of both; warps 2-5 of both
 // blocks run the epilogue on their own accumulator rows and hand the
 // accumulator back by arriving on the leader's `tmem_empty` barrier.
-// No cluster-multicast load is used anywhere.
+// Every TMA load is issued by the block that consumes it (plain per-block loads).
 #pragma once
 #include "gemm_tcgen05.cuh"
 
