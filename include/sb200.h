@@ -159,6 +159,21 @@ SB200_API int sb200_ir_auto_fuse_pipeline(const char *const *kernels, int count,
 /* analyze (Sarek_fusion.ml:340-354): one line per array "read|write NAME one_to_one|stencil[..]|gather|unknown",
  * then "barriers yes|no" */
 SB200_API int sb200_ir_analyze(const char *kernel, char *out, int outlen);
+/* The other fusion forms of the reference, selected by `kind`:
+ *   SB200_FUSE_PLAIN      can_fuse / fuse                          (Sarek_fusion.ml:401-547)
+ *   SB200_FUSE_REDUCTION  can_fuse_reduction / fuse_reduction       (:636-757)
+ *   SB200_FUSE_STENCIL    can_fuse_stencil / fuse_stencil           (:795-1018)
+ *   SB200_FUSE_TRY        try_fuse: reduction, else plain           (:759-766)
+ *   SB200_FUSE_TRY_ALL    try_fuse_all: reduction, stencil, plain   (:1022-1030)
+ * For the TRY kinds *fused is 0 when the reference would return None (out is then empty). */
+#define SB200_FUSE_PLAIN 0
+#define SB200_FUSE_REDUCTION 1
+#define SB200_FUSE_STENCIL 2
+#define SB200_FUSE_TRY 3
+#define SB200_FUSE_TRY_ALL 4
+SB200_API int sb200_ir_can_fuse_as(const char *producer, const char *consumer, const char *intermediate, int kind, int *result);
+SB200_API int sb200_ir_fuse_as(const char *producer, const char *consumer, const char *intermediate, int kind,
+                               char *out, int outlen, int *fused);
 
 /* ---- direct operators (what a recognised kernel launch dispatches to) ---
  * D[M x N] = act(alpha * A[M x K] . B[K x N] + beta * C[M x N] + bias[N]),

@@ -79,6 +79,8 @@ SIGNATURES = {
     "sb200_ir_should_fuse": ([C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, i32, C.c_char_p, i32], i32),
     "sb200_ir_auto_fuse_pipeline": ([p(C.c_char_p), i32, C.c_char_p, i32, C.c_char_p, i32, C.c_char_p, i32], i32),
     "sb200_ir_analyze": ([C.c_char_p, C.c_char_p, i32], i32),
+    "sb200_ir_can_fuse_as": ([C.c_char_p, C.c_char_p, C.c_char_p, i32, p(i32)], i32),
+    "sb200_ir_fuse_as": ([C.c_char_p, C.c_char_p, C.c_char_p, i32, C.c_char_p, i32, p(i32)], i32),
     "sb200_gemm_f32": ([i32, u64, i32, i64, i64, i64, u64, i64, u64, i64, u64, i64, f32, u64, i64, f32, u64, i32], i32),
     "sb200_gemm_f32_noalloc": ([i32, u64, i32, i64, i64, i64, u64, i64, u64, i64, u64, i64, f32, u64, i64, f32, u64, i32], i32),
     "sb200_gemm_f32_host": ([i32, i32, i64, i64, i64, C.c_void_p, i64, C.c_void_p, i64, C.c_void_p, i64, f32, C.c_void_p, i64, f32,

@@ -12,11 +12,13 @@
 //   fuse_pipeline         :570-598   greedy left to right
 //   should_fuse           :1068-1098 Fuse / DontFuse / MaybeFuse with reason
 //   auto_fuse_pipeline    :1133-1165
-// Reduction and stencil fusion (:667-1030) are not part of this backend's
-// path; a consumer that reads the intermediate more than once is classified
-// as a stencil here exactly as in the reference, so can_fuse refuses it while
-// a direct fuse still rewrites every read that uses the matching index.
+//   fuse_reduction        :609-766   map -> fold, try_fuse
+//   fuse_stencil          :772-1030  shifted producer expressions, try_fuse_all
+// A consumer that reads the intermediate more than once is classified as a
+// stencil exactly as in the reference, so can_fuse refuses it while a direct
+// fuse, fuse_stencil and try_fuse_all rewrite every read.
 #include <algorithm>
+#include <functional>
 #include <set>
 
 #include "../../include/sb200.h"
@@ -340,6 +342,214 @@ Kernel fuse_k(const Kernel& prod, const Kernel& cons, const std::string& inter) 
   return out;
 }
 
+// ---- reduction fusion (Sarek_fusion.ml:609-770) ---------------------------
+// for i = a to b: acc = acc op arr[i]  (or arr[i] op acc); returns the operator
+bool detect_reduction(const Sx& s, std::string* op, std::string* arr, std::string* loop_id) {
+  if (!s.is("for") || s.size() != 7 || s[5].s != "upto") return false;
+  const Sx& body = s[6];
+  if (!body.is("assign") || body.size() != 3 || !body[1].is("lvar") || body[1].size() < 3) return false;
+  const std::string acc = body[1][2].s;
+  const Sx& e = body[2];
+  if (!e.is("binop") || e.size() != 4) return false;
+  auto is_acc = [&](const Sx& x) { return x.is("evar") && x.size() >= 3 && x[2].s == acc; };
+  auto is_elem = [&](const Sx& x) {
+    return x.is("read") && x.size() == 3 && x[2].is("evar") && x[2].size() >= 3 && x[2][2].s == s[2].s;
+  };
+  const Sx* rd = nullptr;
+  if (is_acc(e[2]) && is_elem(e[3])) rd = &e[3];
+  else if (is_elem(e[2]) && is_acc(e[3])) rd = &e[2];
+  if (!rd) return false;
+  *op = e[1].s;
+  *arr = (*rd)[1].s;
+  *loop_id = s[2].s;
+  return true;
+}
+
+// the reference looks at the body itself and at the direct children of a top-level seq only
+bool is_reduction_kernel(const Kernel& k, const std::string& arr, std::string* op) {
+  std::function<bool(const Sx&)> find = [&](const Sx& s) -> bool {
+    if (s.is("seq")) {
+      for (size_t i = 1; i < s.size(); ++i)
+        if (find(s[i])) return true;
+      return false;
+    }
+    std::string o, a, l;
+    return detect_reduction(s, &o, &a, &l) && a == arr && ((*op = o), true);
+  };
+  return find(k.body());
+}
+
+bool can_fuse_reduction_k(const Kernel& map_k, const Kernel& red_k, const std::string& inter) {
+  Info mi = analyze(map_k), ri = analyze(red_k);
+  if (!contains(mi.write_arrays, inter) || analyze_pattern(mi.writes, inter).kind != P_ONE_TO_ONE) return false;
+  std::string op;
+  if (!is_reduction_kernel(red_k, inter, &op)) return false;
+  return !mi.barriers && !ri.barriers;
+}
+
+Sx merged_params(const Kernel& prod, const Kernel& cons, const std::string& inter) {
+  Sx params = Sx::L({Sx::A("params")});
+  std::set<std::string> names;
+  for (size_t i = 1; i < cons.params().size(); ++i) {
+    const Sx& p = cons.params()[i];
+    if (p[1].s == inter) continue;
+    params.kids.push_back(p);
+    names.insert(p[1].s);
+  }
+  for (size_t i = 1; i < prod.params().size(); ++i) {
+    const Sx& p = prod.params()[i];
+    if (p[1].s == inter || names.count(p[1].s)) continue;
+    params.kids.push_back(p);
+  }
+  return params;
+}
+
+Kernel fuse_reduction_k(const Kernel& map_k, const Kernel& red_k, const std::string& inter) {
+  AccessList w;
+  writes_stmt(map_k.body(), &w);
+  const Sx* idx = nullptr;
+  for (const Access& a : w)
+    if (a.first == inter) {
+      idx = &a.second;
+      break;
+    }
+  if (!idx) return red_k;
+  const Sx* repl = find_write_expr(map_k.body(), inter, *idx);
+  if (!repl) return red_k;
+  std::function<Sx(const Sx&)> tr = [&](const Sx& s) -> Sx {
+    if (s.atom || s.kids.empty()) return s;
+    if (s.is("for") && s.size() == 7) {
+      std::string op, arr, loop_id;
+      if (detect_reduction(s, &op, &arr, &loop_id) && arr == inter) {
+        // arr[loop_var] -> the map's expression, as written (the reference does not re-index it)
+        Sx loop_var = Sx::L({Sx::A("evar"), s[1], s[2]});
+        return Sx::L({s[0], s[1], s[2], s[3], s[4], s[5], subst_stmt(s[6], inter, loop_var, *repl)});
+      }
+      return Sx::L({s[0], s[1], s[2], s[3], s[4], s[5], tr(s[6])});
+    }
+    if (s.is("seq")) {
+      Sx o = Sx::L({s[0]});
+      for (size_t i = 1; i < s.size(); ++i) o.kids.push_back(tr(s[i]));
+      return o;
+    }
+    if (s.is("sif")) {
+      Sx o = Sx::L({s[0], s[1]});
+      for (size_t i = 2; i < s.size(); ++i) o.kids.push_back(tr(s[i]));
+      return o;
+    }
+    if (s.is("while") && s.size() == 3) return Sx::L({s[0], s[1], tr(s[2])});
+    return s;
+  };
+  Kernel out;
+  out.root = Sx::L({Sx::A("kernel"), Sx::A(red_k.name() + "_fused"), merged_params(map_k, red_k, inter),
+                    Sx::L({Sx::A("body"), tr(red_k.body())})});
+  return out;
+}
+
+// ---- stencil fusion (Sarek_fusion.ml:772-1018) ------------------------------
+bool can_fuse_stencil_k(const Kernel& prod, const Kernel& cons, const std::string& inter) {
+  Info pi = analyze(prod), ci = analyze(cons);
+  if (!contains(pi.write_arrays, inter)) return false;
+  if (!contains(ci.read_arrays, inter)) return false;
+  PatternKind k = analyze_pattern(ci.reads, inter).kind;
+  if (k != P_STENCIL && k != P_ONE_TO_ONE) return false;
+  return !pi.barriers && !ci.barriers;
+}
+
+Sx shift_expr(const Sx& e, int offset) {
+  if (offset == 0 || e.atom || e.kids.empty()) return e;
+  auto shift_idx = [&](const Sx& idx) {
+    return Sx::L({Sx::A("binop"), Sx::A(offset > 0 ? "add" : "sub"), idx,
+                  Sx::L({Sx::A("const"), Sx::A("i32"), Sx::A(std::to_string(offset > 0 ? offset : -offset))})});
+  };
+  if (e.is("read") && e.size() == 3) return Sx::L({e[0], e[1], shift_idx(e[2])});
+  if (e.is("binop") && e.size() == 4) return Sx::L({e[0], e[1], shift_expr(e[2], offset), shift_expr(e[3], offset)});
+  if (e.is("unop") && e.size() == 3) return Sx::L({e[0], e[1], shift_expr(e[2], offset)});
+  if (e.is("cast") && e.size() == 3) return Sx::L({e[0], e[1], shift_expr(e[2], offset)});
+  if (e.is("intrinsic")) {
+    Sx o = Sx::L({e[0], e[1], e[2]});
+    for (size_t i = 3; i < e.size(); ++i) o.kids.push_back(shift_expr(e[i], offset));
+    return o;
+  }
+  return e;
+}
+
+Sx subst_stencil(const Sx& e, const std::string& arr, const Sx& base_idx, const Sx& prod_expr) {
+  if (e.atom || e.kids.empty()) return e;
+  if (e.is("read") && e.size() == 3 && e[1].s == arr) {
+    Sx base;
+    int off;
+    if (extract_offset(e[2], &base, &off)) {
+      if (expr_equal(base, base_idx)) return shift_expr(prod_expr, off);
+      return e;
+    }
+    if (expr_equal(e[2], base_idx)) return prod_expr;
+    return e;
+  }
+  if (e.is("binop") && e.size() == 4)
+    return Sx::L({e[0], e[1], subst_stencil(e[2], arr, base_idx, prod_expr), subst_stencil(e[3], arr, base_idx, prod_expr)});
+  if (e.is("unop") && e.size() == 3) return Sx::L({e[0], e[1], subst_stencil(e[2], arr, base_idx, prod_expr)});
+  if (e.is("cast") && e.size() == 3) return Sx::L({e[0], e[1], subst_stencil(e[2], arr, base_idx, prod_expr)});
+  if (e.is("intrinsic")) {
+    Sx o = Sx::L({e[0], e[1], e[2]});
+    for (size_t i = 3; i < e.size(); ++i) o.kids.push_back(subst_stencil(e[i], arr, base_idx, prod_expr));
+    return o;
+  }
+  return e;
+}
+
+Kernel fuse_stencil_k(const Kernel& prod, const Kernel& cons, const std::string& inter) {
+  AccessList w;
+  writes_stmt(prod.body(), &w);
+  const Sx* widx = nullptr;
+  for (const Access& a : w)
+    if (a.first == inter) {
+      widx = &a.second;
+      break;
+    }
+  if (!widx) return cons;
+  const Sx* repl = find_write_expr(prod.body(), inter, *widx);
+  if (!repl) return cons;
+  std::function<Sx(const Sx&)> tr = [&](const Sx& s) -> Sx {
+    if (s.atom || s.kids.empty()) return s;
+    if (s.is("assign") && s.size() == 3) return Sx::L({s[0], s[1], subst_stencil(s[2], inter, *widx, *repl)});
+    if (s.is("seq")) {
+      Sx o = Sx::L({s[0]});
+      for (size_t i = 1; i < s.size(); ++i) o.kids.push_back(tr(s[i]));
+      return o;
+    }
+    if (s.is("sif")) {
+      Sx o = Sx::L({s[0], subst_stencil(s[1], inter, *widx, *repl)});
+      for (size_t i = 2; i < s.size(); ++i) o.kids.push_back(tr(s[i]));
+      return o;
+    }
+    if (s.is("while") && s.size() == 3) return Sx::L({s[0], subst_stencil(s[1], inter, *widx, *repl), tr(s[2])});
+    if (s.is("for") && s.size() == 7) return Sx::L({s[0], s[1], s[2], s[3], s[4], s[5], tr(s[6])});
+    return s;  // the reference leaves let / block bodies untouched here
+  };
+  Kernel out;
+  out.root = Sx::L({Sx::A("kernel"), Sx::A(cons.name() + "_stencil_fused"), merged_params(prod, cons, inter),
+                    Sx::L({Sx::A("body"), tr(cons.body())})});
+  return out;
+}
+
+// try_fuse (:759-766): reduction, else plain.  try_fuse_all (:1022-1030): reduction, stencil, plain.
+bool try_fuse_k(const Kernel& p, const Kernel& c, const std::string& inter, bool with_stencil, Kernel* out) {
+  if (can_fuse_reduction_k(p, c, inter)) {
+    *out = fuse_reduction_k(p, c, inter);
+    return true;
+  }
+  if (with_stencil && can_fuse_stencil_k(p, c, inter)) {
+    *out = fuse_stencil_k(p, c, inter);
+    return true;
+  }
+  if (can_fuse_k(p, c, inter)) {
+    *out = fuse_k(p, c, inter);
+    return true;
+  }
+  return false;
+}
+
 struct Hint {
   const char* decision;
   const char* reason;
@@ -438,8 +648,9 @@ int ir_auto_fuse_pipeline(const std::vector<std::string>& kernels, std::string* 
       continue;
     }
     Hint h = should_fuse_k(cur, ks[i], c[0]);
-    if (std::string(h.decision) == "Fuse" && can_fuse_k(cur, ks[i], c[0])) {
-      cur = fuse_k(cur, ks[i], c[0]);
+    Kernel fused;
+    if (std::string(h.decision) == "Fuse" && try_fuse_k(cur, ks[i], c[0], false, &fused)) {
+      cur = fused;
       eliminated->insert(eliminated->begin(), c[0]);
     } else {
       skipped->insert(skipped->begin(), h.reason);
@@ -447,6 +658,40 @@ int ir_auto_fuse_pipeline(const std::vector<std::string>& kernels, std::string* 
     }
   }
   *out = sx_print(cur.root);
+  return SB200_OK;
+}
+
+// kind: 0 plain (can_fuse / fuse), 1 reduction, 2 stencil, 3 try_fuse, 4 try_fuse_all
+int ir_can_fuse_as(const std::string& producer, const std::string& consumer, const std::string& inter, int kind, bool* ok,
+                   std::string* err) {
+  Kernel p, c;
+  if (!load_kernel(producer, &p, err) || !load_kernel(consumer, &c, err)) return SB200_ERR_PARSE;
+  Kernel tmp;
+  switch (kind) {
+    case 0: *ok = can_fuse_k(p, c, inter); break;
+    case 1: *ok = can_fuse_reduction_k(p, c, inter); break;
+    case 2: *ok = can_fuse_stencil_k(p, c, inter); break;
+    case 3: *ok = try_fuse_k(p, c, inter, false, &tmp); break;
+    case 4: *ok = try_fuse_k(p, c, inter, true, &tmp); break;
+    default: *err = "unknown fusion kind"; return SB200_ERR_INVALID_VALUE;
+  }
+  return SB200_OK;
+}
+
+int ir_fuse_as(const std::string& producer, const std::string& consumer, const std::string& inter, int kind, std::string* out,
+               bool* fused, std::string* err) {
+  Kernel p, c, r;
+  if (!load_kernel(producer, &p, err) || !load_kernel(consumer, &c, err)) return SB200_ERR_PARSE;
+  *fused = true;
+  switch (kind) {
+    case 0: r = fuse_k(p, c, inter); break;
+    case 1: r = fuse_reduction_k(p, c, inter); break;
+    case 2: r = fuse_stencil_k(p, c, inter); break;
+    case 3: *fused = try_fuse_k(p, c, inter, false, &r); break;
+    case 4: *fused = try_fuse_k(p, c, inter, true, &r); break;
+    default: *err = "unknown fusion kind"; return SB200_ERR_INVALID_VALUE;
+  }
+  *out = *fused ? sx_print(r.root) : std::string();
   return SB200_OK;
 }
 

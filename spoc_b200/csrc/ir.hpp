@@ -116,5 +116,10 @@ int ir_should_fuse(const std::string& producer, const std::string& consumer, con
 int ir_auto_fuse_pipeline(const std::vector<std::string>& kernels, std::string* out, std::vector<std::string>* eliminated,
                           std::vector<std::string>* skipped, std::string* err);
 int ir_analyze(const std::string& kernel, std::string* report, std::string* err);
+// kind: 0 plain, 1 reduction (fuse_reduction), 2 stencil (fuse_stencil), 3 try_fuse, 4 try_fuse_all
+int ir_can_fuse_as(const std::string& producer, const std::string& consumer, const std::string& inter, int kind, bool* ok,
+                   std::string* err);
+int ir_fuse_as(const std::string& producer, const std::string& consumer, const std::string& inter, int kind, std::string* out,
+               bool* fused, std::string* err);
 
 }  // namespace sb200

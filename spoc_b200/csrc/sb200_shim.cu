@@ -1088,6 +1088,27 @@ int sb200_ir_auto_fuse_pipeline(const char* const* kernels, int count, char* out
   return copy_out(text, out, outlen);
 }
 
+int sb200_ir_can_fuse_as(const char* producer, const char* consumer, const char* intermediate, int kind, int* result) {
+  if (!producer || !consumer || !intermediate || !result) return fail(SB200_ERR_INVALID_VALUE, "null argument");
+  bool ok = false;
+  std::string err;
+  int rc = ir_can_fuse_as(producer, consumer, intermediate, kind, &ok, &err);
+  if (rc) return fail(rc, "%s", err.c_str());
+  *result = ok ? 1 : 0;
+  return SB200_OK;
+}
+
+int sb200_ir_fuse_as(const char* producer, const char* consumer, const char* intermediate, int kind, char* out, int outlen,
+                     int* fused) {
+  if (!producer || !consumer || !intermediate || !fused) return fail(SB200_ERR_INVALID_VALUE, "null argument");
+  std::string text, err;
+  bool f = false;
+  int rc = ir_fuse_as(producer, consumer, intermediate, kind, &text, &f, &err);
+  if (rc) return fail(rc, "%s", err.c_str());
+  *fused = f ? 1 : 0;
+  return copy_out(text, out, outlen);
+}
+
 int sb200_ir_analyze(const char* kernel, char* out, int outlen) {
   if (!kernel) return fail(SB200_ERR_INVALID_VALUE, "null argument");
   std::string rep, err;

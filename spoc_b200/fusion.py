@@ -62,3 +62,43 @@ def auto_fuse_pipeline(kernels: Sequence[str]) -> tuple[str, list[str], list[str
     _check(L.load().sb200_ir_auto_fuse_pipeline(arr, n, out, _BUF, elim, 4096, skip, 8192))
     e, s = elim.value.decode(), skip.value.decode()
     return out.value.decode(), (e.split(",") if e else []), (s.split("\n") if s else [])
+
+
+PLAIN, REDUCTION, STENCIL, TRY, TRY_ALL = 0, 1, 2, 3, 4
+
+
+def _can_as(producer: str, consumer: str, intermediate: str, kind: int) -> bool:
+    r = C.c_int(0)
+    _check(L.load().sb200_ir_can_fuse_as(producer.encode(), consumer.encode(), intermediate.encode(), kind, C.byref(r)))
+    return bool(r.value)
+
+
+def _fuse_as(producer: str, consumer: str, intermediate: str, kind: int):
+    out, f = C.create_string_buffer(_BUF), C.c_int(0)
+    _check(L.load().sb200_ir_fuse_as(producer.encode(), consumer.encode(), intermediate.encode(), kind, out, _BUF, C.byref(f)))
+    return out.value.decode() if f.value else None
+
+
+def can_fuse_reduction(map_kernel: str, reduce_kernel: str, intermediate: str) -> bool:
+    return _can_as(map_kernel, reduce_kernel, intermediate, REDUCTION)
+
+
+def fuse_reduction(map_kernel: str, reduce_kernel: str, intermediate: str) -> str:
+    return _fuse_as(map_kernel, reduce_kernel, intermediate, REDUCTION)
+
+
+def can_fuse_stencil(producer: str, consumer: str, intermediate: str) -> bool:
+    return _can_as(producer, consumer, intermediate, STENCIL)
+
+
+def fuse_stencil(producer: str, consumer: str, intermediate: str) -> str:
+    return _fuse_as(producer, consumer, intermediate, STENCIL)
+
+
+def try_fuse(producer: str, consumer: str, intermediate: str):
+    """Fused kernel text, or None (the reference's `kernel option`)."""
+    return _fuse_as(producer, consumer, intermediate, TRY)
+
+
+def try_fuse_all(producer: str, consumer: str, intermediate: str):
+    return _fuse_as(producer, consumer, intermediate, TRY_ALL)

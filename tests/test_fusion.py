@@ -104,6 +104,53 @@ def test_auto_fuse_pipeline():          # test_fusion.ml:836-943
     assert eliminated == [] and len(skipped) == 1
 
 
+def reduce_kernel(arr="temp"):
+    loop = ("for", "i", 1, c_i32(0), c_i32(100), "upto",
+            ("assign", ("lvar", "sum", 2), ("binop", "add", ("evar", "sum", 2), ("read", arr, ("evar", "i", 1)))))
+    return kern("reduce", ("seq", ("assign", ("lvar", "sum", 2), c_i32(0)), loop), [("vec", arr, 5, "i32")])
+
+
+def test_reduction_fusion():            # test_fusion.ml:298-522
+    m = scale("map", "temp", "input", "mul", 2)
+    r = reduce_kernel()
+    assert F.can_fuse_reduction(m, r, "temp")
+    assert not F.can_fuse_reduction(m, reduce_kernel("other"), "temp")
+    fused = F.fuse_reduction(m, r, "temp")
+    assert fused.startswith("(kernel reduce_fused ")
+    assert "temp" not in F.analyze(fused)["reads"] and "(vec temp" not in fused and "(vec input" in fused
+    # the fold keeps its structure, with the map's expression at each step
+    assert "(binop add (evar sum 2) (binop mul (read input" in fused
+    assert F.try_fuse(m, r, "temp") == fused            # try_fuse prefers the reduction form
+    assert F.try_fuse(PRODUCER, CONSUMER, "temp") == F.fuse(PRODUCER, CONSUMER, "temp")
+    assert F.try_fuse(PRODUCER, stencil_consumer([-1, 1]), "temp") is None
+
+
+def test_stencil_fusion():              # test_fusion.ml:525-710
+    cons = stencil_consumer([-1, 1])
+    assert F.can_fuse_stencil(PRODUCER, cons, "temp")
+    fused = F.fuse_stencil(PRODUCER, cons, "temp")
+    assert fused.startswith("(kernel consumer_stencil_fused ")
+    info = F.analyze(fused)
+    assert "temp" not in info["reads"] and info["reads"]["input"] == "stencil[-1,1]"
+    # temp[i-1] became input[i-1] * 2: the producer's expression shifted by the read's offset
+    assert "(binop mul (read input (binop sub (intrinsic (Gpu) thread_idx_x) (const i32 1))) (const i32 2))" in fused
+    # try_fuse_all: stencil fusion also takes the one-to-one case, before plain fusion is tried
+    out = F.try_fuse_all(PRODUCER, CONSUMER, "temp")
+    assert out is not None and out.startswith("(kernel consumer_stencil_fused ")
+    gather = kern("consumer", ("assign", ("elem", "output", TX),
+                               ("binop", "add", ("read", "temp", ("read", "index", TX)), ("read", "temp", TX))))
+    assert F.try_fuse_all(PRODUCER, gather, "temp") is None
+
+
+def test_config2_chain_through_try_fuse_all():
+    """The route that does fuse a = b + 3c ; d = a*a + b automatically: try_fuse_all takes the stencil branch
+    (offsets [0]) and yields the same body as a direct fuse."""
+    p, c = S.triad_producer_ir(3.0), S.square_add_consumer_ir()
+    out = F.try_fuse_all(p, c, "a")
+    assert out is not None and out.startswith("(kernel square_add_stencil_fused ")
+    assert out.replace("square_add_stencil_fused", "square_add_fused") == F.fuse(p, c, "a")
+
+
 def test_config2_chain_behaves_like_the_reference():
     """a = b + 3c ; d = a*a + b: the consumer reads `a` twice, which the reference classifies as a
     stencil with offsets [0] (Sarek_fusion.ml:301-322): can_fuse is false, should_fuse says MaybeFuse,
