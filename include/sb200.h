@@ -51,6 +51,7 @@ extern "C" {
 #define SB200_KIND_MAP 1          /* element-wise map (vector_add, triad, fused chains) */
 #define SB200_KIND_GEMM_NAIVE 2   /* the matrix_mul IR shape */
 #define SB200_KIND_GEMM_TILED 3   /* the matrix_mul_tiled IR shape */
+#define SB200_KIND_BLOCK_REDUCE 4 /* shared-memory tree reduction with a fused map (reduce_sum, dot_product) */
 
 /* ---- argument tags for sb200_kernel_launch ---------------------------- */
 /* One entry per value the caller's run_source receives, in order: a vector

@@ -379,6 +379,30 @@ SO_EXPORT void so_par_matmul_tiled(const float *a, const float *b, float *c,
   par_run(&j, workers);
 }
 
+/* Shared-memory tree reduction, block by block, as the Native runtime runs the
+ * reduce_sum / dot_product kernels (benchmarks/bench_reduction.ml:62-105,
+ * benchmarks/bench_dot_product.ml:17-57): sdata is a double array (R2), thread
+ * t loads f(gid) or 0.0, then for c = block/2 ... 1 threads t < c add
+ * sdata[t + c] into sdata[t]; thread 0 stores sdata[0] rounded to float32.
+ * b == NULL: plain sum of a; otherwise the dot-product map a[gid] * b[gid]. */
+SO_EXPORT void so_block_tree_reduce(const float *a, const float *b, float *out,
+                                    int64_t n, int64_t nblocks, int block) {
+  double *sdata = (double *)malloc(sizeof(double) * (size_t)block);
+  for (int64_t blk = 0; blk < nblocks; ++blk) {
+    for (int t = 0; t < block; ++t) {
+      int64_t gid = blk * block + t;
+      if (gid < n)
+        sdata[t] = b ? ((double)a[gid] * (double)b[gid]) : (double)a[gid];
+      else
+        sdata[t] = 0.0;
+    }
+    for (int c = block / 2; c >= 1; c /= 2)
+      for (int t = 0; t < c; ++t) sdata[t] = sdata[t] + sdata[t + c];
+    out[blk] = (float)sdata[0];
+  }
+  free(sdata);
+}
+
 /* float32 helpers the tests use to state tolerances in ulps */
 SO_EXPORT int32_t so_ulp_distance(float x, float y) {
   int32_t ix, iy;

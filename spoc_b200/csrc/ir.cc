@@ -808,6 +808,166 @@ bool match_map_generic(Ctx& cx, const Sx& body) {
   return true;
 }
 
+void walk(const Sx& s, Env env, const std::function<void(const Sx&, const Env&)>& f);
+
+// ------------------------------------------------------- block tree reduction
+// The shape of benchmarks/bench_reduction.ml:62-105 and bench_dot_product.ml:17-57:
+//   sdata[tid] <- (gid < n ? f(a[gid], ...) : 0);  barrier
+//   for c = B/2 ... 1:  if tid < c then sdata[tid] <- sdata[tid] + sdata[tid + c];  barrier
+//   if tid = 0 then out[block_idx_x] <- sdata[0]
+std::string block_reduce_source(const KernelPlan& plan, const GenericMap& gm, const std::string& expr, int block) {
+  const size_t ni = gm.inputs.size(), ns = gm.scalars.size();
+  auto scalar_type = [&](size_t i) {
+    const std::string& elt = plan.params[gm.scalars[i]].elt;
+    return (elt == "f32" || elt == "f64") ? "double" : "long long";
+  };
+  std::ostringstream o;
+  o << "// generated for kernel '" << plan.name << "' (block tree reduction, block = " << block << ")\n";
+  o << "__device__ __forceinline__ double sb200_elem(";
+  for (size_t i = 0; i < ni; ++i) o << "float x" << i << (i + 1 < ni || ns ? ", " : "");
+  for (size_t i = 0; i < ns; ++i) o << scalar_type(i) << " s" << i << (i + 1 < ns ? ", " : "");
+  o << ") {\n";
+  for (size_t i = 0; i < ni; ++i) o << "  const double X" << i << " = (double)x" << i << ";\n";
+  o << "  return " << expr << ";\n}\n";
+  o << "extern \"C\" __global__ void __launch_bounds__(256) sb200_reduce(";
+  for (size_t i = 0; i < ni; ++i) o << "const float* __restrict__ in" << i << ", ";
+  o << "float* __restrict__ out, ";
+  for (size_t i = 0; i < ns; ++i) o << scalar_type(i) << " s" << i << ", ";
+  o << "long long n, long long nseg) {\n";
+  o << "  constexpr int B = " << block << ", PER = B / 32;\n";
+  o << "  const int lane = threadIdx.x & 31;\n";
+  o << "  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;\n";
+  o << "  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;\n";
+  o << "  for (long long seg = warp; seg < nseg; seg += nwarps) {\n";
+  o << "    double v[PER];\n";
+  o << "#pragma unroll\n    for (int j = 0; j < PER; ++j) {\n";
+  o << "      const long long g = seg * B + lane + 32 * j;\n";
+  o << "      v[j] = g < n ? sb200_elem(";
+  for (size_t i = 0; i < ni; ++i) o << "in" << i << "[g]" << (i + 1 < ni || ns ? ", " : "");
+  for (size_t i = 0; i < ns; ++i) o << "s" << i << (i + 1 < ns ? ", " : "");
+  o << ") : 0.0;\n    }\n";
+  // strides B/2 ... 32 pair registers of one lane; strides 16 ... 1 pair lanes: the reference's tree order
+  o << "#pragma unroll\n    for (int h = PER / 2; h >= 1; h >>= 1)\n";
+  o << "#pragma unroll\n      for (int j = 0; j < h; ++j) v[j] = __dadd_rn(v[j], v[j + h]);\n";
+  o << "    double r = v[0];\n";
+  o << "#pragma unroll\n    for (int c = 16; c >= 1; c >>= 1) r = __dadd_rn(r, __shfl_down_sync(0xffffffffu, r, c));\n";
+  o << "    if (lane == 0) out[seg] = (float)r;\n";
+  o << "  }\n}\n";
+  return o.str();
+}
+
+bool match_block_reduce(Ctx& cx, const Sx& body) {
+  KernelPlan& plan = *cx.plan;
+  Peeled pl;
+  peel(body, &pl, false);
+  if (pl.shared.size() != 1) return false;
+  const std::string S = *pl.shared.begin();
+  auto strip = [](const Sx* s) {
+    while ((s->is("block") && s->size() == 2) || (s->is("seq") && s->size() == 2)) s = &(*s)[1];
+    return s;
+  };
+  auto is_tid = [](const Sx& e) { return is_intrinsic(e, "thread_idx_x"); };
+  std::set<const Sx*> handled;
+  std::vector<long long> steps;
+  int barriers = 0, out = -1, n_param = -1;
+  bool bad = false, have_load = false, have_final = false;
+  Sx load_expr, gid;
+  std::string why;
+  walk(*pl.core, pl.env, [&](const Sx& s, const Env& env) {
+    if (bad) return;
+    if (s.is("barrier")) ++barriers;
+    if (s.is("for") || s.is("while") || s.is("letmut")) {
+      bad = true;
+      why = "loops are not part of the block-reduction shape";
+      return;
+    }
+    if (s.is("sif") && s.size() >= 3) {
+      const Sx cond = inline_expr(s[1], env);
+      const Sx* th = strip(&s[2]);
+      const Sx* el = s.size() == 4 ? strip(&s[3]) : nullptr;
+      const Sx *l, *r;
+      if (!th->is("assign") || th->size() != 3 || !(*th)[1].is("elem")) return;
+      const Sx& lv = (*th)[1];
+      const Sx lidx = inline_expr(lv[2], env);
+      const Sx rhs = inline_expr((*th)[2], env);
+      if (lv[1].s == S && is_tid(lidx)) {
+        if (el) {  // load step
+          if (have_load || !is_binop(cond, "lt", &l, &r) || !is_global_x(*l) || cx.scalar_param(*r, "i32") < 0 ||
+              !el->is("assign") || !(*el)[1].is("elem") || (*el)[1][1].s != S || !is_tid(inline_expr((*el)[1][2], env)) ||
+              !is_const_f_zero(inline_expr((*el)[2], env))) {
+            bad = true;
+            why = "load step is not `if gid < n then s[tid] <- f(...) else s[tid] <- 0.0`";
+            return;
+          }
+          have_load = true;
+          n_param = cx.scalar_param(*r, "i32");
+          gid = *l;
+          load_expr = rhs;
+          handled.insert(th);
+          handled.insert(el);
+        } else {  // tree step: if tid < c then s[tid] <- s[tid] + s[tid + c]
+          long long c = -1;
+          if (is_binop(cond, "lt", &l, &r) && is_tid(*l) && r->is("const")) c = atoll((*r)[2].s.c_str());
+          bool ok = c > 0 && is_comm(rhs, "add", [&](const Sx& a, const Sx& b) {
+                      if (!a.is("read") || a[1].s != S || !is_tid(a[2])) return false;
+                      if (!b.is("read") || b[1].s != S) return false;
+                      return is_comm(b[2], "add", [&](const Sx& p, const Sx& q) { return is_tid(p) && is_const_i32(q, c); });
+                    });
+          if (!ok) {
+            bad = true;
+            why = "reduction step is not `if tid < c then s[tid] <- s[tid] + s[tid + c]`";
+            return;
+          }
+          steps.push_back(c);
+          handled.insert(th);
+        }
+      } else if (lv[1].s != S) {  // final store
+        if (have_final || el || !is_binop(cond, "eq", &l, &r) || !is_tid(*l) || !is_const_i32(*r, 0) ||
+            !is_intrinsic(lidx, "block_idx_x") || !rhs.is("read") || rhs[1].s != S || !is_const_i32(rhs[2], 0) ||
+            (out = cx.vec_param(lv[1].s, "f32")) < 0) {
+          bad = true;
+          why = "final store is not `if tid = 0 then out[block_idx_x] <- s[0]`";
+          return;
+        }
+        have_final = true;
+        handled.insert(th);
+      }
+    }
+    if (s.is("assign") && s.size() == 3 && s[1].is("elem") && !handled.count(&s)) {
+      bad = true;
+      why = "store outside the load / tree / final steps";
+    }
+  });
+  if (bad || !have_load || !have_final || steps.empty()) {
+    if (!why.empty()) cx.why = why;
+    return false;
+  }
+  const long long B = steps[0] * 2;
+  bool pow2 = B >= 32 && B <= 1024 && (B & (B - 1)) == 0;
+  for (size_t i = 0; i < steps.size() && pow2; ++i)
+    if (steps[i] != (B >> (i + 1))) pow2 = false;
+  if (!pow2 || steps.back() != 1 || barriers < static_cast<int>(steps.size())) {
+    cx.why = "tree steps are not B/2, B/4, ..., 1 for a power-of-two block size of 32 to 1024";
+    return false;
+  }
+  GenericMap gm;
+  GenCtx g{&cx, &gid, &gm, {}, ""};
+  std::string code;
+  if (!gen_float(g, load_expr, &code)) {
+    cx.why = g.why;
+    return false;
+  }
+  gm.outputs.push_back(out);
+  gm.source = block_reduce_source(plan, gm, code, static_cast<int>(B));
+  plan.kind = KIND_BLOCK_REDUCE;
+  plan.generic = gm;
+  plan.reduce.n_param = n_param;
+  plan.reduce.block = static_cast<int>(B);
+  plan.description = "reduce:block_tree(jit) block=" + std::to_string(B) + " inputs=" + std::to_string(gm.inputs.size()) +
+                     " out=" + plan.params[out].name;
+  return true;
+}
+
 // ------------------------------------------------------------------- GEMM
 
 // relu wrapper: (if (binop gt X (const f32 0)) X (const f32 0))
@@ -1236,6 +1396,9 @@ int ir_compile(const std::string& text, KernelPlan* plan, std::string* err) {
     return 0;
   }
   reasons += "; tiled gemm: " + (cx.why.empty() ? std::string("shape mismatch") : cx.why);
+  cx.why.clear();
+  if (match_block_reduce(cx, *body)) return 0;
+  reasons += "; block reduction: " + (cx.why.empty() ? std::string("shape mismatch") : cx.why);
   cx.why.clear();
   if (match_map_generic(cx, *body)) return 0;
   reasons += "; generic map: " + cx.why;

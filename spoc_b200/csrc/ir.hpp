@@ -61,7 +61,7 @@ struct Coef {
 
 enum { OP_VECADD = 0, OP_TRIAD = 1, OP_CHAIN = 2, OP_CHAIN_KEEP = 3, OP_GENERIC = 4 };
 enum { IDX_GLOBAL = 0, IDX_THREAD_X = 1 };
-enum { KIND_MAP = 1, KIND_GEMM_NAIVE = 2, KIND_GEMM_TILED = 3 };
+enum { KIND_MAP = 1, KIND_GEMM_NAIVE = 2, KIND_GEMM_TILED = 3, KIND_BLOCK_REDUCE = 4 };
 
 struct MapPlan {
   int op = -1;
@@ -91,12 +91,21 @@ struct GemmPlan {
   int tile = 0;                // tiled shape: the kernel's tile size (16)
 };
 
+// Block-level tree reduction with a fused map (the reduce_sum / dot_product kernel shape):
+// out[block] = sum over the block's elements of f(inputs[gid]), zero past n.  Inputs, scalars and
+// the generated source live in KernelPlan::generic; outputs[0] is the per-block result vector.
+struct ReducePlan {
+  int n_param = -1;
+  int block = 0;  // the kernel's block size (shared array length)
+};
+
 struct KernelPlan {
   std::string name;
   std::vector<ParamInfo> params;
   int kind = 0;
   MapPlan map;
-  GenericMap generic;  // when map.op == OP_GENERIC
+  GenericMap generic;  // when map.op == OP_GENERIC, or kind == KIND_BLOCK_REDUCE
+  ReducePlan reduce;
   GemmPlan gemm;
   std::string description;
 };

@@ -131,7 +131,7 @@ int jit_compile_cubin(const std::string& source, const std::string& name, std::s
   return SB200_OK;
 }
 
-int jit_load(const std::string& cubin, JitModule* out, std::string* err) {
+int jit_load(const std::string& cubin, bool reduce, JitModule* out, std::string* err) {
   std::call_once(g_drv_once, load_driver);
   if (!g_drv.ok) {
     *err = "CUDA driver entry points for module loading are unavailable";
@@ -143,9 +143,13 @@ int jit_load(const std::string& cubin, JitModule* out, std::string* err) {
     *err = "cuModuleLoadData failed with CUresult " + std::to_string(static_cast<int>(r));
     return static_cast<int>(r);
   }
-  CUfunction fv = nullptr, fs = nullptr;
-  if ((r = g_drv.ModuleGetFunction(&fv, mod, "sb200_map_vec")) != CUDA_SUCCESS ||
-      (r = g_drv.ModuleGetFunction(&fs, mod, "sb200_map_scalar")) != CUDA_SUCCESS) {
+  CUfunction fv = nullptr, fs = nullptr, fr = nullptr;
+  if (reduce) {
+    r = g_drv.ModuleGetFunction(&fr, mod, "sb200_reduce");
+  } else if ((r = g_drv.ModuleGetFunction(&fv, mod, "sb200_map_vec")) == CUDA_SUCCESS) {
+    r = g_drv.ModuleGetFunction(&fs, mod, "sb200_map_scalar");
+  }
+  if (r != CUDA_SUCCESS) {
     g_drv.ModuleUnload(mod);
     *err = "cuModuleGetFunction failed with CUresult " + std::to_string(static_cast<int>(r));
     return static_cast<int>(r);
@@ -153,12 +157,13 @@ int jit_load(const std::string& cubin, JitModule* out, std::string* err) {
   out->module = mod;
   out->vec_fn = fv;
   out->scalar_fn = fs;
+  out->reduce_fn = fr;
   return SB200_OK;
 }
 
 void jit_unload(JitModule* m) {
   if (m->module && g_drv.ok) g_drv.ModuleUnload(static_cast<CUmodule>(m->module));
-  m->module = m->vec_fn = m->scalar_fn = nullptr;
+  m->module = m->vec_fn = m->scalar_fn = m->reduce_fn = nullptr;
 }
 
 int jit_launch(void* fn, unsigned grid, unsigned block, void* stream, void** args, std::string* err) {

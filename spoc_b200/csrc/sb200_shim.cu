@@ -518,7 +518,7 @@ int launch_generic_map(DeviceState& d, KernelObj& k, const std::vector<Slot>& s,
     std::lock_guard<std::mutex> lock(k.mu);
     if (!jm->module) {
       std::string err;
-      int rc = jit_load(k.cubin, jm, &err);
+      int rc = jit_load(k.cubin, false, jm, &err);
       if (rc) return fail(rc, "kernel '%s': %s", k.plan.name.c_str(), err.c_str());
     }
   }
@@ -584,6 +584,68 @@ int launch_generic_map(DeviceState& d, KernelObj& k, const std::vector<Slot>& s,
     count_launch();
   }
   if (body_end < n && (rc = run_scalar(body_end, n))) return rc;
+  return SB200_OK;
+}
+
+// out[b] = sum of f(inputs[gid]) over block b's elements, for the b < grid.x blocks of the reference launch
+int launch_block_reduce(DeviceState& d, KernelObj& k, const std::vector<Slot>& s, const uint32_t grid[3], const uint32_t block[3],
+                        cudaStream_t st) {
+  const KernelPlan& plan = k.plan;
+  const GenericMap& gm = plan.generic;
+  if (static_cast<int>(block[0]) != plan.reduce.block || block[1] != 1 || block[2] != 1)
+    return fail(SB200_ERR_ARGS, "kernel '%s': block is %ux%ux%u but the kernel reduces blocks of %d threads", plan.name.c_str(),
+                block[0], block[1], block[2], plan.reduce.block);
+  long long n = s[plan.reduce.n_param].i;
+  if (n < 0) n = 0;
+  long long nseg = grid[0];
+  const long long covered = std::min<long long>(n, nseg * plan.reduce.block);
+  for (int p : gm.inputs)
+    if (s[p].len < covered)
+      return fail(SB200_ERR_BOUNDS, "kernel '%s': launch reads %lld elements but vector %s holds %lld", plan.name.c_str(), covered,
+                  plan.params[p].name.c_str(), s[p].len);
+  const int out = gm.outputs[0];
+  if (s[out].len < nseg)
+    return fail(SB200_ERR_BOUNDS, "kernel '%s': %lld blocks but vector %s holds %lld", plan.name.c_str(), nseg,
+                plan.params[out].name.c_str(), s[out].len);
+  JitModule* jm = &k.jit[k.dev];
+  {
+    std::lock_guard<std::mutex> lock(k.mu);
+    if (!jm->module) {
+      std::string err;
+      int rc = jit_load(k.cubin, true, jm, &err);
+      if (rc) return fail(rc, "kernel '%s': %s", plan.name.c_str(), err.c_str());
+    }
+  }
+  std::vector<uint64_t> ptrs;
+  for (int p : gm.inputs) ptrs.push_back(s[p].ptr);
+  ptrs.push_back(s[out].ptr);
+  for (uint64_t p : ptrs)
+    if (!p || (p & 3)) return fail(SB200_ERR_INVALID_VALUE, "kernel '%s': null or misaligned device pointer", plan.name.c_str());
+  const size_t ns = gm.scalars.size();
+  std::vector<double> sd(ns);
+  std::vector<long long> si(ns);
+  std::vector<void*> args;
+  for (auto& p : ptrs) args.push_back(&p);
+  for (size_t i = 0; i < ns; ++i) {
+    const std::string& elt = plan.params[gm.scalars[i]].elt;
+    if (elt == "f32" || elt == "f64") {
+      sd[i] = s[gm.scalars[i]].f;
+      args.push_back(&sd[i]);
+    } else {
+      si[i] = s[gm.scalars[i]].i;
+      args.push_back(&si[i]);
+    }
+  }
+  args.push_back(&n);
+  args.push_back(&nseg);
+  // one warp per segment, 8 warps per block
+  long long blocks = (nseg + 7) / 8;
+  const long long cap = static_cast<long long>(d.sm_count) * 16;
+  if (blocks > cap) blocks = cap;
+  std::string err;
+  int rc = jit_launch(jm->reduce_fn, static_cast<unsigned>(blocks), 256, st, args.data(), &err);
+  if (rc) return fail(rc, "kernel '%s': %s", plan.name.c_str(), err.c_str());
+  count_launch();
   return SB200_OK;
 }
 
@@ -950,7 +1012,7 @@ int sb200_kernel_compile(int dev, const char* ir_text, const char* name, uint64_
     delete k;
     return fail(rc, "%s", err.c_str());
   }
-  if (k->plan.kind == KIND_MAP && k->plan.map.op == OP_GENERIC) {
+  if ((k->plan.kind == KIND_MAP && k->plan.map.op == OP_GENERIC) || k->plan.kind == KIND_BLOCK_REDUCE) {
     rc = jit_compile_cubin(k->plan.generic.source, k->plan.name, &k->cubin, &err);
     if (rc) {
       delete k;
@@ -1012,6 +1074,7 @@ int sb200_kernel_launch(uint64_t kernel, const sb200_arg* args, int nargs, const
     fprintf(stderr, "[sarek-b200] launch %s grid=(%u,%u,%u) block=(%u,%u,%u)\n", k->plan.description.c_str(), grid[0], grid[1],
             grid[2], block[0], block[1], block[2]);
   if (k->plan.kind == KIND_MAP) return launch_map_kernel(*d, *k, slots, grid, block, as_stream(stream));
+  if (k->plan.kind == KIND_BLOCK_REDUCE) return launch_block_reduce(*d, *k, slots, grid, block, as_stream(stream));
   return launch_gemm_kernel(*d, k->plan, slots, grid, block, as_stream(stream));
 }
 

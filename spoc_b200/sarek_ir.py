@@ -17,6 +17,7 @@ from typing import Iterable, Sequence
 __all__ = [
     "sx", "Builder", "vector_add_ir", "stream_triad_ir", "matmul_naive_ir", "matmul_tiled_ir",
     "triad_producer_ir", "square_add_consumer_ir", "chain_fused_ir", "generic_example_ir",
+    "block_reduce_ir",
 ]
 
 
@@ -282,3 +283,41 @@ def generic_example_ir() -> str:
         return ("sif", b.binop("lt", i, b.evar("n")), ("seq", ("assign", ("elem", "u", i), e1), ("assign", ("elem", "v", i), e2)))
 
     return _kernel("generic_example", p, b.let("i", "i32", b.intr("global_thread_id"), body))
+
+
+def block_reduce_ir(kind: str = "dot", block: int = 256) -> str:
+    """The shared-memory tree reductions of the reference: kind "sum" is reduce_sum_kernel
+    (benchmarks/bench_reduction.ml:62-105), kind "dot" is dot_product_kernel
+    (benchmarks/bench_dot_product.ml:17-57).  One let%superstep per line of the source:
+    load, then reduce<block/2> ... reduce1, then the final guarded store."""
+    b = Builder()
+    if kind == "dot":
+        p = b.params([("vec", "a", "f32"), ("vec", "b", "f32"), ("vec", "output", "f32"), ("scalar", "n", "i32")])
+    else:
+        p = b.params([("vec", "input", "f32"), ("vec", "output", "f32"), ("scalar", "n", "i32")])
+
+    def steps():
+        tid, gid = b.evar("tid"), b.evar("gid")
+        elem = b.binop("mul", b.read("a", gid), b.read("b", gid)) if kind == "dot" else b.read("input", gid)
+        load = ("sif", b.binop("lt", gid, b.evar("n")), ("assign", ("elem", "sdata", tid), elem),
+                ("assign", ("elem", "sdata", tid), b.c_f32(0.0)))
+        final = ("sif", b.binop("eq", tid, b.c_i32(0)),
+                 ("assign", ("elem", "output", b.intr("block_idx_x")), b.read("sdata", b.c_i32(0))))
+        chain = final
+        c = 1
+        tree = []
+        while c < block:
+            tree.append(c)
+            c *= 2
+        for c in tree:          # innermost continuation first: reduce1 wraps final, reduce2 wraps that, ...
+            step = ("sif", b.binop("lt", tid, b.c_i32(c)),
+                    ("assign", ("elem", "sdata", tid),
+                     b.binop("add", b.read("sdata", tid), b.read("sdata", b.binop("add", tid, b.c_i32(c))))))
+            chain = ("seq", ("block", step), ("barrier",), chain)
+        return ("seq", ("block", load), ("barrier",), chain)
+
+    body = b.let("sdata", ("array", "f32", "shared"), ("arraycreate", "f32", b.c_i32(block), "shared"), lambda:
+        b.let("tid", "i32", b.intr("thread_idx_x"), lambda:
+        b.let("gid", "i32", b.binop("add", b.intr("thread_idx_x"), b.binop("mul", b.intr("block_dim_x"), b.intr("block_idx_x"))),
+              steps)))
+    return _kernel("dot_product" if kind == "dot" else "reduce_sum", p, body)

@@ -44,6 +44,8 @@ def load():
     lib.so_par_chain_triad_square.argtypes = [_f, _f, _f, _f, f64, i64, i32]
     lib.so_par_matmul_naive.argtypes = [_f, _f, _f, i64, i64, i64, i64, i64, f64, f64, vp, vp, i32, i32, i32]
     lib.so_par_matmul_tiled.argtypes = [_f, _f, _f, i64, i64, i64, i64, i64, i32]
+    lib.so_block_tree_reduce.argtypes = [_f, vp, _f, i64, i64, i32]
+    lib.so_block_tree_reduce.restype = None
     lib.so_ulp_distance.argtypes = [C.c_float, C.c_float]
     lib.so_ulp_distance.restype = C.c_int32
     for n in ("so_fill", "so_vector_add", "so_stream_triad", "so_chain_triad_square", "so_matmul_rows", "so_matmul_points",

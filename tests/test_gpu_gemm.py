@@ -337,3 +337,78 @@ def test_config_8192_cubed_epilogue_sampled(backend, device, mode):
     finally:
         for x in bufs + [Bi]:
             backend.Memory.free(x)
+
+
+def _sampled_check(backend, device, lib, mode, M, N, K, A, B, D, a_rows_needed, rng, alpha=1.0, beta=0.0, Cm=None, Bi=None, act=0,
+                   n_rows=4, n_points=512, scale=1.0):
+    """Compare sampled rows and points of a device result with the oracle, downloading only what is needed:
+    all of B, the sampled rows of A (and of C)."""
+    import ctypes as C
+    from spoc_b200.plugin import _check
+    b = np.empty(K * N, np.float32)
+    backend.Memory.device_to_host(src=B, dst=b)
+    bias = None
+    if Bi is not None:
+        bias = np.empty(N, np.float32)
+        backend.Memory.device_to_host(src=Bi, dst=bias)
+    rows = sorted(set(rng.integers(0, M, n_rows).tolist()) | {0, M - 1})
+    pr, pc = rng.integers(0, M, n_points), rng.integers(0, N, n_points)
+    need = sorted(set(rows) | set(pr.tolist()))
+    index = {r: i for i, r in enumerate(need)}
+    a_s, c_s, d_s = np.empty((len(need), K), np.float32), np.empty((len(need), N), np.float32), np.empty((len(need), N), np.float32)
+    for i, r in enumerate(need):
+        _check(lib.sb200_memcpy_dtoh(device.id, a_s[i].ctypes.data_as(C.c_void_p), A.ptr + 4 * r * K, 4 * K))
+        _check(lib.sb200_memcpy_dtoh(device.id, d_s[i].ctypes.data_as(C.c_void_p), D.ptr + 4 * r * N, 4 * N))
+        if Cm is not None:
+            _check(lib.sb200_memcpy_dtoh(device.id, c_s[i].ctypes.data_as(C.c_void_p), Cm.ptr + 4 * r * N, 4 * N))
+    a_flat, c_flat = a_s.ravel(), (c_s.ravel() if Cm is not None else None)
+    # the oracle sees the sampled rows as a small matrix whose row i is original row need[i]
+    ri = [index[r] for r in rows]
+    ref_rows = np.vstack([O.gemm(a_flat, b, len(need), N, K, alpha, beta, c_flat, bias, act, r0=i, r1=i + 1) for i in ri])
+    rms = float(np.sqrt(np.mean(ref_rows.astype(np.float64) ** 2)))
+    bound = tol(mode, K) * scale
+    err = np.abs(d_s[ri].astype(np.float64) - ref_rows) / np.maximum(np.abs(ref_rows), rms)
+    assert err.max() <= bound
+    pi = np.array([index[r] for r in pr.tolist()])
+    ref_pts = O.gemm_points(a_flat, b, N, K, pi, pc, alpha, beta, c_flat, bias, act)
+    err = np.abs(d_s[pi, pc].astype(np.float64) - ref_pts) / np.maximum(np.abs(ref_pts), rms)
+    assert err.max() <= bound
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_config_skinny_65536x4096x4096_normal_inputs_sampled(backend, device, mode):
+    """M=65536, N=K=4096; A rows N(0,1), B N(0, 1/sqrt(K)) generated on the device; plain product."""
+    from spoc_b200.plugin import _check
+    lib = L.load()
+    M, N, K = 65536, 4096, 4096
+    A, B, D = (backend.Memory.alloc(device, n, np.float32) for n in (M * K, K * N, M * N))
+    try:
+        _check(lib.sb200_fill_f32(device.id, 0, A.ptr, M * K, 20260101, 1, 2, 1.0, 0))
+        _check(lib.sb200_fill_f32(device.id, 0, B.ptr, K * N, 20260101, 2, 2, 1.0 / math.sqrt(K), 0))
+        _check(lib.sb200_gemm_f32(device.id, 0, mode, M, N, K, A.ptr, K, B.ptr, N, D.ptr, N, 1.0, 0, 0, 0.0, 0, 0))
+        backend.Device.synchronize(device)
+        _sampled_check(backend, device, lib, mode, M, N, K, A, B, D, None, np.random.default_rng(4), n_rows=8, n_points=1024)
+    finally:
+        for x in (A, B, D):
+            backend.Memory.free(x)
+
+
+def test_config_32768_cubed_epilogue_sampled(backend, device):
+    """M=N=K=32768 with D = max(0, 1.5 A.B + 0.5 C + bias), 3xTF32, on one GPU (the 8-GPU configuration's
+    single-device reference run: 4 x 4 GiB operands + 16 GiB of panels); sampled rows and points."""
+    from spoc_b200.plugin import _check
+    lib = L.load()
+    M = N = K = 32768
+    mode = L.MODE_3XTF32
+    A, B, Cm, D = (backend.Memory.alloc(device, M * K, np.float32) for _ in range(4))
+    Bi = backend.Memory.alloc(device, N, np.float32)
+    try:
+        for buf, sid, kind, cnt in ((A, 1, 0, M * K), (B, 2, 0, K * N), (Cm, 3, 0, M * N), (Bi, 4, 1, N)):
+            _check(lib.sb200_fill_f32(device.id, 0, buf.ptr, cnt, 20260101, sid, kind, 1.0, 0))
+        _check(lib.sb200_gemm_f32(device.id, 0, mode, M, N, K, A.ptr, K, B.ptr, N, D.ptr, N, 1.5, Cm.ptr, N, 0.5, Bi.ptr, 1))
+        backend.Device.synchronize(device)
+        _sampled_check(backend, device, lib, mode, M, N, K, A, B, D, None, np.random.default_rng(5), alpha=1.5, beta=0.5, Cm=Cm,
+                       Bi=Bi, act=1, n_rows=2, n_points=256, scale=1.5 * math.sqrt(2))
+    finally:
+        for x in (A, B, Cm, D, Bi):
+            backend.Memory.free(x)

@@ -222,3 +222,34 @@ def test_unfused_consumer_runs_through_the_generated_path(backend, device):
     assert np.array_equal(vd.to_array(), want)
     for t in (vd, va, vb):
         t.free()
+
+
+@pytest.mark.parametrize("kind", ["dot", "sum"])
+@pytest.mark.parametrize("n,block", [(1000, 256), (256 * 40, 256), (100003, 256), (5000, 64), (70000, 1024)])
+def test_block_tree_reduction_is_bit_exact(backend, device, oracle, kind, n, block):
+    """reduce_sum / dot_product: one output per block, summed in the reference's tree order in double."""
+    import ctypes as C
+    a, b = O.fill(n, 41, 1), O.fill(n, 41, 2)
+    nblocks = (n + block - 1) // block
+    va, vb, vo = Vector(backend, a.copy()), Vector(backend, b.copy()), Vector(backend, np.full(nblocks + 3, CANARY, np.float32))
+    args = [va, vb, vo, ("int32", n)] if kind == "dot" else [va, vo, ("int32", n)]
+    run_vectors(backend, device=device, ir=sarek_ir.block_reduce_ir(kind, block), args=args, block=dims1d(block), grid=dims1d(nblocks),
+                shared_mem=block * 4)
+    want = np.empty(nblocks, np.float32)
+    oracle.so_block_tree_reduce(a, b.ctypes.data_as(C.c_void_p) if kind == "dot" else None, want, n, nblocks, block)
+    got = vo.to_array()
+    assert np.array_equal(got[:nblocks], want)
+    assert np.all(got[nblocks:] == CANARY)
+    for v in (va, vb, vo):
+        v.free()
+
+
+def test_block_reduction_with_wrong_block_size_is_rejected(backend, device):
+    n = 1024
+    va, vo = Vector.create(backend, n), Vector.create(backend, 8)
+    with pytest.raises(BackendError) as e:
+        run_vectors(backend, device=device, ir=sarek_ir.block_reduce_ir("sum", 256), args=[va, vo, ("int32", n)], block=dims1d(128),
+                    grid=dims1d(8))
+    assert e.value.code == L.ERR_ARGS
+    va.free()
+    vo.free()

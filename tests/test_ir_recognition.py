@@ -40,6 +40,13 @@ def test_other_elementwise_expressions_take_the_generated_kernel_path():
     assert "map:generic(jit) inputs=3 outputs=2 scalars=1 guarded" in k.describe()
 
 
+@pytest.mark.parametrize("kind,block,inputs", [("dot", 256, 2), ("sum", 256, 1), ("sum", 64, 1)])
+def test_block_tree_reductions_are_recognised(kind, block, inputs):
+    k = compile_(S.block_reduce_ir(kind, block))
+    assert k.kind == L.KIND_BLOCK_REDUCE
+    assert f"reduce:block_tree(jit) block={block} inputs={inputs} out=output" in k.describe()
+
+
 def test_commuted_operands_and_expanded_thread_id_are_recognised():
     b = S.Builder()
     p = b.params([("vec", "a", "f32"), ("vec", "b", "f32"), ("vec", "c", "f32"), ("scalar", "s", "f32"), ("scalar", "n", "i32")])

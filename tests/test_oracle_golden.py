@@ -142,3 +142,26 @@ def test_ulp_distance_helper():
     y = np.array([np.nextafter(np.float32(1.0), np.float32(2.0)), -1.0, -0.0, 1.5], np.float32)
     d = O.ulp_distance(x, y)
     assert d[0] == 1 and d[1] == 0 and d[2] == 0 and d[3] > 1000
+
+
+def test_block_tree_reduce_matches_reference_fixture():
+    """benchmarks/bench_dot_product.ml:58-66: a=(i mod 100)/100, b=((i+1) mod 100)/100, expected = sequential
+    double sum of a*b; the benchmark sums the per-block partial results on the host."""
+    n, block = 100000, 256
+    i = np.arange(n)
+    a64, b64 = (i % 100) / 100.0, ((i + 1) % 100) / 100.0
+    a, b = a64.astype(np.float32), b64.astype(np.float32)
+    nblocks = (n + block - 1) // block
+    out = np.empty(nblocks, np.float32)
+    O.load().so_block_tree_reduce(a, b.ctypes.data_as(C.c_void_p), out, n, nblocks, block)
+    expected = float(np.sum(a64 * b64))
+    assert abs(float(out.astype(np.float64).sum()) - expected) / expected < 1e-5
+    # per block: the tree order in double, against an independent numpy evaluation of the same tree
+    prod = np.zeros(nblocks * block)
+    prod[:n] = a.astype(np.float64) * b.astype(np.float64)
+    t = prod.reshape(nblocks, block)
+    c = block // 2
+    while c >= 1:
+        t = t[:, :c] + t[:, c:2 * c]
+        c //= 2
+    assert np.array_equal(out, t[:, 0].astype(np.float32))
