@@ -83,6 +83,7 @@ class _Device:
 
     def __init__(self) -> None:
         self._current = 0
+        self._cache: dict[int, "_Device.T"] = {}   # device properties are slow to query: ask once
 
     def init(self) -> None:
         _check(L.load().sb200_init())
@@ -93,10 +94,13 @@ class _Device:
         return n.value
 
     def get(self, idx: int) -> "_Device.T":
-        info = L.DeviceInfo()
-        _check(L.load().sb200_device_get_info(idx, C.byref(info)))
-        return _Device.T(idx, info.name.decode(), info.total_mem, (info.cc_major, info.cc_minor), info.sm_count,
-                         info.max_shared_per_block, info.l2_bytes)
+        d = self._cache.get(idx)
+        if d is None:
+            info = L.DeviceInfo()
+            _check(L.load().sb200_device_get_info(idx, C.byref(info)))
+            d = self._cache[idx] = _Device.T(idx, info.name.decode(), info.total_mem, (info.cc_major, info.cc_minor),
+                                             info.sm_count, info.max_shared_per_block, info.l2_bytes)
+        return d
 
     def id(self, d: "_Device.T") -> int:
         return d.id
