@@ -1,0 +1,375 @@
+// sarek_b200.hpp — C++ host side of the B200 plugin, above the C ABI.
+//
+// The reference's host language (OCaml) has no toolchain where this library is
+// built, so the plugin's host half is written in C++ with the members, argument
+// meaning and error behaviour of the interface it stands for:
+//
+//   sarek_b200::Backend        Framework_sig.BACKEND  (spoc/framework/Framework_sig.ml:137-350),
+//                              arranged like sarek-cuda/Cuda_plugin.ml:146-224
+//   Backend::Device/Stream/Memory/Event/Kernel   the nested modules of BACKEND
+//   Backend::run_source        Cuda_plugin.ml:174-210 (compile cached, bind args in order, launch)
+//   sarek_b200::Vector         Spoc_core.Vector for float32 (sarek/core/Vector_types.ml:198-229):
+//                              host storage + lazily allocated device buffer + location state
+//   sarek_b200::run_vectors    Sarek.Execute.run_vectors (sarek/sarek/Execute.ml:197-216,231-304,
+//                              321-335,520-543): transfer, expand Vec -> (buffer, int32 length),
+//                              launch, mark every vector argument stale on the CPU
+//   sarek_b200::fusion::*      Sarek_fusion (sarek/sarek/Sarek_fusion.ml) over IR text
+//
+// Errors are exceptions (BackendError, UnsupportedConstruct), like Cuda_api.Cuda_error
+// (sarek-cuda/Cuda_api.ml:27-31) and Backend_error (spoc/framework/Backend_error.ml:21-78).
+// Header-only; link with -lsarek_b200.  Nothing here computes.
+#pragma once
+#include <cstdint>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <variant>
+#include <vector>
+
+#include "../../include/sb200.h"
+
+namespace sarek_b200 {
+
+struct BackendError : std::runtime_error {
+  int code;
+  BackendError(int c, const std::string& m) : std::runtime_error("[sarek-b200] error " + std::to_string(c) + ": " + m), code(c) {}
+};
+struct UnsupportedConstruct : BackendError {
+  using BackendError::BackendError;
+};
+
+inline void check(int rc) {
+  if (rc == SB200_OK) return;
+  const std::string msg = sb200_last_error_string();
+  if (rc == SB200_ERR_UNSUPPORTED) throw UnsupportedConstruct(rc, msg);
+  throw BackendError(rc, msg);
+}
+
+struct Dims {  // Framework_sig.dims
+  uint32_t x = 1, y = 1, z = 1;
+};
+inline Dims dims1d(uint32_t x) { return {x, 1, 1}; }
+inline Dims dims2d(uint32_t x, uint32_t y) { return {x, y, 1}; }
+
+// Framework_sig.run_source_arg
+struct RSA_Buffer { uint64_t device_ptr; int length; };
+struct RSA_Int32 { int32_t v; };
+struct RSA_Int64 { int64_t v; };
+struct RSA_Float32 { float v; };
+struct RSA_Float64 { double v; };
+using RunSourceArg = std::variant<RSA_Buffer, RSA_Int32, RSA_Int64, RSA_Float32, RSA_Float64>;
+
+class Backend {
+ public:
+  static constexpr const char* name = "B200";
+  static constexpr const char* execution_model = "JIT";
+  static constexpr const char* source_lang = "SarekIR_sexp";
+
+  // ---- Device ----------------------------------------------------------
+  struct DeviceT {
+    int id = 0;
+    std::string name;
+    uint64_t total_mem = 0;
+    int cc_major = 0, cc_minor = 0, sm_count = 0;
+  };
+  struct DeviceM {
+    Backend* b;
+    void init() const { check(sb200_init()); }
+    int count() const {
+      int n = 0;
+      check(sb200_device_count(&n));
+      return n;
+    }
+    const DeviceT& get(int idx) const {
+      auto it = b->devices_.find(idx);
+      if (it == b->devices_.end()) {
+        sb200_device_info info;
+        check(sb200_device_get_info(idx, &info));
+        DeviceT d{idx, info.name, info.total_mem, info.cc_major, info.cc_minor, info.sm_count};
+        it = b->devices_.emplace(idx, d).first;
+      }
+      return it->second;
+    }
+    void set_current(const DeviceT& d) const {
+      check(sb200_device_set_current(d.id));
+      b->current_ = d.id;
+    }
+    int get_current_device() const { return b->current_; }
+    void synchronize(const DeviceT& d) const { check(sb200_device_synchronize(d.id)); }
+  };
+
+  // ---- Stream / Event --------------------------------------------------
+  struct StreamT { int dev; uint64_t handle; };
+  struct StreamM {
+    StreamT create(const DeviceT& d) const {
+      uint64_t h = 0;
+      check(sb200_stream_create(d.id, &h));
+      return {d.id, h};
+    }
+    void destroy(StreamT& s) const {
+      check(sb200_stream_destroy(s.dev, s.handle));
+      s.handle = 0;
+    }
+    void synchronize(const StreamT& s) const { check(sb200_stream_synchronize(s.dev, s.handle)); }
+    StreamT default_stream(const DeviceT& d) const { return {d.id, 0}; }
+  };
+  struct EventT { int dev; uint64_t handle; };
+  struct EventM {
+    Backend* b;
+    EventT create() const {
+      uint64_t h = 0;
+      check(sb200_event_create(b->current_, &h));
+      return {b->current_, h};
+    }
+    void destroy(EventT& e) const {
+      check(sb200_event_destroy(e.dev, e.handle));
+      e.handle = 0;
+    }
+    void record(const EventT& e, const StreamT& s) const { check(sb200_event_record(e.dev, e.handle, s.handle)); }
+    void synchronize(const EventT& e) const { check(sb200_event_synchronize(e.dev, e.handle)); }
+    float elapsed(const EventT& start, const EventT& stop) const {
+      float ms = 0;
+      check(sb200_event_elapsed_ms(start.dev, start.handle, stop.handle, &ms));
+      return ms;
+    }
+  };
+
+  // ---- Memory ----------------------------------------------------------
+  struct Buffer {
+    int dev = 0;
+    uint64_t ptr = 0;
+    size_t size = 0;       // elements
+    size_t elem_size = 0;  // bytes
+  };
+  struct MemoryM {
+    Buffer alloc_custom(const DeviceT& d, size_t size, size_t elem_size) const {
+      uint64_t p = 0;
+      check(sb200_mem_alloc(d.id, size * elem_size, &p));
+      return {d.id, p, size, elem_size};
+    }
+    Buffer alloc(const DeviceT& d, size_t size) const { return alloc_custom(d, size, sizeof(float)); }
+    void free(Buffer& b) const { check(sb200_mem_free(b.dev, b.ptr)); }  // idempotent in the library
+    void host_ptr_to_device(const void* src, size_t bytes, const Buffer& dst) const {
+      check(sb200_memcpy_htod(dst.dev, dst.ptr, src, bytes));
+    }
+    void device_to_host_ptr(const Buffer& src, void* dst, size_t bytes) const {
+      check(sb200_memcpy_dtoh(src.dev, dst, src.ptr, bytes));
+    }
+    void device_to_device(const Buffer& src, const Buffer& dst) const {
+      check(sb200_memcpy_dtod(dst.dev, dst.ptr, src.ptr, std::min(src.size * src.elem_size, dst.size * dst.elem_size)));
+    }
+    size_t size(const Buffer& b) const { return b.size; }
+    uint64_t device_ptr(const Buffer& b) const { return b.ptr; }
+    bool is_zero_copy(const Buffer&) const { return false; }
+  };
+
+  // ---- Kernel ----------------------------------------------------------
+  struct KernelT { int dev; uint64_t handle; };
+  struct Args {
+    std::vector<sb200_arg> items;  // positional: set_arg_* append and ignore their index, as the reference's do
+  };
+  struct KernelM {
+    Backend* b;
+    KernelT compile(const DeviceT& d, const std::string& name, const std::string& source) const {
+      uint64_t h = 0;
+      check(sb200_kernel_compile(d.id, source.c_str(), name.c_str(), &h));
+      return {d.id, h};
+    }
+    KernelT compile_cached(const DeviceT& d, const std::string& name, const std::string& source) const {
+      auto key = std::make_pair(d.id, source);
+      auto it = b->kernels_.find(key);
+      if (it == b->kernels_.end()) it = b->kernels_.emplace(key, compile(d, name, source)).first;
+      return it->second;
+    }
+    void clear_cache() const {
+      for (auto& kv : b->kernels_) sb200_kernel_destroy(kv.second.handle);
+      b->kernels_.clear();
+    }
+    int kind(const KernelT& k) const {
+      int v = 0;
+      check(sb200_kernel_kind(k.handle, &v));
+      return v;
+    }
+    std::string describe(const KernelT& k) const {
+      char buf[512];
+      check(sb200_kernel_describe(k.handle, buf, sizeof buf));
+      return buf;
+    }
+    Args create_args() const { return {}; }
+    static sb200_arg make(int tag) {
+      sb200_arg a;
+      std::memset(&a, 0, sizeof a);
+      a.tag = tag;
+      return a;
+    }
+    void set_arg_buffer(Args& a, int, const Buffer& buf) const { auto x = make(SB200_ARG_BUFFER); x.v.buffer = buf.ptr; a.items.push_back(x); }
+    void set_arg_ptr(Args& a, int, uint64_t p) const { auto x = make(SB200_ARG_BUFFER); x.v.buffer = p; a.items.push_back(x); }
+    void set_arg_int32(Args& a, int, int32_t v) const { auto x = make(SB200_ARG_I32); x.v.i32 = v; a.items.push_back(x); }
+    void set_arg_int64(Args& a, int, int64_t v) const { auto x = make(SB200_ARG_I64); x.v.i64 = v; a.items.push_back(x); }
+    void set_arg_float32(Args& a, int, float v) const { auto x = make(SB200_ARG_F32); x.v.f32 = v; a.items.push_back(x); }
+    void set_arg_float64(Args& a, int, double v) const { auto x = make(SB200_ARG_F64); x.v.f64 = v; a.items.push_back(x); }
+    void launch(const KernelT& k, const Args& a, Dims grid, Dims block, uint32_t shared_mem, uint64_t stream = 0) const {
+      const uint32_t g[3] = {grid.x, grid.y, grid.z}, bl[3] = {block.x, block.y, block.z};
+      check(sb200_kernel_launch(k.handle, a.items.data(), static_cast<int>(a.items.size()), g, bl, shared_mem, stream));
+    }
+  };
+
+  Backend() : Device{this}, Event{this}, Kernel{this} {}
+  ~Backend() { Kernel.clear_cache(); }
+  Backend(const Backend&) = delete;
+  Backend& operator=(const Backend&) = delete;
+
+  DeviceM Device;
+  StreamM Stream;
+  MemoryM Memory;
+  EventM Event;
+  KernelM Kernel;
+
+  bool is_available() const {
+    int n = 0;
+    return sb200_device_count(&n) == SB200_OK && n > 0;
+  }
+  // IR -> source: the IR text is its own source language
+  std::string generate_source(const std::string& ir) const { return ir; }
+  void enable_profiling() const { check(sb200_enable_profiling(1)); }
+  void disable_profiling() const { check(sb200_enable_profiling(0)); }
+  void set_mode(int mode) const { check(sb200_set_mode(mode)); }
+
+  void run_source(const std::string& source, const std::string& lang, const std::string& kernel_name, Dims block, Dims grid,
+                  uint32_t shared_mem, const std::vector<RunSourceArg>& args) {
+    if (lang != source_lang) throw BackendError(SB200_ERR_UNSUPPORTED, "run_source: source language " + lang + " not supported");
+    const DeviceT& dev = Device.get(Device.get_current_device());
+    KernelT k = Kernel.compile_cached(dev, kernel_name, source);
+    Args ka = Kernel.create_args();
+    int i = 0;
+    for (const RunSourceArg& a : args) {
+      if (auto* p = std::get_if<RSA_Buffer>(&a)) Kernel.set_arg_ptr(ka, i, p->device_ptr);
+      else if (auto* q = std::get_if<RSA_Int32>(&a)) Kernel.set_arg_int32(ka, i, q->v);
+      else if (auto* r = std::get_if<RSA_Int64>(&a)) Kernel.set_arg_int64(ka, i, r->v);
+      else if (auto* s = std::get_if<RSA_Float32>(&a)) Kernel.set_arg_float32(ka, i, s->v);
+      else Kernel.set_arg_float64(ka, i, std::get<RSA_Float64>(a).v);
+      ++i;
+    }
+    Kernel.launch(k, ka, grid, block, shared_mem);
+  }
+
+ private:
+  int current_ = 0;
+  std::map<int, DeviceT> devices_;
+  std::map<std::pair<int, std::string>, KernelT> kernels_;
+};
+
+// ---- Vector / run_vectors ------------------------------------------------
+class Vector {
+ public:
+  enum Location { CPU, Both, Stale_CPU };
+  Vector(Backend& b, size_t n) : backend_(&b), host_(n, 0.0f) {}
+  Vector(Backend& b, std::vector<float> data) : backend_(&b), host_(std::move(data)) {}
+  ~Vector() { free_buffer(); }
+  Vector(const Vector&) = delete;
+  Vector& operator=(const Vector&) = delete;
+
+  size_t length() const { return host_.size(); }
+  Location location() const { return loc_; }
+  void to_device(const Backend::DeviceT& dev) {
+    if (!buf_.ptr) buf_ = backend_->Memory.alloc(dev, host_.size());
+    if (loc_ == CPU) {
+      backend_->Memory.host_ptr_to_device(host_.data(), host_.size() * sizeof(float), buf_);
+      loc_ = Both;
+    }
+  }
+  const std::vector<float>& to_array() {
+    if (loc_ == Stale_CPU) {
+      backend_->Memory.device_to_host_ptr(buf_, host_.data(), host_.size() * sizeof(float));
+      loc_ = Both;
+    }
+    return host_;
+  }
+  float get(size_t i) { return to_array().at(i); }
+  void set(size_t i, float v) {
+    to_array();
+    host_.at(i) = v;
+    loc_ = CPU;
+  }
+  void mark_stale() {
+    if (loc_ == Both) loc_ = Stale_CPU;
+  }
+  void free_buffer() {
+    if (buf_.ptr) {
+      sb200_mem_free(buf_.dev, buf_.ptr);
+      buf_ = {};
+      if (loc_ == Stale_CPU) loc_ = CPU;  // the device copy is gone; what the host holds is all there is
+    }
+  }
+  const Backend::Buffer& buffer() const { return buf_; }
+
+ private:
+  Backend* backend_;
+  std::vector<float> host_;
+  Backend::Buffer buf_;
+  Location loc_ = CPU;
+};
+
+struct ScalarArg {
+  enum Kind { Int32, Int64, Float32, Float64 } kind;
+  double f = 0;
+  int64_t i = 0;
+  static ScalarArg int32(int32_t v) { return {Int32, double(v), v}; }
+  static ScalarArg int64(int64_t v) { return {Int64, double(v), v}; }
+  static ScalarArg float32(float v) { return {Float32, v, int64_t(v)}; }
+  static ScalarArg float64(double v) { return {Float64, v, int64_t(v)}; }
+};
+using ExecArg = std::variant<Vector*, ScalarArg>;
+
+inline void run_vectors(Backend& backend, const Backend::DeviceT& device, const std::string& ir, const std::vector<ExecArg>& args,
+                        Dims block, Dims grid, uint32_t shared_mem = 0, const std::string& kernel_name = "sarek_kern") {
+  std::vector<RunSourceArg> rs;
+  for (const ExecArg& a : args) {
+    if (auto* v = std::get_if<Vector*>(&a)) {
+      (*v)->to_device(device);
+      rs.push_back(RSA_Buffer{(*v)->buffer().ptr, static_cast<int>((*v)->length())});
+      rs.push_back(RSA_Int32{static_cast<int32_t>((*v)->length())});
+    } else {
+      const ScalarArg& s = std::get<ScalarArg>(a);
+      switch (s.kind) {
+        case ScalarArg::Int32: rs.push_back(RSA_Int32{static_cast<int32_t>(s.i)}); break;
+        case ScalarArg::Int64: rs.push_back(RSA_Int64{s.i}); break;
+        case ScalarArg::Float32: rs.push_back(RSA_Float32{static_cast<float>(s.f)}); break;
+        case ScalarArg::Float64: rs.push_back(RSA_Float64{s.f}); break;
+      }
+    }
+  }
+  backend.Device.set_current(device);
+  backend.run_source(backend.generate_source(ir), Backend::source_lang, kernel_name, block, grid, shared_mem, rs);
+  for (const ExecArg& a : args)
+    if (auto* v = std::get_if<Vector*>(&a)) (*v)->mark_stale();
+}
+
+// ---- Sarek_fusion over IR text ---------------------------------------------
+namespace fusion {
+inline bool can_fuse(const std::string& p, const std::string& c, const std::string& inter) {
+  int r = 0;
+  check(sb200_ir_can_fuse(p.c_str(), c.c_str(), inter.c_str(), &r));
+  return r != 0;
+}
+inline std::string fuse(const std::string& p, const std::string& c, const std::string& inter) {
+  std::string out(1 << 20, '\0');
+  check(sb200_ir_fuse(p.c_str(), c.c_str(), inter.c_str(), &out[0], static_cast<int>(out.size())));
+  out.resize(std::strlen(out.c_str()));
+  return out;
+}
+// try_fuse_all: empty optional-like result (false) when the reference returns None
+inline bool try_fuse_all(const std::string& p, const std::string& c, const std::string& inter, std::string* fused) {
+  std::string out(1 << 20, '\0');
+  int f = 0;
+  check(sb200_ir_fuse_as(p.c_str(), c.c_str(), inter.c_str(), SB200_FUSE_TRY_ALL, &out[0], static_cast<int>(out.size()), &f));
+  out.resize(std::strlen(out.c_str()));
+  if (f) *fused = out;
+  return f != 0;
+}
+}  // namespace fusion
+
+}  // namespace sarek_b200
