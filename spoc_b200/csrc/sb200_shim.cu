@@ -286,17 +286,9 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   // against one prepared B pass the largest block so that the B panels keep their place.
   if (panel_rows_a < M) panel_rows_a = M;
   using Cfg = GemmCfg<MODE>;
-  static std::once_flag attr_once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(attr_once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_tf32_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(Cfg::kSmemBytes));
-  });
-  // the attribute is per device; set it again when several devices are in use
-  cudaError_t ae = cudaFuncSetAttribute(gemm_tf32_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(Cfg::kSmemBytes));
-  if (ae != cudaSuccess) return cuda_fail(ae, "cudaFuncSetAttribute(max dynamic shared memory)");
-  (void)attr_err;
+  // the attribute is per device, so it is set on every call (a cheap host-side call)
+  CU_TRY(cudaFuncSetAttribute(gemm_tf32_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(Cfg::kSmemBytes)));
 
   const long long kp = round_up(K, GEMM_BK);
   const size_t a_bytes = round_up(panel_rows_a * kp * 4, 1024), b_bytes = round_up(N * kp * 4, 1024);
