@@ -234,8 +234,11 @@ SB200_API int sb200_set_mode(int mode);
 SB200_API int sb200_get_mode(int *mode);
 /* which tensor-core kernel sb200_gemm_f32 launches: 0 = automatic (CTA pairs on
  * 256x256 tiles when M > 128, else single-CTA 128x256 tiles), 1 = always
- * single-CTA tiles, 2 = always CTA pairs.  Also SAREK_B200_GEMM=single|pair.
- * Results of the two kernels agree to the last bit. */
+ * single-CTA tiles, 2 = always CTA pairs, 3 = CTA pairs fed from prepared
+ * operand panels even where TF32 mode could read the caller's matrices
+ * directly.  Also SAREK_B200_GEMM=single|pair|pair-panels.  All variants round
+ * operands to TF32 the same way (nearest-even) and sum k ascending, so their
+ * results agree to the last bit. */
 SB200_API int sb200_set_gemm_variant(int variant);
 
 /* seeded synthetic data written on the device: kind 0 U[-1,1), 1 U[-0.1,0.1),

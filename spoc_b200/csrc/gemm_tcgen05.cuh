@@ -9,7 +9,7 @@
 //
 // Two stages:
 //  1. operand preparation (prep_a_kernel / prep_b_kernel): A and B are split
-//     into TF32-exact panels  hi = rna_tf32(x),  lo = rna_tf32(x - hi)  (lo only
+//     into TF32-exact panels  hi = rn_tf32(x),  lo = rn_tf32(x - hi)  (lo only
 //     in 3xTF32 mode).  B is transposed on the way so both panels are K-major,
 //     and K is zero-padded to a multiple of 32 so every TMA box starts on a
 //     128-byte boundary whatever K is.
@@ -328,10 +328,10 @@ __global__ void prep_a_kernel(const float* __restrict__ A, long long lda, float*
       if (k + 2 < K) x.z = src[2];
       if (k + 3 < K) x.w = src[3];
     }
-    float4 h = make_float4(tf32_rna(x.x), tf32_rna(x.y), tf32_rna(x.z), tf32_rna(x.w));
+    float4 h = make_float4(tf32_round(x.x), tf32_round(x.y), tf32_round(x.z), tf32_round(x.w));
     *reinterpret_cast<float4*>(hi + row * Kp + k) = h;
     if (MODE == 3) {
-      float4 l = make_float4(tf32_rna(x.x - h.x), tf32_rna(x.y - h.y), tf32_rna(x.z - h.z), tf32_rna(x.w - h.w));
+      float4 l = make_float4(tf32_round(x.x - h.x), tf32_round(x.y - h.y), tf32_round(x.z - h.z), tf32_round(x.w - h.w));
       *reinterpret_cast<float4*>(lo + row * Kp + k) = l;
     }
   }
@@ -363,9 +363,9 @@ __global__ void prep_b_kernel(const float* __restrict__ B, long long ldb, float*
       const int n = n0 + threadIdx.y + j, k = k0 + threadIdx.x;
       if (n < N) {
         const float x = tile[threadIdx.x][threadIdx.y + j];
-        const float h = tf32_rna(x);
+        const float h = tf32_round(x);
         hi[static_cast<long long>(n) * Kp + k] = h;
-        if (MODE == 3) lo[static_cast<long long>(n) * Kp + k] = tf32_rna(x - h);
+        if (MODE == 3) lo[static_cast<long long>(n) * Kp + k] = tf32_round(x - h);
       }
     }
     __syncthreads();

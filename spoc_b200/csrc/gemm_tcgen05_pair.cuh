@@ -46,7 +46,11 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
   tn = within / band_m;
 }
 
-template <int MODE>
+// DIRECT (TF32 mode only): no operand panels.  map_a_hi is a TFLOAT32 tensor map over the caller's
+// row-major A (TMA rounds to TF32 on the way in) and map_b_hi one over the caller's row-major B, loaded
+// as four [32 k][32 n] slabs per stage (swizzle 128B with 32-byte atoms) and consumed through an
+// MN-major descriptor.
+template <int MODE, bool DIRECT = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_b_hi,
                  const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
@@ -125,7 +129,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
           uint8_t* sp = stage_base + stage * Cfg::kStageBytes;
           tma_load_2d_pair(smem_u32(sp), &map_a_hi, bar, kb * GEMM_BK, m0);
-          tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES), &map_b_hi, bar, kb * GEMM_BK, n0);
+          if (DIRECT) {
+            // B is K x N row-major: x = column, y = k; four slabs of 32 columns cover this block's 128
+#pragma unroll
+            for (int sl = 0; sl < 4; ++sl)
+              tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES + sl * 4096), &map_b_hi, bar, n0 + 32 * sl, kb * GEMM_BK);
+          } else {
+            tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES), &map_b_hi, bar, kb * GEMM_BK, n0);
+          }
           if (MODE == 3) {
             tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES + PAIR_B_BYTES), &map_a_lo, bar, kb * GEMM_BK, m0);
             tma_load_2d_pair(smem_u32(sp + 2 * PAIR_A_BYTES + PAIR_B_BYTES), &map_b_lo, bar, kb * GEMM_BK, n0);
@@ -146,7 +157,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------- MMA issuer (leader block)
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = umma_idesc_tf32(PAIR_BM, PAIR_BN);
+      constexpr uint32_t idesc = umma_idesc_tf32(PAIR_BM, PAIR_BN, DIRECT);
       int stage = 0;
       uint32_t phase = 0;
       int local_tile = 0;
@@ -176,7 +187,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
             const uint32_t koff = k * GEMM_UMMA_K * 4;
             const uint64_t da_hi = umma_desc_k_sw128(sa_hi + koff);
-            const uint64_t db_hi = umma_desc_k_sw128(sb_hi + koff);
+            // MN-major B: k-step k is the k-th 8-row group (1024 bytes) of every slab
+            const uint64_t db_hi = DIRECT ? umma_desc_mn_sw128_32b(sb_hi + k * 1024, 4096) : umma_desc_k_sw128(sb_hi + koff);
             const uint32_t accumulate = (kb | k) ? 1u : 0u;
             if (MODE == 3) {
               const uint64_t da_lo = umma_desc_k_sw128(sa_lo + koff);

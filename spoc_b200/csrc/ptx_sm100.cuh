@@ -213,15 +213,34 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
 
 // Instruction descriptor for kind::tf32, fp32 accumulate, both operands
 // K-major, no negation, dense: c_format=1 at bit 4, a_format=2 at bit 7,
-// b_format=2 at bit 10, N>>3 at bit 17, M>>4 at bit 24.
-__host__ __device__ constexpr uint32_t umma_idesc_tf32(uint32_t m, uint32_t n) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+// b_format=2 at bit 10, B MN-major flag at bit 16, N>>3 at bit 17, M>>4 at bit 24.
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(uint32_t m, uint32_t n, bool b_mn_major = false) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-__device__ __forceinline__ float tf32_rna(float x) {
+// Round to TF32 (10 explicit mantissa bits), nearest-even: the same rounding a
+// tensor map of type TFLOAT32 applies when TMA loads float32 data, so operands
+// rounded here and operands rounded by TMA are bit-identical.
+__device__ __forceinline__ float tf32_round(float x) {
   uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
   return __uint_as_float(r);
+}
+
+// Shared-memory matrix descriptor for an MN-major TF32 operand (rows of the tile run along N, as in a
+// row-major K x N matrix).  32-bit MN-major operands have one legal swizzled layout: 128-byte rows whose
+// 32-byte pieces are permuted by (row mod 4), layout type 1, which is what a tensor map with swizzle mode
+// 128B_ATOM_32B writes.  The tile is held as slabs of [k rows][32 floats]: four k-rows (512 bytes) form
+// one swizzle atom, an MMA k-step of 8 spans two atoms 512 bytes apart (the stride byte offset), and
+// consecutive 32-column slabs are `slab_bytes` apart (the leading byte offset).
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128_32b(uint32_t smem_addr, uint32_t slab_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((slab_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>(512 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(1) << 61;
+  return d;
 }
 
 }  // namespace sb200

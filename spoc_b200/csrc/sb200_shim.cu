@@ -248,7 +248,19 @@ int ensure_workspace(DeviceState& d, size_t bytes) {
   return SB200_OK;
 }
 
+int encode_map_2d(CUtensorMap* map, const float* base, long long inner, long long rows, long long row_stride_elems, int box_inner,
+                  int box_rows, bool round_tf32, bool atom32 = false);
+
 int encode_panel_map(CUtensorMap* map, const float* base, long long kp, long long rows, int box_rows) {
+  return encode_map_2d(map, base, kp, rows, kp, GEMM_BK, box_rows, false);
+}
+
+// 2-D float32 tensor map with the 128-byte swizzle.  round_tf32 selects the TFLOAT32 element type:
+// TMA then rounds each value to TF32 (nearest-even) while loading.
+// atom32 selects the 128-byte swizzle with 32-byte atoms, the layout an MN-major TF32 operand needs.
+int encode_map_2d(CUtensorMap* map, const float* base, long long inner, long long rows, long long row_stride_elems, int box_inner,
+                  int box_rows, bool round_tf32, bool atom32) {
+  const long long kp = inner;
   std::call_once(g_encode_once, [] {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -259,11 +271,12 @@ int encode_panel_map(CUtensorMap* map, const float* base, long long kp, long lon
   });
   if (!g_encode_tiled) return fail(SB200_ERR_NO_DEVICE, "driver does not export cuTensorMapEncodeTiled");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(kp), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(kp) * 4};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(GEMM_BK), static_cast<cuuint32_t>(box_rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride_elems) * 4};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box,
-                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  CUresult r = g_encode_tiled(map, round_tf32 ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(SB200_ERR_INVALID_VALUE, "cuTensorMapEncodeTiled failed with CUresult %d (kp=%lld rows=%lld)", (int)r, kp,
@@ -290,10 +303,27 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   CU_TRY(cudaFuncSetAttribute(gemm_tf32_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               static_cast<int>(Cfg::kSmemBytes)));
 
+  int variant = g_gemm_variant.load();
+  if (variant < 0) {
+    const char* e = getenv("SAREK_B200_GEMM");
+    variant = (e && !strcmp(e, "single")) ? 1 : (e && !strcmp(e, "pair")) ? 2 : (e && !strcmp(e, "pair-panels")) ? 3 : 0;
+    g_gemm_variant.store(variant);
+  }
+  // CTA pairs work on 256-row tiles; a problem with at most 128 rows would leave the second block idle
+  const bool pair = variant >= 2 || (variant == 0 && M > GEMM_BM);
+  // TF32 mode on CTA pairs reads the caller's matrices directly when TMA can address them: 16-byte
+  // aligned bases and row strides.  TMA rounds A and B to TF32 while loading, B is consumed N-major,
+  // so neither preparation kernels nor panel scratch are needed.
+  const bool direct = MODE == 1 && pair && variant != 3 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0 &&
+                      (reinterpret_cast<uintptr_t>(B) & 15) == 0 && (ldb & 3) == 0;
+
   const long long kp = round_up(K, GEMM_BK);
   const size_t a_bytes = round_up(panel_rows_a * kp * 4, 1024), b_bytes = round_up(N * kp * 4, 1024);
-  int rc = ensure_workspace(d, gemm_workspace_need(MODE == 3 ? SB200_MODE_3XTF32 : SB200_MODE_TF32, panel_rows_a, N, K));
-  if (rc) return rc;
+  int rc = SB200_OK;
+  if (!direct) {
+    rc = ensure_workspace(d, gemm_workspace_need(MODE == 3 ? SB200_MODE_3XTF32 : SB200_MODE_TF32, panel_rows_a, N, K));
+    if (rc) return rc;
+  }
   const bool prof = g_profiling.load() != 0;
   DeviceState::ProfRec rec{nullptr, nullptr, nullptr};
   if (prof) {
@@ -302,51 +332,47 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
     CU_TRY(cudaEventCreate(&rec.e2));
     CU_TRY(cudaEventRecord(rec.e0, st));
   }
-  // workspace layout: B panels first (their size does not depend on M), then the A panels
-  uint8_t* ws = static_cast<uint8_t*>(d.workspace);
-  constexpr size_t kOps = MODE == 3 ? 2 : 1;
-  float* b_hi = reinterpret_cast<float*>(ws);
-  float* b_lo = MODE == 3 ? reinterpret_cast<float*>(ws + b_bytes) : b_hi;
-  float* a_hi = reinterpret_cast<float*>(ws + kOps * b_bytes);
-  float* a_lo = MODE == 3 ? reinterpret_cast<float*>(ws + kOps * b_bytes + a_bytes) : a_hi;
-
-  {
-    const long long quads = M * (kp >> 2);
-    long long grid = (quads + 255) / 256;
-    const long long cap = static_cast<long long>(d.sm_count) * 16;
-    if (grid > cap) grid = cap;
-    const int vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0) ? 1 : 0;
-    prep_a_kernel<MODE><<<static_cast<unsigned>(grid), 256, 0, st>>>(A, lda, a_hi, a_lo, static_cast<int>(M),
-                                                                      static_cast<int>(K), static_cast<int>(kp), vec_ok);
-    rc = launch_check("prep_a_kernel");
-    if (rc) return rc;
-  }
-  if (!b_panels_ready) {
-    const long long tiles = (kp >> 5) * ((N + 31) >> 5);
-    long long grid = tiles;
-    const long long cap = static_cast<long long>(d.sm_count) * 32;
-    if (grid > cap) grid = cap;
-    prep_b_kernel<MODE><<<static_cast<unsigned>(grid), dim3(32, 8), 0, st>>>(B, ldb, b_hi, b_lo, static_cast<int>(K),
-                                                                               static_cast<int>(N), static_cast<int>(kp));
-    rc = launch_check("prep_b_kernel");
-    if (rc) return rc;
-  }
-
-  int variant = g_gemm_variant.load();
-  if (variant < 0) {
-    const char* e = getenv("SAREK_B200_GEMM");
-    variant = (e && !strcmp(e, "single")) ? 1 : (e && !strcmp(e, "pair")) ? 2 : 0;
-    g_gemm_variant.store(variant);
-  }
-  // CTA pairs work on 256-row tiles; a problem with at most 128 rows would leave the second block idle
-  const bool pair = variant == 2 || (variant == 0 && M > GEMM_BM);
-
   CUtensorMap ma_hi, mb_hi, ma_lo, mb_lo;
-  const int b_box_rows = pair ? 128 : GEMM_BN;
-  if ((rc = encode_panel_map(&ma_hi, a_hi, kp, M, GEMM_BM))) return rc;
-  if ((rc = encode_panel_map(&mb_hi, b_hi, kp, N, b_box_rows))) return rc;
-  if ((rc = encode_panel_map(&ma_lo, a_lo, kp, M, GEMM_BM))) return rc;
-  if ((rc = encode_panel_map(&mb_lo, b_lo, kp, N, b_box_rows))) return rc;
+  if (direct) {
+    if ((rc = encode_map_2d(&ma_hi, A, K, M, lda, GEMM_BK, GEMM_BM, true))) return rc;
+    if ((rc = encode_map_2d(&mb_hi, B, N, K, ldb, 32, GEMM_BK, true, true))) return rc;
+    ma_lo = ma_hi;
+    mb_lo = mb_hi;
+  } else {
+    // workspace layout: B panels first (their size does not depend on M), then the A panels
+    uint8_t* ws = static_cast<uint8_t*>(d.workspace);
+    constexpr size_t kOps = MODE == 3 ? 2 : 1;
+    float* b_hi = reinterpret_cast<float*>(ws);
+    float* b_lo = MODE == 3 ? reinterpret_cast<float*>(ws + b_bytes) : b_hi;
+    float* a_hi = reinterpret_cast<float*>(ws + kOps * b_bytes);
+    float* a_lo = MODE == 3 ? reinterpret_cast<float*>(ws + kOps * b_bytes + a_bytes) : a_hi;
+    {
+      const long long quads = M * (kp >> 2);
+      long long grid = (quads + 255) / 256;
+      const long long cap = static_cast<long long>(d.sm_count) * 16;
+      if (grid > cap) grid = cap;
+      const int vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0) ? 1 : 0;
+      prep_a_kernel<MODE><<<static_cast<unsigned>(grid), 256, 0, st>>>(A, lda, a_hi, a_lo, static_cast<int>(M),
+                                                                        static_cast<int>(K), static_cast<int>(kp), vec_ok);
+      rc = launch_check("prep_a_kernel");
+      if (rc) return rc;
+    }
+    if (!b_panels_ready) {
+      const long long tiles = (kp >> 5) * ((N + 31) >> 5);
+      long long grid = tiles;
+      const long long cap = static_cast<long long>(d.sm_count) * 32;
+      if (grid > cap) grid = cap;
+      prep_b_kernel<MODE><<<static_cast<unsigned>(grid), dim3(32, 8), 0, st>>>(B, ldb, b_hi, b_lo, static_cast<int>(K),
+                                                                                 static_cast<int>(N), static_cast<int>(kp));
+      rc = launch_check("prep_b_kernel");
+      if (rc) return rc;
+    }
+    const int b_box_rows = pair ? 128 : GEMM_BN;
+    if ((rc = encode_panel_map(&ma_hi, a_hi, kp, M, GEMM_BM))) return rc;
+    if ((rc = encode_panel_map(&mb_hi, b_hi, kp, N, b_box_rows))) return rc;
+    if ((rc = encode_panel_map(&ma_lo, a_lo, kp, M, GEMM_BM))) return rc;
+    if ((rc = encode_panel_map(&mb_lo, b_lo, kp, N, b_box_rows))) return rc;
+  }
 
   GemmParams gp = gp_in;
   gp.num_k_blocks = static_cast<int>(kp / GEMM_BK);
@@ -380,8 +406,17 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
     }
     const long long tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n;
     const long long pairs = tiles < max_clusters ? tiles : max_clusters;
-    gemm_pair_kernel<MODE><<<static_cast<unsigned>(2 * pairs), GEMM_THREADS, PCfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo, mb_lo,
-                                                                                                    gp);
+    if (direct) {
+      if constexpr (MODE == 1) {
+        CU_TRY(cudaFuncSetAttribute(gemm_pair_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(PCfg::kSmemBytes)));
+        gemm_pair_kernel<1, true><<<static_cast<unsigned>(2 * pairs), GEMM_THREADS, PCfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo,
+                                                                                                           mb_lo, gp);
+      }
+    } else {
+      gemm_pair_kernel<MODE><<<static_cast<unsigned>(2 * pairs), GEMM_THREADS, PCfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo, mb_lo,
+                                                                                                      gp);
+    }
     rc = launch_check("gemm_pair_kernel");
   } else {
     gp.tiles_m = static_cast<int>((M + GEMM_BM - 1) / GEMM_BM);
@@ -1217,7 +1252,8 @@ int sb200_set_mode(int mode) {
 }
 
 int sb200_set_gemm_variant(int variant) {
-  if (variant < 0 || variant > 2) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM variant %d (0 auto, 1 single, 2 pair)", variant);
+  if (variant < 0 || variant > 3)
+    return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM variant %d (0 auto, 1 single, 2 pair, 3 pair with panels)", variant);
   g_gemm_variant.store(variant);
   return SB200_OK;
 }
