@@ -285,7 +285,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     main2 = prof2["main_ms"] / max(prof2["calls"], 1)
     tf32_mode = {
         "value": world * flops_step / (ms2 / s2 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms2 / s2,
-        "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel<1>", "achieved": flops_step / (main2 * 1e-3) / 1e12,
+        "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel<1, true> (operands read directly, no preparation)", "achieved": flops_step / (main2 * 1e-3) / 1e12,
                      "peak": tf32_peak, "unit": "TFLOP/s", "frac": flops_step / (main2 * 1e-3) / 1e12 / tf32_peak,
                      "kernel_ms": main2, "prep_ms": prof2["prep_ms"] / max(prof2["calls"], 1)},
     }
