@@ -271,7 +271,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     prep_ms = prof["prep_ms"] / max(prof["calls"], 1)
     achieved = flops_step / (main_ms * 1e-3) / 1e12
     roofline = {
-        "bound": "tensor", "kernel": "gemm_pair_kernel<3>", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
+        "bound": "tensor", "kernel": "gemm_pair_kernel<3, true>", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
         "frac": achieved / tf32_peak, "traffic": None,
         "peak_source": f"{peaks['source']}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 = dense TF32",
         "mma_frac": 3.0 * achieved / tf32_peak,

@@ -309,7 +309,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
 
 // A[M x K] (row stride lda) -> hi[M x Kp] (and lo[M x Kp]), Kp = K rounded up
 // to 32, columns K..Kp zero.  One thread per 4 consecutive k.
-template <int MODE>
+// LO_ONLY: store just the low parts (the high parts are then taken from the source matrix itself by a
+// TFLOAT32 tensor map, which applies the same rounding).
+template <int MODE, bool LO_ONLY = false>
 __global__ void prep_a_kernel(const float* __restrict__ A, long long lda, float* __restrict__ hi,
                               float* __restrict__ lo, int M, int K, int Kp, int vec_ok) {
   const long long quads_per_row = Kp >> 2;
@@ -329,7 +331,7 @@ __global__ void prep_a_kernel(const float* __restrict__ A, long long lda, float*
       if (k + 3 < K) x.w = src[3];
     }
     float4 h = make_float4(tf32_round(x.x), tf32_round(x.y), tf32_round(x.z), tf32_round(x.w));
-    *reinterpret_cast<float4*>(hi + row * Kp + k) = h;
+    if (!LO_ONLY) *reinterpret_cast<float4*>(hi + row * Kp + k) = h;
     if (MODE == 3) {
       float4 l = make_float4(tf32_round(x.x - h.x), tf32_round(x.y - h.y), tf32_round(x.z - h.z), tf32_round(x.w - h.w));
       *reinterpret_cast<float4*>(lo + row * Kp + k) = l;

@@ -46,10 +46,11 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
   tn = within / band_m;
 }
 
-// DIRECT (TF32 mode only): no operand panels.  map_a_hi is a TFLOAT32 tensor map over the caller's
-// row-major A (TMA rounds to TF32 on the way in) and map_b_hi one over the caller's row-major B, loaded
-// as four [32 k][32 n] slabs per stage (swizzle 128B with 32-byte atoms) and consumed through an
-// MN-major descriptor.
+// DIRECT: map_a_hi is a TFLOAT32 tensor map over the caller's row-major A (TMA rounds to TF32 on the
+// way in) and map_b_hi one over the caller's row-major B, loaded as four [32 k][32 n] slabs per stage
+// (swizzle 128B with 32-byte atoms) and consumed through an MN-major descriptor.  TF32 mode then needs
+// no panels at all; 3xTF32 mode needs only the low parts: map_a_lo over an [M x Kp] panel, map_b_lo
+// over a row-major [K x Np] panel read as slabs like B itself.
 template <int MODE, bool DIRECT = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_b_hi,
@@ -139,7 +140,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           }
           if (MODE == 3) {
             tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES + PAIR_B_BYTES), &map_a_lo, bar, kb * GEMM_BK, m0);
-            tma_load_2d_pair(smem_u32(sp + 2 * PAIR_A_BYTES + PAIR_B_BYTES), &map_b_lo, bar, kb * GEMM_BK, n0);
+            if (DIRECT) {
+#pragma unroll
+              for (int sl = 0; sl < 4; ++sl)
+                tma_load_2d_pair(smem_u32(sp + 2 * PAIR_A_BYTES + PAIR_B_BYTES + sl * 4096), &map_b_lo, bar, n0 + 32 * sl,
+                                 kb * GEMM_BK);
+            } else {
+              tma_load_2d_pair(smem_u32(sp + 2 * PAIR_A_BYTES + PAIR_B_BYTES), &map_b_lo, bar, kb * GEMM_BK, n0);
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -192,7 +200,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             const uint32_t accumulate = (kb | k) ? 1u : 0u;
             if (MODE == 3) {
               const uint64_t da_lo = umma_desc_k_sw128(sa_lo + koff);
-              const uint64_t db_lo = umma_desc_k_sw128(sb_lo + koff);
+              const uint64_t db_lo = DIRECT ? umma_desc_mn_sw128_32b(sb_lo + k * 1024, 4096) : umma_desc_k_sw128(sb_lo + koff);
               umma_tf32_pair(tmem_d, da_lo, db_hi, idesc, accumulate);
               umma_tf32_pair(tmem_d, da_hi, db_lo, idesc, 1u);
               umma_tf32_pair(tmem_d, da_hi, db_hi, idesc, 1u);

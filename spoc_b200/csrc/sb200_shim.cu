@@ -311,17 +311,22 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   }
   // CTA pairs work on 256-row tiles; a problem with at most 128 rows would leave the second block idle
   const bool pair = variant >= 2 || (variant == 0 && M > GEMM_BM);
-  // TF32 mode on CTA pairs reads the caller's matrices directly when TMA can address them: 16-byte
-  // aligned bases and row strides.  TMA rounds A and B to TF32 while loading, B is consumed N-major,
-  // so neither preparation kernels nor panel scratch are needed.
-  const bool direct = MODE == 1 && pair && variant != 3 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0 &&
+  // CTA pairs read the caller's matrices directly when TMA can address them: 16-byte aligned bases and
+  // row strides.  TMA rounds A and B to TF32 while loading and B is consumed N-major, so TF32 mode needs
+  // neither preparation kernels nor panel scratch, and 3xTF32 mode prepares only the low parts.
+  const bool direct = pair && variant != 3 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0 &&
                       (reinterpret_cast<uintptr_t>(B) & 15) == 0 && (ldb & 3) == 0;
 
   const long long kp = round_up(K, GEMM_BK);
   const size_t a_bytes = round_up(panel_rows_a * kp * 4, 1024), b_bytes = round_up(N * kp * 4, 1024);
   int rc = SB200_OK;
+  const long long np = round_up(N, 32);  // row length of the low-part panel of B in the direct layout
+  const size_t blo_bytes = round_up(K * np * 4, 1024);
   if (!direct) {
     rc = ensure_workspace(d, gemm_workspace_need(MODE == 3 ? SB200_MODE_3XTF32 : SB200_MODE_TF32, panel_rows_a, N, K));
+    if (rc) return rc;
+  } else if (MODE == 3) {
+    rc = ensure_workspace(d, blo_bytes + a_bytes);
     if (rc) return rc;
   }
   const bool prof = g_profiling.load() != 0;
@@ -338,6 +343,29 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
     if ((rc = encode_map_2d(&mb_hi, B, N, K, ldb, 32, GEMM_BK, true, true))) return rc;
     ma_lo = ma_hi;
     mb_lo = mb_hi;
+    if constexpr (MODE == 3) {
+      // low parts only: B's first (K x np, row-major like B), then A's (rows x kp)
+      uint8_t* ws = static_cast<uint8_t*>(d.workspace);
+      float* b_lo = reinterpret_cast<float*>(ws);
+      float* a_lo = reinterpret_cast<float*>(ws + blo_bytes);
+      const long long cap = static_cast<long long>(d.sm_count) * 16;
+      {
+        long long grid = (M * (kp >> 2) + 255) / 256;
+        if (grid > cap) grid = cap;
+        prep_a_kernel<3, true><<<static_cast<unsigned>(grid), 256, 0, st>>>(A, lda, nullptr, a_lo, static_cast<int>(M),
+                                                                             static_cast<int>(K), static_cast<int>(kp), 1);
+        if ((rc = launch_check("prep_a_kernel(lo)"))) return rc;
+      }
+      if (!b_panels_ready) {
+        long long grid = (K * (np >> 2) + 255) / 256;
+        if (grid > cap) grid = cap;
+        prep_a_kernel<3, true><<<static_cast<unsigned>(grid), 256, 0, st>>>(B, ldb, nullptr, b_lo, static_cast<int>(K),
+                                                                             static_cast<int>(N), static_cast<int>(np), 1);
+        if ((rc = launch_check("prep_b_kernel(lo)"))) return rc;
+      }
+      if ((rc = encode_map_2d(&ma_lo, a_lo, kp, M, kp, GEMM_BK, GEMM_BM, false))) return rc;
+      if ((rc = encode_map_2d(&mb_lo, b_lo, N, K, np, 32, GEMM_BK, false, true))) return rc;
+    }
   } else {
     // workspace layout: B panels first (their size does not depend on M), then the A panels
     uint8_t* ws = static_cast<uint8_t*>(d.workspace);
@@ -407,12 +435,10 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
     const long long tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n;
     const long long pairs = tiles < max_clusters ? tiles : max_clusters;
     if (direct) {
-      if constexpr (MODE == 1) {
-        CU_TRY(cudaFuncSetAttribute(gemm_pair_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(PCfg::kSmemBytes)));
-        gemm_pair_kernel<1, true><<<static_cast<unsigned>(2 * pairs), GEMM_THREADS, PCfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo,
-                                                                                                           mb_lo, gp);
-      }
+      CU_TRY(cudaFuncSetAttribute(gemm_pair_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(PCfg::kSmemBytes)));
+      gemm_pair_kernel<MODE, true><<<static_cast<unsigned>(2 * pairs), GEMM_THREADS, PCfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo,
+                                                                                                            mb_lo, gp);
     } else {
       gemm_pair_kernel<MODE><<<static_cast<unsigned>(2 * pairs), GEMM_THREADS, PCfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo, mb_lo,
                                                                                                       gp);
