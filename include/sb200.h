@@ -257,6 +257,13 @@ SB200_API int sb200_fill_f32(int dev, uint64_t stream, uint64_t dptr, int64_t n,
 SB200_API int sb200_enable_profiling(int on);
 SB200_API int sb200_profile_gemm_read(int dev, uint64_t *calls, double *prep_ms, double *main_ms);
 
+/* Failure-detection self-test, fault-free: launches one block whose only thread waits, for at most
+ * limit_ms (1..1000), on a barrier that nothing signals, then gives up the way the GEMM pipeline's roles
+ * do.  The next sb200_device_synchronize / sb200_stream_synchronize / sb200_memcpy_dtoh on that device
+ * returns SB200_ERR_TIMEOUT once, and the device stays usable.  No counterpart in the reference, whose
+ * calls are synchronous and carry no device-side waits. */
+SB200_API int sb200_selftest_wait_timeout(int dev, uint32_t limit_ms);
+
 /* number of kernels this library has launched on this thread's behalf since
  * load (monotonic; used by benchmarks to report launch counts) */
 SB200_API int sb200_launch_count(uint64_t *count);

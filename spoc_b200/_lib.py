@@ -95,6 +95,7 @@ SIGNATURES = {
     "sb200_fill_f32": ([i32, u64, u64, i64, u64, u64, i32, f64, i64], i32),
     "sb200_enable_profiling": ([i32], i32),
     "sb200_profile_gemm_read": ([i32, p(u64), p(f64), p(f64)], i32),
+    "sb200_selftest_wait_timeout": ([i32, C.c_uint32], i32),
     "sb200_launch_count": ([p(u64)], i32),
 }
 

@@ -62,6 +62,7 @@ struct GemmParams {
   float alpha, beta;
   int act;      // 0 none, 1 relu
   int* status;  // device word, set non-zero when a bounded wait expired
+  int group_m;  // CTA-pair kernel: row tiles per rasterisation band
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -371,6 +372,20 @@ __global__ void prep_b_kernel(const float* __restrict__ B, long long ldb, float*
       }
     }
     __syncthreads();
+  }
+}
+
+// Exercises the bounded-wait path without any fault: one thread waits on an mbarrier that nothing ever
+// arrives on, for at most limit_ns, then records the give-up in the status word exactly as the GEMM
+// roles do, and the block returns normally.
+__global__ void wait_timeout_probe_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    mbar_fence_init();
+    if (!mbar_wait_bounded(smem_u32(&bar), 0, &abort_flag, limit_ns)) atomicCAS(status, 0, 0x900);
   }
 }
 

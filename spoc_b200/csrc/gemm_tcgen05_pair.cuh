@@ -36,12 +36,12 @@ struct PairCfg {
   static constexpr uint32_t kSmemBytes = kStages * kStageBytes + GEMM_EPI_BUF_BYTES + GEMM_CTRL_BYTES + 1024;
 };
 
-__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-  const int band_tiles = PAIR_GROUP_M * tiles_n;
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  const int band_tiles = group_m * tiles_n;
   const int band = tile / band_tiles;
   const int within = tile - band * band_tiles;
-  const int first_m = band * PAIR_GROUP_M;
-  const int band_m = min(PAIR_GROUP_M, tiles_m - first_m);
+  const int first_m = band * group_m;
+  const int band_m = min(group_m, tiles_m - first_m);
   tm = first_m + within % band_m;
   tn = within / band_m;
 }
@@ -116,7 +116,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
         int tm, tn;
-        pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        pair_tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const int m0 = tm * PAIR_BM + static_cast<int>(rank) * 128;  // this block's rows of A
         const int n0 = tn * PAIR_BN + static_cast<int>(rank) * 128;  // this block's half of B's N-rows
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
@@ -233,7 +233,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       const int acc = local_tile & 1;
       const uint32_t acc_phase = (local_tile >> 1) & 1;
       int tm, tn;
-      pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      pair_tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int row0 = tm * PAIR_BM + static_cast<int>(rank) * 128 + quarter * 32;
       const int n0 = tn * PAIR_BN;
       const bool landed = mbar_wait_bounded(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag);

@@ -412,6 +412,7 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
                                 static_cast<int>(PCfg::kSmemBytes)));
     gp.tiles_m = static_cast<int>((M + PAIR_BM - 1) / PAIR_BM);
     gp.tiles_n = static_cast<int>((N + PAIR_BN - 1) / PAIR_BN);
+    gp.group_m = PAIR_GROUP_M;  // 8 measured best at 8192^3 against 2, 4, 16, 32 (both modes)
     // how many 2-block clusters can be resident at once with this much shared memory
     int max_clusters = 0;
     {
@@ -1337,6 +1338,15 @@ int sb200_profile_gemm_read(int dev, uint64_t* calls, double* prep_ms, double* m
     *main_ms += b;
   }
   return SB200_OK;
+}
+
+int sb200_selftest_wait_timeout(int dev, uint32_t limit_ms) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (limit_ms == 0 || limit_ms > 1000) return fail(SB200_ERR_INVALID_VALUE, "limit must be 1..1000 ms");
+  wait_timeout_probe_kernel<<<1, 32>>>(d->status, static_cast<unsigned long long>(limit_ms) * 1000000ull);
+  return launch_check("wait_timeout_probe_kernel");
 }
 
 int sb200_launch_count(uint64_t* count) {

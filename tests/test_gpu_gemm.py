@@ -417,3 +417,25 @@ def test_config_32768_cubed_epilogue_sampled(backend, device):
     finally:
         for x in (A, B, Cm, D, Bi):
             backend.Memory.free(x)
+
+
+def test_bounded_wait_gives_up_cleanly_and_the_device_stays_usable(backend, device):
+    """Every device-side wait in the GEMM pipeline is bounded; when one runs out the kernel records it and returns.
+    Exercised without any fault: a wait on a barrier nothing signals, limited to 20 ms."""
+    import time
+    lib = L.load()
+    t0 = time.perf_counter()
+    assert lib.sb200_selftest_wait_timeout(device.id, 20) == 0
+    rc = lib.sb200_device_synchronize(device.id)
+    assert rc == L.ERR_TIMEOUT and b"bounded device-side wait" in lib.sb200_last_error_string()
+    assert time.perf_counter() - t0 < 5.0
+    assert lib.sb200_device_synchronize(device.id) == 0          # reported once, then cleared
+    M, N, K = 256, 256, 64                                       # and the context is intact
+    a, b = O.fill(M * K, 77, 1), O.fill(K * N, 77, 2)
+    A, B, D = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * N)
+    try:
+        gemm(backend, device, L.MODE_3XTF32, M, N, K, A, B, D)
+        assert O.gemm_rel_error(D.download().reshape(M, N), O.gemm(a, b, M, N, K)) <= tol(L.MODE_3XTF32, K)
+    finally:
+        for x in (A, B, D):
+            x.free()
