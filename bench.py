@@ -273,9 +273,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     roofline = {
         "bound": "tensor", "kernel": "gemm_pair_kernel<3, true>", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
         "frac": achieved / tf32_peak,
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, from the ncu capture
-        # summarised in profiles/gemm_pair_kernel_3xtf32_direct_8192cubed_ncu.md (not measured in this run)
-        "traffic": 8.144e9 + 0.262e9, "traffic_unit": "bytes per launch (ncu capture, see profiles/)",
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, taken from an
+        # ncu capture of this same kernel and size (a profiler figure, not measured in this run)
+        "traffic": 8.144e9 + 0.262e9, "traffic_unit": "bytes per launch (ncu capture of this kernel at this size)",
         "peak_source": f"{peaks['source']}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 = dense TF32",
         "mma_frac": 3.0 * achieved / tf32_peak,
         "kernel_ms": main_ms, "prep_ms": prep_ms,
@@ -333,9 +333,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
                      "unit": "GB/s", "ms_per_step": ms4 / s4, "launches_per_step": l4 / s4,
                      "roofline": {"bound": "hbm", "kernel": "map2_vec_kernel<ChainOp>", "achieved": gbs,
                                   "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
-                                  # ncu capture at 2^26 elements scaled x4 (traffic is proportional to N: no reuse),
-                                  # profiles/map2_vec_kernel_chain_2p26_ncu.md
-                                  "traffic": 4 * (536.9e6 + 268.4e6), "traffic_unit": "bytes per launch (ncu capture scaled, see profiles/)",
+                                  # ncu capture at 2^26 elements scaled x4 (traffic is proportional to N: no reuse)
+                                  "traffic": 4 * (536.9e6 + 268.4e6),
+                                  "traffic_unit": "bytes per launch (ncu capture at 2^26 elements, scaled x4)",
                                   "peak_source": f"{peaks['source']} copy bandwidth",
                                   "frac_of_nominal_8TBs": gbs / 8000.0}}
 
