@@ -51,13 +51,17 @@ def load_peaks() -> dict:
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi samples (every 20 ms) taken while the GPU is under the benchmark's load.  The sampler is
+    started early because nvidia-smi needs a moment to come up; begin()/end() bracket the loaded window
+    (untimed pre-load + warm-up + timed steps) and only samples inside it are used."""
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
         self.proc = None
         self.gpu_index = gpu_index
+        self.t_begin = self.t_end = None
 
     def start(self):
         try:
@@ -67,38 +71,47 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def begin(self):
+        self.t_begin = time.time()
+
+    def end(self):
+        self.t_end = time.time()
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, power, reasons = [], [], [], set()
+        import datetime
+        sm, mx, power, reasons, total = [], [], [], set(), 0
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.splitlines():
             f = [x.strip() for x in line.split(",")]
-            if len(f) < 8:
+            if len(f) < 9:
                 continue
+            total += 1
             try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-                power.append(float(f[3]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                c, m, pw = float(f[2]), float(f[3]), float(f[4])
             except ValueError:
                 continue
-            for name, v in zip(names, f[4:8]):
+            if self.t_begin is not None and not (self.t_begin + 0.05 <= ts <= (self.t_end or ts)):
+                continue
+            sm.append(c)
+            mx.append(m)
+            power.append(pw)
+            for name, v in zip(names, f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        # "under load" = samples in the upper half of the observed power range
-        thr = (max(power) + min(power)) / 2 if power else 0
-        loaded = [c for c, p in zip(sm, power) if p >= thr] or sm
-        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm), "power_w_max": max(power) if power else None}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [f"no samples inside the loaded window ({total} outside)"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                "power_w_max": max(power), "window_s": round((self.t_end or 0) - (self.t_begin or 0), 3)}
 
 
 # --------------------------------------------------------------------------- reference arm
@@ -183,6 +196,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     tdev = torch.device("cuda", local_rank)
     stream = torch.cuda.current_stream().cuda_stream
     peaks = load_peaks()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()   # nvidia-smi takes a moment to come up; samples are windowed later
 
     def fill(t, sid, kind, first=0):
         _check(lib.sb200_fill_f32(dev.id, stream, t.data_ptr(), t.numel(), SEED, sid, kind, 1.0, first))
@@ -254,14 +270,18 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 
     flops_step = 2.0 * M * N * K
     # ---- headline: 3xTF32 ------------------------------------------------------------
-    sampler = ClockSampler(local_rank)
-    for _ in range(args.warmup):
-        gemm(L.MODE_3XTF32)
-    torch.cuda.synchronize()
+    # Untimed pre-load: the same step for about half a second, so that the timed steps run at the clock the
+    # power cap settles on rather than at the burst clock of a cold GPU, and the clock sampler has samples.
     if rank == 0:
-        sampler.start()
-        time.sleep(0.05)
+        sampler.begin()
+    t_pre = time.time()
+    while time.time() - t_pre < 0.5:
+        for _ in range(5):
+            gemm(L.MODE_3XTF32)
+        torch.cuda.synchronize()
     ms, launches, prof = timed(lambda: gemm(L.MODE_3XTF32), args.steps, args.warmup, profile=True)
+    if rank == 0:
+        sampler.end()
     clocks = sampler.stop() if rank == 0 else None
     _check(lib.sb200_device_synchronize(dev.id))  # also surfaces a device-side timeout flag
     ms_step = ms / args.steps
@@ -354,7 +374,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32x3 (f32 in/out)",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "rows_per_gpu": M, "l2": "inputs larger than L2 (4 x 256 MiB per GPU)",
+            "config": {"workload": WORKLOAD, "rows_per_gpu": M, "l2": "inputs larger than L2 (4 x 256 MiB per GPU)", "preload_s": 0.5,
                        "sharding": "row blocks of A/C/D per rank, B replicated by NCCL broadcast before the timed region"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "tf32_mode": tf32_mode, "fused_map": fused_map, "b_broadcast_ms": bcast_ms,
@@ -411,8 +431,127 @@ def run_case(args) -> None:
     print(json.dumps({"case": args.case, "size": S, "ms_per_call": ms, "rate": work / (ms * 1e-3), "unit": unit}), flush=True)
 
 
+def run_gather(args, rank: int, local_rank: int, world: int) -> None:
+    """Strong-scaling run of the large square GEMM with epilogue and a gathered result: M = N = K = --size
+    (default 32768), rows of A/C/D split over the ranks, B replicated.  Two ways to leave the whole D on every
+    GPU are timed: the GEMM followed by an NCCL all-gather of the row blocks, and the GEMM whose epilogue stores
+    each tile into every GPU's copy (peer stores over NVLink)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from spoc_b200 import Backend, _lib as L
+    from spoc_b200.plugin import _check
+    from spoc_b200.sharding import row_block
+    lib = L.load()
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    backend = Backend()
+    backend.Device.init()
+    dev = backend.Device.get(local_rank)
+    backend.Device.set_current(dev)
+    tdev = torch.device("cuda", local_rank)
+    stream = torch.cuda.current_stream().cuda_stream
+    S = args.size
+    r0, rows = row_block(S, world, rank)
+
+    def fill(ptr, n, sid, kind, first=0):
+        _check(lib.sb200_fill_f32(dev.id, stream, ptr, n, SEED, sid, kind, 1.0, first))
+
+    A = torch.empty(rows * S, dtype=torch.float32, device=tdev)
+    Cm = torch.empty(rows * S, dtype=torch.float32, device=tdev)
+    B = torch.empty(S * S, dtype=torch.float32, device=tdev)
+    bias = torch.empty(S, dtype=torch.float32, device=tdev)
+    fill(A.data_ptr(), A.numel(), 1, 0, r0 * S)
+    fill(Cm.data_ptr(), Cm.numel(), 3, 0, r0 * S)
+    fill(bias.data_ptr(), S, 4, 1)
+    if rank == 0:
+        fill(B.data_ptr(), B.numel(), 2, 0)
+    if world > 1:
+        dist.broadcast(B, src=0)
+    D_nccl = torch.empty(S * S, dtype=torch.float32, device=tdev)     # gathered by NCCL
+    D_own = backend.Memory.alloc(dev, S * S, np.float32)              # gathered by the epilogue (IPC-shareable memory)
+    copies = [D_own.ptr]
+    opened = []
+    if world > 1:
+        handle = C.create_string_buffer(64)
+        _check(lib.sb200_ipc_export(dev.id, D_own.ptr, handle))
+        handles = [None] * world
+        dist.all_gather_object(handles, handle.raw)
+        for r in range(world):
+            if r != rank:
+                pp = C.c_uint64(0)
+                _check(lib.sb200_ipc_open(dev.id, C.create_string_buffer(handles[r], 64), C.byref(pp)))
+                copies.append(pp.value)
+                opened.append(pp.value)
+    ptrs = (C.c_uint64 * len(copies))(*copies)
+    torch.cuda.synchronize()
+
+    def step_nccl():
+        shard = D_nccl[r0 * S:(r0 + rows) * S]
+        _check(lib.sb200_gemm_f32(dev.id, stream, L.MODE_3XTF32, rows, S, S, A.data_ptr(), S, B.data_ptr(), S, shard.data_ptr(), S,
+                                  1.5, Cm.data_ptr(), S, 0.5, bias.data_ptr(), L.ACT_RELU))
+        if world > 1:
+            dist.all_gather_into_tensor(D_nccl, shard)
+
+    def step_fused():
+        _check(lib.sb200_gemm_f32_gather(dev.id, stream, L.MODE_3XTF32, rows, S, S, A.data_ptr(), S, B.data_ptr(), S, ptrs,
+                                         len(copies), r0, S, 1.5, Cm.data_ptr(), S, 0.5, bias.data_ptr(), L.ACT_RELU))
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 1)):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = e0.elapsed_time(e1) / args.steps
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=tdev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    ms_nccl = timed(step_nccl)
+    ms_fused = timed(step_fused)
+    # the two gathered results must agree bit for bit on this rank
+    own = torch.empty(S * S, dtype=torch.float32, device=tdev)
+    _check(lib.sb200_memcpy_dtod(dev.id, own.data_ptr(), D_own.ptr, 4 * S * S))
+    same = bool(torch.equal(own, D_nccl))
+    if world > 1:
+        flag = torch.tensor([1 if same else 0], device=tdev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        same = bool(flag.item())
+        dist.barrier()
+    for pp in opened:
+        _check(lib.sb200_ipc_close(dev.id, pp))
+    flops = 2.0 * S ** 3
+    if rank == 0:
+        print(json.dumps({
+            "metric": f"fp32_gemm_fused_epilogue_{S}cubed_gathered", "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "scaling": "strong", "higher_is_better": True, "data": "synthetic", "dtype": "tf32x3 (f32 in/out)",
+            "config": {"workload": f"gemm M=N=K={S} with epilogue, rows of A/C/D split over the ranks, whole D on every GPU"},
+            "value": flops / (ms_fused * 1e-3) / 1e12, "ms_per_step": ms_fused,
+            "gemm_then_nccl_all_gather": {"value": flops / (ms_nccl * 1e-3) / 1e12, "ms_per_step": ms_nccl},
+            "gather_fused_in_epilogue": {"value": flops / (ms_fused * 1e-3) / 1e12, "ms_per_step": ms_fused},
+            "results_identical": same}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="gemm8192", choices=["gemm8192", "gather"],
+                    help="gemm8192: the headline run; gather: large square GEMM with the result gathered on every GPU")
     ap.add_argument("--case", default=None, choices=["gemm3", "gemm1", "map"],
                     help="profiler-sized single-operator run (square size --size; map uses size^2 elements)")
     ap.add_argument("--size", type=int, default=4096)
@@ -428,6 +567,10 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.case:
         run_case(args)
+    elif args.workload == "gather":
+        if args.size == 4096:
+            args.size = 32768
+        run_gather(args, rank, local_rank, world)
     elif args.impl == "reference":
         run_reference(args, rank, world)
     else:

@@ -206,6 +206,26 @@ SB200_API int sb200_gemm_f32_noalloc(int dev, uint64_t stream, int mode,
                                      uint64_t D, int64_t ldd,
                                      float alpha, uint64_t C, int64_t ldc, float beta,
                                      uint64_t bias, int act);
+/* Row-sharded product with the gather fused into the store.  Each GPU computes the M_local rows of D that start
+ * at global row `row_offset` and writes every element to the same position of `n_copies` (1..8) full-size copies
+ * of D, whose base addresses are d_copies[]: entry 0 this GPU's own copy, the others the peers' copies mapped
+ * into this process (sb200_ipc_open) — plain stores over NVLink from the epilogue, so the all-gather of the
+ * row blocks overlaps the tensor-core work instead of following it.  When every GPU has returned from its
+ * stream synchronise and the ranks have met at a host barrier, each copy holds the whole D.  The reference has
+ * no multi-GPU path (sarek/core/Vector.ml:284-296 leaves gather a stub); this is the gathered-result form of
+ * the row-block sharding described for it.  A, C (M_local rows) and B, bias (whole) are local. */
+SB200_API int sb200_gemm_f32_gather(int dev, uint64_t stream, int mode, int64_t M_local, int64_t N, int64_t K,
+                                    uint64_t A, int64_t lda, uint64_t B, int64_t ldb,
+                                    const uint64_t *d_copies, int n_copies, int64_t row_offset, int64_t ldd,
+                                    float alpha, uint64_t C, int64_t ldc, float beta, uint64_t bias, int act);
+/* Sharing a buffer obtained from sb200_mem_alloc with the other processes of the node (one process per GPU):
+ * export writes a 64-byte handle to pass to the peers by any host channel; open maps the peer's buffer into
+ * this process (peer access over NVLink is enabled on first use) and returns a device pointer usable in
+ * d_copies[]; close unmaps it.  Thin wrappers of cudaIpcGetMemHandle / OpenMemHandle / CloseMemHandle. */
+SB200_API int sb200_ipc_export(int dev, uint64_t dptr, void *handle64);
+SB200_API int sb200_ipc_open(int dev, const void *handle64, uint64_t *dptr);
+SB200_API int sb200_ipc_close(int dev, uint64_t dptr);
+
 /* The same operator on HOST operands (pinned memory for full overlap; pageable
  * memory works but serialises the copies).  Replaces the reference's sequence
  * Transfer.to_device of every argument, launch, Transfer.to_cpu of the result

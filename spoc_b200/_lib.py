@@ -83,6 +83,10 @@ SIGNATURES = {
     "sb200_ir_fuse_as": ([C.c_char_p, C.c_char_p, C.c_char_p, i32, C.c_char_p, i32, p(i32)], i32),
     "sb200_gemm_f32": ([i32, u64, i32, i64, i64, i64, u64, i64, u64, i64, u64, i64, f32, u64, i64, f32, u64, i32], i32),
     "sb200_gemm_f32_noalloc": ([i32, u64, i32, i64, i64, i64, u64, i64, u64, i64, u64, i64, f32, u64, i64, f32, u64, i32], i32),
+    "sb200_gemm_f32_gather": ([i32, u64, i32, i64, i64, i64, u64, i64, u64, i64, p(u64), i32, i64, i64, f32, u64, i64, f32, u64, i32], i32),
+    "sb200_ipc_export": ([i32, u64, C.c_void_p], i32),
+    "sb200_ipc_open": ([i32, C.c_void_p, p(u64)], i32),
+    "sb200_ipc_close": ([i32, u64], i32),
     "sb200_gemm_f32_host": ([i32, i32, i64, i64, i64, C.c_void_p, i64, C.c_void_p, i64, C.c_void_p, i64, f32, C.c_void_p, i64, f32,
                              C.c_void_p, i32], i32),
     "sb200_gemm_workspace_bytes": ([i32, i64, i64, i64, p(u64)], i32),

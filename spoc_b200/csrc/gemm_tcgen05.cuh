@@ -63,7 +63,17 @@ struct GemmParams {
   int act;      // 0 none, 1 relu
   int* status;  // device word, set non-zero when a bounded wait expired
   int group_m;  // CTA-pair kernel: row tiles per rasterisation band
+  // Gathered result: when n_replicas > 0 every output element is also stored to the same position of
+  // these further copies of D (this GPU's own or peers' memory mapped into this process), so that a
+  // row-sharded product leaves the whole matrix on every GPU without a separate all-gather.
+  int n_replicas;
+  float* replicas[7];
 };
+
+__device__ __forceinline__ void store_replicas(const GemmParams& p, long long offset, float x) {
+#pragma unroll 1
+  for (int r = 0; r < p.n_replicas; ++r) p.replicas[r][offset] = x;
+}
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int band_tiles = GEMM_GROUP_M * tiles_n;
@@ -275,6 +285,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
               x += bias_v;
               if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
               dp[rr * p.ldd] = x;
+              if (p.n_replicas) store_replicas(p, static_cast<long long>(row0 + rr) * p.ldd + col, x);
             }
           } else {
             for (int rr = 0; rr < rows_here; ++rr) {
@@ -284,6 +295,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
               x += bias_v;
               if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
               p.D[row * p.ldd + col] = x;
+              if (p.n_replicas) store_replicas(p, row * p.ldd + col, x);
             }
           }
         }
@@ -401,6 +413,7 @@ __global__ void gemm_k0_kernel(GemmParams p) {
     if (p.bias) x += p.bias[col];
     if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
     p.D[row * p.ldd + col] = x;
+    if (p.n_replicas) store_replicas(p, row * p.ldd + col, x);
   }
 }
 

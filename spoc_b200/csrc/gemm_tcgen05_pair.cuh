@@ -273,6 +273,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
               x += bias_v;
               if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
               dp[rr * p.ldd] = x;
+              if (p.n_replicas) store_replicas(p, static_cast<long long>(row0 + rr) * p.ldd + col, x);
             }
           } else {
             for (int rr = 0; rr < rows_here; ++rr) {
@@ -282,6 +283,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
               x += bias_v;
               if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
               p.D[row * p.ldd + col] = x;
+              if (p.n_replicas) store_replicas(p, row * p.ldd + col, x);
             }
           }
         }

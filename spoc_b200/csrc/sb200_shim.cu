@@ -463,7 +463,7 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
 
 int run_gemm(DeviceState& d, cudaStream_t st, int mode, long long M, long long N, long long K, uint64_t A, long long lda,
              uint64_t B, long long ldb, uint64_t D, long long ldd, float alpha, uint64_t C, long long ldc, float beta,
-             uint64_t bias, int act) {
+             uint64_t bias, int act, const uint64_t* replicas = nullptr, int n_replicas = 0) {
   if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   if (M < 0 || N < 0 || K < 0) return fail(SB200_ERR_INVALID_VALUE, "negative GEMM dimension (M=%lld N=%lld K=%lld)", M, N, K);
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL - 64)
@@ -487,6 +487,8 @@ int run_gemm(DeviceState& d, cudaStream_t st, int mode, long long M, long long N
   gp.alpha = alpha;
   gp.beta = beta;
   gp.act = act;
+  gp.n_replicas = n_replicas;
+  for (int r = 0; r < n_replicas; ++r) gp.replicas[r] = as_ptr<float>(replicas[r]);
   if (K == 0) {
     const long long total = M * N;
     long long grid = (total + 255) / 256;
@@ -1241,6 +1243,58 @@ int sb200_gemm_f32(int dev, uint64_t stream, int mode, int64_t M, int64_t N, int
   int rc = device_ready(dev, &d);
   if (rc) return rc;
   return run_gemm(*d, as_stream(stream), mode, M, N, K, A, lda, B, ldb, D, ldd, alpha, C, ldc, beta, bias, act);
+}
+
+int sb200_gemm_f32_gather(int dev, uint64_t stream, int mode, int64_t M_local, int64_t N, int64_t K, uint64_t A, int64_t lda,
+                          uint64_t B, int64_t ldb, const uint64_t* d_copies, int n_copies, int64_t row_offset, int64_t ldd,
+                          float alpha, uint64_t C, int64_t ldc, float beta, uint64_t bias, int act) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (!d_copies || n_copies < 1 || n_copies > 8) return fail(SB200_ERR_INVALID_VALUE, "between 1 and 8 copies of D are supported");
+  if (row_offset < 0 || ldd < N) return fail(SB200_ERR_INVALID_VALUE, "bad row offset or leading dimension");
+  uint64_t shifted[8];
+  for (int r = 0; r < n_copies; ++r) {
+    if (!d_copies[r] || (d_copies[r] & 3)) return fail(SB200_ERR_INVALID_VALUE, "null or misaligned copy of D (%d)", r);
+    shifted[r] = d_copies[r] + static_cast<uint64_t>(row_offset) * static_cast<uint64_t>(ldd) * 4;
+  }
+  // copy 0 is the kernel's primary output (and what C may alias); the others are the replicas
+  return run_gemm(*d, as_stream(stream), mode, M_local, N, K, A, lda, B, ldb, shifted[0], ldd, alpha, C, ldc, beta, bias, act,
+                  shifted + 1, n_copies - 1);
+}
+
+int sb200_ipc_export(int dev, uint64_t dptr, void* handle64) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (!dptr || !handle64) return fail(SB200_ERR_INVALID_VALUE, "null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+  cudaIpcMemHandle_t h;
+  CU_TRY(cudaIpcGetMemHandle(&h, as_ptr<void>(dptr)));
+  memcpy(handle64, &h, 64);
+  return SB200_OK;
+}
+
+int sb200_ipc_open(int dev, const void* handle64, uint64_t* dptr) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (!handle64 || !dptr) return fail(SB200_ERR_INVALID_VALUE, "null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  CU_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *dptr = reinterpret_cast<uintptr_t>(p);
+  return SB200_OK;
+}
+
+int sb200_ipc_close(int dev, uint64_t dptr) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (!dptr) return SB200_OK;
+  CU_TRY(cudaIpcCloseMemHandle(as_ptr<void>(dptr)));
+  return SB200_OK;
 }
 
 int sb200_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, uint64_t* bytes) {

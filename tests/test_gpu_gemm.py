@@ -439,3 +439,33 @@ def test_bounded_wait_gives_up_cleanly_and_the_device_stays_usable(backend, devi
     finally:
         for x in (A, B, D):
             x.free()
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_gather_epilogue_writes_every_copy(backend, device, mode):
+    """sb200_gemm_f32_gather on one GPU: three copies of the gathered D in local memory; the row block must land
+    at its global row offset in each of them, identical to the plain operator, and nothing else may be touched."""
+    import ctypes as C
+    lib = L.load()
+    M_total, M_local, N, K, row_offset = 700, 300, 260, 200, 256
+    a, b, c = O.fill(M_local * K, 51, 1), O.fill(K * N, 51, 2), O.fill(M_local * N, 51, 3)
+    bias = O.fill(N, 51, 4, kind=1)
+    A, B, Cm, Bi = (dev_from(backend, device, x) for x in (a, b, c, bias))
+    copies = [Dev(backend, device, M_total * N) for _ in range(3)]
+    Dref = Dev(backend, device, M_local * N)
+    try:
+        ptrs = (C.c_uint64 * 3)(*[d.ptr for d in copies])
+        rc = lib.sb200_gemm_f32_gather(device.id, 0, mode, M_local, N, K, A.ptr, K, B.ptr, N, ptrs, 3, row_offset, N, 1.5, Cm.ptr, N,
+                                       0.5, Bi.ptr, 1)
+        assert rc == 0, lib.sb200_last_error_string()
+        gemm(backend, device, mode, M_local, N, K, A, B, Dref, alpha=1.5, C_=Cm, beta=0.5, bias=Bi, act=1)
+        want = Dref.download().reshape(M_local, N)
+        for d in copies:
+            got = d.download().reshape(M_total, N)
+            assert np.array_equal(got[row_offset:row_offset + M_local], want)
+            assert np.all(got[:row_offset] == CANARY) and np.all(got[row_offset + M_local:] == CANARY)
+        assert lib.sb200_gemm_f32_gather(device.id, 0, mode, M_local, N, K, A.ptr, K, B.ptr, N, ptrs, 9, 0, N, 1.0, 0, 0, 0.0, 0,
+                                         0) == L.ERR_INVALID_VALUE
+    finally:
+        for x in [A, B, Cm, Bi, Dref] + copies:
+            x.free()
