@@ -270,12 +270,12 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 
     flops_step = 2.0 * M * N * K
     # ---- headline: 3xTF32 ------------------------------------------------------------
-    # Untimed pre-load: the same step for about half a second, so that the timed steps run at the clock the
-    # power cap settles on rather than at the burst clock of a cold GPU, and the clock sampler has samples.
+    # Optional untimed pre-load (--preload-s): the same step for that long, so that the timed steps run at the
+    # clock the power cap settles on rather than at the clock of a GPU that was idle a moment ago.
     if rank == 0:
         sampler.begin()
     t_pre = time.time()
-    while time.time() - t_pre < 0.5:
+    while time.time() - t_pre < args.preload_s:
         for _ in range(5):
             gemm(L.MODE_3XTF32)
         torch.cuda.synchronize()
@@ -374,7 +374,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32x3 (f32 in/out)",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "rows_per_gpu": M, "l2": "inputs larger than L2 (4 x 256 MiB per GPU)", "preload_s": 0.5,
+            "config": {"workload": WORKLOAD, "rows_per_gpu": M, "l2": "inputs larger than L2 (4 x 256 MiB per GPU)", "preload_s": args.preload_s,
                        "sharding": "row blocks of A/C/D per rank, B replicated by NCCL broadcast before the timed region"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "tf32_mode": tf32_mode, "fused_map": fused_map, "b_broadcast_ms": bcast_ms,
@@ -560,6 +560,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--preload-s", type=float, default=0.0,
+                    help="seconds of untimed identical steps before the warm-up (sustained-clock measurement)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
