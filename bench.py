@@ -51,9 +51,10 @@ def load_peaks() -> dict:
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """nvidia-smi samples (every 20 ms) taken while the GPU is under the benchmark's load.  The sampler is
-    started early because nvidia-smi needs a moment to come up; begin()/end() bracket the loaded window
-    (untimed pre-load + warm-up + timed steps) and only samples inside it are used."""
+    """SM clock, power and clock-event reasons sampled while the GPU is under the benchmark's load: NVML queries
+    from a thread of this process every 5 ms, or, where NVML cannot be loaded, nvidia-smi every 20 ms (started
+    early because it needs a moment to come up).  begin()/end() bracket the loaded window (optional pre-load +
+    warm-up + timed steps) and only samples inside it are used."""
     FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
@@ -63,7 +64,59 @@ class ClockSampler:
         self.gpu_index = gpu_index
         self.t_begin = self.t_end = None
 
-    def start(self):
+    def _nvml_loop(self):
+        import pynvml as nv
+        reasons_of = {nv.nvmlClocksEventReasonHwSlowdown: "hw_slowdown",
+                      nv.nvmlClocksEventReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                      nv.nvmlClocksEventReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                      nv.nvmlClocksEventReasonSwPowerCap: "sw_power_cap"}
+        while not self._stop.is_set():
+            try:
+                c = nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM)
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
+                pw = nv.nvmlDeviceGetPowerUsage(self._handle) / 1000.0
+                self._nvml_samples.append((time.time(), float(c), pw,
+                                           [name for bit, name in reasons_of.items() if mask & bit]))
+            except Exception:  # a failed read drops one sample, nothing else
+                pass
+            self._stop.wait(0.005)
+
+    def _start_nvml(self, uuid) -> bool:
+        """Reads clocks, power and event reasons through NVML in a thread of this process (read-only queries)."""
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            self._handle = (nv.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode()) if uuid
+                            else nv.nvmlDeviceGetHandleByIndex(self.gpu_index))
+            self._nvml_max = float(nv.nvmlDeviceGetMaxClockInfo(self._handle, nv.NVML_CLOCK_SM))
+            nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM)
+        except Exception:
+            return False
+        import threading
+        self._stop = threading.Event()
+        self._nvml_samples = []
+        self._thread = threading.Thread(target=self._nvml_loop, daemon=True)
+        self._thread.start()
+        return True
+
+    def _stop_nvml(self) -> dict:
+        self._stop.set()
+        self._thread.join(timeout=2)
+        inside = [x for x in self._nvml_samples
+                  if self.t_begin is None or self.t_begin + 0.01 <= x[0] <= (self.t_end or x[0])]
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None,
+                    "reasons": [f"no samples inside the loaded window ({len(self._nvml_samples)} outside)"]}
+        reasons = sorted({r for x in inside for r in x[3]})
+        return {"sm_mhz": statistics.median(x[1] for x in inside), "sm_min_mhz": min(x[1] for x in inside),
+                "sm_max_mhz": self._nvml_max, "reasons": reasons, "samples": len(inside),
+                "power_w_max": max(x[2] for x in inside), "source": "nvml, 5 ms period",
+                "window_s": round((self.t_end or 0) - (self.t_begin or 0), 3)}
+
+    def start(self, uuid=None):
+        self._thread = None
+        if self._start_nvml(uuid):
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -78,6 +131,8 @@ class ClockSampler:
         self.t_end = time.time()
 
     def stop(self) -> dict:
+        if getattr(self, "_thread", None) is not None:
+            return self._stop_nvml()
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.1)
@@ -198,7 +253,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     peaks = load_peaks()
     sampler = ClockSampler(local_rank)
     if rank == 0:
-        sampler.start()   # nvidia-smi takes a moment to come up; samples are windowed later
+        sampler.start(getattr(torch.cuda.get_device_properties(local_rank), "uuid", None))  # windowed later
 
     def fill(t, sid, kind, first=0):
         _check(lib.sb200_fill_f32(dev.id, stream, t.data_ptr(), t.numel(), SEED, sid, kind, 1.0, first))
@@ -548,10 +603,89 @@ def run_gather(args, rank: int, local_rank: int, world: int) -> None:
         dist.destroy_process_group()
 
 
+def run_skinny(args, rank: int, local_rank: int, world: int) -> None:
+    """Strong-scaling run of the skinny GEMM: C = A.B with M = 65536, N = K = 4096, rows of A drawn from N(0,1),
+    B from N(0,1/sqrt(K)); rows of A and C split over the ranks, B broadcast from rank 0 (NCCL).  Timed twice:
+    with B already on every GPU, and with the broadcast of B inside every timed step."""
+    import math
+
+    import torch
+    import torch.distributed as dist
+
+    from spoc_b200 import Backend, _lib as L
+    from spoc_b200.plugin import _check
+    from spoc_b200.sharding import row_block
+    lib = L.load()
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    backend = Backend()
+    backend.Device.init()
+    dev = backend.Device.get(local_rank)
+    backend.Device.set_current(dev)
+    tdev = torch.device("cuda", local_rank)
+    stream = torch.cuda.current_stream().cuda_stream
+    Mt, Nn, Kk = 65536, 4096, 4096
+    r0, rows = row_block(Mt, world, rank)
+    A = torch.empty(rows * Kk, dtype=torch.float32, device=tdev)
+    Cm = torch.empty(rows * Nn, dtype=torch.float32, device=tdev)
+    B = torch.empty(Kk * Nn, dtype=torch.float32, device=tdev)
+    _check(lib.sb200_fill_f32(dev.id, stream, A.data_ptr(), A.numel(), SEED, 1, 2, 1.0, r0 * Kk))
+    if rank == 0:
+        _check(lib.sb200_fill_f32(dev.id, stream, B.data_ptr(), B.numel(), SEED, 2, 2, 1.0 / math.sqrt(Kk), 0))
+    if world > 1:
+        dist.broadcast(B, src=0)
+    torch.cuda.synchronize()
+    out = {}
+    for mode, label in ((L.MODE_3XTF32, "3xtf32"), (L.MODE_TF32, "tf32")):
+        def gemm():
+            _check(lib.sb200_gemm_f32(dev.id, stream, mode, rows, Nn, Kk, A.data_ptr(), Kk, B.data_ptr(), Nn, Cm.data_ptr(), Nn,
+                                      1.0, 0, 0, 0.0, 0, L.ACT_NONE))
+
+        def gemm_after_broadcast():
+            if world > 1:
+                dist.broadcast(B, src=0)
+            gemm()
+
+        for name, fn in (("b_resident", gemm), ("b_broadcast_timed", gemm_after_broadcast)):
+            for _ in range(max(args.warmup, 3)):
+                fn()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            ms = e0.elapsed_time(e1) / args.steps
+            if world > 1:
+                t = torch.tensor([ms], dtype=torch.float64, device=tdev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            out.setdefault(label, {})[name] = {"ms_per_step": ms, "value": 2.0 * Mt * Nn * Kk / (ms * 1e-3) / 1e12}
+    if rank == 0:
+        print(json.dumps({
+            "metric": "fp32_gemm_65536x4096x4096_row_sharded", "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "scaling": "strong", "higher_is_better": True, "data": "synthetic",
+            "dtype": "tf32x3 (f32 in/out)",
+            "config": {"workload": "gemm M=65536 N=K=4096, A ~ N(0,1), B ~ N(0,1/sqrt(K)), rows of A/C split over the ranks, "
+                                   "B broadcast from rank 0 (64 MiB, NCCL)"},
+            "value": out["3xtf32"]["b_resident"]["value"], "ms_per_step": out["3xtf32"]["b_resident"]["ms_per_step"],
+            "modes": out}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="gemm8192", choices=["gemm8192", "gather"],
-                    help="gemm8192: the headline run; gather: large square GEMM with the result gathered on every GPU")
+    ap.add_argument("--workload", default="gemm8192", choices=["gemm8192", "gather", "skinny"],
+                    help="gemm8192: the headline run; gather: large square GEMM with the result gathered on every GPU; "
+                         "skinny: 65536x4096x4096 GEMM, rows split over the ranks, B broadcast")
     ap.add_argument("--case", default=None, choices=["gemm3", "gemm1", "map"],
                     help="profiler-sized single-operator run (square size --size; map uses size^2 elements)")
     ap.add_argument("--size", type=int, default=4096)
@@ -573,6 +707,8 @@ def main() -> None:
         if args.size == 4096:
             args.size = 32768
         run_gather(args, rank, local_rank, world)
+    elif args.workload == "skinny":
+        run_skinny(args, rank, local_rank, world)
     elif args.impl == "reference":
         run_reference(args, rank, world)
     else:

@@ -166,12 +166,20 @@ SB200_API int sb200_ir_analyze(const char *kernel, char *out, int outlen);
  *   SB200_FUSE_STENCIL    can_fuse_stencil / fuse_stencil           (:795-1018)
  *   SB200_FUSE_TRY        try_fuse: reduction, else plain           (:759-766)
  *   SB200_FUSE_TRY_ALL    try_fuse_all: reduction, stencil, plain   (:1022-1030)
- * For the TRY kinds *fused is 0 when the reference would return None (out is then empty). */
+ *   SB200_FUSE_GUARDED    no counterpart in the reference: fuses kernels of the form its own benchmarks use,
+ *                         `let tid = global_thread_id in if tid < n then out.(tid) <- e`, which the reference's
+ *                         pass leaves unfused (find_write_expr stops at a conditional, :370-375; the two kernels'
+ *                         `tid` have different ids, :38).  Index lets are inlined and the guards peeled; the
+ *                         producer must be unguarded or guarded exactly as the consumer (parameters compared by
+ *                         name), the consumer must read the intermediate only at the producer's store index.
+ * For the TRY and GUARDED kinds *fused is 0 when nothing was fused (out is then empty); for GUARDED
+ * sb200_last_error_string then says which condition failed. */
 #define SB200_FUSE_PLAIN 0
 #define SB200_FUSE_REDUCTION 1
 #define SB200_FUSE_STENCIL 2
 #define SB200_FUSE_TRY 3
 #define SB200_FUSE_TRY_ALL 4
+#define SB200_FUSE_GUARDED 5
 SB200_API int sb200_ir_can_fuse_as(const char *producer, const char *consumer, const char *intermediate, int kind, int *result);
 SB200_API int sb200_ir_fuse_as(const char *producer, const char *consumer, const char *intermediate, int kind,
                                char *out, int outlen, int *fused);

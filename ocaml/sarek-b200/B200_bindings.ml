@@ -71,6 +71,10 @@ let sb200_kernel_launch =
     (uint64_t @-> ptr sb200_arg @-> int @-> ptr uint32_t @-> ptr uint32_t @-> uint32_t @-> uint64_t @-> returning int)
 let sb200_enable_profiling = fn "sb200_enable_profiling" (int @-> returning int)
 let sb200_set_mode = fn "sb200_set_mode" (int @-> returning int)
+(* fusion on IR text; kind 5 = the backend's guarded fusion of `if tid < n then ..` kernels,
+   which Sarek_fusion leaves unfused (sarek/sarek/Sarek_fusion.ml:370-375) *)
+let sb200_ir_fuse_as =
+  fn "sb200_ir_fuse_as" (string @-> string @-> string @-> int @-> ptr char @-> int @-> ptr int @-> returning int)
 
 exception B200_error of int * string
 

@@ -70,6 +70,23 @@ module Backend : Framework_sig.BACKEND = struct
   let unwrap_kargs = function B200_kargs a -> Some a | _ -> None
 end
 
+(** The backend's guarded fusion: [Some text] is the fused kernel in the text form [run_source]
+    takes (pass it as [~source] with the merged argument list: the consumer's arguments without the
+    intermediate, then the producer's that are new by name), [None] when a condition fails — the
+    library's last error string then names it.  Covers the kernel form of the benchmarks,
+    [let tid = global_thread_id in if tid < n then ...], which [Sarek_fusion.fuse] gives back
+    unfused (sarek/sarek/Sarek_fusion.ml:370-375). *)
+let fuse_guarded (producer : Sarek_ir_types.kernel) (consumer : Sarek_ir_types.kernel) (intermediate : string) :
+    string option =
+  let open Ctypes in
+  let len = 1 lsl 20 in
+  let buf = allocate_n char ~count:len in
+  let fused = allocate int 0 in
+  B200_bindings.check "sb200_ir_fuse_as"
+    (Lazy.force B200_bindings.sb200_ir_fuse_as
+       (B200_ir_ser.to_sexp producer) (B200_ir_ser.to_sexp consumer) intermediate 5 buf len fused) ;
+  if !@fused = 0 then None else Some (Ctypes.coerce (ptr char) string buf)
+
 let is_disabled () =
   Sys.getenv_opt "SPOC_DISABLE_GPU" = Some "1" || Sys.getenv_opt "SPOC_DISABLE_B200" = Some "1"
 

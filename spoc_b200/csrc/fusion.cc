@@ -19,6 +19,7 @@
 // fuse, fuse_stencil and try_fuse_all rewrite every read.
 #include <algorithm>
 #include <functional>
+#include <map>
 #include <set>
 
 #include "../../include/sb200.h"
@@ -533,6 +534,185 @@ Kernel fuse_stencil_k(const Kernel& prod, const Kernel& cons, const std::string&
   return out;
 }
 
+// ---- guarded fusion (an extension of this backend; no counterpart in the reference) ----------
+// The reference's own benchmark kernels have the form
+//   let tid = global_thread_id in if tid < n then out.(tid) <- e
+// which its pass cannot fuse: find_write_expr gives up inside a conditional (:370-375) and two
+// kernels never share the id of their `tid` (:38).  Here both kernels are normalised first:
+// index lets (pure, free of array reads) are inlined, so that both index the intermediate by
+// the same intrinsic expression, and else-less guards are peeled off.  Fusion then needs
+//   * no barrier in either kernel;
+//   * every read of the intermediate in the consumer at the producer's store index;
+//   * the producer unguarded, or guarded exactly as the consumer (parameters compared by name,
+//     the reference's convention for "the same argument"), so that the consumer never reads an
+//     element the producer would not have written;
+//   * a producer expression built from parameters only.
+// The result is the consumer's guarded body with the reads replaced, named <consumer>_fused,
+// parameters merged as fuse does.
+using VarEnv = std::map<std::string, Sx>;  // variable id -> defining expression (already inlined)
+
+Sx inline_vars(const Sx& e, const VarEnv& env) {
+  if (e.atom) return e;
+  if (e.is("evar") && e.size() >= 3) {
+    auto it = env.find(e[2].s);
+    return it == env.end() ? e : it->second;
+  }
+  Sx o;
+  o.kids.reserve(e.kids.size());
+  for (const Sx& k : e.kids) o.kids.push_back(inline_vars(k, env));
+  return o;
+}
+
+bool has_read(const Sx& e) {
+  if (e.atom) return false;
+  if (e.is("read")) return true;
+  for (const Sx& k : e.kids)
+    if (has_read(k)) return true;
+  return false;
+}
+
+struct Normal {
+  std::vector<Sx> guards;  // outermost first, index lets inlined
+  Sx inner;                // the guarded statement, index lets inlined
+};
+
+Normal normalise(const Sx& body) {
+  Normal n;
+  VarEnv env;
+  const Sx* s = &body;
+  for (;;) {
+    if (s->is("let") && s->size() == 6 && !(*s)[4].is("arraycreate") && !has_read((*s)[4])) {
+      env[(*s)[2].s] = inline_vars((*s)[4], env);
+      s = &(*s)[5];
+    } else if (s->is("block") && s->size() == 2) {
+      s = &(*s)[1];
+    } else if (s->is("pragma") && s->size() == 3) {
+      s = &(*s)[2];
+    } else if (s->is("seq") && s->size() == 2) {
+      s = &(*s)[1];
+    } else if (s->is("sif") && s->size() == 3) {
+      n.guards.push_back(inline_vars((*s)[1], env));
+      s = &(*s)[2];
+    } else {
+      break;
+    }
+  }
+  n.inner = inline_vars(*s, env);
+  return n;
+}
+
+// structural equality with variables compared by NAME (parameters of two different kernels)
+bool equal_by_name(const Sx& a, const Sx& b) {
+  if (a.atom || b.atom) return a.atom && b.atom && a.s == b.s;
+  if (a.is("evar") && b.is("evar")) return a.size() >= 2 && b.size() >= 2 && a[1].s == b[1].s;
+  if (a.size() != b.size()) return false;
+  for (size_t i = 0; i < a.size(); ++i)
+    if (!equal_by_name(a[i], b[i])) return false;
+  return true;
+}
+
+const Sx* find_param(const Kernel& k, const std::string& name) {
+  for (size_t i = 1; i < k.params().size(); ++i)
+    if (k.params()[i].size() >= 3 && k.params()[i][1].s == name) return &k.params()[i];
+  return nullptr;
+}
+
+// Producer variables become the consumer's where both kernels have a parameter of that name;
+// false when the expression uses anything that is not a producer parameter.
+bool rebind_params(const Sx& e, const Kernel& prod, const Kernel& cons, Sx* out, std::string* why) {
+  if (e.atom) {
+    *out = e;
+    return true;
+  }
+  if (e.is("evar") && e.size() >= 3) {
+    const Sx* pp = find_param(prod, e[1].s);
+    if (!pp || (*pp)[2].s != e[2].s) {
+      *why = "the producer's stored expression uses the local variable '" + e[1].s + "'";
+      return false;
+    }
+    const Sx* cp = find_param(cons, e[1].s);
+    *out = cp ? Sx::L({e[0], e[1], (*cp)[2]}) : e;
+    return true;
+  }
+  Sx o;
+  for (const Sx& k : e.kids) {
+    Sx r;
+    if (!rebind_params(k, prod, cons, &r, why)) return false;
+    o.kids.push_back(r);
+  }
+  *out = o;
+  return true;
+}
+
+bool fuse_guarded_k(const Kernel& prod, const Kernel& cons, const std::string& inter, Kernel* out, std::string* why) {
+  if (has_barrier(prod.body()) || has_barrier(cons.body())) {
+    *why = "a barrier prevents fusion";
+    return false;
+  }
+  Normal np = normalise(prod.body()), nc = normalise(cons.body());
+  AccessList pw, cr, gr;
+  writes_stmt(np.inner, &pw);
+  reads_stmt(nc.inner, &cr);
+  for (const Sx& g : nc.guards) reads_expr(g, &gr);
+  for (const Sx& g : np.guards) reads_expr(g, &gr);
+  for (const Access& a : gr)
+    if (a.first == inter) {
+      *why = "a guard reads the intermediate";
+      return false;
+    }
+  const Sx* widx = nullptr;
+  int nwrites = 0;
+  for (const Access& a : pw)
+    if (a.first == inter) {
+      widx = &a.second;
+      ++nwrites;
+    }
+  if (nwrites != 1) {
+    *why = nwrites ? "the producer stores the intermediate more than once" : "the producer does not store the intermediate";
+    return false;
+  }
+  int nreads = 0;
+  for (const Access& a : cr)
+    if (a.first == inter) {
+      ++nreads;
+      if (!expr_equal(a.second, *widx)) {
+        *why = "the consumer reads the intermediate at an index other than the producer's store index";
+        return false;
+      }
+    }
+  if (!nreads) {
+    *why = "the consumer does not read the intermediate";
+    return false;
+  }
+  AccessList cw;
+  writes_stmt(nc.inner, &cw);
+  for (const Access& a : cw)
+    if (a.first == inter) {
+      *why = "the consumer stores to the intermediate";
+      return false;
+    }
+  if (!np.guards.empty()) {
+    bool same = np.guards.size() == nc.guards.size();
+    for (size_t i = 0; same && i < np.guards.size(); ++i) same = equal_by_name(np.guards[i], nc.guards[i]);
+    if (!same) {
+      *why = "the producer's guard differs from the consumer's: the consumer could read elements the producer skips";
+      return false;
+    }
+  }
+  const Sx* stored = find_write_expr(np.inner, inter, *widx);
+  if (!stored) {
+    *why = "the producer's store of the intermediate is inside a conditional or a loop";
+    return false;
+  }
+  Sx repl;
+  if (!rebind_params(*stored, prod, cons, &repl, why)) return false;
+  Sx body = subst_stmt(nc.inner, inter, *widx, repl);
+  for (size_t i = nc.guards.size(); i-- > 0;) body = Sx::L({Sx::A("sif"), nc.guards[i], body});
+  out->root = Sx::L({Sx::A("kernel"), Sx::A(cons.name() + "_fused"), merged_params(prod, cons, inter),
+                     Sx::L({Sx::A("body"), body})});
+  return true;
+}
+
 // try_fuse (:759-766): reduction, else plain.  try_fuse_all (:1022-1030): reduction, stencil, plain.
 bool try_fuse_k(const Kernel& p, const Kernel& c, const std::string& inter, bool with_stencil, Kernel* out) {
   if (can_fuse_reduction_k(p, c, inter)) {
@@ -661,7 +841,7 @@ int ir_auto_fuse_pipeline(const std::vector<std::string>& kernels, std::string* 
   return SB200_OK;
 }
 
-// kind: 0 plain (can_fuse / fuse), 1 reduction, 2 stencil, 3 try_fuse, 4 try_fuse_all
+// kind: 0 plain (can_fuse / fuse), 1 reduction, 2 stencil, 3 try_fuse, 4 try_fuse_all, 5 guarded (this backend's)
 int ir_can_fuse_as(const std::string& producer, const std::string& consumer, const std::string& inter, int kind, bool* ok,
                    std::string* err) {
   Kernel p, c;
@@ -673,6 +853,7 @@ int ir_can_fuse_as(const std::string& producer, const std::string& consumer, con
     case 2: *ok = can_fuse_stencil_k(p, c, inter); break;
     case 3: *ok = try_fuse_k(p, c, inter, false, &tmp); break;
     case 4: *ok = try_fuse_k(p, c, inter, true, &tmp); break;
+    case 5: *ok = fuse_guarded_k(p, c, inter, &tmp, err); break;
     default: *err = "unknown fusion kind"; return SB200_ERR_INVALID_VALUE;
   }
   return SB200_OK;
@@ -689,6 +870,7 @@ int ir_fuse_as(const std::string& producer, const std::string& consumer, const s
     case 2: r = fuse_stencil_k(p, c, inter); break;
     case 3: *fused = try_fuse_k(p, c, inter, false, &r); break;
     case 4: *fused = try_fuse_k(p, c, inter, true, &r); break;
+    case 5: *fused = fuse_guarded_k(p, c, inter, &r, err); break;
     default: *err = "unknown fusion kind"; return SB200_ERR_INVALID_VALUE;
   }
   *out = *fused ? sx_print(r.root) : std::string();

@@ -1213,6 +1213,7 @@ int sb200_ir_can_fuse_as(const char* producer, const char* consumer, const char*
   std::string err;
   int rc = ir_can_fuse_as(producer, consumer, intermediate, kind, &ok, &err);
   if (rc) return fail(rc, "%s", err.c_str());
+  if (!ok && !err.empty()) fail(SB200_OK, "%s", err.c_str());  // the reason, for sb200_last_error_string
   *result = ok ? 1 : 0;
   return SB200_OK;
 }
@@ -1224,6 +1225,7 @@ int sb200_ir_fuse_as(const char* producer, const char* consumer, const char* int
   bool f = false;
   int rc = ir_fuse_as(producer, consumer, intermediate, kind, &text, &f, &err);
   if (rc) return fail(rc, "%s", err.c_str());
+  if (!f && !err.empty()) fail(SB200_OK, "%s", err.c_str());  // the reason, for sb200_last_error_string
   *fused = f ? 1 : 0;
   return copy_out(text, out, outlen);
 }

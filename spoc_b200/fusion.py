@@ -64,7 +64,7 @@ def auto_fuse_pipeline(kernels: Sequence[str]) -> tuple[str, list[str], list[str
     return out.value.decode(), (e.split(",") if e else []), (s.split("\n") if s else [])
 
 
-PLAIN, REDUCTION, STENCIL, TRY, TRY_ALL = 0, 1, 2, 3, 4
+PLAIN, REDUCTION, STENCIL, TRY, TRY_ALL, GUARDED = 0, 1, 2, 3, 4, 5
 
 
 def _can_as(producer: str, consumer: str, intermediate: str, kind: int) -> bool:
@@ -102,3 +102,19 @@ def try_fuse(producer: str, consumer: str, intermediate: str):
 
 def try_fuse_all(producer: str, consumer: str, intermediate: str):
     return _fuse_as(producer, consumer, intermediate, TRY_ALL)
+
+
+def can_fuse_guarded(producer: str, consumer: str, intermediate: str) -> bool:
+    """This backend's extension (not in the reference): kernels of the guarded form
+    ``let tid = global_thread_id in if tid < n then out.(tid) <- e`` — the form of the reference's own
+    benchmark kernels, which its pass leaves unfused (sarek/sarek/Sarek_fusion.ml:370-375)."""
+    return _can_as(producer, consumer, intermediate, GUARDED)
+
+
+def fuse_guarded(producer: str, consumer: str, intermediate: str):
+    """Fused kernel text, or None; ``why_not_fused()`` then names the failed condition."""
+    return _fuse_as(producer, consumer, intermediate, GUARDED)
+
+
+def why_not_fused() -> str:
+    return L.load().sb200_last_error_string().decode()

@@ -370,6 +370,15 @@ inline bool try_fuse_all(const std::string& p, const std::string& c, const std::
   if (f) *fused = out;
   return f != 0;
 }
+// this backend's extension: fusion of the guarded `let tid = .. in if tid < n then ..` kernel form
+inline bool fuse_guarded(const std::string& p, const std::string& c, const std::string& inter, std::string* fused) {
+  std::string out(1 << 20, '\0');
+  int f = 0;
+  check(sb200_ir_fuse_as(p.c_str(), c.c_str(), inter.c_str(), SB200_FUSE_GUARDED, &out[0], static_cast<int>(out.size()), &f));
+  out.resize(std::strlen(out.c_str()));
+  if (f) *fused = out;
+  return f != 0;
+}
 }  // namespace fusion
 
 }  // namespace sarek_b200

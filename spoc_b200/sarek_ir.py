@@ -17,7 +17,7 @@ from typing import Iterable, Sequence
 __all__ = [
     "sx", "Builder", "vector_add_ir", "stream_triad_ir", "matmul_naive_ir", "matmul_tiled_ir",
     "triad_producer_ir", "square_add_consumer_ir", "chain_fused_ir", "generic_example_ir",
-    "block_reduce_ir",
+    "block_reduce_ir", "square_add_guarded_ir",
 ]
 
 
@@ -262,6 +262,19 @@ def chain_fused_ir(scalar: float = 3.0, index: str = "global_thread_id") -> str:
     t = b.binop("add", b.read("b", idx), b.binop("mul", b.c_f32(scalar), b.read("c", idx)))
     body = ("assign", ("elem", "d", idx), b.binop("add", b.binop("mul", t, t), b.read("b", idx)))
     return _kernel("square_add_fused", p, body)
+
+
+def square_add_guarded_ir(name: str = "square_add") -> str:
+    """d.(tid) <- a.(tid) *. a.(tid) +. b.(tid) in the guarded form of the reference's benchmark kernels
+    (let tid = global_thread_id in if tid < n then ..., benchmarks/bench_stream_triad.ml:22-31): the
+    consumer that follows stream_triad_ir in the chain a = b + s*c ; d = a*a + b."""
+    b = Builder()
+    p = b.params([("vec", "d", "f32"), ("vec", "a", "f32"), ("vec", "b", "f32"), ("scalar", "n", "i32")])
+    body = b.let("tid", "i32", b.intr("global_thread_id"), lambda: (
+        "sif", b.binop("lt", b.evar("tid"), b.evar("n")),
+        ("assign", ("elem", "d", b.evar("tid")),
+         b.binop("add", b.binop("mul", b.read("a", b.evar("tid")), b.read("a", b.evar("tid"))), b.read("b", b.evar("tid"))))))
+    return _kernel(name, p, body)
 
 
 def generic_example_ir() -> str:

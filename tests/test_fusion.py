@@ -171,3 +171,81 @@ def test_errors():
         F.fuse("(kernel", CONSUMER, "temp")
     with pytest.raises(BackendError):
         F.fuse_pipeline([])
+
+
+# ---- guarded fusion: this backend's extension for the reference's own benchmark kernel form ----
+
+def test_reference_pass_leaves_guarded_benchmark_kernels_unfused():
+    """Sarek_fusion.ml:370-375: find_write_expr returns None inside SIf, so fuse gives the consumer back."""
+    prod, cons = S.stream_triad_ir("triad"), S.square_add_guarded_ir()
+    assert not F.can_fuse(prod, cons, "a")
+    for out in (F.fuse(prod, cons, "a"), F.try_fuse_all(prod, cons, "a")):
+        assert "(read a" in out and "(read c" not in out     # the consumer comes back, still reading the intermediate
+
+
+def test_guarded_fusion_of_the_benchmark_kernel_form():
+    prod, cons = S.stream_triad_ir("triad"), S.square_add_guarded_ir()
+    assert F.can_fuse_guarded(prod, cons, "a")
+    fused = F.fuse_guarded(prod, cons, "a")
+    assert fused.startswith("(kernel square_add_fused ")
+    assert "(read a" not in fused and "(vec a " not in fused        # intermediate eliminated
+    assert fused.count("(read c ") == 2 and fused.count("(read b ") == 3
+    assert "(sif (binop lt (intrinsic (Gpu) global_thread_id) (evar n 4))" in fused   # consumer's guard and its n
+    # parameters: the consumer's without the intermediate, then the producer's that are new by name
+    names = [p.split()[1] for p in fused.split("(params ")[1].split("(body")[0].split("(")[1:]]
+    assert names == ["d", "b", "n", "c", "scalar"]
+    info = F.analyze(fused)
+    assert info["writes"] == {"d": "one_to_one"} and set(info["reads"]) == {"b", "c"}
+
+
+def test_guarded_fusion_accepts_an_unguarded_producer_and_chains():
+    prod = S.triad_producer_ir()                   # unguarded store at global_thread_id
+    fused = F.fuse_guarded(prod, S.square_add_guarded_ir(), "a")
+    assert fused is not None and "(read a" not in fused and "(sif " in fused
+    # a three-kernel chain: (triad ; square_add) ; e = d + d
+    b = S.Builder()
+    p = b.params([("vec", "e", "f32"), ("vec", "d", "f32"), ("scalar", "n", "i32")])
+    body = b.let("i", "i32", b.intr("global_thread_id"), lambda: (
+        "sif", b.binop("lt", b.evar("i"), b.evar("n")),
+        ("assign", ("elem", "e", b.evar("i")), b.binop("add", b.read("d", b.evar("i")), b.read("d", b.evar("i"))))))
+    third = S.sx(("kernel", "twice", p, ("body", body)))
+    both = F.fuse_guarded(F.fuse_guarded(S.stream_triad_ir("triad"), S.square_add_guarded_ir(), "a"), third, "d")
+    assert both is not None and both.startswith("(kernel twice_fused ")
+    assert "(read d" not in both and "(read a" not in both and both.count("(read c ") == 4
+
+
+@pytest.mark.parametrize("case,needle", [
+    ("guards_differ", "guard differs"),
+    ("other_index", "index other than"),
+    ("unguarded_consumer", "guard differs"),
+    ("barrier", "barrier"),
+    ("not_read", "does not read"),
+    ("local_variable", "local variable"),
+])
+def test_guarded_fusion_refuses_with_a_reason(case, needle):
+    prod, cons = S.stream_triad_ir("triad"), S.square_add_guarded_ir()
+    if case == "guards_differ":
+        cons = cons.replace("(evar n 4)", "(evar m 4)").replace("(scalar n 4 i32)", "(scalar m 4 i32)")
+    elif case == "other_index":
+        cons = cons.replace("(read a (evar tid 5)) (read a (evar tid 5))",
+                            "(read a (evar tid 5)) (read a (binop add (evar tid 5) (const i32 1)))")
+    elif case == "unguarded_consumer":
+        cons = S.square_add_consumer_ir()
+    elif case == "barrier":
+        cons = cons.replace("(body ", "(body (seq (barrier) ").replace(")))", "))))", 1)[:-0] if False else \
+            S.sx(("kernel", "k", ("params", ("vec", "d", 1, "f32"), ("vec", "a", 2, "f32")),
+                  ("body", ("seq", ("barrier",), ("assign", ("elem", "d", TX), ("read", "a", TX))))))
+    elif case == "not_read":
+        cons = S.vector_add_ir("add").replace("(read a ", "(read z ").replace("(vec a ", "(vec z ")
+    elif case == "local_variable":
+        # producer:  let x = b[tid] in a[tid] <- x + x   (a let that reads an array stays in place)
+        b = S.Builder()
+        p = b.params([("vec", "a", "f32"), ("vec", "b", "f32"), ("scalar", "n", "i32")])
+        body = b.let("tid", "i32", b.intr("global_thread_id"), lambda: (
+            "sif", b.binop("lt", b.evar("tid"), b.evar("n")),
+            b.let("x", "f32", b.read("b", b.evar("tid")), lambda:
+                  ("assign", ("elem", "a", b.evar("tid")), b.binop("add", b.evar("x"), b.evar("x"))))))
+        prod = S.sx(("kernel", "p", p, ("body", body)))
+    assert not F.can_fuse_guarded(prod, cons, "a")
+    assert needle in F.why_not_fused()
+    assert F.fuse_guarded(prod, cons, "a") is None

@@ -224,6 +224,37 @@ def test_unfused_consumer_runs_through_the_generated_path(backend, device):
         t.free()
 
 
+@pytest.mark.parametrize("n", [1, 255, 1000, 256 * 40, 100003])
+def test_guarded_benchmark_kernels_fused_by_the_backend(backend, device, oracle, n):
+    """stream_triad followed by a guarded consumer, the kernel form of the reference's benchmarks
+    (benchmarks/bench_stream_triad.ml:22-31), run unfused (two launches) and fused by the backend's
+    guarded fusion (one launch); both against Native's result of the two kernels in sequence."""
+    from spoc_b200 import fusion as F
+    b, c = _inputs(n, seed=11)
+    grid = dims1d((n + 255) // 256)               # the launch covers more threads than elements: the guard matters
+    va, vd = Vector.create(backend, n), Vector.create(backend, n)
+    vb, vc = Vector(backend, b.copy()), Vector(backend, c.copy())
+    run_vectors(backend, device=device, ir=sarek_ir.stream_triad_ir("triad"), args=[va, vb, vc, ("float32", 3.0), ("int32", n)],
+                block=dims1d(256), grid=grid)
+    run_vectors(backend, device=device, ir=sarek_ir.square_add_guarded_ir(), args=[vd, va, vb, ("int32", n)],
+                block=dims1d(256), grid=grid)
+    unfused = vd.to_array().copy()
+    fused_ir = F.fuse_guarded(sarek_ir.stream_triad_ir("triad"), sarek_ir.square_add_guarded_ir(), "a")
+    assert fused_ir is not None
+    vf = Vector.create(backend, n)
+    before = backend.launch_count()
+    run_vectors(backend, device=device, ir=fused_ir, args=[vf, vb, ("int32", n), vc, ("float32", 3.0)],
+                block=dims1d(256), grid=grid, kernel_name="square_add_fused")
+    assert backend.launch_count() - before <= 3   # vector body + scalar head/tail, never two passes over the data
+    fused = vf.to_array()
+    ref = np.empty(n, np.float32)
+    oracle.so_chain_triad_square(ref, None, b, c, 3.0, n)
+    assert O.ulp_distance(unfused, ref).max() <= 1
+    assert O.ulp_distance(fused, ref).max() <= 1
+    for v in (va, vd, vb, vc, vf):
+        v.free()
+
+
 @pytest.mark.parametrize("kind", ["dot", "sum"])
 @pytest.mark.parametrize("n,block", [(1000, 256), (256 * 40, 256), (100003, 256), (5000, 64), (70000, 1024)])
 def test_block_tree_reduction_is_bit_exact(backend, device, oracle, kind, n, block):
