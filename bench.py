@@ -445,6 +445,40 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         dist.destroy_process_group()
 
 
+def run_transfer_case(lib, dev, S: int) -> None:
+    """Whole-vector copies of S*S float32 (1 GiB at --size 16384) between the device and (a) pageable host
+    memory through the library's staged path, (b) the same with the staged path switched off in a child
+    process, (c) pinned host memory.  Wall-clock of the synchronous call, best of 3."""
+    import ctypes as Ct
+    import numpy as np
+    from spoc_b200.plugin import _check
+    n = S * S
+    dptr = Ct.c_uint64(0)
+    _check(lib.sb200_mem_alloc(dev.id, 4 * n, Ct.byref(dptr)))
+    host = np.ones(n, np.float32)
+    pinned = Ct.c_void_p()
+    _check(lib.sb200_host_alloc(4 * n, Ct.byref(pinned)))
+
+    def best(fn):
+        fn()
+        ts = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return 4 * n / min(ts) / 1e9
+
+    out = {"case": "transfer", "bytes": 4 * n, "unit": "GB/s",
+           "staged_path": os.environ.get("SAREK_B200_STAGED_COPY", "1") != "0",
+           "pageable_htod": best(lambda: _check(lib.sb200_memcpy_htod(dev.id, dptr.value, host.ctypes.data, 4 * n))),
+           "pageable_dtoh": best(lambda: _check(lib.sb200_memcpy_dtoh(dev.id, host.ctypes.data, dptr.value, 4 * n))),
+           "pinned_htod": best(lambda: _check(lib.sb200_memcpy_htod(dev.id, dptr.value, pinned, 4 * n))),
+           "pinned_dtoh": best(lambda: _check(lib.sb200_memcpy_dtoh(dev.id, pinned, dptr.value, 4 * n)))}
+    _check(lib.sb200_host_free(pinned))
+    _check(lib.sb200_mem_free(dev.id, dptr.value))
+    print(json.dumps(out), flush=True)
+
+
 def run_case(args) -> None:
     """A small single-operator run for profiler captures: one warm-up call and two
     measured calls of one operator on inputs larger than L2 but well under a GB."""
@@ -461,6 +495,8 @@ def run_case(args) -> None:
     tdev = torch.device("cuda", 0)
     stream = torch.cuda.current_stream().cuda_stream
     S = args.size
+    if args.case == "transfer":
+        return run_transfer_case(lib, dev, S)
     if args.case in ("gemm3", "gemm1"):
         mode = L.MODE_3XTF32 if args.case == "gemm3" else L.MODE_TF32
         bufs = [torch.empty(S * S, dtype=torch.float32, device=tdev) for _ in range(4)]
@@ -692,7 +728,7 @@ def main() -> None:
     ap.add_argument("--workload", default="gemm8192", choices=["gemm8192", "gather", "skinny"],
                     help="gemm8192: the headline run; gather: large square GEMM with the result gathered on every GPU; "
                          "skinny: 65536x4096x4096 GEMM, rows split over the ranks, B broadcast")
-    ap.add_argument("--case", default=None, choices=["gemm3", "gemm1", "map"],
+    ap.add_argument("--case", default=None, choices=["gemm3", "gemm1", "map", "transfer"],
                     help="profiler-sized single-operator run (square size --size; map uses size^2 elements)")
     ap.add_argument("--size", type=int, default=4096)
     ap.add_argument("--gpus", type=int, default=1)

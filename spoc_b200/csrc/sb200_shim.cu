@@ -28,6 +28,7 @@
 #include "ir.hpp"
 #include "map_fused.cuh"
 #include "map_jit.hpp"
+#include "transfer.hpp"
 
 using namespace sb200;
 
@@ -917,6 +918,11 @@ int sb200_memcpy_htod(int dev, uint64_t dst, const void* src, uint64_t bytes) {
   if (rc) return rc;
   if (bytes == 0) return SB200_OK;
   if (!dst || !src) return fail(SB200_ERR_INVALID_VALUE, "null pointer passed to memcpy_htod");
+  if (bytes >= kStagedCopyMinBytes && staged_copy_enabled() && host_memory_is_pageable(src)) {
+    const int e = staged_copy_to_device(dev, as_ptr<void>(dst), src, bytes);
+    if (e) return cuda_fail(static_cast<cudaError_t>(e), "staged host-to-device copy");
+    return SB200_OK;
+  }
   CU_TRY(cudaMemcpy(as_ptr<void>(dst), src, bytes, cudaMemcpyHostToDevice));
   return SB200_OK;
 }
@@ -927,6 +933,11 @@ int sb200_memcpy_dtoh(int dev, void* dst, uint64_t src, uint64_t bytes) {
   if (rc) return rc;
   if (bytes == 0) return SB200_OK;
   if (!dst || !src) return fail(SB200_ERR_INVALID_VALUE, "null pointer passed to memcpy_dtoh");
+  if (bytes >= kStagedCopyMinBytes && staged_copy_enabled() && host_memory_is_pageable(dst)) {
+    const int e = staged_copy_to_host(dev, dst, as_ptr<void>(src), bytes);
+    if (e) return cuda_fail(static_cast<cudaError_t>(e), "staged device-to-host copy");
+    return check_status_word(*d);
+  }
   CU_TRY(cudaMemcpy(dst, as_ptr<void>(src), bytes, cudaMemcpyDeviceToHost));
   return check_status_word(*d);
 }

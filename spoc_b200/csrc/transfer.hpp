@@ -1,0 +1,16 @@
+// transfer.hpp — staged copies between pageable host memory and the device (transfer.cc).
+#pragma once
+#include <cstddef>
+
+namespace sb200 {
+
+// Copies at least this large, from or to pageable host memory, take the staged path.
+constexpr size_t kStagedCopyMinBytes = size_t(16) << 20;
+
+bool staged_copy_enabled();                     // SAREK_B200_STAGED_COPY=0 switches the staged path off
+bool host_memory_is_pageable(const void* p);    // false for pinned / registered / managed memory
+// Both return 0 or a cudaError_t value; synchronous, ordered after all work launched on the device before the call.
+int staged_copy_to_device(int dev, void* dst, const void* src, size_t bytes);
+int staged_copy_to_host(int dev, void* dst, const void* src, size_t bytes);
+
+}  // namespace sb200
