@@ -274,6 +274,9 @@ SB200_API int sb200_get_mode(int *mode);
  * operands to TF32 the same way (nearest-even) and sum k ascending, so their
  * results agree to the last bit. */
 SB200_API int sb200_set_gemm_variant(int variant);
+/* tile columns of the CTA-pair kernel: 0 = automatic (256, or 128 / 64 for problems with too few 256-column
+ * tiles to occupy the SMs), else 64, 128 or 256.  Also SAREK_B200_TILE_N.  Results do not depend on it. */
+SB200_API int sb200_set_gemm_tile_n(int tile_n);
 
 /* seeded synthetic data written on the device: kind 0 U[-1,1), 1 U[-0.1,0.1),
  * 2 N(0,sigma); element i of the stream is a pure function of (seed, stream_id,

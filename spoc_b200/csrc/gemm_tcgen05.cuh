@@ -352,6 +352,44 @@ __global__ void prep_a_kernel(const float* __restrict__ A, long long lda, float*
   }
 }
 
+// The low parts of two row-major matrices in one launch (A and B of a 3xTF32 product whose high parts TMA
+// takes from the caller's matrices): lo[r][c] = rn_tf32(x - rn_tf32(x)), row length padded to colsp with
+// zeros.  Blocks [0, blocks_a) work on job a, the rest on job b.
+struct PrepLoJob {
+  const float* src;
+  long long ld;
+  float* lo;
+  int rows, cols, colsp;
+};
+
+__device__ __forceinline__ void prep_lo_rows(const PrepLoJob& j, long long block, long long nblocks) {
+  const long long quads_per_row = j.colsp >> 2;
+  const long long total = static_cast<long long>(j.rows) * quads_per_row;
+  for (long long q = block * blockDim.x + threadIdx.x; q < total; q += nblocks * blockDim.x) {
+    const long long row = q / quads_per_row;
+    const int k = static_cast<int>(q - row * quads_per_row) << 2;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* src = j.src + row * j.ld + k;   // callers guarantee 16-byte aligned rows
+    if (k + 3 < j.cols) {
+      x = *reinterpret_cast<const float4*>(src);
+    } else {
+      if (k < j.cols) x.x = src[0];
+      if (k + 1 < j.cols) x.y = src[1];
+      if (k + 2 < j.cols) x.z = src[2];
+    }
+    const float4 l = make_float4(tf32_round(x.x - tf32_round(x.x)), tf32_round(x.y - tf32_round(x.y)),
+                                 tf32_round(x.z - tf32_round(x.z)), tf32_round(x.w - tf32_round(x.w)));
+    *reinterpret_cast<float4*>(j.lo + row * j.colsp + k) = l;
+  }
+}
+
+__global__ void prep_lo_two_kernel(const PrepLoJob a, const PrepLoJob b, int blocks_a) {
+  if (static_cast<int>(blockIdx.x) < blocks_a)
+    prep_lo_rows(a, blockIdx.x, blocks_a);
+  else
+    prep_lo_rows(b, blockIdx.x - blocks_a, gridDim.x - blocks_a);
+}
+
 // B[K x N] (row stride ldb) -> hi[N x Kp] (and lo[N x Kp]): 32x32 tiles
 // transposed through shared memory; block (32, 8); 1-D grid over
 // (Kp/32) * ceil(N/32) tiles.

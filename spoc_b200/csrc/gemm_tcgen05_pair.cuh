@@ -23,16 +23,21 @@
 namespace sb200 {
 
 constexpr int PAIR_BM = 256;        // tile rows (128 per block)
-constexpr int PAIR_BN = 256;        // tile columns
+constexpr int PAIR_BN = 256;        // tile columns of the large tile; 128 and 64 serve problems with few tiles
 constexpr int PAIR_GROUP_M = 8;     // rasterisation: bands of 8 row tiles
 constexpr uint32_t PAIR_A_BYTES = 128 * GEMM_BK * 4;  // this block's A rows: 16 KiB
-constexpr uint32_t PAIR_B_BYTES = 128 * GEMM_BK * 4;  // this block's half of B: 16 KiB
 
-template <int MODE>
+// BN = tile columns (256, 128 or 64).  Each block loads BN/2 columns of B.  The narrower tiles need more
+// shared-memory bandwidth per MMA cycle and exist for problems that would otherwise fill only a
+// fraction of the SMs with 256x256 tiles; results do not depend on BN.
+template <int MODE, int BN = PAIR_BN>
 struct PairCfg {
+  static_assert(BN == 256 || BN == 128 || BN == 64, "tile columns");
   static constexpr int kOperands = (MODE == 3) ? 2 : 1;
-  static constexpr int kStages = (MODE == 3) ? 3 : 6;
-  static constexpr uint32_t kStageBytes = kOperands * (PAIR_A_BYTES + PAIR_B_BYTES);
+  static constexpr uint32_t kBBytes = (BN / 2) * GEMM_BK * 4;  // this block's half of B: 16, 8 or 4 KiB
+  static constexpr uint32_t kStageBytes = kOperands * (PAIR_A_BYTES + kBBytes);
+  static constexpr int kStagesFit = (192 * 1024) / kStageBytes;
+  static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;  // 6 / 8 / 8 (TF32), 3 / 4 / 4 (3xTF32)
   static constexpr uint32_t kSmemBytes = kStages * kStageBytes + GEMM_EPI_BUF_BYTES + GEMM_CTRL_BYTES + 1024;
 };
 
@@ -51,13 +56,16 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
 // (swizzle 128B with 32-byte atoms) and consumed through an MN-major descriptor.  TF32 mode then needs
 // no panels at all; 3xTF32 mode needs only the low parts: map_a_lo over an [M x Kp] panel, map_b_lo
 // over a row-major [K x Np] panel read as slabs like B itself.
-template <int MODE, bool DIRECT = false>
+template <int MODE, bool DIRECT = false, int BN = PAIR_BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_b_hi,
                  const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
                  const GemmParams p) {
-  using Cfg = PairCfg<MODE>;
+  using Cfg = PairCfg<MODE, BN>;
   constexpr int STAGES = Cfg::kStages;
+  constexpr uint32_t B_BYTES = Cfg::kBBytes;
+  constexpr int HALF_N = BN / 2;        // columns of B this block loads
+  constexpr int SLABS = HALF_N / 32;    // [32 k][32 n] slabs per stage in the direct layout
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
@@ -118,7 +126,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         int tm, tn;
         pair_tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const int m0 = tm * PAIR_BM + static_cast<int>(rank) * 128;  // this block's rows of A
-        const int n0 = tn * PAIR_BN + static_cast<int>(rank) * 128;  // this block's half of B's N-rows
+        const int n0 = tn * BN + static_cast<int>(rank) * HALF_N;    // this block's half of B's N-rows
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
             atomicCAS(p.status, 0, 0x1100 | (rank << 4) | stage);
@@ -131,22 +139,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           uint8_t* sp = stage_base + stage * Cfg::kStageBytes;
           tma_load_2d_pair(smem_u32(sp), &map_a_hi, bar, kb * GEMM_BK, m0);
           if (DIRECT) {
-            // B is K x N row-major: x = column, y = k; four slabs of 32 columns cover this block's 128
+            // B is K x N row-major: x = column, y = k; slabs of 32 columns cover this block's half
 #pragma unroll
-            for (int sl = 0; sl < 4; ++sl)
+            for (int sl = 0; sl < SLABS; ++sl)
               tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES + sl * 4096), &map_b_hi, bar, n0 + 32 * sl, kb * GEMM_BK);
           } else {
             tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES), &map_b_hi, bar, kb * GEMM_BK, n0);
           }
           if (MODE == 3) {
-            tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES + PAIR_B_BYTES), &map_a_lo, bar, kb * GEMM_BK, m0);
+            tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES + B_BYTES), &map_a_lo, bar, kb * GEMM_BK, m0);
             if (DIRECT) {
 #pragma unroll
-              for (int sl = 0; sl < 4; ++sl)
-                tma_load_2d_pair(smem_u32(sp + 2 * PAIR_A_BYTES + PAIR_B_BYTES + sl * 4096), &map_b_lo, bar, n0 + 32 * sl,
+              for (int sl = 0; sl < SLABS; ++sl)
+                tma_load_2d_pair(smem_u32(sp + 2 * PAIR_A_BYTES + B_BYTES + sl * 4096), &map_b_lo, bar, n0 + 32 * sl,
                                  kb * GEMM_BK);
             } else {
-              tma_load_2d_pair(smem_u32(sp + 2 * PAIR_A_BYTES + PAIR_B_BYTES), &map_b_lo, bar, kb * GEMM_BK, n0);
+              tma_load_2d_pair(smem_u32(sp + 2 * PAIR_A_BYTES + B_BYTES), &map_b_lo, bar, kb * GEMM_BK, n0);
             }
           }
           if (++stage == STAGES) {
@@ -165,7 +173,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------- MMA issuer (leader block)
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = umma_idesc_tf32(PAIR_BM, PAIR_BN, DIRECT);
+      constexpr uint32_t idesc = umma_idesc_tf32(PAIR_BM, BN, DIRECT);
       int stage = 0;
       uint32_t phase = 0;
       int local_tile = 0;
@@ -179,7 +187,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           break;
         }
         tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + acc * PAIR_BN;
+        const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&full_bar[stage]), phase, abort_flag)) {
             atomicCAS(p.status, 0, 0x1300 | stage);
@@ -189,7 +197,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           tc_fence_after_sync();
           const uint32_t sa_hi = smem_u32(stage_base + stage * Cfg::kStageBytes);
           const uint32_t sb_hi = sa_hi + PAIR_A_BYTES;
-          const uint32_t sa_lo = sb_hi + PAIR_B_BYTES;
+          const uint32_t sa_lo = sb_hi + B_BYTES;
           const uint32_t sb_lo = sa_lo + PAIR_A_BYTES;
 #pragma unroll
           for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
@@ -235,7 +243,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       int tm, tn;
       pair_tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int row0 = tm * PAIR_BM + static_cast<int>(rank) * 128 + quarter * 32;
-      const int n0 = tn * PAIR_BN;
+      const int n0 = tn * BN;
       const bool landed = mbar_wait_bounded(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag);
       if (!__all_sync(0xffffffffu, landed)) {
         if (lane == 0) atomicCAS(p.status, 0, 0x1400 | (rank << 4) | acc);
@@ -245,11 +253,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       tc_fence_after_sync();
       const int rows_here = min(32, p.M - row0);
 #pragma unroll 1
-      for (int chunk = 0; chunk < PAIR_BN / 32; ++chunk) {
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
         const int col = n0 + chunk * 32 + lane;
         if (n0 + chunk * 32 >= p.N) break;  // warp-uniform
         uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * PAIR_BN + chunk * 32, v);
+        tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + chunk * 32, v);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) tbuf[lane * 33 + j] = __uint_as_float(v[j]);

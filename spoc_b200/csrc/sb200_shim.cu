@@ -292,6 +292,96 @@ size_t gemm_workspace_need(int mode, long long M, long long N, long long K) {
   return ops * (a + b);
 }
 
+std::atomic<int> g_tile_n{-1};  // -1 = not yet read from the environment; 0 automatic, else 64 / 128 / 256
+
+// Tile columns for the CTA-pair kernel.  256x256 tiles have the best ratio of tensor-core work to
+// shared-memory and L2 traffic, so they serve every problem that fills the GPU with them.  A problem
+// with fewer tiles than CTA pairs takes a narrower tile, which puts more SMs to work and shortens
+// the epilogue that nothing overlaps when a pair computes a single tile.  The estimate is in
+// MMA-cycle units per pair: waves * (k-blocks * cycles per k-block + fill and epilogue).
+int choose_tile_n(long long M, long long N, long long kblocks, int clusters, int mode) {
+  int forced = g_tile_n.load();
+  if (forced < 0) {
+    const char* e = getenv("SAREK_B200_TILE_N");
+    forced = e ? atoi(e) : 0;
+    if (forced != 64 && forced != 128 && forced != 256) forced = 0;
+    g_tile_n.store(forced);
+  }
+  if (forced) return forced;
+  const long long tiles_m = (M + PAIR_BM - 1) / PAIR_BM;
+  const double mmas = mode == 3 ? 3.0 : 1.0;
+  auto cost = [&](int bn) {
+    const long long tiles = tiles_m * ((N + bn - 1) / bn);
+    const long long waves = (tiles + clusters - 1) / clusters;
+    // cycles per k-block: 4 MMAs of bn/2 cycles each (x3 in 3xTF32 mode), or the time to fetch the stage
+    // from L2 at about 60 bytes per cycle and SM, whichever is longer (measured: 256-column tiles are
+    // tensor-bound, narrower ones fetch-bound because A is re-read once per column of tiles)
+    const double mma_cycles = 4.0 * (bn / 2.0) * mmas;
+    const double fetch_cycles = (mode == 3 ? 2.0 : 1.0) * (16384.0 + bn * 64.0) / 60.0;
+    const double per_kblock = (mma_cycles > fetch_cycles ? mma_cycles : fetch_cycles) * (bn == 256 ? 1.0 : 1.1);
+    const double fixed = 6000.0 + 1000.0 * (bn / 32.0);
+    return static_cast<double>(waves) * (static_cast<double>(kblocks) * per_kblock + fixed);
+  };
+  int best = 256;
+  double best_cost = cost(256);
+  for (int bn : {128, 64}) {
+    const double c = cost(bn);
+    if (c < 0.97 * best_cost) {  // a narrower tile must win clearly
+      best = bn;
+      best_cost = c;
+    }
+  }
+  return best;
+}
+
+// One instantiation of the CTA-pair kernel: shared-memory attribute and resident-cluster count are
+// looked up once per device, then the launch.
+template <int MODE, bool DIRECT, int BN>
+int launch_pair(DeviceState& d, int dev_index, cudaStream_t st, const CUtensorMap& ma_hi, const CUtensorMap& mb_hi,
+                const CUtensorMap& ma_lo, const CUtensorMap& mb_lo, GemmParams gp, long long M, long long N) {
+  using PCfg = PairCfg<MODE, BN>;
+  static std::atomic<int> resident[kMaxDevices];  // 0 = not yet asked
+  int max_clusters = resident[dev_index].load();
+  if (max_clusters == 0) {
+    CU_TRY(cudaFuncSetAttribute(gemm_pair_kernel<MODE, DIRECT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                static_cast<int>(PCfg::kSmemBytes)));
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(static_cast<unsigned>(d.sm_count & ~1), 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = PCfg::kSmemBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&max_clusters, gemm_pair_kernel<MODE, DIRECT, BN>, &cfg) != cudaSuccess ||
+        max_clusters <= 0) {
+      cudaGetLastError();
+      max_clusters = d.sm_count / 2;
+    }
+    resident[dev_index].store(max_clusters);
+  }
+  gp.tiles_m = static_cast<int>((M + PAIR_BM - 1) / PAIR_BM);
+  gp.tiles_n = static_cast<int>((N + BN - 1) / BN);
+  gp.group_m = PAIR_GROUP_M;  // 8 measured best at 8192^3 against 2, 4, 16, 32 (both modes)
+  const long long tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n;
+  const long long pairs = tiles < max_clusters ? tiles : max_clusters;
+  gemm_pair_kernel<MODE, DIRECT, BN><<<static_cast<unsigned>(2 * pairs), GEMM_THREADS, PCfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo,
+                                                                                                                mb_lo, gp);
+  return launch_check("gemm_pair_kernel");
+}
+
+template <int MODE, bool DIRECT>
+int launch_pair_bn(int bn, DeviceState& d, int dev_index, cudaStream_t st, const CUtensorMap& ma_hi, const CUtensorMap& mb_hi,
+                   const CUtensorMap& ma_lo, const CUtensorMap& mb_lo, const GemmParams& gp, long long M, long long N) {
+  if (bn == 64) return launch_pair<MODE, DIRECT, 64>(d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N);
+  if (bn == 128) return launch_pair<MODE, DIRECT, 128>(d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N);
+  return launch_pair<MODE, DIRECT, 256>(d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N);
+}
+
 template <int MODE>
 int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, long long K, const float* A,
                      long long lda, const float* B, long long ldb, const GemmParams& gp_in, long long panel_rows_a = 0,
@@ -300,9 +390,6 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   // against one prepared B pass the largest block so that the B panels keep their place.
   if (panel_rows_a < M) panel_rows_a = M;
   using Cfg = GemmCfg<MODE>;
-  // the attribute is per device, so it is set on every call (a cheap host-side call)
-  CU_TRY(cudaFuncSetAttribute(gemm_tf32_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(Cfg::kSmemBytes)));
 
   int variant = g_gemm_variant.load();
   if (variant < 0) {
@@ -319,6 +406,7 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
                       (reinterpret_cast<uintptr_t>(B) & 15) == 0 && (ldb & 3) == 0;
 
   const long long kp = round_up(K, GEMM_BK);
+  const int tile_n = pair ? choose_tile_n(M, N, kp / GEMM_BK, d.sm_count / 2, MODE) : GEMM_BN;
   const size_t a_bytes = round_up(panel_rows_a * kp * 4, 1024), b_bytes = round_up(N * kp * 4, 1024);
   int rc = SB200_OK;
   const long long np = round_up(N, 32);  // row length of the low-part panel of B in the direct layout
@@ -350,19 +438,20 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
       float* b_lo = reinterpret_cast<float*>(ws);
       float* a_lo = reinterpret_cast<float*>(ws + blo_bytes);
       const long long cap = static_cast<long long>(d.sm_count) * 16;
-      {
-        long long grid = (M * (kp >> 2) + 255) / 256;
-        if (grid > cap) grid = cap;
-        prep_a_kernel<3, true><<<static_cast<unsigned>(grid), 256, 0, st>>>(A, lda, nullptr, a_lo, static_cast<int>(M),
-                                                                             static_cast<int>(K), static_cast<int>(kp), 1);
+      long long grid_a = (M * (kp >> 2) + 255) / 256;
+      if (grid_a > cap) grid_a = cap;
+      if (b_panels_ready) {
+        prep_a_kernel<3, true><<<static_cast<unsigned>(grid_a), 256, 0, st>>>(A, lda, nullptr, a_lo, static_cast<int>(M),
+                                                                               static_cast<int>(K), static_cast<int>(kp), 1);
         if ((rc = launch_check("prep_a_kernel(lo)"))) return rc;
-      }
-      if (!b_panels_ready) {
-        long long grid = (K * (np >> 2) + 255) / 256;
-        if (grid > cap) grid = cap;
-        prep_a_kernel<3, true><<<static_cast<unsigned>(grid), 256, 0, st>>>(B, ldb, nullptr, b_lo, static_cast<int>(K),
-                                                                             static_cast<int>(N), static_cast<int>(np), 1);
-        if ((rc = launch_check("prep_b_kernel(lo)"))) return rc;
+      } else {
+        // both low-part panels in one launch
+        long long grid_b = (K * (np >> 2) + 255) / 256;
+        if (grid_b > cap) grid_b = cap;
+        const PrepLoJob ja{A, lda, a_lo, static_cast<int>(M), static_cast<int>(K), static_cast<int>(kp)};
+        const PrepLoJob jb{B, ldb, b_lo, static_cast<int>(K), static_cast<int>(N), static_cast<int>(np)};
+        prep_lo_two_kernel<<<static_cast<unsigned>(grid_a + grid_b), 256, 0, st>>>(ja, jb, static_cast<int>(grid_a));
+        if ((rc = launch_check("prep_lo_two_kernel"))) return rc;
       }
       if ((rc = encode_map_2d(&ma_lo, a_lo, kp, M, kp, GEMM_BK, GEMM_BM, false))) return rc;
       if ((rc = encode_map_2d(&mb_lo, b_lo, N, K, np, 32, GEMM_BK, false, true))) return rc;
@@ -396,7 +485,7 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
       rc = launch_check("prep_b_kernel");
       if (rc) return rc;
     }
-    const int b_box_rows = pair ? 128 : GEMM_BN;
+    const int b_box_rows = pair ? tile_n / 2 : GEMM_BN;
     if ((rc = encode_panel_map(&ma_hi, a_hi, kp, M, GEMM_BM))) return rc;
     if ((rc = encode_panel_map(&mb_hi, b_hi, kp, N, b_box_rows))) return rc;
     if ((rc = encode_panel_map(&ma_lo, a_lo, kp, M, GEMM_BM))) return rc;
@@ -408,49 +497,21 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   gp.status = d.status;
   if (prof) CU_TRY(cudaEventRecord(rec.e1, st));
   if (pair) {
-    using PCfg = PairCfg<MODE>;
-    CU_TRY(cudaFuncSetAttribute(gemm_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                static_cast<int>(PCfg::kSmemBytes)));
-    gp.tiles_m = static_cast<int>((M + PAIR_BM - 1) / PAIR_BM);
-    gp.tiles_n = static_cast<int>((N + PAIR_BN - 1) / PAIR_BN);
-    gp.group_m = PAIR_GROUP_M;  // 8 measured best at 8192^3 against 2, 4, 16, 32 (both modes)
-    // how many 2-block clusters can be resident at once with this much shared memory
-    int max_clusters = 0;
-    {
-      cudaLaunchConfig_t cfg;
-      memset(&cfg, 0, sizeof cfg);
-      cfg.gridDim = dim3(static_cast<unsigned>(d.sm_count & ~1), 1, 1);
-      cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
-      cfg.dynamicSmemBytes = PCfg::kSmemBytes;
-      cudaLaunchAttribute attr;
-      attr.id = cudaLaunchAttributeClusterDimension;
-      attr.val.clusterDim.x = 2;
-      attr.val.clusterDim.y = 1;
-      attr.val.clusterDim.z = 1;
-      cfg.attrs = &attr;
-      cfg.numAttrs = 1;
-      if (cudaOccupancyMaxActiveClusters(&max_clusters, gemm_pair_kernel<MODE>, &cfg) != cudaSuccess || max_clusters <= 0) {
-        cudaGetLastError();
-        max_clusters = d.sm_count / 2;
-      }
-    }
-    const long long tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n;
-    const long long pairs = tiles < max_clusters ? tiles : max_clusters;
-    if (direct) {
-      CU_TRY(cudaFuncSetAttribute(gemm_pair_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(PCfg::kSmemBytes)));
-      gemm_pair_kernel<MODE, true><<<static_cast<unsigned>(2 * pairs), GEMM_THREADS, PCfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo,
-                                                                                                            mb_lo, gp);
-    } else {
-      gemm_pair_kernel<MODE><<<static_cast<unsigned>(2 * pairs), GEMM_THREADS, PCfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo, mb_lo,
-                                                                                                      gp);
-    }
-    rc = launch_check("gemm_pair_kernel");
+    const int dev_index = static_cast<int>(&d - g_dev);
+    rc = direct ? launch_pair_bn<MODE, true>(tile_n, d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N)
+                : launch_pair_bn<MODE, false>(tile_n, d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N);
   } else {
     gp.tiles_m = static_cast<int>((M + GEMM_BM - 1) / GEMM_BM);
     gp.tiles_n = static_cast<int>((N + GEMM_BN - 1) / GEMM_BN);
     const long long tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n;
     const unsigned grid = static_cast<unsigned>(tiles < d.sm_count ? tiles : d.sm_count);
+    static std::atomic<int> attr_set[kMaxDevices];  // the shared-memory attribute is per device: set once on each
+    const int dev_index = static_cast<int>(&d - g_dev);
+    if (!attr_set[dev_index].load()) {
+      CU_TRY(cudaFuncSetAttribute(gemm_tf32_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(Cfg::kSmemBytes)));
+      attr_set[dev_index].store(1);
+    }
     gemm_tf32_kernel<MODE><<<grid, GEMM_THREADS, Cfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo, mb_lo, gp);
     rc = launch_check("gemm_tf32_kernel");
   }
@@ -1342,6 +1403,13 @@ int sb200_chain_triad_square_f32(int dev, uint64_t stream, uint64_t dd, uint64_t
 int sb200_set_mode(int mode) {
   if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   g_mode.store(mode);
+  return SB200_OK;
+}
+
+int sb200_set_gemm_tile_n(int tile_n) {
+  if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256)
+    return fail(SB200_ERR_INVALID_VALUE, "tile columns must be 0 (automatic), 64, 128 or 256, not %d", tile_n);
+  g_tile_n.store(tile_n);
   return SB200_OK;
 }
 

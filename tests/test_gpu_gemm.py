@@ -114,9 +114,41 @@ def test_single_and_pair_kernels_agree_bit_for_bit(backend, device, mode):
             D2.clear()
             gemm(backend, device, mode, M, N, K, A, B, D2)
             assert np.array_equal(want, D2.download()), f"variant {v}"
+            for tile_n in (64, 128, 256):      # narrower tiles of the pair kernel: same sums, same bits
+                assert L.load().sb200_set_gemm_tile_n(tile_n) == 0
+                D2.clear()
+                gemm(backend, device, mode, M, N, K, A, B, D2)
+                assert np.array_equal(want, D2.download()), f"variant {v} tile_n {tile_n}"
+            assert L.load().sb200_set_gemm_tile_n(0) == 0
     finally:
+        L.load().sb200_set_gemm_tile_n(0)
         backend.set_gemm_variant(0)
         for x in (A, B, D1, D2):
+            x.free()
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("tile_n", [64, 128])
+@pytest.mark.parametrize("shape", [(256, 64, 32), (300, 200, 70), (513, 129, 257), (1024, 1024, 1024)])
+def test_narrow_tiles_with_epilogue_match_oracle(backend, device, mode, tile_n, shape):
+    """The 256x128 and 256x64 tiles of the pair kernel, forced, with ragged edges and the fused epilogue."""
+    M, N, K = shape
+    lib = L.load()
+    a, b, c = O.fill(M * K, 61, 1), O.fill(K * N, 61, 2), O.fill(M * N, 61, 3)
+    bias = O.fill(N, 61, 4, kind=1)
+    A, B, Cm, Bi = (dev_from(backend, device, x) for x in (a, b, c, bias))
+    D = Dev(backend, device, M * N)
+    try:
+        assert lib.sb200_set_gemm_tile_n(tile_n) == 0
+        backend.set_gemm_variant(2)
+        gemm(backend, device, mode, M, N, K, A, B, D, alpha=1.5, C_=Cm, beta=0.5, bias=Bi, act=1)
+        got = D.download().reshape(M, N)          # also checks the canaries around D
+        ref = O.gemm(a, b, M, N, K, alpha=1.5, beta=0.5, cin=c, bias=bias, act=1)
+        assert O.gemm_rel_error(got, ref) <= tol(mode, K) * 1.5 * math.sqrt(2)
+    finally:
+        lib.sb200_set_gemm_tile_n(0)
+        backend.set_gemm_variant(0)
+        for x in (A, B, Cm, Bi, D):
             x.free()
 
 
