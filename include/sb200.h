@@ -267,7 +267,9 @@ SB200_API int sb200_chain_triad_square_f32(int dev, uint64_t stream, uint64_t d,
 SB200_API int sb200_set_mode(int mode);
 SB200_API int sb200_get_mode(int *mode);
 /* which tensor-core kernel sb200_gemm_f32 launches: 0 = automatic (CTA pairs on
- * 256x256 tiles when M > 128, else single-CTA 128x256 tiles), 1 = always
+ * 256-row tiles when M > 128 or when the operands are 16-byte aligned with row
+ * strides that are multiples of 4 floats, so that the kernel reads them directly;
+ * else single-CTA 128x256 tiles fed from prepared panels), 1 = always
  * single-CTA tiles, 2 = always CTA pairs, 3 = CTA pairs fed from prepared
  * operand panels even where TF32 mode could read the caller's matrices
  * directly.  Also SAREK_B200_GEMM=single|pair|pair-panels.  All variants round

@@ -397,13 +397,16 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
     variant = (e && !strcmp(e, "single")) ? 1 : (e && !strcmp(e, "pair")) ? 2 : (e && !strcmp(e, "pair-panels")) ? 3 : 0;
     g_gemm_variant.store(variant);
   }
-  // CTA pairs work on 256-row tiles; a problem with at most 128 rows would leave the second block idle
-  const bool pair = variant >= 2 || (variant == 0 && M > GEMM_BM);
   // CTA pairs read the caller's matrices directly when TMA can address them: 16-byte aligned bases and
   // row strides.  TMA rounds A and B to TF32 while loading and B is consumed N-major, so TF32 mode needs
   // neither preparation kernels nor panel scratch, and 3xTF32 mode prepares only the low parts.
-  const bool direct = pair && variant != 3 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0 &&
-                      (reinterpret_cast<uintptr_t>(B) & 15) == 0 && (ldb & 3) == 0;
+  const bool addressable = (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0 &&
+                           (reinterpret_cast<uintptr_t>(B) & 15) == 0 && (ldb & 3) == 0;
+  // CTA pairs work on 256-row tiles.  With at most 128 rows the second block of a pair computes nothing, and
+  // the pair kernel still wins when it can read the operands directly (measured 2x at 64..128 rows: no
+  // transposing pass over B); from prepared panels the single-CTA kernel serves such problems.
+  const bool pair = variant >= 2 || (variant == 0 && (M > GEMM_BM || addressable));
+  const bool direct = pair && variant != 3 && addressable;
 
   const long long kp = round_up(K, GEMM_BK);
   const int tile_n = pair ? choose_tile_n(M, N, kp / GEMM_BK, d.sm_count / 2, MODE) : GEMM_BN;
