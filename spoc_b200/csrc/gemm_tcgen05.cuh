@@ -384,6 +384,7 @@ __device__ __forceinline__ void prep_lo_rows(const PrepLoJob& j, long long block
 }
 
 __global__ void prep_lo_two_kernel(const PrepLoJob a, const PrepLoJob b, int blocks_a) {
+  grid_launch_dependents();  // the GEMM behind this launch may set itself up now; it waits before reading
   if (static_cast<int>(blockIdx.x) < blocks_a)
     prep_lo_rows(a, blockIdx.x, blocks_a);
   else

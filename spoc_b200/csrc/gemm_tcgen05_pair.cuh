@@ -115,6 +115,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   cluster_wait();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched no global memory, so it may overlap the tail of the kernel before this one in
+  // the stream (the preparation of the low-part panels); from here on its results are needed.
+  grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer

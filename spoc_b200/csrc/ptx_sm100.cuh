@@ -143,6 +143,13 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
 }
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may
+// start while the kernel before it in the stream still runs; grid_dependency_wait() returns once that kernel
+// has completed and its writes are visible (at once when there is no such kernel).  A kernel lets its
+// successor start early with grid_launch_dependents().
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }

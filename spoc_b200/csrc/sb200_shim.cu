@@ -369,8 +369,19 @@ int launch_pair(DeviceState& d, int dev_index, cudaStream_t st, const CUtensorMa
   gp.group_m = PAIR_GROUP_M;  // 8 measured best at 8192^3 against 2, 4, 16, 32 (both modes)
   const long long tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n;
   const long long pairs = tiles < max_clusters ? tiles : max_clusters;
-  gemm_pair_kernel<MODE, DIRECT, BN><<<static_cast<unsigned>(2 * pairs), GEMM_THREADS, PCfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo,
-                                                                                                                mb_lo, gp);
+  // programmatic dependent launch: the kernel's set-up may overlap the preparation launch in front of it
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = PCfg::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  CU_TRY(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<MODE, DIRECT, BN>, ma_hi, mb_hi, ma_lo, mb_lo, gp));
   return launch_check("gemm_pair_kernel");
 }
 
