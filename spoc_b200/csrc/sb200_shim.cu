@@ -313,9 +313,10 @@ int choose_tile_n(long long M, long long N, long long kblocks, int clusters, int
   auto cost = [&](int bn) {
     const long long tiles = tiles_m * ((N + bn - 1) / bn);
     const long long waves = (tiles + clusters - 1) / clusters;
-    // cycles per k-block: 4 MMAs of bn/2 cycles each (x3 in 3xTF32 mode), or the time to fetch the stage
-    // from L2 at about 60 bytes per cycle and SM, whichever is longer (measured: 256-column tiles are
-    // tensor-bound, narrower ones fetch-bound because A is re-read once per column of tiles)
+    // cycles per k-block: 4 MMAs of bn/2 cycles each (x3 in 3xTF32 mode), or the time to fetch the stage at
+    // about 60 bytes per cycle and SM, whichever is longer.  That rate is the 192 KiB ring divided by the
+    // loaded TMA latency (measured); narrow tiles need more bytes per MMA cycle because A is re-read once
+    // per column of tiles, so they are fetch-bound where 256-column tiles are tensor-bound
     const double mma_cycles = 4.0 * (bn / 2.0) * mmas;
     const double fetch_cycles = (mode == 3 ? 2.0 : 1.0) * (16384.0 + bn * 64.0) / 60.0;
     const double per_kblock = (mma_cycles > fetch_cycles ? mma_cycles : fetch_cycles) * (bn == 256 ? 1.0 : 1.1);
