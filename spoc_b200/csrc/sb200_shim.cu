@@ -1747,11 +1747,30 @@ extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int6
   float* dD = reinterpret_cast<float*>(base + szA + szB + szC);
   float* dBias = bias ? reinterpret_cast<float*>(base + szA + szB + szC + szD) : nullptr;
 
-  // row blocks: about eight, multiples of 256 rows so that block edges are tile edges
+  // row blocks, multiples of 256 rows so that block edges are tile edges: about eight equal ones, the last of
+  // them halved down to 256 rows, because what follows the last inbound copy — that block's GEMM and its
+  // copy back — is the part of the call that nothing overlaps
   long long block_rows = (M + 7) / 8;
   block_rows = (block_rows + 255) / 256 * 256;
   if (block_rows > M) block_rows = M;
-  const int nblocks = static_cast<int>((M + block_rows - 1) / block_rows);
+  std::vector<std::pair<long long, long long>> blocks;  // (first row, rows)
+  {
+    long long r = 0;
+    while (M - r > block_rows) {
+      blocks.emplace_back(r, block_rows);
+      r += block_rows;
+    }
+    long long rem = M - r;
+    while (rem > 256) {
+      const long long h = (rem / 2 + 255) / 256 * 256;
+      if (h >= rem) break;
+      blocks.emplace_back(r, h);
+      r += h;
+      rem -= h;
+    }
+    if (rem > 0) blocks.emplace_back(r, rem);
+  }
+  const int nblocks = static_cast<int>(blocks.size());
 
   std::vector<cudaEvent_t> ev_in(nblocks), ev_done(nblocks);
   cudaEvent_t ev_b = nullptr;
@@ -1781,7 +1800,7 @@ extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int6
   if (bias) PIPE_TRY(cudaMemcpyAsync(dBias, bias, size_t(N) * 4, cudaMemcpyHostToDevice, d->pipe_in));
   PIPE_TRY(cudaEventRecord(ev_b, d->pipe_in));
   for (int i = 0; i < nblocks; ++i) {
-    const long long r0 = i * block_rows, rows = std::min<long long>(block_rows, M - r0);
+    const long long r0 = blocks[i].first, rows = blocks[i].second;
     if (K > 0)
       PIPE_TRY(cudaMemcpy2DAsync(dA + r0 * K, size_t(K) * 4, A + r0 * lda, size_t(lda) * 4, size_t(K) * 4, size_t(rows),
                                  cudaMemcpyHostToDevice, d->pipe_in));
@@ -1793,7 +1812,7 @@ extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int6
   // compute stream: one GEMM per row block, B's panels prepared by the first
   PIPE_TRY(cudaStreamWaitEvent(d->pipe_compute, ev_b, 0));
   for (int i = 0; i < nblocks && rc == SB200_OK; ++i) {
-    const long long r0 = i * block_rows, rows = std::min<long long>(block_rows, M - r0);
+    const long long r0 = blocks[i].first, rows = blocks[i].second;
     PIPE_TRY(cudaStreamWaitEvent(d->pipe_compute, ev_in[i], 0));
     GemmParams gp;
     memset(&gp, 0, sizeof gp);
