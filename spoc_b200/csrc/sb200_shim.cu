@@ -17,6 +17,7 @@
 #include <algorithm>
 #include <atomic>
 #include <mutex>
+#include <thread>
 #include <string>
 #include <unordered_map>
 #include <unordered_set>
@@ -1771,6 +1772,90 @@ extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int6
     if (rem > 0) blocks.emplace_back(r, rem);
   }
   const int nblocks = static_cast<int>(blocks.size());
+
+  // Pageable host operands (what a Bigarray is): asynchronous copies from pageable memory are neither
+  // asynchronous nor fast, so such a call moves its operands with the staged copier instead — several host
+  // threads through pinned slots — block by block, synchronously for the host, while the GEMM of the block
+  // before runs on the compute stream.  Needs contiguous rows; strided pageable operands take the plain path.
+  const bool contiguous = (K == 0 || (lda == K && ldb == N)) && ldd == N && (!C || ldc == N);
+  const bool any_pageable = staged_copy_enabled() && contiguous &&
+                            ((K > 0 && (host_memory_is_pageable(A) || host_memory_is_pageable(B))) ||
+                             (C && host_memory_is_pageable(C)) || host_memory_is_pageable(D));
+  if (any_pageable) {
+    auto copy_in = [&](void* dst, const void* src, size_t bytes) -> int {
+      if (bytes == 0) return 0;
+      if (bytes >= (size_t(1) << 20) && host_memory_is_pageable(src)) return staged_copy_to_device(dev, dst, src, bytes, false);
+      return static_cast<int>(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice));
+    };
+    auto copy_out = [&](void* dst, const void* src, size_t bytes) -> int {
+      if (bytes == 0) return 0;
+      if (bytes >= (size_t(1) << 20) && host_memory_is_pageable(dst)) return staged_copy_to_host(dev, dst, src, bytes, false);
+      return static_cast<int>(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost));
+    };
+    std::vector<cudaEvent_t> done(nblocks, nullptr);
+    std::thread* out_thread_ptr = nullptr;
+    auto finish = [&](int code, const char* what) -> int {
+      if (out_thread_ptr && out_thread_ptr->joinable()) out_thread_ptr->join();
+      cudaDeviceSynchronize();
+      for (auto e : done) if (e) cudaEventDestroy(e);
+      if (code > 0) return cuda_fail(static_cast<cudaError_t>(code), what);
+      return code;
+    };
+    std::atomic<int> out_error{0};
+    std::thread out_thread;
+    out_thread_ptr = &out_thread;
+    auto copy_block_out = [&](int blk) {
+      cudaSetDevice(dev);
+      int oe = static_cast<int>(cudaEventSynchronize(done[blk]));
+      const long long p0 = blocks[blk].first, prows = blocks[blk].second;
+      if (!oe) oe = copy_out(D + p0 * N, dD + p0 * N, size_t(prows) * N * 4);
+      if (oe) out_error.store(oe);
+    };
+    int e = 0;
+    if (K > 0 && (e = copy_in(dB, B, size_t(K) * N * 4))) return finish(e, "copy of B");
+    if (bias && (e = copy_in(dBias, bias, size_t(N) * 4))) return finish(e, "copy of bias");
+    for (int i = 0; i < nblocks; ++i) {
+      const long long r0 = blocks[i].first, rows = blocks[i].second;
+      if (K > 0 && (e = copy_in(dA + r0 * K, A + r0 * K, size_t(rows) * K * 4))) return finish(e, "copy of an A block");
+      if (C && (e = copy_in(dC + r0 * N, C + r0 * N, size_t(rows) * N * 4))) return finish(e, "copy of a C block");
+      GemmParams gp;
+      memset(&gp, 0, sizeof gp);
+      gp.M = static_cast<int>(rows);
+      gp.N = static_cast<int>(N);
+      gp.D = dD + r0 * N;
+      gp.ldd = N;
+      gp.C = dC ? dC + r0 * N : nullptr;
+      gp.ldc = N;
+      gp.bias = dBias;
+      gp.alpha = alpha;
+      gp.beta = beta;
+      gp.act = act;
+      if (K == 0) {
+        long long grid = (rows * N + 255) / 256;
+        const long long cap = static_cast<long long>(d->sm_count) * 16;
+        if (grid > cap) grid = cap;
+        gemm_k0_kernel<<<static_cast<unsigned>(grid), 256, 0, d->pipe_compute>>>(gp);
+        rc = launch_check("gemm_k0_kernel");
+      } else if (mode == SB200_MODE_3XTF32) {
+        rc = launch_gemm_mode<3>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);
+      } else {
+        rc = launch_gemm_mode<1>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);
+      }
+      if (rc) return finish(rc, "");
+      if ((e = static_cast<int>(cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming)))) return finish(e, "event");
+      if ((e = static_cast<int>(cudaEventRecord(done[i], d->pipe_compute)))) return finish(e, "event");
+      // the block before goes back on a thread of its own, beside the next block's copies in
+      if (out_thread.joinable()) out_thread.join();
+      if (out_error.load()) return finish(out_error.load(), "copy of a D block");
+      if (i > 0) out_thread = std::thread(copy_block_out, i - 1);
+    }
+    if (out_thread.joinable()) out_thread.join();
+    if (out_error.load()) return finish(out_error.load(), "copy of a D block");
+    copy_block_out(nblocks - 1);
+    if (out_error.load()) return finish(out_error.load(), "copy of a D block");
+    rc = finish(0, "");
+    return rc ? rc : check_status_word(*d);
+  }
 
   std::vector<cudaEvent_t> ev_in(nblocks), ev_done(nblocks);
   cudaEvent_t ev_b = nullptr;

@@ -21,7 +21,7 @@
 namespace sb200 {
 namespace {
 
-constexpr size_t kChunk = size_t(4) << 20;
+constexpr size_t kSlotBytes = size_t(4) << 20;  // a staging slot; chunks are at most this large
 constexpr int kMaxLanes = 8;
 constexpr int kMaxDevices = 16;
 
@@ -32,11 +32,11 @@ struct Lane {
 };
 
 struct Pool {
-  std::mutex mu;  // one staged transfer per device at a time
+  std::mutex mu;  // one staged transfer per device and direction at a time
   int lanes = 0;
   Lane lane[kMaxLanes];
 };
-Pool g_pool[kMaxDevices];
+Pool g_pool[kMaxDevices][2];  // [device][0 = to the device, 1 = to the host]: the two directions can run side by side
 
 int lane_count() {
   static int n = [] {
@@ -57,7 +57,7 @@ cudaError_t ensure_pool(Pool& p) {
     Lane& l = p.lane[p.lanes];
     cudaError_t e = cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking);
     for (int s = 0; s < 2 && e == cudaSuccess; ++s) {
-      e = cudaMallocHost(&l.slot[s], kChunk);
+      e = cudaMallocHost(&l.slot[s], kSlotBytes);
       if (e == cudaSuccess) e = cudaEventCreateWithFlags(&l.ev[s], cudaEventDisableTiming);
     }
     if (e != cudaSuccess) return e;  // the lanes built so far stay usable
@@ -70,6 +70,8 @@ struct Job {
   char* dev_ptr;
   char* host_ptr;
   size_t bytes;
+  size_t chunk;  // bytes per chunk: large copies use whole slots, small ones are cut finer so that every lane
+                 // gets several chunks and its host copy overlaps its DMA
   size_t nchunks;
   std::atomic<size_t> next{0};
   std::atomic<int> error{0};
@@ -89,7 +91,7 @@ void to_device_worker(Job* j, Lane* l) {
   while (j->error.load() == 0) {
     const size_t i = j->next.fetch_add(1);
     if (i >= j->nchunks) break;
-    const size_t off = i * kChunk, len = (j->bytes - off < kChunk) ? j->bytes - off : kChunk;
+    const size_t off = i * j->chunk, len = (j->bytes - off < j->chunk) ? j->bytes - off : j->chunk;
     if (used[s]) note(*j, cudaEventSynchronize(l->ev[s]));  // the slot's previous DMA has read it
     memcpy(l->slot[s], j->host_ptr + off, len);
     note(*j, cudaMemcpyAsync(j->dev_ptr + off, l->slot[s], len, cudaMemcpyHostToDevice, l->stream));
@@ -115,7 +117,7 @@ void to_host_worker(Job* j, Lane* l) {
   while (j->error.load() == 0) {
     const size_t i = j->next.fetch_add(1);
     if (i >= j->nchunks) break;
-    const size_t off = i * kChunk, len = (j->bytes - off < kChunk) ? j->bytes - off : kChunk;
+    const size_t off = i * j->chunk, len = (j->bytes - off < j->chunk) ? j->bytes - off : j->chunk;
     note(*j, cudaMemcpyAsync(l->slot[s], j->dev_ptr + off, len, cudaMemcpyDeviceToHost, l->stream));
     note(*j, cudaEventRecord(l->ev[s], l->stream));
     drain();  // the previous chunk's host copy overlaps this chunk's DMA
@@ -129,22 +131,31 @@ void to_host_worker(Job* j, Lane* l) {
   note(*j, cudaStreamSynchronize(l->stream));
 }
 
-int run(int dev, void* dev_ptr, void* host_ptr, size_t bytes, bool to_device) {
+int run(int dev, void* dev_ptr, void* host_ptr, size_t bytes, bool to_device, bool after_device_work) {
   if (dev < 0 || dev >= kMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
-  Pool& p = g_pool[dev];
+  Pool& p = g_pool[dev][to_device ? 0 : 1];
   std::lock_guard<std::mutex> lock(p.mu);
   cudaError_t e = ensure_pool(p);
   if (p.lanes == 0) return static_cast<int>(e);
   cudaGetLastError();
-  // a synchronous copy on the default stream waits for the work launched before it; keep that order
-  e = cudaDeviceSynchronize();
-  if (e != cudaSuccess) return static_cast<int>(e);
+  if (after_device_work) {
+    // a synchronous copy on the default stream waits for the work launched before it; keep that order
+    e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
   Job j;
   j.dev = dev;
   j.dev_ptr = static_cast<char*>(dev_ptr);
   j.host_ptr = static_cast<char*>(host_ptr);
   j.bytes = bytes;
-  j.nchunks = (bytes + kChunk - 1) / kChunk;
+  {
+    size_t c = bytes / (static_cast<size_t>(p.lanes) * 4);
+    c = (c + (size_t(256) << 10) - 1) / (size_t(256) << 10) * (size_t(256) << 10);
+    if (c < (size_t(512) << 10)) c = size_t(512) << 10;
+    if (c > kSlotBytes) c = kSlotBytes;
+    j.chunk = c;
+  }
+  j.nchunks = (bytes + j.chunk - 1) / j.chunk;
   const int workers = static_cast<int>(j.nchunks < static_cast<size_t>(p.lanes) ? j.nchunks : p.lanes);
   std::vector<std::thread> threads;
   threads.reserve(workers);
@@ -174,12 +185,12 @@ bool host_memory_is_pageable(const void* p) {
   return attr.type == cudaMemoryTypeUnregistered;
 }
 
-int staged_copy_to_device(int dev, void* dst, const void* src, size_t bytes) {
-  return run(dev, dst, const_cast<void*>(src), bytes, true);
+int staged_copy_to_device(int dev, void* dst, const void* src, size_t bytes, bool after_device_work) {
+  return run(dev, dst, const_cast<void*>(src), bytes, true, after_device_work);
 }
 
-int staged_copy_to_host(int dev, void* dst, const void* src, size_t bytes) {
-  return run(dev, const_cast<void*>(src), dst, bytes, false);
+int staged_copy_to_host(int dev, void* dst, const void* src, size_t bytes, bool after_device_work) {
+  return run(dev, const_cast<void*>(src), dst, bytes, false, after_device_work);
 }
 
 }  // namespace sb200

@@ -194,6 +194,38 @@ def test_host_operand_gemm_matches_device_path(backend, device, mode, pinned):
             lib.sb200_host_free(p)
 
 
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("mixed", [False, True])
+def test_host_operand_gemm_with_pageable_contiguous_operands(backend, device, mode, mixed):
+    """Contiguous pageable operands take the staged copier block by block (several host threads through pinned
+    slots) while the GEMM of the block before runs; `mixed` keeps C in pinned memory.  Same bits as the device path."""
+    import ctypes as C
+    lib = L.load()
+    M, N, K = 2048 + 300, 1024, 2048          # row blocks of 512 rows (the last ones halved) move 1-4 MiB each
+    a, b, c = O.fill(M * K, 23, 1), O.fill(K * N, 23, 2), O.fill(M * N, 23, 3)
+    bias = O.fill(N, 23, 4, kind=1)
+    d_host = np.full(M * N, CANARY, np.float32)
+    pinned = C.c_void_p()
+    c_arg = c
+    if mixed:
+        assert lib.sb200_host_alloc(c.nbytes, C.byref(pinned)) == 0
+        C.memmove(pinned, c.ctypes.data, c.nbytes)
+        c_arg = np.ctypeslib.as_array(C.cast(pinned, C.POINTER(C.c_float)), shape=(c.size,))
+    ptr = lambda x: x.ctypes.data_as(C.c_void_p)
+    try:
+        rc = lib.sb200_gemm_f32_host(device.id, mode, M, N, K, ptr(a), K, ptr(b), N, ptr(d_host), N, 1.5, ptr(c_arg), N, 0.5,
+                                     ptr(bias), 1)
+        assert rc == 0, lib.sb200_last_error_string()
+        A, B, Cd, Bi, D = (dev_from(backend, device, x) for x in (a, b, c, bias, np.zeros(M * N, np.float32)))
+        gemm(backend, device, mode, M, N, K, A, B, D, alpha=1.5, C_=Cd, beta=0.5, bias=Bi, act=1)
+        assert np.array_equal(d_host, D.download())
+        for x in (A, B, Cd, Bi, D):
+            x.free()
+    finally:
+        if mixed:
+            lib.sb200_host_free(pinned)
+
+
 def test_leading_dimensions_and_submatrices(backend, device):
     M, N, K, lda, ldb, ldd = 70, 90, 50, 64, 100, 128
     a, b = O.fill(M * lda, 3, 1), O.fill(K * ldb, 3, 2)
