@@ -257,6 +257,11 @@ SB200_API int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int64
                                   float beta, const float *bias, int act);
 /* bytes of library-owned scratch sb200_gemm_f32 needs for these sizes */
 SB200_API int sb200_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, uint64_t *bytes);
+/* how sb200_gemm_f32 would run these sizes on a device with sm_count SMs, as text:
+ * "pair|single direct|panels tile=RxC stages=S tiles=T waves=W workspace=BYTES launches=L".
+ * addressable = operands 16-byte aligned with row strides that are multiples of 4 floats.  Needs no GPU. */
+SB200_API int sb200_gemm_describe(int mode, int64_t M, int64_t N, int64_t K, int addressable, int sm_count,
+                                  char *out, int outlen);
 
 /* c = a + b  (benchmarks/bench_vector_add.ml:47-55) */
 SB200_API int sb200_vector_add_f32(int dev, uint64_t stream, uint64_t c, uint64_t a, uint64_t b, int64_t n);

@@ -395,6 +395,62 @@ int launch_pair_bn(int bn, DeviceState& d, int dev_index, cudaStream_t st, const
   return launch_pair<MODE, DIRECT, 256>(d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N);
 }
 
+// How sb200_gemm_f32 will run a product: which kernel, which tile, how much scratch.  One function decides, the
+// launch path and sb200_gemm_describe both ask it.
+struct GemmRoute {
+  bool pair = false;    // CTA-pair kernel (else the single-CTA kernel)
+  bool direct = false;  // operands read where they lie (else from prepared panels)
+  int tile_n = GEMM_BN;
+  int stages = 0;
+  long long tiles = 0, waves = 0;
+  size_t workspace = 0;  // bytes of library scratch
+};
+
+int gemm_variant_setting() {
+  int variant = g_gemm_variant.load();
+  if (variant < 0) {
+    const char* e = getenv("SAREK_B200_GEMM");
+    variant = (e && !strcmp(e, "single")) ? 1 : (e && !strcmp(e, "pair")) ? 2 : (e && !strcmp(e, "pair-panels")) ? 3 : 0;
+    g_gemm_variant.store(variant);
+  }
+  return variant;
+}
+
+GemmRoute route_gemm(int mode, long long M, long long N, long long K, bool addressable, int sm_count, long long panel_rows_a) {
+  GemmRoute r;
+  const int variant = gemm_variant_setting();
+  // CTA pairs work on 256-row tiles.  With at most 128 rows the second block of a pair computes nothing, and
+  // the pair kernel still wins when it can read the operands directly (measured 2x at 64..128 rows: no
+  // transposing pass over B); from prepared panels the single-CTA kernel serves such problems.
+  r.pair = variant >= 2 || (variant == 0 && (M > GEMM_BM || addressable));
+  // CTA pairs read the caller's matrices directly when TMA can address them: 16-byte aligned bases and
+  // row strides.  TMA rounds A and B to TF32 while loading and B is consumed N-major, so TF32 mode needs
+  // neither preparation kernels nor panel scratch, and 3xTF32 mode prepares only the low parts.
+  r.direct = r.pair && variant != 3 && addressable;
+  const long long kp = round_up(K, GEMM_BK);
+  const int clusters = sm_count / 2 > 0 ? sm_count / 2 : 1;
+  r.tile_n = r.pair ? choose_tile_n(M, N, kp / GEMM_BK, clusters, mode == SB200_MODE_3XTF32 ? 3 : 1) : GEMM_BN;
+  if (r.pair) {
+    const bool three = mode == SB200_MODE_3XTF32;
+    r.stages = r.tile_n == 256 ? (three ? PairCfg<3, 256>::kStages : PairCfg<1, 256>::kStages)
+             : r.tile_n == 128 ? (three ? PairCfg<3, 128>::kStages : PairCfg<1, 128>::kStages)
+                               : (three ? PairCfg<3, 64>::kStages : PairCfg<1, 64>::kStages);
+    r.tiles = ((M + PAIR_BM - 1) / PAIR_BM) * ((N + r.tile_n - 1) / r.tile_n);
+    r.waves = (r.tiles + clusters - 1) / clusters;
+  } else {
+    r.stages = mode == SB200_MODE_3XTF32 ? GemmCfg<3>::kStages : GemmCfg<1>::kStages;
+    r.tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + GEMM_BN - 1) / GEMM_BN);
+    r.waves = (r.tiles + sm_count - 1) / (sm_count > 0 ? sm_count : 1);
+  }
+  if (panel_rows_a < M) panel_rows_a = M;
+  if (!r.direct) {
+    r.workspace = gemm_workspace_need(mode, panel_rows_a, N, K);
+  } else if (mode == SB200_MODE_3XTF32) {
+    r.workspace = round_up(K * round_up(N, 32) * 4, 1024) + round_up(panel_rows_a * kp * 4, 1024);
+  }
+  return r;
+}
+
 template <int MODE>
 int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, long long K, const float* A,
                      long long lda, const float* B, long long ldb, const GemmParams& gp_in, long long panel_rows_a = 0,
@@ -404,34 +460,19 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   if (panel_rows_a < M) panel_rows_a = M;
   using Cfg = GemmCfg<MODE>;
 
-  int variant = g_gemm_variant.load();
-  if (variant < 0) {
-    const char* e = getenv("SAREK_B200_GEMM");
-    variant = (e && !strcmp(e, "single")) ? 1 : (e && !strcmp(e, "pair")) ? 2 : (e && !strcmp(e, "pair-panels")) ? 3 : 0;
-    g_gemm_variant.store(variant);
-  }
-  // CTA pairs read the caller's matrices directly when TMA can address them: 16-byte aligned bases and
-  // row strides.  TMA rounds A and B to TF32 while loading and B is consumed N-major, so TF32 mode needs
-  // neither preparation kernels nor panel scratch, and 3xTF32 mode prepares only the low parts.
   const bool addressable = (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0 &&
                            (reinterpret_cast<uintptr_t>(B) & 15) == 0 && (ldb & 3) == 0;
-  // CTA pairs work on 256-row tiles.  With at most 128 rows the second block of a pair computes nothing, and
-  // the pair kernel still wins when it can read the operands directly (measured 2x at 64..128 rows: no
-  // transposing pass over B); from prepared panels the single-CTA kernel serves such problems.
-  const bool pair = variant >= 2 || (variant == 0 && (M > GEMM_BM || addressable));
-  const bool direct = pair && variant != 3 && addressable;
+  const GemmRoute route = route_gemm(MODE == 3 ? SB200_MODE_3XTF32 : SB200_MODE_TF32, M, N, K, addressable, d.sm_count, panel_rows_a);
+  const bool pair = route.pair, direct = route.direct;
+  const int tile_n = route.tile_n;
 
   const long long kp = round_up(K, GEMM_BK);
-  const int tile_n = pair ? choose_tile_n(M, N, kp / GEMM_BK, d.sm_count / 2, MODE) : GEMM_BN;
   const size_t a_bytes = round_up(panel_rows_a * kp * 4, 1024), b_bytes = round_up(N * kp * 4, 1024);
   int rc = SB200_OK;
   const long long np = round_up(N, 32);  // row length of the low-part panel of B in the direct layout
   const size_t blo_bytes = round_up(K * np * 4, 1024);
-  if (!direct) {
-    rc = ensure_workspace(d, gemm_workspace_need(MODE == 3 ? SB200_MODE_3XTF32 : SB200_MODE_TF32, panel_rows_a, N, K));
-    if (rc) return rc;
-  } else if (MODE == 3) {
-    rc = ensure_workspace(d, blo_bytes + a_bytes);
+  if (route.workspace) {
+    rc = ensure_workspace(d, route.workspace);
     if (rc) return rc;
   }
   const bool prof = g_profiling.load() != 0;
@@ -1392,6 +1433,19 @@ int sb200_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, uint64
   if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   *bytes = (M == 0 || N == 0 || K == 0) ? 0 : gemm_workspace_need(mode, M, N, K);
   return SB200_OK;
+}
+
+int sb200_gemm_describe(int mode, int64_t M, int64_t N, int64_t K, int addressable, int sm_count, char* out, int outlen) {
+  if (M < 0 || N < 0 || K < 0 || sm_count <= 0) return fail(SB200_ERR_INVALID_VALUE, "bad argument");
+  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  if (M == 0 || N == 0) return copy_out("nothing to do", out, outlen);
+  if (K == 0) return copy_out("gemm_k0_kernel (epilogue only)", out, outlen);
+  const GemmRoute r = route_gemm(mode, M, N, K, addressable != 0, sm_count, M);
+  char buf[256];
+  snprintf(buf, sizeof buf, "%s %s tile=%dx%d stages=%d tiles=%lld waves=%lld workspace=%zu launches=%d",
+           r.pair ? "pair" : "single", r.direct ? "direct" : "panels", r.pair ? PAIR_BM : GEMM_BM, r.tile_n, r.stages, r.tiles,
+           r.waves, r.workspace, r.direct ? (mode == SB200_MODE_3XTF32 ? 2 : 1) : 3);
+  return copy_out(buf, out, outlen);
 }
 
 int sb200_vector_add_f32(int dev, uint64_t stream, uint64_t c, uint64_t a, uint64_t b, int64_t n) {
