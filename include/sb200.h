@@ -194,7 +194,10 @@ SB200_API int sb200_ir_fuse_as(const char *producer, const char *consumer, const
  * D[M x N] = act(alpha * A[M x K] . B[K x N] + beta * C[M x N] + bias[N]),
  * all row-major float32 with leading dimensions in elements; C and bias may
  * be 0.  D may alias C.  Replaces the matrix_mul / matrix_mul_tiled kernels
- * (benchmarks/bench_matrix_mul.ml:55-73, bench_matrix_mul_tiled.ml:55-94). */
+ * (benchmarks/bench_matrix_mul.ml:55-73, bench_matrix_mul_tiled.ml:55-94).
+ * Once a first call with the same sizes has sized the library's scratch, a call enqueues nothing but kernel launches
+ * (the GEMM launch carries the programmatic-stream-serialization attribute), so it can be captured into a CUDA graph
+ * together with the map operators and replayed (tests/test_gpu_gemm.py). */
 SB200_API int sb200_gemm_f32(int dev, uint64_t stream, int mode,
                              int64_t M, int64_t N, int64_t K,
                              uint64_t A, int64_t lda, uint64_t B, int64_t ldb,

@@ -226,6 +226,41 @@ def test_host_operand_gemm_with_pageable_contiguous_operands(backend, device, mo
             lib.sb200_host_free(pinned)
 
 
+@pytest.mark.parametrize("mode", MODES)
+def test_gemm_and_map_calls_can_be_captured_in_a_cuda_graph(backend, device, mode):
+    """After one eager call has sized the library's scratch, the operators enqueue nothing but kernel launches, so
+    a launch-bound loop can be captured once and replayed; the replay gives the eager bits."""
+    import torch
+    lib = L.load()
+    torch.cuda.set_device(device.id)
+    S = 320
+    A, B = torch.empty(S * S, device="cuda"), torch.empty(S * S, device="cuda")
+    D, E = torch.zeros(S * S, device="cuda"), torch.zeros(S * S, device="cuda")
+    s0 = torch.cuda.current_stream().cuda_stream
+    assert lib.sb200_fill_f32(device.id, s0, A.data_ptr(), S * S, 9, 1, 0, 1.0, 0) == 0
+    assert lib.sb200_fill_f32(device.id, s0, B.data_ptr(), S * S, 9, 2, 0, 1.0, 0) == 0
+
+    def step(stream):
+        assert lib.sb200_gemm_f32(device.id, stream, mode, S, S, S, A.data_ptr(), S, B.data_ptr(), S, D.data_ptr(), S,
+                                  1.0, 0, 0, 0.0, 0, 0) == 0
+        assert lib.sb200_vector_add_f32(device.id, stream, E.data_ptr(), D.data_ptr(), D.data_ptr(), S * S) == 0
+
+    step(s0)
+    torch.cuda.synchronize()
+    want = E.clone()
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.graph(graph, stream=side):
+        for _ in range(3):
+            step(torch.cuda.current_stream().cuda_stream)
+    for _ in range(2):
+        D.zero_()
+        E.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(E, want)
+    assert lib.sb200_device_synchronize(device.id) == 0
+
+
 def test_leading_dimensions_and_submatrices(backend, device):
     M, N, K, lda, ldb, ldd = 70, 90, 50, 64, 100, 128
     a, b = O.fill(M * lda, 3, 1), O.fill(K * ldb, 3, 2)
