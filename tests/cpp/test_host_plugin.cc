@@ -66,6 +66,13 @@ static int run_cpu(const std::string& dir) {
   EXPECT(fusion::try_fuse_all(prod, cons, "a", &fused));
   EXPECT(fused.find("(read a") == std::string::npos);
   EXPECT(fusion::fuse(prod, cons, "a").find("square_add_fused") != std::string::npos);
+  // the guarded kernel form of the benchmarks: the reference's pass gives the consumer back, the backend's fuses it
+  const std::string gprod = slurp(dir + "/stream_triad.ir"), gcons = slurp(dir + "/square_add_guarded.ir");
+  EXPECT(fusion::fuse(gprod, gcons, "a").find("(read a") != std::string::npos);
+  std::string gfused;
+  EXPECT(fusion::fuse_guarded(gprod, gcons, "a", &gfused));
+  EXPECT(gfused.find("(read a") == std::string::npos && gfused.find("(kernel square_add_fused") == 0);
+  EXPECT(!fusion::fuse_guarded(gprod, cons, "a", &gfused));  // unguarded consumer behind a guarded producer
   // argument binding errors come before any device work
   bool args_error = false;
   try {

@@ -26,7 +26,8 @@ def program(tmp_path_factory):
     irdir.mkdir()
     for name, text in {"vector_add": S.vector_add_ir(), "stream_triad": S.stream_triad_ir(), "matmul_naive": S.matmul_naive_ir(),
                        "matmul_tiled": S.matmul_tiled_ir(), "dot_product": S.block_reduce_ir("dot"),
-                       "triad_producer": S.triad_producer_ir(), "square_add_consumer": S.square_add_consumer_ir()}.items():
+                       "triad_producer": S.triad_producer_ir(), "square_add_consumer": S.square_add_consumer_ir(),
+                       "square_add_guarded": S.square_add_guarded_ir()}.items():
         (irdir / f"{name}.ir").write_text(text)
     return exe, str(irdir)
 
