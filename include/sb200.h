@@ -189,6 +189,10 @@ SB200_API int sb200_ir_analyze(const char *kernel, char *out, int outlen);
 SB200_API int sb200_ir_can_fuse_as(const char *producer, const char *consumer, const char *intermediate, int kind, int *result);
 SB200_API int sb200_ir_fuse_as(const char *producer, const char *consumer, const char *intermediate, int kind,
                                char *out, int outlen, int *fused);
+/* fuse_pipeline (Sarek_fusion.ml:570-598: greedy, left to right, first candidate array) with the fusion form of
+ * each step chosen by `kind`; with SB200_FUSE_GUARDED a chain of benchmark-form kernels collapses into one kernel. */
+SB200_API int sb200_ir_fuse_pipeline_as(const char *const *kernels, int count, int kind, char *out, int outlen,
+                                        char *eliminated, int elimlen);
 
 /* ---- direct operators (what a recognised kernel launch dispatches to) ---
  * D[M x N] = act(alpha * A[M x K] . B[K x N] + beta * C[M x N] + bias[N]),

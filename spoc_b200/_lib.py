@@ -76,6 +76,7 @@ SIGNATURES = {
     "sb200_ir_can_fuse": ([C.c_char_p, C.c_char_p, C.c_char_p, p(i32)], i32),
     "sb200_ir_fuse": ([C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, i32], i32),
     "sb200_ir_fuse_pipeline": ([p(C.c_char_p), i32, C.c_char_p, i32, C.c_char_p, i32], i32),
+    "sb200_ir_fuse_pipeline_as": ([p(C.c_char_p), i32, i32, C.c_char_p, i32, C.c_char_p, i32], i32),
     "sb200_ir_should_fuse": ([C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, i32, C.c_char_p, i32], i32),
     "sb200_ir_auto_fuse_pipeline": ([p(C.c_char_p), i32, C.c_char_p, i32, C.c_char_p, i32, C.c_char_p, i32], i32),
     "sb200_ir_analyze": ([C.c_char_p, C.c_char_p, i32], i32),

@@ -877,6 +877,50 @@ int ir_fuse_as(const std::string& producer, const std::string& consumer, const s
   return SB200_OK;
 }
 
+// fuse_pipeline with a chosen fusion form per step (greedy, left to right, first candidate array as the
+// reference's fuse_pipeline does, :570-598); kind as in ir_fuse_as.  With kind 5 a chain of guarded benchmark-form
+// kernels collapses into one kernel.
+int ir_fuse_pipeline_as(const std::vector<std::string>& kernels, int kind, std::string* out, std::vector<std::string>* eliminated,
+                        std::string* err) {
+  if (kernels.empty()) {
+    *err = "fuse_pipeline: empty pipeline";
+    return SB200_ERR_INVALID_VALUE;
+  }
+  if (kind < 0 || kind > 5) {
+    *err = "unknown fusion kind";
+    return SB200_ERR_INVALID_VALUE;
+  }
+  std::vector<Kernel> ks(kernels.size());
+  for (size_t i = 0; i < kernels.size(); ++i)
+    if (!load_kernel(kernels[i], &ks[i], err)) return SB200_ERR_PARSE;
+  Kernel cur = ks[0];
+  eliminated->clear();
+  for (size_t i = 1; i < ks.size(); ++i) {
+    std::vector<std::string> c = candidates(analyze(cur), analyze(ks[i]));
+    Kernel fused;
+    bool ok = false;
+    if (!c.empty()) {
+      std::string why;
+      switch (kind) {
+        case 0: ok = can_fuse_k(cur, ks[i], c[0]); if (ok) fused = fuse_k(cur, ks[i], c[0]); break;
+        case 1: ok = can_fuse_reduction_k(cur, ks[i], c[0]); if (ok) fused = fuse_reduction_k(cur, ks[i], c[0]); break;
+        case 2: ok = can_fuse_stencil_k(cur, ks[i], c[0]); if (ok) fused = fuse_stencil_k(cur, ks[i], c[0]); break;
+        case 3: ok = try_fuse_k(cur, ks[i], c[0], false, &fused); break;
+        case 4: ok = try_fuse_k(cur, ks[i], c[0], true, &fused); break;
+        case 5: ok = fuse_guarded_k(cur, ks[i], c[0], &fused, &why); break;
+      }
+    }
+    if (ok) {
+      cur = fused;
+      eliminated->insert(eliminated->begin(), c[0]);
+    } else {
+      cur = ks[i];
+    }
+  }
+  *out = sx_print(cur.root);
+  return SB200_OK;
+}
+
 // One line per array: "read|write NAME one_to_one|stencil[o1,o2]|gather|unknown", then "barriers yes|no".
 int ir_analyze(const std::string& kernel, std::string* report, std::string* err) {
   Kernel k;

@@ -131,4 +131,7 @@ int ir_can_fuse_as(const std::string& producer, const std::string& consumer, con
 int ir_fuse_as(const std::string& producer, const std::string& consumer, const std::string& inter, int kind, std::string* out,
                bool* fused, std::string* err);
 
+int ir_fuse_pipeline_as(const std::vector<std::string>& kernels, int kind, std::string* out, std::vector<std::string>* eliminated,
+                        std::string* err);
+
 }  // namespace sb200

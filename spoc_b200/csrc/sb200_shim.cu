@@ -1306,6 +1306,24 @@ int sb200_ir_fuse_pipeline(const char* const* kernels, int count, char* out, int
   return copy_out(text, out, outlen);
 }
 
+int sb200_ir_fuse_pipeline_as(const char* const* kernels, int count, int kind, char* out, int outlen, char* eliminated,
+                              int elimlen) {
+  if (!kernels || count <= 0) return fail(SB200_ERR_INVALID_VALUE, "empty kernel list");
+  std::vector<std::string> ks;
+  for (int i = 0; i < count; ++i) {
+    if (!kernels[i]) return fail(SB200_ERR_INVALID_VALUE, "null kernel text");
+    ks.push_back(kernels[i]);
+  }
+  std::string text, err;
+  std::vector<std::string> elim;
+  int rc = ir_fuse_pipeline_as(ks, kind, &text, &elim, &err);
+  if (rc) return fail(rc, "%s", err.c_str());
+  std::string joined;
+  for (size_t i = 0; i < elim.size(); ++i) joined += (i ? "," : "") + elim[i];
+  if (eliminated && elimlen > 0 && (rc = copy_out(joined, eliminated, elimlen))) return rc;
+  return copy_out(text, out, outlen);
+}
+
 int sb200_ir_should_fuse(const char* producer, const char* consumer, const char* intermediate, char* decision, int declen,
                          char* reason, int reasonlen) {
   if (!producer || !consumer || !intermediate) return fail(SB200_ERR_INVALID_VALUE, "null argument");

@@ -118,3 +118,12 @@ def fuse_guarded(producer: str, consumer: str, intermediate: str):
 
 def why_not_fused() -> str:
     return L.load().sb200_last_error_string().decode()
+
+
+def fuse_pipeline_as(kernels: Sequence[str], kind: int) -> tuple[str, list[str]]:
+    """fuse_pipeline with the fusion form of each step chosen by ``kind`` (PLAIN ... GUARDED)."""
+    arr, n = _arr(kernels)
+    out, elim = C.create_string_buffer(_BUF), C.create_string_buffer(4096)
+    _check(L.load().sb200_ir_fuse_pipeline_as(arr, n, kind, out, _BUF, elim, 4096))
+    e = elim.value.decode()
+    return out.value.decode(), (e.split(",") if e else [])

@@ -249,3 +249,21 @@ def test_guarded_fusion_refuses_with_a_reason(case, needle):
     assert not F.can_fuse_guarded(prod, cons, "a")
     assert needle in F.why_not_fused()
     assert F.fuse_guarded(prod, cons, "a") is None
+
+
+def test_pipeline_of_guarded_benchmark_kernels_collapses_into_one_kernel():
+    b = S.Builder()
+    p = b.params([("vec", "e", "f32"), ("vec", "d", "f32"), ("scalar", "n", "i32")])
+    body = b.let("i", "i32", b.intr("global_thread_id"), lambda: (
+        "sif", b.binop("lt", b.evar("i"), b.evar("n")),
+        ("assign", ("elem", "e", b.evar("i")), b.binop("mul", b.read("d", b.evar("i")), b.c_f32(0.5)))))
+    third = S.sx(("kernel", "halve", p, ("body", body)))
+    chain = [S.stream_triad_ir("triad"), S.square_add_guarded_ir(), third]
+    fused, eliminated = F.fuse_pipeline_as(chain, F.GUARDED)
+    assert fused.startswith("(kernel halve_fused ") and eliminated == ["d", "a"]       # newest first, as the reference lists them
+    assert "(read a" not in fused and "(read d" not in fused
+    # the reference's own pipeline fuses nothing here: it hands back the last kernel, still reading d (and, since
+    # can_fuse holds for a single guarded read, lists d as eliminated all the same — Sarek_fusion.ml:590-593)
+    plain, eliminated = F.fuse_pipeline(chain)
+    assert plain.startswith("(kernel halve ") and "(read d" in plain and eliminated == ["d"]
+    assert F.fuse_pipeline_as(chain, F.PLAIN) == (plain, eliminated)
