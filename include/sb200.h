@@ -178,6 +178,8 @@ SB200_API int sb200_ir_analyze(const char *kernel, char *out, int outlen);
  *                         `tid` have different ids, :38).  Index lets are inlined and the guards peeled; the
  *                         producer must be unguarded or guarded exactly as the consumer (parameters compared by
  *                         name), the consumer must read the intermediate only at the producer's store index.
+ *                         Replaced reads of a float32 intermediate are wrapped in (intrinsic (B200) stored_f32 e), "e as
+ *                         the vector would have held it", so the fused kernel rounds where the unfused pair stored.
  * For the TRY and GUARDED kinds *fused is 0 when nothing was fused (out is then empty); for GUARDED
  * sb200_last_error_string then says which condition failed. */
 #define SB200_FUSE_PLAIN 0

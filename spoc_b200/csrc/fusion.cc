@@ -548,7 +548,9 @@ Kernel fuse_stencil_k(const Kernel& prod, const Kernel& cons, const std::string&
 //     element the producer would not have written;
 //   * a producer expression built from parameters only.
 // The result is the consumer's guarded body with the reads replaced, named <consumer>_fused,
-// parameters merged as fuse does.
+// parameters merged as fuse does.  Each replaced read of a float32 intermediate is wrapped in
+// (intrinsic (B200) stored_f32 e): "e as the vector would have held it", so the fused kernel rounds
+// where the unfused pair did.
 using VarEnv = std::map<std::string, Sx>;  // variable id -> defining expression (already inlined)
 
 Sx inline_vars(const Sx& e, const VarEnv& env) {
@@ -706,6 +708,11 @@ bool fuse_guarded_k(const Kernel& prod, const Kernel& cons, const std::string& i
   }
   Sx repl;
   if (!rebind_params(*stored, prod, cons, &repl, why)) return false;
+  // The unfused kernels round the intermediate to float32 when they store it; the mark keeps that rounding
+  // in the fused kernel (generated code evaluates in double), so fused and unfused runs agree bit for bit.
+  const Sx* ip = find_param(prod, inter);
+  if (ip && ip->size() >= 4 && (*ip)[3].atom && (*ip)[3].s == "f32")
+    repl = Sx::L({Sx::A("intrinsic"), Sx::L({Sx::A("B200")}), Sx::A("stored_f32"), repl});
   Sx body = subst_stmt(nc.inner, inter, *widx, repl);
   for (size_t i = nc.guards.size(); i-- > 0;) body = Sx::L({Sx::A("sif"), nc.guards[i], body});
   out->root = Sx::L({Sx::A("kernel"), Sx::A(cons.name() + "_fused"), merged_params(prod, cons, inter),

@@ -321,6 +321,15 @@ std::vector<const Sx*> seq_items(const Sx& s) {
 
 // ------------------------------------------------------------------- maps
 
+Sx strip_stored_marks(const Sx& e) {
+  if (e.atom) return e;
+  if (e.is("intrinsic") && e.size() == 4 && e[2].atom && e[2].s == "stored_f32") return strip_stored_marks(e[3]);
+  Sx o;
+  o.kids.reserve(e.kids.size());
+  for (const Sx& k : e.kids) o.kids.push_back(strip_stored_marks(k));
+  return o;
+}
+
 // Substitute reads of arrays written earlier in the same straight-line body.
 Sx subst_reads(const Sx& e, const std::map<std::string, Sx>& written, const Sx& idx) {
   if (e.atom) return e;
@@ -416,8 +425,11 @@ bool match_map(Ctx& cx, const Sx& body) {
       return false;
     }
   }
-  // classify the final store (and the optional kept intermediate)
-  const Sx& rhs = stores.back().second;
+  // classify the final store (and the optional kept intermediate).  The ahead-of-time operators round an
+  // eliminated intermediate to float32 themselves (one fused multiply-add per former kernel), so the
+  // stored_f32 marks of the backend's guarded fusion are dropped for the classification.
+  const Sx rhs_unmarked = strip_stored_marks(stores.back().second);
+  const Sx& rhs = rhs_unmarked;
   mp.out0 = stores.back().first;
   Triad t;
   bool ok = false;
@@ -620,6 +632,14 @@ bool gen_float(GenCtx& g, const Sx& e, std::string* out) {
       std::string a;
       if (!gen_float(g, e[3], &a)) return false;
       *out = std::string(un.at(name)) + "(" + a + ")";
+      return true;
+    }
+    if (name == "stored_f32" && e.size() == 4) {
+      // the value as a float32 vector would have held it: the backend's guarded fusion marks the store it
+      // eliminated this way, so that the fused kernel rounds where the unfused kernels did
+      std::string a;
+      if (!gen_float(g, e[3], &a)) return false;
+      *out = "((double)(float)(" + a + "))";
       return true;
     }
     if (name == "rsqrt" && e.size() == 4) {

@@ -255,6 +255,51 @@ def test_guarded_benchmark_kernels_fused_by_the_backend(backend, device, oracle,
         v.free()
 
 
+@pytest.mark.parametrize("n", [5, 1000, 70001])
+def test_pipeline_of_three_guarded_kernels_fused_matches_the_unfused_sequence_bit_for_bit(backend, device, n):
+    """a = b + s*c ; d = a*a + b ; e = d*0.5 + a... as three guarded kernels and as the one generated kernel the
+    backend's guarded pipeline fusion builds: the eliminated stores are marked, so the fused kernel rounds where the
+    unfused kernels stored, and both agree with Native's result of the sequence to the last bit."""
+    from spoc_b200 import fusion as F
+    S = sarek_ir
+    bld = S.Builder()
+    p = bld.params([("vec", "e", "f32"), ("vec", "d", "f32"), ("vec", "c", "f32"), ("scalar", "n", "i32")])
+    body = bld.let("i", "i32", bld.intr("global_thread_id"), lambda: (
+        "sif", bld.binop("lt", bld.evar("i"), bld.evar("n")),
+        ("assign", ("elem", "e", bld.evar("i")),
+         bld.binop("sub", bld.binop("div", bld.read("d", bld.evar("i")), bld.c_f32(3.0)), bld.read("c", bld.evar("i"))))))
+    third = S.sx(("kernel", "third", p, ("body", body)))
+    b, c = _inputs(n, seed=13)
+    grid = dims1d((n + 255) // 256)
+    va, vd, ve = (Vector.create(backend, n) for _ in range(3))
+    vb, vc = Vector(backend, b.copy()), Vector(backend, c.copy())
+    run_vectors(backend, device=device, ir=S.stream_triad_ir("triad"), args=[va, vb, vc, ("float32", 3.0), ("int32", n)],
+                block=dims1d(256), grid=grid)
+    run_vectors(backend, device=device, ir=S.square_add_guarded_ir(),
+                args=[vd, va, vb, ("int32", n)], block=dims1d(256), grid=grid)
+    run_vectors(backend, device=device, ir=third, args=[ve, vd, vc, ("int32", n)], block=dims1d(256), grid=grid, kernel_name="third")
+    unfused = ve.to_array().copy()
+    fused_ir, eliminated = F.fuse_pipeline_as([S.stream_triad_ir("triad"), S.square_add_guarded_ir(), third], F.GUARDED)
+    assert eliminated == ["d", "a"] and fused_ir.count("stored_f32") == 3      # a twice (read twice), d once
+    # parameters of the fused kernel: third's without d, then the new ones of the kernel in front of it
+    names = [q.split()[1] for q in fused_ir.split("(params ")[1].split("(body")[0].split("(")[1:]]
+    assert names == ["e", "c", "n", "b", "scalar"]
+    vf = Vector.create(backend, n)
+    before = backend.launch_count()
+    run_vectors(backend, device=device, ir=fused_ir, args=[vf, vc, ("int32", n), vb, ("float32", 3.0)],
+                block=dims1d(256), grid=grid, kernel_name="third_fused")
+    assert backend.launch_count() - before <= 3
+    fused = vf.to_array()
+    # Native's result of the three kernels in sequence: double arithmetic, one rounding per store
+    a64 = (b.astype(np.float64) + c.astype(np.float64) * 3.0).astype(np.float32).astype(np.float64)
+    d64 = (a64 * a64 + b.astype(np.float64)).astype(np.float32).astype(np.float64)
+    ref = (d64 / 3.0 - c.astype(np.float64)).astype(np.float32)
+    assert np.array_equal(fused, ref)
+    assert O.ulp_distance(unfused, ref).max() <= 1     # the unfused run goes through the fused-multiply-add operators
+    for v in (va, vd, ve, vb, vc, vf):
+        v.free()
+
+
 @pytest.mark.parametrize("kind", ["dot", "sum"])
 @pytest.mark.parametrize("n,block", [(1000, 256), (256 * 40, 256), (100003, 256), (5000, 64), (70000, 1024)])
 def test_block_tree_reduction_is_bit_exact(backend, device, oracle, kind, n, block):
