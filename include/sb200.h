@@ -253,7 +253,7 @@ SB200_API int sb200_ipc_close(int dev, uint64_t dptr);
  * overlap with asynchronous copies: 15.9 ms at 8192^3.  Contiguous pageable operands
  * (a Bigarray) are moved block by block by the staged copier — host threads through
  * pinned slots, copy-out on a thread of its own — beside the GEMM of the block
- * before: 29.8 ms at 8192^3, against 93.6 ms with plain pageable copies; strided
+ * before: 27.0 ms at 8192^3, against 93.6 ms with plain pageable copies; strided
  * pageable operands take the plain copies.  Replaces the reference's sequence
  * Transfer.to_device of every argument, launch, Transfer.to_cpu of the result
  * (sarek/core/Transfer.ml:229-322, sarek/sarek/Execute.ml:520-543) with one call

@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <condition_variable>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -31,12 +32,33 @@ struct Lane {
   cudaEvent_t ev[2] = {nullptr, nullptr};
 };
 
+struct Job;
+
+// Lanes of one device and direction.  Lane 0 is driven by the thread that calls the copy; lanes 1.. have a
+// worker thread each, started with the lane and parked on a condition variable between copies (starting
+// threads per copy cost as much as the copy itself for 16-64 MiB).  Pools are never destroyed: their
+// parked workers end with the process.
 struct Pool {
   std::mutex mu;  // one staged transfer per device and direction at a time
   int lanes = 0;
   Lane lane[kMaxLanes];
+  std::mutex wm;
+  std::condition_variable wake, done;
+  unsigned long generation = 0;
+  Job* job = nullptr;
+  bool job_to_device = true;
+  int job_workers = 0;  // lanes taking part in the current copy, lane 0 included
+  int running = 0;      // worker threads still busy with it
 };
-Pool g_pool[kMaxDevices][2];  // [device][0 = to the device, 1 = to the host]: the two directions can run side by side
+Pool* g_pool[kMaxDevices][2];  // [device][0 = to the device, 1 = to the host]: the two directions can run side by side
+std::mutex g_pool_mu;
+
+Pool* pool_for(int dev, bool to_device) {
+  std::lock_guard<std::mutex> lock(g_pool_mu);
+  Pool*& p = g_pool[dev][to_device ? 0 : 1];
+  if (!p) p = new Pool();
+  return p;
+}
 
 int lane_count() {
   static int n = [] {
@@ -51,6 +73,30 @@ int lane_count() {
   return n;
 }
 
+void to_device_worker(Job* j, Lane* l);
+void to_host_worker(Job* j, Lane* l);
+
+void worker_main(Pool* p, int lane_index) {
+  unsigned long seen = 0;
+  for (;;) {
+    Job* job;
+    bool to_device;
+    {
+      std::unique_lock<std::mutex> lk(p->wm);
+      p->wake.wait(lk, [&] { return p->generation != seen; });
+      seen = p->generation;
+      if (lane_index >= p->job_workers) continue;  // a small copy: this lane sits it out
+      job = p->job;
+      to_device = p->job_to_device;
+    }
+    (to_device ? to_device_worker : to_host_worker)(job, &p->lane[lane_index]);
+    {
+      std::lock_guard<std::mutex> lk(p->wm);
+      if (--p->running == 0) p->done.notify_one();
+    }
+  }
+}
+
 cudaError_t ensure_pool(Pool& p) {
   const int want = lane_count();
   for (; p.lanes < want; ++p.lanes) {
@@ -61,6 +107,7 @@ cudaError_t ensure_pool(Pool& p) {
       if (e == cudaSuccess) e = cudaEventCreateWithFlags(&l.ev[s], cudaEventDisableTiming);
     }
     if (e != cudaSuccess) return e;  // the lanes built so far stay usable
+    if (p.lanes > 0) std::thread(worker_main, &p, p.lanes).detach();
   }
   return cudaSuccess;
 }
@@ -133,7 +180,7 @@ void to_host_worker(Job* j, Lane* l) {
 
 int run(int dev, void* dev_ptr, void* host_ptr, size_t bytes, bool to_device, bool after_device_work) {
   if (dev < 0 || dev >= kMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
-  Pool& p = g_pool[dev][to_device ? 0 : 1];
+  Pool& p = *pool_for(dev, to_device);
   std::lock_guard<std::mutex> lock(p.mu);
   cudaError_t e = ensure_pool(p);
   if (p.lanes == 0) return static_cast<int>(e);
@@ -157,11 +204,21 @@ int run(int dev, void* dev_ptr, void* host_ptr, size_t bytes, bool to_device, bo
   }
   j.nchunks = (bytes + j.chunk - 1) / j.chunk;
   const int workers = static_cast<int>(j.nchunks < static_cast<size_t>(p.lanes) ? j.nchunks : p.lanes);
-  std::vector<std::thread> threads;
-  threads.reserve(workers);
-  for (int w = 1; w < workers; ++w) threads.emplace_back(to_device ? to_device_worker : to_host_worker, &j, &p.lane[w]);
+  {
+    std::lock_guard<std::mutex> lk(p.wm);
+    p.job = &j;
+    p.job_to_device = to_device;
+    p.job_workers = workers;
+    p.running = workers - 1;
+    ++p.generation;
+  }
+  p.wake.notify_all();
   (to_device ? to_device_worker : to_host_worker)(&j, &p.lane[0]);  // the calling thread is lane 0
-  for (std::thread& t : threads) t.join();
+  {
+    std::unique_lock<std::mutex> lk(p.wm);
+    p.done.wait(lk, [&] { return p.running == 0; });
+    p.job = nullptr;
+  }
   return j.error.load();
 }
 
