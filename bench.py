@@ -406,6 +406,24 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     ms5, _, _ = timed(e2e_pageable_step, 3, 1)
     e2e["pageable_host_buffers"] = {"value": world * flops_step / (ms5 / 3 * 1e-3) / 1e12, "unit": "TFLOP/s",
                                     "ms_per_step": ms5 / 3}
+    # the plugin path itself: Execute.run_vectors on the epilogue kernel's IR with host-resident vectors, i.e.
+    # Transfer.to_device of every argument, the launch, Transfer.to_cpu of the result, one after the other
+    from spoc_b200 import Vector, run_vectors, dims1d, sarek_ir
+    epi_ir = sarek_ir.matmul_naive_ir(epilogue=dict(alpha=1.5, beta=0.5, c="c", bias="bias", relu=True))
+    vecs = [Vector(backend, t.numpy()) for t in (pA, pB, pC)] + [Vector(backend, hbias.numpy().copy()), Vector(backend, pD.numpy())]
+
+    def plugin_step():
+        for v in vecs[:4]:
+            v.location = Vector.CPU          # the host copy is the valid one again: the next launch re-uploads it
+        run_vectors(backend, device=dev, ir=epi_ir, args=vecs + [("int32", M), ("int32", N), ("int32", K)],
+                    block=dims1d(256), grid=dims1d((M * N + 255) // 256))
+        vecs[4].to_array()
+
+    ms6, _, _ = timed(plugin_step, 3, 1)
+    e2e["plugin_run_vectors"] = {"value": world * flops_step / (ms6 / 3 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms6 / 3,
+                                 "note": "run_vectors on the kernel's IR, pageable host vectors, synchronous transfers as in the reference"}
+    for v in vecs:
+        v.free()
     del hA, hB, hC, hD, pA, pB, pC, pD
 
     # ---- fused-map chain (HBM bound) ---------------------------------------------------------
