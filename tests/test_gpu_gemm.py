@@ -261,6 +261,55 @@ def test_gemm_and_map_calls_can_be_captured_in_a_cuda_graph(backend, device, mod
     assert lib.sb200_device_synchronize(device.id) == 0
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_randomised_shapes_strides_tiles_and_epilogues(backend, device, seed):
+    """Eighty seeded draws per seed of sizes around the tile edges, aligned and unaligned operands and strides (direct
+    and panel paths), forced and automatic tile widths, both modes and every epilogue combination."""
+    lib = L.load()
+    rng = np.random.default_rng(seed)
+    try:
+        for case in range(80):
+            M = int(rng.choice([1, 2, 31, 64, 100, 128, 129, 200, 256, 257, 300, 511, 513, 700, 1000]))
+            N = int(rng.choice([1, 3, 32, 33, 63, 64, 65, 100, 127, 128, 129, 255, 256, 257, 400, 513, 900]))
+            K = int(rng.choice([1, 2, 7, 8, 31, 32, 33, 64, 100, 127, 128, 200, 255, 256, 300, 513, 1000]))
+            aligned = rng.random() < 0.7
+            lda = K + (int(rng.integers(0, 3)) * 4 if aligned else int(rng.integers(1, 4)))
+            ldb = N + (int(rng.integers(0, 3)) * 4 if aligned else int(rng.integers(1, 4)))
+            if aligned:
+                lda, ldb = (lda + 3) // 4 * 4, (ldb + 3) // 4 * 4
+            ldd, ldc = N + int(rng.integers(0, 9)), N + int(rng.integers(0, 9))
+            mode = int(rng.choice(MODES))
+            tile = int(rng.choice([0, 0, 64, 128, 256]))
+            use_c, use_bias, act = rng.random() < 0.6, rng.random() < 0.6, int(rng.random() < 0.5)
+            alpha, beta = (1.5, 0.5) if rng.random() < 0.5 else (1.0, 0.25)
+            tag = 1000 * seed + case
+            a, bm, c = O.fill(M * lda, tag, 1), O.fill(K * ldb, tag, 2), O.fill(M * ldc, tag, 3)
+            bias = O.fill(N, tag, 4, kind=1)
+            off = 0 if aligned else int(rng.integers(0, 4))
+            A, B = dev_from(backend, device, a, offset=off), dev_from(backend, device, bm, offset=off)
+            Cd = dev_from(backend, device, c) if use_c else None
+            Bi = dev_from(backend, device, bias) if use_bias else None
+            D = Dev(backend, device, M * ldd)
+            what = dict(M=M, N=N, K=K, lda=lda, ldb=ldb, ldd=ldd, ldc=ldc, mode=mode, tile=tile, off=off, c=use_c, bias=use_bias, act=act)
+            try:
+                assert lib.sb200_set_gemm_tile_n(tile) == 0
+                gemm(backend, device, mode, M, N, K, A, B, D, alpha=alpha, C_=Cd, beta=beta if use_c else 0.0, bias=Bi, act=act,
+                     lda=lda, ldb=ldb, ldd=ldd, ldc=ldc)
+                got = D.download().reshape(M, ldd)
+                a2 = np.ascontiguousarray(a.reshape(M, lda)[:, :K]).ravel()
+                b2 = np.ascontiguousarray(bm.reshape(K, ldb)[:, :N]).ravel()
+                c2 = np.ascontiguousarray(c.reshape(M, ldc)[:, :N]).ravel()
+                ref = O.gemm(a2, b2, M, N, K, alpha, beta if use_c else 0.0, c2 if use_c else None, bias if use_bias else None, act)
+                assert O.gemm_rel_error(got[:, :N], ref) <= tol(mode, K) * 1.5 * math.sqrt(2), what
+                assert np.all(got[:, N:] == CANARY), what
+            finally:
+                for x in (A, B, Cd, Bi, D):
+                    if x is not None:
+                        x.free()
+    finally:
+        lib.sb200_set_gemm_tile_n(0)
+
+
 def test_leading_dimensions_and_submatrices(backend, device):
     M, N, K, lda, ldb, ldd = 70, 90, 50, 64, 100, 128
     a, b = O.fill(M * lda, 3, 1), O.fill(K * ldb, 3, 2)
