@@ -300,6 +300,70 @@ def test_pipeline_of_three_guarded_kernels_fused_matches_the_unfused_sequence_bi
         v.free()
 
 
+def _random_expression(rng, bld, depth):
+    """A random float32 expression over x, y, z and the scalar s, with the function that evaluates it in float64."""
+    f32 = ("Float32",)
+    if depth == 0 or rng.random() < 0.15:
+        k = int(rng.integers(0, 3))
+        if k == 0:
+            name = "xyz"[int(rng.integers(0, 3))]
+            return bld.read(name, bld.evar("i")), (lambda env, name=name: env[name])
+        if k == 1:
+            v = round(float(rng.uniform(-2, 2)), 3)
+            return bld.c_f32(v), (lambda env, v=v: np.float64(v))
+        return bld.evar("s"), (lambda env: env["s"])
+    op = str(rng.choice(["add", "sub", "mul", "div", "neg", "if", "sqrtabs", "fabs"]))
+    sub = lambda: _random_expression(rng, bld, depth - 1)
+    if op in ("add", "sub", "mul"):
+        (ea, fa), (eb, fb) = sub(), sub()
+        fn = {"add": np.add, "sub": np.subtract, "mul": np.multiply}[op]
+        return bld.binop(op, ea, eb), (lambda env: fn(fa(env), fb(env)))
+    if op == "div":
+        (ea, fa), (eb, fb) = sub(), sub()
+        return (bld.binop("div", ea, bld.binop("add", ("intrinsic", f32, "abs_float", eb), bld.c_f32(1.5))),
+                lambda env: fa(env) / (np.abs(fb(env)) + 1.5))
+    if op == "neg":
+        ea, fa = sub()
+        return ("unop", "neg", ea), (lambda env: -fa(env))
+    if op == "fabs":
+        ea, fa = sub()
+        return ("intrinsic", f32, "abs_float", ea), (lambda env: np.abs(fa(env)))
+    if op == "sqrtabs":
+        ea, fa = sub()
+        return ("intrinsic", f32, "sqrt", ("intrinsic", f32, "abs_float", ea)), (lambda env: np.sqrt(np.abs(fa(env))))
+    (ec, fc), (ea, fa), (eb, fb) = sub(), sub(), sub()
+    return ("if", bld.binop("gt", ec, bld.c_f32(0.25)), ea, eb), (lambda env: np.where(fc(env) > 0.25, fa(env), fb(env)))
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_random_expressions_on_the_generated_path_are_bit_exact(backend, device, seed):
+    """Twelve seeded random expression trees per seed (+ - * / neg abs sqrt if, constants, a scalar parameter), guarded,
+    against the same tree evaluated in float64 and rounded once — the Native backend's rule."""
+    rng = np.random.default_rng(seed)
+    for case in range(12):
+        n = int(rng.choice([1, 7, 255, 1000, 4099, 70001]))
+        bld = sarek_ir.Builder()
+        p = bld.params([("vec", "o", "f32"), ("vec", "x", "f32"), ("vec", "y", "f32"), ("vec", "z", "f32"),
+                        ("scalar", "s", "f32"), ("scalar", "n", "i32")])
+        made = {}
+
+        def body():
+            e, made["f"] = _random_expression(rng, bld, int(rng.integers(1, 5)))
+            return ("sif", bld.binop("lt", bld.evar("i"), bld.evar("n")), ("assign", ("elem", "o", bld.evar("i")), e))
+
+        ir = sarek_ir.sx(("kernel", "rnd", p, ("body", bld.let("i", "i32", bld.intr("global_thread_id"), body))))
+        x, y, z = O.fill(n, 100 * seed + case, 1), O.fill(n, 100 * seed + case, 2), O.fill(n, 100 * seed + case, 3)
+        sval = float(np.float32(rng.uniform(-3, 3)))
+        vo, vx, vy, vz = Vector.create(backend, n), Vector(backend, x.copy()), Vector(backend, y.copy()), Vector(backend, z.copy())
+        run_vectors(backend, device=device, ir=ir, args=[vo, vx, vy, vz, ("float32", sval), ("int32", n)], block=dims1d(256),
+                    grid=dims1d((n + 255) // 256), kernel_name="rnd")
+        env = {"x": x.astype(np.float64), "y": y.astype(np.float64), "z": z.astype(np.float64), "s": np.float64(sval)}
+        ref = np.broadcast_to(np.asarray(made["f"](env), dtype=np.float64), (n,)).astype(np.float32)
+        assert np.array_equal(vo.to_array(), ref), ir
+        for v in (vo, vx, vy, vz):
+            v.free()
+
+
 @pytest.mark.parametrize("kind", ["dot", "sum"])
 @pytest.mark.parametrize("n,block", [(1000, 256), (256 * 40, 256), (100003, 256), (5000, 64), (70000, 1024)])
 def test_block_tree_reduction_is_bit_exact(backend, device, oracle, kind, n, block):
