@@ -1358,6 +1358,86 @@ bool has_unsupported_stmt(const Sx& s, std::string* what) {
   return false;
 }
 
+// ---------------------------------------------------------------- grammar check
+// Every form the grammar in ir.hpp names must have the shape given there: the recogniser and the fusion pass
+// index into these lists without further checks.  Forms with a head the grammar does not know pass through
+// (their children are not inspected): the recogniser simply does not match them.
+bool atom_at(const Sx& e, size_t i) { return i < e.size() && e[i].atom; }
+
+bool bad_form(const Sx& e, std::string* err) {
+  std::string t = sx_print(e);
+  if (t.size() > 120) t = t.substr(0, 117) + "...";
+  *err = "malformed IR form: " + t;
+  return false;
+}
+
+bool validate_expr(const Sx& e, std::string* err);
+
+bool validate_exprs(const Sx& e, size_t from, std::string* err) {
+  for (size_t i = from; i < e.size(); ++i)
+    if (!validate_expr(e[i], err)) return false;
+  return true;
+}
+
+bool validate_expr(const Sx& e, std::string* err) {
+  if (e.atom || e.kids.empty() || !e[0].atom) return bad_form(e, err);
+  const std::string& h = e[0].s;
+  if (h == "const") return (e.size() == 3 && atom_at(e, 2)) || bad_form(e, err);
+  if (h == "evar") return (e.size() == 3 && atom_at(e, 1) && atom_at(e, 2)) || bad_form(e, err);
+  if (h == "binop") return (e.size() == 4 && atom_at(e, 1) && validate_exprs(e, 2, err)) || (err->empty() ? bad_form(e, err) : false);
+  if (h == "unop") return (e.size() == 3 && atom_at(e, 1) && validate_exprs(e, 2, err)) || (err->empty() ? bad_form(e, err) : false);
+  if (h == "read") return (e.size() == 3 && atom_at(e, 1) && validate_exprs(e, 2, err)) || (err->empty() ? bad_form(e, err) : false);
+  if (h == "intrinsic") {
+    if (e.size() < 3 || e[1].atom || !atom_at(e, 2)) return bad_form(e, err);
+    for (const Sx& k : e[1].kids)
+      if (!k.atom) return bad_form(e, err);
+    return validate_exprs(e, 3, err);
+  }
+  if (h == "cast") return (e.size() == 3 && validate_exprs(e, 2, err)) || (err->empty() ? bad_form(e, err) : false);
+  if (h == "if") return (e.size() == 4 && validate_exprs(e, 1, err)) || (err->empty() ? bad_form(e, err) : false);
+  if (h == "arraylen") return (e.size() == 2 && atom_at(e, 1)) || bad_form(e, err);
+  if (h == "arraycreate")
+    return (e.size() == 4 && atom_at(e, 3) && validate_expr(e[2], err)) || (err->empty() ? bad_form(e, err) : false);
+  return true;  // a form this grammar does not know
+}
+
+bool validate_stmt(const Sx& s, std::string* err) {
+  if (s.atom || s.kids.empty() || !s[0].atom) return bad_form(s, err);
+  const std::string& h = s[0].s;
+  auto fail_or = [&](bool ok) { return ok || (err->empty() ? bad_form(s, err) : false); };
+  if (h == "assign") {
+    if (s.size() != 3 || s[1].atom) return bad_form(s, err);
+    const Sx& lv = s[1];
+    if (lv.is("lvar")) {
+      if (lv.size() != 3 || !atom_at(lv, 1) || !atom_at(lv, 2)) return bad_form(s, err);
+    } else if (lv.is("elem")) {
+      if (lv.size() != 3 || !atom_at(lv, 1) || !validate_expr(lv[2], err)) return err->empty() ? bad_form(s, err) : false;
+    } else {
+      return bad_form(s, err);
+    }
+    return validate_expr(s[2], err);
+  }
+  if (h == "seq") {
+    for (size_t i = 1; i < s.size(); ++i)
+      if (!validate_stmt(s[i], err)) return false;
+    return true;
+  }
+  if (h == "sif")
+    return fail_or((s.size() == 3 || s.size() == 4) && validate_expr(s[1], err) && validate_stmt(s[2], err) &&
+                   (s.size() == 3 || validate_stmt(s[3], err)));
+  if (h == "for")
+    return fail_or(s.size() == 7 && atom_at(s, 1) && atom_at(s, 2) && atom_at(s, 5) && (s[5].s == "upto" || s[5].s == "downto") &&
+                   validate_expr(s[3], err) && validate_expr(s[4], err) && validate_stmt(s[6], err));
+  if (h == "let" || h == "letmut")
+    return fail_or(s.size() == 6 && atom_at(s, 1) && atom_at(s, 2) && validate_expr(s[4], err) && validate_stmt(s[5], err));
+  if (h == "while") return fail_or(s.size() == 3 && validate_expr(s[1], err) && validate_stmt(s[2], err));
+  if (h == "block") return fail_or(s.size() == 2 && validate_stmt(s[1], err));
+  if (h == "pragma") return fail_or(s.size() == 3 && validate_stmt(s[2], err));
+  if (h == "barrier" || h == "warpbarrier" || h == "memfence" || h == "empty") return fail_or(s.size() == 1);
+  if (h == "return" || h == "expr") return fail_or(s.size() == 2 && validate_expr(s[1], err));
+  return true;  // a form this grammar does not know
+}
+
 }  // namespace
 
 bool parse_kernel_form(const std::string& text, Sx* root, KernelPlan* plan, const Sx** body, std::string* err) {
@@ -1384,7 +1464,8 @@ bool parse_kernel_form(const std::string& text, Sx* root, KernelPlan* plan, cons
     plan->params.push_back(pi);
   }
   *body = &(*root)[3][1];
-  return true;
+  err->clear();
+  return validate_stmt(**body, err);
 }
 
 int ir_compile(const std::string& text, KernelPlan* plan, std::string* err) {
