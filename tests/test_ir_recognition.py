@@ -165,3 +165,33 @@ def test_mode_setting():
     assert b.get_mode() == L.MODE_3XTF32
     with pytest.raises(BackendError):
         b.set_mode(2)
+
+
+@pytest.mark.parametrize("find,replace", [
+    ("(elem c (evar tid 5))", "(elem (evar tid 5))"),            # array name missing
+    ("(read a (evar tid 5))", "(read a)"),                       # index missing
+    ("(binop add ", "(binop add add "),                          # an atom where an expression belongs
+    ("(evar n 4)", "(evar n)"),
+    ("(let tid 5 i32 ", "(let tid 5 "),
+    ("(sif ", "(sif) (sif "),                                     # a condition-less if, and a let with two bodies
+    ("(intrinsic (Gpu) global_thread_id)", "(intrinsic Gpu global_thread_id)"),
+])
+def test_malformed_forms_are_parse_errors(find, replace):
+    """Every form is checked against the grammar before the recogniser or the fusion pass indexes into it."""
+    from spoc_b200 import fusion as F
+    ir = S.vector_add_ir()
+    assert find in ir
+    bad = ir.replace(find, replace, 1)
+    with pytest.raises(BackendError) as e:
+        compile_(bad)
+    assert e.value.code == L.ERR_PARSE and "malformed IR form" in str(e.value)
+    with pytest.raises(BackendError):
+        F.analyze(bad)
+    with pytest.raises(BackendError):
+        F.fuse_guarded(bad, S.square_add_guarded_ir(), "c")
+
+
+def test_forms_outside_the_grammar_are_unsupported_not_malformed():
+    ir = S.vector_add_ir().replace("(sif ", "(seq (match (evar n 4) (case 0 (empty))) (sif ", 1).replace("))))", ")))))", 1)
+    with pytest.raises(UnsupportedConstruct):
+        compile_(ir)
