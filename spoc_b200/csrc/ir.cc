@@ -1438,6 +1438,72 @@ bool validate_stmt(const Sx& s, std::string* err) {
   return true;  // a form this grammar does not know
 }
 
+// ---------------------------------------------------------------- binding check
+// A kernel that is executed must refer only to what it declares: variables bound by a parameter, a let or a
+// loop in scope (compared by id, as the reference's IR does), arrays that are vector parameters or shared
+// arrays created by a let in scope.  The recogniser inlines lets on demand and never looks at a binding
+// nothing uses, so without this pass dead code could name anything.
+struct Scope {
+  std::set<std::string> vars;    // variable ids
+  std::set<std::string> arrays;  // array names
+};
+
+bool unbound(const std::string& what, const std::string& name, std::string* err) {
+  *err = "the kernel refers to " + what + " '" + name + "', which it does not declare";
+  return false;
+}
+
+bool check_expr_bindings(const Sx& e, const Scope& sc, std::string* err) {
+  if (e.atom || e.kids.empty()) return true;
+  if (e.is("evar") && e.size() == 3 && e[2].atom) {
+    if (!sc.vars.count(e[2].s)) return unbound("variable", e[1].s, err);
+    return true;
+  }
+  if ((e.is("read") && e.size() == 3 && e[1].atom) || (e.is("arraylen") && e.size() == 2 && e[1].atom)) {
+    if (!sc.arrays.count(e[1].s)) return unbound("array", e[1].s, err);
+  }
+  for (size_t i = 1; i < e.size(); ++i)
+    if (!check_expr_bindings(e[i], sc, err)) return false;
+  return true;
+}
+
+bool check_stmt_bindings(const Sx& s, Scope sc, std::string* err) {
+  if (s.atom || s.kids.empty()) return true;
+  if ((s.is("let") || s.is("letmut")) && s.size() == 6) {
+    if (!check_expr_bindings(s[4], sc, err)) return false;
+    if (s[4].is("arraycreate")) sc.arrays.insert(s[1].s);
+    sc.vars.insert(s[2].s);
+    return check_stmt_bindings(s[5], sc, err);
+  }
+  if (s.is("for") && s.size() == 7) {
+    if (!check_expr_bindings(s[3], sc, err) || !check_expr_bindings(s[4], sc, err)) return false;
+    sc.vars.insert(s[2].s);
+    return check_stmt_bindings(s[6], sc, err);
+  }
+  if (s.is("assign") && s.size() == 3 && !s[1].atom) {
+    const Sx& lv = s[1];
+    if (lv.is("lvar") && lv.size() == 3 && !sc.vars.count(lv[2].s)) return unbound("variable", lv[1].s, err);
+    if (lv.is("elem") && lv.size() == 3) {
+      if (!sc.arrays.count(lv[1].s)) return unbound("array", lv[1].s, err);
+      if (!check_expr_bindings(lv[2], sc, err)) return false;
+    }
+    return check_expr_bindings(s[2], sc, err);
+  }
+  if (s.is("seq") || s.is("block") || s.is("pragma")) {
+    for (size_t i = 1; i < s.size(); ++i)
+      if (!s[i].atom && !(s.is("pragma") && i == 1) && !check_stmt_bindings(s[i], sc, err)) return false;
+    return true;
+  }
+  if (s.is("sif") && s.size() >= 3) {
+    if (!check_expr_bindings(s[1], sc, err)) return false;
+    for (size_t i = 2; i < s.size(); ++i)
+      if (!check_stmt_bindings(s[i], sc, err)) return false;
+    return true;
+  }
+  if ((s.is("expr") || s.is("return")) && s.size() == 2) return check_expr_bindings(s[1], sc, err);
+  return true;
+}
+
 }  // namespace
 
 bool parse_kernel_form(const std::string& text, Sx* root, KernelPlan* plan, const Sx** body, std::string* err) {
@@ -1480,6 +1546,18 @@ int ir_compile(const std::string& text, KernelPlan* plan, std::string* err) {
   if (has_unsupported_stmt(*body, &what)) {
     if (err) *err = "unsupported construct in kernel '" + plan->name + "': " + what;
     return SB200_ERR_UNSUPPORTED;
+  }
+  {
+    Scope sc;
+    for (const ParamInfo& pi : plan->params) {
+      sc.vars.insert(std::to_string(pi.id));
+      if (pi.is_vec) sc.arrays.insert(pi.name);
+    }
+    std::string berr;
+    if (!check_stmt_bindings(*body, sc, &berr)) {
+      if (err) *err = berr;
+      return SB200_ERR_PARSE;
+    }
   }
   Ctx cx{plan, ""};
   std::string reasons;

@@ -195,3 +195,22 @@ def test_forms_outside_the_grammar_are_unsupported_not_malformed():
     ir = S.vector_add_ir().replace("(sif ", "(seq (match (evar n 4) (case 0 (empty))) (sif ", 1).replace("))))", ")))))", 1)
     with pytest.raises(UnsupportedConstruct):
         compile_(ir)
+
+
+@pytest.mark.parametrize("find,replace,needle", [
+    ("(let tid 5 i32 (intrinsic (Gpu) global_thread_id) ", "(let dead 9 f32 (read y (evar tid 5)) (let tid 5 i32 (intrinsic (Gpu) global_thread_id) ", None),
+    ("(read a (evar tid 5))", "(read zz (evar tid 5))", "array 'zz'"),
+    ("(elem c (evar tid 5))", "(elem out (evar tid 5))", "array 'out'"),
+    ("(evar n 4)", "(evar n 44)", "variable 'n'"),
+])
+def test_kernels_must_declare_what_they_use(find, replace, needle):
+    """Even in a binding nothing uses: the recogniser never looks at dead lets, the binding check does."""
+    ir = S.vector_add_ir()
+    assert find in ir
+    bad = ir.replace(find, replace, 1)
+    if needle is None:
+        bad += ")"                      # the extra let needs its closing parenthesis
+        needle = "array 'y'"            # read by a binding that nothing uses
+    with pytest.raises(BackendError) as e:
+        compile_(bad)
+    assert e.value.code == L.ERR_PARSE and needle in str(e.value) and "does not declare" in str(e.value)
