@@ -963,6 +963,20 @@ bool match_block_reduce(Ctx& cx, const Sx& body) {
     return false;
   }
   const long long B = steps[0] * 2;
+  {
+    // the shared array must hold the block's B partial sums
+    const Sx* q = &body;
+    long long size = -1;
+    while ((q->is("let") || q->is("letmut")) && q->size() == 6) {
+      if (is_shared_let(*q) && (*q)[1].s == S && (*q)[4].size() == 4 && (*q)[4][2].is("const") && (*q)[4][2].size() == 3)
+        size = atoll((*q)[4][2][2].s.c_str());
+      q = &(*q)[5];
+    }
+    if (size < B) {
+      cx.why = "shared array is shorter than the block the tree steps imply";
+      return false;
+    }
+  }
   bool pow2 = B >= 32 && B <= 1024 && (B & (B - 1)) == 0;
   for (size_t i = 0; i < steps.size() && pow2; ++i)
     if (steps[i] != (B >> (i + 1))) pow2 = false;
@@ -1210,6 +1224,117 @@ void walk(const Sx& s, Env env, const std::function<void(const Sx&, const Env&)>
   }
 }
 
+// ---- integer index expressions as polynomials ----------------------------------------------
+// Index arithmetic can be written in many equivalent ways (operands commuted, products distributed, the
+// global index spelt out or taken from an intrinsic).  The tiled-kernel recogniser therefore compares
+// index expressions as polynomials with integer coefficients over opaque atoms: scalar parameters,
+// thread/block intrinsics, loop variables, and whole div/mod sub-expressions.
+using Mono = std::vector<std::string>;  // sorted atom names; empty = the constant term
+using Poly = std::map<Mono, long long>;
+
+Poly poly_const(long long c) {
+  Poly p;
+  if (c) p[Mono{}] = c;
+  return p;
+}
+Poly poly_atom(const std::string& a) {
+  Poly p;
+  p[Mono{a}] = 1;
+  return p;
+}
+Poly poly_add(const Poly& a, const Poly& b, long long sign = 1) {
+  Poly r = a;
+  for (const auto& kv : b) {
+    long long& c = r[kv.first];
+    c += sign * kv.second;
+    if (c == 0) r.erase(kv.first);
+  }
+  return r;
+}
+Poly poly_mul(const Poly& a, const Poly& b) {
+  Poly r;
+  for (const auto& x : a)
+    for (const auto& y : b) {
+      Mono m = x.first;
+      m.insert(m.end(), y.first.begin(), y.first.end());
+      std::sort(m.begin(), m.end());
+      long long& c = r[m];
+      c += x.second * y.second;
+      if (c == 0) r.erase(m);
+    }
+  return r;
+}
+std::string poly_print(const Poly& p) {
+  std::string o;
+  for (const auto& kv : p) {
+    o += (kv.second >= 0 ? "+" : "") + std::to_string(kv.second);
+    for (const std::string& a : kv.first) o += "*" + a;
+  }
+  return o.empty() ? "0" : o;
+}
+
+// e must already have its lets inlined.  False for anything that is not integer index arithmetic.
+bool poly_of(const Ctx& cx, const Sx& e, Poly* out) {
+  if (e.is("const") && e.size() == 3 && (e[1].s == "i32" || e[1].s == "i64")) {
+    *out = poly_const(atoll(e[2].s.c_str()));
+    return true;
+  }
+  if (e.is("evar") && e.size() == 3) {
+    const int prm = cx.scalar_param(e, nullptr);
+    *out = poly_atom(prm >= 0 ? "p" + std::to_string(prm) : "v" + e[2].s);
+    return true;
+  }
+  if (e.is("intrinsic") && e.size() == 3) {
+    const std::string& n = e[2].s;
+    auto global = [](const char* t, const char* bd, const char* bi) {
+      return poly_add(poly_atom(t), poly_mul(poly_atom(bd), poly_atom(bi)));
+    };
+    if (n == "global_idx_x" || n == "global_thread_id") {
+      *out = global("i:thread_idx_x", "i:block_dim_x", "i:block_idx_x");
+    } else if (n == "global_idx_y") {
+      *out = global("i:thread_idx_y", "i:block_dim_y", "i:block_idx_y");
+    } else {
+      *out = poly_atom("i:" + n);
+    }
+    return true;
+  }
+  if (e.is("binop") && e.size() == 4) {
+    Poly l, r;
+    if (!poly_of(cx, e[2], &l) || !poly_of(cx, e[3], &r)) return false;
+    const std::string& op = e[1].s;
+    if (op == "add") *out = poly_add(l, r);
+    else if (op == "sub") *out = poly_add(l, r, -1);
+    else if (op == "mul") *out = poly_mul(l, r);
+    else if (op == "div" || op == "mod") *out = poly_atom(op + "(" + poly_print(l) + "|" + poly_print(r) + ")");
+    else return false;
+    return true;
+  }
+  return false;
+}
+
+bool poly_is(const Ctx& cx, const Sx& e, const Poly& want) {
+  Poly got;
+  return poly_of(cx, e, &got) && got == want;
+}
+
+// cond is (l1 < r1) && (l2 < r2), either order, with the given polynomials
+bool guard_is(const Ctx& cx, const Sx& cond, const Poly& l1, const Poly& r1, const Poly& l2, const Poly& r2) {
+  return is_comm(cond, "and", [&](const Sx& a, const Sx& b) {
+    const Sx *al, *ar, *bl, *br;
+    return is_binop(a, "lt", &al, &ar) && is_binop(b, "lt", &bl, &br) && poly_is(cx, *al, l1) && poly_is(cx, *ar, r1) &&
+           poly_is(cx, *bl, l2) && poly_is(cx, *br, r2);
+  });
+}
+
+// The tiled kernel of benchmarks/bench_matrix_mul_tiled.ml:55-94, checked statement by statement:
+//   shared tile_a[T*T], tile_b[T*T];  sum := 0
+//   for t = 0 .. (k+T-1)/T - 1:
+//     tile_a[ty*T+tx] <- (row < m && t*T+tx < k) ? a[row*k + t*T+tx] : 0        barrier
+//     tile_b[ty*T+tx] <- (t*T+ty < k && col < n) ? b[(t*T+ty)*n + col] : 0      barrier
+//     for i = 0 .. T-1: sum := sum + tile_a[ty*T+i] * tile_b[i*T+tx]            barrier
+//   if row < m && col < n then out[row*n+col] <- epilogue(sum)
+// with row / col the global y / x indices and tx / ty the thread indices.  Index expressions are compared as
+// polynomials, so any equivalent spelling is accepted and nothing else is.
 bool match_gemm_tiled(Ctx& cx, const Sx& body) {
   KernelPlan& plan = *cx.plan;
   Peeled pl;
@@ -1219,52 +1344,11 @@ bool match_gemm_tiled(Ctx& cx, const Sx& body) {
   if (!core.is("letmut") || core.size() != 6 || !is_const_f_zero(inline_expr(core[4], pl.env))) return false;
   const std::string acc_id = core[2].s;
   std::vector<const Sx*> items = seq_items(core[5]);
-  if (items.size() != 2 || !items[0]->is("for")) return false;
+  if (items.size() != 2 || !items[0]->is("for") || items[0]->size() != 7 || (*items[0])[5].s != "upto") return false;
+  const Sx& outer = *items[0];
   GemmPlan g;
-  // facts gathered from the k-tile loop
-  std::string tile_a, tile_b;
-  int barriers = 0;
-  long long tile = 0;
-  struct Load {
-    std::string tile;
-    int param;
-    Sx idx;
-  };
-  std::vector<Load> loads;
-  bool bad = false;
-  walk(*items[0], pl.env, [&](const Sx& s, const Env& env) {
-    if (s.is("barrier")) ++barriers;
-    std::string aid;
-    const Sx *x, *y;
-    if (match_accumulate(s, &aid, &x, &y) && aid == acc_id) {
-      if (x->is("read") && y->is("read") && pl.shared.count((*x)[1].s) && pl.shared.count((*y)[1].s)) {
-        tile_a = (*x)[1].s;
-        tile_b = (*y)[1].s;
-      } else {
-        bad = true;
-      }
-    }
-    if (s.is("for") && s.size() == 7 && &s != items[0]) {
-      Sx hi = inline_expr(s[4], env);
-      const Sx *l, *r;
-      if (is_binop(hi, "sub", &l, &r) && l->is("const") && is_const_i32(*r, 1)) tile = atoll((*l)[2].s.c_str());
-    }
-    if (s.is("assign") && s.size() == 3 && s[1].is("elem") && pl.shared.count(s[1][1].s)) {
-      Sx rhs = inline_expr(s[2], env);
-      int prm;
-      const Sx* idx;
-      if (cx.is_read(rhs, &prm, &idx)) {
-        loads.push_back({s[1][1].s, prm, *idx});
-      } else if (!is_const_f_zero(rhs)) {
-        bad = true;
-      }
-    }
-  });
-  if (bad || tile_a.empty() || tile_a == tile_b || barriers < 2 || tile <= 0 || loads.size() != 2) {
-    cx.why = "k-tile loop is not load A tile / load B tile / accumulate with barriers";
-    return false;
-  }
-  // final guarded store
+
+  // final guarded store: gives row, col, m, n and the output
   Peeled fin;
   fin.env = pl.env;
   peel(*items[1], &fin, true);
@@ -1289,36 +1373,186 @@ bool match_gemm_tiled(Ctx& cx, const Sx& body) {
     return false;
   }
   if (!match_guard_mn(cx, fin.guards[0], row, col, &g) || g.n != nn) return false;
-  for (const Load& ld : loads) {
-    if (ld.tile == tile_a) {
-      // a[row*k + a_col]
+
+  // the statements of one k-tile iteration, in order
+  std::vector<const Sx*> steps;
+  std::function<void(const Sx&)> flat = [&](const Sx& s) {
+    if (s.is("seq")) {
+      for (size_t i = 1; i < s.size(); ++i) flat(s[i]);
+    } else if (s.is("block") && s.size() == 2) {
+      flat(s[1]);
+    } else if (!s.is("empty")) {
+      steps.push_back(&s);
+    }
+  };
+  flat(outer[6]);
+  // a load may be wrapped in lets (a_col, b_row): peel them into an environment of its own
+  struct Step {
+    char kind;  // 'L' load, 'B' barrier, 'C' compute
+    const Sx* core;
+    Env env;
+  };
+  std::vector<Step> seq;
+  for (const Sx* sp : steps) {
+    if (sp->is("barrier")) {
+      seq.push_back({'B', sp, pl.env});
+      continue;
+    }
+    Peeled one;
+    one.env = pl.env;
+    peel(*sp, &one, false);
+    if (!one.shared.empty()) return false;
+    if (one.core->is("sif") && one.core->size() == 4) seq.push_back({'L', one.core, one.env});
+    else if (one.core->is("for") && one.core->size() == 7) seq.push_back({'C', one.core, one.env});
+    else {
+      cx.why = "k-tile loop holds a statement that is neither a tile load, a barrier nor the inner product loop";
+      return false;
+    }
+  }
+  std::string shape;
+  for (const Step& x : seq) shape += x.kind;
+  if (shape != "LBLBCB" && shape != "LLBCB") {
+    cx.why = "k-tile loop is not load, barrier, load, barrier, accumulate, barrier";
+    return false;
+  }
+  std::vector<const Step*> loads;
+  const Step* comp = nullptr;
+  for (const Step& x : seq) {
+    if (x.kind == 'L') loads.push_back(&x);
+    if (x.kind == 'C') comp = &x;
+  }
+
+  // inner product loop: tile size, tile names
+  const Sx& inner = *comp->core;
+  if (inner[5].s != "upto" || !is_const_i32(inline_expr(inner[3], comp->env), 0)) return false;
+  Poly hi_poly;
+  if (!poly_of(cx, inline_expr(inner[4], comp->env), &hi_poly) || hi_poly.size() != 1 || !hi_poly.count(Mono{})) {
+    cx.why = "inner loop bound is not a constant tile size";
+    return false;
+  }
+  const long long T = hi_poly[Mono{}] + 1;
+  if (T < 1 || T > 32) return false;
+  const Poly TX = poly_atom("i:thread_idx_x"), TY = poly_atom("i:thread_idx_y"), PT = poly_const(T);
+  Poly ROW, COL;
+  if (!poly_of(cx, row, &ROW) || !poly_of(cx, col, &COL)) return false;
+  const Poly IV = poly_atom("v" + inner[2].s), TV = poly_atom("v" + outer[2].s);
+  std::string aid, tile_a, tile_b;
+  {
+    const Sx* acc_stmt = &inner[6];
+    while ((acc_stmt->is("block") && acc_stmt->size() == 2) || (acc_stmt->is("seq") && acc_stmt->size() == 2)) acc_stmt = &(*acc_stmt)[1];
+    const Sx *x, *y;
+    if (!match_accumulate(*acc_stmt, &aid, &x, &y) || aid != acc_id) {
+      cx.why = "inner loop body is not sum := sum + tile_a[..] * tile_b[..]";
+      return false;
+    }
+    const Sx xi = inline_expr(*x, comp->env), yi = inline_expr(*y, comp->env);
+    if (!xi.is("read") || !yi.is("read") || !pl.shared.count(xi[1].s) || !pl.shared.count(yi[1].s) || xi[1].s == yi[1].s) return false;
+    const Poly want_a = poly_add(poly_mul(TY, PT), IV), want_b = poly_add(poly_mul(IV, PT), TX);
+    if (poly_is(cx, xi[2], want_a) && poly_is(cx, yi[2], want_b)) {
+      tile_a = xi[1].s;
+      tile_b = yi[1].s;
+    } else if (poly_is(cx, yi[2], want_a) && poly_is(cx, xi[2], want_b)) {
+      tile_a = yi[1].s;
+      tile_b = xi[1].s;
+    } else {
+      cx.why = "inner product does not read tile_a[ty*T+i] and tile_b[i*T+tx]";
+      return false;
+    }
+  }
+  // shared tiles hold T*T floats
+  {
+    const Sx* s = &body;
+    int sized = 0;
+    while ((s->is("let") || s->is("letmut")) && s->size() == 6) {
+      if (is_shared_let(*s)) {
+        const Sx& ac = (*s)[4];
+        if (ac.size() != 4 || !is_const_i32(ac[2], T * T)) {
+          cx.why = "shared tiles are not tile_size*tile_size long";
+          return false;
+        }
+        ++sized;
+      }
+      s = &(*s)[5];
+    }
+    if (sized != 2) return false;
+  }
+  // the two loads
+  const Poly tile_idx = poly_add(poly_mul(TY, PT), TX);
+  const Poly M_ = poly_atom("p" + std::to_string(g.m)), N_ = poly_atom("p" + std::to_string(g.n));
+  for (const Step* ld : loads) {
+    const Sx& sif = *ld->core;
+    const Sx cond = inline_expr(sif[1], ld->env);
+    const Sx* th = &sif[2];
+    const Sx* el = &sif[3];
+    auto strip = [](const Sx* q) {
+      while ((q->is("block") && q->size() == 2) || (q->is("seq") && q->size() == 2)) q = &(*q)[1];
+      return q;
+    };
+    th = strip(th);
+    el = strip(el);
+    if (!th->is("assign") || !el->is("assign") || !(*th)[1].is("elem") || !(*el)[1].is("elem") || (*th)[1][1].s != (*el)[1][1].s ||
+        !poly_is(cx, inline_expr((*th)[1][2], ld->env), tile_idx) || !poly_is(cx, inline_expr((*el)[1][2], ld->env), tile_idx) ||
+        !is_const_f_zero(inline_expr((*el)[2], ld->env))) {
+      cx.why = "tile load is not `if in range then tile[ty*T+tx] <- x[..] else tile[ty*T+tx] <- 0.0`";
+      return false;
+    }
+    const std::string tile_name = (*th)[1][1].s;
+    const Sx rhs = inline_expr((*th)[2], ld->env);
+    int prm;
+    const Sx* pidx;
+    if (!cx.is_read(rhs, &prm, &pidx)) return false;
+    if (tile_name == tile_a && g.a < 0) {
+      // a[row*k + t*T + tx], guarded by row < m && t*T+tx < k: k is whatever parameter makes both hold
+      const Poly a_col = poly_add(poly_mul(TV, PT), TX);
       int kk = -1;
-      bool ok = is_comm(ld.idx, "add", [&](const Sx& p, const Sx&) {
-        return is_comm(p, "mul", [&](const Sx& rr, const Sx& ss) {
-          kk = cx.scalar_param(ss, "i32");
-          return sx_equal(rr, row) && kk >= 0;
-        });
-      });
-      if (!ok) return false;
-      g.a = ld.param;
+      for (size_t i = 0; i < plan.params.size() && kk < 0; ++i) {
+        if (plan.params[i].is_vec || plan.params[i].elt != "i32") continue;
+        const Poly K_ = poly_atom("p" + std::to_string(i));
+        if (poly_is(cx, *pidx, poly_add(poly_mul(ROW, K_), a_col)) && guard_is(cx, cond, ROW, M_, a_col, K_)) kk = static_cast<int>(i);
+      }
+      if (kk < 0) {
+        cx.why = "A tile is not loaded from a[row*k + t*T+tx] under row < m && t*T+tx < k";
+        return false;
+      }
+      g.a = prm;
       g.k = kk;
-    } else if (ld.tile == tile_b) {
-      // b[b_row*n + col]
-      bool ok = is_comm(ld.idx, "add", [&](const Sx& p, const Sx& q) {
-        return sx_equal(q, col) && is_comm(p, "mul", [&](const Sx&, const Sx& ss) {
-                 return cx.scalar_param(ss, "i32") == nn;
-               });
-      });
-      if (!ok) return false;
-      g.b = ld.param;
+    } else if (tile_name == tile_b && g.b < 0) {
+      const Poly b_row = poly_add(poly_mul(TV, PT), TY);
+      bool ok = false;
+      for (size_t i = 0; i < plan.params.size() && !ok; ++i) {
+        if (plan.params[i].is_vec || plan.params[i].elt != "i32") continue;
+        const Poly K_ = poly_atom("p" + std::to_string(i));
+        if (poly_is(cx, *pidx, poly_add(poly_mul(b_row, N_), COL)) && guard_is(cx, cond, b_row, K_, COL, N_)) {
+          ok = true;
+          if (g.k >= 0 && g.k != static_cast<int>(i)) ok = false;
+          if (g.k < 0) g.k = static_cast<int>(i);
+        }
+      }
+      if (!ok) {
+        cx.why = "B tile is not loaded from b[(t*T+ty)*n + col] under t*T+ty < k && col < n";
+        return false;
+      }
+      g.b = prm;
+    } else {
+      cx.why = "the k-tile loop loads the same tile twice";
+      return false;
     }
   }
   if (g.a < 0 || g.b < 0 || g.k < 0) return false;
+  // outer loop: t = 0 .. (k + T - 1) / T - 1
+  {
+    const Poly K_ = poly_atom("p" + std::to_string(g.k));
+    const Poly num_tiles = poly_atom("div(" + poly_print(poly_add(K_, poly_const(T - 1))) + "|" + poly_print(PT) + ")");
+    if (!is_const_i32(inline_expr(outer[3], pl.env), 0) || !poly_is(cx, inline_expr(outer[4], pl.env), poly_add(num_tiles, poly_const(-1)))) {
+      cx.why = "k-tile loop does not run from 0 to (k + T - 1) / T - 1";
+      return false;
+    }
+  }
   if (!match_epilogue(cx, inline_expr(st[2], fin.env), acc_id, out_idx, col, &g)) {
     cx.why = "stored expression is not act(alpha*sum + beta*c[row*n+col] + bias[col])";
     return false;
   }
-  g.tile = static_cast<int>(tile);
+  g.tile = static_cast<int>(T);
   plan.kind = KIND_GEMM_TILED;
   plan.gemm = g;
   return true;

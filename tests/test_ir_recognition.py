@@ -214,3 +214,66 @@ def test_kernels_must_declare_what_they_use(find, replace, needle):
     with pytest.raises(BackendError) as e:
         compile_(bad)
     assert e.value.code == L.ERR_PARSE and needle in str(e.value) and "does not declare" in str(e.value)
+
+
+TILED_WRONG = [
+    # (what, find, replace): each changes what the kernel computes while keeping its overall look
+    ("A read with the wrong row stride", "(read a (binop add (binop mul (evar row 11) (evar k 6)) (evar a_col 17)))",
+     "(read a (binop add (binop mul (evar row 11) (evar n 5)) (evar a_col 17)))"),
+    ("A column taken from ty", "(let a_col 17 i32 (binop add (binop mul (evar t 16) (evar tile_size 13)) (evar tx 9))",
+     "(let a_col 17 i32 (binop add (binop mul (evar t 16) (evar tile_size 13)) (evar ty 10))"),
+    ("B row guard against n", "(binop lt (evar b_row 18) (evar k 6))", "(binop lt (evar b_row 18) (evar n 5))"),
+    ("A guard dropped to one half", "(binop and (binop lt (evar row 11) (evar m 4)) (binop lt (evar a_col 17) (evar k 6)))",
+     "(binop and (binop lt (evar row 11) (evar m 4)) (binop lt (evar row 11) (evar m 4)))"),
+    ("tile_b stored transposed", "(assign (elem tile_b (binop add (binop mul (evar ty 10) (evar tile_size 13)) (evar tx 9))) (read b",
+     "(assign (elem tile_b (binop add (binop mul (evar tx 9) (evar tile_size 13)) (evar ty 10))) (read b"),
+    ("inner product walks tile_a by column", "(read tile_a (binop add (binop mul (evar ty 10) (evar tile_size 13)) (evar i 19)))",
+     "(read tile_a (binop add (binop mul (evar i 19) (evar tile_size 13)) (evar ty 10)))"),
+    ("one k-tile too few", "(for t 16 (const i32 0) (binop sub (evar num_tiles 14) (const i32 1)) upto",
+     "(for t 16 (const i32 0) (binop sub (evar num_tiles 14) (const i32 2)) upto"),
+    ("k-tiles start at 1", "(for t 16 (const i32 0) ", "(for t 16 (const i32 1) "),
+    ("inner loop one short", "(for i 19 (const i32 0) (binop sub (evar tile_size 13) (const i32 1)) upto",
+     "(for i 19 (const i32 0) (binop sub (evar tile_size 13) (const i32 2)) upto"),
+    ("barrier between the loads and the product missing",
+     "(const f32 0.0))))) (barrier) (seq (block (for i 19", "(const f32 0.0))))) (empty) (seq (block (for i 19"),
+    ("out-of-range elements of A not zeroed", "(evar tx 9))) (const f32 0.0))))) (barrier) (seq (block (let b_row",
+     "(evar tx 9))) (const f32 1.0))))) (barrier) (seq (block (let b_row"),
+    ("shared tile too small", "(let tile_a 7 (array f32 shared) (arraycreate f32 (const i32 256) shared)",
+     "(let tile_a 7 (array f32 shared) (arraycreate f32 (const i32 128) shared)"),
+    ("row taken from the x index", "(let row 11 i32 (binop add (evar ty 10) (binop mul (intrinsic (Gpu) block_dim_y) (intrinsic (Gpu) block_idx_y)))",
+     "(let row 11 i32 (binop add (evar tx 9) (binop mul (intrinsic (Gpu) block_dim_x) (intrinsic (Gpu) block_idx_x)))"),
+]
+
+
+@pytest.mark.parametrize("what,find,replace", TILED_WRONG, ids=[w for w, _, _ in TILED_WRONG])
+def test_tiled_kernels_that_compute_something_else_are_not_taken_for_gemm(what, find, replace):
+    ir = S.matmul_tiled_ir()
+    assert ir.count(find) >= 1, what
+    with pytest.raises(UnsupportedConstruct):
+        compile_(ir.replace(find, replace, 1))
+
+
+def test_equivalent_spellings_of_the_tiled_kernel_are_recognised():
+    ir = S.matmul_tiled_ir()
+    same = [
+        # index arithmetic commuted and the global indices taken from the intrinsics
+        ir.replace("(binop add (binop mul (evar row 11) (evar k 6)) (evar a_col 17))", "(binop add (evar a_col 17) (binop mul (evar k 6) (evar row 11)))"),
+        ir.replace("(let row 11 i32 (binop add (evar ty 10) (binop mul (intrinsic (Gpu) block_dim_y) (intrinsic (Gpu) block_idx_y)))",
+                   "(let row 11 i32 (intrinsic (Gpu) global_idx_y)"),
+        ir.replace("(binop add (binop mul (evar t 16) (evar tile_size 13)) (evar ty 10))", "(binop add (evar ty 10) (binop mul (const i32 16) (evar t 16)))"),
+        ir.replace("(binop and (binop lt (evar b_row 18) (evar k 6)) (binop lt (evar col 12) (evar n 5)))",
+                   "(binop and (binop lt (evar col 12) (evar n 5)) (binop lt (evar b_row 18) (evar k 6)))"),
+        ir.replace("(binop mul (read tile_a (binop add (binop mul (evar ty 10) (evar tile_size 13)) (evar i 19))) (read tile_b (binop add (binop mul (evar i 19) (evar tile_size 13)) (evar tx 9))))",
+                   "(binop mul (read tile_b (binop add (evar tx 9) (binop mul (evar tile_size 13) (evar i 19)))) (read tile_a (binop add (evar i 19) (binop mul (evar tile_size 13) (evar ty 10)))))"),
+    ]
+    for text in same:
+        assert text != ir
+        k = compile_(text)
+        assert k.kind == L.KIND_GEMM_TILED and "tile=16" in k.describe()
+
+
+def test_reduction_whose_shared_array_is_too_short_is_rejected():
+    ir = S.block_reduce_ir("sum", 64)
+    assert "(arraycreate f32 (const i32 64) shared)" in ir
+    with pytest.raises(UnsupportedConstruct):
+        compile_(ir.replace("(arraycreate f32 (const i32 64) shared)", "(arraycreate f32 (const i32 32) shared)"))
