@@ -201,6 +201,9 @@ SB200_API int sb200_ir_fuse_pipeline_as(const char *const *kernels, int count, i
  * all row-major float32 with leading dimensions in elements; C and bias may
  * be 0.  D may alias C.  Replaces the matrix_mul / matrix_mul_tiled kernels
  * (benchmarks/bench_matrix_mul.ml:55-73, bench_matrix_mul_tiled.ml:55-94).
+ * Calls may be issued on any streams of the device: those that use the library's scratch (3xTF32 mode, or operands
+ * TMA cannot address as they lie) are ordered against each other across streams by the library, the others run
+ * concurrently.
  * Once a first call with the same sizes has sized the library's scratch, a call enqueues nothing but kernel launches
  * (the GEMM launch carries the programmatic-stream-serialization attribute), so it can be captured into a CUDA graph
  * together with the map operators and replayed (tests/test_gpu_gemm.py). */

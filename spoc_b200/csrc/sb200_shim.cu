@@ -80,6 +80,10 @@ struct DeviceState {
   int cc_major = 0;
   void* workspace = nullptr;
   size_t workspace_bytes = 0;
+  // the scratch is shared by every stream of the device: a call on another stream than the last user's waits for it
+  cudaEvent_t ws_event = nullptr;
+  cudaStream_t ws_last_stream = nullptr;
+  bool ws_in_use = false;
   int* status = nullptr;  // device word written by kernels whose bounded waits expire
   std::unordered_map<uint64_t, uint64_t> allocs;
   // kernel profiling (enable_profiling): event triples recorded around the GEMM stages
@@ -471,9 +475,23 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   int rc = SB200_OK;
   const long long np = round_up(N, 32);  // row length of the low-part panel of B in the direct layout
   const size_t blo_bytes = round_up(K * np * 4, 1024);
+  // Calls that use the device's scratch are ordered across streams: two streams would otherwise write their
+  // operand panels into the same memory at once.  Not while the stream is being captured into a graph (an
+  // event of the capture cannot order work outside it): a captured sequence is ordered by its own stream.
+  bool track_scratch = false;
   if (route.workspace) {
     rc = ensure_workspace(d, route.workspace);
     if (rc) return rc;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) {
+      cudaGetLastError();
+      cap = cudaStreamCaptureStatusActive;
+    }
+    track_scratch = cap == cudaStreamCaptureStatusNone;
+    if (track_scratch) {
+      std::lock_guard<std::mutex> lock(d.mu);
+      if (d.ws_in_use && d.ws_last_stream != st) CU_TRY(cudaStreamWaitEvent(st, d.ws_event, 0));
+    }
   }
   const bool prof = g_profiling.load() != 0;
   DeviceState::ProfRec rec{nullptr, nullptr, nullptr};
@@ -576,6 +594,13 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
     CU_TRY(cudaEventRecord(rec.e2, st));
     std::lock_guard<std::mutex> lock(d.mu);
     d.prof.push_back(rec);
+  }
+  if (track_scratch && rc == SB200_OK) {
+    std::lock_guard<std::mutex> lock(d.mu);
+    if (!d.ws_event) CU_TRY(cudaEventCreateWithFlags(&d.ws_event, cudaEventDisableTiming));
+    CU_TRY(cudaEventRecord(d.ws_event, st));
+    d.ws_last_stream = st;
+    d.ws_in_use = true;
   }
   return rc;
 }

@@ -310,6 +310,38 @@ def test_randomised_shapes_strides_tiles_and_epilogues(backend, device, seed):
         lib.sb200_set_gemm_tile_n(0)
 
 
+def test_calls_on_two_streams_share_the_scratch_safely(backend, device):
+    """3xTF32 products prepare operand panels in the device's one scratch area; calls issued on different streams
+    are ordered by the library, so interleaving two streams gives the results of running them one after the other."""
+    lib = L.load()
+    shapes = [(512, 384, 640), (300, 1000, 513)]
+    bufs, want = [], []
+    for i, (M, N, K) in enumerate(shapes):
+        a, b = O.fill(M * K, 40 + i, 1), O.fill(K * N, 40 + i, 2)
+        A, B, D = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * N)
+        gemm(backend, device, L.MODE_3XTF32, M, N, K, A, B, D)
+        want.append(D.download())
+        bufs.append((A, B, D))
+    streams = [backend.Stream.create(device) for _ in shapes]
+    try:
+        for rep in range(5):
+            for D in (x[2] for x in bufs):
+                D.clear()
+            for _ in range(4):                       # interleaved, nothing waits in between
+                for (M, N, K), (A, B, D), st in zip(shapes, bufs, streams):
+                    assert lib.sb200_gemm_f32(device.id, st.handle, L.MODE_3XTF32, M, N, K, A.ptr, K, B.ptr, N, D.ptr, N,
+                                              1.0, 0, 0, 0.0, 0, 0) == 0
+            backend.Device.synchronize(device)
+            for (A, B, D), w in zip(bufs, want):
+                assert np.array_equal(D.download(), w), f"repetition {rep}"
+    finally:
+        for st in streams:
+            backend.Stream.destroy(st)
+        for A, B, D in bufs:
+            for x in (A, B, D):
+                x.free()
+
+
 def test_leading_dimensions_and_submatrices(backend, device):
     M, N, K, lda, ldb, ldd = 70, 90, 50, 64, 100, 128
     a, b = O.fill(M * lda, 3, 1), O.fill(K * ldb, 3, 2)
