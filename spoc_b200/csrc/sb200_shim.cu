@@ -95,6 +95,7 @@ struct DeviceState {
   void* host_stage = nullptr;
   size_t host_stage_bytes = 0;
   cudaStream_t pipe_in = nullptr, pipe_compute = nullptr, pipe_out = nullptr;
+  std::mutex host_call_mu;  // one host-operand call per device at a time: they share the mirrors and the three streams
 };
 DeviceState g_dev[kMaxDevices];
 std::atomic<int> g_profiling{0};
@@ -1818,6 +1819,7 @@ extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int6
   DeviceState* d;
   int rc = device_ready(dev, &d);
   if (rc) return rc;
+  std::lock_guard<std::mutex> host_call_lock(d->host_call_mu);
   if (!d->pipe_in) {
     CU_TRY(cudaStreamCreateWithFlags(&d->pipe_in, cudaStreamNonBlocking));
     CU_TRY(cudaStreamCreateWithFlags(&d->pipe_compute, cudaStreamNonBlocking));
