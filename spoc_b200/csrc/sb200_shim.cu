@@ -1281,6 +1281,19 @@ int sb200_kernel_launch(uint64_t kernel, const sb200_arg* args, int nargs, const
   DeviceState* d;
   rc = device_ready(k->dev, &d);
   if (rc) return rc;
+  {
+    // A vector that this library allocated cannot be longer than its allocation, whatever length the caller
+    // passes with it; buffers from elsewhere (or interior pointers) are taken at the caller's word.
+    std::lock_guard<std::mutex> lock(d->mu);
+    for (size_t p = 0; p < slots.size(); ++p) {
+      if (!slots[p].is_vec) continue;
+      auto it = d->allocs.find(slots[p].ptr);
+      if (it != d->allocs.end() && static_cast<uint64_t>(slots[p].len) * 4 > it->second)
+        return fail(SB200_ERR_BOUNDS, "kernel '%s': vector %s is passed with length %lld but its buffer holds %llu bytes",
+                    k->plan.name.c_str(), k->plan.params[p].name.c_str(), slots[p].len,
+                    static_cast<unsigned long long>(it->second));
+    }
+  }
   if (debug_kernel())
     fprintf(stderr, "[sarek-b200] launch %s grid=(%u,%u,%u) block=(%u,%u,%u)\n", k->plan.description.c_str(), grid[0], grid[1],
             grid[2], block[0], block[1], block[2]);

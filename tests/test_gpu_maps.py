@@ -138,6 +138,28 @@ def test_launch_past_vector_length_is_rejected(backend, device):
         v.free()
 
 
+def test_length_larger_than_the_buffer_is_rejected(backend, device):
+    """The caller states each vector's length; for a buffer the library allocated a length beyond the allocation is
+    refused before anything is launched."""
+    import ctypes as C
+    from spoc_b200.plugin import RSA_Buffer, RSA_Float32, RSA_Int32
+    n = 256
+    bufs = [backend.Memory.alloc(device, n, np.float32) for _ in range(3)]
+    short = backend.Memory.alloc(device, n // 2, np.float32)
+    try:
+        args = []
+        for b, stated in ((bufs[0], n), (bufs[1], n), (short, n)):         # the third vector claims n elements in n/2
+            args += [RSA_Buffer(b, stated), RSA_Int32(stated)]
+        args += [RSA_Float32(3.0), RSA_Int32(n)]
+        with pytest.raises(BackendError) as e:
+            backend.run_source(source=sarek_ir.stream_triad_ir(), lang=backend.supported_source_langs[0], kernel_name="sarek_kern",
+                               block=dims1d(256), grid=dims1d(1), shared_mem=0, args=args)
+        assert e.value.code == L.ERR_BOUNDS and "its buffer holds" in str(e.value)
+    finally:
+        for b in bufs + [short]:
+            backend.Memory.free(b)
+
+
 def test_fused_chain_ir_runs_in_one_pass(backend, device, oracle):
     """The kernel Sarek_fusion.fuse builds from a = b + 3c ; d = a*a + b (sarek/sarek/Sarek_fusion.ml:482-547),
     against Native's result of the two unfused kernels."""
