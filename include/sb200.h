@@ -201,6 +201,8 @@ SB200_API int sb200_ir_fuse_pipeline_as(const char *const *kernels, int count, i
  * all row-major float32 with leading dimensions in elements; C and bias may
  * be 0.  D may alias C.  Replaces the matrix_mul / matrix_mul_tiled kernels
  * (benchmarks/bench_matrix_mul.ml:55-73, bench_matrix_mul_tiled.ml:55-94).
+ * Operands that lie inside buffers from sb200_mem_alloc are checked against the end of their buffer
+ * (SB200_ERR_BOUNDS, nothing is launched); memory from other allocators is taken at the caller's word.
  * Calls may be issued on any streams of the device: those that use the library's scratch (3xTF32 mode, or operands
  * TMA cannot address as they lie) are ordered against each other across streams by the library, the others run
  * concurrently.

@@ -16,6 +16,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <map>
 #include <mutex>
 #include <thread>
 #include <string>
@@ -85,7 +86,7 @@ struct DeviceState {
   cudaStream_t ws_last_stream = nullptr;
   bool ws_in_use = false;
   int* status = nullptr;  // device word written by kernels whose bounded waits expire
-  std::unordered_map<uint64_t, uint64_t> allocs;
+  std::map<uint64_t, uint64_t> allocs;  // base address -> bytes of every buffer sb200_mem_alloc handed out (ordered: range lookups)
   // kernel profiling (enable_profiling): event triples recorded around the GEMM stages
   struct ProfRec {
     cudaEvent_t e0, e1, e2;
@@ -142,6 +143,21 @@ int check_status_word(DeviceState& d) {
     cudaMemset(d.status, 0, sizeof(int));
     return fail(SB200_ERR_TIMEOUT, "a bounded device-side wait expired in the GEMM pipeline (site 0x%x)", h);
   }
+  return SB200_OK;
+}
+
+// An operand that lies inside a buffer this library allocated must end inside it too; operands in memory from
+// elsewhere (another allocator's) are taken at the caller's word.  Turns a wrong size into an error instead of a fault.
+int check_extent(DeviceState& d, uint64_t ptr, uint64_t bytes, const char* what) {
+  if (!ptr || bytes == 0) return SB200_OK;
+  std::lock_guard<std::mutex> lock(d.mu);
+  auto it = d.allocs.upper_bound(ptr);
+  if (it == d.allocs.begin()) return SB200_OK;
+  --it;
+  if (ptr >= it->first + it->second) return SB200_OK;  // not inside one of ours
+  if (ptr + bytes > it->first + it->second)
+    return fail(SB200_ERR_BOUNDS, "%s needs %llu bytes from its address but the buffer it lies in ends after %llu", what,
+                static_cast<unsigned long long>(bytes), static_cast<unsigned long long>(it->first + it->second - ptr));
   return SB200_OK;
 }
 
@@ -224,6 +240,10 @@ int run_map(DeviceState& d, cudaStream_t st, int op, uint64_t out0, uint64_t out
   if (n == 0) return SB200_OK;
   if (!out0 || !in0 || !in1) return fail(SB200_ERR_INVALID_VALUE, "null device pointer passed to a map operator");
   if ((out0 | out1 | in0 | in1) & 3) return fail(SB200_ERR_ALIGNMENT, "float32 vectors must be 4-byte aligned");
+  for (uint64_t p : {out0, out1, in0, in1}) {
+    int rc = check_extent(d, p, static_cast<uint64_t>(n) * 4, "map operand");
+    if (rc) return rc;
+  }
   const float* p0 = as_ptr<const float>(in0);
   const float* p1 = as_ptr<const float>(in1);
   float* q0 = as_ptr<float>(out0);
@@ -620,6 +640,19 @@ int run_gemm(DeviceState& d, cudaStream_t st, int mode, long long M, long long N
     return fail(SB200_ERR_INVALID_VALUE, "leading dimension smaller than the row length (lda=%lld ldb=%lld ldc=%lld ldd=%lld)",
                 lda, ldb, ldc, ldd);
   if ((A | B | C | D | bias) & 3) return fail(SB200_ERR_ALIGNMENT, "float32 matrices must be 4-byte aligned");
+  {
+    auto extent = [](long long rows, long long cols, long long ld) {
+      return static_cast<uint64_t>((rows - 1) * ld + cols) * 4;
+    };
+    int rc = SB200_OK;
+    if (K > 0 && ((rc = check_extent(d, A, extent(M, K, lda), "GEMM operand A")) || (rc = check_extent(d, B, extent(K, N, ldb), "GEMM operand B"))))
+      return rc;
+    if ((rc = check_extent(d, D, extent(M, N, ldd), "GEMM result D")) || (rc = check_extent(d, C, extent(M, N, ldc), "GEMM operand C")) ||
+        (rc = check_extent(d, bias, static_cast<uint64_t>(N) * 4, "GEMM bias")))
+      return rc;
+    for (int r = 0; r < n_replicas; ++r)
+      if ((rc = check_extent(d, replicas[r], 0, "replica"))) return rc;
+  }
   GemmParams gp;
   memset(&gp, 0, sizeof gp);
   gp.M = static_cast<int>(M);
@@ -1281,18 +1314,13 @@ int sb200_kernel_launch(uint64_t kernel, const sb200_arg* args, int nargs, const
   DeviceState* d;
   rc = device_ready(k->dev, &d);
   if (rc) return rc;
-  {
-    // A vector that this library allocated cannot be longer than its allocation, whatever length the caller
-    // passes with it; buffers from elsewhere (or interior pointers) are taken at the caller's word.
-    std::lock_guard<std::mutex> lock(d->mu);
-    for (size_t p = 0; p < slots.size(); ++p) {
-      if (!slots[p].is_vec) continue;
-      auto it = d->allocs.find(slots[p].ptr);
-      if (it != d->allocs.end() && static_cast<uint64_t>(slots[p].len) * 4 > it->second)
-        return fail(SB200_ERR_BOUNDS, "kernel '%s': vector %s is passed with length %lld but its buffer holds %llu bytes",
-                    k->plan.name.c_str(), k->plan.params[p].name.c_str(), slots[p].len,
-                    static_cast<unsigned long long>(it->second));
-    }
+  // a vector that lies in a buffer of this library cannot be longer than what is left of that buffer,
+  // whatever length the caller passes with it
+  for (size_t p = 0; p < slots.size(); ++p) {
+    if (!slots[p].is_vec) continue;
+    const std::string what = "kernel '" + k->plan.name + "': vector " + k->plan.params[p].name + " of stated length " +
+                             std::to_string(slots[p].len);
+    if ((rc = check_extent(*d, slots[p].ptr, static_cast<uint64_t>(slots[p].len) * 4, what.c_str()))) return rc;
   }
   if (debug_kernel())
     fprintf(stderr, "[sarek-b200] launch %s grid=(%u,%u,%u) block=(%u,%u,%u)\n", k->plan.description.c_str(), grid[0], grid[1],

@@ -342,6 +342,30 @@ def test_calls_on_two_streams_share_the_scratch_safely(backend, device):
                 x.free()
 
 
+def test_operands_that_overrun_their_buffer_are_refused(backend, device):
+    """Sizes and strides are the caller's word; for operands inside buffers the library allocated they are checked
+    against the allocation, so a wrong size is an error (SB200_ERR_BOUNDS) and nothing is launched."""
+    lib = L.load()
+    M, N, K = 64, 96, 32
+    A = backend.Memory.alloc(device, M * K, np.float32)
+    B = backend.Memory.alloc(device, K * N, np.float32)
+    D = backend.Memory.alloc(device, M * N, np.float32)
+    try:
+        ok = lambda *a: lib.sb200_gemm_f32(device.id, 0, L.MODE_TF32, *a, 1.0, 0, 0, 0.0, 0, 0)
+        assert ok(M, N, K, A.ptr, K, B.ptr, N, D.ptr, N) == 0
+        assert ok(M + 1, N, K, A.ptr, K, B.ptr, N, D.ptr, N) == L.ERR_BOUNDS           # A and D one row short
+        assert "GEMM operand A" in lib.sb200_last_error_string().decode()
+        assert ok(M, N, K, A.ptr, K, B.ptr, N + 4, D.ptr, N) == L.ERR_BOUNDS           # B's stride walks out of B
+        assert ok(M, N, K, A.ptr, K, B.ptr, N, D.ptr + 4 * N, N) == L.ERR_BOUNDS       # D shifted by a row
+        assert "GEMM result D" in lib.sb200_last_error_string().decode()
+        assert lib.sb200_vector_add_f32(device.id, 0, D.ptr, A.ptr, A.ptr, M * K + 1) == L.ERR_BOUNDS
+        assert lib.sb200_vector_add_f32(device.id, 0, D.ptr, A.ptr, A.ptr, M * K) == 0
+        backend.Device.synchronize(device)
+    finally:
+        for x in (A, B, D):
+            backend.Memory.free(x)
+
+
 def test_leading_dimensions_and_submatrices(backend, device):
     M, N, K, lda, ldb, ldd = 70, 90, 50, 64, 100, 128
     a, b = O.fill(M * lda, 3, 1), O.fill(K * ldb, 3, 2)

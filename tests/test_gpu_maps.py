@@ -154,7 +154,7 @@ def test_length_larger_than_the_buffer_is_rejected(backend, device):
         with pytest.raises(BackendError) as e:
             backend.run_source(source=sarek_ir.stream_triad_ir(), lang=backend.supported_source_langs[0], kernel_name="sarek_kern",
                                block=dims1d(256), grid=dims1d(1), shared_mem=0, args=args)
-        assert e.value.code == L.ERR_BOUNDS and "its buffer holds" in str(e.value)
+        assert e.value.code == L.ERR_BOUNDS and "the buffer it lies in ends after 512" in str(e.value)
     finally:
         for b in bufs + [short]:
             backend.Memory.free(b)
