@@ -1070,6 +1070,7 @@ int sb200_memset32(int dev, uint64_t dptr, uint32_t value, uint64_t count, uint6
   if (rc) return rc;
   if (count == 0) return SB200_OK;
   if (!dptr || (dptr & 3)) return fail(SB200_ERR_INVALID_VALUE, "memset32 needs a 4-byte aligned device pointer");
+  if ((rc = check_extent(*d, dptr, count * 4, "memset32 destination"))) return rc;
   if (value == 0) {
     CU_TRY(cudaMemsetAsync(as_ptr<void>(dptr), 0, count * 4, as_stream(stream)));
     return SB200_OK;
@@ -1095,6 +1096,7 @@ int sb200_memcpy_htod(int dev, uint64_t dst, const void* src, uint64_t bytes) {
   if (rc) return rc;
   if (bytes == 0) return SB200_OK;
   if (!dst || !src) return fail(SB200_ERR_INVALID_VALUE, "null pointer passed to memcpy_htod");
+  if ((rc = check_extent(*d, dst, bytes, "copy destination"))) return rc;
   if (bytes >= kStagedCopyMinBytes && staged_copy_enabled() && host_memory_is_pageable(src)) {
     const int e = staged_copy_to_device(dev, as_ptr<void>(dst), src, bytes);
     if (e) return cuda_fail(static_cast<cudaError_t>(e), "staged host-to-device copy");
@@ -1110,6 +1112,7 @@ int sb200_memcpy_dtoh(int dev, void* dst, uint64_t src, uint64_t bytes) {
   if (rc) return rc;
   if (bytes == 0) return SB200_OK;
   if (!dst || !src) return fail(SB200_ERR_INVALID_VALUE, "null pointer passed to memcpy_dtoh");
+  if ((rc = check_extent(*d, src, bytes, "copy source"))) return rc;
   if (bytes >= kStagedCopyMinBytes && staged_copy_enabled() && host_memory_is_pageable(dst)) {
     const int e = staged_copy_to_host(dev, dst, as_ptr<void>(src), bytes);
     if (e) return cuda_fail(static_cast<cudaError_t>(e), "staged device-to-host copy");
@@ -1125,6 +1128,7 @@ int sb200_memcpy_dtod(int dev, uint64_t dst, uint64_t src, uint64_t bytes) {
   if (rc) return rc;
   if (bytes == 0) return SB200_OK;
   if (!dst || !src) return fail(SB200_ERR_INVALID_VALUE, "null pointer passed to memcpy_dtod");
+  if ((rc = check_extent(*d, dst, bytes, "copy destination")) || (rc = check_extent(*d, src, bytes, "copy source"))) return rc;
   CU_TRY(cudaMemcpy(as_ptr<void>(dst), as_ptr<void>(src), bytes, cudaMemcpyDeviceToDevice));
   return SB200_OK;
 }
@@ -1135,6 +1139,7 @@ int sb200_memcpy_htod_async(int dev, uint64_t dst, const void* src, uint64_t byt
   if (rc) return rc;
   if (bytes == 0) return SB200_OK;
   if (!dst || !src) return fail(SB200_ERR_INVALID_VALUE, "null pointer passed to memcpy_htod_async");
+  if ((rc = check_extent(*d, dst, bytes, "copy destination"))) return rc;
   CU_TRY(cudaMemcpyAsync(as_ptr<void>(dst), src, bytes, cudaMemcpyHostToDevice, as_stream(stream)));
   return SB200_OK;
 }
@@ -1145,6 +1150,7 @@ int sb200_memcpy_dtoh_async(int dev, void* dst, uint64_t src, uint64_t bytes, ui
   if (rc) return rc;
   if (bytes == 0) return SB200_OK;
   if (!dst || !src) return fail(SB200_ERR_INVALID_VALUE, "null pointer passed to memcpy_dtoh_async");
+  if ((rc = check_extent(*d, src, bytes, "copy source"))) return rc;
   CU_TRY(cudaMemcpyAsync(dst, as_ptr<void>(src), bytes, cudaMemcpyDeviceToHost, as_stream(stream)));
   return SB200_OK;
 }
@@ -1589,6 +1595,7 @@ int sb200_fill_f32(int dev, uint64_t stream, uint64_t dptr, int64_t n, uint64_t 
   if (n < 0 || kind < 0 || kind > 2) return fail(SB200_ERR_INVALID_VALUE, "bad fill arguments");
   if (n == 0) return SB200_OK;
   if (!dptr || (dptr & 3)) return fail(SB200_ERR_INVALID_VALUE, "fill needs a 4-byte aligned device pointer");
+  if ((rc = check_extent(*d, dptr, static_cast<uint64_t>(n) * 4, "fill destination"))) return rc;
   long long grid = (n + 255) / 256;
   const long long cap = static_cast<long long>(d->sm_count) * 16;
   if (grid > cap) grid = cap;

@@ -360,6 +360,13 @@ def test_operands_that_overrun_their_buffer_are_refused(backend, device):
         assert "GEMM result D" in lib.sb200_last_error_string().decode()
         assert lib.sb200_vector_add_f32(device.id, 0, D.ptr, A.ptr, A.ptr, M * K + 1) == L.ERR_BOUNDS
         assert lib.sb200_vector_add_f32(device.id, 0, D.ptr, A.ptr, A.ptr, M * K) == 0
+        host = np.zeros(M * K + 8, np.float32)
+        assert lib.sb200_memcpy_htod(device.id, A.ptr, host.ctypes.data, 4 * (M * K + 1)) == L.ERR_BOUNDS
+        assert lib.sb200_memcpy_dtoh(device.id, host.ctypes.data, A.ptr + 8, 4 * M * K) == L.ERR_BOUNDS
+        assert lib.sb200_memcpy_dtod(device.id, D.ptr, A.ptr, 4 * (M * K + 1)) == L.ERR_BOUNDS
+        assert lib.sb200_memset32(device.id, A.ptr, 7, M * K + 1, 0) == L.ERR_BOUNDS
+        assert lib.sb200_fill_f32(device.id, 0, A.ptr + 4, M * K, 1, 1, 0, 1.0, 0) == L.ERR_BOUNDS
+        assert lib.sb200_memcpy_htod(device.id, A.ptr, host.ctypes.data, 4 * M * K) == 0
         backend.Device.synchronize(device)
     finally:
         for x in (A, B, D):
