@@ -508,6 +508,44 @@ def run_transfer_case(lib, dev, S: int) -> None:
     print(json.dumps(out), flush=True)
 
 
+def run_tiles_case(lib, dev) -> None:
+    """Per-call time of sb200_gemm_f32 (plain product, aligned operands) for the tile widths of the CTA-pair kernel
+    — 256, 128, 64 columns and the automatic choice — over a range of sizes and both modes: 5 warm-up calls, then
+    back-to-back calls and one synchronise, wall-clock / calls (launch gaps included)."""
+    import numpy as np
+    from spoc_b200 import Backend, _lib as L
+    from spoc_b200.plugin import _check
+    b = Backend()
+    shapes = [(128, 128, 128), (256, 256, 256), (512, 512, 512), (768, 768, 768), (1024, 1024, 1024), (1280, 1280, 1280),
+              (1536, 1536, 1536), (1792, 1792, 1792), (2048, 2048, 2048), (2560, 2560, 2560), (4096, 4096, 4096),
+              (512, 4096, 512), (4096, 512, 4096), (1024, 1024, 8192), (64, 8192, 8192), (8192, 4096, 4096)]
+    rows = []
+    for (M, N, K) in shapes:
+        A, B, D = (b.Memory.alloc(dev, n, np.float32) for n in (M * K, K * N, M * N))
+        _check(lib.sb200_fill_f32(dev.id, 0, A.ptr, M * K, SEED, 1, 0, 1.0, 0))
+        _check(lib.sb200_fill_f32(dev.id, 0, B.ptr, K * N, SEED, 2, 0, 1.0, 0))
+        for mode, label in ((L.MODE_TF32, "tf32"), (L.MODE_3XTF32, "3xtf32")):
+            row = {"M": M, "N": N, "K": K, "mode": label}
+            for tile in (256, 128, 64, 0):
+                _check(lib.sb200_set_gemm_tile_n(tile))
+                call = lambda: _check(lib.sb200_gemm_f32(dev.id, 0, mode, M, N, K, A.ptr, K, B.ptr, N, D.ptr, N, 1.0, 0, 0, 0.0, 0, 0))
+                for _ in range(5):
+                    call()
+                _check(lib.sb200_device_synchronize(dev.id))
+                calls = 200 if M * N * K < 2 ** 33 else 30
+                t0 = time.perf_counter()
+                for _ in range(calls):
+                    call()
+                _check(lib.sb200_device_synchronize(dev.id))
+                row["auto_us" if tile == 0 else f"tile{tile}_us"] = round((time.perf_counter() - t0) / calls * 1e6, 1)
+            row["auto_tflops"] = round(2.0 * M * N * K / row["auto_us"] / 1e6, 1)
+            rows.append(row)
+        for m in (A, B, D):
+            b.Memory.free(m)
+    _check(lib.sb200_set_gemm_tile_n(0))
+    print(json.dumps({"case": "tiles", "unit": "us per call", "rows": rows}), flush=True)
+
+
 def run_case(args) -> None:
     """A small single-operator run for profiler captures: one warm-up call and two
     measured calls of one operator on inputs larger than L2 but well under a GB."""
@@ -526,6 +564,8 @@ def run_case(args) -> None:
     S = args.size
     if args.case == "transfer":
         return run_transfer_case(lib, dev, S)
+    if args.case == "tiles":
+        return run_tiles_case(lib, dev)
     if args.case in ("gemm3", "gemm1"):
         mode = L.MODE_3XTF32 if args.case == "gemm3" else L.MODE_TF32
         bufs = [torch.empty(S * S, dtype=torch.float32, device=tdev) for _ in range(4)]
@@ -757,7 +797,7 @@ def main() -> None:
     ap.add_argument("--workload", default="gemm8192", choices=["gemm8192", "gather", "skinny"],
                     help="gemm8192: the headline run; gather: large square GEMM with the result gathered on every GPU; "
                          "skinny: 65536x4096x4096 GEMM, rows split over the ranks, B broadcast")
-    ap.add_argument("--case", default=None, choices=["gemm3", "gemm1", "map", "transfer"],
+    ap.add_argument("--case", default=None, choices=["gemm3", "gemm1", "map", "transfer", "tiles"],
                     help="profiler-sized single-operator run (square size --size; map uses size^2 elements)")
     ap.add_argument("--size", type=int, default=4096)
     ap.add_argument("--gpus", type=int, default=1)
