@@ -277,3 +277,95 @@ def test_reduction_whose_shared_array_is_too_short_is_rejected():
     assert "(arraycreate f32 (const i32 64) shared)" in ir
     with pytest.raises(UnsupportedConstruct):
         compile_(ir.replace("(arraycreate f32 (const i32 64) shared)", "(arraycreate f32 (const i32 32) shared)"))
+
+
+def _parse_sx(text):
+    toks = text.replace("(", " ( ").replace(")", " ) ").split()
+    pos = 0
+
+    def rd():
+        nonlocal pos
+        if toks[pos] == "(":
+            pos += 1
+            out = []
+            while toks[pos] != ")":
+                out.append(rd())
+            pos += 1
+            return out
+        pos += 1
+        return toks[pos - 1]
+    return rd()
+
+
+def _show_sx(x):
+    return "(" + " ".join(_show_sx(i) for i in x) + ")" if isinstance(x, list) else x
+
+
+def _subtrees(x, heads, acc, parent=None, idx=None):
+    if isinstance(x, list):
+        if x and isinstance(x[0], str) and x[0] in heads and parent is not None:
+            acc.append((parent, idx))
+        for i, k in enumerate(x):
+            _subtrees(k, heads, acc, x, i)
+    return acc
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_mutated_kernels_never_crash_the_entry_points(seed):
+    """Seeded mutation fuzz of the text entry points: characters and tokens dropped, swapped or inserted, and
+    sub-expressions / statements of one reference kernel grafted into another.  Every call must come back with
+    success, SB200_ERR_UNSUPPORTED or SB200_ERR_PARSE (a crash would take the test process down)."""
+    import copy
+    import random
+    from spoc_b200 import fusion as F
+    lib = L.load()
+    rnd = random.Random(seed)
+    texts = [S.vector_add_ir(), S.stream_triad_ir(), S.matmul_naive_ir(), S.matmul_tiled_ir(), S.chain_fused_ir(), S.generic_example_ir(),
+             S.block_reduce_ir("dot"), S.square_add_guarded_ir(), S.matmul_tiled_ir(epilogue=EPI)]
+    trees = [_parse_sx(t) for t in texts]
+    exprs = {"const", "evar", "binop", "unop", "read", "intrinsic", "if"}
+    stmts = {"assign", "seq", "sif", "for", "let", "letmut", "block", "barrier", "empty"}
+    out = C.create_string_buffer(1 << 20)
+    seen = set()
+    for it in range(400):
+        if it % 2:
+            t = rnd.choice(texts)
+            toks = t.replace("(", " ( ").replace(")", " ) ").split()
+            k = rnd.randrange(5)
+            if k == 0:
+                t = t[:rnd.randrange(1, len(t))]
+            elif k == 1:
+                del toks[rnd.randrange(len(toks))]
+                t = " ".join(toks)
+            elif k == 2:
+                i, j = rnd.randrange(len(toks)), rnd.randrange(len(toks))
+                toks[i], toks[j] = toks[j], toks[i]
+                t = " ".join(toks)
+            elif k == 3:
+                toks.insert(rnd.randrange(len(toks)), rnd.choice(["(", ")", "evar", "read", "-1", "()", "f32", "let", "99999999999999999999"]))
+                t = " ".join(toks)
+            else:
+                i = rnd.randrange(len(toks))
+                t = " ".join(toks[:i] + toks[min(len(toks), i + rnd.randrange(1, 30)):])
+        else:
+            tree = copy.deepcopy(rnd.choice(trees))
+            for _ in range(rnd.randrange(1, 4)):
+                heads = rnd.choice([exprs, stmts])
+                here, donor = _subtrees(tree[3], heads, []), _subtrees(copy.deepcopy(rnd.choice(trees))[3], heads, [])
+                if here and donor:
+                    (p, i), (dp, di) = rnd.choice(here), rnd.choice(donor)
+                    p[i] = dp[di]
+            t = _show_sx(tree)
+        h = C.c_uint64(0)
+        rc = lib.sb200_kernel_compile(0, t.encode(), b"k", C.byref(h))
+        assert rc in (0, L.ERR_UNSUPPORTED, L.ERR_PARSE), (rc, t[:200])
+        seen.add(rc)
+        if rc == 0:
+            assert lib.sb200_kernel_destroy(h.value) == 0
+        assert lib.sb200_ir_analyze(t.encode(), out, 1 << 20) in (0, L.ERR_PARSE)
+        other = rnd.choice(texts).encode()
+        fused = C.c_int(0)
+        for kind in range(6):
+            for a, b in ((t.encode(), other), (other, t.encode())):
+                assert lib.sb200_ir_fuse_as(a, b, rnd.choice([b"a", b"c", b"d", b"sdata"]), kind, out, 1 << 20, C.byref(fused)) in (0, L.ERR_PARSE)
+    assert seen == {0, L.ERR_UNSUPPORTED, L.ERR_PARSE}
