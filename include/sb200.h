@@ -227,7 +227,9 @@ SB200_API int sb200_gemm_f32(int dev, uint64_t stream, int mode,
  * share the array and it keeps the last call's contents (each call rewrites
  * all it reads); calls that overlap on the GPU race on it.  The first call on a
  * device looks up the array's address and should come before any stream
- * capture.  The call returns after its kernels have finished. */
+ * capture.  Every call waits on `stream` until its kernels have finished and reads
+ * a status word back with a synchronous copy: do not issue it on a stream that is
+ * being captured.  Operand extents are checked as in sb200_gemm_f32. */
 SB200_API int sb200_gemm_f32_noalloc(int dev, uint64_t stream, int mode,
                                      int64_t M, int64_t N, int64_t K,
                                      uint64_t A, int64_t lda, uint64_t B, int64_t ldb,
@@ -302,6 +304,13 @@ SB200_API int sb200_set_gemm_variant(int variant);
 /* tile columns of the CTA-pair kernel: 0 = automatic (256, or 128 / 64 for problems with too few 256-column
  * tiles to occupy the SMs), else 64, 128 or 256.  Also SAREK_B200_TILE_N.  Results do not depend on it. */
 SB200_API int sb200_set_gemm_tile_n(int tile_n);
+
+/* L2 eviction policies the GEMM kernels attach to their memory instructions (a per-instruction cache hint;
+ * no device setting is touched): three 2-bit fields, each 0 = normal, 1 = evict first, 2 = evict last —
+ * bits 0-1 the TMA loads of A (high and low parts), bits 2-3 the TMA loads of B, bits 4-5 the epilogue's reads
+ * of C and writes of D.  -1 returns to the built-in default (also SAREK_B200_L2_POLICY).  Results do not
+ * depend on it.  No counterpart in the reference, whose generated kernels carry no cache hints. */
+SB200_API int sb200_set_l2_policy(int bits);
 
 /* seeded synthetic data written on the device: kind 0 U[-1,1), 1 U[-0.1,0.1),
  * 2 N(0,sigma); element i of the stream is a pure function of (seed, stream_id,

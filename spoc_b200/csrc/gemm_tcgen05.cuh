@@ -39,7 +39,8 @@ constexpr int GEMM_GROUP_M = 16;  // tile rasterisation: bands of 16 row tiles
 constexpr uint32_t GEMM_A_BYTES = GEMM_BM * GEMM_BK * 4;  // 16 KiB
 constexpr uint32_t GEMM_B_BYTES = GEMM_BN * GEMM_BK * 4;  // 32 KiB
 constexpr uint32_t GEMM_TMEM_COLS = 512;                  // two 256-column accumulators
-constexpr uint32_t GEMM_EPI_BUF_BYTES = 4 * 32 * 33 * 4;  // per-warp 32x33 transpose tiles
+constexpr int GEMM_EPI_LD = 36;                           // row stride (floats) of a warp's staging tile: 144 B, 16-byte aligned, conflict-free
+constexpr uint32_t GEMM_EPI_BUF_BYTES = 4 * 32 * GEMM_EPI_LD * 4;  // per-warp 32-row staging tiles
 constexpr uint32_t GEMM_CTRL_BYTES = 256;
 
 template <int MODE>
@@ -68,6 +69,12 @@ struct GemmParams {
   // row-sharded product leaves the whole matrix on every GPU without a separate all-gather.
   int n_replicas;
   float* replicas[7];
+  // Set by the host when D, C, bias and every replica are 16-byte aligned with leading dimensions and N that
+  // are multiples of 4: the epilogue then moves 128-bit vectors (four rows of 128 bytes per warp instruction).
+  int vec_epilogue;
+  // L2 eviction policies, 2 bits each (0 normal, 1 evict first, 2 evict last): bits 0-1 loads of A (hi and lo),
+  // bits 2-3 loads of B, bits 4-5 the epilogue's reads of C and writes of D.
+  int l2_policy;
 };
 
 __device__ __forceinline__ void store_replicas(const GemmParams& p, long long offset, float x) {
@@ -83,6 +90,132 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   const int band_m = min(GEMM_GROUP_M, tiles_m - first_m);
   tm = first_m + within % band_m;
   tn = within / band_m;
+}
+
+// Epilogue of one warp for its 32 rows x BN columns of a finished accumulator: tensor memory -> registers
+// (lane = row) -> the warp's staging tile in shared memory -> D = act(alpha*acc + beta*C + bias), and the same
+// values to every replica of D.  `taddr` addresses the warp's 32 tensor-memory lanes at the accumulator's
+// first column.  Both GEMM kernels use it; every element goes through the same operations in the same order
+// on either path, so the vector and scalar paths give the same bits.
+template <int BN>
+__device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t taddr, float* tbuf, int lane, int row0, int n0) {
+  const int rows_here = min(32, p.M - row0);  // may be <= 0 for a ragged last tile
+  if (p.vec_epilogue) {
+    const int sub = lane >> 3;       // this lane's row within each group of four rows
+    const int cq = (lane & 7) * 4;   // first column of this lane's quad within a 32-column chunk
+    const uint64_t pol = l2_policy((p.l2_policy >> 4) & 3);
+#pragma unroll 1
+    for (int chunk = 0; chunk < BN / 32; ++chunk) {
+      if (n0 + chunk * 32 >= p.N) break;  // warp-uniform
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(taddr + chunk * 32, v);
+      tmem_ld_wait();
+      float4* trow = reinterpret_cast<float4*>(tbuf + lane * GEMM_EPI_LD);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        trow[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                              __uint_as_float(v[4 * j + 3]));
+      __syncwarp();
+      const int col = n0 + chunk * 32 + cq;
+      if (col < p.N) {  // N is a multiple of 4 on this path: the whole quad is inside
+        const float4 bv = p.bias ? *reinterpret_cast<const float4*>(p.bias + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 cv[8];
+        if (p.C) {
+          // all loads of C before the first use, so that their latencies overlap
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = sub + 4 * i;
+            if (r < rows_here) cv[i] = ld_global_v4_hint(p.C + static_cast<long long>(row0 + r) * p.ldc + col, pol);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = sub + 4 * i;
+          if (r < rows_here) {
+            const float4 a = *reinterpret_cast<const float4*>(tbuf + r * GEMM_EPI_LD + cq);
+            float4 x = make_float4(p.alpha * a.x, p.alpha * a.y, p.alpha * a.z, p.alpha * a.w);
+            if (p.C) {
+              x.x = fmaf(p.beta, cv[i].x, x.x);
+              x.y = fmaf(p.beta, cv[i].y, x.y);
+              x.z = fmaf(p.beta, cv[i].z, x.z);
+              x.w = fmaf(p.beta, cv[i].w, x.w);
+            }
+            x.x += bv.x;
+            x.y += bv.y;
+            x.z += bv.z;
+            x.w += bv.w;
+            if (p.act == 1) {
+              x.x = (x.x > 0.0f) ? x.x : 0.0f;
+              x.y = (x.y > 0.0f) ? x.y : 0.0f;
+              x.z = (x.z > 0.0f) ? x.z : 0.0f;
+              x.w = (x.w > 0.0f) ? x.w : 0.0f;
+            }
+            const long long off = static_cast<long long>(row0 + r) * p.ldd + col;
+            st_global_v4_hint(p.D + off, x, pol);
+            cv[i] = x;  // kept for the replicas
+          }
+        }
+        // gathered result: the same four rows x 128 bytes per instruction to every other copy of D
+#pragma unroll 1
+        for (int rep = 0; rep < p.n_replicas; ++rep) {
+          float* base = p.replicas[rep];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = sub + 4 * i;
+            if (r < rows_here) *reinterpret_cast<float4*>(base + static_cast<long long>(row0 + r) * p.ldd + col) = cv[i];
+          }
+        }
+      }
+      __syncwarp();
+    }
+    return;
+  }
+  // general path: any alignment, any N; the tile is staged transposed so that lane = column
+#pragma unroll 1
+  for (int chunk = 0; chunk < BN / 32; ++chunk) {
+    const int col = n0 + chunk * 32 + lane;
+    if (n0 + chunk * 32 >= p.N) break;  // warp-uniform
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(taddr + chunk * 32, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) tbuf[lane * 33 + j] = __uint_as_float(v[j]);
+    __syncwarp();
+    if (col < p.N) {
+      const float bias_v = p.bias ? p.bias[col] : 0.0f;
+      if (rows_here >= 32) {
+        // full 32-row slab: issue all 32 loads of C before the first use so that
+        // their latencies overlap instead of adding up
+        float cv[32];
+        if (p.C) {
+          const float* cp = p.C + static_cast<long long>(row0) * p.ldc + col;
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr) cv[rr] = cp[rr * p.ldc];
+        }
+        float* dp = p.D + static_cast<long long>(row0) * p.ldd + col;
+#pragma unroll
+        for (int rr = 0; rr < 32; ++rr) {
+          float x = p.alpha * tbuf[rr * 33 + lane];
+          if (p.C) x = fmaf(p.beta, cv[rr], x);
+          x += bias_v;
+          if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
+          dp[rr * p.ldd] = x;
+          if (p.n_replicas) store_replicas(p, static_cast<long long>(row0 + rr) * p.ldd + col, x);
+        }
+      } else {
+        for (int rr = 0; rr < rows_here; ++rr) {
+          const long long row = row0 + rr;
+          float x = p.alpha * tbuf[rr * 33 + lane];
+          if (p.C) x = fmaf(p.beta, p.C[row * p.ldc + col], x);
+          x += bias_v;
+          if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
+          p.D[row * p.ldd + col] = x;
+          if (p.n_replicas) store_replicas(p, row * p.ldd + col, x);
+        }
+      }
+    }
+    __syncwarp();
+  }
 }
 
 template <int MODE>
@@ -236,7 +369,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   } else {
     // --------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, 32*quarter+32)
-    float* tbuf = epi_buf + (warp - 2) * (32 * 33);
+    float* tbuf = epi_buf + (warp - 2) * (32 * GEMM_EPI_LD);
     int local_tile = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
@@ -255,52 +388,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         break;
       }
       tc_fence_after_sync();
-      const int rows_here = min(32, p.M - row0);  // may be <= 0 for a ragged last tile
-#pragma unroll 1
-      for (int chunk = 0; chunk < GEMM_BN / 32; ++chunk) {
-        const int col = n0 + chunk * 32 + lane;
-        if (n0 + chunk * 32 >= p.N) break;  // warp-uniform
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * GEMM_BN + chunk * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) tbuf[lane * 33 + j] = __uint_as_float(v[j]);
-        __syncwarp();
-        if (col < p.N) {
-          const float bias_v = p.bias ? p.bias[col] : 0.0f;
-          if (rows_here >= 32) {
-            // full 32-row slab: issue all 32 loads of C before the first use so that
-            // their latencies overlap instead of adding up
-            float cv[32];
-            if (p.C) {
-              const float* cp = p.C + static_cast<long long>(row0) * p.ldc + col;
-#pragma unroll
-              for (int rr = 0; rr < 32; ++rr) cv[rr] = cp[rr * p.ldc];
-            }
-            float* dp = p.D + static_cast<long long>(row0) * p.ldd + col;
-#pragma unroll
-            for (int rr = 0; rr < 32; ++rr) {
-              float x = p.alpha * tbuf[rr * 33 + lane];
-              if (p.C) x = fmaf(p.beta, cv[rr], x);
-              x += bias_v;
-              if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
-              dp[rr * p.ldd] = x;
-              if (p.n_replicas) store_replicas(p, static_cast<long long>(row0 + rr) * p.ldd + col, x);
-            }
-          } else {
-            for (int rr = 0; rr < rows_here; ++rr) {
-              const long long row = row0 + rr;
-              float x = p.alpha * tbuf[rr * 33 + lane];
-              if (p.C) x = fmaf(p.beta, p.C[row * p.ldc + col], x);
-              x += bias_v;
-              if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
-              p.D[row * p.ldd + col] = x;
-              if (p.n_replicas) store_replicas(p, row * p.ldd + col, x);
-            }
-          }
-        }
-        __syncwarp();
-      }
+      epilogue_rows<GEMM_BN>(p, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * GEMM_BN, tbuf, lane, row0, n0);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
@@ -319,6 +407,16 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
 // ------------------------------------------------------------------------
 // Operand preparation
 // ------------------------------------------------------------------------
+
+// Low part of the 3xTF32 split: rn_tf32(x - hi).  When hi is not finite (x is an infinity or a NaN, or a
+// finite x so close to FLT_MAX that rounding to TF32 overflows) x - hi would be Inf - Inf; the low part is
+// then zero.  Non-finite operands still do not follow fp32 exactly in 3xTF32 mode: the cross term
+// hi(a) * lo(b) is Inf * 0 = NaN whenever the other operand is exactly representable in TF32, so an element
+// whose row of A or column of B holds an infinity comes out non-finite (Inf or NaN) where fp32 gives Inf.
+// Elements that no non-finite operand reaches are unaffected; TF32 mode keeps fp32's Inf/NaN semantics.
+__device__ __forceinline__ float tf32_lo(float x, float hi) {
+  return (fabsf(hi) <= 3.402823466e+38f) ? tf32_round(x - hi) : 0.0f;
+}
 
 // A[M x K] (row stride lda) -> hi[M x Kp] (and lo[M x Kp]), Kp = K rounded up
 // to 32, columns K..Kp zero.  One thread per 4 consecutive k.
@@ -346,7 +444,7 @@ __global__ void prep_a_kernel(const float* __restrict__ A, long long lda, float*
     float4 h = make_float4(tf32_round(x.x), tf32_round(x.y), tf32_round(x.z), tf32_round(x.w));
     if (!LO_ONLY) *reinterpret_cast<float4*>(hi + row * Kp + k) = h;
     if (MODE == 3) {
-      float4 l = make_float4(tf32_round(x.x - h.x), tf32_round(x.y - h.y), tf32_round(x.z - h.z), tf32_round(x.w - h.w));
+      float4 l = make_float4(tf32_lo(x.x, h.x), tf32_lo(x.y, h.y), tf32_lo(x.z, h.z), tf32_lo(x.w, h.w));
       *reinterpret_cast<float4*>(lo + row * Kp + k) = l;
     }
   }
@@ -377,8 +475,8 @@ __device__ __forceinline__ void prep_lo_rows(const PrepLoJob& j, long long block
       if (k + 1 < j.cols) x.y = src[1];
       if (k + 2 < j.cols) x.z = src[2];
     }
-    const float4 l = make_float4(tf32_round(x.x - tf32_round(x.x)), tf32_round(x.y - tf32_round(x.y)),
-                                 tf32_round(x.z - tf32_round(x.z)), tf32_round(x.w - tf32_round(x.w)));
+    const float4 l = make_float4(tf32_lo(x.x, tf32_round(x.x)), tf32_lo(x.y, tf32_round(x.y)),
+                                 tf32_lo(x.z, tf32_round(x.z)), tf32_lo(x.w, tf32_round(x.w)));
     *reinterpret_cast<float4*>(j.lo + row * j.colsp + k) = l;
   }
 }
@@ -419,7 +517,7 @@ __global__ void prep_b_kernel(const float* __restrict__ B, long long ldb, float*
         const float x = tile[threadIdx.x][threadIdx.y + j];
         const float h = tf32_round(x);
         hi[static_cast<long long>(n) * Kp + k] = h;
-        if (MODE == 3) lo[static_cast<long long>(n) * Kp + k] = tf32_round(x - h);
+        if (MODE == 3) lo[static_cast<long long>(n) * Kp + k] = tf32_lo(x, h);
       }
     }
     __syncthreads();

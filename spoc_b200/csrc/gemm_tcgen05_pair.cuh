@@ -125,6 +125,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint64_t pol_a = l2_policy(p.l2_policy & 3), pol_b = l2_policy((p.l2_policy >> 2) & 3);
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
         int tm, tn;
         pair_tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
@@ -140,24 +141,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * Cfg::kStageBytes);
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
           uint8_t* sp = stage_base + stage * Cfg::kStageBytes;
-          tma_load_2d_pair(smem_u32(sp), &map_a_hi, bar, kb * GEMM_BK, m0);
+          tma_load_2d_pair_hint(smem_u32(sp), &map_a_hi, bar, kb * GEMM_BK, m0, pol_a);
           if (DIRECT) {
             // B is K x N row-major: x = column, y = k; slabs of 32 columns cover this block's half
 #pragma unroll
             for (int sl = 0; sl < SLABS; ++sl)
-              tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES + sl * 4096), &map_b_hi, bar, n0 + 32 * sl, kb * GEMM_BK);
+              tma_load_2d_pair_hint(smem_u32(sp + PAIR_A_BYTES + sl * 4096), &map_b_hi, bar, n0 + 32 * sl, kb * GEMM_BK, pol_b);
           } else {
-            tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES), &map_b_hi, bar, kb * GEMM_BK, n0);
+            tma_load_2d_pair_hint(smem_u32(sp + PAIR_A_BYTES), &map_b_hi, bar, kb * GEMM_BK, n0, pol_b);
           }
           if (MODE == 3) {
-            tma_load_2d_pair(smem_u32(sp + PAIR_A_BYTES + B_BYTES), &map_a_lo, bar, kb * GEMM_BK, m0);
+            tma_load_2d_pair_hint(smem_u32(sp + PAIR_A_BYTES + B_BYTES), &map_a_lo, bar, kb * GEMM_BK, m0, pol_a);
             if (DIRECT) {
 #pragma unroll
               for (int sl = 0; sl < SLABS; ++sl)
-                tma_load_2d_pair(smem_u32(sp + 2 * PAIR_A_BYTES + B_BYTES + sl * 4096), &map_b_lo, bar, n0 + 32 * sl,
-                                 kb * GEMM_BK);
+                tma_load_2d_pair_hint(smem_u32(sp + 2 * PAIR_A_BYTES + B_BYTES + sl * 4096), &map_b_lo, bar, n0 + 32 * sl,
+                                 kb * GEMM_BK, pol_b);
             } else {
-              tma_load_2d_pair(smem_u32(sp + 2 * PAIR_A_BYTES + B_BYTES), &map_b_lo, bar, kb * GEMM_BK, n0);
+              tma_load_2d_pair_hint(smem_u32(sp + 2 * PAIR_A_BYTES + B_BYTES), &map_b_lo, bar, kb * GEMM_BK, n0, pol_b);
             }
           }
           if (++stage == STAGES) {
@@ -237,7 +238,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   } else {
     // --------------------------------------------------------- epilogue
     const int quarter = warp & 3;
-    float* tbuf = epi_buf + (warp - 2) * (32 * 33);
+    float* tbuf = epi_buf + (warp - 2) * (32 * GEMM_EPI_LD);
     int local_tile = 0;
     bool ok = true;
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
@@ -254,52 +255,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         break;
       }
       tc_fence_after_sync();
-      const int rows_here = min(32, p.M - row0);
-#pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
-        const int col = n0 + chunk * 32 + lane;
-        if (n0 + chunk * 32 >= p.N) break;  // warp-uniform
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + chunk * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) tbuf[lane * 33 + j] = __uint_as_float(v[j]);
-        __syncwarp();
-        if (col < p.N) {
-          const float bias_v = p.bias ? p.bias[col] : 0.0f;
-          if (rows_here >= 32) {
-            // full 32-row slab: issue all 32 loads of C before the first use so that
-            // their latencies overlap instead of adding up
-            float cv[32];
-            if (p.C) {
-              const float* cp = p.C + static_cast<long long>(row0) * p.ldc + col;
-#pragma unroll
-              for (int rr = 0; rr < 32; ++rr) cv[rr] = cp[rr * p.ldc];
-            }
-            float* dp = p.D + static_cast<long long>(row0) * p.ldd + col;
-#pragma unroll
-            for (int rr = 0; rr < 32; ++rr) {
-              float x = p.alpha * tbuf[rr * 33 + lane];
-              if (p.C) x = fmaf(p.beta, cv[rr], x);
-              x += bias_v;
-              if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
-              dp[rr * p.ldd] = x;
-              if (p.n_replicas) store_replicas(p, static_cast<long long>(row0 + rr) * p.ldd + col, x);
-            }
-          } else {
-            for (int rr = 0; rr < rows_here; ++rr) {
-              const long long row = row0 + rr;
-              float x = p.alpha * tbuf[rr * 33 + lane];
-              if (p.C) x = fmaf(p.beta, p.C[row * p.ldc + col], x);
-              x += bias_v;
-              if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
-              p.D[row * p.ldd + col] = x;
-              if (p.n_replicas) store_replicas(p, row * p.ldd + col, x);
-            }
-          }
-        }
-        __syncwarp();
-      }
+      epilogue_rows<BN>(p, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN, tbuf, lane, row0, n0);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));

@@ -707,12 +707,29 @@ std::string generic_map_source(const KernelPlan& plan, const GenericMap& gm, con
   for (size_t i = 0; i < ni; ++i) o << "  const double X" << i << " = (double)x" << i << ";\n";
   for (size_t i = 0; i < no; ++i) o << "  const float t" << i << " = (float)(" << store_exprs[i] << ");\n  y" << i << " = t" << i << ";\n";
   o << "}\n";
-  // vector kernel: 2 x 128-bit per operand per thread per iteration
+  // vector kernel, one launch for any n: after `head` (0..3) single elements every operand is 16-byte aligned and
+  // nvec whole vectors follow; the ragged ends (head, and up to 3 elements after the vectors) are taken by the
+  // first threads of block 0
   o << "extern \"C\" __global__ void __launch_bounds__(256) sb200_map_vec(";
-  for (size_t i = 0; i < ni; ++i) o << "const float4* __restrict__ in" << i << ", ";
-  for (size_t i = 0; i < no; ++i) o << "float4* __restrict__ out" << i << ", ";
+  for (size_t i = 0; i < ni; ++i) o << "const float* __restrict__ sin" << i << ", ";
+  for (size_t i = 0; i < no; ++i) o << "float* __restrict__ sout" << i << ", ";
   for (size_t i = 0; i < ns; ++i) o << scalar_type(i) << " s" << i << ", ";
-  o << "long long nvec) {\n";
+  o << "int head, long long nvec, long long n) {\n";
+  o << "  if (blockIdx.x == 0) {\n";
+  o << "    const long long body_end = head + nvec * 4;\n";
+  o << "    const int ragged = head + (int)(n - body_end);\n";
+  o << "    if ((int)threadIdx.x < ragged) {\n";
+  o << "      const long long e = (int)threadIdx.x < head ? (long long)threadIdx.x : body_end + ((int)threadIdx.x - head);\n";
+  for (size_t i = 0; i < no; ++i) o << "      float r" << i << ";\n";
+  o << "      sb200_elem(";
+  for (size_t i = 0; i < ni; ++i) o << "sin" << i << "[e], ";
+  for (size_t i = 0; i < ns; ++i) o << "s" << i << ", ";
+  for (size_t i = 0; i < no; ++i) o << "r" << i << (i + 1 < no ? ", " : "");
+  o << ");\n";
+  for (size_t i = 0; i < no; ++i) o << "      sout" << i << "[e] = r" << i << ";\n";
+  o << "    }\n  }\n";
+  for (size_t i = 0; i < ni; ++i) o << "  const float4* __restrict__ in" << i << " = reinterpret_cast<const float4*>(sin" << i << " + head);\n";
+  for (size_t i = 0; i < no; ++i) o << "  float4* __restrict__ out" << i << " = reinterpret_cast<float4*>(sout" << i << " + head);\n";
   o << "  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {\n";
   for (size_t i = 0; i < ni; ++i) o << "    const float4 a" << i << " = in" << i << "[v];\n";
   for (size_t i = 0; i < no; ++i) o << "    float4 r" << i << ";\n";

@@ -10,8 +10,10 @@
 // the first use, so 2 inputs x 4 x 16 B are in flight per thread), evaluates
 // the expression in registers with explicit FMAs, and writes 128-bit vectors
 // with a streaming hint.  Nothing is re-read, so the traffic is the
-// algorithmic 4 bytes per element per operand.  The ragged tail (n mod 4, or
-// whole vectors when a pointer is not 16-byte aligned) takes a scalar path.
+// algorithmic 4 bytes per element per operand.  The ragged ends (up to 3 elements
+// before the first aligned vector and up to 3 after the last) are handled inside
+// the same launch; operands with differing misalignment take a scalar kernel.
+// Either way a map is exactly one launch.
 //
 // Arithmetic contract (what the parity tests check against the Native
 // backend's double-then-round result, <= 1 ulp): one fmaf per multiply-add,
@@ -69,13 +71,30 @@ __device__ __forceinline__ void apply4(const float4& x0, const float4& x1, float
   Op::apply(x0.w, x1.w, s, y0.w, y1.w);
 }
 
-// Vector body: elements [0, nvec*4); in0/in1/out0/out1 all 16-byte aligned.
-// Each block owns contiguous chunks of MAP_THREADS*MAP_UNROLL vectors so a
-// warp's accesses are 512-byte runs.
+// Vector body with ragged ends, one launch: the operands share one 16-byte misalignment, so after
+// `head` (0..3) leading elements all four pointers are 16-byte aligned and `nvec` whole vectors follow;
+// the up to 3 elements after them and the head are single elements handled by the first threads of
+// block 0 (a branch only the first warp of that block diverges on).  Each block owns contiguous chunks
+// of MAP_THREADS*MAP_UNROLL vectors so a warp's accesses are 512-byte runs.
 template <class Op>
 __global__ void __launch_bounds__(MAP_THREADS)
-map2_vec_kernel(const float4* __restrict__ in0, const float4* __restrict__ in1, float4* __restrict__ out0,
-                float4* __restrict__ out1, float s, long long nvec) {
+map2_vec_kernel(const float* __restrict__ sin0, const float* __restrict__ sin1, float* __restrict__ sout0,
+                float* __restrict__ sout1, float s, int head, long long nvec, long long n) {
+  if (blockIdx.x == 0) {
+    const long long body_end = head + nvec * 4;
+    const int ragged = head + static_cast<int>(n - body_end);  // at most 6
+    if (static_cast<int>(threadIdx.x) < ragged) {
+      const long long i = static_cast<int>(threadIdx.x) < head ? threadIdx.x : body_end + (threadIdx.x - head);
+      float y0, y1;
+      Op::apply(sin0[i], sin1[i], s, y0, y1);
+      sout0[i] = y0;
+      if (Op::kOutputs == 2) sout1[i] = y1;
+    }
+  }
+  const float4* __restrict__ in0 = reinterpret_cast<const float4*>(sin0 + head);
+  const float4* __restrict__ in1 = reinterpret_cast<const float4*>(sin1 + head);
+  float4* __restrict__ out0 = reinterpret_cast<float4*>(sout0 + head);
+  float4* __restrict__ out1 = Op::kOutputs == 2 ? reinterpret_cast<float4*>(sout1 + head) : nullptr;
   constexpr long long kChunk = static_cast<long long>(MAP_THREADS) * MAP_UNROLL;
   const long long nchunks = (nvec + kChunk - 1) / kChunk;
   for (long long c = blockIdx.x; c < nchunks; c += gridDim.x) {
@@ -108,8 +127,8 @@ map2_vec_kernel(const float4* __restrict__ in0, const float4* __restrict__ in1, 
   }
 }
 
-// Scalar path: elements [first, n).  Used for tails and for operands whose
-// addresses are not all 16-byte aligned (4-byte accesses stay coalesced).
+// Scalar path: elements [first, n).  Used for vectors shorter than one 128-bit vector after the head
+// and for operands whose addresses differ in their 16-byte misalignment (4-byte accesses stay coalesced).
 template <class Op>
 __global__ void __launch_bounds__(MAP_THREADS)
 map2_scalar_kernel(const float* __restrict__ in0, const float* __restrict__ in1, float* __restrict__ out0,

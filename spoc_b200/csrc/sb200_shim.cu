@@ -85,6 +85,9 @@ struct DeviceState {
   cudaEvent_t ws_event = nullptr;
   cudaStream_t ws_last_stream = nullptr;
   bool ws_in_use = false;
+  // held by a call from the moment it sizes the scratch until its launches are enqueued and its event recorded, so
+  // that another host thread cannot free and regrow the scratch under launches that already point into it
+  std::mutex scratch_mu;
   int* status = nullptr;  // device word written by kernels whose bounded waits expire
   std::map<uint64_t, uint64_t> allocs;  // base address -> bytes of every buffer sb200_mem_alloc handed out (ordered: range lookups)
   // kernel profiling (enable_profiling): event triples recorded around the GEMM stages
@@ -203,32 +206,23 @@ int launch_map2(DeviceState& d, cudaStream_t st, const float* in0, const float* 
     if (head > n) head = n;
     nvec = (n - head) >> 2;
   }
-  const long long body_end = head + nvec * 4;
-  if (head > 0) {
-    map2_scalar_kernel<Op><<<1, MAP_THREADS, 0, st>>>(in0, in1, out0, out1, s, 0, head);
-    int rc = launch_check("map head");
-    if (rc) return rc;
-  }
   if (nvec > 0) {
+    // one launch: vector body, with the ragged ends taken by the first threads of block 0
     const long long chunk = static_cast<long long>(MAP_THREADS) * MAP_UNROLL;
     const long long nchunks = (nvec + chunk - 1) / chunk;
     long long grid = nchunks;
     const long long cap = static_cast<long long>(d.sm_count) * 32;
     if (grid > cap) grid = cap;
-    map2_vec_kernel<Op><<<static_cast<unsigned>(grid), MAP_THREADS, 0, st>>>(
-        reinterpret_cast<const float4*>(in0 + head), reinterpret_cast<const float4*>(in1 + head),
-        reinterpret_cast<float4*>(out0 + head), Op::kOutputs == 2 ? reinterpret_cast<float4*>(out1 + head) : nullptr, s,
-        nvec);
-    int rc = launch_check("map body");
-    if (rc) return rc;
+    map2_vec_kernel<Op><<<static_cast<unsigned>(grid), MAP_THREADS, 0, st>>>(in0, in1, out0, Op::kOutputs == 2 ? out1 : nullptr, s,
+                                                                             static_cast<int>(head), nvec, n);
+    return launch_check("map body");
   }
-  if (body_end < n) {
-    const long long rem = n - body_end;
-    long long grid = (rem + MAP_THREADS - 1) / MAP_THREADS;
+  {
+    long long grid = (n + MAP_THREADS - 1) / MAP_THREADS;
     const long long cap = static_cast<long long>(d.sm_count) * 16;
     if (grid > cap) grid = cap;
-    map2_scalar_kernel<Op><<<static_cast<unsigned>(grid), MAP_THREADS, 0, st>>>(in0, in1, out0, out1, s, body_end, n);
-    int rc = launch_check("map tail");
+    map2_scalar_kernel<Op><<<static_cast<unsigned>(grid), MAP_THREADS, 0, st>>>(in0, in1, out0, out1, s, 0, n);
+    int rc = launch_check("map scalar");
     if (rc) return rc;
   }
   return SB200_OK;
@@ -309,6 +303,31 @@ int encode_map_2d(CUtensorMap* map, const float* base, long long inner, long lon
     return fail(SB200_ERR_INVALID_VALUE, "cuTensorMapEncodeTiled failed with CUresult %d (kp=%lld rows=%lld)", (int)r, kp,
                 rows);
   return SB200_OK;
+}
+
+std::atomic<int> g_l2_policy{-1};  // -1 = not yet read from the environment
+
+// Eviction-policy bits the GEMM kernels attach to their loads and stores (GemmParams::l2_policy);
+// SAREK_B200_L2_POLICY overrides the default for experiments.
+int l2_policy_setting() {
+  int v = g_l2_policy.load();
+  if (v < 0) {
+    const char* e = getenv("SAREK_B200_L2_POLICY");
+    v = e ? (atoi(e) & 63) : 0;
+    g_l2_policy.store(v);
+  }
+  return v;
+}
+
+// Fields of GemmParams that follow from the others: whether the epilogue may move 128-bit vectors, and the
+// eviction policies.
+void derive_params(GemmParams* gp) {
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  bool vec = (gp->N & 3) == 0 && al16(gp->D) && (gp->ldd & 3) == 0 && (!gp->C || (al16(gp->C) && (gp->ldc & 3) == 0)) &&
+             (!gp->bias || al16(gp->bias));
+  for (int r = 0; r < gp->n_replicas; ++r) vec = vec && al16(gp->replicas[r]);
+  gp->vec_epilogue = vec ? 1 : 0;
+  gp->l2_policy = l2_policy_setting();
 }
 
 size_t gemm_workspace_need(int mode, long long M, long long N, long long K) {
@@ -500,7 +519,9 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   // operand panels into the same memory at once.  Not while the stream is being captured into a graph (an
   // event of the capture cannot order work outside it): a captured sequence is ordered by its own stream.
   bool track_scratch = false;
+  std::unique_lock<std::mutex> scratch_lock(d.scratch_mu, std::defer_lock);
   if (route.workspace) {
+    scratch_lock.lock();
     rc = ensure_workspace(d, route.workspace);
     if (rc) return rc;
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
@@ -591,6 +612,7 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   GemmParams gp = gp_in;
   gp.num_k_blocks = static_cast<int>(kp / GEMM_BK);
   gp.status = d.status;
+  derive_params(&gp);
   if (prof) CU_TRY(cudaEventRecord(rec.e1, st));
   if (pair) {
     const int dev_index = static_cast<int>(&d - g_dev);
@@ -774,7 +796,6 @@ int launch_generic_map(DeviceState& d, KernelObj& k, const std::vector<Slot>& s,
     if (head > n) head = n;
     nvec = (n - head) >> 2;
   }
-  const long long body_end = head + nvec * 4;
   std::vector<double> sd(ns);
   std::vector<long long> si(ns);
   auto scalar_arg = [&](size_t i) -> void* {
@@ -801,24 +822,24 @@ int launch_generic_map(DeviceState& d, KernelObj& k, const std::vector<Slot>& s,
     count_launch();
     return SB200_OK;
   };
-  int rc;
-  if (head > 0 && (rc = run_scalar(0, head))) return rc;
   if (nvec > 0) {
-    std::vector<uint64_t> vp(ptrs);
-    for (auto& p : vp) p += static_cast<uint64_t>(head) * 4;
+    // one launch: the vector kernel takes the ragged ends in block 0
+    int head_i = static_cast<int>(head);
     std::vector<void*> args;
-    for (size_t i = 0; i < ni + no; ++i) args.push_back(&vp[i]);
+    for (size_t i = 0; i < ni + no; ++i) args.push_back(&ptrs[i]);
     for (size_t i = 0; i < ns; ++i) args.push_back(scalar_arg(i));
+    args.push_back(&head_i);
     args.push_back(&nvec);
+    args.push_back(&n);
     long long grid = (nvec + 255) / 256;
     const long long cap = static_cast<long long>(d.sm_count) * 8;
     if (grid > cap) grid = cap;
-    rc = jit_launch(jm->vec_fn, static_cast<unsigned>(grid), 256, st, args.data(), &err);
+    int rc = jit_launch(jm->vec_fn, static_cast<unsigned>(grid), 256, st, args.data(), &err);
     if (rc) return fail(rc, "kernel '%s': %s", k.plan.name.c_str(), err.c_str());
     count_launch();
+    return SB200_OK;
   }
-  if (body_end < n && (rc = run_scalar(body_end, n))) return rc;
-  return SB200_OK;
+  return run_scalar(0, n);
 }
 
 // out[b] = sum of f(inputs[gid]) over block b's elements, for the b < grid.x blocks of the reference launch
@@ -1581,6 +1602,13 @@ int sb200_set_gemm_variant(int variant) {
   return SB200_OK;
 }
 
+int sb200_set_l2_policy(int bits) {
+  if (bits < -1 || bits > 63 || (bits >= 0 && ((bits & 3) == 3 || ((bits >> 2) & 3) == 3 || ((bits >> 4) & 3) == 3)))
+    return fail(SB200_ERR_INVALID_VALUE, "L2 policy bits %d: three 2-bit fields, each 0 (normal), 1 (evict first) or 2 (evict last)", bits);
+  g_l2_policy.store(bits);
+  return SB200_OK;
+}
+
 int sb200_get_mode(int* mode) {
   if (!mode) return fail(SB200_ERR_INVALID_VALUE, "null mode pointer");
   *mode = current_mode();
@@ -1682,9 +1710,12 @@ int sb200_launch_count(uint64_t* count) {
 //    or different host threads) race on the panels; serialise them.
 //  * The first call on each device looks up the array's device address.  Make
 //    that first call before any stream capture begins.
-//  * The call returns after its kernels have finished (it waits on `stream`),
-//    so that a device-side wait that ran out of time is reported by the call
-//    that suffered it, as SB200_ERR_TIMEOUT.
+//  * Every call waits on `stream` until its kernels have finished and then reads
+//    a status word back with a synchronous copy, so that a device-side wait that
+//    ran out of time is reported by the call that suffered it, as
+//    SB200_ERR_TIMEOUT.  Do not issue it on a stream that is being captured.
+//  * Operands that lie inside buffers from sb200_mem_alloc are checked against
+//    the end of their buffer exactly as sb200_gemm_f32 does (SB200_ERR_BOUNDS).
 namespace {
 
 constexpr size_t kNoAllocScratchBytes = size_t(32) << 20;
@@ -1773,6 +1804,7 @@ int launch_gemm_fixed_scratch(const NoAllocDevice& nd, cudaStream_t st, long lon
   gp.tiles_m = static_cast<int>((M + GEMM_BM - 1) / GEMM_BM);
   gp.tiles_n = static_cast<int>((N + GEMM_BN - 1) / GEMM_BN);
   gp.status = nd.status;
+  derive_params(&gp);
   const long long tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n;
   const unsigned grid = static_cast<unsigned>(tiles < nd.sm_count ? tiles : nd.sm_count);
   gemm_tf32_kernel<MODE><<<grid, GEMM_THREADS, Cfg::kSmemBytes, st>>>(ma_hi, mb_hi, ma_lo, mb_lo, gp);
@@ -1807,6 +1839,17 @@ extern "C" int sb200_gemm_f32_noalloc(int dev, uint64_t stream, int mode, int64_
   NoAllocDevice* nd;
   int rc = noalloc_setup(dev, &nd);
   if (rc) return rc;
+  {
+    // operands inside buffers from sb200_mem_alloc must end inside them (a table lookup: allocates nothing)
+    DeviceState& ds = g_dev[dev];
+    auto extent = [](long long rows, long long cols, long long ld) { return static_cast<uint64_t>((rows - 1) * ld + cols) * 4; };
+    if (K > 0 && ((rc = check_extent(ds, A, extent(M, K, lda), "GEMM operand A")) ||
+                  (rc = check_extent(ds, B, extent(K, N, ldb), "GEMM operand B"))))
+      return rc;
+    if ((rc = check_extent(ds, D, extent(M, N, ldd), "GEMM result D")) || (rc = check_extent(ds, C, extent(M, N, ldc), "GEMM operand C")) ||
+        (rc = check_extent(ds, bias, static_cast<uint64_t>(N) * 4, "GEMM bias")))
+      return rc;
+  }
   cudaStream_t st = as_stream(stream);
   GemmParams gp;
   memset(&gp, 0, sizeof gp);
@@ -1932,7 +1975,11 @@ extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int6
     auto copy_in = [&](void* dst, const void* src, size_t bytes) -> int {
       if (bytes == 0) return 0;
       if (bytes >= (size_t(1) << 20) && host_memory_is_pageable(src)) return staged_copy_to_device(dev, dst, src, bytes, false);
-      return static_cast<int>(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice));
+      // a copy from pageable memory may return once the data is staged, before the DMA has landed, and the
+      // compute stream is non-blocking: wait for the legacy stream so that the kernel cannot read early
+      cudaError_t ce = cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice);
+      if (ce == cudaSuccess) ce = cudaStreamSynchronize(0);
+      return static_cast<int>(ce);
     };
     auto copy_out = [&](void* dst, const void* src, size_t bytes) -> int {
       if (bytes == 0) return 0;

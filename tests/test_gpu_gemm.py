@@ -653,16 +653,20 @@ def test_bounded_wait_gives_up_cleanly_and_the_device_stays_usable(backend, devi
 
 
 @pytest.mark.parametrize("mode", MODES)
-def test_gather_epilogue_writes_every_copy(backend, device, mode):
-    """sb200_gemm_f32_gather on one GPU: three copies of the gathered D in local memory; the row block must land
-    at its global row offset in each of them, identical to the plain operator, and nothing else may be touched."""
+@pytest.mark.parametrize("misaligned", [False, True], ids=["vector-stores", "scalar-stores"])
+def test_gather_epilogue_writes_every_copy(backend, device, mode, variant, misaligned):
+    """sb200_gemm_f32_gather on one GPU: three copies of the gathered D in local memory; the row block (a ragged
+    number of rows, at a row offset that is no tile edge) must land at its global row offset in each of them,
+    identical to the plain operator, and nothing else may be touched.  Run for every kernel variant, and for
+    copies that are 16-byte aligned (the epilogue stores 128-bit vectors) as well as copies that are not (it
+    stores single elements)."""
     import ctypes as C
     lib = L.load()
-    M_total, M_local, N, K, row_offset = 700, 300, 260, 200, 256
+    M_total, M_local, N, K, row_offset = 700, 301, 260, 200, 250
     a, b, c = O.fill(M_local * K, 51, 1), O.fill(K * N, 51, 2), O.fill(M_local * N, 51, 3)
     bias = O.fill(N, 51, 4, kind=1)
     A, B, Cm, Bi = (dev_from(backend, device, x) for x in (a, b, c, bias))
-    copies = [Dev(backend, device, M_total * N) for _ in range(3)]
+    copies = [Dev(backend, device, M_total * N, offset=(i % 2 + 1) if misaligned else 0) for i in range(3)]
     Dref = Dev(backend, device, M_local * N)
     try:
         ptrs = (C.c_uint64 * 3)(*[d.ptr for d in copies])
@@ -671,6 +675,8 @@ def test_gather_epilogue_writes_every_copy(backend, device, mode):
         assert rc == 0, lib.sb200_last_error_string()
         gemm(backend, device, mode, M_local, N, K, A, B, Dref, alpha=1.5, C_=Cm, beta=0.5, bias=Bi, act=1)
         want = Dref.download().reshape(M_local, N)
+        ref = O.gemm(a, b, M_local, N, K, 1.5, 0.5, c, bias, 1)
+        assert O.gemm_rel_error(want, ref) <= tol(mode, K) * 1.5 * math.sqrt(2)
         for d in copies:
             got = d.download().reshape(M_total, N)
             assert np.array_equal(got[row_offset:row_offset + M_local], want)
@@ -679,4 +685,63 @@ def test_gather_epilogue_writes_every_copy(backend, device, mode):
                                          0) == L.ERR_INVALID_VALUE
     finally:
         for x in [A, B, Cm, Bi, Dref] + copies:
+            x.free()
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_vector_and_scalar_epilogues_agree_bit_for_bit(backend, device, mode, variant):
+    """The epilogue stores 128-bit vectors when D, C and bias are 16-byte aligned with N a multiple of 4 and single
+    elements otherwise; both must give the same bits.  The same product is run into an aligned D and into a D that
+    starts 4 bytes later."""
+    M, N, K = 389, 516, 96
+    a, b, c = O.fill(M * K, 61, 1), O.fill(K * N, 61, 2), O.fill(M * N, 61, 3)
+    bias = O.fill(N, 61, 4, kind=1)
+    A, B, Cm, Bi = (dev_from(backend, device, x) for x in (a, b, c, bias))
+    D0, D1 = Dev(backend, device, M * N), Dev(backend, device, M * N, offset=1)
+    try:
+        gemm(backend, device, mode, M, N, K, A, B, D0, alpha=1.5, C_=Cm, beta=0.5, bias=Bi, act=1)
+        gemm(backend, device, mode, M, N, K, A, B, D1, alpha=1.5, C_=Cm, beta=0.5, bias=Bi, act=1)
+        x0, x1 = D0.download(), D1.download()
+        assert np.array_equal(x0, x1)
+        ref = O.gemm(a, b, M, N, K, 1.5, 0.5, c, bias, 1).ravel()
+        assert O.gemm_rel_error(x0, ref) <= tol(mode, K) * 1.5 * math.sqrt(2)
+    finally:
+        for x in (A, B, Cm, Bi, D0, D1):
+            x.free()
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_non_finite_operands_stay_confined_to_their_rows_and_columns(backend, device, mode, variant):
+    """An infinity, a NaN or a value at the edge of the float32 range in A or B reaches only the elements of D whose
+    row of A or column of B holds it; every other element must match the oracle as usual.  In TF32 mode the affected
+    elements follow the oracle's class (NaN where it has NaN, the same infinity where it has one; FLT_MAX rounds up to
+    an infinity in TF32, which the test allows for).  In 3xTF32 mode the split's cross terms can turn an infinity into
+    a NaN (Inf * 0 when the other operand has no low part), so there the affected elements only have to be
+    non-finite wherever the oracle is."""
+    M, N, K = 200, 264, 72
+    a, b = O.fill(M * K, 71, 1).reshape(M, K), O.fill(K * N, 71, 2).reshape(K, N)
+    a[3, 5], a[77, 0], a[150, 71] = np.inf, np.nan, -np.inf
+    b[9, 17], b[40, 200] = np.inf, np.float32(3.4028235e38)
+    bad_rows, bad_cols = [3, 77, 150], [17, 200]
+    A, B, D = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * N)
+    try:
+        gemm(backend, device, mode, M, N, K, A, B, D)
+        got = D.download().reshape(M, N)
+        with np.errstate(all="ignore"):
+            ref = O.gemm(a.ravel(), b.ravel(), M, N, K)
+        clean = np.ones((M, N), bool)
+        clean[bad_rows, :] = False
+        clean[:, bad_cols] = False
+        assert np.all(np.isfinite(got[clean]))
+        assert O.gemm_rel_error(got[clean], ref[clean]) <= tol(mode, K)
+        dirty = ~clean & ~np.isfinite(ref)
+        assert np.all(~np.isfinite(got[dirty]))
+        if mode == L.MODE_TF32:
+            nan_ref = np.isnan(ref) & ~clean
+            assert np.all(np.isnan(got[nan_ref]))
+            inf_ref = np.isinf(ref) & ~clean
+            inf_ref[:, 200] = False   # FLT_MAX in B rounds to +Inf in TF32: sign follows A, may also meet Inf - Inf
+            assert np.array_equal(got[inf_ref], ref[inf_ref])
+    finally:
+        for x in (A, B, D):
             x.free()

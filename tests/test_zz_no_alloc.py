@@ -72,3 +72,22 @@ def test_noalloc_gemm_rejects_sizes_beyond_its_fixed_scratch(backend, device):
         assert lib.sb200_gemm_f32_noalloc(device.id, 0, L.MODE_3XTF32, 0, 8, 8, 0, 8, 0, 8, 0, 8, 1.0, 0, 0, 0.0, 0, 0) == 0
     finally:
         D.free()
+
+
+def test_noalloc_gemm_checks_operand_extents_like_the_regular_entry_point(backend, device):
+    """A result matrix that lies in a library buffer and would run past its end is refused before anything is
+    launched, exactly as sb200_gemm_f32 refuses it: a wrong size must not become a memory fault."""
+    lib = L.load()
+    M, N, K = 64, 64, 64
+    A, B = Dev(backend, device, M * K), Dev(backend, device, K * N)
+    D_short = Dev(backend, device, M * N - 4096, pad=0)    # the buffer ends 4096 elements before D would
+    try:
+        rc = lib.sb200_gemm_f32_noalloc(device.id, 0, L.MODE_TF32, M, N, K, A.ptr, K, B.ptr, N, D_short.ptr, N,
+                                        1.0, 0, 0, 0.0, 0, 0)
+        assert rc == L.ERR_BOUNDS
+        assert "GEMM result D" in lib.sb200_last_error_string().decode()
+        rc = lib.sb200_gemm_f32(device.id, 0, L.MODE_TF32, M, N, K, A.ptr, K, B.ptr, N, D_short.ptr, N, 1.0, 0, 0, 0.0, 0, 0)
+        assert rc == L.ERR_BOUNDS
+    finally:
+        for x in (A, B, D_short):
+            x.free()
