@@ -17,7 +17,7 @@ from typing import Iterable, Sequence
 __all__ = [
     "sx", "Builder", "vector_add_ir", "stream_triad_ir", "matmul_naive_ir", "matmul_tiled_ir",
     "triad_producer_ir", "square_add_consumer_ir", "chain_fused_ir", "generic_example_ir",
-    "block_reduce_ir", "square_add_guarded_ir",
+    "block_reduce_ir", "square_add_guarded_ir", "vector_copy_ir",
 ]
 
 
@@ -96,6 +96,16 @@ def vector_add_ir(name: str = "sarek_kern") -> str:
         "sif", b.binop("lt", b.evar("tid"), b.evar("n")),
         ("assign", ("elem", "c", b.evar("tid")),
          b.binop("add", b.read("a", b.evar("tid")), b.read("b", b.evar("tid"))))))
+    return _kernel(name, p, body)
+
+
+def vector_copy_ir(name: str = "sarek_kern") -> str:
+    """benchmarks/bench_vector_copy.ml:22-30: b.(tid) <- a.(tid) under the guard tid < n."""
+    b = Builder()
+    p = b.params([("vec", "a", "f32"), ("vec", "b", "f32"), ("scalar", "n", "i32")])
+    body = b.let("tid", "i32", b.intr("global_thread_id"), lambda: (
+        "sif", b.binop("lt", b.evar("tid"), b.evar("n")),
+        ("assign", ("elem", "b", b.evar("tid")), b.read("a", b.evar("tid")))))
     return _kernel(name, p, body)
 
 
@@ -298,11 +308,16 @@ def generic_example_ir() -> str:
     return _kernel("generic_example", p, b.let("i", "i32", b.intr("global_thread_id"), body))
 
 
-def block_reduce_ir(kind: str = "dot", block: int = 256) -> str:
+def block_reduce_ir(kind: str = "dot", block: int = 256, name: str | None = None, final_superstep: bool | None = None) -> str:
     """The shared-memory tree reductions of the reference: kind "sum" is reduce_sum_kernel
     (benchmarks/bench_reduction.ml:62-105), kind "dot" is dot_product_kernel
     (benchmarks/bench_dot_product.ml:17-57).  One let%superstep per line of the source:
-    load, then reduce<block/2> ... reduce1, then the final guarded store."""
+    load, then reduce<block/2> ... reduce1, then the final guarded store.  The reference's generated code shows
+    the final store of reduce_sum as a superstep of its own (a block followed by a barrier,
+    benchmarks/descriptions/generated/reduction_generated.md) and that of dot_product as a plain statement
+    (dot_product_generated.md); final_superstep selects the form and defaults to that difference."""
+    if final_superstep is None:
+        final_superstep = kind != "dot"
     b = Builder()
     if kind == "dot":
         p = b.params([("vec", "a", "f32"), ("vec", "b", "f32"), ("vec", "output", "f32"), ("scalar", "n", "i32")])
@@ -316,7 +331,7 @@ def block_reduce_ir(kind: str = "dot", block: int = 256) -> str:
                 ("assign", ("elem", "sdata", tid), b.c_f32(0.0)))
         final = ("sif", b.binop("eq", tid, b.c_i32(0)),
                  ("assign", ("elem", "output", b.intr("block_idx_x")), b.read("sdata", b.c_i32(0))))
-        chain = final
+        chain = ("seq", ("block", final), ("barrier",), ("empty",)) if final_superstep else final
         c = 1
         tree = []
         while c < block:
@@ -333,4 +348,4 @@ def block_reduce_ir(kind: str = "dot", block: int = 256) -> str:
         b.let("tid", "i32", b.intr("thread_idx_x"), lambda:
         b.let("gid", "i32", b.binop("add", b.intr("thread_idx_x"), b.binop("mul", b.intr("block_dim_x"), b.intr("block_idx_x"))),
               steps)))
-    return _kernel("dot_product" if kind == "dot" else "reduce_sum", p, body)
+    return _kernel(name or ("dot_product" if kind == "dot" else "reduce_sum"), p, body)

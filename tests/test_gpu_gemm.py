@@ -511,11 +511,80 @@ def test_config_1024_cubed_full_compare(backend, device, mode, variant):
             x.free()
 
 
+def _download(backend, device, lib, buf, first_elem, count):
+    import ctypes as C
+    from spoc_b200.plugin import _check
+    host = np.empty(count, np.float32)
+    _check(lib.sb200_memcpy_dtoh(device.id, host.ctypes.data_as(C.c_void_p), buf.ptr + 4 * first_elem, 4 * count))
+    return host
+
+
+def _columns_of(backend, device, lib, buf, M, N, cols, chunk_rows=2048):
+    """Columns `cols` of a device-resident M x N matrix, fetched in row chunks so that host memory stays bounded."""
+    out = np.empty((M, len(cols)), np.float32)
+    for r0 in range(0, M, chunk_rows):
+        r1 = min(M, r0 + chunk_rows)
+        out[r0:r1] = _download(backend, device, lib, buf, r0 * N, (r1 - r0) * N).reshape(r1 - r0, N)[:, cols]
+    return out
+
+
+def _full_config_check(backend, device, lib, mode, M, N, K, A, B, D, seed, alpha=1.0, beta=0.0, Cm=None, Bi=None, act=0,
+                       n_rows=64, n_cols=64, n_points=4096, scale=1.0):
+    """The sample the benchmark configurations are checked on: n_rows full rows (first and last included), n_cols full
+    columns (first and last included) and n_points random elements of the device result against the oracle, which
+    sees the operands exactly as the device holds them (A and B are read back whole, C and D by rows and by column
+    chunks).  Oracle rows and columns are evaluated on a thread per host core."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+    rng = np.random.default_rng(seed)
+    a = _download(backend, device, lib, A, 0, M * K)
+    b = _download(backend, device, lib, B, 0, K * N)
+    bias = _download(backend, device, lib, Bi, 0, N) if Bi is not None else None
+    rows = sorted(set(rng.integers(0, M, n_rows - 2).tolist()) | {0, M - 1})
+    cols = sorted(set(rng.integers(0, N, n_cols - 2).tolist()) | {0, N - 1})
+    pr, pc = rng.integers(0, M, n_points), rng.integers(0, N, n_points)
+    need = sorted(set(rows) | set(pr.tolist()))
+    index = {r: i for i, r in enumerate(need)}
+    d_s = np.vstack([_download(backend, device, lib, D, r * N, N) for r in need])
+    c_s = np.vstack([_download(backend, device, lib, Cm, r * N, N) for r in need]) if Cm is not None else None
+    a_s = np.ascontiguousarray(a.reshape(M, K)[need]).ravel()
+    c_flat = c_s.ravel() if c_s is not None else None
+    workers = max(1, (os.cpu_count() or 2) - 1)
+    bound = tol(mode, K) * scale
+    with ThreadPoolExecutor(workers) as pool:
+        ri = [index[r] for r in rows]
+        ref_rows = np.vstack(list(pool.map(
+            lambda i: O.gemm(a_s, b, len(need), N, K, alpha, beta, c_flat, bias, act, r0=i, r1=i + 1), ri)))
+        rms = float(np.sqrt(np.mean(ref_rows.astype(np.float64) ** 2)))
+        err = np.abs(d_s[ri].astype(np.float64) - ref_rows) / np.maximum(np.abs(ref_rows), rms)
+        assert err.max() <= bound, f"rows: {err.max()} above {bound}"
+        # columns: each sampled column is handed to the oracle as a problem of its own with N = 1 — B, C and the
+        # bias restricted to that column — so that the oracle walks contiguous memory
+        d_c = _columns_of(backend, device, lib, D, M, N, cols)
+        c_c = _columns_of(backend, device, lib, Cm, M, N, cols) if Cm is not None else None
+        b2 = b.reshape(K, N)
+        nc = len(cols)
+
+        def one_col(j):
+            b_col = np.ascontiguousarray(b2[:, cols[j]])
+            c_col = np.ascontiguousarray(c_c[:, j]) if c_c is not None else None
+            bias_col = np.ascontiguousarray(bias[cols[j]:cols[j] + 1]) if bias is not None else None
+            return O.gemm_cols(a, b_col, M, 1, K, [0], alpha, beta, c_col, bias_col, act)
+
+        ref_cols = np.hstack(list(pool.map(one_col, range(nc))))
+        err = np.abs(d_c.astype(np.float64) - ref_cols) / np.maximum(np.abs(ref_cols), rms)
+        assert err.max() <= bound, f"columns: {err.max()} above {bound}"
+    pi = np.array([index[r] for r in pr.tolist()])
+    ref_pts = O.gemm_points(a_s, b, N, K, pi, pc, alpha, beta, c_flat, bias, act)
+    err = np.abs(d_s[pi, pc].astype(np.float64) - ref_pts) / np.maximum(np.abs(ref_pts), rms)
+    assert err.max() <= bound, f"points: {err.max()} above {bound}"
+    return a
+
+
 @pytest.mark.parametrize("mode", MODES)
 def test_config_8192_cubed_epilogue_sampled(backend, device, mode):
-    """M=N=K=8192 with D = max(0, 1.5 A.B + 0.5 C + bias): 16 rows + 16 columns + 1024 points
+    """M=N=K=8192 with D = max(0, 1.5 A.B + 0.5 C + bias): 64 rows + 64 columns + 4096 points
     against the oracle, inputs generated on the device and read back for the oracle."""
-    import ctypes as C
     from spoc_b200.plugin import _check
     lib = L.load()
     M = N = K = 8192
@@ -527,73 +596,18 @@ def test_config_8192_cubed_epilogue_sampled(backend, device, mode):
             _check(lib.sb200_fill_f32(device.id, 0, buf.ptr, cnt, 20260101, sid, kind, 1.0, 0))
         _check(lib.sb200_gemm_f32(device.id, 0, mode, M, N, K, A.ptr, K, B.ptr, N, D.ptr, N, 1.5, Cm.ptr, N, 0.5, Bi.ptr, 1))
         backend.Device.synchronize(device)
-        a, b, c = (np.empty(M * K, np.float32) for _ in range(3))
-        got = np.empty(M * N, np.float32)
-        bias = np.empty(N, np.float32)
-        for host, buf in ((a, A), (b, B), (c, Cm), (got, D), (bias, Bi)):
-            backend.Memory.device_to_host(src=buf, dst=host)
-        assert np.array_equal(a[:4096], O.fill(4096, 20260101, 1))
-        got = got.reshape(M, N)
-        rng = np.random.default_rng(1)
-        bound = tol(mode, K) * 1.5 * math.sqrt(2)
-        rms = None
-        rows = sorted(set(rng.integers(0, M, 14).tolist()) | {0, M - 1})
-        ref_rows = np.vstack([O.gemm(a, b, M, N, K, 1.5, 0.5, c, bias, 1, r0=r, r1=r + 1) for r in rows])
-        rms = float(np.sqrt(np.mean(ref_rows.astype(np.float64) ** 2)))
-        err = np.abs(got[rows].astype(np.float64) - ref_rows) / np.maximum(np.abs(ref_rows), rms)
-        assert err.max() <= bound
-        cols = sorted(set(rng.integers(0, N, 14).tolist()) | {0, N - 1})
-        ref_cols = O.gemm_cols(a, b, M, N, K, cols, 1.5, 0.5, c, bias, 1)
-        err = np.abs(got[:, cols].astype(np.float64) - ref_cols) / np.maximum(np.abs(ref_cols), rms)
-        assert err.max() <= bound
-        pr, pc = rng.integers(0, M, 1024), rng.integers(0, N, 1024)
-        ref_pts = O.gemm_points(a, b, N, K, pr, pc, 1.5, 0.5, c, bias, 1)
-        err = np.abs(got[pr, pc].astype(np.float64) - ref_pts) / np.maximum(np.abs(ref_pts), rms)
-        assert err.max() <= bound
+        a = _full_config_check(backend, device, lib, mode, M, N, K, A, B, D, 1, alpha=1.5, beta=0.5, Cm=Cm, Bi=Bi, act=1,
+                               scale=1.5 * math.sqrt(2))
+        assert np.array_equal(a[:4096], O.fill(4096, 20260101, 1)), "device fill differs from the host generator"
     finally:
         for x in bufs + [Bi]:
             backend.Memory.free(x)
 
 
-def _sampled_check(backend, device, lib, mode, M, N, K, A, B, D, a_rows_needed, rng, alpha=1.0, beta=0.0, Cm=None, Bi=None, act=0,
-                   n_rows=4, n_points=512, scale=1.0):
-    """Compare sampled rows and points of a device result with the oracle, downloading only what is needed:
-    all of B, the sampled rows of A (and of C)."""
-    import ctypes as C
-    from spoc_b200.plugin import _check
-    b = np.empty(K * N, np.float32)
-    backend.Memory.device_to_host(src=B, dst=b)
-    bias = None
-    if Bi is not None:
-        bias = np.empty(N, np.float32)
-        backend.Memory.device_to_host(src=Bi, dst=bias)
-    rows = sorted(set(rng.integers(0, M, n_rows).tolist()) | {0, M - 1})
-    pr, pc = rng.integers(0, M, n_points), rng.integers(0, N, n_points)
-    need = sorted(set(rows) | set(pr.tolist()))
-    index = {r: i for i, r in enumerate(need)}
-    a_s, c_s, d_s = np.empty((len(need), K), np.float32), np.empty((len(need), N), np.float32), np.empty((len(need), N), np.float32)
-    for i, r in enumerate(need):
-        _check(lib.sb200_memcpy_dtoh(device.id, a_s[i].ctypes.data_as(C.c_void_p), A.ptr + 4 * r * K, 4 * K))
-        _check(lib.sb200_memcpy_dtoh(device.id, d_s[i].ctypes.data_as(C.c_void_p), D.ptr + 4 * r * N, 4 * N))
-        if Cm is not None:
-            _check(lib.sb200_memcpy_dtoh(device.id, c_s[i].ctypes.data_as(C.c_void_p), Cm.ptr + 4 * r * N, 4 * N))
-    a_flat, c_flat = a_s.ravel(), (c_s.ravel() if Cm is not None else None)
-    # the oracle sees the sampled rows as a small matrix whose row i is original row need[i]
-    ri = [index[r] for r in rows]
-    ref_rows = np.vstack([O.gemm(a_flat, b, len(need), N, K, alpha, beta, c_flat, bias, act, r0=i, r1=i + 1) for i in ri])
-    rms = float(np.sqrt(np.mean(ref_rows.astype(np.float64) ** 2)))
-    bound = tol(mode, K) * scale
-    err = np.abs(d_s[ri].astype(np.float64) - ref_rows) / np.maximum(np.abs(ref_rows), rms)
-    assert err.max() <= bound
-    pi = np.array([index[r] for r in pr.tolist()])
-    ref_pts = O.gemm_points(a_flat, b, N, K, pi, pc, alpha, beta, c_flat, bias, act)
-    err = np.abs(d_s[pi, pc].astype(np.float64) - ref_pts) / np.maximum(np.abs(ref_pts), rms)
-    assert err.max() <= bound
-
-
 @pytest.mark.parametrize("mode", MODES)
 def test_config_skinny_65536x4096x4096_normal_inputs_sampled(backend, device, mode):
-    """M=65536, N=K=4096; A rows N(0,1), B N(0, 1/sqrt(K)) generated on the device; plain product."""
+    """M=65536, N=K=4096; A rows N(0,1), B N(0, 1/sqrt(K)) generated on the device; plain product;
+    64 rows + 64 columns + 4096 points against the oracle."""
     from spoc_b200.plugin import _check
     lib = L.load()
     M, N, K = 65536, 4096, 4096
@@ -603,7 +617,8 @@ def test_config_skinny_65536x4096x4096_normal_inputs_sampled(backend, device, mo
         _check(lib.sb200_fill_f32(device.id, 0, B.ptr, K * N, 20260101, 2, 2, 1.0 / math.sqrt(K), 0))
         _check(lib.sb200_gemm_f32(device.id, 0, mode, M, N, K, A.ptr, K, B.ptr, N, D.ptr, N, 1.0, 0, 0, 0.0, 0, 0))
         backend.Device.synchronize(device)
-        _sampled_check(backend, device, lib, mode, M, N, K, A, B, D, None, np.random.default_rng(4), n_rows=8, n_points=1024)
+        a = _full_config_check(backend, device, lib, mode, M, N, K, A, B, D, 4)
+        assert np.array_equal(a[:4096], O.fill(4096, 20260101, 1, kind=2)), "device normal fill differs from the host generator"
     finally:
         for x in (A, B, D):
             backend.Memory.free(x)
@@ -611,7 +626,7 @@ def test_config_skinny_65536x4096x4096_normal_inputs_sampled(backend, device, mo
 
 def test_config_32768_cubed_epilogue_sampled(backend, device):
     """M=N=K=32768 with D = max(0, 1.5 A.B + 0.5 C + bias), 3xTF32, on one GPU (the 8-GPU configuration's
-    single-device reference run: 4 x 4 GiB operands + 16 GiB of panels); sampled rows and points."""
+    single-device reference run: 4 x 4 GiB operands + 8 GiB of low-part panels); 64 rows + 64 columns + 4096 points."""
     from spoc_b200.plugin import _check
     lib = L.load()
     M = N = K = 32768
@@ -623,8 +638,8 @@ def test_config_32768_cubed_epilogue_sampled(backend, device):
             _check(lib.sb200_fill_f32(device.id, 0, buf.ptr, cnt, 20260101, sid, kind, 1.0, 0))
         _check(lib.sb200_gemm_f32(device.id, 0, mode, M, N, K, A.ptr, K, B.ptr, N, D.ptr, N, 1.5, Cm.ptr, N, 0.5, Bi.ptr, 1))
         backend.Device.synchronize(device)
-        _sampled_check(backend, device, lib, mode, M, N, K, A, B, D, None, np.random.default_rng(5), alpha=1.5, beta=0.5, Cm=Cm,
-                       Bi=Bi, act=1, n_rows=2, n_points=256, scale=1.5 * math.sqrt(2))
+        _full_config_check(backend, device, lib, mode, M, N, K, A, B, D, 5, alpha=1.5, beta=0.5, Cm=Cm, Bi=Bi, act=1,
+                           scale=1.5 * math.sqrt(2))
     finally:
         for x in (A, B, Cm, D, Bi):
             backend.Memory.free(x)

@@ -5,6 +5,7 @@ Native backend rounds a double result once: they differ only in double-rounding
 corner cases), bit-exact for vector_add.
 """
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
@@ -181,9 +182,11 @@ def test_fused_chain_ir_runs_in_one_pass(backend, device, oracle):
         v.free()
 
 
-def test_full_size_chain_properties(backend, device, oracle):
-    """N = 2^28 (the benchmark size): sampled blocks against the oracle, plus the
-    size-independent property that the fused pass equals two unfused passes bit for bit."""
+def test_full_size_chain_every_element(backend, device, oracle):
+    """N = 2^28 (the benchmark size), every element: the fused pass d = (b + 3c)^2 + b against the oracle's two
+    unfused kernels (<= 1 ulp), the same pass with the intermediate kept (d2 must equal d bit for bit, a <= 1 ulp
+    from the oracle's intermediate), and the device generator against the host generator (bit for bit).  The
+    vectors are walked in chunks of 2^24 elements so that host memory stays bounded."""
     lib = L.load()
     n = 1 << 28
     bufs = [backend.Memory.alloc(device, n, np.float32) for _ in range(5)]
@@ -192,21 +195,25 @@ def test_full_size_chain_properties(backend, device, oracle):
         _check(lib.sb200_fill_f32(device.id, 0, b.ptr, n, 20260101, 2, 0, 1.0, 0))
         _check(lib.sb200_fill_f32(device.id, 0, c.ptr, n, 20260101, 3, 0, 1.0, 0))
         _check(lib.sb200_chain_triad_square_f32(device.id, 0, d.ptr, 0, b.ptr, c.ptr, 3.0, n))
-        # unfused: a = b + 3c (triad) then d2 = a*a + b computed as chain-keep's second output check
         _check(lib.sb200_chain_triad_square_f32(device.id, 0, d2.ptr, a.ptr, b.ptr, c.ptr, 3.0, n))
         backend.Device.synchronize(device)
-        blk = 1 << 16
-        for start in (0, 12345 * 4, n // 2 - 7, n - blk):
+        blk = 1 << 24
+        workers = max(1, (os.cpu_count() or 2) - 1)
+        got = {k: np.empty(blk, np.float32) for k in "bcda2"}
+        exact = total = 0
+        for start in range(0, n, blk):
             hb, hc = O.fill(blk, 20260101, 2, first=start), O.fill(blk, 20260101, 3, first=start)
-            got_b = np.empty(blk, np.float32)
-            _check(lib.sb200_memcpy_dtoh(device.id, got_b.ctypes.data_as(C.c_void_p), b.ptr + 4 * start, 4 * blk))
-            assert np.array_equal(got_b, hb), "device fill differs from the host generator"
+            for key, src in (("b", b), ("c", c), ("d", d), ("a", a), ("2", d2)):
+                _check(lib.sb200_memcpy_dtoh(device.id, got[key].ctypes.data_as(C.c_void_p), src.ptr + 4 * start, 4 * blk))
+            assert np.array_equal(got["b"], hb) and np.array_equal(got["c"], hc), "device fill differs from the host generator"
             ref, ref_a = np.empty(blk, np.float32), np.empty(blk, np.float32)
-            oracle.so_chain_triad_square(ref, ref_a.ctypes.data_as(C.c_void_p), hb, hc, 3.0, blk)
-            for src, want in ((d, ref), (d2, ref), (a, ref_a)):
-                got = np.empty(blk, np.float32)
-                _check(lib.sb200_memcpy_dtoh(device.id, got.ctypes.data_as(C.c_void_p), src.ptr + 4 * start, 4 * blk))
-                assert O.ulp_distance(got, want).max() <= 1
+            oracle.so_par_chain_triad_square(ref, ref_a, hb, hc, 3.0, blk, workers)
+            assert np.array_equal(got["d"], got["2"]), "eliminating the intermediate changed the result"
+            dist = O.ulp_distance(got["d"], ref)
+            assert dist.max() <= 1 and O.ulp_distance(got["a"], ref_a).max() <= 1
+            exact += int((dist == 0).sum())
+            total += blk
+        assert exact / total > 0.99
     finally:
         for x in bufs:
             backend.Memory.free(x)
