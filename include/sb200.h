@@ -38,6 +38,7 @@ extern "C" {
 #define SB200_ERR_NO_DEVICE (-8)       /* no sm_100 device / CUDA unavailable */
 #define SB200_ERR_TOO_LARGE (-9)       /* size beyond a stated maximum */
 #define SB200_ERR_ALIGNMENT (-10)      /* pointer or leading dimension misaligned */
+#define SB200_ERR_COMM (-11)           /* NCCL could not be loaded or one of its calls failed */
 
 /* ---- numeric mode of the GEMM ------------------------------------------ */
 #define SB200_MODE_3XTF32 3 /* split accumulation, fp32-grade accuracy (default) */
@@ -255,6 +256,53 @@ SB200_API int sb200_gemm_f32_gather(int dev, uint64_t stream, int mode, int64_t 
 SB200_API int sb200_ipc_export(int dev, uint64_t dptr, void *handle64);
 SB200_API int sb200_ipc_open(int dev, const void *handle64, uint64_t *dptr);
 SB200_API int sb200_ipc_close(int dev, uint64_t dptr);
+
+/* ---- one process, several GPUs ------------------------------------------------------------------------
+ * The reference's host is a single process whose multi-device model is to partition a vector and launch once
+ * per device (sarek/core/Vector.ml:273-296, split rule sarek/core/Vector_storage.ml:261-272: the first
+ * `total mod parts` parts get one element more); it binds peer access (sarek-cuda/Cuda_bindings.ml:472-493)
+ * and never uses it.  A group is that model for the GEMM path: 1 to 8 distinct GPUs of this process (devices ==
+ * NULL means 0..ngpus-1), each with its own streams; with more than one GPU the library loads NCCL (dlopen of
+ * libnccl.so.2) and creates one communicator per GPU (ncclCommInitAll), and enables peer access between the
+ * members.  Errors in the arguments (size, device index out of range or repeated) are reported before any GPU
+ * work; SB200_ERR_COMM means NCCL could not be loaded or failed. */
+SB200_API int sb200_group_create(int ngpus, const int *devices, uint64_t *group);
+SB200_API int sb200_group_destroy(uint64_t group);
+SB200_API int sb200_group_size(uint64_t group, int *ngpus);
+SB200_API int sb200_group_device(uint64_t group, int index, int *dev);
+/* rows [first, first+count) of part `index` when `total` rows are split into `parts` (Vector_storage.ml:261-272) */
+SB200_API int sb200_row_block(int64_t total, int parts, int index, int64_t *first, int64_t *count);
+/* Row-sharded D = act(alpha*A.B + beta*C + bias) on device-resident operands.  a_shards[i] / c_shards[i] (table or
+ * entries may be 0 when there is no C) hold member i's row block of A / C on member i's GPU; B (ldb == N when the
+ * group has more than one GPU) and bias lie on the first member's GPU and are replicated into group-owned buffers
+ * on the others with ncclBroadcast at every call, unless SB200_SHARD_B_RESIDENT says that the replicas made by the
+ * previous call (same B, bias and sizes) are still valid.  Without a gather flag d[i] is member i's row block of D.
+ * With SB200_SHARD_GATHER_FUSED or SB200_SHARD_GATHER_NCCL d[i] is a whole M x N copy of D on member i's GPU and
+ * every copy is complete on return: FUSED stores each finished tile into all copies from the GEMM epilogue (plain
+ * peer stores over NVLink, overlapping the tensor-core work; needs peer access between all members), NCCL runs
+ * the GEMM into the member's own rows and then gathers in place (ncclAllGather, or one ncclBroadcast per block
+ * when M does not divide; needs ldd == N).  All forms give the same bits.  The call returns when every member's
+ * stream has finished; sb200_group_last_ms then gives the device time of the call (CUDA events around the
+ * member's work, maximum over members). */
+#define SB200_SHARD_GATHER_FUSED 1
+#define SB200_SHARD_GATHER_NCCL 2
+#define SB200_SHARD_B_RESIDENT 4
+SB200_API int sb200_gemm_sharded(uint64_t group, int mode, int64_t M, int64_t N, int64_t K,
+                                 const uint64_t *a_shards, int64_t lda, uint64_t b, int64_t ldb,
+                                 const uint64_t *d, int64_t ldd, float alpha,
+                                 const uint64_t *c_shards, int64_t ldc, float beta, uint64_t bias, int act, int flags);
+SB200_API int sb200_group_last_ms(uint64_t group, float *ms);
+/* The same on HOST operands, the multi-GPU form of sb200_gemm_f32_host below: B and the bias cross PCIe once, to
+ * the first GPU, and reach the others over NVLink (ncclBroadcast); each GPU pulls only its own rows of A and C
+ * and pushes only its own rows of D over its own PCIe link, driven by a host thread of its own, in row chunks so
+ * that copies in, GEMM and copies out overlap.  Pinned memory is copied asynchronously, contiguous pageable
+ * memory through the staged copier.  Returns when D is complete in host memory.  Replaces, for several devices,
+ * Transfer.to_device of every argument, one launch per device and Transfer.to_cpu
+ * (sarek/core/Transfer.ml:229-322, sarek/core/Vector.ml:273-296). */
+SB200_API int sb200_gemm_sharded_host(uint64_t group, int mode, int64_t M, int64_t N, int64_t K,
+                                      const float *A, int64_t lda, const float *B, int64_t ldb,
+                                      float *D, int64_t ldd, float alpha, const float *C, int64_t ldc,
+                                      float beta, const float *bias, int act);
 
 /* The same operator on HOST operands.  Pinned memory (sb200_host_alloc) gives full
  * overlap with asynchronous copies: 15.9 ms at 8192^3.  Contiguous pageable operands

@@ -15,7 +15,8 @@ LIB_PATH = os.path.join(HERE, "libsarek_b200.so")
 # status codes (include/sb200.h)
 OK = 0
 ERR_INVALID_VALUE, ERR_INVALID_HANDLE, ERR_UNSUPPORTED, ERR_PARSE, ERR_ARGS = -1, -2, -3, -4, -5
-ERR_BOUNDS, ERR_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE, ERR_ALIGNMENT = -6, -7, -8, -9, -10
+ERR_BOUNDS, ERR_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE, ERR_ALIGNMENT, ERR_COMM = -6, -7, -8, -9, -10, -11
+SHARD_GATHER_FUSED, SHARD_GATHER_NCCL, SHARD_B_RESIDENT = 1, 2, 4
 MODE_3XTF32, MODE_TF32 = 3, 1
 ACT_NONE, ACT_RELU = 0, 1
 KIND_MAP, KIND_GEMM_NAIVE, KIND_GEMM_TILED, KIND_BLOCK_REDUCE = 1, 2, 3, 4
@@ -85,6 +86,15 @@ SIGNATURES = {
     "sb200_gemm_f32": ([i32, u64, i32, i64, i64, i64, u64, i64, u64, i64, u64, i64, f32, u64, i64, f32, u64, i32], i32),
     "sb200_gemm_f32_noalloc": ([i32, u64, i32, i64, i64, i64, u64, i64, u64, i64, u64, i64, f32, u64, i64, f32, u64, i32], i32),
     "sb200_gemm_f32_gather": ([i32, u64, i32, i64, i64, i64, u64, i64, u64, i64, p(u64), i32, i64, i64, f32, u64, i64, f32, u64, i32], i32),
+    "sb200_group_create": ([i32, p(i32), p(u64)], i32),
+    "sb200_group_destroy": ([u64], i32),
+    "sb200_group_size": ([u64, p(i32)], i32),
+    "sb200_group_device": ([u64, i32, p(i32)], i32),
+    "sb200_row_block": ([i64, i32, i32, p(i64), p(i64)], i32),
+    "sb200_gemm_sharded": ([u64, i32, i64, i64, i64, p(u64), i64, u64, i64, p(u64), i64, f32, p(u64), i64, f32, u64, i32, i32], i32),
+    "sb200_group_last_ms": ([u64, p(f32)], i32),
+    "sb200_gemm_sharded_host": ([u64, i32, i64, i64, i64, C.c_void_p, i64, C.c_void_p, i64, C.c_void_p, i64, f32, C.c_void_p, i64,
+                                 f32, C.c_void_p, i32], i32),
     "sb200_ipc_export": ([i32, u64, C.c_void_p], i32),
     "sb200_ipc_open": ([i32, C.c_void_p, p(u64)], i32),
     "sb200_ipc_close": ([i32, u64], i32),

@@ -13,13 +13,13 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsarek_b200.so")
 
-SOURCES = ["sb200_shim.cu", "ir.cc", "fusion.cc", "map_jit.cc", "transfer.cc"]
-HEADERS = ["gemm_tcgen05.cuh", "gemm_tcgen05_pair.cuh", "map_fused.cuh", "ptx_sm100.cuh", "ir.hpp", "map_jit.hpp", "transfer.hpp",
+SOURCES = ["sb200_shim.cu", "sb200_group.cu", "ir.cc", "fusion.cc", "map_jit.cc", "transfer.cc"]
+HEADERS = ["gemm_tcgen05.cuh", "gemm_tcgen05_pair.cuh", "map_fused.cuh", "ptx_sm100.cuh", "ir.hpp", "map_jit.hpp", "transfer.hpp", "internal.hpp",
            os.path.join("..", "..", "include", "sb200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared", "-cudart", "static",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared", "-cudart", "static", "-ldl",
 ]
 
 

@@ -27,6 +27,7 @@
 #include "../../include/sb200.h"
 #include "gemm_tcgen05.cuh"
 #include "gemm_tcgen05_pair.cuh"
+#include "internal.hpp"
 #include "ir.hpp"
 #include "map_fused.cuh"
 #include "map_jit.hpp"
@@ -970,6 +971,18 @@ int launch_gemm_kernel(DeviceState& d, const KernelPlan& plan, const std::vector
 }
 
 }  // namespace
+
+namespace sb200 {
+int set_error(int code, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+}  // namespace sb200
 
 // =========================================================================
 // C ABI

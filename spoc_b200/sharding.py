@@ -33,3 +33,61 @@ def row_block(m: int, world: int, rank: int) -> tuple[int, int]:
 def gather_counts(m: int, n: int, world: int) -> list[int]:
     """Element counts of each rank's block of a row-major m x n result, in rank order."""
     return [rows * n for _, rows in partition(m, world)]
+
+
+class DeviceGroup:
+    """Several GPUs of this process driven through the library's group entry points (include/sb200.h:
+    sb200_group_create, sb200_gemm_sharded, sb200_gemm_sharded_host).  The library owns the streams, the NCCL
+    communicators and the replicas of B; this class only passes pointers and sizes, like the ctypes-foreign
+    binding of an OCaml host would."""
+
+    GATHER_NONE, GATHER_FUSED, GATHER_NCCL = 0, 1, 2
+
+    def __init__(self, devices=None, ngpus: int | None = None):
+        import ctypes as C
+        from . import _lib as L
+        from .plugin import _check
+        self._C, self._L, self._check = C, L, _check
+        self._lib = L.load()
+        if devices is None:
+            devices = list(range(ngpus if ngpus is not None else 1))
+        self.devices = list(devices)
+        arr = (C.c_int * len(self.devices))(*self.devices)
+        h = C.c_uint64(0)
+        _check(self._lib.sb200_group_create(len(self.devices), arr, C.byref(h)))
+        self.handle = h.value
+
+    def __len__(self) -> int:
+        return len(self.devices)
+
+    def row_block(self, m: int, index: int) -> tuple[int, int]:
+        C = self._C
+        first, count = C.c_int64(0), C.c_int64(0)
+        self._check(self._lib.sb200_row_block(m, len(self.devices), index, C.byref(first), C.byref(count)))
+        return first.value, count.value
+
+    def gemm(self, mode: int, m: int, n: int, k: int, a_shards, b: int, d, *, alpha=1.0, c_shards=None, beta=0.0, bias: int = 0,
+             act: int = 0, gather: int = 0, b_resident: bool = False, lda=None, ldb=None, ldc=None, ldd=None) -> float:
+        """Device-resident operands (device pointers as integers); returns the device time of the call in ms."""
+        C, L = self._C, self._L
+        g = len(self.devices)
+        tab = lambda xs: (C.c_uint64 * g)(*[int(x or 0) for x in xs])
+        flags = {0: 0, 1: L.SHARD_GATHER_FUSED, 2: L.SHARD_GATHER_NCCL}[gather] | (L.SHARD_B_RESIDENT if b_resident else 0)
+        self._check(self._lib.sb200_gemm_sharded(self.handle, mode, m, n, k, tab(a_shards), k if lda is None else lda, int(b),
+                                                 n if ldb is None else ldb, tab(d), n if ldd is None else ldd, alpha,
+                                                 tab(c_shards) if c_shards is not None else None, n if ldc is None else ldc, beta,
+                                                 int(bias), act, flags))
+        ms = C.c_float(0)
+        self._check(self._lib.sb200_group_last_ms(self.handle, C.byref(ms)))
+        return ms.value
+
+    def gemm_host(self, mode: int, m: int, n: int, k: int, a, b, d, *, alpha=1.0, c=None, beta=0.0, bias=None, act: int = 0) -> None:
+        """Host operands (numpy float32 arrays, row-major contiguous); D is written in place."""
+        ptr = lambda x: None if x is None else x.ctypes.data
+        self._check(self._lib.sb200_gemm_sharded_host(self.handle, mode, m, n, k, ptr(a), k, ptr(b), n, ptr(d), n, alpha, ptr(c), n,
+                                                      beta, ptr(bias), act))
+
+    def close(self) -> None:
+        if self.handle:
+            self._check(self._lib.sb200_group_destroy(self.handle))
+            self.handle = 0
