@@ -36,7 +36,16 @@ M = N = K = 8192
 SEED = 20260101
 MAP_N = 1 << 28
 METRIC = "fp32_gemm_fused_epilogue_8192cubed"
-WORKLOAD = "gemm M=N=K=8192 fp32, D=max(0,1.5*A.B+0.5*C+bias[col]), 3xTF32 split accumulation"
+WORKLOAD = "gemm M=N=K=8192 fp32 in/out, D=max(0,1.5*A.B+0.5*C+bias[col]), seeded uniform inputs (BASELINE configs[2])"
+NOMINAL_TF32_TFLOPS = 1100.0   # dense TF32 tensor peak of a B200, nominal
+NOMINAL_HBM_GBS = 8000.0
+
+
+def make_config(args) -> dict:
+    """The `config` of the JSON line: the same dict in both arms (what differs between the arms — arithmetic,
+    threads, sampling — is said in `dtype`, `cpu_baseline` and `arm`)."""
+    return {"workload": WORKLOAD, "rows_per_gpu": M, "l2": "inputs larger than L2 (4 x 256 MiB per GPU)",
+            "sharding": "row blocks of A/C/D per GPU, B replicated (NCCL broadcast) before the timed region"}
 
 
 def load_peaks() -> dict:
@@ -184,6 +193,11 @@ def cpu_slab_rate(workers: int, target_s: float):
 
 
 def run_reference(args, rank: int, world: int) -> None:
+    """The reference's own CPU implementation of the path, timed on this box's host cores: Sarek's Native backend runs
+    the kernel on (cores - 1) OCaml domains (sarek/sarek/Sarek_cpu_runtime.ml:1190); with no OCaml toolchain on the
+    box the C restatement of that backend (oracle/native_oracle.c, same partition of the global ids over the workers,
+    same double arithmetic) is what runs.  Each step computes a bounded slab of output elements of the 8192^3
+    problem with the fused epilogue; the full-problem time is extrapolated linearly from it."""
     if rank != 0:
         return
     workers = max(1, (os.cpu_count() or 2) - 1)
@@ -196,15 +210,20 @@ def run_reference(args, rank: int, world: int) -> None:
     dt = time.perf_counter() - t0
     flops = 2.0 * K * ids * args.steps
     value = flops / dt / 1e12
+    sample_ms = dt / args.steps * 1e3
+    full_ms = sample_ms * (float(M) * N / ids)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": full_ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f64 accumulate, f32 store", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": "inputs larger than any cache"},
+        "config": make_config(args),
+        "arm": {"threads": workers, "sample_ms_per_step": sample_ms, "sample_elements_per_step": ids,
+                "note": f"ms_per_step is extrapolated: the time of one full 8192^3 step at the rate measured on a slab of {ids} "
+                        f"output elements ({ids / N:.2f} rows) per step on {workers} threads"},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": workers, "kind": "port",
-                         "sample": f"first {ids} output elements ({ids / N:.2f} rows) of the 8192^3 problem per step; "
-                                   "C restatement of Sarek Native (no OCaml toolchain here), faster than the real OCaml "
-                                   "backend because it has none of its per-element boxing"},
+                         "sample": f"first {ids} output elements ({ids / N:.2f} rows) of the 8192^3 problem per step, "
+                                   f"extrapolated to the full problem; C restatement of Sarek Native (no OCaml toolchain here), "
+                                   "faster than the real OCaml backend because it has none of its per-element boxing"},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -217,22 +236,16 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     import torch
     import torch.distributed as dist
 
-    from spoc_b200 import Backend, _lib as L
+    from spoc_b200 import _lib as L
     from spoc_b200.build import build_library
     from spoc_b200.plugin import _check
 
     if not os.path.exists(L.LIB_PATH):
         build_library()
-    lib = L.load()  # raises when the CUDA library is missing: there is no fallback
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    backend = Backend()
-    backend.Device.init()
-    dev = backend.Device.get(local_rank)
-    backend.Device.set_current(dev)
-    tdev = torch.device("cuda", local_rank)
-    stream = torch.cuda.current_stream().cuda_stream
+    L.load()  # raises when the CUDA library is missing: there is no fallback
+    ctx = Ctx(rank, local_rank, world)
+    lib, backend, dev, tdev, stream = ctx.lib, ctx.backend, ctx.dev, ctx.tdev, ctx.stream
+    host_group = dist.new_group(backend="gloo") if world > 1 else None   # host-side barrier: parks ranks without GPU work
     peaks = load_peaks()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -375,56 +388,100 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             burst["clocks"] = sampler.summary(t_b0, t_b1)
 
     # ---- e2e: host buffers, copies inside the timed region ---------------------------------
-    hA = torch.empty(M * K, dtype=torch.float32).pin_memory()
-    hB = torch.empty(K * N, dtype=torch.float32).pin_memory()
-    hC = torch.empty(M * N, dtype=torch.float32).pin_memory()
-    hbias = torch.empty(N, dtype=torch.float32).pin_memory()
-    hD = torch.empty(M * N, dtype=torch.float32).pin_memory()
-    for h, d in ((hA, A), (hB, B), (hC, Cm), (hbias, bias)):
-        h.copy_(d)
-    torch.cuda.synchronize()
+    # One GPU: the headline is the plugin path itself — Execute.run_vectors on the epilogue kernel's IR with host-resident
+    # vectors in ordinary pageable memory (what a Bigarray is): Transfer.to_device of every argument, the launch,
+    # Transfer.to_cpu of the result, one after the other as in the reference.  The direct operator on pinned and on
+    # pageable buffers (one C-ABI call that overlaps copies and row-block GEMMs) is reported beside it.
+    # Several GPUs: the call a single-process host makes, sb200_gemm_sharded_host on a group of all the GPUs — B
+    # crosses PCIe once and reaches the other GPUs by NCCL broadcast, every GPU moves only its own rows — issued by
+    # rank 0 on pageable operands of world x 8192 rows while the other ranks wait at a host-side barrier with
+    # nothing running on their GPUs.
+    e2e = None
+    e2e_bytes_in, e2e_bytes_out = 4 * (M * K + K * N + M * N + N), 4 * M * N
+    if world == 1:
+        hA = torch.empty(M * K, dtype=torch.float32).pin_memory()
+        hB = torch.empty(K * N, dtype=torch.float32).pin_memory()
+        hC = torch.empty(M * N, dtype=torch.float32).pin_memory()
+        hbias = torch.empty(N, dtype=torch.float32).pin_memory()
+        hD = torch.empty(M * N, dtype=torch.float32).pin_memory()
+        for h, d in ((hA, A), (hB, B), (hC, Cm), (hbias, bias)):
+            h.copy_(d)
+        torch.cuda.synchronize()
 
-    def e2e_step():
-        # the call a user with host data makes: one C-ABI call, copies inside it
-        _check(lib.sb200_gemm_f32_host(dev.id, L.MODE_3XTF32, M, N, K, hA.data_ptr(), K, hB.data_ptr(), N, hD.data_ptr(), N,
-                                       1.5, hC.data_ptr(), N, 0.5, hbias.data_ptr(), L.ACT_RELU))
+        def e2e_pinned_step():
+            _check(lib.sb200_gemm_f32_host(dev.id, L.MODE_3XTF32, M, N, K, hA.data_ptr(), K, hB.data_ptr(), N, hD.data_ptr(), N,
+                                           1.5, hC.data_ptr(), N, 0.5, hbias.data_ptr(), L.ACT_RELU))
 
-    s3 = max(3, min(args.steps, 10))
-    ms3, _, _ = timed(e2e_step, s3, 2)
-    e2e = {"value": world * flops_step / (ms3 / s3 * 1e-3) / 1e12, "unit": "TFLOP/s",
-           "h2d_bytes_per_step": 4 * (M * K + K * N + M * N + N), "d2h_bytes_per_step": 4 * M * N,
-           "ms_per_step": ms3 / s3,
-           "api": "sb200_gemm_f32_host: pinned host A, B, C, bias in, D out; copies, row-block GEMMs and copy-out overlapped"}
-    # the same call on ordinary pageable host memory (what a Bigarray is): staged by host threads inside the call
-    pA, pB, pC, pD = (torch.empty(n, dtype=torch.float32) for n in (M * K, K * N, M * N, M * N))
-    pA.copy_(hA); pB.copy_(hB); pC.copy_(hC)
+        s3 = max(3, min(args.steps, 10))
+        ms3, _, _ = timed(e2e_pinned_step, s3, 2)
+        pA, pB, pC, pD = (torch.empty(n, dtype=torch.float32) for n in (M * K, K * N, M * N, M * N))
+        pA.copy_(hA); pB.copy_(hB); pC.copy_(hC)
 
-    def e2e_pageable_step():
-        _check(lib.sb200_gemm_f32_host(dev.id, L.MODE_3XTF32, M, N, K, pA.data_ptr(), K, pB.data_ptr(), N, pD.data_ptr(), N,
-                                       1.5, pC.data_ptr(), N, 0.5, hbias.data_ptr(), L.ACT_RELU))
+        def e2e_pageable_step():
+            _check(lib.sb200_gemm_f32_host(dev.id, L.MODE_3XTF32, M, N, K, pA.data_ptr(), K, pB.data_ptr(), N, pD.data_ptr(), N,
+                                           1.5, pC.data_ptr(), N, 0.5, hbias.data_ptr(), L.ACT_RELU))
 
-    ms5, _, _ = timed(e2e_pageable_step, 3, 1)
-    e2e["pageable_host_buffers"] = {"value": world * flops_step / (ms5 / 3 * 1e-3) / 1e12, "unit": "TFLOP/s",
-                                    "ms_per_step": ms5 / 3}
-    # the plugin path itself: Execute.run_vectors on the epilogue kernel's IR with host-resident vectors, i.e.
-    # Transfer.to_device of every argument, the launch, Transfer.to_cpu of the result, one after the other
-    from spoc_b200 import Vector, run_vectors, dims1d, sarek_ir
-    epi_ir = sarek_ir.matmul_naive_ir(epilogue=dict(alpha=1.5, beta=0.5, c="c", bias="bias", relu=True))
-    vecs = [Vector(backend, t.numpy()) for t in (pA, pB, pC)] + [Vector(backend, hbias.numpy().copy()), Vector(backend, pD.numpy())]
+        ms5, _, _ = timed(e2e_pageable_step, 3, 1)
+        from spoc_b200 import Vector, run_vectors, dims1d, sarek_ir
+        epi_ir = sarek_ir.matmul_naive_ir(epilogue=dict(alpha=1.5, beta=0.5, c="c", bias="bias", relu=True))
+        vecs = [Vector(backend, t.numpy()) for t in (pA, pB, pC)] + [Vector(backend, hbias.numpy().copy()), Vector(backend, pD.numpy())]
 
-    def plugin_step():
-        for v in vecs[:4]:
-            v.location = Vector.CPU          # the host copy is the valid one again: the next launch re-uploads it
-        run_vectors(backend, device=dev, ir=epi_ir, args=vecs + [("int32", M), ("int32", N), ("int32", K)],
-                    block=dims1d(256), grid=dims1d((M * N + 255) // 256))
-        vecs[4].to_array()
+        def plugin_step():
+            for v in vecs[:4]:
+                v.location = Vector.CPU          # the host copy is the valid one again: the next launch re-uploads it
+            run_vectors(backend, device=dev, ir=epi_ir, args=vecs + [("int32", M), ("int32", N), ("int32", K)],
+                        block=dims1d(256), grid=dims1d((M * N + 255) // 256))
+            vecs[4].to_array()
 
-    ms6, _, _ = timed(plugin_step, 3, 1)
-    e2e["plugin_run_vectors"] = {"value": world * flops_step / (ms6 / 3 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms6 / 3,
-                                 "note": "run_vectors on the kernel's IR, pageable host vectors, synchronous transfers as in the reference"}
-    for v in vecs:
-        v.free()
-    del hA, hB, hC, hD, pA, pB, pC, pD
+        s6 = max(3, min(args.steps, 5))
+        ms6, _, _ = timed(plugin_step, s6, 1)
+        e2e = {"value": flops_step / (ms6 / s6 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms6 / s6,
+               "h2d_bytes_per_step": e2e_bytes_in, "d2h_bytes_per_step": e2e_bytes_out,
+               "api": "Execute.run_vectors mirror (spoc_b200.plugin.run_vectors) on the epilogue kernel's IR: pageable host "
+                      "vectors, synchronous upload of A, B, C, bias, launch, download of D",
+               "direct_operator_pinned": {"value": flops_step / (ms3 / s3 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms3 / s3,
+                                          "api": "sb200_gemm_f32_host on pinned buffers: copies, row-block GEMMs and copy-out overlapped"},
+               "direct_operator_pageable": {"value": flops_step / (ms5 / 3 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms5 / 3,
+                                            "api": "sb200_gemm_f32_host on pageable buffers (staged copier)"}}
+        for v in vecs:
+            v.free()
+        del hA, hB, hC, hD, pA, pB, pC, pD
+    else:
+        from spoc_b200.sharding import DeviceGroup
+        torch.cuda.synchronize()
+        dist.barrier(group=host_group)
+        if rank == 0:
+          try:
+              Mg = M * world
+              gA, gC, gD = (np.empty(Mg * K, np.float32), np.empty(Mg * N, np.float32), np.empty(Mg * N, np.float32))
+              gB, gbias = B.cpu().numpy(), bias.cpu().numpy()
+              blockA, blockC = A.cpu().numpy(), Cm.cpu().numpy()
+              for r in range(world):                  # any finite data: the rate does not depend on the values
+                  gA[r * M * K:(r + 1) * M * K] = blockA
+                  gC[r * M * N:(r + 1) * M * N] = blockC
+              grp = DeviceGroup(list(range(world)))
+              call = lambda: grp.gemm_host(L.MODE_3XTF32, Mg, N, K, gA, gB, gD, alpha=1.5, c=gC, beta=0.5, bias=gbias, act=L.ACT_RELU)
+              call()
+              sg = 3
+              t0 = time.perf_counter()
+              for _ in range(sg):
+                  call()
+              ms_g = (time.perf_counter() - t0) / sg * 1e3
+              # the block of rank 0 must equal what this rank's own operator produced for the same rows
+              gemm(L.MODE_3XTF32)
+              torch.cuda.synchronize()
+              same = bool(np.array_equal(gD[:M * N], D.cpu().numpy()))
+              grp.close()
+              e2e = {"value": world * flops_step / (ms_g * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_g,
+                     "h2d_bytes_per_step": 4 * (Mg * K + K * N + Mg * N + N), "d2h_bytes_per_step": 4 * Mg * N,
+                     "api": "sb200_gemm_sharded_host on a group of all GPUs, one process (rank 0), pageable host operands of "
+                            f"{Mg} rows: B over PCIe once then NCCL broadcast, each GPU moves its own rows; wall clock of the call",
+                     "first_block_identical_to_single_gpu": same}
+              del gA, gC, gD
+          except Exception as ex:  # the line must still be printed: say what failed
+            e2e = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                   "error": f"{type(ex).__name__}: {ex}"}
+        dist.barrier(group=host_group)
 
     # ---- fused-map chain (HBM bound) ---------------------------------------------------------
     fused_map = None
@@ -449,6 +506,115 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
                                   "peak_source": f"{peaks['source']} copy bandwidth",
                                   "frac_of_nominal_8TBs": gbs / 8000.0}}
 
+    # ---- the other kernels of the path, the TF32 yardstick, the small configuration (one GPU only) -------------
+    reductions = small_triad = cfg1 = tf32_yardstick = None
+    if world == 1:
+        from spoc_b200 import sarek_ir, dims1d, dims2d
+        from spoc_b200.plugin import RSA_Buffer, RSA_Int32, RSA_Float32, _Memory
+        lang = backend.supported_source_langs[0]
+        buf_of = lambda t: _Memory.Buffer(dev.id, t.data_ptr(), t.numel(), 4)
+        # block tree reductions over the same 2^28-element vectors (benchmarks/bench_reduction.ml, bench_dot_product.ml)
+        nblocks = MAP_N // 256
+        part = torch.empty(nblocks, dtype=torch.float32, device=tdev)
+        reductions = {}
+        for kind, vecs_in, bytes_elem in (("dot", (b, c), 8.0), ("sum", (b,), 4.0)):
+            rs_args = []
+            for t in vecs_in + (part,):
+                rs_args += [RSA_Buffer(buf_of(t), t.numel()), RSA_Int32(t.numel())]
+            rs_args.append(RSA_Int32(MAP_N))
+            src = sarek_ir.block_reduce_ir(kind, 256)
+            fn = lambda: backend.run_source(source=src, lang=lang, kernel_name="k", block=dims1d(256), grid=dims1d(nblocks),
+                                            shared_mem=1024, args=rs_args)
+            msr, lr, _ = timed(fn, 10, 3)
+            g = (bytes_elem * MAP_N + 4.0 * nblocks) / (msr / 10 * 1e-3) / 1e9
+            reductions["dot_product" if kind == "dot" else "reduce_sum"] = {
+                "value": g, "unit": "GB/s", "ms_per_step": msr / 10, "launches_per_step": lr / 10,
+                "frac_of_measured_hbm": g / peaks["hbm_gbs"], "frac_of_nominal_8TBs": g / NOMINAL_HBM_GBS}
+        # stream_triad at the reference's own small benchmark size (10^6 elements): launch-latency territory; one launch
+        n_small = 1_000_000
+        tri_args = []
+        for t in (d, b, c):
+            tri_args += [RSA_Buffer(buf_of(t), n_small), RSA_Int32(n_small)]
+        tri_args += [RSA_Float32(3.0), RSA_Int32(n_small)]
+        tri_src = sarek_ir.stream_triad_ir()
+        tri = lambda: backend.run_source(source=tri_src, lang=lang, kernel_name="sarek_kern", block=dims1d(256),
+                                         grid=dims1d((n_small + 255) // 256), shared_mem=0, args=tri_args)
+        mst, lt, _ = timed(tri, 200, 20)
+        # the reference's own protocol: 5 warm-ups, then 20 x (launch + device synchronise) by the host clock, median
+        # (benchmarks/benchmark_runner.ml:24-30, benchmarks/common.ml:222-232)
+        walls = []
+        for it in range(25):
+            t0 = time.perf_counter()
+            tri()
+            _check(lib.sb200_device_synchronize(dev.id))
+            if it >= 5:
+                walls.append((time.perf_counter() - t0) * 1e6)
+        small_triad = {"n": n_small, "us_per_launch": mst / 200 * 1e3, "launches_per_step": lt / 200,
+                       "launch_plus_sync_median_us": statistics.median(walls),
+                       "reference_published_median_us": {"value": 14.07, "where": "benchmarks/results/drangleic_stream_triad_1000000_2026-01-12T17-51-33.json, CUDA backend on an RTX 5070 Ti (other hardware)"},
+                       "value": 12.0 * n_small / (mst / 200 * 1e-3) / 1e9, "unit": "GB/s",
+                       "note": "through run_source on the kernel's IR, back to back on one stream (inputs stay in L2 at this size)"}
+        del b, c, d, part
+        # configuration 1: 1024^3 through the tiled kernel's IR (cache-resident: a parity and CPU-baseline anchor)
+        S1 = 1024
+        t1 = [torch.empty(S1 * S1, dtype=torch.float32, device=tdev) for _ in range(3)]
+        fill(t1[0], 1, 0)
+        fill(t1[1], 2, 0)
+        mm_args = []
+        for t in t1:
+            mm_args += [RSA_Buffer(buf_of(t), t.numel()), RSA_Int32(t.numel())]
+        mm_args += [RSA_Int32(S1)] * 3
+        mm_src = sarek_ir.matmul_tiled_ir()
+        cfg1 = {"workload": "gemm M=N=K=1024 (BASELINE configs[0]) through the matrix_mul_tiled IR, block 16x16, grid 64x64"}
+        for mode, label in ((L.MODE_3XTF32, "3xtf32"), (L.MODE_TF32, "tf32")):
+            backend.set_mode(mode)
+            mm = lambda: backend.run_source(source=mm_src, lang=lang, kernel_name="sarek_kern", block=dims2d(16, 16),
+                                            grid=dims2d(S1 // 16, S1 // 16), shared_mem=0, args=mm_args)
+            ms1, _, _ = timed(mm, 100, 10)
+            cfg1[label] = {"us_per_launch": ms1 / 100 * 1e3, "value": 2.0 * S1 ** 3 / (ms1 / 100 * 1e-3) / 1e12, "unit": "TFLOP/s"}
+        backend.set_mode(L.MODE_3XTF32)
+        del t1
+        # yardstick: a TF32 library GEMM (cuBLAS through torch.matmul with TF32 allowed) at 8192^3, best of 10 and 4 s
+        # back to back — the measured dense-TF32 rate of this GPU, beside the nominal figure.  A yardstick only.
+        ya = torch.empty(M, K, dtype=torch.float32, device=tdev).uniform_(-1, 1)
+        yb = torch.empty(K, N, dtype=torch.float32, device=tdev).uniform_(-1, 1)
+        yc = torch.empty(M, N, dtype=torch.float32, device=tdev)
+        prev_tf32 = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+        time.sleep(0.5)
+        best = 1e9
+        for _ in range(3):
+            torch.matmul(ya, yb, out=yc)
+        torch.cuda.synchronize()
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(ya, yb, out=yc)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        t_y = time.time()
+        cnt = 0
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        while time.time() - t_y < 4.0:
+            for _ in range(20):
+                torch.matmul(ya, yb, out=yc)
+            cnt += 20
+            torch.cuda.synchronize()
+        e1.record()
+        torch.cuda.synchronize()
+        sustained_ms = e0.elapsed_time(e1) / cnt
+        torch.backends.cuda.matmul.allow_tf32 = prev_tf32
+        tf32_yardstick = {"library": "cuBLAS via torch.matmul, allow_tf32", "burst_tflops": flops_step / (best * 1e-3) / 1e12,
+                          "sustained_tflops": flops_step / (sustained_ms * 1e-3) / 1e12, "nominal_tflops": NOMINAL_TF32_TFLOPS}
+        del ya, yb, yc
+        torch.cuda.empty_cache()
+        for rf in (roofline, tf32_mode["roofline"]):
+            rf["frac_of_nominal_tf32_peak"] = rf["achieved"] / NOMINAL_TF32_TFLOPS
+            rf["frac_of_measured_tf32_library_sustained"] = rf["achieved"] / tf32_yardstick["sustained_tflops"]
+            rf["frac_of_measured_tf32_library_burst"] = rf["achieved"] / tf32_yardstick["burst_tflops"]
+
     # ---- CPU baseline (rank 0, N = 1 only) -----------------------------------------------------
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
@@ -457,17 +623,49 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         dt = step()
         cpu_baseline = {"value": 2.0 * K * ids / dt / 1e12, "unit": "TFLOP/s", "cores": workers, "kind": "port",
                         "sample": f"first {ids} output elements ({ids / N:.2f} rows) of the same 8192^3 problem, "
-                                  f"{dt:.1f} s; C restatement of Sarek Native's naive kernel with the epilogue"}
+                                  f"{dt:.1f} s, extrapolated; C restatement of Sarek Native's naive kernel with the epilogue"}
+        # the two configurations a CPU can run in full: 1024^3 on Native's tiled (barrier) path with all cores
+        # (sarek/sarek/Sarek_cpu_runtime.ml:1025), and the 2^28-element chain as two unfused kernels
+        import numpy as np
+        O = oracle_lib()
+        olib = O.load()
+        a1, b1, c1 = O.fill(1024 * 1024, SEED, 1), O.fill(1024 * 1024, SEED, 2), np.zeros(1024 * 1024, np.float32)
+        t0 = time.perf_counter()
+        olib.so_par_matmul_tiled(a1, b1, c1, 1024, 1024, 1024, 0, 64 * 64, workers + 1)
+        dt1 = time.perf_counter() - t0
+        cpu_baseline["config_1024cubed_tiled"] = {"value": 2.0 * 1024 ** 3 / dt1 / 1e12, "unit": "TFLOP/s", "seconds": dt1,
+                                                  "cores": workers + 1, "sample": "the full problem, tiled kernel, barrier path"}
+        hb, hc = O.fill(MAP_N, SEED, 2), O.fill(MAP_N, SEED, 3)
+        ha, hd = np.empty(MAP_N, np.float32), np.empty(MAP_N, np.float32)
+        t0 = time.perf_counter()
+        olib.so_par_chain_triad_square(hd, ha, hb, hc, 3.0, MAP_N, workers)
+        dt2 = time.perf_counter() - t0
+        cpu_baseline["config_chain_2p28_unfused"] = {"value": 12.0 * MAP_N / dt2 / 1e9, "unit": "GB/s (12 B per element, as the fused GPU pass)",
+                                                     "seconds": dt2, "cores": workers,
+                                                     "sample": "the full 2^28 elements, two unfused kernels (the second reads the stored intermediate)"}
+        del hb, hc, ha, hd
+
+    # ---- the strong-scaling configurations, at every N -----------------------------------------------------------
+    try:
+        del A, Cm
+    except NameError:
+        pass
+    del B, D
+    torch.cuda.empty_cache()
+    skinny = skinny_leg(ctx, max(3, min(args.steps, 10)), 3)
+    gather = gather_leg(ctx, args.gather_size, 3, 1)
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32x3 (f32 in/out)",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "rows_per_gpu": M, "l2": "inputs larger than L2 (4 x 256 MiB per GPU)", "preload_s": args.preload_s,
-                       "sharding": "row blocks of A/C/D per rank, B replicated by NCCL broadcast before the timed region"},
+            "config": make_config(args),
+            "arm": {"mode": "3xTF32 split accumulation on tcgen05 tensor cores", "preload_s": args.preload_s},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "burst": burst, "tf32_mode": tf32_mode, "fused_map": fused_map, "b_broadcast_ms": bcast_ms,
+            "reductions": reductions, "stream_triad_1e6": small_triad, "config_1024cubed": cfg1, "tf32_yardstick": tf32_yardstick,
+            "skinny_65536x4096x4096": skinny, f"gather_{args.gather_size}cubed": gather,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -597,30 +795,98 @@ def run_case(args) -> None:
     print(json.dumps({"case": args.case, "size": S, "ms_per_call": ms, "rate": work / (ms * 1e-3), "unit": unit}), flush=True)
 
 
-def run_gather(args, rank: int, local_rank: int, world: int) -> None:
-    """Strong-scaling run of the large square GEMM with epilogue and a gathered result: M = N = K = --size
-    (default 32768), rows of A/C/D split over the ranks, B replicated.  Two ways to leave the whole D on every
-    GPU are timed: the GEMM followed by an NCCL all-gather of the row blocks, and the GEMM whose epilogue stores
-    each tile into every GPU's copy (peer stores over NVLink)."""
-    import numpy as np
-    import torch
-    import torch.distributed as dist
+class Ctx:
+    """What the multi-GPU legs share: the library, this rank's device and stream, the process group."""
 
-    from spoc_b200 import Backend, _lib as L
+    def __init__(self, rank: int, local_rank: int, world: int):
+        import torch
+        import torch.distributed as dist
+        from spoc_b200 import Backend, _lib as L
+        self.torch, self.dist, self.L = torch, dist, L
+        self.lib = L.load()
+        self.rank, self.local_rank, self.world = rank, local_rank, world
+        torch.cuda.set_device(local_rank)
+        if world > 1 and not dist.is_initialized():
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        self.backend = Backend()
+        self.backend.Device.init()
+        self.dev = self.backend.Device.get(local_rank)
+        self.backend.Device.set_current(self.dev)
+        self.tdev = torch.device("cuda", local_rank)
+        self.stream = torch.cuda.current_stream().cuda_stream
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+
+    def max_over_ranks(self, x: float) -> float:
+        if self.world == 1:
+            return x
+        t = self.torch.tensor([x], dtype=self.torch.float64, device=self.tdev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def all_true(self, flag: bool) -> bool:
+        if self.world == 1:
+            return flag
+        t = self.torch.tensor([1 if flag else 0], device=self.tdev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    def timed(self, fn, steps: int, warmup: int) -> float:
+        """ms per step: CUDA events on the launch stream, a barrier and a synchronise on both sides, max over ranks."""
+        torch = self.torch
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        self.barrier()
+        return self.max_over_ranks(e0.elapsed_time(e1) / steps)
+
+
+def oracle_parity(ctx, D_rows_fn, A, B, M_rows, N, K, row_ids, a_row_fn, c_row_fn, bias, alpha, beta, act, bound_scale, mode_is_3x=True):
+    """Checker, outside every timed region: sampled rows x 64 random columns of a device result against the CPU
+    oracle (tests/oracle_lib.py).  The oracle sees B's sampled columns as the device holds them and regenerates the
+    rows of A and C with the host generator.  Returns (ok, worst error / bound)."""
+    import math
+    import numpy as np
+    O = oracle_lib()
+    torch = ctx.torch
+    rng = np.random.default_rng(1234 + ctx.rank)
+    cols = np.sort(rng.choice(N, size=min(64, N), replace=False))
+    tcols = torch.from_numpy(cols).to(ctx.tdev)
+    b_c = B.view(K, N).index_select(1, tcols).contiguous().cpu().numpy()            # K x 64, as the device holds B
+    a_s = np.vstack([a_row_fn(r) for r in row_ids])                                  # rows x K
+    c_s = np.vstack([c_row_fn(r)[cols] for r in row_ids]) if c_row_fn else None
+    bias_c = np.ascontiguousarray(bias[cols]) if bias is not None else None
+    ref = O.gemm(np.ascontiguousarray(a_s).ravel(), np.ascontiguousarray(b_c).ravel(), len(row_ids), len(cols), K, alpha, beta,
+                 None if c_s is None else np.ascontiguousarray(c_s).ravel(), bias_c, act)
+    got = np.vstack([D_rows_fn(r)[cols] for r in row_ids])
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2))) or 1.0
+    err = float(np.max(np.abs(got.astype(np.float64) - ref) / np.maximum(np.abs(ref), rms)))
+    bound = (1e-5 * math.sqrt(K) if mode_is_3x else 2e-3) * bound_scale
+    return err <= bound, err / bound
+
+
+def gather_leg(ctx, S: int, steps: int, warmup: int) -> dict:
+    """Strong scaling of the large square GEMM with epilogue and a gathered result (BASELINE configs[4]): M = N = K = S,
+    rows of A/C/D split over the ranks, B replicated by NCCL broadcast.  Two ways to leave the whole D on every GPU
+    are timed: the GEMM followed by an NCCL all-gather of the row blocks, and the GEMM whose epilogue stores each
+    tile into every GPU's copy (peer stores over NVLink).  The two forms alternate over three rounds so that a
+    drift of the clocks under the power cap hits both alike; each form's figure is the best of its rounds.  Sampled rows
+    of every rank's gathered copy — rows computed by every rank — are checked against the CPU oracle."""
+    import numpy as np
+    torch, dist, L, lib = ctx.torch, ctx.dist, ctx.L, ctx.lib
     from spoc_b200.plugin import _check
-    from spoc_b200.sharding import row_block
-    lib = L.load()
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    backend = Backend()
-    backend.Device.init()
-    dev = backend.Device.get(local_rank)
-    backend.Device.set_current(dev)
-    tdev = torch.device("cuda", local_rank)
-    stream = torch.cuda.current_stream().cuda_stream
-    S = args.size
+    from spoc_b200.sharding import row_block, partition
+    dev, stream, rank, world, tdev = ctx.dev, ctx.stream, ctx.rank, ctx.world, ctx.tdev
     r0, rows = row_block(S, world, rank)
 
     def fill(ptr, n, sid, kind, first=0):
@@ -637,10 +903,9 @@ def run_gather(args, rank: int, local_rank: int, world: int) -> None:
         fill(B.data_ptr(), B.numel(), 2, 0)
     if world > 1:
         dist.broadcast(B, src=0)
-    D_nccl = torch.empty(S * S, dtype=torch.float32, device=tdev)     # gathered by NCCL
-    D_own = backend.Memory.alloc(dev, S * S, np.float32)              # gathered by the epilogue (IPC-shareable memory)
-    copies = [D_own.ptr]
-    opened = []
+    D_nccl = torch.empty(S * S, dtype=torch.float32, device=tdev)        # gathered by NCCL
+    D_own = ctx.backend.Memory.alloc(dev, S * S, np.float32)              # gathered by the epilogue (IPC-shareable memory)
+    copies, opened = [D_own.ptr], []
     if world > 1:
         handle = C.create_string_buffer(64)
         _check(lib.sb200_ipc_export(dev.id, D_own.ptr, handle))
@@ -666,77 +931,82 @@ def run_gather(args, rank: int, local_rank: int, world: int) -> None:
         _check(lib.sb200_gemm_f32_gather(dev.id, stream, L.MODE_3XTF32, rows, S, S, A.data_ptr(), S, B.data_ptr(), S, ptrs,
                                          len(copies), r0, S, 1.5, Cm.data_ptr(), S, 0.5, bias.data_ptr(), L.ACT_RELU))
 
-    def timed(fn):
-        for _ in range(max(args.warmup, 1)):
-            fn()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        ms = e0.elapsed_time(e1) / args.steps
-        if world > 1:
-            t = torch.tensor([ms], dtype=torch.float64, device=tdev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+    rounds = {"nccl": [], "fused": []}
+    for rnd in range(3):
+        rounds["nccl"].append(ctx.timed(step_nccl, steps, warmup if rnd == 0 else 1))
+        rounds["fused"].append(ctx.timed(step_fused, steps, warmup if rnd == 0 else 1))
+    ms_nccl, ms_fused = min(rounds["nccl"]), min(rounds["fused"])
+    # the two gathered results must agree bit for bit on this rank (compared in slabs: no third 4 GiB buffer)
+    same = True
+    slab = max(1, (1 << 28) // S) * S
+    own_view = torch.empty(min(slab, S * S), dtype=torch.float32, device=tdev)
+    for off in range(0, S * S, slab):
+        cnt = min(slab, S * S - off)
+        _check(lib.sb200_memcpy_dtod(dev.id, own_view.data_ptr(), D_own.ptr + 4 * off, 4 * cnt))
+        same = same and bool(torch.equal(own_view[:cnt], D_nccl[off:off + cnt]))
+    same = ctx.all_true(same)
+    # oracle check of this rank's gathered copy: four rows out of every rank's block
+    O = oracle_lib()
+    rng = np.random.default_rng(99)
+    row_ids = []
+    for f, cnt in partition(S, world):
+        if cnt:
+            row_ids += sorted(set([f, f + cnt - 1] + (f + rng.integers(0, cnt, 2)).tolist()))
+    hbias = bias.cpu().numpy()
 
-    ms_nccl = timed(step_nccl)
-    ms_fused = timed(step_fused)
-    # the two gathered results must agree bit for bit on this rank
-    own = torch.empty(S * S, dtype=torch.float32, device=tdev)
-    _check(lib.sb200_memcpy_dtod(dev.id, own.data_ptr(), D_own.ptr, 4 * S * S))
-    same = bool(torch.equal(own, D_nccl))
-    if world > 1:
-        flag = torch.tensor([1 if same else 0], device=tdev)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        same = bool(flag.item())
-        dist.barrier()
+    def d_row(r):
+        out = np.empty(S, np.float32)
+        _check(lib.sb200_memcpy_dtoh(dev.id, out.ctypes.data_as(C.c_void_p), D_own.ptr + 4 * r * S, 4 * S))
+        return out
+
+    ok, rel = oracle_parity(ctx, d_row, A, B, S, S, S, row_ids, lambda r: O.fill(S, SEED, 1, first=r * S),
+                            lambda r: O.fill(S, SEED, 3, first=r * S), hbias, 1.5, 0.5, 1, 1.5 * 2 ** 0.5)
+    ok = ctx.all_true(ok)
+    rel = ctx.max_over_ranks(rel)
+    ctx.barrier()
     for pp in opened:
         _check(lib.sb200_ipc_close(dev.id, pp))
+    ctx.backend.Memory.free(D_own)
+    del A, Cm, B, D_nccl, own_view
+    torch.cuda.empty_cache()
     flops = 2.0 * S ** 3
+    nvlink_bytes = 4.0 * rows * S * (world - 1)       # what this rank's epilogue stores into its peers' copies per step
+    return {
+        "metric": f"fp32_gemm_fused_epilogue_{S}cubed_gathered", "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+        "scaling": "strong", "dtype": "tf32x3 (f32 in/out)",
+        "workload": f"gemm M=N=K={S} with epilogue (BASELINE configs[4]), rows of A/C/D split over the GPUs, whole D on every GPU",
+        "value": flops / (ms_fused * 1e-3) / 1e12, "ms_per_step": ms_fused,
+        "gemm_then_nccl_all_gather": {"value": flops / (ms_nccl * 1e-3) / 1e12, "ms_per_step": ms_nccl, "rounds_ms": rounds["nccl"]},
+        "gather_fused_in_epilogue": {"value": flops / (ms_fused * 1e-3) / 1e12, "ms_per_step": ms_fused, "rounds_ms": rounds["fused"],
+                                     "peer_store_bytes_per_gpu": nvlink_bytes,
+                                     "peer_store_gbs_per_gpu": nvlink_bytes / (ms_fused * 1e-3) / 1e9},
+        "results_identical": same, "parity_ok": ok, "parity_worst_over_bound": rel,
+        "parity": f"{len(row_ids)} rows (every rank's block) x 64 columns of each rank's gathered copy against the CPU oracle, "
+                  "bound 1e-5*sqrt(K)*1.5*sqrt(2) relative to max(|ref|, rms)"}
+
+
+def run_gather(args, rank: int, local_rank: int, world: int) -> None:
+    ctx = Ctx(rank, local_rank, world)
+    out = gather_leg(ctx, args.size, args.steps, max(args.warmup, 1))
     if rank == 0:
-        print(json.dumps({
-            "metric": f"fp32_gemm_fused_epilogue_{S}cubed_gathered", "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "scaling": "strong", "higher_is_better": True, "data": "synthetic", "dtype": "tf32x3 (f32 in/out)",
-            "config": {"workload": f"gemm M=N=K={S} with epilogue, rows of A/C/D split over the ranks, whole D on every GPU"},
-            "value": flops / (ms_fused * 1e-3) / 1e12, "ms_per_step": ms_fused,
-            "gemm_then_nccl_all_gather": {"value": flops / (ms_nccl * 1e-3) / 1e12, "ms_per_step": ms_nccl},
-            "gather_fused_in_epilogue": {"value": flops / (ms_fused * 1e-3) / 1e12, "ms_per_step": ms_fused},
-            "results_identical": same}), flush=True)
+        out.update({"warmup": max(args.warmup, 1), "higher_is_better": True, "data": "synthetic",
+                    "config": {"workload": out["workload"]}})
+        print(json.dumps(out), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        ctx.dist.destroy_process_group()
 
 
-def run_skinny(args, rank: int, local_rank: int, world: int) -> None:
-    """Strong-scaling run of the skinny GEMM: C = A.B with M = 65536, N = K = 4096, rows of A drawn from N(0,1),
-    B from N(0,1/sqrt(K)); rows of A and C split over the ranks, B broadcast from rank 0 (NCCL).  Timed twice:
-    with B already on every GPU, and with the broadcast of B inside every timed step."""
+def skinny_leg(ctx, steps: int, warmup: int) -> dict:
+    """Strong scaling of the skinny GEMM (BASELINE configs[3]): C = A.B with M = 65536, N = K = 4096, rows of A drawn
+    from N(0,1), B from N(0,1/sqrt(K)); rows of A and C split over the ranks, B broadcast from rank 0 (NCCL).  Timed
+    with B already on every GPU and with the broadcast of B inside every timed step, in both modes; sampled rows of
+    every rank's block are checked against the CPU oracle."""
     import math
-
-    import torch
-    import torch.distributed as dist
-
-    from spoc_b200 import Backend, _lib as L
+    import numpy as np
+    torch, dist, L, lib = ctx.torch, ctx.dist, ctx.L, ctx.lib
     from spoc_b200.plugin import _check
     from spoc_b200.sharding import row_block
-    lib = L.load()
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    backend = Backend()
-    backend.Device.init()
-    dev = backend.Device.get(local_rank)
-    backend.Device.set_current(dev)
-    tdev = torch.device("cuda", local_rank)
-    stream = torch.cuda.current_stream().cuda_stream
+    dev, stream, rank, world, tdev = ctx.dev, ctx.stream, ctx.rank, ctx.world, ctx.tdev
     Mt, Nn, Kk = 65536, 4096, 4096
     r0, rows = row_block(Mt, world, rank)
     A = torch.empty(rows * Kk, dtype=torch.float32, device=tdev)
@@ -748,7 +1018,8 @@ def run_skinny(args, rank: int, local_rank: int, world: int) -> None:
     if world > 1:
         dist.broadcast(B, src=0)
     torch.cuda.synchronize()
-    out = {}
+    O = oracle_lib()
+    out, parity_ok, parity_rel = {}, True, 0.0
     for mode, label in ((L.MODE_3XTF32, "3xtf32"), (L.MODE_TF32, "tf32")):
         def gemm():
             _check(lib.sb200_gemm_f32(dev.id, stream, mode, rows, Nn, Kk, A.data_ptr(), Kk, B.data_ptr(), Nn, Cm.data_ptr(), Nn,
@@ -760,36 +1031,39 @@ def run_skinny(args, rank: int, local_rank: int, world: int) -> None:
             gemm()
 
         for name, fn in (("b_resident", gemm), ("b_broadcast_timed", gemm_after_broadcast)):
-            for _ in range(max(args.warmup, 3)):
-                fn()
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(args.steps):
-                fn()
-            e1.record()
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
-            ms = e0.elapsed_time(e1) / args.steps
-            if world > 1:
-                t = torch.tensor([ms], dtype=torch.float64, device=tdev)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                ms = float(t.item())
+            ms = ctx.timed(fn, steps, max(warmup, 3))
             out.setdefault(label, {})[name] = {"ms_per_step": ms, "value": 2.0 * Mt * Nn * Kk / (ms * 1e-3) / 1e12}
-    if rank == 0:
-        print(json.dumps({
-            "metric": "fp32_gemm_65536x4096x4096_row_sharded", "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "scaling": "strong", "higher_is_better": True, "data": "synthetic",
-            "dtype": "tf32x3 (f32 in/out)",
-            "config": {"workload": "gemm M=65536 N=K=4096, A ~ N(0,1), B ~ N(0,1/sqrt(K)), rows of A/C split over the ranks, "
-                                   "B broadcast from rank 0 (64 MiB, NCCL)"},
+        rng = np.random.default_rng(7 + rank)
+        row_ids = sorted(set([0, rows - 1] + rng.integers(0, rows, 6).tolist()))
+        hC = Cm.view(rows, Nn)
+        ok, rel = oracle_parity(ctx, lambda r: hC[r].cpu().numpy(), A, B, rows, Nn, Kk, row_ids,
+                                lambda r: O.fill(Kk, SEED, 1, kind=2, first=(r0 + r) * Kk), None, None, 1.0, 0.0, 0, 1.0,
+                                mode_is_3x=(mode == L.MODE_3XTF32))
+        parity_ok = parity_ok and ok
+        parity_rel = max(parity_rel, rel)
+    parity_ok = ctx.all_true(parity_ok)
+    parity_rel = ctx.max_over_ranks(parity_rel)
+    del A, Cm, B
+    torch.cuda.empty_cache()
+    return {"metric": "fp32_gemm_65536x4096x4096_row_sharded", "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "scaling": "strong", "dtype": "tf32x3 and tf32 (f32 in/out)",
+            "workload": "gemm M=65536 N=K=4096 (BASELINE configs[3]), A ~ N(0,1), B ~ N(0,1/sqrt(K)), rows of A/C split over the "
+                        "GPUs, B broadcast from rank 0 (64 MiB, NCCL)",
             "value": out["3xtf32"]["b_resident"]["value"], "ms_per_step": out["3xtf32"]["b_resident"]["ms_per_step"],
-            "modes": out}), flush=True)
+            "modes": out, "parity_ok": parity_ok, "parity_worst_over_bound": parity_rel,
+            "parity": "8 rows of every rank's block x 64 columns against the CPU oracle in both modes "
+                      "(bounds 1e-5*sqrt(K) and 2e-3 relative to max(|ref|, rms))"}
+
+
+def run_skinny(args, rank: int, local_rank: int, world: int) -> None:
+    ctx = Ctx(rank, local_rank, world)
+    out = skinny_leg(ctx, args.steps, args.warmup)
+    if rank == 0:
+        out.update({"warmup": max(args.warmup, 3), "higher_is_better": True, "data": "synthetic",
+                    "config": {"workload": out["workload"]}})
+        print(json.dumps(out), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        ctx.dist.destroy_process_group()
 
 
 def main() -> None:
@@ -805,6 +1079,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather-size", type=int, default=32768, help="M = N = K of the gathered-result configuration in the default run")
     ap.add_argument("--preload-s", type=float, default=0.5,
                     help="seconds of untimed identical steps before the headline pass, so that it is measured at the "
                          "sustained clock; 0 measures the first pass on the idle GPU only")
