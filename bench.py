@@ -379,6 +379,21 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
                      "frac_of_burst_peak": flops_step / (main2 * 1e-3) / 1e12 / burst_peak,
                      "kernel_ms": main2, "prep_ms": prof2["prep_ms"] / max(prof2["calls"], 1)},
     }
+    # ---- the fp16 three-term split: fp32-grade accuracy (same bound as 3xTF32 on these inputs) at the fp16 tensor rate ---
+    s5 = max(3, min(args.steps, 10))
+    ms_h, _, prof_h = timed(lambda: gemm(L.MODE_3XF16), s5, 3, profile=True)
+    main_h = prof_h["main_ms"] / max(prof_h["calls"], 1)
+    f16_peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
+    f16_split_mode = {
+        "value": world * flops_step / (ms_h / s5 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_h / s5,
+        "note": "SB200_MODE_3XF16: operands scaled by powers of two and split hi + lo in fp16, three kind::f16 MMAs per k-step; "
+                "parity bound 1e-5*sqrt(K) as for 3xTF32 (tests/test_gpu_gemm.py::test_f16_split_*); not the headline because its "
+                "accuracy depends on the dynamic range inside each matrix",
+        "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel<4, false> (fp16 panels)", "achieved": flops_step / (main_h * 1e-3) / 1e12,
+                     "peak": f16_peak, "unit": "TFLOP/s", "frac": flops_step / (main_h * 1e-3) / 1e12 / f16_peak,
+                     "mma_frac": 3.0 * flops_step / (main_h * 1e-3) / 1e12 / f16_peak,
+                     "peak_source": f"{peaks['source']}: dense bf16/fp16 library GEMM, {'sustained' if sustained else 'burst'}",
+                     "kernel_ms": main_h, "prep_ms": prof_h["prep_ms"] / max(prof_h["calls"], 1)}}
     clocks = None
     if rank == 0:
         sampler.stop()
@@ -663,7 +678,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "config": make_config(args),
             "arm": {"mode": "3xTF32 split accumulation on tcgen05 tensor cores", "preload_s": args.preload_s},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-            "burst": burst, "tf32_mode": tf32_mode, "fused_map": fused_map, "b_broadcast_ms": bcast_ms,
+            "burst": burst, "tf32_mode": tf32_mode, "f16_split_mode": f16_split_mode, "fused_map": fused_map, "b_broadcast_ms": bcast_ms,
             "reductions": reductions, "stream_triad_1e6": small_triad, "config_1024cubed": cfg1, "tf32_yardstick": tf32_yardstick,
             "skinny_65536x4096x4096": skinny, f"gather_{args.gather_size}cubed": gather,
         }

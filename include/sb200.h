@@ -43,6 +43,13 @@ extern "C" {
 /* ---- numeric mode of the GEMM ------------------------------------------ */
 #define SB200_MODE_3XTF32 3 /* split accumulation, fp32-grade accuracy (default) */
 #define SB200_MODE_TF32 1   /* operands rounded to TF32 once, one MMA per k-step */
+#define SB200_MODE_3XF16 4  /* the same three-term split on half-precision panels (fp16 has TF32's 11 significant
+                               bits and twice its tensor-core rate): each matrix is scaled by a power of two so
+                               that its largest magnitude lies in [2^14, 2^15), split hi + lo in fp16, and the
+                               accumulators are scaled back exactly.  Same error class as 3xTF32 for matrices whose
+                               elements lie within about 2^16 of the largest one (smaller elements lose low bits of
+                               their low part: absolute error below 2^-39 of the largest element); about twice as
+                               fast.  sb200_gemm_f32 and sb200_gemm_f32_gather only. */
 
 /* ---- epilogue activation ------------------------------------------------ */
 #define SB200_ACT_NONE 0

@@ -76,10 +76,22 @@ let sb200_set_mode = fn "sb200_set_mode" (int @-> returning int)
 let sb200_ir_fuse_as =
   fn "sb200_ir_fuse_as" (string @-> string @-> string @-> int @-> ptr char @-> int @-> ptr int @-> returning int)
 
-exception B200_error of int * string
+(* one process, several GPUs (include/sb200.h: device groups) *)
+let sb200_group_create = fn "sb200_group_create" (int @-> ptr int @-> ptr uint64_t @-> returning int)
+let sb200_group_destroy = fn "sb200_group_destroy" (uint64_t @-> returning int)
+let sb200_row_block = fn "sb200_row_block" (int64_t @-> int @-> int @-> ptr int64_t @-> ptr int64_t @-> returning int)
+let sb200_gemm_sharded =
+  fn "sb200_gemm_sharded"
+    (uint64_t @-> int @-> int64_t @-> int64_t @-> int64_t @-> ptr uint64_t @-> int64_t @-> uint64_t @-> int64_t
+   @-> ptr uint64_t @-> int64_t @-> float @-> ptr uint64_t @-> int64_t @-> float @-> uint64_t @-> int @-> int
+   @-> returning int)
+let sb200_gemm_sharded_host =
+  fn "sb200_gemm_sharded_host"
+    (uint64_t @-> int @-> int64_t @-> int64_t @-> int64_t @-> ptr float @-> int64_t @-> ptr float @-> int64_t
+   @-> ptr float @-> int64_t @-> float @-> ptr float @-> int64_t @-> float @-> ptr float @-> int @-> returning int)
 
-(** Non-zero status -> exception carrying the library's message; -3 is the
-    Unsupported_construct of spoc/framework/Backend_error.ml. *)
+(** Non-zero status -> [Backend_error.Backend_error] (see B200_error.of_status for the mapping: -3 is
+    Unsupported_construct, -4 Compilation_failed, -5/-6 Kernel_launch_failed, -7 Synchronization_failed, ...),
+    carrying the library's message. *)
 let check ctx rc =
-  if rc <> 0 then
-    raise (B200_error (rc, Printf.sprintf "%s: %s" ctx (Lazy.force sb200_last_error_string ())))
+  if rc <> 0 then B200_error.raise_status ~ctx rc (Lazy.force sb200_last_error_string ())

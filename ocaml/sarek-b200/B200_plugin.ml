@@ -33,12 +33,27 @@ module Backend : Framework_sig.BACKEND = struct
 
   let execution_model = Framework_sig.JIT
 
-  (** The IR text is the backend's source language. *)
+  (** The IR text is the backend's source language.  Execute calls this on every launch
+      (sarek/sarek/Execute.ml:250-264); the kernel value of a [%kernel] is built once, so the text is cached
+      per IR value (physical equality, weak in the key) and a launch re-serialises nothing. *)
+  module Ir_cache = Ephemeron.K1.Make (struct
+    type t = Sarek_ir_types.kernel
+    let equal = ( == )
+    let hash (k : t) = Hashtbl.hash k.kern_name
+  end)
+
+  let ir_cache : string option Ir_cache.t = Ir_cache.create 16
+
   let generate_source ?block:_ (ir : Sarek_ir_types.kernel) : string option =
-    try Some (B200_ir_ser.to_sexp ir) with _ -> None
+    match Ir_cache.find_opt ir_cache ir with
+    | Some s -> s
+    | None ->
+        let s = try Some (B200_ir_ser.to_sexp ir) with _ -> None in
+        Ir_cache.replace ir_cache ir s ;
+        s
 
   let execute_direct ~native_fn:_ ~ir:_ ~block:_ ~grid:_ _args =
-    failwith "B200: direct execution is not supported by a JIT backend"
+    B200_error.raise_error (B200_error.feature_not_supported "execute_direct (this is a JIT backend)")
 
   module Intrinsics = B200_intrinsics
 
@@ -50,7 +65,7 @@ module Backend : Framework_sig.BACKEND = struct
     let dev =
       match Device.get_current_device () with
       | Some d -> d
-      | None -> failwith "B200.run_source: no device selected"
+      | None -> B200_error.raise_error (B200_error.no_device_selected "run_source")
     in
     let compiled = Kernel.compile_cached dev ~name:kernel_name ~source in
     let kargs = Kernel.create_args () in

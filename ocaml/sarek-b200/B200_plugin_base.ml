@@ -151,23 +151,44 @@ module B200 = struct
 
     let cache : (int * string, t) Hashtbl.t = Hashtbl.create 16
 
+    (* Launch path: Execute hands run_source the string that generate_source returned, and generate_source
+       returns the same string object for the same IR value (B200_plugin.generate_source caches by physical
+       equality).  So the common case is a lookup by the string's identity, with no digest of the text; the
+       digest-keyed table is the reference's own caching level (sarek-cuda/Cuda_api.ml:399-412) behind it. *)
+    module By_identity = Ephemeron.K1.Make (struct
+      type t = string
+      let equal = ( == )
+      let hash s = Hashtbl.hash (String.length s)
+    end)
+
+    let by_identity : (int * t) list By_identity.t = By_identity.create 16
+
     let compile (d : Device.t) ~name ~source =
       let h = allocate uint64_t Unsigned.UInt64.zero in
       B.check "sb200_kernel_compile" (Lazy.force B.sb200_kernel_compile d.idx source name h) ;
       {dev = d.idx; handle = !@h}
 
     let compile_cached (d : Device.t) ~name ~source =
-      let key = (d.idx, Digest.string source) in
-      match Hashtbl.find_opt cache key with
+      let known = match By_identity.find_opt by_identity source with Some l -> l | None -> [] in
+      match List.assoc_opt d.idx known with
       | Some k -> k
       | None ->
-          let k = compile d ~name ~source in
-          Hashtbl.replace cache key k ;
+          let key = (d.idx, Digest.string source) in
+          let k =
+            match Hashtbl.find_opt cache key with
+            | Some k -> k
+            | None ->
+                let k = compile d ~name ~source in
+                Hashtbl.replace cache key k ;
+                k
+          in
+          By_identity.replace by_identity source ((d.idx, k) :: known) ;
           k
 
     let clear_cache () =
       Hashtbl.iter (fun _ k -> ignore (Lazy.force B.sb200_kernel_destroy k.handle)) cache ;
-      Hashtbl.reset cache
+      Hashtbl.reset cache ;
+      By_identity.reset by_identity
 
     let create_args () = {items = []}
     let push a x = a.items <- x :: a.items

@@ -33,8 +33,8 @@ constexpr uint32_t PAIR_A_BYTES = 128 * GEMM_BK * 4;  // this block's A rows: 16
 template <int MODE, int BN = PAIR_BN>
 struct PairCfg {
   static_assert(BN == 256 || BN == 128 || BN == 64, "tile columns");
-  static constexpr int kOperands = (MODE == 3) ? 2 : 1;
-  static constexpr uint32_t kBBytes = (BN / 2) * GEMM_BK * 4;  // this block's half of B: 16, 8 or 4 KiB
+  static constexpr int kOperands = (MODE == 3 || MODE == 4) ? 2 : 1;  // high parts (+ low parts)
+  static constexpr uint32_t kBBytes = (BN / 2) * GEMM_BK * 4;  // this block's half of B: 16, 8 or 4 KiB (rows of 128 bytes)
   static constexpr uint32_t kStageBytes = kOperands * (PAIR_A_BYTES + kBBytes);
   static constexpr int kStagesFit = (192 * 1024) / kStageBytes;
   static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;  // 6 / 8 / 8 (TF32), 3 / 4 / 4 (3xTF32)
@@ -62,6 +62,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                  const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
                  const GemmParams p) {
   using Cfg = PairCfg<MODE, BN>;
+  // MODE 1: TF32, one MMA per k-step.  MODE 3: 3xTF32, lo*hi + hi*lo + hi*hi.  MODE 4: the same three-term split on
+  // fp16 panels (kind::f16): a 128-byte operand row holds 64 halves instead of 32 floats, so a k-block spans 64 k
+  // and a k-step 16, in the same bytes, descriptors and cycles as the TF32 forms.
+  constexpr bool THREE = MODE == 3 || MODE == 4;
+  constexpr bool F16 = MODE == 4;
+  constexpr int BK_ELEMS = F16 ? 2 * GEMM_BK : GEMM_BK;  // elements of K per k-block
+  static_assert(!(F16 && DIRECT), "fp16 panels are always prepared");
   constexpr int STAGES = Cfg::kStages;
   constexpr uint32_t B_BYTES = Cfg::kBBytes;
   constexpr int HALF_N = BN / 2;        // columns of B this block loads
@@ -99,7 +106,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     mbar_fence_init();
     tma_prefetch_desc(&map_a_hi);
     tma_prefetch_desc(&map_b_hi);
-    if (MODE == 3) {
+    if (THREE) {
       tma_prefetch_desc(&map_a_lo);
       tma_prefetch_desc(&map_b_lo);
     }
@@ -141,24 +148,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * Cfg::kStageBytes);
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
           uint8_t* sp = stage_base + stage * Cfg::kStageBytes;
-          tma_load_2d_pair_hint(smem_u32(sp), &map_a_hi, bar, kb * GEMM_BK, m0, pol_a);
+          tma_load_2d_pair_hint(smem_u32(sp), &map_a_hi, bar, kb * BK_ELEMS, m0, pol_a);
           if (DIRECT) {
             // B is K x N row-major: x = column, y = k; slabs of 32 columns cover this block's half
 #pragma unroll
             for (int sl = 0; sl < SLABS; ++sl)
-              tma_load_2d_pair_hint(smem_u32(sp + PAIR_A_BYTES + sl * 4096), &map_b_hi, bar, n0 + 32 * sl, kb * GEMM_BK, pol_b);
+              tma_load_2d_pair_hint(smem_u32(sp + PAIR_A_BYTES + sl * 4096), &map_b_hi, bar, n0 + 32 * sl, kb * BK_ELEMS, pol_b);
           } else {
-            tma_load_2d_pair_hint(smem_u32(sp + PAIR_A_BYTES), &map_b_hi, bar, kb * GEMM_BK, n0, pol_b);
+            tma_load_2d_pair_hint(smem_u32(sp + PAIR_A_BYTES), &map_b_hi, bar, kb * BK_ELEMS, n0, pol_b);
           }
-          if (MODE == 3) {
-            tma_load_2d_pair_hint(smem_u32(sp + PAIR_A_BYTES + B_BYTES), &map_a_lo, bar, kb * GEMM_BK, m0, pol_a);
+          if (THREE) {
+            tma_load_2d_pair_hint(smem_u32(sp + PAIR_A_BYTES + B_BYTES), &map_a_lo, bar, kb * BK_ELEMS, m0, pol_a);
             if (DIRECT) {
 #pragma unroll
               for (int sl = 0; sl < SLABS; ++sl)
                 tma_load_2d_pair_hint(smem_u32(sp + 2 * PAIR_A_BYTES + B_BYTES + sl * 4096), &map_b_lo, bar, n0 + 32 * sl,
-                                 kb * GEMM_BK, pol_b);
+                                 kb * BK_ELEMS, pol_b);
             } else {
-              tma_load_2d_pair_hint(smem_u32(sp + 2 * PAIR_A_BYTES + B_BYTES), &map_b_lo, bar, kb * GEMM_BK, n0, pol_b);
+              tma_load_2d_pair_hint(smem_u32(sp + 2 * PAIR_A_BYTES + B_BYTES), &map_b_lo, bar, kb * BK_ELEMS, n0, pol_b);
             }
           }
           if (++stage == STAGES) {
@@ -177,7 +184,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------- MMA issuer (leader block)
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = umma_idesc_tf32(PAIR_BM, BN, DIRECT);
+      constexpr uint32_t idesc = F16 ? umma_idesc_f16(PAIR_BM, BN) : umma_idesc_tf32(PAIR_BM, BN, DIRECT);
       int stage = 0;
       uint32_t phase = 0;
       int local_tile = 0;
@@ -210,7 +217,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             // MN-major B: k-step k is the k-th 8-row group (1024 bytes) of every slab
             const uint64_t db_hi = DIRECT ? umma_desc_mn_sw128_32b(sb_hi + k * 1024, 4096) : umma_desc_k_sw128(sb_hi + koff);
             const uint32_t accumulate = (kb | k) ? 1u : 0u;
-            if (MODE == 3) {
+            if (F16) {
+              const uint64_t da_lo = umma_desc_k_sw128(sa_lo + koff);
+              const uint64_t db_lo = umma_desc_k_sw128(sb_lo + koff);
+              umma_f16_pair(tmem_d, da_lo, db_hi, idesc, accumulate);
+              umma_f16_pair(tmem_d, da_hi, db_lo, idesc, 1u);
+              umma_f16_pair(tmem_d, da_hi, db_hi, idesc, 1u);
+            } else if (MODE == 3) {
               const uint64_t da_lo = umma_desc_k_sw128(sa_lo + koff);
               const uint64_t db_lo = DIRECT ? umma_desc_mn_sw128_32b(sb_lo + k * 1024, 4096) : umma_desc_k_sw128(sb_lo + koff);
               umma_tf32_pair(tmem_d, da_lo, db_hi, idesc, accumulate);

@@ -231,6 +231,19 @@ __device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t adesc, 
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same MMA on half-precision (fp16) operands with fp32 accumulation: 256 x N x 16 per instruction,
+// twice the arithmetic of the TF32 form in the same number of operand bytes and cycles.
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on one mbarrier (a shared::cluster address: this block's or the
 // peer's) once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
@@ -258,6 +271,12 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
 // b_format=2 at bit 10, B MN-major flag at bit 16, N>>3 at bit 17, M>>4 at bit 24.
 __host__ __device__ constexpr uint32_t umma_idesc_tf32(uint32_t m, uint32_t n, bool b_mn_major = false) {
   return (1u << 4) | (2u << 7) | (2u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// Instruction descriptor for kind::f16 with fp16 operands (a_format = b_format = 0), fp32 accumulate, both
+// operands K-major: same fields as above.
+__host__ __device__ constexpr uint32_t umma_idesc_f16(uint32_t m, uint32_t n) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 // Round to TF32 (10 explicit mantissa bits), nearest-even: the same rounding a

@@ -185,7 +185,8 @@ int current_mode() {
   int m = g_mode.load();
   if (m == 0) {
     const char* s = getenv("SAREK_B200_MODE");
-    m = (s && (!strcmp(s, "tf32") || !strcmp(s, "TF32"))) ? SB200_MODE_TF32 : SB200_MODE_3XTF32;
+    m = (s && (!strcmp(s, "tf32") || !strcmp(s, "TF32"))) ? SB200_MODE_TF32
+        : (s && (!strcmp(s, "3xf16") || !strcmp(s, "3xF16"))) ? SB200_MODE_3XF16 : SB200_MODE_3XTF32;
     g_mode.store(m);
   }
   return m;
@@ -273,6 +274,19 @@ int ensure_workspace(DeviceState& d, size_t bytes) {
 int encode_map_2d(CUtensorMap* map, const float* base, long long inner, long long rows, long long row_stride_elems, int box_inner,
                   int box_rows, bool round_tf32, bool atom32 = false);
 
+int resolve_encode_tiled() {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    cudaGetLastError();
+  });
+  if (!g_encode_tiled) return fail(SB200_ERR_NO_DEVICE, "driver does not export cuTensorMapEncodeTiled");
+  return SB200_OK;
+}
+
 int encode_panel_map(CUtensorMap* map, const float* base, long long kp, long long rows, int box_rows) {
   return encode_map_2d(map, base, kp, rows, kp, GEMM_BK, box_rows, false);
 }
@@ -283,15 +297,7 @@ int encode_panel_map(CUtensorMap* map, const float* base, long long kp, long lon
 int encode_map_2d(CUtensorMap* map, const float* base, long long inner, long long rows, long long row_stride_elems, int box_inner,
                   int box_rows, bool round_tf32, bool atom32) {
   const long long kp = inner;
-  std::call_once(g_encode_once, [] {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
-    cudaGetLastError();
-  });
-  if (!g_encode_tiled) return fail(SB200_ERR_NO_DEVICE, "driver does not export cuTensorMapEncodeTiled");
+  if (int rc = resolve_encode_tiled()) return rc;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(kp), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride_elems) * 4};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_rows)};
@@ -649,10 +655,125 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   return rc;
 }
 
+// ---- mode 4: the three-term split on fp16 panels -------------------------------------------------------
+int encode_map_f16(CUtensorMap* map, const __half* base, long long kp, long long rows, int box_rows) {
+  if (int rc = resolve_encode_tiled()) return rc;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(kp), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(kp) * 2};
+  cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(SB200_ERR_INVALID_VALUE, "cuTensorMapEncodeTiled (fp16 panel) failed with CUresult %d (kp=%lld rows=%lld)", (int)r, kp, rows);
+  return SB200_OK;
+}
+
+size_t gemm_f16_workspace_need(long long M, long long N, long long K) {
+  const long long kp = round_up(K, 64);
+  return 1024 + 2 * (round_up(M * kp * 2, 1024) + round_up(N * kp * 2, 1024));
+}
+
+int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, long long K, const float* A, long long lda,
+                    const float* B, long long ldb, const GemmParams& gp_in) {
+  const long long kp = round_up(K, 64);
+  const size_t a_bytes = round_up(M * kp * 2, 1024), b_bytes = round_up(N * kp * 2, 1024);
+  const size_t need = gemm_f16_workspace_need(M, N, K);
+  std::unique_lock<std::mutex> scratch_lock(d.scratch_mu);
+  int rc = ensure_workspace(d, need);
+  if (rc) return rc;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) {
+    cudaGetLastError();
+    cap = cudaStreamCaptureStatusActive;
+  }
+  const bool track_scratch = cap == cudaStreamCaptureStatusNone;
+  if (track_scratch) {
+    std::lock_guard<std::mutex> lock(d.mu);
+    if (d.ws_in_use && d.ws_last_stream != st) CU_TRY(cudaStreamWaitEvent(st, d.ws_event, 0));
+  }
+  const bool prof = g_profiling.load() != 0;
+  DeviceState::ProfRec rec{nullptr, nullptr, nullptr};
+  if (prof) {
+    CU_TRY(cudaEventCreate(&rec.e0));
+    CU_TRY(cudaEventCreate(&rec.e1));
+    CU_TRY(cudaEventCreate(&rec.e2));
+    CU_TRY(cudaEventRecord(rec.e0, st));
+  }
+  // scratch: [max |A| bits, max |B| bits, 1/scale_A, 1/scale_B | pad to 1 KiB][A_hi][A_lo][B_hi][B_lo]
+  uint8_t* ws = static_cast<uint8_t*>(d.workspace);
+  unsigned int* maxbits = reinterpret_cast<unsigned int*>(ws);
+  float* inv_scale = reinterpret_cast<float*>(ws + 8);
+  __half* a_hi = reinterpret_cast<__half*>(ws + 1024);
+  __half* a_lo = reinterpret_cast<__half*>(ws + 1024 + a_bytes);
+  __half* b_hi = reinterpret_cast<__half*>(ws + 1024 + 2 * a_bytes);
+  __half* b_lo = reinterpret_cast<__half*>(ws + 1024 + 2 * a_bytes + b_bytes);
+  CU_TRY(cudaMemsetAsync(maxbits, 0, 8, st));
+  const long long cap16 = static_cast<long long>(d.sm_count) * 16;
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  {
+    // largest magnitudes of A and B in one launch
+    long long ga = (M * K + 4095) / 4096, gb = (K * N + 4095) / 4096;
+    if (ga > cap16) ga = cap16;
+    if (gb > cap16) gb = cap16;
+    if (ga < 1) ga = 1;
+    if (gb < 1) gb = 1;
+    const AbsmaxJob ja{A, lda, static_cast<int>(M), static_cast<int>(K), (lda == K && al16(A)) ? 1 : 0};
+    const AbsmaxJob jb{B, ldb, static_cast<int>(K), static_cast<int>(N), (ldb == N && al16(B)) ? 1 : 0};
+    absmax_two_kernel<<<static_cast<unsigned>(ga + gb), 256, 0, st>>>(ja, jb, static_cast<int>(ga), maxbits);
+    if ((rc = launch_check("absmax_two_kernel"))) return rc;
+  }
+  {
+    long long grid = (M * (kp >> 3) + 255) / 256;
+    if (grid > cap16) grid = cap16;
+    const int vec_ok = (al16(A) && (lda & 3) == 0) ? 1 : 0;
+    prep_a_f16_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(A, lda, a_hi, a_lo, static_cast<int>(M), static_cast<int>(K),
+                                                                    static_cast<int>(kp), maxbits, inv_scale, 0, vec_ok);
+    if ((rc = launch_check("prep_a_f16_kernel"))) return rc;
+    long long tiles = (kp >> 6) * ((N + 31) >> 5);
+    const long long cap32 = static_cast<long long>(d.sm_count) * 32;
+    if (tiles > cap32) tiles = cap32;
+    prep_b_f16_kernel<<<static_cast<unsigned>(tiles), dim3(32, 8), 0, st>>>(B, ldb, b_hi, b_lo, static_cast<int>(K),
+                                                                             static_cast<int>(N), static_cast<int>(kp), maxbits + 1,
+                                                                             inv_scale, 1);
+    if ((rc = launch_check("prep_b_f16_kernel"))) return rc;
+  }
+  const int clusters = d.sm_count / 2 > 0 ? d.sm_count / 2 : 1;
+  const int tile_n = choose_tile_n(M, N, kp / 64, clusters, 3);
+  CUtensorMap ma_hi, mb_hi, ma_lo, mb_lo;
+  if ((rc = encode_map_f16(&ma_hi, a_hi, kp, M, GEMM_BM))) return rc;
+  if ((rc = encode_map_f16(&ma_lo, a_lo, kp, M, GEMM_BM))) return rc;
+  if ((rc = encode_map_f16(&mb_hi, b_hi, kp, N, tile_n / 2))) return rc;
+  if ((rc = encode_map_f16(&mb_lo, b_lo, kp, N, tile_n / 2))) return rc;
+  GemmParams gp = gp_in;
+  gp.num_k_blocks = static_cast<int>(kp / 64);
+  gp.status = d.status;
+  derive_params(&gp);
+  gp.acc_scale = inv_scale;
+  if (prof) CU_TRY(cudaEventRecord(rec.e1, st));
+  const int dev_index = static_cast<int>(&d - g_dev);
+  rc = launch_pair_bn<4, false>(tile_n, d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N);
+  if (prof) {
+    CU_TRY(cudaEventRecord(rec.e2, st));
+    std::lock_guard<std::mutex> lock(d.mu);
+    d.prof.push_back(rec);
+  }
+  if (track_scratch && rc == SB200_OK) {
+    std::lock_guard<std::mutex> lock(d.mu);
+    if (!d.ws_event) CU_TRY(cudaEventCreateWithFlags(&d.ws_event, cudaEventDisableTiming));
+    CU_TRY(cudaEventRecord(d.ws_event, st));
+    d.ws_last_stream = st;
+    d.ws_in_use = true;
+  }
+  return rc;
+}
+
 int run_gemm(DeviceState& d, cudaStream_t st, int mode, long long M, long long N, long long K, uint64_t A, long long lda,
              uint64_t B, long long ldb, uint64_t D, long long ldd, float alpha, uint64_t C, long long ldc, float beta,
              uint64_t bias, int act, const uint64_t* replicas = nullptr, int n_replicas = 0) {
-  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16)
+    return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   if (M < 0 || N < 0 || K < 0) return fail(SB200_ERR_INVALID_VALUE, "negative GEMM dimension (M=%lld N=%lld K=%lld)", M, N, K);
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL - 64)
     return fail(SB200_ERR_TOO_LARGE, "GEMM dimension beyond 2^31-1 (M=%lld N=%lld K=%lld)", M, N, K);
@@ -698,6 +819,8 @@ int run_gemm(DeviceState& d, cudaStream_t st, int mode, long long M, long long N
     gemm_k0_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(gp);
     return launch_check("gemm_k0_kernel");
   }
+  if (mode == SB200_MODE_3XF16)
+    return launch_gemm_f16(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
   if (mode == SB200_MODE_3XTF32)
     return launch_gemm_mode<3>(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
   return launch_gemm_mode<1>(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
@@ -1596,7 +1719,7 @@ int sb200_chain_triad_square_f32(int dev, uint64_t stream, uint64_t dd, uint64_t
 }
 
 int sb200_set_mode(int mode) {
-  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   g_mode.store(mode);
   return SB200_OK;
 }

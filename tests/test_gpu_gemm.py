@@ -32,7 +32,7 @@ def variant(request, backend):
 def tol(mode, K):
     # the floor keeps the 3xTF32 bound meaningful for tiny K, where a single
     # float32 rounding of the result (6e-8) is comparable to 1e-5*sqrt(K)
-    return max(1e-5 * math.sqrt(max(K, 1)), 1e-6) if mode == L.MODE_3XTF32 else 2e-3
+    return max(1e-5 * math.sqrt(max(K, 1)), 1e-6) if mode in (L.MODE_3XTF32, L.MODE_3XF16) else 2e-3
 
 
 SHAPES = [(1, 1, 1), (5, 7, 3), (16, 16, 16), (128, 256, 32), (128, 256, 64), (129, 257, 33), (100, 300, 70),
@@ -759,4 +759,128 @@ def test_non_finite_operands_stay_confined_to_their_rows_and_columns(backend, de
             assert np.array_equal(got[inf_ref], ref[inf_ref])
     finally:
         for x in (A, B, D):
+            x.free()
+
+
+# ---- the three-term split on fp16 panels (SB200_MODE_3XF16): fp32-grade accuracy at twice the tensor-core rate ----
+
+@pytest.mark.parametrize("shape", SHAPES + [(512, 768, 1000), (1024, 1024, 1024)])
+def test_f16_split_plain_product_matches_oracle_within_the_3xtf32_bound(backend, device, shape):
+    M, N, K = shape
+    a, b = O.fill(M * K, 91, 1), O.fill(K * N, 91, 2)
+    A, B, D = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * N)
+    try:
+        gemm(backend, device, L.MODE_3XF16, M, N, K, A, B, D)
+        assert O.gemm_rel_error(D.download().reshape(M, N), O.gemm(a, b, M, N, K)) <= tol(L.MODE_3XF16, K)
+    finally:
+        for x in (A, B, D):
+            x.free()
+
+
+@pytest.mark.parametrize("scales", [(1.0, 1.0), (2.0 ** -60, 2.0 ** 40), (1e-20, 1e15), (3e4, 7e-3), (1e-30, 1e-5)])
+@pytest.mark.parametrize("dist", ["uniform", "normal"])
+def test_f16_split_is_independent_of_the_operands_magnitude(backend, device, scales, dist):
+    """The panels are scaled by powers of two taken from each matrix's largest magnitude, so the accuracy does not
+    depend on where in the float32 range the operands lie, with the epilogue's alpha, beta*C and bias applied to the
+    rescaled product."""
+    M, N, K = 300, 260, 520
+    kind = 0 if dist == "uniform" else 2
+    a = (O.fill(M * K, 92, 1, kind=kind).astype(np.float64) * scales[0]).astype(np.float32)
+    b = (O.fill(K * N, 92, 2, kind=kind).astype(np.float64) * scales[1]).astype(np.float32)
+    mag = scales[0] * scales[1] * math.sqrt(K)
+    c = (O.fill(M * N, 92, 3).astype(np.float64) * mag).astype(np.float32)
+    bias = (O.fill(N, 92, 4, kind=1).astype(np.float64) * mag).astype(np.float32)
+    A, B, Cm, Bi = (dev_from(backend, device, x) for x in (a, b, c, bias))
+    D = Dev(backend, device, M * N)
+    try:
+        gemm(backend, device, L.MODE_3XF16, M, N, K, A, B, D, alpha=1.5, C_=Cm, beta=0.5, bias=Bi, act=1)
+        ref = O.gemm(a, b, M, N, K, 1.5, 0.5, c, bias, 1)
+        assert O.gemm_rel_error(D.download().reshape(M, N), ref) <= tol(L.MODE_3XF16, K) * 1.5 * math.sqrt(2)
+    finally:
+        for x in (A, B, Cm, Bi, D):
+            x.free()
+
+
+def test_f16_split_small_integers_are_bit_exact_and_tiles_agree(backend, device):
+    rng = np.random.default_rng(5)
+    M, N, K = 260, 392, 136
+    a = rng.integers(-8, 9, M * K).astype(np.float32)
+    b = rng.integers(-8, 9, K * N).astype(np.float32)
+    A, B, D = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * N)
+    try:
+        want = (a.reshape(M, K).astype(np.float64) @ b.reshape(K, N).astype(np.float64)).astype(np.float32)
+        for tile in (256, 128, 64, 0):
+            backend_lib = L.load()
+            assert backend_lib.sb200_set_gemm_tile_n(tile) == 0
+            D.clear()
+            gemm(backend, device, L.MODE_3XF16, M, N, K, A, B, D)
+            assert np.array_equal(D.download().reshape(M, N), want)
+    finally:
+        L.load().sb200_set_gemm_tile_n(0)
+        for x in (A, B, D):
+            x.free()
+
+
+def test_f16_split_wide_dynamic_range_inside_a_matrix(backend, device):
+    """Elements far below a matrix's largest lose low bits of their low part (fp16's exponent is 5 bits wide).  With
+    magnitudes spread over 2^12 inside each matrix the result still meets the 3xTF32 bound; this is the documented
+    operating range of the mode, beyond which 3xTF32 is the mode to use."""
+    M, N, K = 256, 256, 512
+    rng = np.random.default_rng(6)
+    a = (O.fill(M * K, 93, 1).astype(np.float64) * np.exp2(-rng.integers(0, 13, M * K))).astype(np.float32)
+    b = (O.fill(K * N, 93, 2).astype(np.float64) * np.exp2(-rng.integers(0, 13, K * N))).astype(np.float32)
+    A, B, D = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * N)
+    try:
+        gemm(backend, device, L.MODE_3XF16, M, N, K, A, B, D)
+        assert O.gemm_rel_error(D.download().reshape(M, N), O.gemm(a, b, M, N, K)) <= tol(L.MODE_3XF16, K)
+    finally:
+        for x in (A, B, D):
+            x.free()
+
+
+def test_f16_split_config_8192_cubed_epilogue_sampled(backend, device):
+    """The headline configuration in the fp16-split mode: 64 rows + 64 columns + 4096 points against the oracle, same bound
+    as 3xTF32."""
+    from spoc_b200.plugin import _check
+    lib = L.load()
+    M = N = K = 8192
+    mode = L.MODE_3XF16
+    bufs = [backend.Memory.alloc(device, M * K, np.float32) for _ in range(4)]
+    A, B, Cm, D = bufs
+    Bi = backend.Memory.alloc(device, N, np.float32)
+    try:
+        for buf, sid, kind, cnt in ((A, 1, 0, M * K), (B, 2, 0, K * N), (Cm, 3, 0, M * N), (Bi, 4, 1, N)):
+            _check(lib.sb200_fill_f32(device.id, 0, buf.ptr, cnt, 20260101, sid, kind, 1.0, 0))
+        _check(lib.sb200_gemm_f32(device.id, 0, mode, M, N, K, A.ptr, K, B.ptr, N, D.ptr, N, 1.5, Cm.ptr, N, 0.5, Bi.ptr, 1))
+        backend.Device.synchronize(device)
+        _full_config_check(backend, device, lib, mode, M, N, K, A, B, D, 11, alpha=1.5, beta=0.5, Cm=Cm, Bi=Bi, act=1,
+                           scale=1.5 * math.sqrt(2))
+    finally:
+        for x in bufs + [Bi]:
+            backend.Memory.free(x)
+
+
+def test_f16_split_gather_writes_every_copy(backend, device):
+    import ctypes as C
+    lib = L.load()
+    mode = L.MODE_3XF16
+    M_total, M_local, N, K, row_offset = 700, 301, 260, 200, 250
+    a, b, c = O.fill(M_local * K, 51, 1), O.fill(K * N, 51, 2), O.fill(M_local * N, 51, 3)
+    bias = O.fill(N, 51, 4, kind=1)
+    A, B, Cm, Bi = (dev_from(backend, device, x) for x in (a, b, c, bias))
+    copies = [Dev(backend, device, M_total * N) for _ in range(3)]
+    Dref = Dev(backend, device, M_local * N)
+    try:
+        ptrs = (C.c_uint64 * 3)(*[d.ptr for d in copies])
+        assert lib.sb200_gemm_f32_gather(device.id, 0, mode, M_local, N, K, A.ptr, K, B.ptr, N, ptrs, 3, row_offset, N, 1.5, Cm.ptr, N,
+                                         0.5, Bi.ptr, 1) == 0, lib.sb200_last_error_string()
+        gemm(backend, device, mode, M_local, N, K, A, B, Dref, alpha=1.5, C_=Cm, beta=0.5, bias=Bi, act=1)
+        want = Dref.download().reshape(M_local, N)
+        assert O.gemm_rel_error(want, O.gemm(a, b, M_local, N, K, 1.5, 0.5, c, bias, 1)) <= tol(mode, K) * 1.5 * math.sqrt(2)
+        for d in copies:
+            got = d.download().reshape(M_total, N)
+            assert np.array_equal(got[row_offset:row_offset + M_local], want)
+            assert np.all(got[:row_offset] == CANARY) and np.all(got[row_offset + M_local:] == CANARY)
+    finally:
+        for x in [A, B, Cm, Bi, Dref] + copies:
             x.free()
