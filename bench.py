@@ -779,8 +779,8 @@ def run_case(args) -> None:
         return run_transfer_case(lib, dev, S)
     if args.case == "tiles":
         return run_tiles_case(lib, dev)
-    if args.case in ("gemm3", "gemm1"):
-        mode = L.MODE_3XTF32 if args.case == "gemm3" else L.MODE_TF32
+    if args.case in ("gemm3", "gemm1", "gemm4"):
+        mode = {"gemm3": L.MODE_3XTF32, "gemm1": L.MODE_TF32, "gemm4": L.MODE_3XF16}[args.case]
         bufs = [torch.empty(S * S, dtype=torch.float32, device=tdev) for _ in range(4)]
         bias = torch.empty(S, dtype=torch.float32, device=tdev)
         for i, t in enumerate(bufs[:3]):
@@ -1086,7 +1086,7 @@ def main() -> None:
     ap.add_argument("--workload", default="gemm8192", choices=["gemm8192", "gather", "skinny"],
                     help="gemm8192: the headline run; gather: large square GEMM with the result gathered on every GPU; "
                          "skinny: 65536x4096x4096 GEMM, rows split over the ranks, B broadcast")
-    ap.add_argument("--case", default=None, choices=["gemm3", "gemm1", "map", "transfer", "tiles"],
+    ap.add_argument("--case", default=None, choices=["gemm3", "gemm1", "gemm4", "map", "transfer", "tiles"],
                     help="profiler-sized single-operator run (square size --size; map uses size^2 elements)")
     ap.add_argument("--size", type=int, default=4096)
     ap.add_argument("--gpus", type=int, default=1)
