@@ -482,6 +482,23 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
               for _ in range(sg):
                   call()
               ms_g = (time.perf_counter() - t0) / sg * 1e3
+              # the same call on pinned host memory: plain DMA, no staging copies on the host cores
+              pinned = {}
+              try:
+                  tp = [torch.from_numpy(x).pin_memory() for x in (gA, gB, gC, gD)]
+                  nA, nB, nC, nD = (t.numpy() for t in tp)
+                  callp = lambda: grp.gemm_host(L.MODE_3XTF32, Mg, N, K, nA, nB, nD, alpha=1.5, c=nC, beta=0.5, bias=gbias,
+                                                act=L.ACT_RELU)
+                  callp()
+                  t0 = time.perf_counter()
+                  for _ in range(sg):
+                      callp()
+                  ms_p = (time.perf_counter() - t0) / sg * 1e3
+                  pinned = {"value": world * flops_step / (ms_p * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_p,
+                            "identical_to_pageable": bool(np.array_equal(nD, gD))}
+                  del tp, nA, nB, nC, nD
+              except Exception as ex:
+                  pinned = {"error": f"{type(ex).__name__}: {ex}"}
               # the block of rank 0 must equal what this rank's own operator produced for the same rows
               gemm(L.MODE_3XTF32)
               torch.cuda.synchronize()
@@ -491,7 +508,10 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
                      "h2d_bytes_per_step": 4 * (Mg * K + K * N + Mg * N + N), "d2h_bytes_per_step": 4 * Mg * N,
                      "api": "sb200_gemm_sharded_host on a group of all GPUs, one process (rank 0), pageable host operands of "
                             f"{Mg} rows: B over PCIe once then NCCL broadcast, each GPU moves its own rows; wall clock of the call",
-                     "first_block_identical_to_single_gpu": same}
+                     "first_block_identical_to_single_gpu": same, "pinned_host_operands": pinned,
+                     "host_io_note": "perfect weak scaling of this step needs world x 67 GB/s of host memory traffic to and from "
+                                     "the GPUs (1.07 GB per GPU per 16 ms); one process's pageable buffers are staged through "
+                                     "pinned slots by host threads, which multiplies the host-side memory traffic by about four"}
               del gA, gC, gD
           except Exception as ex:  # the line must still be printed: say what failed
             e2e = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
@@ -895,7 +915,7 @@ def gather_leg(ctx, S: int, steps: int, warmup: int) -> dict:
     rows of A/C/D split over the ranks, B replicated by NCCL broadcast.  Two ways to leave the whole D on every GPU
     are timed: the GEMM followed by an NCCL all-gather of the row blocks, and the GEMM whose epilogue stores each
     tile into every GPU's copy (peer stores over NVLink).  The two forms alternate over three rounds so that a
-    drift of the clocks under the power cap hits both alike; each form's figure is the best of its rounds.  Sampled rows
+    drift of the clocks under the power cap hits both alike; each form's figure is the median of its rounds.  Sampled rows
     of every rank's gathered copy — rows computed by every rank — are checked against the CPU oracle."""
     import numpy as np
     torch, dist, L, lib = ctx.torch, ctx.dist, ctx.L, ctx.lib
@@ -950,7 +970,7 @@ def gather_leg(ctx, S: int, steps: int, warmup: int) -> dict:
     for rnd in range(3):
         rounds["nccl"].append(ctx.timed(step_nccl, steps, warmup if rnd == 0 else 1))
         rounds["fused"].append(ctx.timed(step_fused, steps, warmup if rnd == 0 else 1))
-    ms_nccl, ms_fused = min(rounds["nccl"]), min(rounds["fused"])
+    ms_nccl, ms_fused = statistics.median(rounds["nccl"]), statistics.median(rounds["fused"])
     # the two gathered results must agree bit for bit on this rank (compared in slabs: no third 4 GiB buffer)
     same = True
     slab = max(1, (1 << 28) // S) * S
