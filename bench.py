@@ -355,7 +355,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         "frac": achieved / tf32_peak,
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, taken from an
         # ncu capture of this same kernel and size (a profiler figure, not measured in this run)
-        "traffic": 8.144e9 + 0.262e9, "traffic_unit": "bytes per launch (ncu capture of this kernel at this size)",
+        "traffic": 6.956e9 + 0.258e9,
+        "traffic_unit": "bytes per launch (ncu capture of this kernel at this size, profiles/gemm_pair_kernel_8192cubed_modes_and_l2_policies_ncu.md; "
+                        "box to box the figure varies by about 30 %)",
         "peak_source": (f"{peaks['source']}: bf16 sustained {peaks['bf16_tflops_sustained']} TF/s / 2 = dense TF32 under the power cap "
                         "(the timed steps follow a pre-load)" if sustained else
                         f"{peaks['source']}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 = dense TF32"),
@@ -536,7 +538,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
                      "roofline": {"bound": "hbm", "kernel": "map2_vec_kernel<ChainOp>", "achieved": gbs,
                                   "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
                                   # ncu capture at 2^26 elements scaled x4 (traffic is proportional to N: no reuse)
-                                  "traffic": 4 * (536.9e6 + 268.4e6),
+                                  "traffic": 4 * (536.9e6 + 228.2e6),
                                   "traffic_unit": "bytes per launch (ncu capture at 2^26 elements, scaled x4)",
                                   "peak_source": f"{peaks['source']} copy bandwidth",
                                   "frac_of_nominal_8TBs": gbs / 8000.0}}

@@ -18,7 +18,7 @@ let is_available () = match Lazy.force lib with Some _ -> true | None -> false
 let get () =
   match Lazy.force lib with
   | Some l -> l
-  | None -> failwith "sarek-b200: libsarek_b200.so not found (set SAREK_B200_LIB or LD_LIBRARY_PATH)"
+  | None -> B200_error.raise_error (B200_error.library_not_found "libsarek_b200.so" ["LD_LIBRARY_PATH"; "SAREK_B200_LIB"])
 
 let fn name typ = lazy (foreign ~from:(get ()) name typ)
 

@@ -884,3 +884,45 @@ def test_f16_split_gather_writes_every_copy(backend, device):
     finally:
         for x in [A, B, Cm, Bi, Dref] + copies:
             x.free()
+
+
+def test_exhaustive_small_shapes(backend, device):
+    """Every shape with M, N, K in 1..40, plus the tile-edge sizes, in 3xTF32 mode (TF32 and the fp16 split on every
+    seventh shape): ragged edges in all three dimensions, K far below one k-block, rows and columns below one tile.
+    Operands are prefixes of fixed vectors, so a shape costs one launch, one small download and one oracle call.
+    Error measure: |gpu - ref| / sum_k |a_ik||b_kj| against the mode's bound."""
+    import ctypes as C
+    from spoc_b200.plugin import _check
+    lib = L.load()
+    big = 40 * 40
+    a_all, b_all = O.fill(300 * 300, 33, 1), O.fill(300 * 300, 33, 2)
+    A, B = dev_from(backend, device, a_all, pad=0), dev_from(backend, device, b_all, pad=0)
+    D = backend.Memory.alloc(device, 300 * 300 + 1, np.float32)
+    host = np.empty(300 * 300 + 1, np.float32)
+    edge = [63, 64, 65, 127, 128, 129, 255, 256, 257]
+    shapes = [(m, n, k) for m in range(1, 41) for n in range(1, 41) for k in range(1, 41)]
+    shapes += [(m, n, k) for m in edge for n in (1, 33, 256, 257) for k in (1, 31, 32, 33, 64, 65)]
+    worst = {L.MODE_3XTF32: 0.0, L.MODE_TF32: 0.0, L.MODE_3XF16: 0.0}
+    try:
+        for idx, (m, n, k) in enumerate(shapes):
+            modes = [L.MODE_3XTF32] + ([L.MODE_TF32, L.MODE_3XF16] if idx % 7 == 0 else [])
+            ref = None
+            for mode in modes:
+                _check(lib.sb200_memset32(device.id, D.ptr, 0xFFC00000, m * n + 1, 0))   # NaN pattern: an unwritten element shows
+                _check(lib.sb200_gemm_f32(device.id, 0, mode, m, n, k, A.ptr, k, B.ptr, n, D.ptr, n, 1.0, 0, 0, 0.0, 0, 0))
+                _check(lib.sb200_memcpy_dtoh(device.id, host.ctypes.data_as(C.c_void_p), D.ptr, 4 * (m * n + 1)))
+                got = host[:m * n].reshape(m, n)
+                assert np.isnan(host[m * n]), f"{(m, n, k)}: wrote past the result"
+                if ref is None:
+                    ref = O.gemm(a_all[:m * k], b_all[:k * n], m, n, k)
+                    # results of a handful of elements have no meaningful rms: the error is taken relative to
+                    # sum_k |a_ik| |b_kj|, the scale rounding errors of a dot product are proportional to
+                    scale = np.abs(a_all[:m * k].astype(np.float64)).reshape(m, k) @ np.abs(b_all[:k * n].astype(np.float64)).reshape(k, n)
+                err = float(np.max(np.abs(got.astype(np.float64) - ref) / scale)) / tol(mode, k)
+                assert err <= 1.0, f"shape {(m, n, k)} mode {mode}: {err} of the bound"
+                worst[mode] = max(worst[mode], err)
+    finally:
+        A.free()
+        B.free()
+        backend.Memory.free(D)
+    assert all(v > 0.0 for v in worst.values())
