@@ -381,4 +381,49 @@ inline bool fuse_guarded(const std::string& p, const std::string& c, const std::
 }
 }  // namespace fusion
 
+// ---- several GPUs of one process ----------------------------------------------
+// The reference's multi-device model is to partition a vector and launch once per device
+// (sarek/core/Vector.ml:273-296, split rule sarek/core/Vector_storage.ml:261-272).  A DeviceGroup is that model
+// for the GEMM path over the library's group entry points: the library owns streams, NCCL communicators and
+// the replicas of B; this class passes pointers and sizes.
+class DeviceGroup {
+ public:
+  enum Gather { None = 0, Fused = SB200_SHARD_GATHER_FUSED, Nccl = SB200_SHARD_GATHER_NCCL };
+  explicit DeviceGroup(const std::vector<int>& devices) : devices_(devices) {
+    check(sb200_group_create(static_cast<int>(devices.size()), devices.data(), &handle_));
+  }
+  DeviceGroup(const DeviceGroup&) = delete;
+  DeviceGroup& operator=(const DeviceGroup&) = delete;
+  ~DeviceGroup() {
+    if (handle_) sb200_group_destroy(handle_);
+  }
+  size_t size() const { return devices_.size(); }
+  // (first row, rows) of member `index` when m rows are split over the group
+  std::pair<int64_t, int64_t> row_block(int64_t m, int index) const {
+    int64_t first = 0, count = 0;
+    check(sb200_row_block(m, static_cast<int>(devices_.size()), index, &first, &count));
+    return {first, count};
+  }
+  // D = act(alpha*A.B + beta*C + bias) on device-resident row shards; returns the device time in ms
+  float gemm(int mode, int64_t m, int64_t n, int64_t k, const std::vector<uint64_t>& a_shards, uint64_t b,
+             const std::vector<uint64_t>& d, float alpha = 1.0f, const std::vector<uint64_t>* c_shards = nullptr, float beta = 0.0f,
+             uint64_t bias = 0, int act = SB200_ACT_NONE, Gather gather = None, bool b_resident = false) {
+    check(sb200_gemm_sharded(handle_, mode, m, n, k, a_shards.data(), k, b, n, d.data(), n, alpha,
+                             c_shards ? c_shards->data() : nullptr, n, beta, bias, act,
+                             static_cast<int>(gather) | (b_resident ? SB200_SHARD_B_RESIDENT : 0)));
+    float ms = 0.f;
+    check(sb200_group_last_ms(handle_, &ms));
+    return ms;
+  }
+  // the same on host operands (row-major contiguous); d is written in place
+  void gemm_host(int mode, int64_t m, int64_t n, int64_t k, const float* a, const float* b, float* d, float alpha = 1.0f,
+                 const float* c = nullptr, float beta = 0.0f, const float* bias = nullptr, int act = SB200_ACT_NONE) {
+    check(sb200_gemm_sharded_host(handle_, mode, m, n, k, a, k, b, n, d, n, alpha, c, n, beta, bias, act));
+  }
+
+ private:
+  std::vector<int> devices_;
+  uint64_t handle_ = 0;
+};
+
 }  // namespace sarek_b200

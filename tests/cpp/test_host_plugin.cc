@@ -145,6 +145,30 @@ static int run_gpu(const std::string& dir) {
     for (int i = 0; i < m * n; ++i) worst = std::fmax(worst, std::fabs(got[i] - expected[i]));
     EXPECT(worst <= 1e-3);
   }
+  {  // a group of one GPU: the sharded product on host operands against the reference's host baseline
+    const int m = 300, n = 48, k = 80;
+    std::vector<float> a(m * k), bb(k * n), d(size_t(m) * n, -1.0f);
+    for (int i = 0; i < m * k; ++i) a[i] = static_cast<float>((i % 10) / 10.0);
+    for (int i = 0; i < k * n; ++i) bb[i] = static_cast<float>(((i + 1) % 10) / 10.0);
+    DeviceGroup grp({dev.id});
+    EXPECT(grp.size() == 1 && grp.row_block(m, 0).second == m);
+    grp.gemm_host(SB200_MODE_3XTF32, m, n, k, a.data(), bb.data(), d.data());
+    double worst = 0;
+    for (int row = 0; row < m; row += 37)
+      for (int col = 0; col < n; ++col) {
+        double sum = 0.0;
+        for (int i = 0; i < k; ++i) sum += double(a[row * k + i]) * double(bb[i * n + col]);
+        worst = std::fmax(worst, std::fabs(d[size_t(row) * n + col] - sum));
+      }
+    EXPECT(worst <= 1e-3);
+    bool threw = false;
+    try {
+      DeviceGroup bad({dev.id, dev.id});
+    } catch (const BackendError& e) {
+      threw = e.code == SB200_ERR_INVALID_VALUE;
+    }
+    EXPECT(threw);
+  }
   {  // event timing and an explicit stream, as Spoc_core.Profiling uses them
     auto e0 = b.Event.create(), e1 = b.Event.create();
     auto s = b.Stream.default_stream(dev);
