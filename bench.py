@@ -396,6 +396,16 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
                      "mma_frac": 3.0 * flops_step / (main_h * 1e-3) / 1e12 / f16_peak,
                      "peak_source": f"{peaks['source']}: dense bf16/fp16 library GEMM, {'sustained' if sustained else 'burst'}",
                      "kernel_ms": main_h, "prep_ms": prof_h["prep_ms"] / max(prof_h["calls"], 1)}}
+    ms_q, _, prof_q = timed(lambda: gemm(L.MODE_F16), s5, 3, profile=True)
+    main_q = prof_q["main_ms"] / max(prof_q["calls"], 1)
+    f16_single_mode = {
+        "value": world * flops_step / (ms_q / s5 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_q / s5,
+        "note": "SB200_MODE_F16: one kind::f16 MMA per k-step on power-of-two-scaled fp16 panels; TF32 mode's 11 significant bits "
+                "and error bound (2e-3) at the fp16 tensor rate",
+        "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel<2, false> (fp16 panels)", "achieved": flops_step / (main_q * 1e-3) / 1e12,
+                     "peak": f16_peak, "unit": "TFLOP/s", "frac": flops_step / (main_q * 1e-3) / 1e12 / f16_peak,
+                     "peak_source": f16_split_mode["roofline"]["peak_source"], "kernel_ms": main_q,
+                     "prep_ms": prof_q["prep_ms"] / max(prof_q["calls"], 1)}}
     clocks = None
     if rank == 0:
         sampler.stop()
@@ -700,7 +710,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "config": make_config(args),
             "arm": {"mode": "3xTF32 split accumulation on tcgen05 tensor cores", "preload_s": args.preload_s},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-            "burst": burst, "tf32_mode": tf32_mode, "f16_split_mode": f16_split_mode, "fused_map": fused_map, "b_broadcast_ms": bcast_ms,
+            "burst": burst, "tf32_mode": tf32_mode, "f16_split_mode": f16_split_mode, "f16_single_mode": f16_single_mode, "fused_map": fused_map, "b_broadcast_ms": bcast_ms,
             "reductions": reductions, "stream_triad_1e6": small_triad, "config_1024cubed": cfg1, "tf32_yardstick": tf32_yardstick,
             "skinny_65536x4096x4096": skinny, f"gather_{args.gather_size}cubed": gather,
         }

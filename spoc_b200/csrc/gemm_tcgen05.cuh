@@ -598,7 +598,7 @@ __device__ __forceinline__ void f16_split(float x, float s, __half& hi, __half& 
   lo = (fabsf(h) <= 65504.0f) ? __float2half_rn(xs - h) : __float2half_rn(0.0f);
 }
 
-// A[M x K] -> hi, lo [M x Kp] halves, Kp = K rounded up to 64, padding zero.  One thread per 8 consecutive k: two
+// A[M x K] -> hi, lo [M x Kp] halves (lo may be null: single-pass fp16 mode), Kp = K rounded up to 64, padding zero.  One thread per 8 consecutive k: two
 // 128-bit loads when the rows allow it (vec_ok), one 128-bit store per panel.  Thread 0 also leaves 1/scale in
 // inv_scale[slot] for the GEMM's epilogue.
 __global__ void prep_a_f16_kernel(const float* __restrict__ A, long long lda, __half* __restrict__ hi, __half* __restrict__ lo,
@@ -626,7 +626,7 @@ __global__ void prep_a_f16_kernel(const float* __restrict__ A, long long lda, __
 #pragma unroll
     for (int j = 0; j < 8; ++j) f16_split(x[j], s, h[j], l[j]);
     *reinterpret_cast<uint4*>(hi + row * Kp + k) = *reinterpret_cast<const uint4*>(h);
-    *reinterpret_cast<uint4*>(lo + row * Kp + k) = *reinterpret_cast<const uint4*>(l);
+    if (lo) *reinterpret_cast<uint4*>(lo + row * Kp + k) = *reinterpret_cast<const uint4*>(l);
   }
 }
 
@@ -661,7 +661,7 @@ __global__ void prep_b_f16_kernel(const float* __restrict__ B, long long ldb, __
         f16_split(tile[2 * threadIdx.x + 1][nl], s, h1, l1);
         const long long off = static_cast<long long>(n) * Kp + k0 + 2 * threadIdx.x;
         *reinterpret_cast<__half2*>(hi + off) = __halves2half2(h0, h1);
-        *reinterpret_cast<__half2*>(lo + off) = __halves2half2(l0, l1);
+        if (lo) *reinterpret_cast<__half2*>(lo + off) = __halves2half2(l0, l1);
       }
     }
     __syncthreads();

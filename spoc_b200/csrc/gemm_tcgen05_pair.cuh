@@ -64,9 +64,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   using Cfg = PairCfg<MODE, BN>;
   // MODE 1: TF32, one MMA per k-step.  MODE 3: 3xTF32, lo*hi + hi*lo + hi*hi.  MODE 4: the same three-term split on
   // fp16 panels (kind::f16): a 128-byte operand row holds 64 halves instead of 32 floats, so a k-block spans 64 k
-  // and a k-step 16, in the same bytes, descriptors and cycles as the TF32 forms.
+  // and a k-step 16, in the same bytes, descriptors and cycles as the TF32 forms.  MODE 2: fp16 panels, one MMA.
   constexpr bool THREE = MODE == 3 || MODE == 4;
-  constexpr bool F16 = MODE == 4;
+  constexpr bool F16 = MODE == 4 || MODE == 2;  // MODE 2: one fp16 MMA per k-step on the high parts alone
   constexpr int BK_ELEMS = F16 ? 2 * GEMM_BK : GEMM_BK;  // elements of K per k-block
   static_assert(!(F16 && DIRECT), "fp16 panels are always prepared");
   constexpr int STAGES = Cfg::kStages;
@@ -217,7 +217,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             // MN-major B: k-step k is the k-th 8-row group (1024 bytes) of every slab
             const uint64_t db_hi = DIRECT ? umma_desc_mn_sw128_32b(sb_hi + k * 1024, 4096) : umma_desc_k_sw128(sb_hi + koff);
             const uint32_t accumulate = (kb | k) ? 1u : 0u;
-            if (F16) {
+            if (F16 && !THREE) {
+              umma_f16_pair(tmem_d, da_hi, db_hi, idesc, accumulate);
+            } else if (F16) {
               const uint64_t da_lo = umma_desc_k_sw128(sa_lo + koff);
               const uint64_t db_lo = umma_desc_k_sw128(sb_lo + koff);
               umma_f16_pair(tmem_d, da_lo, db_hi, idesc, accumulate);

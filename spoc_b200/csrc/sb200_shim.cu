@@ -186,7 +186,8 @@ int current_mode() {
   if (m == 0) {
     const char* s = getenv("SAREK_B200_MODE");
     m = (s && (!strcmp(s, "tf32") || !strcmp(s, "TF32"))) ? SB200_MODE_TF32
-        : (s && (!strcmp(s, "3xf16") || !strcmp(s, "3xF16"))) ? SB200_MODE_3XF16 : SB200_MODE_3XTF32;
+        : (s && (!strcmp(s, "3xf16") || !strcmp(s, "3xF16"))) ? SB200_MODE_3XF16
+        : (s && (!strcmp(s, "f16") || !strcmp(s, "F16"))) ? SB200_MODE_F16 : SB200_MODE_3XTF32;
     g_mode.store(m);
   }
   return m;
@@ -670,16 +671,18 @@ int encode_map_f16(CUtensorMap* map, const __half* base, long long kp, long long
   return SB200_OK;
 }
 
-size_t gemm_f16_workspace_need(long long M, long long N, long long K) {
+size_t gemm_f16_workspace_need(long long M, long long N, long long K, bool three) {
   const long long kp = round_up(K, 64);
-  return 1024 + 2 * (round_up(M * kp * 2, 1024) + round_up(N * kp * 2, 1024));
+  return 1024 + (three ? 2 : 1) * (round_up(M * kp * 2, 1024) + round_up(N * kp * 2, 1024));
 }
 
+// THREE: hi and lo panels, three MMAs per k-step (SB200_MODE_3XF16); else hi panels only, one MMA (SB200_MODE_F16).
+template <bool THREE>
 int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, long long K, const float* A, long long lda,
                     const float* B, long long ldb, const GemmParams& gp_in) {
   const long long kp = round_up(K, 64);
   const size_t a_bytes = round_up(M * kp * 2, 1024), b_bytes = round_up(N * kp * 2, 1024);
-  const size_t need = gemm_f16_workspace_need(M, N, K);
+  const size_t need = gemm_f16_workspace_need(M, N, K, THREE);
   std::unique_lock<std::mutex> scratch_lock(d.scratch_mu);
   int rc = ensure_workspace(d, need);
   if (rc) return rc;
@@ -701,14 +704,14 @@ int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, l
     CU_TRY(cudaEventCreate(&rec.e2));
     CU_TRY(cudaEventRecord(rec.e0, st));
   }
-  // scratch: [max |A| bits, max |B| bits, 1/scale_A, 1/scale_B | pad to 1 KiB][A_hi][A_lo][B_hi][B_lo]
+  // scratch: [max |A| bits, max |B| bits, 1/scale_A, 1/scale_B | pad to 1 KiB][A_hi][B_hi]([A_lo][B_lo])
   uint8_t* ws = static_cast<uint8_t*>(d.workspace);
   unsigned int* maxbits = reinterpret_cast<unsigned int*>(ws);
   float* inv_scale = reinterpret_cast<float*>(ws + 8);
   __half* a_hi = reinterpret_cast<__half*>(ws + 1024);
-  __half* a_lo = reinterpret_cast<__half*>(ws + 1024 + a_bytes);
-  __half* b_hi = reinterpret_cast<__half*>(ws + 1024 + 2 * a_bytes);
-  __half* b_lo = reinterpret_cast<__half*>(ws + 1024 + 2 * a_bytes + b_bytes);
+  __half* b_hi = reinterpret_cast<__half*>(ws + 1024 + a_bytes);
+  __half* a_lo = THREE ? reinterpret_cast<__half*>(ws + 1024 + a_bytes + b_bytes) : nullptr;
+  __half* b_lo = THREE ? reinterpret_cast<__half*>(ws + 1024 + 2 * a_bytes + b_bytes) : nullptr;
   CU_TRY(cudaMemsetAsync(maxbits, 0, 8, st));
   const long long cap16 = static_cast<long long>(d.sm_count) * 16;
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
@@ -740,12 +743,16 @@ int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, l
     if ((rc = launch_check("prep_b_f16_kernel"))) return rc;
   }
   const int clusters = d.sm_count / 2 > 0 ? d.sm_count / 2 : 1;
-  const int tile_n = choose_tile_n(M, N, kp / 64, clusters, 3);
+  const int tile_n = choose_tile_n(M, N, kp / 64, clusters, THREE ? 3 : 1);
   CUtensorMap ma_hi, mb_hi, ma_lo, mb_lo;
   if ((rc = encode_map_f16(&ma_hi, a_hi, kp, M, GEMM_BM))) return rc;
-  if ((rc = encode_map_f16(&ma_lo, a_lo, kp, M, GEMM_BM))) return rc;
   if ((rc = encode_map_f16(&mb_hi, b_hi, kp, N, tile_n / 2))) return rc;
-  if ((rc = encode_map_f16(&mb_lo, b_lo, kp, N, tile_n / 2))) return rc;
+  ma_lo = ma_hi;
+  mb_lo = mb_hi;
+  if (THREE) {
+    if ((rc = encode_map_f16(&ma_lo, a_lo, kp, M, GEMM_BM))) return rc;
+    if ((rc = encode_map_f16(&mb_lo, b_lo, kp, N, tile_n / 2))) return rc;
+  }
   GemmParams gp = gp_in;
   gp.num_k_blocks = static_cast<int>(kp / 64);
   gp.status = d.status;
@@ -753,7 +760,8 @@ int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, l
   gp.acc_scale = inv_scale;
   if (prof) CU_TRY(cudaEventRecord(rec.e1, st));
   const int dev_index = static_cast<int>(&d - g_dev);
-  rc = launch_pair_bn<4, false>(tile_n, d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N);
+  rc = THREE ? launch_pair_bn<4, false>(tile_n, d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N)
+             : launch_pair_bn<2, false>(tile_n, d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N);
   if (prof) {
     CU_TRY(cudaEventRecord(rec.e2, st));
     std::lock_guard<std::mutex> lock(d.mu);
@@ -772,7 +780,7 @@ int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, l
 int run_gemm(DeviceState& d, cudaStream_t st, int mode, long long M, long long N, long long K, uint64_t A, long long lda,
              uint64_t B, long long ldb, uint64_t D, long long ldd, float alpha, uint64_t C, long long ldc, float beta,
              uint64_t bias, int act, const uint64_t* replicas = nullptr, int n_replicas = 0) {
-  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16)
+  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16 && mode != SB200_MODE_F16)
     return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   if (M < 0 || N < 0 || K < 0) return fail(SB200_ERR_INVALID_VALUE, "negative GEMM dimension (M=%lld N=%lld K=%lld)", M, N, K);
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL - 64)
@@ -820,7 +828,9 @@ int run_gemm(DeviceState& d, cudaStream_t st, int mode, long long M, long long N
     return launch_check("gemm_k0_kernel");
   }
   if (mode == SB200_MODE_3XF16)
-    return launch_gemm_f16(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
+    return launch_gemm_f16<true>(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
+  if (mode == SB200_MODE_F16)
+    return launch_gemm_f16<false>(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
   if (mode == SB200_MODE_3XTF32)
     return launch_gemm_mode<3>(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
   return launch_gemm_mode<1>(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
@@ -1719,7 +1729,7 @@ int sb200_chain_triad_square_f32(int dev, uint64_t stream, uint64_t dd, uint64_t
 }
 
 int sb200_set_mode(int mode) {
-  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16 && mode != SB200_MODE_F16) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   g_mode.store(mode);
   return SB200_OK;
 }

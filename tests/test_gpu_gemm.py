@@ -926,3 +926,55 @@ def test_exhaustive_small_shapes(backend, device):
         B.free()
         backend.Memory.free(D)
     assert all(v > 0.0 for v in worst.values())
+
+
+# ---- single-pass fp16 (SB200_MODE_F16): TF32-mode accuracy at the fp16 tensor-core rate ----
+
+@pytest.mark.parametrize("shape", SHAPES + [(512, 768, 1000), (1024, 1024, 1024)])
+def test_f16_single_pass_matches_oracle_within_the_tf32_bound(backend, device, shape):
+    M, N, K = shape
+    a, b, c = O.fill(M * K, 94, 1), O.fill(K * N, 94, 2), O.fill(M * N, 94, 3)
+    bias = O.fill(N, 94, 4, kind=1)
+    A, B, Cm, Bi = (dev_from(backend, device, x) for x in (a, b, c, bias))
+    D = Dev(backend, device, M * N)
+    try:
+        gemm(backend, device, L.MODE_F16, M, N, K, A, B, D, alpha=1.5, C_=Cm, beta=0.5, bias=Bi, act=1)
+        ref = O.gemm(a, b, M, N, K, 1.5, 0.5, c, bias, 1)
+        assert O.gemm_rel_error(D.download().reshape(M, N), ref) <= tol(L.MODE_F16, K) * 1.5 * math.sqrt(2)
+    finally:
+        for x in (A, B, Cm, Bi, D):
+            x.free()
+
+
+@pytest.mark.parametrize("scales", [(2.0 ** -60, 2.0 ** 40), (1e-20, 1e15), (1e-30, 1e-5)])
+def test_f16_single_pass_is_independent_of_the_operands_magnitude(backend, device, scales):
+    M, N, K = 300, 260, 520
+    a = (O.fill(M * K, 95, 1, kind=2).astype(np.float64) * scales[0]).astype(np.float32)
+    b = (O.fill(K * N, 95, 2, kind=2).astype(np.float64) * scales[1]).astype(np.float32)
+    A, B, D = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * N)
+    try:
+        gemm(backend, device, L.MODE_F16, M, N, K, A, B, D)
+        assert O.gemm_rel_error(D.download().reshape(M, N), O.gemm(a, b, M, N, K)) <= tol(L.MODE_F16, K)
+    finally:
+        for x in (A, B, D):
+            x.free()
+
+
+def test_f16_single_pass_config_8192_cubed_epilogue_sampled(backend, device):
+    from spoc_b200.plugin import _check
+    lib = L.load()
+    M = N = K = 8192
+    mode = L.MODE_F16
+    bufs = [backend.Memory.alloc(device, M * K, np.float32) for _ in range(4)]
+    A, B, Cm, D = bufs
+    Bi = backend.Memory.alloc(device, N, np.float32)
+    try:
+        for buf, sid, kind, cnt in ((A, 1, 0, M * K), (B, 2, 0, K * N), (Cm, 3, 0, M * N), (Bi, 4, 1, N)):
+            _check(lib.sb200_fill_f32(device.id, 0, buf.ptr, cnt, 20260101, sid, kind, 1.0, 0))
+        _check(lib.sb200_gemm_f32(device.id, 0, mode, M, N, K, A.ptr, K, B.ptr, N, D.ptr, N, 1.5, Cm.ptr, N, 0.5, Bi.ptr, 1))
+        backend.Device.synchronize(device)
+        _full_config_check(backend, device, lib, mode, M, N, K, A, B, D, 12, alpha=1.5, beta=0.5, Cm=Cm, Bi=Bi, act=1,
+                           scale=1.5 * math.sqrt(2))
+    finally:
+        for x in bufs + [Bi]:
+            backend.Memory.free(x)
