@@ -49,11 +49,11 @@ extern "C" {
                                accumulators are scaled back exactly.  Same error class as 3xTF32 for matrices whose
                                elements lie within about 2^16 of the largest one (smaller elements lose low bits of
                                their low part: absolute error below 2^-39 of the largest element); about twice as
-                               fast.  sb200_gemm_f32 and sb200_gemm_f32_gather only. */
+                               fast.  Every GEMM entry point except sb200_gemm_f32_noalloc takes it. */
 #define SB200_MODE_F16 2    /* the high parts of that split alone, one fp16 MMA per k-step: the 11 significant bits of
                                TF32 mode (same error bound) at the fp16 tensor-core rate, with the same power-of-two
-                               scaling; faster than TF32 mode where the tensor work outweighs the conversion pass.
-                               sb200_gemm_f32 and sb200_gemm_f32_gather only. */
+                               scaling; faster than TF32 mode where the tensor work outweighs the conversion pass
+                               (from about 4096^3).  Every GEMM entry point except sb200_gemm_f32_noalloc. */
 
 /* ---- epilogue activation ------------------------------------------------ */
 #define SB200_ACT_NONE 0

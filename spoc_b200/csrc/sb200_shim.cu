@@ -1688,16 +1688,36 @@ int sb200_ipc_close(int dev, uint64_t dptr) {
 
 int sb200_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, uint64_t* bytes) {
   if (!bytes || M < 0 || N < 0 || K < 0) return fail(SB200_ERR_INVALID_VALUE, "bad argument");
-  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16 && mode != SB200_MODE_F16)
+    return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  if (mode == SB200_MODE_3XF16 || mode == SB200_MODE_F16) {
+    *bytes = (M == 0 || N == 0 || K == 0) ? 0 : gemm_f16_workspace_need(M, N, K, mode == SB200_MODE_3XF16);
+    return SB200_OK;
+  }
   *bytes = (M == 0 || N == 0 || K == 0) ? 0 : gemm_workspace_need(mode, M, N, K);
   return SB200_OK;
 }
 
 int sb200_gemm_describe(int mode, int64_t M, int64_t N, int64_t K, int addressable, int sm_count, char* out, int outlen) {
   if (M < 0 || N < 0 || K < 0 || sm_count <= 0) return fail(SB200_ERR_INVALID_VALUE, "bad argument");
-  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16 && mode != SB200_MODE_F16)
+    return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   if (M == 0 || N == 0) return copy_out("nothing to do", out, outlen);
   if (K == 0) return copy_out("gemm_k0_kernel (epilogue only)", out, outlen);
+  if (mode == SB200_MODE_3XF16 || mode == SB200_MODE_F16) {
+    const bool three = mode == SB200_MODE_3XF16;
+    const long long kp = round_up(K, 64);
+    const int clusters = sm_count / 2 > 0 ? sm_count / 2 : 1;
+    const int tn = choose_tile_n(M, N, kp / 64, clusters, three ? 3 : 1);
+    const long long tiles = ((M + PAIR_BM - 1) / PAIR_BM) * ((N + tn - 1) / tn);
+    const int stages = tn == 256 ? (three ? PairCfg<4, 256>::kStages : PairCfg<2, 256>::kStages)
+                     : tn == 128 ? (three ? PairCfg<4, 128>::kStages : PairCfg<2, 128>::kStages)
+                                 : (three ? PairCfg<4, 64>::kStages : PairCfg<2, 64>::kStages);
+    char fb[256];
+    snprintf(fb, sizeof fb, "pair fp16-panels tile=%dx%d stages=%d tiles=%lld waves=%lld workspace=%zu launches=4", PAIR_BM, tn, stages,
+             tiles, (tiles + clusters - 1) / clusters, gemm_f16_workspace_need(M, N, K, three));
+    return copy_out(fb, out, outlen);
+  }
   const GemmRoute r = route_gemm(mode, M, N, K, addressable != 0, sm_count, M);
   char buf[256];
   snprintf(buf, sizeof buf, "%s %s tile=%dx%d stages=%d tiles=%lld waves=%lld workspace=%zu launches=%d",
@@ -2045,7 +2065,8 @@ extern "C" int sb200_gemm_f32_noalloc(int dev, uint64_t stream, int mode, int64_
 extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                                    const float* B, int64_t ldb, float* D, int64_t ldd, float alpha, const float* C,
                                    int64_t ldc, float beta, const float* bias, int act) {
-  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16 && mode != SB200_MODE_F16)
+    return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   if (M < 0 || N < 0 || K < 0) return fail(SB200_ERR_INVALID_VALUE, "negative GEMM dimension");
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL - 64) return fail(SB200_ERR_TOO_LARGE, "GEMM dimension beyond 2^31-1");
   if (act != SB200_ACT_NONE && act != SB200_ACT_RELU) return fail(SB200_ERR_INVALID_VALUE, "unknown activation %d", act);
@@ -2176,6 +2197,10 @@ extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int6
         if (grid > cap) grid = cap;
         gemm_k0_kernel<<<static_cast<unsigned>(grid), 256, 0, d->pipe_compute>>>(gp);
         rc = launch_check("gemm_k0_kernel");
+      } else if (mode == SB200_MODE_3XF16) {  // fp16 panels are prepared per row block (B's with every block)
+        rc = launch_gemm_f16<true>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp);
+      } else if (mode == SB200_MODE_F16) {
+        rc = launch_gemm_f16<false>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp);
       } else if (mode == SB200_MODE_3XTF32) {
         rc = launch_gemm_mode<3>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);
       } else {
@@ -2257,6 +2282,10 @@ extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int6
       if (grid > cap) grid = cap;
       gemm_k0_kernel<<<static_cast<unsigned>(grid), 256, 0, d->pipe_compute>>>(gp);
       rc = launch_check("gemm_k0_kernel");
+    } else if (mode == SB200_MODE_3XF16) {
+      rc = launch_gemm_f16<true>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp);
+    } else if (mode == SB200_MODE_F16) {
+      rc = launch_gemm_f16<false>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp);
     } else if (mode == SB200_MODE_3XTF32) {
       rc = launch_gemm_mode<3>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);
     } else {

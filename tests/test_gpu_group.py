@@ -18,11 +18,11 @@ from tests import oracle_lib as O
 from tests.gpu_util import CANARY, Dev, dev_from, gemm
 
 pytestmark = pytest.mark.gpu
-MODES = [L.MODE_3XTF32, L.MODE_TF32]
+MODES = [L.MODE_3XTF32, L.MODE_TF32, L.MODE_3XF16, L.MODE_F16]
 
 
 def _tol(mode, K):
-    return (max(1e-5 * math.sqrt(K), 1e-6) if mode == L.MODE_3XTF32 else 2e-3) * 1.5 * math.sqrt(2)
+    return (max(1e-5 * math.sqrt(K), 1e-6) if mode in (L.MODE_3XTF32, L.MODE_3XF16) else 2e-3) * 1.5 * math.sqrt(2)
 
 
 def _problem(M, N, K, seed):
