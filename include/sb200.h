@@ -273,8 +273,9 @@ SB200_API int sb200_ipc_close(int dev, uint64_t dptr);
  * per device (sarek/core/Vector.ml:273-296, split rule sarek/core/Vector_storage.ml:261-272: the first
  * `total mod parts` parts get one element more); it binds peer access (sarek-cuda/Cuda_bindings.ml:472-493)
  * and never uses it.  A group is that model for the GEMM path: 1 to 8 distinct GPUs of this process (devices ==
- * NULL means 0..ngpus-1), each with its own streams; with more than one GPU the library loads NCCL (dlopen of
- * libnccl.so.2) and creates one communicator per GPU (ncclCommInitAll), and enables peer access between the
+ * NULL means 0..ngpus-1), each with its own streams; with more than one GPU the library loads NCCL (a copy the
+ * process has already loaded, else the file SAREK_B200_NCCL names, else libnccl.so.2 from the library path)
+ * and creates one communicator per GPU (ncclCommInitAll), and enables peer access between the
  * members.  Errors in the arguments (size, device index out of range or repeated) are reported before any GPU
  * work; SB200_ERR_COMM means NCCL could not be loaded or failed. */
 SB200_API int sb200_group_create(int ngpus, const int *devices, uint64_t *group);

@@ -19,6 +19,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -53,10 +54,16 @@ std::mutex g_nccl_mu;
 int load_nccl() {
   std::lock_guard<std::mutex> lock(g_nccl_mu);
   if (g_nccl.handle) return SB200_OK;
-  void* h = nullptr;
+  // One NCCL per process: a copy that the host program has already loaded (a framework's bundled one, say) is
+  // taken as it is; otherwise SAREK_B200_NCCL names the file, and the system's libnccl.so.2 is the default.
+  void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+  if (!h) {
+    const char* named = getenv("SAREK_B200_NCCL");
+    if (named && *named) h = dlopen(named, RTLD_NOW | RTLD_GLOBAL);
+  }
   for (const char* name : {"libnccl.so.2", "libnccl.so"}) {
-    h = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
     if (h) break;
+    h = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
   }
   if (!h) return set_error(SB200_ERR_COMM, "NCCL is needed for a group of more than one GPU and could not be loaded: %s", dlerror());
   NcclApi api;

@@ -11,6 +11,9 @@ contiguous.
 """
 from __future__ import annotations
 
+import importlib.util
+import os
+
 
 def partition(total: int, parts: int) -> list[tuple[int, int]]:
     """[(start, length)] for each part: the first `total % parts` parts get one extra element."""
@@ -52,6 +55,15 @@ class DeviceGroup:
         if devices is None:
             devices = list(range(ngpus if ngpus is not None else 1))
         self.devices = list(devices)
+        if len(self.devices) > 1 and not os.environ.get("SAREK_B200_NCCL"):
+            # a Python process usually also holds a framework with its own NCCL; point the library at that file so that
+            # the process ends up with one NCCL whichever of the two is loaded first
+            spec = importlib.util.find_spec("nvidia.nccl")
+            for base in (list(spec.submodule_search_locations) if spec and spec.submodule_search_locations else []):
+                cand = os.path.join(base, "lib", "libnccl.so.2")
+                if os.path.exists(cand):
+                    os.environ["SAREK_B200_NCCL"] = cand
+                    break
         arr = (C.c_int * len(self.devices))(*self.devices)
         h = C.c_uint64(0)
         _check(self._lib.sb200_group_create(len(self.devices), arr, C.byref(h)))
