@@ -4,6 +4,8 @@
 //
 //   test_host_plugin cpu <dir-with-ir-files>     no GPU needed: recognition, fusion, error behaviour
 //   test_host_plugin gpu <dir-with-ir-files>     runs the kernels on device 0
+#include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <fstream>
@@ -122,6 +124,23 @@ static int run_gpu(const std::string& dir) {
     double worst = 0;
     for (int i = 0; i < n; ++i) worst = std::fmax(worst, std::fabs(got[i] - expected[i]));
     EXPECT(worst <= 1e-5);
+  }
+  {  // the reference's timing protocol at its small benchmark size: 5 warm-ups, 20 x (launch + synchronise), median
+    const int n = 1000000;
+    Vector va(b, size_t(n)), vb(b, std::vector<float>(n, 0.5f)), vc(b, std::vector<float>(n, 0.25f));
+    const std::string ir = slurp(dir + "/stream_triad.ir");
+    std::vector<double> us;
+    for (int it = 0; it < 25; ++it) {
+      const auto t0 = std::chrono::steady_clock::now();
+      run_vectors(b, dev, ir, {&va, &vb, &vc, ScalarArg::float32(3.0f), ScalarArg::int32(n)}, dims1d(256), dims1d((n + 255) / 256));
+      b.Device.synchronize(dev);
+      const auto t1 = std::chrono::steady_clock::now();
+      if (it >= 5) us.push_back(std::chrono::duration<double, std::micro>(t1 - t0).count());
+    }
+    std::sort(us.begin(), us.end());
+    std::printf("stream_triad n=1000000 launch+synchronise through run_vectors (C++ host): median %.1f us, min %.1f us\n",
+                us[us.size() / 2], us.front());
+    EXPECT(va.to_array()[n - 1] == 0.5f + 0.25f * 3.0f);
   }
   for (const char* file : {"/matmul_naive.ir", "/matmul_tiled.ir"}) {
     // benchmarks/bench_matrix_mul_tiled.ml:41-52,109-112,194-212 (tolerance 1e-3)
