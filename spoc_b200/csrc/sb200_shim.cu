@@ -90,6 +90,9 @@ struct DeviceState {
   // that another host thread cannot free and regrow the scratch under launches that already point into it
   std::mutex scratch_mu;
   int* status = nullptr;  // device word written by kernels whose bounded waits expire
+  // set by every launch of a kernel that has bounded waits; while it is clear a synchronise has nothing to read
+  // back, which keeps the launch-plus-synchronise latency of the map kernels free of a device-to-host copy
+  std::atomic<bool> status_armed{false};
   std::map<uint64_t, uint64_t> allocs;  // base address -> bytes of every buffer sb200_mem_alloc handed out (ordered: range lookups)
   // kernel profiling (enable_profiling): event triples recorded around the GEMM stages
   struct ProfRec {
@@ -140,7 +143,11 @@ int device_ready(int dev, DeviceState** out) {
   return SB200_OK;
 }
 
-int check_status_word(DeviceState& d) {
+// device_wide: the caller has just synchronised the whole device, so nothing that could still raise the word is in
+// flight and the check is disarmed until the next such launch; after a stream synchronise it stays armed.
+int check_status_word(DeviceState& d, bool device_wide = false) {
+  if (!d.status_armed.load()) return SB200_OK;
+  if (device_wide) d.status_armed.store(false);
   int h = 0;
   CU_TRY(cudaMemcpy(&h, d.status, sizeof(int), cudaMemcpyDeviceToHost));
   if (h != 0) {
@@ -620,6 +627,7 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
   GemmParams gp = gp_in;
   gp.num_k_blocks = static_cast<int>(kp / GEMM_BK);
   gp.status = d.status;
+  d.status_armed.store(true);
   derive_params(&gp);
   if (prof) CU_TRY(cudaEventRecord(rec.e1, st));
   if (pair) {
@@ -756,6 +764,7 @@ int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, l
   GemmParams gp = gp_in;
   gp.num_k_blocks = static_cast<int>(kp / 64);
   gp.status = d.status;
+  d.status_armed.store(true);
   derive_params(&gp);
   gp.acc_scale = inv_scale;
   if (prof) CU_TRY(cudaEventRecord(rec.e1, st));
@@ -1188,7 +1197,7 @@ int sb200_device_synchronize(int dev) {
   int rc = device_ready(dev, &d);
   if (rc) return rc;
   CU_TRY(cudaDeviceSynchronize());
-  return check_status_word(*d);
+  return check_status_word(*d, true);
 }
 
 int sb200_mem_alloc(int dev, uint64_t bytes, uint64_t* dptr) {
@@ -1836,6 +1845,7 @@ int sb200_selftest_wait_timeout(int dev, uint32_t limit_ms) {
   int rc = device_ready(dev, &d);
   if (rc) return rc;
   if (limit_ms == 0 || limit_ms > 1000) return fail(SB200_ERR_INVALID_VALUE, "limit must be 1..1000 ms");
+  d->status_armed.store(true);
   wait_timeout_probe_kernel<<<1, 32>>>(d->status, static_cast<unsigned long long>(limit_ms) * 1000000ull);
   return launch_check("wait_timeout_probe_kernel");
 }
