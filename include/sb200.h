@@ -348,7 +348,7 @@ SB200_API int sb200_stream_triad_f32(int dev, uint64_t stream, uint64_t a, uint6
 SB200_API int sb200_chain_triad_square_f32(int dev, uint64_t stream, uint64_t d, uint64_t a_out, uint64_t b, uint64_t c, float scalar, int64_t n);
 
 /* default numeric mode for GEMM kernels launched through sb200_kernel_launch
- * (also read once from the environment variable SAREK_B200_MODE=3xtf32|tf32) */
+ * (also read once from the environment variable SAREK_B200_MODE=3xtf32|tf32|3xf16|f16) */
 SB200_API int sb200_set_mode(int mode);
 SB200_API int sb200_get_mode(int *mode);
 /* which tensor-core kernel sb200_gemm_f32 launches: 0 = automatic (CTA pairs on
