@@ -44,15 +44,16 @@ extern "C" {
 #define SB200_MODE_3XTF32 3 /* split accumulation, fp32-grade accuracy (default) */
 #define SB200_MODE_TF32 1   /* operands rounded to TF32 once, one MMA per k-step */
 #define SB200_MODE_3XF16 4  /* the same three-term split on half-precision panels (fp16 has TF32's 11 significant
-                               bits and twice its tensor-core rate): each matrix is scaled by a power of two so
-                               that its largest magnitude lies in [2^14, 2^15), split hi + lo in fp16, and the
-                               accumulators are scaled back exactly.  Same error class as 3xTF32 for matrices whose
-                               elements lie within about 2^16 of the largest one (smaller elements lose low bits of
-                               their low part: absolute error below 2^-39 of the largest element); about twice as
-                               fast.  Every GEMM entry point except sb200_gemm_f32_noalloc takes it. */
+                               bits and twice its tensor-core rate): every row of A and every column of B is scaled
+                               by a power of two of its own so that its largest magnitude lies in [2^14, 2^15), split
+                               hi + lo in fp16, and the accumulators are scaled back exactly.  Same error class as
+                               3xTF32 when the elements of a row of A (column of B) lie within about 2^16 of its
+                               largest (smaller elements lose low bits of their low part: absolute error below 2^-39
+                               of that largest element); about 1.65x as fast at 8192^3.  Every GEMM entry point except
+                               sb200_gemm_f32_noalloc takes it. */
 #define SB200_MODE_F16 2    /* the high parts of that split alone, one fp16 MMA per k-step: the 11 significant bits of
-                               TF32 mode (same error bound) at the fp16 tensor-core rate, with the same power-of-two
-                               scaling; faster than TF32 mode where the tensor work outweighs the conversion pass
+                               TF32 mode (same error bound) at the fp16 tensor-core rate, with the same per-row and
+                               per-column power-of-two scaling; faster than TF32 mode where the tensor work outweighs the conversion pass
                                (from about 4096^3).  Every GEMM entry point except sb200_gemm_f32_noalloc. */
 
 /* ---- epilogue activation ------------------------------------------------ */

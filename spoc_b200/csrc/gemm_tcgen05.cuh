@@ -77,10 +77,11 @@ struct GemmParams {
   // L2 eviction policies, 2 bits each (0 normal, 1 evict first, 2 evict last): bits 0-1 loads of A (hi and lo),
   // bits 2-3 loads of B, bits 4-5 the epilogue's reads of C and writes of D.
   int l2_policy;
-  // Mode 4 (fp16 panels): the panels hold A * 2^ea and B * 2^eb, and the preparation kernels leave 2^-ea and
-  // 2^-eb here; the epilogue multiplies each accumulator by both (exact: powers of two) before anything else.
-  // Null in the TF32 modes.
-  const float* acc_scale;
+  // fp16 modes: row i of the A panel holds A[i,:] * 2^ea(i) and row j of the B panel holds B[:,j] * 2^eb(j); the
+  // preparation kernels leave 2^-ea(i) in row_scale[i] and 2^-eb(j) in col_scale[j], and the epilogue multiplies
+  // each accumulator by both (exact: powers of two) before anything else.  Null in the TF32 modes.
+  const float* row_scale;
+  const float* col_scale;
 };
 
 __device__ __forceinline__ void store_replicas(const GemmParams& p, long long offset, float x) {
@@ -106,7 +107,6 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 template <int BN>
 __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t taddr, float* tbuf, int lane, int row0, int n0) {
   const int rows_here = min(32, p.M - row0);  // may be <= 0 for a ragged last tile
-  const float s0 = p.acc_scale ? p.acc_scale[0] : 1.0f, s1 = p.acc_scale ? p.acc_scale[1] : 1.0f;
   if (p.vec_epilogue) {
     const int sub = lane >> 3;       // this lane's row within each group of four rows
     const int cq = (lane & 7) * 4;   // first column of this lane's quad within a 32-column chunk
@@ -126,6 +126,7 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t tadd
       const int col = n0 + chunk * 32 + cq;
       if (col < p.N) {  // N is a multiple of 4 on this path: the whole quad is inside
         const float4 bv = p.bias ? *reinterpret_cast<const float4*>(p.bias + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 cs = p.col_scale ? *reinterpret_cast<const float4*>(p.col_scale + col) : make_float4(1.f, 1.f, 1.f, 1.f);
         float4 cv[8];
         if (p.C) {
           // all loads of C before the first use, so that their latencies overlap
@@ -140,8 +141,9 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t tadd
           const int r = sub + 4 * i;
           if (r < rows_here) {
             const float4 a = *reinterpret_cast<const float4*>(tbuf + r * GEMM_EPI_LD + cq);
-            float4 x = make_float4(p.alpha * ((a.x * s0) * s1), p.alpha * ((a.y * s0) * s1), p.alpha * ((a.z * s0) * s1),
-                                   p.alpha * ((a.w * s0) * s1));
+            const float rs = p.row_scale ? p.row_scale[row0 + r] : 1.0f;
+            float4 x = make_float4(p.alpha * ((a.x * rs) * cs.x), p.alpha * ((a.y * rs) * cs.y), p.alpha * ((a.z * rs) * cs.z),
+                                   p.alpha * ((a.w * rs) * cs.w));
             if (p.C) {
               x.x = fmaf(p.beta, cv[i].x, x.x);
               x.y = fmaf(p.beta, cv[i].y, x.y);
@@ -191,6 +193,7 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t tadd
     __syncwarp();
     if (col < p.N) {
       const float bias_v = p.bias ? p.bias[col] : 0.0f;
+      const float cs = p.col_scale ? p.col_scale[col] : 1.0f;
       if (rows_here >= 32) {
         // full 32-row slab: issue all 32 loads of C before the first use so that
         // their latencies overlap instead of adding up
@@ -203,7 +206,8 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t tadd
         float* dp = p.D + static_cast<long long>(row0) * p.ldd + col;
 #pragma unroll
         for (int rr = 0; rr < 32; ++rr) {
-          float x = p.alpha * ((tbuf[rr * 33 + lane] * s0) * s1);
+          const float rs = p.row_scale ? p.row_scale[row0 + rr] : 1.0f;
+          float x = p.alpha * ((tbuf[rr * 33 + lane] * rs) * cs);
           if (p.C) x = fmaf(p.beta, cv[rr], x);
           x += bias_v;
           if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
@@ -213,7 +217,8 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t tadd
       } else {
         for (int rr = 0; rr < rows_here; ++rr) {
           const long long row = row0 + rr;
-          float x = p.alpha * ((tbuf[rr * 33 + lane] * s0) * s1);
+          const float rs = p.row_scale ? p.row_scale[row] : 1.0f;
+          float x = p.alpha * ((tbuf[rr * 33 + lane] * rs) * cs);
           if (p.C) x = fmaf(p.beta, p.C[row * p.ldc + col], x);
           x += bias_v;
           if (p.act == 1) x = (x > 0.0f) ? x : 0.0f;
@@ -533,55 +538,18 @@ __global__ void prep_b_kernel(const float* __restrict__ B, long long ldb, float*
 }
 
 // ------------------------------------------------------------------------
-// Operand preparation for the fp16 three-term split (mode 4)
+// Operand preparation for the fp16 modes
 // ------------------------------------------------------------------------
-// fp16 has the mantissa of TF32 (11 significant bits) but a 5-bit exponent, so each matrix is first scaled
-// by a power of two that brings its largest magnitude into [2^14, 2^15) — exact — and then split as
+// fp16 has the mantissa of TF32 (11 significant bits) but a 5-bit exponent, so every row of A and every column of
+// B is first scaled by a power of two of its own that brings its largest magnitude into [2^14, 2^15) — exact — and
+// then split as
 //   hi = rn_f16(x * s),   lo = rn_f16(x * s - hi)        (the difference is exact in fp32).
-// Elements more than 2^16 below the largest lose low bits of `lo` to fp16's subnormal spacing; their absolute
-// error stays below 2^-39 of the largest element.  The scale comes from a max-abs pass over the matrix.
+// The epilogue undoes the scales (row_scale[i] * col_scale[j], exact).  Elements more than 2^16 below the largest
+// of their row (column) lose low bits of `lo` to fp16's subnormal spacing: an absolute error below 2^-39 of that
+// largest element.
 
-// max |x| over two rows x cols matrices as float bits in out[0] and out[1] (non-negative floats order like
-// unsigned integers); both words must be zero before the launch.  A NaN or an infinity ends up as a value above
-// FLT_MAX's bits.  Blocks [0, blocks_a) scan the first matrix, the rest the second; `flat` matrices (contiguous
-// rows, 16-byte aligned) are read as 128-bit vectors.
-struct AbsmaxJob {
-  const float* src;
-  long long ld;
-  int rows, cols;
-  int flat;
-};
-
-__device__ __forceinline__ unsigned int absmax_scan(const AbsmaxJob& j, long long block, long long nblocks) {
-  unsigned int m = 0;
-  const long long total = static_cast<long long>(j.rows) * j.cols;
-  if (j.flat) {
-    const long long nvec = total >> 2;
-    const float4* v = reinterpret_cast<const float4*>(j.src);
-    for (long long i = block * blockDim.x + threadIdx.x; i < nvec; i += nblocks * blockDim.x) {
-      const float4 x = v[i];
-      m = max(max(m, __float_as_uint(x.x) & 0x7fffffffu), __float_as_uint(x.y) & 0x7fffffffu);
-      m = max(max(m, __float_as_uint(x.z) & 0x7fffffffu), __float_as_uint(x.w) & 0x7fffffffu);
-    }
-    if (block == 0 && threadIdx.x < (total & 3)) m = max(m, __float_as_uint(j.src[(nvec << 2) + threadIdx.x]) & 0x7fffffffu);
-  } else {
-    for (long long i = block * blockDim.x + threadIdx.x; i < total; i += nblocks * blockDim.x) {
-      const long long r = i / j.cols;
-      m = max(m, __float_as_uint(j.src[r * j.ld + (i - r * j.cols)]) & 0x7fffffffu);
-    }
-  }
-  return m;
-}
-
-__global__ void absmax_two_kernel(const AbsmaxJob a, const AbsmaxJob b, int blocks_a, unsigned int* out) {
-  const bool first = static_cast<int>(blockIdx.x) < blocks_a;
-  unsigned int m = first ? absmax_scan(a, blockIdx.x, blocks_a) : absmax_scan(b, blockIdx.x - blocks_a, gridDim.x - blocks_a);
-  for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if ((threadIdx.x & 31) == 0 && m) atomicMax(out + (first ? 0 : 1), m);
-}
-
-// The power of two that maps the matrix's largest magnitude into [2^14, 2^15); 1 for an all-zero matrix or one
-// that holds a NaN or an infinity (its product is non-finite whatever the scale).
+// The power of two that maps a largest magnitude (given as float bits) into [2^14, 2^15); 1 for an all-zero row or
+// one that holds a NaN or an infinity (its products are non-finite whatever the scale).
 __device__ __forceinline__ float f16_panel_scale(unsigned int maxbits) {
   const int e = static_cast<int>(maxbits >> 23);           // biased exponent of the maximum
   if (maxbits == 0 || e == 255) return 1.0f;
@@ -598,45 +566,72 @@ __device__ __forceinline__ void f16_split(float x, float s, __half& hi, __half& 
   lo = (fabsf(h) <= 65504.0f) ? __float2half_rn(xs - h) : __float2half_rn(0.0f);
 }
 
-// A[M x K] -> hi, lo [M x Kp] halves (lo may be null: single-pass fp16 mode), Kp = K rounded up to 64, padding zero.  One thread per 8 consecutive k: two
-// 128-bit loads when the rows allow it (vec_ok), one 128-bit store per panel.  Thread 0 also leaves 1/scale in
-// inv_scale[slot] for the GEMM's epilogue.
+__device__ __forceinline__ unsigned int abs_bits(float x) { return __float_as_uint(x) & 0x7fffffffu; }
+
+// A[M x K] -> hi, lo [M x Kp] halves (lo may be null: single-pass mode), Kp = K rounded up to 64, padding zero, and
+// row_scale[M].  One warp per row: a first sweep finds the row's largest magnitude (non-negative floats order like
+// unsigned integers), a second — the row comes from cache — scales, splits and stores 8 elements per lane and step
+// (two 128-bit loads when the rows allow it, one 128-bit store per panel).
 __global__ void prep_a_f16_kernel(const float* __restrict__ A, long long lda, __half* __restrict__ hi, __half* __restrict__ lo,
-                                  int M, int K, int Kp, const unsigned int* maxbits, float* inv_scale, int slot, int vec_ok) {
-  const float s = f16_panel_scale(*maxbits);
-  if (blockIdx.x == 0 && threadIdx.x == 0) inv_scale[slot] = 1.0f / s;  // exact: s is a power of two
-  const long long octs_per_row = Kp >> 3;
-  const long long total = static_cast<long long>(M) * octs_per_row;
-  for (long long q = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; q < total;
-       q += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long row = q / octs_per_row;
-    const int k = static_cast<int>(q - row * octs_per_row) << 3;
-    const float* src = A + row * lda + k;
-    float x[8];
-    if (vec_ok && k + 7 < K) {
-      const float4 u = *reinterpret_cast<const float4*>(src), w = *reinterpret_cast<const float4*>(src + 4);
-      x[0] = u.x; x[1] = u.y; x[2] = u.z; x[3] = u.w;
-      x[4] = w.x; x[5] = w.y; x[6] = w.z; x[7] = w.w;
+                                  float* __restrict__ row_scale, int M, int K, int Kp, int vec_ok) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  for (long long row = blockIdx.x * static_cast<long long>(warps_per_block) + (threadIdx.x >> 5); row < M;
+       row += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const float* src = A + row * lda;
+    unsigned int m = 0;
+    if (vec_ok) {
+      const float4* v = reinterpret_cast<const float4*>(src);
+      for (int q = lane; q < (K >> 2); q += 32) {
+        const float4 x = v[q];
+        m = max(max(m, abs_bits(x.x)), max(abs_bits(x.y), max(abs_bits(x.z), abs_bits(x.w))));
+      }
+      for (int k = (K & ~3) + lane; k < K; k += 32) m = max(m, abs_bits(src[k]));
     } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] = (k + j < K) ? src[j] : 0.0f;
+      for (int k = lane; k < K; k += 32) m = max(m, abs_bits(src[k]));
     }
-    __align__(16) __half h[8];
-    __align__(16) __half l[8];
+    for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float s = f16_panel_scale(m);
+    if (lane == 0) row_scale[row] = 1.0f / s;  // exact: s is a power of two
+    for (int k = lane * 8; k < Kp; k += 256) {
+      float x[8];
+      if (vec_ok && k + 7 < K) {
+        const float4 u = *reinterpret_cast<const float4*>(src + k), w = *reinterpret_cast<const float4*>(src + k + 4);
+        x[0] = u.x; x[1] = u.y; x[2] = u.z; x[3] = u.w;
+        x[4] = w.x; x[5] = w.y; x[6] = w.z; x[7] = w.w;
+      } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) f16_split(x[j], s, h[j], l[j]);
-    *reinterpret_cast<uint4*>(hi + row * Kp + k) = *reinterpret_cast<const uint4*>(h);
-    if (lo) *reinterpret_cast<uint4*>(lo + row * Kp + k) = *reinterpret_cast<const uint4*>(l);
+        for (int j = 0; j < 8; ++j) x[j] = (k + j < K) ? src[k + j] : 0.0f;
+      }
+      __align__(16) __half h[8];
+      __align__(16) __half l[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f16_split(x[j], s, h[j], l[j]);
+      *reinterpret_cast<uint4*>(hi + row * Kp + k) = *reinterpret_cast<const uint4*>(h);
+      if (lo) *reinterpret_cast<uint4*>(lo + row * Kp + k) = *reinterpret_cast<const uint4*>(l);
+    }
   }
 }
 
-// B[K x N] -> hi, lo [N x Kp] halves, transposed through shared memory in tiles of 64 k x 32 n so that every
-// warp store writes one 128-byte run of a panel row (64 halves of k); block (32, 8); Kp is a multiple of 64.
+// Largest magnitude of every column of B[K x N] as float bits in col_bits[N] (zero before the launch).  Block
+// (x, y) scans columns [256x, 256x + 256) of rows [rows_per_block * y, ...): one column per thread, so a warp reads
+// 128 contiguous bytes per row.
+__global__ void colmax_kernel(const float* __restrict__ B, long long ldb, int K, int N, int rows_per_block,
+                              unsigned int* __restrict__ col_bits) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const int k0 = blockIdx.y * rows_per_block, k1 = min(K, k0 + rows_per_block);
+  unsigned int m = 0;
+  for (int k = k0; k < k1; ++k) m = max(m, abs_bits(B[static_cast<long long>(k) * ldb + n]));
+  if (m) atomicMax(col_bits + n, m);
+}
+
+// B[K x N] -> hi, lo [N x Kp] halves and col_scale[N], transposed through shared memory in tiles of 64 k x 32 n so
+// that every warp store writes one 128-byte run of a panel row (64 halves of k); block (32, 8); Kp is a multiple
+// of 64; column j is scaled by the power of two its largest magnitude (col_bits) asks for.
 __global__ void prep_b_f16_kernel(const float* __restrict__ B, long long ldb, __half* __restrict__ hi, __half* __restrict__ lo,
-                                  int K, int N, int Kp, const unsigned int* maxbits, float* inv_scale, int slot) {
+                                  float* __restrict__ col_scale, const unsigned int* __restrict__ col_bits, int K, int N, int Kp) {
   __shared__ float tile[64][33];
-  const float s = f16_panel_scale(*maxbits);
-  if (blockIdx.x == 0 && threadIdx.x == 0 && threadIdx.y == 0) inv_scale[slot] = 1.0f / s;
   const long long k_tiles = Kp >> 6;
   const long long n_tiles = (N + 31) >> 5;
   const long long total = k_tiles * n_tiles;
@@ -656,6 +651,8 @@ __global__ void prep_b_f16_kernel(const float* __restrict__ B, long long ldb, __
     for (int j = 0; j < 32; j += 8) {
       const int nl = threadIdx.y + j, n = n0 + nl;
       if (n < N) {
+        const float s = f16_panel_scale(col_bits[n]);
+        if (kt == 0 && threadIdx.x == 0) col_scale[n] = 1.0f / s;
         __half h0, l0, h1, l1;
         f16_split(tile[2 * threadIdx.x][nl], s, h0, l0);
         f16_split(tile[2 * threadIdx.x + 1][nl], s, h1, l1);

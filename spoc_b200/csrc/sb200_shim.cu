@@ -681,7 +681,8 @@ int encode_map_f16(CUtensorMap* map, const __half* base, long long kp, long long
 
 size_t gemm_f16_workspace_need(long long M, long long N, long long K, bool three) {
   const long long kp = round_up(K, 64);
-  return 1024 + (three ? 2 : 1) * (round_up(M * kp * 2, 1024) + round_up(N * kp * 2, 1024));
+  return 2 * round_up(N * 4, 1024) + round_up(M * 4, 1024) +
+         (three ? 2 : 1) * (round_up(M * kp * 2, 1024) + round_up(N * kp * 2, 1024));
 }
 
 // THREE: hi and lo panels, three MMAs per k-step (SB200_MODE_3XF16); else hi panels only, one MMA (SB200_MODE_F16).
@@ -712,42 +713,41 @@ int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, l
     CU_TRY(cudaEventCreate(&rec.e2));
     CU_TRY(cudaEventRecord(rec.e0, st));
   }
-  // scratch: [max |A| bits, max |B| bits, 1/scale_A, 1/scale_B | pad to 1 KiB][A_hi][B_hi]([A_lo][B_lo])
+  // scratch: [column maxima of B, N words][1/scale per column, N floats][1/scale per row of A, M floats]
+  //          [A_hi][B_hi]([A_lo][B_lo]), every part rounded up to 1 KiB
   uint8_t* ws = static_cast<uint8_t*>(d.workspace);
-  unsigned int* maxbits = reinterpret_cast<unsigned int*>(ws);
-  float* inv_scale = reinterpret_cast<float*>(ws + 8);
-  __half* a_hi = reinterpret_cast<__half*>(ws + 1024);
-  __half* b_hi = reinterpret_cast<__half*>(ws + 1024 + a_bytes);
-  __half* a_lo = THREE ? reinterpret_cast<__half*>(ws + 1024 + a_bytes + b_bytes) : nullptr;
-  __half* b_lo = THREE ? reinterpret_cast<__half*>(ws + 1024 + 2 * a_bytes + b_bytes) : nullptr;
-  CU_TRY(cudaMemsetAsync(maxbits, 0, 8, st));
-  const long long cap16 = static_cast<long long>(d.sm_count) * 16;
+  const size_t col_bytes = round_up(N * 4, 1024), row_bytes = round_up(M * 4, 1024);
+  unsigned int* col_bits = reinterpret_cast<unsigned int*>(ws);
+  float* col_scale = reinterpret_cast<float*>(ws + col_bytes);
+  float* row_scale = reinterpret_cast<float*>(ws + 2 * col_bytes);
+  uint8_t* panels = ws + 2 * col_bytes + row_bytes;
+  __half* a_hi = reinterpret_cast<__half*>(panels);
+  __half* b_hi = reinterpret_cast<__half*>(panels + a_bytes);
+  __half* a_lo = THREE ? reinterpret_cast<__half*>(panels + a_bytes + b_bytes) : nullptr;
+  __half* b_lo = THREE ? reinterpret_cast<__half*>(panels + 2 * a_bytes + b_bytes) : nullptr;
+  CU_TRY(cudaMemsetAsync(col_bits, 0, static_cast<size_t>(N) * 4, st));
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   {
-    // largest magnitudes of A and B in one launch
-    long long ga = (M * K + 4095) / 4096, gb = (K * N + 4095) / 4096;
-    if (ga > cap16) ga = cap16;
-    if (gb > cap16) gb = cap16;
-    if (ga < 1) ga = 1;
-    if (gb < 1) gb = 1;
-    const AbsmaxJob ja{A, lda, static_cast<int>(M), static_cast<int>(K), (lda == K && al16(A)) ? 1 : 0};
-    const AbsmaxJob jb{B, ldb, static_cast<int>(K), static_cast<int>(N), (ldb == N && al16(B)) ? 1 : 0};
-    absmax_two_kernel<<<static_cast<unsigned>(ga + gb), 256, 0, st>>>(ja, jb, static_cast<int>(ga), maxbits);
-    if ((rc = launch_check("absmax_two_kernel"))) return rc;
-  }
-  {
-    long long grid = (M * (kp >> 3) + 255) / 256;
-    if (grid > cap16) grid = cap16;
+    // A: one warp per row finds the row's scale and writes its panels
+    long long grid = (M + 7) / 8;
+    const long long cap = static_cast<long long>(d.sm_count) * 8;
+    if (grid > cap) grid = cap;
     const int vec_ok = (al16(A) && (lda & 3) == 0) ? 1 : 0;
-    prep_a_f16_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(A, lda, a_hi, a_lo, static_cast<int>(M), static_cast<int>(K),
-                                                                    static_cast<int>(kp), maxbits, inv_scale, 0, vec_ok);
+    prep_a_f16_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(A, lda, a_hi, a_lo, row_scale, static_cast<int>(M),
+                                                                    static_cast<int>(K), static_cast<int>(kp), vec_ok);
     if ((rc = launch_check("prep_a_f16_kernel"))) return rc;
+    // B: column maxima, then the transposing split
+    const int rows_per_block = 128;
+    const dim3 cgrid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>((K + rows_per_block - 1) / rows_per_block));
+    if (cgrid.y > 65535u) return fail(SB200_ERR_TOO_LARGE, "K beyond the fp16 modes' column scan (K=%lld)", K);
+    colmax_kernel<<<cgrid, 256, 0, st>>>(B, ldb, static_cast<int>(K), static_cast<int>(N), rows_per_block, col_bits);
+    if ((rc = launch_check("colmax_kernel"))) return rc;
     long long tiles = (kp >> 6) * ((N + 31) >> 5);
     const long long cap32 = static_cast<long long>(d.sm_count) * 32;
     if (tiles > cap32) tiles = cap32;
-    prep_b_f16_kernel<<<static_cast<unsigned>(tiles), dim3(32, 8), 0, st>>>(B, ldb, b_hi, b_lo, static_cast<int>(K),
-                                                                             static_cast<int>(N), static_cast<int>(kp), maxbits + 1,
-                                                                             inv_scale, 1);
+    prep_b_f16_kernel<<<static_cast<unsigned>(tiles), dim3(32, 8), 0, st>>>(B, ldb, b_hi, b_lo, col_scale, col_bits,
+                                                                             static_cast<int>(K), static_cast<int>(N),
+                                                                             static_cast<int>(kp));
     if ((rc = launch_check("prep_b_f16_kernel"))) return rc;
   }
   const int clusters = d.sm_count / 2 > 0 ? d.sm_count / 2 : 1;
@@ -766,7 +766,8 @@ int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, l
   gp.status = d.status;
   d.status_armed.store(true);
   derive_params(&gp);
-  gp.acc_scale = inv_scale;
+  gp.row_scale = row_scale;
+  gp.col_scale = col_scale;
   if (prof) CU_TRY(cudaEventRecord(rec.e1, st));
   const int dev_index = static_cast<int>(&d - g_dev);
   rc = THREE ? launch_pair_bn<4, false>(tile_n, d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N)

@@ -978,3 +978,28 @@ def test_f16_single_pass_config_8192_cubed_epilogue_sampled(backend, device):
     finally:
         for x in bufs + [Bi]:
             backend.Memory.free(x)
+
+
+@pytest.mark.parametrize("mode", [L.MODE_3XF16, L.MODE_F16])
+def test_f16_modes_scale_every_row_of_a_and_column_of_b_on_its_own(backend, device, mode):
+    """Rows of A and columns of B that differ by dozens of binary orders of magnitude: each gets its own power-of-two
+    scale, so the panels — and with them the accumulators — are those of the unscaled matrices, and the result is the
+    unscaled result times 2^(e_i + f_j) to the last bit."""
+    M, N, K = 260, 392, 200
+    rng = np.random.default_rng(8)
+    a0, b0 = O.fill(M * K, 96, 1).reshape(M, K), O.fill(K * N, 96, 2).reshape(K, N)
+    e, f = rng.integers(-40, 41, M), rng.integers(-40, 41, N)
+    a1 = (a0.astype(np.float64) * np.exp2(e)[:, None]).astype(np.float32)
+    b1 = (b0.astype(np.float64) * np.exp2(f)[None, :]).astype(np.float32)
+    bufs = [dev_from(backend, device, x) for x in (a0, b0, a1, b1)]
+    D0, D1 = Dev(backend, device, M * N), Dev(backend, device, M * N)
+    try:
+        gemm(backend, device, mode, M, N, K, bufs[0], bufs[1], D0)
+        gemm(backend, device, mode, M, N, K, bufs[2], bufs[3], D1)
+        d0, d1 = D0.download().reshape(M, N), D1.download().reshape(M, N)
+        want = (d0.astype(np.float64) * np.exp2(e)[:, None] * np.exp2(f)[None, :]).astype(np.float32)
+        assert np.array_equal(d1, want)
+        assert O.gemm_rel_error(d0, O.gemm(a0.ravel(), b0.ravel(), M, N, K)) <= tol(mode, K)
+    finally:
+        for x in bufs + [D0, D1]:
+            x.free()
