@@ -614,16 +614,34 @@ __global__ void prep_a_f16_kernel(const float* __restrict__ A, long long lda, __
 }
 
 // Largest magnitude of every column of B[K x N] as float bits in col_bits[N] (zero before the launch).  Block
-// (x, y) scans columns [256x, 256x + 256) of rows [rows_per_block * y, ...): one column per thread, so a warp reads
-// 128 contiguous bytes per row.
+// (x, y) scans rows [rows_per_block * y, ...) of a band of columns.  VEC: four columns per thread with 128-bit loads
+// (B 16-byte aligned, ldb and N multiples of 4), 1024 columns per block; else one column per thread, 256 per block.
+template <bool VEC>
 __global__ void colmax_kernel(const float* __restrict__ B, long long ldb, int K, int N, int rows_per_block,
                               unsigned int* __restrict__ col_bits) {
-  const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  if (n >= N) return;
   const int k0 = blockIdx.y * rows_per_block, k1 = min(K, k0 + rows_per_block);
-  unsigned int m = 0;
-  for (int k = k0; k < k1; ++k) m = max(m, abs_bits(B[static_cast<long long>(k) * ldb + n]));
-  if (m) atomicMax(col_bits + n, m);
+  if (VEC) {
+    const int n = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (n >= N) return;
+    unsigned int m0 = 0, m1 = 0, m2 = 0, m3 = 0;
+    for (int k = k0; k < k1; ++k) {
+      const float4 x = *reinterpret_cast<const float4*>(B + static_cast<long long>(k) * ldb + n);
+      m0 = max(m0, abs_bits(x.x));
+      m1 = max(m1, abs_bits(x.y));
+      m2 = max(m2, abs_bits(x.z));
+      m3 = max(m3, abs_bits(x.w));
+    }
+    if (m0) atomicMax(col_bits + n, m0);
+    if (m1) atomicMax(col_bits + n + 1, m1);
+    if (m2) atomicMax(col_bits + n + 2, m2);
+    if (m3) atomicMax(col_bits + n + 3, m3);
+  } else {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    unsigned int m = 0;
+    for (int k = k0; k < k1; ++k) m = max(m, abs_bits(B[static_cast<long long>(k) * ldb + n]));
+    if (m) atomicMax(col_bits + n, m);
+  }
 }
 
 // B[K x N] -> hi, lo [N x Kp] halves and col_scale[N], transposed through shared memory in tiles of 64 k x 32 n so

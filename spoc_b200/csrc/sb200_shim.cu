@@ -737,10 +737,16 @@ int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, l
                                                                     static_cast<int>(K), static_cast<int>(kp), vec_ok);
     if ((rc = launch_check("prep_a_f16_kernel"))) return rc;
     // B: column maxima, then the transposing split
-    const int rows_per_block = 128;
-    const dim3 cgrid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>((K + rows_per_block - 1) / rows_per_block));
+    const int rows_per_block = 64;
+    const bool vec_b = al16(B) && (ldb & 3) == 0 && (N & 3) == 0;
+    const long long cols_per_block = vec_b ? 1024 : 256;
+    const dim3 cgrid(static_cast<unsigned>((N + cols_per_block - 1) / cols_per_block),
+                     static_cast<unsigned>((K + rows_per_block - 1) / rows_per_block));
     if (cgrid.y > 65535u) return fail(SB200_ERR_TOO_LARGE, "K beyond the fp16 modes' column scan (K=%lld)", K);
-    colmax_kernel<<<cgrid, 256, 0, st>>>(B, ldb, static_cast<int>(K), static_cast<int>(N), rows_per_block, col_bits);
+    if (vec_b)
+      colmax_kernel<true><<<cgrid, 256, 0, st>>>(B, ldb, static_cast<int>(K), static_cast<int>(N), rows_per_block, col_bits);
+    else
+      colmax_kernel<false><<<cgrid, 256, 0, st>>>(B, ldb, static_cast<int>(K), static_cast<int>(N), rows_per_block, col_bits);
     if ((rc = launch_check("colmax_kernel"))) return rc;
     long long tiles = (kp >> 6) * ((N + 31) >> 5);
     const long long cap32 = static_cast<long long>(d.sm_count) * 32;
