@@ -582,7 +582,16 @@ __global__ void prep_a_f16_kernel(const float* __restrict__ A, long long lda, __
     unsigned int m = 0;
     if (vec_ok) {
       const float4* v = reinterpret_cast<const float4*>(src);
-      for (int q = lane; q < (K >> 2); q += 32) {
+      const int nq = K >> 2;
+      int q = lane;
+      for (; q + 96 < nq; q += 128) {  // four independent 128-bit loads in flight per lane
+        const float4 x0 = v[q], x1 = v[q + 32], x2 = v[q + 64], x3 = v[q + 96];
+        m = max(max(m, abs_bits(x0.x)), max(abs_bits(x0.y), max(abs_bits(x0.z), abs_bits(x0.w))));
+        m = max(max(m, abs_bits(x1.x)), max(abs_bits(x1.y), max(abs_bits(x1.z), abs_bits(x1.w))));
+        m = max(max(m, abs_bits(x2.x)), max(abs_bits(x2.y), max(abs_bits(x2.z), abs_bits(x2.w))));
+        m = max(max(m, abs_bits(x3.x)), max(abs_bits(x3.y), max(abs_bits(x3.z), abs_bits(x3.w))));
+      }
+      for (; q < nq; q += 32) {
         const float4 x = v[q];
         m = max(max(m, abs_bits(x.x)), max(abs_bits(x.y), max(abs_bits(x.z), abs_bits(x.w))));
       }

@@ -730,7 +730,7 @@ int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, l
   {
     // A: one warp per row finds the row's scale and writes its panels
     long long grid = (M + 7) / 8;
-    const long long cap = static_cast<long long>(d.sm_count) * 8;
+    const long long cap = static_cast<long long>(d.sm_count) * 8;  // fewer rows in flight (to keep them in L2) measured slower
     if (grid > cap) grid = cap;
     const int vec_ok = (al16(A) && (lda & 3) == 0) ? 1 : 0;
     prep_a_f16_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(A, lda, a_hi, a_lo, row_scale, static_cast<int>(M),
