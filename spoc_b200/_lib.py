@@ -60,6 +60,8 @@ SIGNATURES = {
     "sb200_memcpy_dtoh_async": ([i32, C.c_void_p, u64, u64, u64], i32),
     "sb200_host_alloc": ([u64, p(C.c_void_p)], i32),
     "sb200_host_free": ([C.c_void_p], i32),
+    "sb200_host_register": ([C.c_void_p, u64], i32),
+    "sb200_host_unregister": ([C.c_void_p], i32),
     "sb200_stream_create": ([i32, p(u64)], i32),
     "sb200_stream_destroy": ([i32, u64], i32),
     "sb200_stream_synchronize": ([i32, u64], i32),

@@ -1350,6 +1350,28 @@ int sb200_host_free(void* ptr) {
   return SB200_OK;
 }
 
+int sb200_host_register(void* ptr, uint64_t bytes) {
+  if (!ptr || bytes == 0) return fail(SB200_ERR_INVALID_VALUE, "null pointer or empty range");
+  cudaError_t e = cudaHostRegister(ptr, bytes, cudaHostRegisterPortable);
+  if (e == cudaErrorHostMemoryAlreadyRegistered) {
+    cudaGetLastError();
+    return SB200_OK;
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "cudaHostRegister");
+  return SB200_OK;
+}
+
+int sb200_host_unregister(void* ptr) {
+  if (!ptr) return SB200_OK;
+  cudaError_t e = cudaHostUnregister(ptr);
+  if (e == cudaErrorHostMemoryNotRegistered) {
+    cudaGetLastError();
+    return SB200_OK;
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "cudaHostUnregister");
+  return SB200_OK;
+}
+
 int sb200_stream_create(int dev, uint64_t* stream) {
   if (!stream) return fail(SB200_ERR_INVALID_VALUE, "null stream pointer");
   DeviceState* d;

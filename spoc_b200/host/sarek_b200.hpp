@@ -268,7 +268,10 @@ class Vector {
   enum Location { CPU, Both, Stale_CPU };
   Vector(Backend& b, size_t n) : backend_(&b), host_(n, 0.0f) {}
   Vector(Backend& b, std::vector<float> data) : backend_(&b), host_(std::move(data)) {}
-  ~Vector() { free_buffer(); }
+  ~Vector() {
+    free_buffer();
+    if (pinned_) sb200_host_unregister(host_.data());
+  }
   Vector(const Vector&) = delete;
   Vector& operator=(const Vector&) = delete;
 
@@ -277,12 +280,14 @@ class Vector {
   void to_device(const Backend::DeviceT& dev) {
     if (!buf_.ptr) buf_ = backend_->Memory.alloc(dev, host_.size());
     if (loc_ == CPU) {
+      note_transfer();
       backend_->Memory.host_ptr_to_device(host_.data(), host_.size() * sizeof(float), buf_);
       loc_ = Both;
     }
   }
   const std::vector<float>& to_array() {
     if (loc_ == Stale_CPU) {
+      note_transfer();
       backend_->Memory.device_to_host_ptr(buf_, host_.data(), host_.size() * sizeof(float));
       loc_ = Both;
     }
@@ -307,10 +312,19 @@ class Vector {
   const Backend::Buffer& buffer() const { return buf_; }
 
  private:
+  // The vector owns its host array for its whole life, so the array can be pinned in place: a vector of 16 MiB or
+  // more that is moved a second time is registered with the driver, and this and every later transfer run at the
+  // pinned rate; the destructor unregisters.
+  void note_transfer() {
+    if (++transfers_ == 2 && !pinned_ && host_.size() * sizeof(float) >= (size_t(16) << 20))
+      pinned_ = sb200_host_register(host_.data(), host_.size() * sizeof(float)) == SB200_OK;
+  }
   Backend* backend_;
   std::vector<float> host_;
   Backend::Buffer buf_;
   Location loc_ = CPU;
+  int transfers_ = 0;
+  bool pinned_ = false;
 };
 
 struct ScalarArg {

@@ -23,6 +23,7 @@ computes: every operation is a call into libsarek_b200.so.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 from typing import Sequence
 
@@ -434,12 +435,34 @@ class Vector:
 
     CPU, BOTH, STALE_CPU = "CPU", "Both", "Stale_CPU"
 
+    PIN_MIN_BYTES = 16 << 20   # vectors at least this large are pinned in place on their second transfer
+
     def __init__(self, backend: Backend, host: np.ndarray):
         assert host.dtype == np.float32 and host.ndim == 1 and host.flags["C_CONTIGUOUS"]
         self.backend = backend
         self.host = host
         self.buffer: _Memory.Buffer | None = None
         self.location = Vector.CPU
+        self._transfers = 0
+        self._pinned = False
+
+    def _note_transfer(self) -> None:
+        """A vector owns its host array for its whole life (as Spoc_core.Vector owns its Bigarray), so the array can be
+        pinned in place: the first large transfer goes through the staged pageable copier, and a vector that is moved a
+        second time is registered with the driver (sb200_host_register) so that this and every later transfer run at the
+        pinned rate.  SAREK_B200_PIN_VECTORS=0 switches this off; free() unregisters."""
+        self._transfers += 1
+        if (self._transfers == 2 and not self._pinned and self.host.nbytes >= Vector.PIN_MIN_BYTES
+                and os.environ.get("SAREK_B200_PIN_VECTORS", "1") != "0"):
+            if L.load().sb200_host_register(self.host.ctypes.data_as(C.c_void_p), self.host.nbytes) == 0:
+                self._pinned = True
+
+    def __del__(self):
+        if getattr(self, "_pinned", False):     # never leave a registration behind memory that is being released
+            try:
+                L.load().sb200_host_unregister(self.host.ctypes.data_as(C.c_void_p))
+            except Exception:
+                pass
 
     @classmethod
     def create(cls, backend: Backend, n: int) -> "Vector":
@@ -453,11 +476,13 @@ class Vector:
         if self.buffer is None:
             self.buffer = self.backend.Memory.alloc(dev, self.length, np.float32)
         if self.location == Vector.CPU:
+            self._note_transfer()
             self.backend.Memory.host_to_device(src=self.host, dst=self.buffer)
             self.location = Vector.BOTH
 
     def to_array(self) -> np.ndarray:
         if self.location == Vector.STALE_CPU:
+            self._note_transfer()
             self.backend.Memory.device_to_host(src=self.buffer, dst=self.host)
             self.location = Vector.BOTH
         return self.host
@@ -468,6 +493,9 @@ class Vector:
         self.location = Vector.CPU
 
     def free(self) -> None:
+        if self._pinned:
+            L.load().sb200_host_unregister(self.host.ctypes.data_as(C.c_void_p))
+            self._pinned = False
         if self.buffer is not None:
             self.backend.Memory.free(self.buffer)
             self.buffer = None

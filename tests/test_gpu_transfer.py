@@ -76,3 +76,30 @@ def test_large_vector_round_trip_through_the_host_mirror(backend, device):
     v.host[:] = 0
     assert np.array_equal(v.to_array(), data)
     v.free()
+
+
+def test_vector_is_pinned_in_place_on_its_second_large_transfer(backend, device):
+    """A Vector owns its host array, so the plugin registers it with the driver once it is moved a second time; results
+    are unchanged, the registration goes away with free(), and small vectors are left alone."""
+    from spoc_b200 import Vector
+    n = (16 << 20) // 4
+    big, small = Vector(backend, np.arange(n, dtype=np.float32)), Vector(backend, np.arange(1000, dtype=np.float32))
+    try:
+        for v in (big, small):
+            v.to_device(device)
+            assert not v._pinned
+            v.location = Vector.STALE_CPU     # as after a launch: the next host read downloads
+            v.host[:] = -1.0
+            got = v.to_array()
+            assert got[0] == 0.0 and got[-1] == np.float32(len(got) - 1)
+        assert big._pinned and not small._pinned
+        big.location = Vector.CPU
+        big.host[:] = 7.0
+        big.to_device(device)                 # third transfer: from registered memory
+        big.location = Vector.STALE_CPU
+        big.host[:] = 0.0
+        assert np.all(big.to_array() == 7.0)
+    finally:
+        big.free()
+        small.free()
+    assert not big._pinned
