@@ -56,6 +56,8 @@ let sb200_mem_free = fn "sb200_mem_free" (int @-> uint64_t @-> returning int)
 let sb200_memcpy_htod = fn "sb200_memcpy_htod" (int @-> uint64_t @-> ptr void @-> uint64_t @-> returning int)
 let sb200_memcpy_dtoh = fn "sb200_memcpy_dtoh" (int @-> ptr void @-> uint64_t @-> uint64_t @-> returning int)
 let sb200_memcpy_dtod = fn "sb200_memcpy_dtod" (int @-> uint64_t @-> uint64_t @-> uint64_t @-> returning int)
+let sb200_host_register = fn "sb200_host_register" (ptr void @-> uint64_t @-> returning int)
+let sb200_host_unregister = fn "sb200_host_unregister" (ptr void @-> returning int)
 let sb200_stream_create = fn "sb200_stream_create" (int @-> ptr uint64_t @-> returning int)
 let sb200_stream_destroy = fn "sb200_stream_destroy" (int @-> uint64_t @-> returning int)
 let sb200_stream_synchronize = fn "sb200_stream_synchronize" (int @-> uint64_t @-> returning int)

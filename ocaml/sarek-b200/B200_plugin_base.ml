@@ -104,12 +104,38 @@ module B200 = struct
       B.check "sb200_memcpy_dtoh"
         (Lazy.force B.sb200_memcpy_dtoh src.dev dst_ptr src.dptr (Unsigned.UInt64.of_int byte_size))
 
+    (* A Bigarray's storage does not move and lives as long as the Bigarray, so it can be pinned in place.  The first
+       transfer of a Bigarray goes through the library's staged pageable copier; one of 16 MiB or more that is moved a
+       second time is registered with the driver (sb200_host_register), after which this and every later transfer run
+       at the pinned rate.  A finaliser on the Bigarray unregisters before its storage is released.
+       SAREK_B200_PIN_VECTORS=0 switches this off. *)
+    let pin_threshold = 16 * 1024 * 1024
+    let pin_enabled = lazy (Sys.getenv_opt "SAREK_B200_PIN_VECTORS" <> Some "0")
+    let seen : (nativeint, int) Hashtbl.t = Hashtbl.create 64
+
+    let note_transfer (type a b) (ba : (a, b, Bigarray.c_layout) Bigarray.Array1.t) bytes =
+      if bytes >= pin_threshold && Lazy.force pin_enabled then begin
+        let p = bigarray_start array1 ba in
+        let key = raw_address_of_ptr (to_voidp p) in
+        let n = 1 + Option.value ~default:0 (Hashtbl.find_opt seen key) in
+        Hashtbl.replace seen key n ;
+        if n = 2 && Lazy.force B.sb200_host_register (to_voidp p) (Unsigned.UInt64.of_int bytes) = 0 then
+          Gc.finalise
+            (fun ba ->
+              let p = to_voidp (bigarray_start array1 ba) in
+              Hashtbl.remove seen (raw_address_of_ptr p) ;
+              ignore (Lazy.force B.sb200_host_unregister p))
+            ba
+      end
+
     let host_to_device ~src ~dst =
       let bytes = Bigarray.Array1.dim src * Bigarray.kind_size_in_bytes (Bigarray.Array1.kind src) in
+      note_transfer src bytes ;
       host_ptr_to_device ~src_ptr:(to_voidp (bigarray_start array1 src)) ~byte_size:bytes ~dst
 
     let device_to_host ~src ~dst =
       let bytes = Bigarray.Array1.dim dst * Bigarray.kind_size_in_bytes (Bigarray.Array1.kind dst) in
+      note_transfer dst bytes ;
       device_to_host_ptr ~src ~dst_ptr:(to_voidp (bigarray_start array1 dst)) ~byte_size:bytes
 
     let device_to_device ~src ~dst =
