@@ -52,6 +52,7 @@ class DeviceGroup:
         from .plugin import _check
         self._C, self._L, self._check = C, L, _check
         self._lib = L.load()
+        self._seen: dict = {}
         if devices is None:
             devices = list(range(ngpus if ngpus is not None else 1))
         self.devices = list(devices)
@@ -93,13 +94,33 @@ class DeviceGroup:
         self._check(self._lib.sb200_group_last_ms(self.handle, C.byref(ms)))
         return ms.value
 
+    PIN_MIN_BYTES = 16 << 20
+
+    def _note_use(self, arr) -> None:
+        """The policy of plugin.Vector for the arrays this group is handed: an array of 16 MiB or more that comes a second
+        time is pinned in place (sb200_host_register) and held until close(), which unregisters it; later calls then move
+        it by plain DMA instead of staging it through host threads.  SAREK_B200_PIN_VECTORS=0 switches this off."""
+        if arr is None or arr.nbytes < self.PIN_MIN_BYTES or os.environ.get("SAREK_B200_PIN_VECTORS", "1") == "0":
+            return
+        key = arr.ctypes.data
+        seen = self._seen.setdefault(key, [0, None])
+        seen[0] += 1
+        if seen[0] == 2 and seen[1] is None and self._lib.sb200_host_register(arr.ctypes.data_as(self._C.c_void_p), arr.nbytes) == 0:
+            seen[1] = arr          # keeps the memory alive while it is registered
+
     def gemm_host(self, mode: int, m: int, n: int, k: int, a, b, d, *, alpha=1.0, c=None, beta=0.0, bias=None, act: int = 0) -> None:
         """Host operands (numpy float32 arrays, row-major contiguous); D is written in place."""
+        for arr in (a, b, c, d):
+            self._note_use(arr)
         ptr = lambda x: None if x is None else x.ctypes.data
         self._check(self._lib.sb200_gemm_sharded_host(self.handle, mode, m, n, k, ptr(a), k, ptr(b), n, ptr(d), n, alpha, ptr(c), n,
                                                       beta, ptr(bias), act))
 
     def close(self) -> None:
+        for key, (_, arr) in list(self._seen.items()):
+            if arr is not None:
+                self._lib.sb200_host_unregister(arr.ctypes.data_as(self._C.c_void_p))
+        self._seen.clear()
         if self.handle:
             self._check(self._lib.sb200_group_destroy(self.handle))
             self.handle = 0
