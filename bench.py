@@ -201,7 +201,7 @@ def run_reference(args, rank: int, world: int) -> None:
     if rank != 0:
         return
     workers = max(1, (os.cpu_count() or 2) - 1)
-    step, ids = cpu_slab_rate(workers, target_s=2.0)
+    step, ids = cpu_slab_rate(workers, target_s=float(os.environ.get("SAREK_BENCH_TARGET_S", "2.0")))
     for _ in range(args.warmup):
         step()
     t0 = time.perf_counter()
