@@ -471,8 +471,10 @@ int copy_in(int dev, cudaStream_t st, float* dst, const float* src, int64_t rows
   return SB200_OK;
 }
 
+// The row block of one member: B and the bias are already on their way on the member's main stream (the broadcast was
+// enqueued there), so the GEMMs launched on that stream below follow their arrival.
 void member_main(Group* g, int i, const HostCall* hc, int64_t first, int64_t rows, float* dB, float* dBias, float* dA, float* dC,
-                 float* dD, cudaEvent_t b_ready, MemberResult* out) {
+                 float* dD, MemberResult* out) {
   auto fail_here = [&](int rc) {
     out->rc = rc;
     out->msg = sb200_last_error_string();
@@ -484,9 +486,6 @@ void member_main(Group* g, int i, const HostCall* hc, int64_t first, int64_t row
   const bool staged_a = sb200::staged_copy_enabled() && c.K > 0 && sb200::host_memory_is_pageable(c.A);
   const bool staged_c = sb200::staged_copy_enabled() && c.C && sb200::host_memory_is_pageable(c.C);
   const bool staged_d = sb200::staged_copy_enabled() && sb200::host_memory_is_pageable(c.D) && c.ldd == c.N;
-  // the GEMMs of this GPU follow the arrival of B on its main stream
-  if (b_ready && cudaStreamWaitEvent(g->s_main[i], b_ready, 0) != cudaSuccess)
-    return fail_here(set_error(SB200_ERR_INVALID_VALUE, "waiting for B on device %d", dev));
   int64_t chunk = (rows + kHostChunks - 1) / kHostChunks;
   chunk = (chunk + 255) / 256 * 256;  // chunk edges on tile edges
   if (chunk <= 0) chunk = 256;
@@ -617,9 +616,8 @@ extern "C" int sb200_gemm_sharded_host(uint64_t group, int mode, int64_t M, int6
   MemberResult res[kMaxGroup];
   std::vector<std::thread> threads;
   for (int i = 0; i + 1 < n; ++i)
-    threads.emplace_back(member_main, g, i, &hc, first[i], rows[i], dB[i], dBias[i], dA[i], dC[i], dD[i], nullptr, &res[i]);
-  member_main(g, n - 1, &hc, first[n - 1], rows[n - 1], dB[n - 1], dBias[n - 1], dA[n - 1], dC[n - 1], dD[n - 1], nullptr,
-              &res[n - 1]);
+    threads.emplace_back(member_main, g, i, &hc, first[i], rows[i], dB[i], dBias[i], dA[i], dC[i], dD[i], &res[i]);
+  member_main(g, n - 1, &hc, first[n - 1], rows[n - 1], dB[n - 1], dBias[n - 1], dA[n - 1], dC[n - 1], dD[n - 1], &res[n - 1]);
   for (auto& t : threads) t.join();
   for (int i = 0; i < n; ++i)
     if (res[i].rc) return set_error(res[i].rc, "%s", res[i].msg.c_str());
