@@ -887,7 +887,7 @@ def test_f16_split_gather_writes_every_copy(backend, device):
 
 
 def test_exhaustive_small_shapes(backend, device):
-    """Every shape with M, N, K in 1..40, plus the tile-edge sizes, in 3xTF32 mode (TF32 and the fp16 split on every
+    """Every shape with M, N, K in 1..40, plus the tile-edge sizes, in 3xTF32 mode (TF32 and the two fp16 modes on every
     seventh shape): ragged edges in all three dimensions, K far below one k-block, rows and columns below one tile.
     Operands are prefixes of fixed vectors, so a shape costs one launch, one small download and one oracle call.
     Error measure: |gpu - ref| / sum_k |a_ik||b_kj| against the mode's bound."""
@@ -902,10 +902,10 @@ def test_exhaustive_small_shapes(backend, device):
     edge = [63, 64, 65, 127, 128, 129, 255, 256, 257]
     shapes = [(m, n, k) for m in range(1, 41) for n in range(1, 41) for k in range(1, 41)]
     shapes += [(m, n, k) for m in edge for n in (1, 33, 256, 257) for k in (1, 31, 32, 33, 64, 65)]
-    worst = {L.MODE_3XTF32: 0.0, L.MODE_TF32: 0.0, L.MODE_3XF16: 0.0}
+    worst = {L.MODE_3XTF32: 0.0, L.MODE_TF32: 0.0, L.MODE_3XF16: 0.0, L.MODE_F16: 0.0}
     try:
         for idx, (m, n, k) in enumerate(shapes):
-            modes = [L.MODE_3XTF32] + ([L.MODE_TF32, L.MODE_3XF16] if idx % 7 == 0 else [])
+            modes = [L.MODE_3XTF32] + ([L.MODE_TF32, L.MODE_3XF16, L.MODE_F16] if idx % 7 == 0 else [])
             ref = None
             for mode in modes:
                 _check(lib.sb200_memset32(device.id, D.ptr, 0xFFC00000, m * n + 1, 0))   # NaN pattern: an unwritten element shows
