@@ -11,7 +11,7 @@
 // epilogue's own stores into the peers' copies (sb200_gemm_f32_gather; peer access enabled between the
 // group's GPUs) or by NCCL (in-place all-gather, or one broadcast per block when the blocks differ in size).
 // Only this library's kernels store to peer memory, with plain stores; no library kernel is handed a peer
-// pointer and no multicast load exists in the library.
+// pointer, and every TMA load in the library reads the issuing GPU's own memory into the issuing block.
 //
 // Everything here is built from the public per-device entry points, so a group of one GPU behaves exactly
 // as those do.

@@ -34,4 +34,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_generated_cuda.py /path/to/reference")
+    main(sys.argv[1])
