@@ -416,8 +416,8 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 
     # ---- e2e: host buffers, copies inside the timed region ---------------------------------
     # One GPU: the headline is the plugin path itself — Execute.run_vectors on the epilogue kernel's IR with host-resident
-    # vectors in ordinary pageable memory (what a Bigarray is): Transfer.to_device of every argument, the launch,
-    # Transfer.to_cpu of the result, one after the other as in the reference.  The direct operator on pinned and on
+    # vectors in ordinary pageable memory (what a Bigarray is): the uploads of Transfer.to_device folded into the launch
+    # call, which overlaps them with the GEMM by row blocks, then Transfer.to_cpu of the result.  The direct operator on pinned and on
     # pageable buffers (one C-ABI call that overlaps copies and row-block GEMMs) is reported beside it.
     # Several GPUs: the call a single-process host makes, sb200_gemm_sharded_host on a group of all the GPUs — B
     # crosses PCIe once and reaches the other GPUs by NCCL broadcast, every GPU moves only its own rows — issued by
@@ -465,8 +465,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         e2e = {"value": flops_step / (ms6 / s6 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms6 / s6,
                "h2d_bytes_per_step": e2e_bytes_in, "d2h_bytes_per_step": e2e_bytes_out,
                "api": "Execute.run_vectors mirror (spoc_b200.plugin.run_vectors) on the epilogue kernel's IR: host vectors in "
-                      "ordinary (pageable) memory, which the plugin pins in place on their second transfer; synchronous upload "
-                      "of A, B, C, bias, launch, download of D, one after the other as in the reference",
+                      "ordinary (pageable) memory, which the plugin pins in place on their second transfer; the launch call "
+                      "(sb200_kernel_launch_from_host) uploads A, B, C, bias by row blocks with the GEMM of each block behind "
+                      "its rows; then the download of D",
                "direct_operator_pinned": {"value": flops_step / (ms3 / s3 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms3 / s3,
                                           "api": "sb200_gemm_f32_host on pinned buffers: copies, row-block GEMMs and copy-out overlapped"},
                "direct_operator_pageable": {"value": flops_step / (ms5 / 3 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms5 / 3,

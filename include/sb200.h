@@ -171,6 +171,28 @@ SB200_API int sb200_kernel_launch(uint64_t kernel, const sb200_arg *args, int na
                                   const uint32_t grid[3], const uint32_t block[3],
                                   uint32_t shared_mem, uint64_t stream);
 
+/* The same launch for arguments that are still in host memory: host_ptrs has one entry per argument; for a
+ * SB200_ARG_BUFFER argument a non-null entry means "fill this device buffer from here first" (as many float32 as the
+ * length argument that follows it says), every other entry is ignored.  It stands for the reference's
+ * Transfer.to_device of each argument followed by the launch (sarek/sarek/Execute.ml:520-543,
+ * sarek/core/Transfer.ml:229-268) in one call, which lets the library overlap the two: when the kernel is a recognised
+ * matmul whose launch covers the whole product and the host arrays are pinned or registered, B and the bias go first and
+ * A and C follow in row blocks, each block's GEMM starting when its rows have arrived; otherwise the vectors are
+ * copied whole (staged when pageable and large) and the kernel is launched behind them.  The call returns when every
+ * upload has completed, so the host arrays may be changed at once; the kernel may still be running on `stream`. */
+SB200_API int sb200_kernel_launch_from_host(uint64_t kernel, const sb200_arg *args, int nargs,
+                                            const void *const *host_ptrs, void *const *host_out,
+                                            int32_t *prefetched, const uint32_t grid[3],
+                                            const uint32_t block[3], uint32_t shared_mem, uint64_t stream);
+/* host_out and prefetched (both null, or both tables of nargs entries) extend the call to the way back: a non-null
+ * host_out entry of a buffer argument names the host array the caller keeps that vector's host copy in.  The reference
+ * marks every vector argument stale on the host after a launch (sarek/sarek/Execute.ml:546-553) and downloads it when
+ * the host next reads it (sarek/core/Transfer.ml:272-322); a stale host copy may therefore be overwritten early.  For
+ * the vector a recognised matmul writes, when that array is pinned or registered, the library sends the result back
+ * behind the kernel (row block by row block on the pipelined route) and sets prefetched[i] = 1; every other entry is
+ * set to 0 and the caller downloads as before.  The host copy is complete once sb200_prefetch_wait has returned. */
+SB200_API int sb200_prefetch_wait(int dev);
+
 /* ---- IR fusion: the host-side rewrite of sarek/sarek/Sarek_fusion.ml
  *      (can_fuse :401-431, fuse :459-547, fuse_pipeline :570-598) on IR text.
  *      Results are written to `out` (NUL-terminated, at most outlen bytes). */

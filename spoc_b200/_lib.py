@@ -76,6 +76,9 @@ SIGNATURES = {
     "sb200_kernel_kind": ([u64, p(i32)], i32),
     "sb200_kernel_describe": ([u64, C.c_char_p, i32], i32),
     "sb200_kernel_launch": ([u64, p(Arg), i32, p(C.c_uint32), p(C.c_uint32), C.c_uint32, u64], i32),
+    "sb200_kernel_launch_from_host": ([u64, p(Arg), i32, p(C.c_void_p), p(C.c_void_p), p(C.c_int32), p(C.c_uint32),
+                                      p(C.c_uint32), C.c_uint32, u64], i32),
+    "sb200_prefetch_wait": ([i32], i32),
     "sb200_ir_can_fuse": ([C.c_char_p, C.c_char_p, C.c_char_p, p(i32)], i32),
     "sb200_ir_fuse": ([C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, i32], i32),
     "sb200_ir_fuse_pipeline": ([p(C.c_char_p), i32, C.c_char_p, i32, C.c_char_p, i32], i32),

@@ -872,12 +872,16 @@ KernelObj* find_kernel(uint64_t h) {
 struct Slot {
   bool is_vec = false;
   uint64_t ptr = 0;
+  const void* host = nullptr;  // launch-from-host: the device buffer is to be filled from here first
+  void* host_out = nullptr;    // launch-from-host: where the caller keeps the host copy (result brought back behind the kernel)
+  int arg = -1;                // position of the buffer in the caller's argument list
   long long len = 0;
   double f = 0.0;
   long long i = 0;
 };
 
-int bind_args(const KernelPlan& plan, const sb200_arg* args, int nargs, std::vector<Slot>* slots) {
+int bind_args(const KernelPlan& plan, const sb200_arg* args, int nargs, std::vector<Slot>* slots,
+              const void* const* host_ptrs = nullptr, void* const* host_out = nullptr) {
   slots->assign(plan.params.size(), Slot());
   int a = 0;
   for (size_t p = 0; p < plan.params.size(); ++p) {
@@ -889,6 +893,9 @@ int bind_args(const KernelPlan& plan, const sb200_arg* args, int nargs, std::vec
                     plan.name.c_str(), p, pi.name.c_str());
       s.is_vec = true;
       s.ptr = args[a].v.buffer;
+      s.host = host_ptrs ? host_ptrs[a] : nullptr;
+      s.host_out = host_out ? host_out[a] : nullptr;
+      s.arg = a;
       s.len = args[a + 1].v.i32;
       if (s.len < 0) return fail(SB200_ERR_ARGS, "kernel '%s': negative length for vector %s", plan.name.c_str(), pi.name.c_str());
       a += 2;
@@ -1079,8 +1086,37 @@ int launch_map_kernel(DeviceState& d, KernelObj& kobj, const std::vector<Slot>& 
                  coef_value(m.scalar, s), n);
 }
 
+int gemm_upload_pipeline(DeviceState& d, cudaStream_t st, int mode, long long M, long long N, long long K, const Slot& a,
+                         const Slot& b, const Slot* c, const Slot* bias, const Slot& dd, float alpha, float beta, int act, void* d_host);
+
+int ensure_pipe_streams(DeviceState& d) {
+  if (!d.pipe_in) {
+    CU_TRY(cudaStreamCreateWithFlags(&d.pipe_in, cudaStreamNonBlocking));
+    CU_TRY(cudaStreamCreateWithFlags(&d.pipe_compute, cudaStreamNonBlocking));
+    CU_TRY(cudaStreamCreateWithFlags(&d.pipe_out, cudaStreamNonBlocking));
+  }
+  return SB200_OK;
+}
+
+// Copies `bytes` from the device to page-locked host memory on the outbound stream, behind what `st` holds so far.
+int download_behind(DeviceState& d, cudaStream_t st, void* host, uint64_t dev_ptr, size_t bytes) {
+  int rc = ensure_pipe_streams(d);
+  if (rc) return rc;
+  cudaEvent_t e = nullptr;
+  CU_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  cudaError_t ce = cudaEventRecord(e, st);
+  if (ce == cudaSuccess) ce = cudaStreamWaitEvent(d.pipe_out, e, 0);
+  if (ce == cudaSuccess && bytes) ce = cudaMemcpyAsync(host, as_ptr<void>(dev_ptr), bytes, cudaMemcpyDeviceToHost, d.pipe_out);
+  cudaEventDestroy(e);
+  return ce == cudaSuccess ? SB200_OK : cuda_fail(ce, "download of a result behind its kernel");
+}
+
+// pipeline_uploads: some operands are still in (pinned) host memory; when the launch covers the whole product they are
+// moved by row blocks with the GEMM of each block behind its rows.  *pipelined tells the caller whether that happened.
+// d_host: page-locked host memory the result is to be brought back to behind the kernel (null: leave it on the device).
 int launch_gemm_kernel(DeviceState& d, const KernelPlan& plan, const std::vector<Slot>& s, const uint32_t grid[3],
-                       const uint32_t block[3], cudaStream_t st) {
+                       const uint32_t block[3], cudaStream_t st, bool pipeline_uploads = false, bool* pipelined = nullptr,
+                       void* d_host = nullptr) {
   const GemmPlan& g = plan.gemm;
   const long long M = s[g.m].i, N = s[g.n].i, K = s[g.k].i;
   if (M < 0 || N < 0 || K < 0) return fail(SB200_ERR_ARGS, "kernel '%s': negative m, n or k", plan.name.c_str());
@@ -1106,17 +1142,111 @@ int launch_gemm_kernel(DeviceState& d, const KernelPlan& plan, const std::vector
     long long Me = static_cast<long long>(grid[1]) * block[1], Ne = static_cast<long long>(grid[0]) * block[0];
     if (Me > M) Me = M;
     if (Ne > N) Ne = N;
-    return run_gemm(d, st, mode, Me, Ne, K, A, K, B, N, D, N, alpha, C, N, beta, bias, g.act);
+    if (pipeline_uploads && Me == M && Ne == N && M > 0 && N > 0) {
+      *pipelined = true;
+      return gemm_upload_pipeline(d, st, mode, M, N, K, s[g.a], s[g.b], g.c >= 0 ? &s[g.c] : nullptr, g.bias >= 0 ? &s[g.bias] : nullptr,
+                                  s[g.d], alpha, beta, g.act, d_host);
+    }
+    if (pipeline_uploads) return SB200_OK;  // partial launch: the caller uploads whole vectors and launches again
+    rc = run_gemm(d, st, mode, Me, Ne, K, A, K, B, N, D, N, alpha, C, N, beta, bias, g.act);
+    if (!rc && d_host) rc = download_behind(d, st, d_host, D, static_cast<size_t>(s[g.d].len) * 4);
+    return rc;
   }
   // naive shape: thread tid computes element tid of the row-major result
   long long covered = static_cast<long long>(grid[0]) * block[0];
   if (covered > M * N) covered = M * N;
-  if (N == 0) return SB200_OK;
+  if (N == 0) return d_host && !pipeline_uploads ? download_behind(d, st, d_host, D, static_cast<size_t>(s[g.d].len) * 4) : SB200_OK;
+  if (pipeline_uploads && covered == M * N && M > 0) {
+    *pipelined = true;
+    return gemm_upload_pipeline(d, st, mode, M, N, K, s[g.a], s[g.b], g.c >= 0 ? &s[g.c] : nullptr, g.bias >= 0 ? &s[g.bias] : nullptr,
+                                s[g.d], alpha, beta, g.act, d_host);
+  }
+  if (pipeline_uploads) return SB200_OK;  // partial launch: as above
   const long long full_rows = covered / N, rest = covered - full_rows * N;
   rc = run_gemm(d, st, mode, full_rows, N, K, A, K, B, N, D, N, alpha, C, N, beta, bias, g.act);
-  if (rc || rest == 0) return rc;
-  const uint64_t off_a = static_cast<uint64_t>(full_rows) * K * 4, off_d = static_cast<uint64_t>(full_rows) * N * 4;
-  return run_gemm(d, st, mode, 1, rest, K, A + off_a, K, B, N, D + off_d, N, alpha, C ? C + off_d : 0, N, beta, bias, g.act);
+  if (!rc && rest != 0) {
+    const uint64_t off_a = static_cast<uint64_t>(full_rows) * K * 4, off_d = static_cast<uint64_t>(full_rows) * N * 4;
+    rc = run_gemm(d, st, mode, 1, rest, K, A + off_a, K, B, N, D + off_d, N, alpha, C ? C + off_d : 0, N, beta, bias, g.act);
+  }
+  if (!rc && d_host) rc = download_behind(d, st, d_host, D, static_cast<size_t>(s[g.d].len) * 4);
+  return rc;
+}
+
+// Operands that still sit in pinned host memory are brought over by row blocks on the device's inbound stream while
+// the GEMM of the blocks that have arrived runs on `st`: B and the bias first, then A and C in about eight row blocks
+// (multiples of 256 rows so that block edges are tile edges).  Returns once every upload has completed — the caller's
+// host arrays may then be changed — while the last GEMMs may still be running on `st`.  With d_host, each block of
+// D follows its GEMM back to the host on the outbound stream (the caller waits for that stream before reading it).
+int gemm_upload_pipeline(DeviceState& d, cudaStream_t st, int mode, long long M, long long N, long long K, const Slot& a,
+                         const Slot& b, const Slot* c, const Slot* bias, const Slot& dd, float alpha, float beta, int act, void* d_host) {
+  std::lock_guard<std::mutex> host_call_lock(d.host_call_mu);  // the inbound stream is shared with the host-operand calls
+  int src = ensure_pipe_streams(d);
+  if (src) return src;
+  long long block_rows = (M + 7) / 8;
+  block_rows = (block_rows + 255) / 256 * 256;
+  if (block_rows > M) block_rows = M;
+  std::vector<cudaEvent_t> events;
+  auto done = [&](int rc) {
+    cudaStreamSynchronize(d.pipe_in);  // every upload has landed (or failed) before the host arrays are given back
+    for (auto e : events) cudaEventDestroy(e);
+    cudaGetLastError();
+    return rc;
+  };
+  auto mark = [&]() -> int {  // `st` continues only after what the inbound stream has been given so far
+    cudaEvent_t e = nullptr;
+    cudaError_t ce = cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
+    if (ce == cudaSuccess) {
+      events.push_back(e);
+      ce = cudaEventRecord(e, d.pipe_in);
+    }
+    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(st, e, 0);
+    return ce == cudaSuccess ? SB200_OK : cuda_fail(ce, "ordering a row block behind its upload");
+  };
+  // the inbound stream must not overtake work that still reads or writes these buffers on `st`
+  {
+    cudaEvent_t e = nullptr;
+    CU_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    events.push_back(e);
+    CU_TRY(cudaEventRecord(e, st));
+    CU_TRY(cudaStreamWaitEvent(d.pipe_in, e, 0));
+  }
+  int rc = SB200_OK;
+  const uint64_t D = dd.ptr;
+  // what lies beyond the operands proper (vectors longer than the product needs) and the old contents of D's vector
+  // travel too, so that every device buffer ends up equal to its host array as after Transfer.to_device; the kernel
+  // overwrites the first M*N elements of D, which therefore need not be sent
+  auto upload_from = [&](const Slot* v, long long first) -> bool {
+    if (!v || !v->host || v->len <= first) return true;
+    return cudaMemcpyAsync(as_ptr<float>(v->ptr) + first, static_cast<const float*>(v->host) + first,
+                           static_cast<size_t>(v->len - first) * 4, cudaMemcpyHostToDevice, d.pipe_in) == cudaSuccess;
+  };
+  if (!upload_from(&a, M * K) || !upload_from(&b, K * N) || !upload_from(c, M * N) || !upload_from(bias, N) ||
+      !upload_from(&dd, c && c->ptr == dd.ptr ? dd.len : M * N))
+    return done(cuda_fail(cudaGetLastError(), "upload of a vector's tail"));
+  if (b.host && K > 0)
+    if (cudaMemcpyAsync(as_ptr<void>(b.ptr), b.host, static_cast<size_t>(K) * N * 4, cudaMemcpyHostToDevice, d.pipe_in) != cudaSuccess)
+      return done(cuda_fail(cudaGetLastError(), "upload of B"));
+  if (bias && bias->host)
+    if (cudaMemcpyAsync(as_ptr<void>(bias->ptr), bias->host, static_cast<size_t>(N) * 4, cudaMemcpyHostToDevice, d.pipe_in) != cudaSuccess)
+      return done(cuda_fail(cudaGetLastError(), "upload of the bias"));
+  if ((rc = mark())) return done(rc);
+  for (long long r0 = 0; r0 < M && !rc; r0 += block_rows) {
+    const long long rows = std::min(block_rows, M - r0);
+    if (a.host && K > 0 &&
+        cudaMemcpyAsync(as_ptr<float>(a.ptr) + r0 * K, static_cast<const float*>(a.host) + r0 * K, static_cast<size_t>(rows) * K * 4,
+                        cudaMemcpyHostToDevice, d.pipe_in) != cudaSuccess)
+      return done(cuda_fail(cudaGetLastError(), "upload of a block of A"));
+    if (c && c->host &&
+        cudaMemcpyAsync(as_ptr<float>(c->ptr) + r0 * N, static_cast<const float*>(c->host) + r0 * N, static_cast<size_t>(rows) * N * 4,
+                        cudaMemcpyHostToDevice, d.pipe_in) != cudaSuccess)
+      return done(cuda_fail(cudaGetLastError(), "upload of a block of C"));
+    if ((rc = mark())) break;
+    rc = run_gemm(d, st, mode, rows, N, K, a.ptr + static_cast<uint64_t>(r0) * K * 4, K, b.ptr, N, D + static_cast<uint64_t>(r0) * N * 4, N,
+                  alpha, c ? c->ptr + static_cast<uint64_t>(r0) * N * 4 : 0, N, beta, bias ? bias->ptr : 0, act);
+    if (!rc && d_host)
+      rc = download_behind(d, st, static_cast<float*>(d_host) + r0 * N, D + static_cast<uint64_t>(r0) * N * 4, static_cast<size_t>(rows) * N * 4);
+  }
+  return done(rc);
 }
 
 }  // namespace
@@ -1511,17 +1641,18 @@ int sb200_kernel_describe(uint64_t kernel, char* buf, int buflen) {
   return SB200_OK;
 }
 
-int sb200_kernel_launch(uint64_t kernel, const sb200_arg* args, int nargs, const uint32_t grid[3], const uint32_t block[3],
-                        uint32_t shared_mem, uint64_t stream) {
-  (void)shared_mem;  // forwarded by the caller even when arrays are static; our kernels size their own
+static int kernel_launch_impl(uint64_t kernel, const sb200_arg* args, int nargs, const void* const* host_ptrs, void* const* host_out,
+                              int32_t* prefetched, const uint32_t grid[3], const uint32_t block[3], uint64_t stream) {
   KernelObj* k = find_kernel(kernel);
   if (!k) return fail(SB200_ERR_INVALID_HANDLE, "unknown kernel handle");
   if ((!args && nargs > 0) || nargs < 0 || !grid || !block) return fail(SB200_ERR_INVALID_VALUE, "null argument list or dims");
   for (int i = 0; i < 3; ++i)
     if (grid[i] == 0 || block[i] == 0) return fail(SB200_ERR_INVALID_VALUE, "grid and block dimensions must be positive");
   std::vector<Slot> slots;
-  int rc = bind_args(k->plan, args, nargs, &slots);
+  int rc = bind_args(k->plan, args, nargs, &slots, host_ptrs, host_out);
   if (rc) return rc;
+  if (prefetched)
+    for (int i = 0; i < nargs; ++i) prefetched[i] = 0;
   DeviceState* d;
   rc = device_ready(k->dev, &d);
   if (rc) return rc;
@@ -1536,9 +1667,79 @@ int sb200_kernel_launch(uint64_t kernel, const sb200_arg* args, int nargs, const
   if (debug_kernel())
     fprintf(stderr, "[sarek-b200] launch %s grid=(%u,%u,%u) block=(%u,%u,%u)\n", k->plan.description.c_str(), grid[0], grid[1],
             grid[2], block[0], block[1], block[2]);
-  if (k->plan.kind == KIND_MAP) return launch_map_kernel(*d, *k, slots, grid, block, as_stream(stream));
-  if (k->plan.kind == KIND_BLOCK_REDUCE) return launch_block_reduce(*d, *k, slots, grid, block, as_stream(stream));
-  return launch_gemm_kernel(*d, k->plan, slots, grid, block, as_stream(stream));
+  cudaStream_t st = as_stream(stream);
+  // launch-from-host: which vectors still have to be brought over, and whether all of them can be copied asynchronously
+  bool any_host = false, all_pinned = true;  // all_pinned: every large host array is page-locked
+  for (const Slot& sl : slots)
+    if (sl.is_vec && sl.host && sl.len > 0) {
+      any_host = true;
+      // small pageable arrays (a bias) go through the driver's own staging and do not stand in the way of the pipeline
+      if (static_cast<size_t>(sl.len) * 4 >= kStagedCopyMinBytes && host_memory_is_pageable(sl.host)) all_pinned = false;
+    }
+  // the result of a matmul follows its kernel back to the host when the caller names a page-locked array for it
+  const bool is_gemm = k->plan.kind != KIND_MAP && k->plan.kind != KIND_BLOCK_REDUCE;
+  void* d_host = nullptr;
+  int d_arg = -1;
+  if (is_gemm && prefetched) {
+    const Slot& out = slots[k->plan.gemm.d];
+    if (out.host_out && out.len > 0 && !host_memory_is_pageable(out.host_out)) {
+      d_host = out.host_out;
+      d_arg = out.arg;
+    }
+  }
+  if (any_host) {
+    if (is_gemm && all_pinned) {
+      bool pipelined = false;
+      rc = launch_gemm_kernel(*d, k->plan, slots, grid, block, st, true, &pipelined, d_host);
+      if (pipelined) {
+        if (!rc && d_host) prefetched[d_arg] = 1;
+        return rc;
+      }
+      if (rc) return rc;
+    }
+    // no pipelining for this launch: whole vectors first (staged when pageable and large), ordered before the kernel
+    CU_TRY(cudaStreamSynchronize(st));
+    for (const Slot& sl : slots) {
+      if (!sl.is_vec || !sl.host || sl.len <= 0) continue;
+      const size_t bytes = static_cast<size_t>(sl.len) * 4;
+      if (staged_copy_enabled() && bytes >= kStagedCopyMinBytes && host_memory_is_pageable(sl.host)) {
+        const int e = staged_copy_to_device(k->dev, as_ptr<void>(sl.ptr), sl.host, bytes, true);
+        if (e) return cuda_fail(static_cast<cudaError_t>(e), "staged copy of a kernel argument");
+      } else {
+        CU_TRY(cudaMemcpy(as_ptr<void>(sl.ptr), sl.host, bytes, cudaMemcpyHostToDevice));
+      }
+    }
+    CU_TRY(cudaStreamSynchronize(0));
+  }
+  if (k->plan.kind == KIND_MAP) return launch_map_kernel(*d, *k, slots, grid, block, st);
+  if (k->plan.kind == KIND_BLOCK_REDUCE) return launch_block_reduce(*d, *k, slots, grid, block, st);
+  rc = launch_gemm_kernel(*d, k->plan, slots, grid, block, st, false, nullptr, d_host);
+  if (!rc && d_host) prefetched[d_arg] = 1;
+  return rc;
+}
+
+int sb200_kernel_launch(uint64_t kernel, const sb200_arg* args, int nargs, const uint32_t grid[3], const uint32_t block[3],
+                        uint32_t shared_mem, uint64_t stream) {
+  (void)shared_mem;  // forwarded by the caller even when arrays are static; our kernels size their own
+  return kernel_launch_impl(kernel, args, nargs, nullptr, nullptr, nullptr, grid, block, stream);
+}
+
+int sb200_kernel_launch_from_host(uint64_t kernel, const sb200_arg* args, int nargs, const void* const* host_ptrs,
+                                  void* const* host_out, int32_t* prefetched, const uint32_t grid[3], const uint32_t block[3],
+                                  uint32_t shared_mem, uint64_t stream) {
+  (void)shared_mem;
+  if (!host_ptrs && nargs > 0) return fail(SB200_ERR_INVALID_VALUE, "null host pointer table");
+  if ((host_out == nullptr) != (prefetched == nullptr))
+    return fail(SB200_ERR_INVALID_VALUE, "host_out and prefetched go together: both tables or neither");
+  return kernel_launch_impl(kernel, args, nargs, host_ptrs, host_out, prefetched, grid, block, stream);
+}
+
+int sb200_prefetch_wait(int dev) {
+  DeviceState* d;
+  int rc = device_ready(dev, &d);
+  if (rc) return rc;
+  if (d->pipe_out) CU_TRY(cudaStreamSynchronize(d->pipe_out));
+  return check_status_word(*d, false);
 }
 
 static int copy_out(const std::string& s, char* out, int outlen) {

@@ -312,12 +312,26 @@ class _Kernel:
         self._push(args, L.ARG_F64, "f64", float(v))
 
     def launch(self, k: "_Kernel.T", *, args: "_Kernel.Args", grid: Dims, block: Dims, shared_mem: int = 0,
-               stream: _Stream.T | None = None) -> None:
+               stream: _Stream.T | None = None, host_arrays: dict | None = None, host_copies: dict | None = None) -> set:
+        """host_arrays maps argument positions (of buffer arguments) to host arrays the buffers are to be filled from
+        first: the launch then goes through sb200_kernel_launch_from_host, which uploads and launches in one call and
+        overlaps the two where it can.  host_copies maps positions to the arrays that hold the vectors' host copies;
+        the positions whose result the library is already sending back there are returned (complete after
+        sb200_prefetch_wait)."""
         n = len(args.items)
         arr = (L.Arg * max(n, 1))(*args.items)
         g = (C.c_uint32 * 3)(grid.x, grid.y, grid.z)
         b = (C.c_uint32 * 3)(block.x, block.y, block.z)
+        if host_arrays or host_copies:
+            host_arrays, host_copies = host_arrays or {}, host_copies or {}
+            hp = (C.c_void_p * max(n, 1))(*[host_arrays[i].ctypes.data if i in host_arrays else None for i in range(n)])
+            ho = (C.c_void_p * max(n, 1))(*[host_copies[i].ctypes.data if i in host_copies else None for i in range(n)])
+            pre = (C.c_int32 * max(n, 1))()
+            _check(L.load().sb200_kernel_launch_from_host(k.handle, arr, n, hp, ho, pre, g, b, shared_mem,
+                                                          stream.handle if stream else 0))
+            return {i for i in range(n) if pre[i]}
         _check(L.load().sb200_kernel_launch(k.handle, arr, n, g, b, shared_mem, stream.handle if stream else 0))
+        return set()
 
 
 # ------------------------------------------------------- run_source args
@@ -325,6 +339,8 @@ class _Kernel:
 class RSA_Buffer:
     buffer: _Memory.Buffer
     length: int
+    host: np.ndarray | None = None   # set when the device buffer has yet to be filled from this host array
+    host_copy: np.ndarray | None = None   # the page-locked array a result may be sent back to behind the kernel
 
 
 @dataclass
@@ -387,16 +403,22 @@ class Backend:
         raise BackendError(L.ERR_UNSUPPORTED, "execute_direct: B200 is a JIT-model backend")
 
     def run_source(self, *, source: str, lang: str, kernel_name: str, block: Dims, grid: Dims, shared_mem: int,
-                   args: Sequence, stream: _Stream.T | None = None) -> None:
-        """sarek-cuda/Cuda_plugin.ml:174-210: compile (cached), bind arguments in order, launch."""
+                   args: Sequence, stream: _Stream.T | None = None) -> set:
+        """sarek-cuda/Cuda_plugin.ml:174-210: compile (cached), bind arguments in order, launch.  Returns the positions
+        of the buffer arguments whose results are on their way back to their host_copy arrays."""
         if lang not in self.supported_source_langs:
             raise BackendError(L.ERR_UNSUPPORTED, f"run_source: source language {lang!r} not supported")
         dev = self.Device.get(self.Device.get_current_device())
         k = self.Kernel.compile_cached(dev, name=kernel_name, source=source)
         ka = self.Kernel.create_args()
+        host_arrays, host_copies = {}, {}
         for i, a in enumerate(args):
             if isinstance(a, RSA_Buffer):
                 self.Kernel.set_arg_buffer(ka, i, a.buffer)
+                if a.host is not None:
+                    host_arrays[i] = a.host
+                if a.host_copy is not None:
+                    host_copies[i] = a.host_copy
             elif isinstance(a, RSA_Int32):
                 self.Kernel.set_arg_int32(ka, i, a.value)
             elif isinstance(a, RSA_Int64):
@@ -407,7 +429,8 @@ class Backend:
                 self.Kernel.set_arg_float64(ka, i, a.value)
             else:
                 raise BackendError(L.ERR_ARGS, f"run_source: unsupported argument {a!r}")
-        self.Kernel.launch(k, args=ka, grid=grid, block=block, shared_mem=shared_mem, stream=stream)
+        return self.Kernel.launch(k, args=ka, grid=grid, block=block, shared_mem=shared_mem, stream=stream,
+                                  host_arrays=host_arrays, host_copies=host_copies)
 
     # -- the direct operators and settings (extras beyond BACKEND) ----------
     def set_mode(self, mode: int) -> None:
@@ -445,6 +468,7 @@ class Vector:
         self.location = Vector.CPU
         self._transfers = 0
         self._pinned = False
+        self._prefetch_dev = None    # device whose outbound stream is bringing the result back to self.host
 
     def _note_transfer(self) -> None:
         """A vector owns its host array for its whole life (as Spoc_core.Vector owns its Bigarray), so the array can be
@@ -480,7 +504,29 @@ class Vector:
             self.backend.Memory.host_to_device(src=self.host, dst=self.buffer)
             self.location = Vector.BOTH
 
+    def pending_upload(self, dev: _Device.T) -> np.ndarray | None:
+        """For run_vectors: makes sure the device buffer exists and, when the host copy is the valid one, hands back the
+        host array for the launch to upload (the launch call then moves it, overlapped with the kernel where possible)
+        instead of copying here; None when the device copy is current."""
+        self._finish_prefetch()      # nothing may still be writing the host array when it is read for an upload
+        if self.buffer is None:
+            self.buffer = self.backend.Memory.alloc(dev, self.length, np.float32)
+        if self.location == Vector.CPU:
+            self._note_transfer()
+            return self.host
+        return None
+
+    def _finish_prefetch(self) -> bool:
+        if self._prefetch_dev is None:
+            return False
+        dev, self._prefetch_dev = self._prefetch_dev, None
+        _check(L.load().sb200_prefetch_wait(dev))
+        return True
+
     def to_array(self) -> np.ndarray:
+        if self._finish_prefetch() and self.location == Vector.STALE_CPU:
+            self._note_transfer()
+            self.location = Vector.BOTH      # the launch that made the host copy stale has already sent the result back
         if self.location == Vector.STALE_CPU:
             self._note_transfer()
             self.backend.Memory.device_to_host(src=self.buffer, dst=self.host)
@@ -493,6 +539,7 @@ class Vector:
         self.location = Vector.CPU
 
     def free(self) -> None:
+        self._finish_prefetch()
         if self._pinned:
             L.load().sb200_host_unregister(self.host.ctypes.data_as(C.c_void_p))
             self._pinned = False
@@ -508,18 +555,29 @@ def run_vectors(backend: Backend, *, device: _Device.T, ir: str, args: Sequence,
     """Sarek.Execute.run_vectors: args are Vector objects or ("int32"|"int64"|
     "float32"|"float64", value) pairs in the kernel's parameter order."""
     rs_args = []
+    uploaded = []
+    prefetch = os.environ.get("SAREK_B200_PREFETCH_RESULTS", "1") != "0"
     for a in args:
         if isinstance(a, Vector):
-            a.to_device(device)
-            rs_args.append(RSA_Buffer(a.buffer, a.length))
+            # Transfer.to_device of the reference, folded into the launch call so that the library can overlap the two
+            host = a.pending_upload(device)
+            if host is not None:
+                uploaded.append(a)
+            # a page-locked host array can take the kernel's result back while later row blocks are still computing
+            rs_args.append(RSA_Buffer(a.buffer, a.length, host, a.host if (a._pinned and prefetch) else None))
             rs_args.append(RSA_Int32(a.length))
         else:
             kind, v = a
             rs_args.append({"int32": RSA_Int32, "int64": RSA_Int64, "float32": RSA_Float32, "float64": RSA_Float64}[kind](v))
     backend.Device.set_current(device)
     source = backend.generate_source(ir, block)
-    backend.run_source(source=source, lang=backend.supported_source_langs[0], kernel_name=kernel_name, block=block,
-                       grid=grid, shared_mem=shared_mem, args=rs_args)
+    coming_back = backend.run_source(source=source, lang=backend.supported_source_langs[0], kernel_name=kernel_name,
+                                     block=block, grid=grid, shared_mem=shared_mem, args=rs_args)
+    for i in coming_back:
+        vec = next(a for a in args if isinstance(a, Vector) and a.buffer is rs_args[i].buffer)
+        vec._prefetch_dev = device.id
+    for a in uploaded:   # the launch call returns when its uploads have completed
+        a.location = Vector.BOTH
     for a in args:  # mark_vectors_stale
         if isinstance(a, Vector) and a.location == Vector.BOTH:
             a.location = Vector.STALE_CPU
