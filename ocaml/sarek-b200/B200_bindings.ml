@@ -71,6 +71,12 @@ let sb200_kernel_destroy = fn "sb200_kernel_destroy" (uint64_t @-> returning int
 let sb200_kernel_launch =
   fn "sb200_kernel_launch"
     (uint64_t @-> ptr sb200_arg @-> int @-> ptr uint32_t @-> ptr uint32_t @-> uint32_t @-> uint64_t @-> returning int)
+(* upload + launch (+ result sent back) in one call; see B200_plugin_base.Deferred *)
+let sb200_kernel_launch_from_host =
+  fn "sb200_kernel_launch_from_host"
+    (uint64_t @-> ptr sb200_arg @-> int @-> ptr (ptr void) @-> ptr (ptr void) @-> ptr int32_t @-> ptr uint32_t
+   @-> ptr uint32_t @-> uint32_t @-> uint64_t @-> returning int)
+let sb200_prefetch_wait = fn "sb200_prefetch_wait" (int @-> returning int)
 let sb200_enable_profiling = fn "sb200_enable_profiling" (int @-> returning int)
 let sb200_set_mode = fn "sb200_set_mode" (int @-> returning int)
 (* fusion on IR text; kind 5 = the backend's guarded fusion of `if tid < n then ..` kernels,

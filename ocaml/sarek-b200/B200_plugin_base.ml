@@ -16,6 +16,49 @@ module B200 = struct
     let n = allocate int 0 in
     Lazy.force B.sb200_device_count n = 0 && !@n > 0
 
+  (* Launch from host (opt-in: SAREK_B200_LAUNCH_FROM_HOST=1).  Execute.run_vectors moves every vector with
+     Transfer.to_device and then launches (sarek/sarek/Execute.ml:520-543); the library can overlap the two when it is
+     given both in one call (sb200_kernel_launch_from_host).  With the switch on, Memory.host_to_device from a Bigarray
+     that is already registered with the driver only records the upload; the next launch that binds the buffer hands
+     the host address to the library, and anything else that touches the buffer (a download, a device copy, a
+     synchronize) carries the recorded upload out first.  The launch also names the registered array of every buffer
+     argument as the place its result may be sent back to; Memory.device_to_host into that same array then only waits.
+     The one observable difference, and the reason for the switch: a Bigarray written behind the vector's back between
+     to_device and the launch is uploaded with its new contents. *)
+  module Deferred = struct
+    let enabled = lazy (Sys.getenv_opt "SAREK_B200_LAUNCH_FROM_HOST" = Some "1")
+
+    type upload = {dev : int; host : unit ptr; bytes : int; keep : Obj.t (* the Bigarray, kept alive *)}
+
+    let key (dptr : Unsigned.UInt64.t) = Unsigned.UInt64.to_int64 dptr
+    let uploads : (int64, Unsigned.UInt64.t * upload) Hashtbl.t = Hashtbl.create 16
+    let host_copy : (int64, unit ptr) Hashtbl.t = Hashtbl.create 16
+
+    (* device buffer -> (device, host address the result goes to, true once it has arrived) *)
+    let results : (int64, int * nativeint * bool) Hashtbl.t = Hashtbl.create 16
+
+    let flush dptr =
+      match Hashtbl.find_opt uploads (key dptr) with
+      | None -> ()
+      | Some (_, u) ->
+          Hashtbl.remove uploads (key dptr) ;
+          B.check "sb200_memcpy_htod"
+            (Lazy.force B.sb200_memcpy_htod u.dev dptr u.host (Unsigned.UInt64.of_int u.bytes))
+
+    let flush_all () = List.iter flush (Hashtbl.fold (fun _ (dptr, _) acc -> dptr :: acc) uploads [])
+
+    let wait_results dev =
+      if Hashtbl.fold (fun _ (d, _, arrived) acc -> acc || (d = dev && not arrived)) results false then begin
+        B.check "sb200_prefetch_wait" (Lazy.force B.sb200_prefetch_wait dev) ;
+        Hashtbl.filter_map_inplace (fun _ (d, h, a) -> Some (d, h, a || d = dev)) results
+      end
+
+    let forget dptr =
+      Hashtbl.remove uploads (key dptr) ;
+      Hashtbl.remove host_copy (key dptr) ;
+      Hashtbl.remove results (key dptr)
+  end
+
   module Device = struct
     type t = {idx : int; dev_name : string; caps : Framework_sig.capabilities}
     type id = int
@@ -65,7 +108,9 @@ module B200 = struct
       current := Some d
 
     let get_current_device () = !current
-    let synchronize d = B.check "sb200_device_synchronize" (Lazy.force B.sb200_device_synchronize d.idx)
+    let synchronize d =
+      Deferred.flush_all () ;
+      B.check "sb200_device_synchronize" (Lazy.force B.sb200_device_synchronize d.idx)
   end
 
   module Stream = struct
@@ -77,7 +122,9 @@ module B200 = struct
       {dev = d.idx; handle = !@h}
 
     let destroy s = B.check "sb200_stream_destroy" (Lazy.force B.sb200_stream_destroy s.dev s.handle)
-    let synchronize s = B.check "sb200_stream_synchronize" (Lazy.force B.sb200_stream_synchronize s.dev s.handle)
+    let synchronize s =
+      Deferred.flush_all () ;
+      B.check "sb200_stream_synchronize" (Lazy.force B.sb200_stream_synchronize s.dev s.handle)
     let default (d : Device.t) = {dev = d.idx; handle = Unsigned.UInt64.zero}
   end
 
@@ -94,7 +141,12 @@ module B200 = struct
     let alloc_zero_copy _ _ _ = None
 
     (* idempotent in the library: a GC finaliser may call it a second time *)
-    let free b = B.check "sb200_mem_free" (Lazy.force B.sb200_mem_free b.dev b.dptr)
+    let free b =
+      (match Hashtbl.find_opt Deferred.results (Deferred.key b.dptr) with
+      | Some (dev, _, false) -> Deferred.wait_results dev
+      | _ -> ()) ;
+      Deferred.forget b.dptr ;
+      B.check "sb200_mem_free" (Lazy.force B.sb200_mem_free b.dev b.dptr)
 
     let host_ptr_to_device ~src_ptr ~byte_size ~dst =
       B.check "sb200_memcpy_htod"
@@ -112,6 +164,7 @@ module B200 = struct
     let pin_threshold = 16 * 1024 * 1024
     let pin_enabled = lazy (Sys.getenv_opt "SAREK_B200_PIN_VECTORS" <> Some "0")
     let seen : (nativeint, int) Hashtbl.t = Hashtbl.create 64
+    let registered : (nativeint, unit) Hashtbl.t = Hashtbl.create 64
 
     let note_transfer (type a b) (ba : (a, b, Bigarray.c_layout) Bigarray.Array1.t) bytes =
       if bytes >= pin_threshold && Lazy.force pin_enabled then begin
@@ -119,26 +172,52 @@ module B200 = struct
         let key = raw_address_of_ptr (to_voidp p) in
         let n = 1 + Option.value ~default:0 (Hashtbl.find_opt seen key) in
         Hashtbl.replace seen key n ;
-        if n = 2 && Lazy.force B.sb200_host_register (to_voidp p) (Unsigned.UInt64.of_int bytes) = 0 then
+        if n = 2 && Lazy.force B.sb200_host_register (to_voidp p) (Unsigned.UInt64.of_int bytes) = 0 then begin
+          Hashtbl.replace registered key () ;
           Gc.finalise
             (fun ba ->
               let p = to_voidp (bigarray_start array1 ba) in
               Hashtbl.remove seen (raw_address_of_ptr p) ;
+              Hashtbl.remove registered (raw_address_of_ptr p) ;
               ignore (Lazy.force B.sb200_host_unregister p))
             ba
+        end
       end
 
     let host_to_device ~src ~dst =
       let bytes = Bigarray.Array1.dim src * Bigarray.kind_size_in_bytes (Bigarray.Array1.kind src) in
       note_transfer src bytes ;
-      host_ptr_to_device ~src_ptr:(to_voidp (bigarray_start array1 src)) ~byte_size:bytes ~dst
+      let p = to_voidp (bigarray_start array1 src) in
+      Hashtbl.remove Deferred.results (Deferred.key dst.dptr) ;
+      if Lazy.force Deferred.enabled && bytes = dst.elems * dst.elem_size && Hashtbl.mem registered (raw_address_of_ptr p) then begin
+        (* recorded, carried out by the next launch that binds dst (or by whatever touches dst first) *)
+        Hashtbl.replace Deferred.uploads (Deferred.key dst.dptr) (dst.dptr, {Deferred.dev = dst.dev; host = p; bytes; keep = Obj.repr src}) ;
+        Hashtbl.replace Deferred.host_copy (Deferred.key dst.dptr) p
+      end
+      else begin
+        Hashtbl.remove Deferred.uploads (Deferred.key dst.dptr) ;
+        host_ptr_to_device ~src_ptr:p ~byte_size:bytes ~dst
+      end
 
     let device_to_host ~src ~dst =
       let bytes = Bigarray.Array1.dim dst * Bigarray.kind_size_in_bytes (Bigarray.Array1.kind dst) in
       note_transfer dst bytes ;
-      device_to_host_ptr ~src ~dst_ptr:(to_voidp (bigarray_start array1 dst)) ~byte_size:bytes
+      let p = to_voidp (bigarray_start array1 dst) in
+      Deferred.flush src.dptr ;
+      (match Hashtbl.find_opt Deferred.results (Deferred.key src.dptr) with
+      | Some (dev, _, false) -> Deferred.wait_results dev
+      | _ -> ()) ;
+      match Hashtbl.find_opt Deferred.results (Deferred.key src.dptr) with
+      | Some (_, host, true) when host = raw_address_of_ptr p && bytes = src.elems * src.elem_size ->
+          ()  (* the launch that wrote src has already sent it back to this very array *)
+      | _ ->
+          if Lazy.force Deferred.enabled && Hashtbl.mem registered (raw_address_of_ptr p) then
+            Hashtbl.replace Deferred.host_copy (Deferred.key src.dptr) p ;
+          device_to_host_ptr ~src ~dst_ptr:p ~byte_size:bytes
 
     let device_to_device ~src ~dst =
+      Deferred.flush src.dptr ;
+      Deferred.forget dst.dptr ;
       let bytes = min (src.elems * src.elem_size) (dst.elems * dst.elem_size) in
       B.check "sb200_memcpy_dtod"
         (Lazy.force B.sb200_memcpy_dtod dst.dev dst.dptr src.dptr (Unsigned.UInt64.of_int bytes))
@@ -249,9 +328,49 @@ module B200 = struct
       in
       let g = dims3 grid and b = dims3 block in
       let st = match stream with Some s -> s.handle | None -> Unsigned.UInt64.zero in
-      B.check "sb200_kernel_launch"
-        (Lazy.force B.sb200_kernel_launch k.handle (CArray.start arr) n (CArray.start g) (CArray.start b)
-           (Unsigned.UInt32.of_int shared_mem) st)
+      let buffers = List.filter_map (function A_buffer p -> Some p | _ -> None) items in
+      let from_host =
+        Lazy.force Deferred.enabled
+        && List.exists (fun p -> Hashtbl.mem Deferred.uploads (Deferred.key p) || Hashtbl.mem Deferred.host_copy (Deferred.key p)) buffers
+      in
+      (* whatever this kernel writes makes host copies that arrived earlier out of date *)
+      List.iter (fun p -> Hashtbl.remove Deferred.results (Deferred.key p)) buffers ;
+      if not from_host then
+        B.check "sb200_kernel_launch"
+          (Lazy.force B.sb200_kernel_launch k.handle (CArray.start arr) n (CArray.start g) (CArray.start b)
+             (Unsigned.UInt32.of_int shared_mem) st)
+      else begin
+        let host_in = CArray.make (ptr void) ~initial:null (max n 1) in
+        let host_out = CArray.make (ptr void) ~initial:null (max n 1) in
+        let coming = CArray.make int32_t ~initial:0l (max n 1) in
+        let kept = ref [] in
+        List.iteri
+          (fun i it ->
+            match it with
+            | A_buffer p ->
+                (match Hashtbl.find_opt Deferred.uploads (Deferred.key p) with
+                | Some (_, u) ->
+                    CArray.set host_in i u.Deferred.host ;
+                    kept := u.Deferred.keep :: !kept ;
+                    Hashtbl.remove Deferred.uploads (Deferred.key p)
+                | None -> ()) ;
+                Option.iter (CArray.set host_out i) (Hashtbl.find_opt Deferred.host_copy (Deferred.key p))
+            | _ -> ())
+          items ;
+        B.check "sb200_kernel_launch_from_host"
+          (Lazy.force B.sb200_kernel_launch_from_host k.handle (CArray.start arr) n (CArray.start host_in)
+             (CArray.start host_out) (CArray.start coming) (CArray.start g) (CArray.start b)
+             (Unsigned.UInt32.of_int shared_mem) st) ;
+        ignore (Sys.opaque_identity !kept) ;  (* the Bigarrays outlive the call, which returns after its uploads *)
+        List.iteri
+          (fun i it ->
+            match it with
+            | A_buffer p when CArray.get coming i <> 0l ->
+                Hashtbl.replace Deferred.results (Deferred.key p)
+                  (k.dev, raw_address_of_ptr (CArray.get host_out i), false)
+            | _ -> ())
+          items
+      end
   end
 
   let enable_profiling () = ignore (Lazy.force B.sb200_enable_profiling 1)

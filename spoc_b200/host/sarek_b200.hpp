@@ -55,7 +55,9 @@ inline Dims dims1d(uint32_t x) { return {x, 1, 1}; }
 inline Dims dims2d(uint32_t x, uint32_t y) { return {x, y, 1}; }
 
 // Framework_sig.run_source_arg
-struct RSA_Buffer { uint64_t device_ptr; int length; };
+// host: the array the device buffer has yet to be filled from (null: the device copy is current); host_copy: the
+// page-locked array a result may be sent back to behind its kernel (null: leave it on the device)
+struct RSA_Buffer { uint64_t device_ptr; int length; const void* host = nullptr; void* host_copy = nullptr; };
 struct RSA_Int32 { int32_t v; };
 struct RSA_Int64 { int64_t v; };
 struct RSA_Float32 { float v; };
@@ -215,6 +217,18 @@ class Backend {
       const uint32_t g[3] = {grid.x, grid.y, grid.z}, bl[3] = {block.x, block.y, block.z};
       check(sb200_kernel_launch(k.handle, a.items.data(), static_cast<int>(a.items.size()), g, bl, shared_mem, stream));
     }
+    // The launch that also uploads (host[i] non-null: fill argument i's buffer from there first) and, for page-locked
+    // host_copy entries of vectors a matmul writes, sends the result back behind the kernel; returns one flag per argument.
+    std::vector<int32_t> launch_from_host(const KernelT& k, const Args& a, const std::vector<const void*>& host,
+                                          const std::vector<void*>& host_copy, Dims grid, Dims block, uint32_t shared_mem,
+                                          uint64_t stream = 0) const {
+      const uint32_t g[3] = {grid.x, grid.y, grid.z}, bl[3] = {block.x, block.y, block.z};
+      std::vector<int32_t> coming(a.items.size() + 1, 0);
+      check(sb200_kernel_launch_from_host(k.handle, a.items.data(), static_cast<int>(a.items.size()), host.data(), host_copy.data(),
+                                          coming.data(), g, bl, shared_mem, stream));
+      coming.resize(a.items.size());
+      return coming;
+    }
   };
 
   Backend() : Device{this}, Event{this}, Kernel{this} {}
@@ -238,22 +252,33 @@ class Backend {
   void disable_profiling() const { check(sb200_enable_profiling(0)); }
   void set_mode(int mode) const { check(sb200_set_mode(mode)); }
 
-  void run_source(const std::string& source, const std::string& lang, const std::string& kernel_name, Dims block, Dims grid,
-                  uint32_t shared_mem, const std::vector<RunSourceArg>& args) {
+  // Returns, per argument, whether its result is already on its way back to its host_copy array.
+  std::vector<int32_t> run_source(const std::string& source, const std::string& lang, const std::string& kernel_name, Dims block,
+                                  Dims grid, uint32_t shared_mem, const std::vector<RunSourceArg>& args) {
     if (lang != source_lang) throw BackendError(SB200_ERR_UNSUPPORTED, "run_source: source language " + lang + " not supported");
     const DeviceT& dev = Device.get(Device.get_current_device());
     KernelT k = Kernel.compile_cached(dev, kernel_name, source);
     Args ka = Kernel.create_args();
     int i = 0;
+    std::vector<const void*> host(args.size() + 1, nullptr);
+    std::vector<void*> host_copy(args.size() + 1, nullptr);
+    bool from_host = false;
     for (const RunSourceArg& a : args) {
-      if (auto* p = std::get_if<RSA_Buffer>(&a)) Kernel.set_arg_ptr(ka, i, p->device_ptr);
+      if (auto* p = std::get_if<RSA_Buffer>(&a)) {
+        Kernel.set_arg_ptr(ka, i, p->device_ptr);
+        host[i] = p->host;
+        host_copy[i] = p->host_copy;
+        from_host = from_host || p->host || p->host_copy;
+      }
       else if (auto* q = std::get_if<RSA_Int32>(&a)) Kernel.set_arg_int32(ka, i, q->v);
       else if (auto* r = std::get_if<RSA_Int64>(&a)) Kernel.set_arg_int64(ka, i, r->v);
       else if (auto* s = std::get_if<RSA_Float32>(&a)) Kernel.set_arg_float32(ka, i, s->v);
       else Kernel.set_arg_float64(ka, i, std::get<RSA_Float64>(a).v);
       ++i;
     }
+    if (from_host) return Kernel.launch_from_host(k, ka, host, host_copy, grid, block, shared_mem);
     Kernel.launch(k, ka, grid, block, shared_mem);
+    return std::vector<int32_t>(args.size(), 0);
   }
 
  private:
@@ -269,6 +294,8 @@ class Vector {
   Vector(Backend& b, size_t n) : backend_(&b), host_(n, 0.0f) {}
   Vector(Backend& b, std::vector<float> data) : backend_(&b), host_(std::move(data)) {}
   ~Vector() {
+    if (prefetch_dev_ >= 0) sb200_prefetch_wait(prefetch_dev_);  // no exception leaves a destructor
+    prefetch_dev_ = -1;
     free_buffer();
     if (pinned_) sb200_host_unregister(host_.data());
   }
@@ -285,7 +312,25 @@ class Vector {
       loc_ = Both;
     }
   }
+  // For run_vectors: the device buffer exists afterwards; returns the host array when the launch has to upload it
+  // (the launch call moves it, overlapped with the kernel where it can), null when the device copy is current.
+  const float* pending_upload(const Backend::DeviceT& dev) {
+    finish_prefetch();  // nothing may still be writing the host array when it is read for an upload
+    if (!buf_.ptr) buf_ = backend_->Memory.alloc(dev, host_.size());
+    if (loc_ != CPU) return nullptr;
+    note_transfer();
+    return host_.data();
+  }
+  void uploaded() {
+    if (loc_ == CPU) loc_ = Both;
+  }
+  float* pinned_host() { return pinned_ ? host_.data() : nullptr; }
+  void result_coming_back(int dev) { prefetch_dev_ = dev; }
   const std::vector<float>& to_array() {
+    if (finish_prefetch() && loc_ == Stale_CPU) {  // the launch that made the host copy stale has already sent the result back
+      note_transfer();
+      loc_ = Both;
+    }
     if (loc_ == Stale_CPU) {
       note_transfer();
       backend_->Memory.device_to_host_ptr(buf_, host_.data(), host_.size() * sizeof(float));
@@ -303,6 +348,7 @@ class Vector {
     if (loc_ == Both) loc_ = Stale_CPU;
   }
   void free_buffer() {
+    finish_prefetch();
     if (buf_.ptr) {
       sb200_mem_free(buf_.dev, buf_.ptr);
       buf_ = {};
@@ -312,6 +358,13 @@ class Vector {
   const Backend::Buffer& buffer() const { return buf_; }
 
  private:
+  bool finish_prefetch() {
+    if (prefetch_dev_ < 0) return false;
+    const int dev = prefetch_dev_;
+    prefetch_dev_ = -1;
+    check(sb200_prefetch_wait(dev));
+    return true;
+  }
   // The vector owns its host array for its whole life, so the array can be pinned in place: a vector of 16 MiB or
   // more that is moved a second time is registered with the driver, and this and every later transfer run at the
   // pinned rate; the destructor unregisters.
@@ -325,6 +378,7 @@ class Vector {
   Location loc_ = CPU;
   int transfers_ = 0;
   bool pinned_ = false;
+  int prefetch_dev_ = -1;  // device whose outbound stream is bringing the result back to host_
 };
 
 struct ScalarArg {
@@ -343,8 +397,9 @@ inline void run_vectors(Backend& backend, const Backend::DeviceT& device, const 
   std::vector<RunSourceArg> rs;
   for (const ExecArg& a : args) {
     if (auto* v = std::get_if<Vector*>(&a)) {
-      (*v)->to_device(device);
-      rs.push_back(RSA_Buffer{(*v)->buffer().ptr, static_cast<int>((*v)->length())});
+      // Transfer.to_device of the reference, folded into the launch call so that the library can overlap the two
+      const float* host = (*v)->pending_upload(device);
+      rs.push_back(RSA_Buffer{(*v)->buffer().ptr, static_cast<int>((*v)->length()), host, (*v)->pinned_host()});
       rs.push_back(RSA_Int32{static_cast<int32_t>((*v)->length())});
     } else {
       const ScalarArg& s = std::get<ScalarArg>(a);
@@ -357,9 +412,19 @@ inline void run_vectors(Backend& backend, const Backend::DeviceT& device, const 
     }
   }
   backend.Device.set_current(device);
-  backend.run_source(backend.generate_source(ir), Backend::source_lang, kernel_name, block, grid, shared_mem, rs);
-  for (const ExecArg& a : args)
-    if (auto* v = std::get_if<Vector*>(&a)) (*v)->mark_stale();
+  const std::vector<int32_t> coming =
+      backend.run_source(backend.generate_source(ir), Backend::source_lang, kernel_name, block, grid, shared_mem, rs);
+  size_t pos = 0;  // position in rs: a vector takes two places (buffer, length), a scalar one
+  for (const ExecArg& a : args) {
+    if (auto* v = std::get_if<Vector*>(&a)) {
+      (*v)->uploaded();  // the launch call returns when its uploads have completed
+      if (coming[pos]) (*v)->result_coming_back(device.id);
+      (*v)->mark_stale();
+      pos += 2;
+    } else {
+      pos += 1;
+    }
+  }
 }
 
 // ---- Sarek_fusion over IR text ---------------------------------------------
