@@ -406,6 +406,20 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
                      "peak": f16_peak, "unit": "TFLOP/s", "frac": flops_step / (main_q * 1e-3) / 1e12 / f16_peak,
                      "peak_source": f16_split_mode["roofline"]["peak_source"], "kernel_ms": main_q,
                      "prep_ms": prof_q["prep_ms"] / max(prof_q["calls"], 1)}}
+    # ---- the mixed mode: 3xTF32's three terms with the two cross terms on the fp16 pipe ---------------------------
+    ms_x, _, prof_x = timed(lambda: gemm(L.MODE_3XMIXED), s5, 3, profile=True)
+    main_x = prof_x["main_ms"] / max(prof_x["calls"], 1)
+    mixed_mode = {
+        "value": world * flops_step / (ms_x / s5 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_x / s5,
+        "note": "SB200_MODE_3XMIXED: hi*hi as TF32 MMAs on the caller's fp32 matrices, hi*lo + lo*hi as fp16 MMAs on panels "
+                "with one power-of-two scale per matrix, the accumulated cross terms rescaled inside the tensor core "
+                "(scale-input-d); the error of 3xTF32 for elements within 2^29 of their matrix's largest "
+                "(tests/test_gpu_gemm_mixed.py); kernel_ms covers the mixed kernel and the two gated 3xTF32 launches behind it",
+        "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel<5, true>", "achieved": flops_step / (main_x * 1e-3) / 1e12,
+                     "peak": tf32_peak, "unit": "TFLOP/s", "frac": flops_step / (main_x * 1e-3) / 1e12 / tf32_peak,
+                     "mma_frac": 2.0 * flops_step / (main_x * 1e-3) / 1e12 / tf32_peak,
+                     "peak_source": roofline["peak_source"], "kernel_ms": main_x,
+                     "prep_ms": prof_x["prep_ms"] / max(prof_x["calls"], 1)}}
     clocks = None
     if rank == 0:
         sampler.stop()
@@ -714,7 +728,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "config": make_config(args),
             "arm": {"mode": "3xTF32 split accumulation on tcgen05 tensor cores", "preload_s": args.preload_s},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-            "burst": burst, "tf32_mode": tf32_mode, "f16_split_mode": f16_split_mode, "f16_single_mode": f16_single_mode, "fused_map": fused_map, "b_broadcast_ms": bcast_ms,
+            "burst": burst, "tf32_mode": tf32_mode, "f16_split_mode": f16_split_mode, "f16_single_mode": f16_single_mode, "mixed_mode": mixed_mode, "fused_map": fused_map, "b_broadcast_ms": bcast_ms,
             "reductions": reductions, "stream_triad_1e6": small_triad, "config_1024cubed": cfg1, "tf32_yardstick": tf32_yardstick,
             "skinny_65536x4096x4096": skinny, f"gather_{args.gather_size}cubed": gather,
         }
@@ -815,8 +829,8 @@ def run_case(args) -> None:
         return run_transfer_case(lib, dev, S)
     if args.case == "tiles":
         return run_tiles_case(lib, dev)
-    if args.case in ("gemm3", "gemm1", "gemm4"):
-        mode = {"gemm3": L.MODE_3XTF32, "gemm1": L.MODE_TF32, "gemm4": L.MODE_3XF16}[args.case]
+    if args.case in ("gemm3", "gemm1", "gemm4", "gemm5"):
+        mode = {"gemm3": L.MODE_3XTF32, "gemm1": L.MODE_TF32, "gemm4": L.MODE_3XF16, "gemm5": L.MODE_3XMIXED}[args.case]
         bufs = [torch.empty(S * S, dtype=torch.float32, device=tdev) for _ in range(4)]
         bias = torch.empty(S, dtype=torch.float32, device=tdev)
         for i, t in enumerate(bufs[:3]):
@@ -1134,7 +1148,7 @@ def main() -> None:
     ap.add_argument("--workload", default="gemm8192", choices=["gemm8192", "gather", "skinny"],
                     help="gemm8192: the headline run; gather: large square GEMM with the result gathered on every GPU; "
                          "skinny: 65536x4096x4096 GEMM, rows split over the ranks, B broadcast")
-    ap.add_argument("--case", default=None, choices=["gemm3", "gemm1", "gemm4", "map", "transfer", "tiles"],
+    ap.add_argument("--case", default=None, choices=["gemm3", "gemm1", "gemm4", "gemm5", "map", "transfer", "tiles"],
                     help="profiler-sized single-operator run (square size --size; map uses size^2 elements)")
     ap.add_argument("--size", type=int, default=4096)
     ap.add_argument("--gpus", type=int, default=1)

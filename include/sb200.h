@@ -55,6 +55,19 @@ extern "C" {
                                TF32 mode (same error bound) at the fp16 tensor-core rate, with the same per-row and
                                per-column power-of-two scaling; faster than TF32 mode where the tensor work outweighs the conversion pass
                                (from about 4096^3).  Every GEMM entry point except sb200_gemm_f32_noalloc. */
+#define SB200_MODE_3XMIXED 5 /* the three-term split of 3xTF32 mode with its two cross terms, hi*lo + lo*hi, on the
+                               fp16 pipe: they are 2^-11 of the main term and need 11-bit factors only, which fp16 holds
+                               at twice TF32's tensor-core rate.  The main term hi*hi stays a TF32 MMA on the caller's
+                               fp32 matrices, so magnitudes are unrestricted where it matters; the fp16 panels of the
+                               cross terms carry ONE power-of-two scale per matrix (from its largest magnitude), and
+                               the accumulated cross terms are brought back to true units exactly, inside the tensor
+                               core (scale-input-d), before the main term is added.  Same error as 3xTF32 for every
+                               element within 2^29 of its matrix's largest; an element further down loses bits of its
+                               cross terms, in the worst case keeping TF32's 2^-11.  Operands it cannot take (product
+                               of the two largest magnitudes above 2^39 or below 2^-58, a NaN or an infinity) are
+                               found on the device and computed by the plain 3xTF32 kernels in the same call; small
+                               products (below 2^34 multiply-adds, see sb200_set_mixed_min_macs) and operands TMA cannot address use
+                               3xTF32 outright.  Every GEMM entry point except sb200_gemm_f32_noalloc takes it. */
 
 /* ---- epilogue activation ------------------------------------------------ */
 #define SB200_ACT_NONE 0
@@ -394,6 +407,9 @@ SB200_API int sb200_set_gemm_variant(int variant);
 /* tile columns of the CTA-pair kernel: 0 = automatic (256, or 128 / 64 for problems with too few 256-column
  * tiles to occupy the SMs), else 64, 128 or 256.  Also SAREK_B200_TILE_N.  Results do not depend on it. */
 SB200_API int sb200_set_gemm_tile_n(int tile_n);
+/* SB200_MODE_3XMIXED hands products of fewer than this many multiply-adds (M*N*K) to 3xTF32, whose two launches cost
+ * less than the mixed mode's seven on small problems; 0 restores the default (2^34).  A tuning and test knob. */
+SB200_API int sb200_set_mixed_min_macs(int64_t macs);
 
 /* L2 eviction policies the GEMM kernels attach to their memory instructions (a per-instruction cache hint;
  * no device setting is touched): three 2-bit fields, each 0 = normal, 1 = evict first, 2 = evict last —

@@ -17,7 +17,7 @@ OK = 0
 ERR_INVALID_VALUE, ERR_INVALID_HANDLE, ERR_UNSUPPORTED, ERR_PARSE, ERR_ARGS = -1, -2, -3, -4, -5
 ERR_BOUNDS, ERR_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE, ERR_ALIGNMENT, ERR_COMM = -6, -7, -8, -9, -10, -11
 SHARD_GATHER_FUSED, SHARD_GATHER_NCCL, SHARD_B_RESIDENT = 1, 2, 4
-MODE_3XTF32, MODE_TF32, MODE_3XF16, MODE_F16 = 3, 1, 4, 2
+MODE_3XTF32, MODE_TF32, MODE_3XF16, MODE_F16, MODE_3XMIXED = 3, 1, 4, 2, 5
 ACT_NONE, ACT_RELU = 0, 1
 KIND_MAP, KIND_GEMM_NAIVE, KIND_GEMM_TILED, KIND_BLOCK_REDUCE = 1, 2, 3, 4
 ARG_BUFFER, ARG_I32, ARG_I64, ARG_F32, ARG_F64 = 0, 1, 2, 3, 4
@@ -113,6 +113,7 @@ SIGNATURES = {
     "sb200_get_mode": ([p(i32)], i32),
     "sb200_set_gemm_variant": ([i32], i32),
     "sb200_set_gemm_tile_n": ([i32], i32),
+    "sb200_set_mixed_min_macs": ([i64], i32),
     "sb200_set_l2_policy": ([i32], i32),
     "sb200_gemm_describe": ([i32, i64, i64, i64, i32, i32, C.c_char_p, i32], i32),
     "sb200_fill_f32": ([i32, u64, u64, i64, u64, u64, i32, f64, i64], i32),

@@ -82,6 +82,22 @@ struct GemmParams {
   // each accumulator by both (exact: powers of two) before anything else.  Null in the TF32 modes.
   const float* row_scale;
   const float* col_scale;
+  // A kernel with a gate runs only when *gate == gate_value (a word an earlier kernel of the stream wrote): the
+  // mixed mode launches its own kernel and, behind it, the plain 3xTF32 pair for operands it cannot take; exactly one
+  // of the two does the work.  Null: always run.
+  const int* gate;
+  int gate_value;
+  // Mixed mode: the control words its preparation wrote (MixCtl below).
+  const int* mix_ctl;
+};
+
+// Control words of the mixed mode, in device memory: the preparation kernels fill them, the GEMM reads them.
+struct MixCtl {
+  unsigned int max_a, max_b;  // largest magnitudes of A and B as float bits (atomicMax; zero before)
+  int ok;                     // 1: the mixed kernel runs; 0: the plain 3xTF32 kernels behind it run instead
+  int rescale_stages;         // stages of zero tiles between the cross terms and the main term, each scaling by 2^-15
+  int first_scale;            // the first main-term MMA scales the accumulated cross terms by 2^-first_scale (0..15)
+  int shift_a, shift_b;       // the fp16 panels hold A * 2^shift_a and B * 2^shift_b (low parts 2^11 times that)
 };
 
 __device__ __forceinline__ void store_replicas(const GemmParams& p, long long offset, float x) {
@@ -494,8 +510,10 @@ __device__ __forceinline__ void prep_lo_rows(const PrepLoJob& j, long long block
   }
 }
 
-__global__ void prep_lo_two_kernel(const PrepLoJob a, const PrepLoJob b, int blocks_a) {
+// gate: when not null the kernel works only if *gate == 0 (the mixed mode declined the operands).
+__global__ void prep_lo_two_kernel(const PrepLoJob a, const PrepLoJob b, int blocks_a, const int* gate = nullptr) {
   grid_launch_dependents();  // the GEMM behind this launch may set itself up now; it waits before reading
+  if (gate && *gate != 0) return;
   if (static_cast<int>(blockIdx.x) < blocks_a)
     prep_lo_rows(a, blockIdx.x, blocks_a);
   else
@@ -686,6 +704,182 @@ __global__ void prep_b_f16_kernel(const float* __restrict__ B, long long ldb, __
         const long long off = static_cast<long long>(n) * Kp + k0 + 2 * threadIdx.x;
         *reinterpret_cast<__half2*>(hi + off) = __halves2half2(h0, h1);
         if (lo) *reinterpret_cast<__half2*>(lo + off) = __halves2half2(l0, l1);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------------
+// Operand preparation for the mixed mode (SB200_MODE_3XMIXED)
+// ------------------------------------------------------------------------
+// The three-term split  a*b ~ hi(a)*hi(b) + hi(a)*lo(b) + lo(a)*hi(b)  with hi = rn_tf32, lo = x - hi, as in 3xTF32 mode,
+// but only the main term runs on the TF32 pipe (from the caller's fp32 matrices, any magnitudes).  The two cross
+// terms are 2^-11 of the main term, need 11-bit factors only, and run on the fp16 pipe at twice the rate: panels
+//   hi16 = f16(hi * 2^sa),  lo16 = f16(lo * 2^(sa+11))        (hi has 11 significant bits: exact when normal)
+// with ONE power of two per matrix, chosen from its largest magnitude so that the panels peak in [2^14, 2^15) when
+// that is possible.  The cross terms are accumulated first, in units of 2^-(sa+sb+11); the accumulator is then scaled by
+// that power of two exactly — tcgen05.mma's scale-input-d, at most 2^-15 per instruction: `rescale_stages` MMAs on
+// zero tiles and the first MMA of the main term — and the main term is accumulated on top in true units.
+// An element more than 2^29 below its matrix's largest loses bits of its cross terms to fp16's subnormal spacing;
+// in the worst case (flushed to zero) its products keep TF32 accuracy, 2^-11 relative.  Every other product carries
+// the error of 3xTF32 mode.  Magnitudes for which no such scaling exists (product of the two maxima above 2^39 or
+// below 2^-60, non-finite values) clear `ok`, and the plain 3xTF32 kernels that follow do the work.
+__device__ __forceinline__ MixCtl mix_plan(unsigned int max_a, unsigned int max_b) {
+  MixCtl c;
+  c.max_a = max_a;
+  c.max_b = max_b;
+  c.ok = 0;
+  c.rescale_stages = 0;
+  c.first_scale = 0;
+  c.shift_a = c.shift_b = 0;
+  const int ea = static_cast<int>(max_a >> 23), eb = static_cast<int>(max_b >> 23);
+  if (ea == 255 || eb == 255) return c;  // an infinity or a NaN somewhere
+  if (max_a == 0 || max_b == 0) {        // a zero matrix: the cross terms vanish whatever the scales
+    c.ok = 1;
+    return c;
+  }
+  // largest magnitudes lie in [2^alpha, 2^(alpha+1)); subnormal maxima count as exponent -126
+  const int alpha = (ea == 0 ? 1 : ea) - 127, beta = (eb == 0 ? 1 : eb) - 127;
+  // panels peak below 2^ta and 2^tb; the total rescaling is T = 11 + shift_a + shift_b = 9 + ta + tb - alpha - beta
+  int T = 39 - alpha - beta;              // ta = tb = 15
+  if (T < 0) return c;                    // magnitudes too large for fp16 panels even unscaled
+  if (T > 75) T = 75;                     // at most four rescale stages; smaller panels' peaks instead
+  const int tsum = T - 9 + alpha + beta;  // ta + tb
+  if (tsum < 8) return c;                 // less than 2^18 of range per matrix: not worth it
+  const int ta = tsum - tsum / 2, tb = tsum / 2;
+  c.shift_a = ta - alpha - 1;
+  c.shift_b = tb - beta - 1;
+  if (c.shift_a + 11 > 126 || c.shift_b + 11 > 126 || c.shift_a < -126 || c.shift_b < -126) return c;
+  c.rescale_stages = T > 15 ? (T - 1) / 15 : 0;
+  c.first_scale = T - 15 * c.rescale_stages;
+  c.ok = 1;
+  return c;
+}
+
+__device__ __forceinline__ float pow2f(int e) { return __uint_as_float(static_cast<unsigned int>(e + 127) << 23); }
+
+__device__ __forceinline__ void mix_split(float x, float s_hi, float s_lo, __half& hi, __half& lo) {
+  const float h = tf32_round(x);
+  hi = __float2half_rn(h * s_hi);
+  lo = __float2half_rn((x - h) * s_lo);
+}
+
+struct AbsMaxJob {
+  const float* src;
+  long long ld;
+  int rows, cols, vec_ok;
+};
+
+__device__ __forceinline__ void absmax_rows(const AbsMaxJob& j, unsigned int block, unsigned int blocks, unsigned int* out) {
+  const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  unsigned int m = 0;
+  for (long long row = static_cast<long long>(block) * warps + (threadIdx.x >> 5); row < j.rows;
+       row += static_cast<long long>(blocks) * warps) {
+    const float* src = j.src + row * j.ld;
+    if (j.vec_ok) {
+      const float4* v = reinterpret_cast<const float4*>(src);
+      const int nq = j.cols >> 2;
+      int q = lane;
+      for (; q + 96 < nq; q += 128) {
+        const float4 x0 = v[q], x1 = v[q + 32], x2 = v[q + 64], x3 = v[q + 96];
+        m = max(max(m, abs_bits(x0.x)), max(abs_bits(x0.y), max(abs_bits(x0.z), abs_bits(x0.w))));
+        m = max(max(m, abs_bits(x1.x)), max(abs_bits(x1.y), max(abs_bits(x1.z), abs_bits(x1.w))));
+        m = max(max(m, abs_bits(x2.x)), max(abs_bits(x2.y), max(abs_bits(x2.z), abs_bits(x2.w))));
+        m = max(max(m, abs_bits(x3.x)), max(abs_bits(x3.y), max(abs_bits(x3.z), abs_bits(x3.w))));
+      }
+      for (; q < nq; q += 32) {
+        const float4 x = v[q];
+        m = max(max(m, abs_bits(x.x)), max(abs_bits(x.y), max(abs_bits(x.z), abs_bits(x.w))));
+      }
+      for (int k = (j.cols & ~3) + lane; k < j.cols; k += 32) m = max(m, abs_bits(src[k]));
+    } else {
+      for (int k = lane; k < j.cols; k += 32) m = max(m, abs_bits(src[k]));
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0 && m) atomicMax(out, m);
+}
+
+// Largest magnitudes of A and of B into ctl->max_a and ctl->max_b (zero before the launch).
+__global__ void absmax_two_kernel(const AbsMaxJob a, const AbsMaxJob b, int blocks_a, MixCtl* ctl) {
+  if (static_cast<int>(blockIdx.x) < blocks_a)
+    absmax_rows(a, blockIdx.x, blocks_a, &ctl->max_a);
+  else
+    absmax_rows(b, blockIdx.x - blocks_a, gridDim.x - blocks_a, &ctl->max_b);
+}
+
+// A[M x K] -> hi16, lo16 [M x Kp] halves, Kp = K rounded up to 64, padding zero; 8 elements per thread and step.
+// Block 0 also publishes the plan (ok, rescale stages, scales) for the kernels behind it.
+__global__ void prep_mix_a_kernel(const float* __restrict__ A, long long lda, __half* __restrict__ hi, __half* __restrict__ lo,
+                                  int M, int K, int Kp, int vec_ok, MixCtl* ctl) {
+  const MixCtl plan = mix_plan(ctl->max_a, ctl->max_b);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    ctl->ok = plan.ok;
+    ctl->rescale_stages = plan.rescale_stages;
+    ctl->first_scale = plan.first_scale;
+    ctl->shift_a = plan.shift_a;
+    ctl->shift_b = plan.shift_b;
+  }
+  if (!plan.ok) return;
+  const float s_hi = pow2f(plan.shift_a), s_lo = pow2f(plan.shift_a + 11);
+  const long long octs_per_row = Kp >> 3;
+  const long long total = static_cast<long long>(M) * octs_per_row;
+  for (long long q = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; q < total;
+       q += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = q / octs_per_row;
+    const int k = static_cast<int>(q - row * octs_per_row) << 3;
+    const float* src = A + row * lda + k;
+    float x[8];
+    if (vec_ok && k + 7 < K) {
+      const float4 u = *reinterpret_cast<const float4*>(src), w = *reinterpret_cast<const float4*>(src + 4);
+      x[0] = u.x; x[1] = u.y; x[2] = u.z; x[3] = u.w;
+      x[4] = w.x; x[5] = w.y; x[6] = w.z; x[7] = w.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = (k + j < K) ? src[j] : 0.0f;
+    }
+    __align__(16) __half h[8];
+    __align__(16) __half l[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mix_split(x[j], s_hi, s_lo, h[j], l[j]);
+    *reinterpret_cast<uint4*>(hi + row * Kp + k) = *reinterpret_cast<const uint4*>(h);
+    *reinterpret_cast<uint4*>(lo + row * Kp + k) = *reinterpret_cast<const uint4*>(l);
+  }
+}
+
+// B[K x N] -> hi16, lo16 [N x Kp] halves, transposed through shared memory in tiles of 64 k x 32 n as in
+// prep_b_f16_kernel; block (32, 8).
+__global__ void prep_mix_b_kernel(const float* __restrict__ B, long long ldb, __half* __restrict__ hi, __half* __restrict__ lo,
+                                  int K, int N, int Kp, const MixCtl* ctl) {
+  grid_launch_dependents();  // the GEMM behind this launch may set itself up now; it waits before reading
+  const MixCtl plan = mix_plan(ctl->max_a, ctl->max_b);
+  if (!plan.ok) return;
+  const float s_hi = pow2f(plan.shift_b), s_lo = pow2f(plan.shift_b + 11);
+  __shared__ float tile[64][33];
+  const long long k_tiles = Kp >> 6;
+  const long long n_tiles = (N + 31) >> 5;
+  const long long total = k_tiles * n_tiles;
+  for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+    const long long kt = t / n_tiles;
+    const int n0 = static_cast<int>(t - kt * n_tiles) << 5;
+    const int k0 = static_cast<int>(kt) << 6;
+#pragma unroll
+    for (int j = 0; j < 64; j += 8) {
+      const int k = k0 + threadIdx.y + j, n = n0 + threadIdx.x;
+      tile[threadIdx.y + j][threadIdx.x] = (k < K && n < N) ? B[static_cast<long long>(k) * ldb + n] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      const int nl = threadIdx.y + j, n = n0 + nl;
+      if (n < N) {
+        __half h0, l0, h1, l1;
+        mix_split(tile[2 * threadIdx.x][nl], s_hi, s_lo, h0, l0);
+        mix_split(tile[2 * threadIdx.x + 1][nl], s_hi, s_lo, h1, l1);
+        const long long off = static_cast<long long>(n) * Kp + k0 + 2 * threadIdx.x;
+        *reinterpret_cast<__half2*>(hi + off) = __halves2half2(h0, h1);
+        *reinterpret_cast<__half2*>(lo + off) = __halves2half2(l0, l1);
       }
     }
     __syncthreads();

@@ -33,7 +33,7 @@ constexpr uint32_t PAIR_A_BYTES = 128 * GEMM_BK * 4;  // this block's A rows: 16
 template <int MODE, int BN = PAIR_BN>
 struct PairCfg {
   static_assert(BN == 256 || BN == 128 || BN == 64, "tile columns");
-  static constexpr int kOperands = (MODE == 3 || MODE == 4) ? 2 : 1;  // high parts (+ low parts)
+  static constexpr int kOperands = (MODE == 3 || MODE == 4 || MODE == 5) ? 2 : 1;  // high parts (+ low parts)
   static constexpr uint32_t kBBytes = (BN / 2) * GEMM_BK * 4;  // this block's half of B: 16, 8 or 4 KiB (rows of 128 bytes)
   static constexpr uint32_t kStageBytes = kOperands * (PAIR_A_BYTES + kBBytes);
   static constexpr int kStagesFit = (192 * 1024) / kStageBytes;
@@ -56,12 +56,23 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
 // (swizzle 128B with 32-byte atoms) and consumed through an MN-major descriptor.  TF32 mode then needs
 // no panels at all; 3xTF32 mode needs only the low parts: map_a_lo over an [M x Kp] panel, map_b_lo
 // over a row-major [K x Np] panel read as slabs like B itself.
+//
+// MODE 5 (mixed; always DIRECT): map_a_hi / map_b_hi are those TFLOAT32 maps over the caller's matrices, map_a_lo /
+// map_b_lo lie over the fp16 panels of the high parts and map_a_x / map_b_x over those of the low parts (all K-major,
+// [rows x Kp], Kp a multiple of 64).  A tile is computed in three runs of stages, every stage the same 4 x 16 KiB:
+// K/64 cross stages (the four fp16 tiles of 64 k: lo*hi + hi*lo, eight fp16 MMAs), then the rescale stages (tiles from
+// beyond the end of K, which TMA fills with zeros: one MMA each whose only effect is the scaling of the
+// accumulator by 2^-15), then K/64 main stages (A and B of two consecutive k-blocks of 32 where the other modes keep
+// high and low parts: eight TF32 MMAs, the first of which scales the accumulator by 2^-first_scale).
 template <int MODE, bool DIRECT = false, int BN = PAIR_BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_b_hi,
                  const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
+                 const __grid_constant__ CUtensorMap map_a_x, const __grid_constant__ CUtensorMap map_b_x,
                  const GemmParams p) {
   using Cfg = PairCfg<MODE, BN>;
+  constexpr bool MIXED = MODE == 5;
+  static_assert(!MIXED || DIRECT, "the mixed mode reads the main term's operands where they lie");
   // MODE 1: TF32, one MMA per k-step.  MODE 3: 3xTF32, lo*hi + hi*lo + hi*hi.  MODE 4: the same three-term split on
   // fp16 panels (kind::f16): a 128-byte operand row holds 64 halves instead of 32 floats, so a k-block spans 64 k
   // and a k-step 16, in the same bytes, descriptors and cycles as the TF32 forms.  MODE 2: fp16 panels, one MMA.
@@ -91,7 +102,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   const uint32_t peer = rank ^ 1u;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int num_tiles = p.tiles_m * p.tiles_n;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -106,9 +116,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     mbar_fence_init();
     tma_prefetch_desc(&map_a_hi);
     tma_prefetch_desc(&map_b_hi);
-    if (THREE) {
+    if (THREE || MIXED) {
       tma_prefetch_desc(&map_a_lo);
       tma_prefetch_desc(&map_b_lo);
+    }
+    if (MIXED) {
+      tma_prefetch_desc(&map_a_x);
+      tma_prefetch_desc(&map_b_x);
     }
   }
   if (warp == 1) {
@@ -125,6 +139,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   // Everything above touched no global memory, so it may overlap the tail of the kernel before this one in
   // the stream (the preparation of the low-part panels); from here on its results are needed.
   grid_dependency_wait();
+  // a gated kernel whose gate is closed has no tiles: every role falls through to the common exit
+  const bool gate_open = !p.gate || *p.gate == p.gate_value;
+  const int num_tiles = gate_open ? p.tiles_m * p.tiles_n : 0;
+  int mix_rescale = 0, mix_first = 0;
+  if (MIXED && gate_open) {
+    const MixCtl* ctl = reinterpret_cast<const MixCtl*>(p.mix_ctl);
+    mix_rescale = ctl->rescale_stages;
+    mix_first = ctl->first_scale;
+  }
+  // stages per tile: the k-blocks; in mixed mode the cross stages, the rescale stages, the main stages
+  const int stages_per_tile = MIXED ? 2 * p.num_k_blocks + mix_rescale : p.num_k_blocks;
 
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer
@@ -138,7 +163,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         pair_tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const int m0 = tm * PAIR_BM + static_cast<int>(rank) * 128;  // this block's rows of A
         const int n0 = tn * BN + static_cast<int>(rank) * HALF_N;    // this block's half of B's N-rows
-        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+        for (int it = 0; it < stages_per_tile; ++it) {
+          const int kb = MIXED ? (it < p.num_k_blocks + mix_rescale ? it : it - p.num_k_blocks - mix_rescale) : it;
           if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
             atomicCAS(p.status, 0, 0x1100 | (rank << 4) | stage);
             ok = false;
@@ -148,6 +174,30 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * Cfg::kStageBytes);
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
           uint8_t* sp = stage_base + stage * Cfg::kStageBytes;
+          if (MIXED) {
+            if (it < p.num_k_blocks + mix_rescale) {
+              // cross stage: 64 k of the four fp16 panels; a rescale stage asks for k-blocks past the end: zeros
+              tma_load_2d_pair_hint(smem_u32(sp), &map_a_lo, bar, kb * 64, m0, pol_a);
+              tma_load_2d_pair_hint(smem_u32(sp + PAIR_A_BYTES), &map_b_lo, bar, kb * 64, n0, pol_b);
+              tma_load_2d_pair_hint(smem_u32(sp + PAIR_A_BYTES + B_BYTES), &map_a_x, bar, kb * 64, m0, pol_a);
+              tma_load_2d_pair_hint(smem_u32(sp + 2 * PAIR_A_BYTES + B_BYTES), &map_b_x, bar, kb * 64, n0, pol_b);
+            } else {
+              // main stage: two consecutive k-blocks of 32 of the caller's A and B
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                uint8_t* hp = sp + h * (PAIR_A_BYTES + B_BYTES);
+                tma_load_2d_pair_hint(smem_u32(hp), &map_a_hi, bar, kb * 64 + 32 * h, m0, pol_a);
+#pragma unroll
+                for (int sl = 0; sl < SLABS; ++sl)
+                  tma_load_2d_pair_hint(smem_u32(hp + PAIR_A_BYTES + sl * 4096), &map_b_hi, bar, n0 + 32 * sl, kb * 64 + 32 * h, pol_b);
+              }
+            }
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            continue;
+          }
           tma_load_2d_pair_hint(smem_u32(sp), &map_a_hi, bar, kb * BK_ELEMS, m0, pol_a);
           if (DIRECT) {
             // B is K x N row-major: x = column, y = k; slabs of 32 columns cover this block's half
@@ -199,7 +249,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         }
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+        for (int kb = 0; kb < stages_per_tile; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&full_bar[stage]), phase, abort_flag)) {
             atomicCAS(p.status, 0, 0x1300 | stage);
             ok = false;
@@ -210,6 +260,44 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           const uint32_t sb_hi = sa_hi + PAIR_A_BYTES;
           const uint32_t sa_lo = sb_hi + B_BYTES;
           const uint32_t sb_lo = sa_lo + PAIR_A_BYTES;
+          if (MIXED) {
+            constexpr uint32_t idesc16 = umma_idesc_f16(PAIR_BM, BN);
+            constexpr uint32_t idesc32 = umma_idesc_tf32(PAIR_BM, BN, true);
+            if (kb < p.num_k_blocks) {
+              // cross terms of 64 k: lo(a)*hi(b) + hi(a)*lo(b), four k-steps of 16
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint32_t koff = k * 32;
+                umma_f16_pair(tmem_d, umma_desc_k_sw128(sa_lo + koff), umma_desc_k_sw128(sb_hi + koff), idesc16, (kb | k) ? 1u : 0u);
+                umma_f16_pair(tmem_d, umma_desc_k_sw128(sa_hi + koff), umma_desc_k_sw128(sb_lo + koff), idesc16, 1u);
+              }
+            } else if (kb < p.num_k_blocks + mix_rescale) {
+              // zero tiles: the product adds nothing, the accumulator is scaled by 2^-15
+              umma_f16_pair_scaled(tmem_d, umma_desc_k_sw128(sa_hi), umma_desc_k_sw128(sb_hi), idesc16, 15);
+            } else {
+              const bool first = kb == p.num_k_blocks + mix_rescale;
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const uint32_t sa = h ? sa_lo : sa_hi, sb = h ? sb_lo : sb_hi;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const uint64_t da = umma_desc_k_sw128(sa + k * 32);
+                  const uint64_t db = umma_desc_mn_sw128_32b(sb + k * 1024, 4096);
+                  if (first && h == 0 && k == 0)
+                    umma_tf32_pair_scaled(tmem_d, da, db, idesc32, mix_first);
+                  else
+                    umma_tf32_pair(tmem_d, da, db, idesc32, 1u);
+                }
+              }
+            }
+            umma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 0));
+            umma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            continue;
+          }
 #pragma unroll
           for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
             const uint32_t koff = k * GEMM_UMMA_K * 4;

@@ -244,6 +244,33 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, u
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same instructions with scale-input-d: D = A*B + D * 2^-scale, scale in 0..15 (an immediate of the instruction,
+// hence the switch).  The accumulator is always an input here.
+#define SB200_UMMA_SCALED_CASE(KIND, N)                                                                      \
+  case N:                                                                                                    \
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, 1, 0;\ntcgen05.mma.cta_group::2.kind::" KIND               \
+                 " [%0], %1, %2, %3, p, " #N ";\n}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc)       \
+                 : "memory");                                                                                \
+    break;
+#define SB200_UMMA_SCALED_BODY(KIND)                                                                       \
+  switch (scale) {                                                                                         \
+    SB200_UMMA_SCALED_CASE(KIND, 0) SB200_UMMA_SCALED_CASE(KIND, 1) SB200_UMMA_SCALED_CASE(KIND, 2)        \
+    SB200_UMMA_SCALED_CASE(KIND, 3) SB200_UMMA_SCALED_CASE(KIND, 4) SB200_UMMA_SCALED_CASE(KIND, 5)        \
+    SB200_UMMA_SCALED_CASE(KIND, 6) SB200_UMMA_SCALED_CASE(KIND, 7) SB200_UMMA_SCALED_CASE(KIND, 8)        \
+    SB200_UMMA_SCALED_CASE(KIND, 9) SB200_UMMA_SCALED_CASE(KIND, 10) SB200_UMMA_SCALED_CASE(KIND, 11)      \
+    SB200_UMMA_SCALED_CASE(KIND, 12) SB200_UMMA_SCALED_CASE(KIND, 13) SB200_UMMA_SCALED_CASE(KIND, 14)     \
+    default:                                                                                               \
+      asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, 1, 0;\ntcgen05.mma.cta_group::2.kind::" KIND           \
+                   " [%0], %1, %2, %3, p, 15;\n}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc)       \
+                   : "memory");                                                                            \
+      break;                                                                                               \
+  }
+__device__ __forceinline__ void umma_tf32_pair_scaled(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, int scale) {
+  SB200_UMMA_SCALED_BODY("tf32")
+}
+__device__ __forceinline__ void umma_f16_pair_scaled(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, int scale) {
+  SB200_UMMA_SCALED_BODY("f16")
+}
 // Arrive on one mbarrier (a shared::cluster address: this block's or the
 // peer's) once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {

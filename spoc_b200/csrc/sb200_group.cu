@@ -565,7 +565,7 @@ extern "C" int sb200_gemm_sharded_host(uint64_t group, int mode, int64_t M, int6
                                        int64_t ldc, float beta, const float* bias, int act) {
   Group* g = find_group(group);
   if (!g) return set_error(SB200_ERR_INVALID_HANDLE, "unknown group");
-  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16 && mode != SB200_MODE_F16)
+  if (!sb200::valid_mode(mode))
     return set_error(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   if (M < 0 || N < 0 || K < 0) return set_error(SB200_ERR_INVALID_VALUE, "negative GEMM dimension");
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL - 64) return set_error(SB200_ERR_TOO_LARGE, "GEMM dimension beyond 2^31-1");

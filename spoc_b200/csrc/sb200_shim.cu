@@ -90,6 +90,7 @@ struct DeviceState {
   // that another host thread cannot free and regrow the scratch under launches that already point into it
   std::mutex scratch_mu;
   int* status = nullptr;  // device word written by kernels whose bounded waits expire
+  MixCtl* mix_ctl = nullptr;  // control words of the mixed mode (largest magnitudes, plan), ordered like the scratch
   // set by every launch of a kernel that has bounded waits; while it is clear a synchronise has nothing to read
   // back, which keeps the launch-plus-synchronise latency of the map kernels free of a device-to-host copy
   std::atomic<bool> status_armed{false};
@@ -194,7 +195,8 @@ int current_mode() {
     const char* s = getenv("SAREK_B200_MODE");
     m = (s && (!strcmp(s, "tf32") || !strcmp(s, "TF32"))) ? SB200_MODE_TF32
         : (s && (!strcmp(s, "3xf16") || !strcmp(s, "3xF16"))) ? SB200_MODE_3XF16
-        : (s && (!strcmp(s, "f16") || !strcmp(s, "F16"))) ? SB200_MODE_F16 : SB200_MODE_3XTF32;
+        : (s && (!strcmp(s, "f16") || !strcmp(s, "F16"))) ? SB200_MODE_F16
+        : (s && (!strcmp(s, "3xmixed") || !strcmp(s, "mixed"))) ? SB200_MODE_3XMIXED : SB200_MODE_3XTF32;
     g_mode.store(m);
   }
   return m;
@@ -399,7 +401,8 @@ int choose_tile_n(long long M, long long N, long long kblocks, int clusters, int
 // looked up once per device, then the launch.
 template <int MODE, bool DIRECT, int BN>
 int launch_pair(DeviceState& d, int dev_index, cudaStream_t st, const CUtensorMap& ma_hi, const CUtensorMap& mb_hi,
-                const CUtensorMap& ma_lo, const CUtensorMap& mb_lo, GemmParams gp, long long M, long long N) {
+                const CUtensorMap& ma_lo, const CUtensorMap& mb_lo, GemmParams gp, long long M, long long N,
+                const CUtensorMap* ma_x = nullptr, const CUtensorMap* mb_x = nullptr) {
   using PCfg = PairCfg<MODE, BN>;
   static std::atomic<int> resident[kMaxDevices];  // 0 = not yet asked
   int max_clusters = resident[dev_index].load();
@@ -442,16 +445,18 @@ int launch_pair(DeviceState& d, int dev_index, cudaStream_t st, const CUtensorMa
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  CU_TRY(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<MODE, DIRECT, BN>, ma_hi, mb_hi, ma_lo, mb_lo, gp));
+  CU_TRY(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<MODE, DIRECT, BN>, ma_hi, mb_hi, ma_lo, mb_lo, ma_x ? *ma_x : ma_lo,
+                            mb_x ? *mb_x : mb_lo, gp));
   return launch_check("gemm_pair_kernel");
 }
 
 template <int MODE, bool DIRECT>
 int launch_pair_bn(int bn, DeviceState& d, int dev_index, cudaStream_t st, const CUtensorMap& ma_hi, const CUtensorMap& mb_hi,
-                   const CUtensorMap& ma_lo, const CUtensorMap& mb_lo, const GemmParams& gp, long long M, long long N) {
-  if (bn == 64) return launch_pair<MODE, DIRECT, 64>(d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N);
-  if (bn == 128) return launch_pair<MODE, DIRECT, 128>(d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N);
-  return launch_pair<MODE, DIRECT, 256>(d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N);
+                   const CUtensorMap& ma_lo, const CUtensorMap& mb_lo, const GemmParams& gp, long long M, long long N,
+                   const CUtensorMap* ma_x = nullptr, const CUtensorMap* mb_x = nullptr) {
+  if (bn == 64) return launch_pair<MODE, DIRECT, 64>(d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N, ma_x, mb_x);
+  if (bn == 128) return launch_pair<MODE, DIRECT, 128>(d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N, ma_x, mb_x);
+  return launch_pair<MODE, DIRECT, 256>(d, dev_index, st, ma_hi, mb_hi, ma_lo, mb_lo, gp, M, N, ma_x, mb_x);
 }
 
 // How sb200_gemm_f32 will run a product: which kernel, which tile, how much scratch.  One function decides, the
@@ -793,10 +798,140 @@ int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, l
   return rc;
 }
 
+// ---- mode 5: main term on the TF32 pipe, cross terms on the fp16 pipe ---------------------------------------
+// Products below this many multiply-adds, operands TMA cannot address, and problems the pair kernel does not serve
+// go to plain 3xTF32: the mixed mode costs five more launches (magnitudes, two panel passes, two gated fallbacks).
+constexpr long long kMixMinMacs = 1ll << 34;  // measured: 1.12x at 4096^3 (2^36), 0.96x at 2048^3 (2^33)
+std::atomic<long long> g_mix_min_macs{0};    // 0 = the default above
+
+bool operands_addressable(const float* A, long long lda, const float* B, long long ldb) {
+  return (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0 && (ldb & 3) == 0;
+}
+
+bool gemm_mix_applies(long long M, long long N, long long K, bool addressable) {
+  const long long set = g_mix_min_macs.load(), least = set > 0 ? set : kMixMinMacs;
+  return addressable && M > GEMM_BM && K >= 64 && M * N * K >= least && gemm_variant_setting() == 0;
+}
+
+size_t gemm_mix_workspace_need(long long M, long long N, long long K) {
+  const long long kp64 = round_up(K, 64), kp32 = round_up(K, GEMM_BK);
+  const size_t mixed = 2 * (round_up(M * kp64 * 2, 1024) + round_up(N * kp64 * 2, 1024));
+  const size_t plain = round_up(K * round_up(N, 32) * 4, 1024) + round_up(M * kp32 * 4, 1024);
+  return mixed > plain ? mixed : plain;  // one or the other runs: the two layouts share the scratch
+}
+
+int launch_gemm_mix(DeviceState& d, cudaStream_t st, long long M, long long N, long long K, const float* A, long long lda,
+                    const float* B, long long ldb, const GemmParams& gp_in) {
+  const long long kp = round_up(K, 64), kp32 = round_up(K, GEMM_BK), np = round_up(N, 32);
+  const size_t a_bytes = round_up(M * kp * 2, 1024), b_bytes = round_up(N * kp * 2, 1024);
+  std::unique_lock<std::mutex> scratch_lock(d.scratch_mu);
+  int rc = ensure_workspace(d, gemm_mix_workspace_need(M, N, K));
+  if (rc) return rc;
+  if (!d.mix_ctl) CU_TRY(cudaMalloc(&d.mix_ctl, sizeof(MixCtl)));
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) {
+    cudaGetLastError();
+    cap = cudaStreamCaptureStatusActive;
+  }
+  const bool track_scratch = cap == cudaStreamCaptureStatusNone;
+  if (track_scratch) {
+    std::lock_guard<std::mutex> lock(d.mu);
+    if (d.ws_in_use && d.ws_last_stream != st) CU_TRY(cudaStreamWaitEvent(st, d.ws_event, 0));
+  }
+  const bool prof = g_profiling.load() != 0;
+  DeviceState::ProfRec rec{nullptr, nullptr, nullptr};
+  if (prof) {
+    CU_TRY(cudaEventCreate(&rec.e0));
+    CU_TRY(cudaEventCreate(&rec.e1));
+    CU_TRY(cudaEventCreate(&rec.e2));
+    CU_TRY(cudaEventRecord(rec.e0, st));
+  }
+  uint8_t* ws = static_cast<uint8_t*>(d.workspace);
+  __half* a_hi = reinterpret_cast<__half*>(ws);
+  __half* b_hi = reinterpret_cast<__half*>(ws + a_bytes);
+  __half* a_lo = reinterpret_cast<__half*>(ws + a_bytes + b_bytes);
+  __half* b_lo = reinterpret_cast<__half*>(ws + 2 * a_bytes + b_bytes);
+  CU_TRY(cudaMemsetAsync(d.mix_ctl, 0, sizeof(MixCtl), st));
+  const long long cap16 = static_cast<long long>(d.sm_count) * 16;
+  {
+    // largest magnitudes of both matrices, one launch: a warp per row
+    long long grid_a = (M + 7) / 8, grid_b = (K + 7) / 8;
+    const long long cap8 = static_cast<long long>(d.sm_count) * 8;
+    if (grid_a > cap8) grid_a = cap8;
+    if (grid_b > cap8) grid_b = cap8;
+    const AbsMaxJob ja{A, lda, static_cast<int>(M), static_cast<int>(K), 1};
+    const AbsMaxJob jb{B, ldb, static_cast<int>(K), static_cast<int>(N), 1};
+    absmax_two_kernel<<<static_cast<unsigned>(grid_a + grid_b), 256, 0, st>>>(ja, jb, static_cast<int>(grid_a), d.mix_ctl);
+    if ((rc = launch_check("absmax_two_kernel"))) return rc;
+    long long grid = (M * (kp >> 3) + 255) / 256;
+    if (grid > cap16) grid = cap16;
+    prep_mix_a_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(A, lda, a_hi, a_lo, static_cast<int>(M), static_cast<int>(K),
+                                                                    static_cast<int>(kp), 1, d.mix_ctl);
+    if ((rc = launch_check("prep_mix_a_kernel"))) return rc;
+    long long tiles = (kp >> 6) * ((N + 31) >> 5);
+    const long long cap32 = static_cast<long long>(d.sm_count) * 32;
+    if (tiles > cap32) tiles = cap32;
+    prep_mix_b_kernel<<<static_cast<unsigned>(tiles), dim3(32, 8), 0, st>>>(B, ldb, b_hi, b_lo, static_cast<int>(K),
+                                                                             static_cast<int>(N), static_cast<int>(kp), d.mix_ctl);
+    if ((rc = launch_check("prep_mix_b_kernel"))) return rc;
+  }
+  const int clusters = d.sm_count / 2 > 0 ? d.sm_count / 2 : 1;
+  const int tile_n = choose_tile_n(M, N, kp32 / GEMM_BK, clusters, 3);
+  CUtensorMap ma, mb, ma_hi16, mb_hi16, ma_lo16, mb_lo16;
+  if ((rc = encode_map_2d(&ma, A, K, M, lda, GEMM_BK, GEMM_BM, true))) return rc;
+  if ((rc = encode_map_2d(&mb, B, N, K, ldb, 32, GEMM_BK, true, true))) return rc;
+  if ((rc = encode_map_f16(&ma_hi16, a_hi, kp, M, GEMM_BM))) return rc;
+  if ((rc = encode_map_f16(&mb_hi16, b_hi, kp, N, tile_n / 2))) return rc;
+  if ((rc = encode_map_f16(&ma_lo16, a_lo, kp, M, GEMM_BM))) return rc;
+  if ((rc = encode_map_f16(&mb_lo16, b_lo, kp, N, tile_n / 2))) return rc;
+  GemmParams gp = gp_in;
+  gp.status = d.status;
+  d.status_armed.store(true);
+  derive_params(&gp);
+  gp.mix_ctl = reinterpret_cast<const int*>(d.mix_ctl);
+  gp.gate = &d.mix_ctl->ok;
+  if (prof) CU_TRY(cudaEventRecord(rec.e1, st));
+  const int dev_index = static_cast<int>(&d - g_dev);
+  gp.num_k_blocks = static_cast<int>(kp / 64);
+  gp.gate_value = 1;
+  rc = launch_pair_bn<5, true>(tile_n, d, dev_index, st, ma, mb, ma_hi16, mb_hi16, gp, M, N, &ma_lo16, &mb_lo16);
+  if (rc == SB200_OK) {
+    // behind it, gated the other way: plain 3xTF32 on the same operands, its low-part panels in the same scratch
+    float* pb_lo = reinterpret_cast<float*>(ws);
+    float* pa_lo = reinterpret_cast<float*>(ws + round_up(K * np * 4, 1024));
+    long long grid_a = (M * (kp32 >> 2) + 255) / 256, grid_b = (K * (np >> 2) + 255) / 256;
+    if (grid_a > cap16) grid_a = cap16;
+    if (grid_b > cap16) grid_b = cap16;
+    const PrepLoJob ja{A, lda, pa_lo, static_cast<int>(M), static_cast<int>(K), static_cast<int>(kp32)};
+    const PrepLoJob jb{B, ldb, pb_lo, static_cast<int>(K), static_cast<int>(N), static_cast<int>(np)};
+    prep_lo_two_kernel<<<static_cast<unsigned>(grid_a + grid_b), 256, 0, st>>>(ja, jb, static_cast<int>(grid_a), gp.gate);
+    if ((rc = launch_check("prep_lo_two_kernel(gated)"))) return rc;
+    CUtensorMap pma_lo, pmb_lo;
+    if ((rc = encode_map_2d(&pma_lo, pa_lo, kp32, M, kp32, GEMM_BK, GEMM_BM, false))) return rc;
+    if ((rc = encode_map_2d(&pmb_lo, pb_lo, N, K, np, 32, GEMM_BK, false, true))) return rc;
+    gp.num_k_blocks = static_cast<int>(kp32 / GEMM_BK);
+    gp.gate_value = 0;
+    rc = launch_pair_bn<3, true>(tile_n, d, dev_index, st, ma, mb, pma_lo, pmb_lo, gp, M, N);
+  }
+  if (prof) {
+    CU_TRY(cudaEventRecord(rec.e2, st));
+    std::lock_guard<std::mutex> lock(d.mu);
+    d.prof.push_back(rec);
+  }
+  if (track_scratch && rc == SB200_OK) {
+    std::lock_guard<std::mutex> lock(d.mu);
+    if (!d.ws_event) CU_TRY(cudaEventCreateWithFlags(&d.ws_event, cudaEventDisableTiming));
+    CU_TRY(cudaEventRecord(d.ws_event, st));
+    d.ws_last_stream = st;
+    d.ws_in_use = true;
+  }
+  return rc;
+}
+
 int run_gemm(DeviceState& d, cudaStream_t st, int mode, long long M, long long N, long long K, uint64_t A, long long lda,
              uint64_t B, long long ldb, uint64_t D, long long ldd, float alpha, uint64_t C, long long ldc, float beta,
              uint64_t bias, int act, const uint64_t* replicas = nullptr, int n_replicas = 0) {
-  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16 && mode != SB200_MODE_F16)
+  if (!sb200::valid_mode(mode))
     return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   if (M < 0 || N < 0 || K < 0) return fail(SB200_ERR_INVALID_VALUE, "negative GEMM dimension (M=%lld N=%lld K=%lld)", M, N, K);
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL - 64)
@@ -847,7 +982,9 @@ int run_gemm(DeviceState& d, cudaStream_t st, int mode, long long M, long long N
     return launch_gemm_f16<true>(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
   if (mode == SB200_MODE_F16)
     return launch_gemm_f16<false>(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
-  if (mode == SB200_MODE_3XTF32)
+  if (mode == SB200_MODE_3XMIXED && gemm_mix_applies(M, N, K, operands_addressable(as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb)))
+    return launch_gemm_mix(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
+  if (mode == SB200_MODE_3XTF32 || mode == SB200_MODE_3XMIXED)
     return launch_gemm_mode<3>(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
   return launch_gemm_mode<1>(d, st, M, N, K, as_ptr<const float>(A), lda, as_ptr<const float>(B), ldb, gp);
 }
@@ -1927,10 +2064,15 @@ int sb200_ipc_close(int dev, uint64_t dptr) {
 
 int sb200_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, uint64_t* bytes) {
   if (!bytes || M < 0 || N < 0 || K < 0) return fail(SB200_ERR_INVALID_VALUE, "bad argument");
-  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16 && mode != SB200_MODE_F16)
+  if (!sb200::valid_mode(mode))
     return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   if (mode == SB200_MODE_3XF16 || mode == SB200_MODE_F16) {
     *bytes = (M == 0 || N == 0 || K == 0) ? 0 : gemm_f16_workspace_need(M, N, K, mode == SB200_MODE_3XF16);
+    return SB200_OK;
+  }
+  if (mode == SB200_MODE_3XMIXED) {  // upper bound: which of the two routes runs depends on the operands' addresses
+    const size_t plain = gemm_workspace_need(SB200_MODE_3XTF32, M, N, K), mixed = gemm_mix_workspace_need(M, N, K);
+    *bytes = (M == 0 || N == 0 || K == 0) ? 0 : (plain > mixed ? plain : mixed);
     return SB200_OK;
   }
   *bytes = (M == 0 || N == 0 || K == 0) ? 0 : gemm_workspace_need(mode, M, N, K);
@@ -1939,7 +2081,7 @@ int sb200_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, uint64
 
 int sb200_gemm_describe(int mode, int64_t M, int64_t N, int64_t K, int addressable, int sm_count, char* out, int outlen) {
   if (M < 0 || N < 0 || K < 0 || sm_count <= 0) return fail(SB200_ERR_INVALID_VALUE, "bad argument");
-  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16 && mode != SB200_MODE_F16)
+  if (!sb200::valid_mode(mode))
     return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   if (M == 0 || N == 0) return copy_out("nothing to do", out, outlen);
   if (K == 0) return copy_out("gemm_k0_kernel (epilogue only)", out, outlen);
@@ -1956,6 +2098,19 @@ int sb200_gemm_describe(int mode, int64_t M, int64_t N, int64_t K, int addressab
     snprintf(fb, sizeof fb, "pair fp16-panels tile=%dx%d stages=%d tiles=%lld waves=%lld workspace=%zu launches=4", PAIR_BM, tn, stages,
              tiles, (tiles + clusters - 1) / clusters, gemm_f16_workspace_need(M, N, K, three));
     return copy_out(fb, out, outlen);
+  }
+  if (mode == SB200_MODE_3XMIXED) {
+    if (gemm_mix_applies(M, N, K, addressable != 0)) {
+      const int clusters = sm_count / 2 > 0 ? sm_count / 2 : 1;
+      const int tn = choose_tile_n(M, N, round_up(K, GEMM_BK) / GEMM_BK, clusters, 3);
+      const long long tiles = ((M + PAIR_BM - 1) / PAIR_BM) * ((N + tn - 1) / tn);
+      const int stages = tn == 256 ? PairCfg<5, 256>::kStages : tn == 128 ? PairCfg<5, 128>::kStages : PairCfg<5, 64>::kStages;
+      char fb[256];
+      snprintf(fb, sizeof fb, "pair mixed tile=%dx%d stages=%d tiles=%lld waves=%lld workspace=%zu launches=7", PAIR_BM, tn, stages,
+               tiles, (tiles + clusters - 1) / clusters, gemm_mix_workspace_need(M, N, K));
+      return copy_out(fb, out, outlen);
+    }
+    mode = SB200_MODE_3XTF32;
   }
   const GemmRoute r = route_gemm(mode, M, N, K, addressable != 0, sm_count, M);
   char buf[256];
@@ -1988,8 +2143,14 @@ int sb200_chain_triad_square_f32(int dev, uint64_t stream, uint64_t dd, uint64_t
 }
 
 int sb200_set_mode(int mode) {
-  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16 && mode != SB200_MODE_F16) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
+  if (!sb200::valid_mode(mode)) return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   g_mode.store(mode);
+  return SB200_OK;
+}
+
+int sb200_set_mixed_min_macs(int64_t macs) {
+  if (macs < 0) return fail(SB200_ERR_INVALID_VALUE, "negative threshold");
+  g_mix_min_macs.store(macs);
   return SB200_OK;
 }
 
@@ -2305,7 +2466,7 @@ extern "C" int sb200_gemm_f32_noalloc(int dev, uint64_t stream, int mode, int64_
 extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                                    const float* B, int64_t ldb, float* D, int64_t ldd, float alpha, const float* C,
                                    int64_t ldc, float beta, const float* bias, int act) {
-  if (mode != SB200_MODE_3XTF32 && mode != SB200_MODE_TF32 && mode != SB200_MODE_3XF16 && mode != SB200_MODE_F16)
+  if (!sb200::valid_mode(mode))
     return fail(SB200_ERR_INVALID_VALUE, "unknown GEMM mode %d", mode);
   if (M < 0 || N < 0 || K < 0) return fail(SB200_ERR_INVALID_VALUE, "negative GEMM dimension");
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL - 64) return fail(SB200_ERR_TOO_LARGE, "GEMM dimension beyond 2^31-1");
@@ -2441,7 +2602,9 @@ extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int6
         rc = launch_gemm_f16<true>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp);
       } else if (mode == SB200_MODE_F16) {
         rc = launch_gemm_f16<false>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp);
-      } else if (mode == SB200_MODE_3XTF32) {
+      } else if (mode == SB200_MODE_3XMIXED && gemm_mix_applies(rows, N, K, operands_addressable(dA + r0 * K, K, dB, N))) {
+        rc = launch_gemm_mix(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp);
+      } else if (mode == SB200_MODE_3XTF32 || mode == SB200_MODE_3XMIXED) {
         rc = launch_gemm_mode<3>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);
       } else {
         rc = launch_gemm_mode<1>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);
@@ -2526,7 +2689,9 @@ extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int6
       rc = launch_gemm_f16<true>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp);
     } else if (mode == SB200_MODE_F16) {
       rc = launch_gemm_f16<false>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp);
-    } else if (mode == SB200_MODE_3XTF32) {
+    } else if (mode == SB200_MODE_3XMIXED && gemm_mix_applies(rows, N, K, operands_addressable(dA + r0 * K, K, dB, N))) {
+      rc = launch_gemm_mix(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp);
+    } else if (mode == SB200_MODE_3XTF32 || mode == SB200_MODE_3XMIXED) {
       rc = launch_gemm_mode<3>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);
     } else {
       rc = launch_gemm_mode<1>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);

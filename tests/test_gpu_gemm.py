@@ -32,7 +32,7 @@ def variant(request, backend):
 def tol(mode, K):
     # the floor keeps the 3xTF32 bound meaningful for tiny K, where a single
     # float32 rounding of the result (6e-8) is comparable to 1e-5*sqrt(K)
-    return max(1e-5 * math.sqrt(max(K, 1)), 1e-6) if mode in (L.MODE_3XTF32, L.MODE_3XF16) else 2e-3
+    return max(1e-5 * math.sqrt(max(K, 1)), 1e-6) if mode in (L.MODE_3XTF32, L.MODE_3XF16, L.MODE_3XMIXED) else 2e-3
 
 
 SHAPES = [(1, 1, 1), (5, 7, 3), (16, 16, 16), (128, 256, 32), (128, 256, 64), (129, 257, 33), (100, 300, 70),
@@ -854,6 +854,28 @@ def test_f16_split_config_8192_cubed_epilogue_sampled(backend, device):
         _check(lib.sb200_gemm_f32(device.id, 0, mode, M, N, K, A.ptr, K, B.ptr, N, D.ptr, N, 1.5, Cm.ptr, N, 0.5, Bi.ptr, 1))
         backend.Device.synchronize(device)
         _full_config_check(backend, device, lib, mode, M, N, K, A, B, D, 11, alpha=1.5, beta=0.5, Cm=Cm, Bi=Bi, act=1,
+                           scale=1.5 * math.sqrt(2))
+    finally:
+        for x in bufs + [Bi]:
+            backend.Memory.free(x)
+
+
+def test_mixed_config_8192_cubed_epilogue_sampled(backend, device):
+    """The headline configuration in the mixed mode (main term TF32, cross terms fp16): 64 rows + 64 columns + 4096 points
+    against the oracle, the bound of 3xTF32."""
+    from spoc_b200.plugin import _check
+    lib = L.load()
+    M = N = K = 8192
+    mode = L.MODE_3XMIXED
+    bufs = [backend.Memory.alloc(device, M * K, np.float32) for _ in range(4)]
+    A, B, Cm, D = bufs
+    Bi = backend.Memory.alloc(device, N, np.float32)
+    try:
+        for buf, sid, kind, cnt in ((A, 1, 0, M * K), (B, 2, 0, K * N), (Cm, 3, 0, M * N), (Bi, 4, 1, N)):
+            _check(lib.sb200_fill_f32(device.id, 0, buf.ptr, cnt, 20260101, sid, kind, 1.0, 0))
+        _check(lib.sb200_gemm_f32(device.id, 0, mode, M, N, K, A.ptr, K, B.ptr, N, D.ptr, N, 1.5, Cm.ptr, N, 0.5, Bi.ptr, 1))
+        backend.Device.synchronize(device)
+        _full_config_check(backend, device, lib, mode, M, N, K, A, B, D, 12, alpha=1.5, beta=0.5, Cm=Cm, Bi=Bi, act=1,
                            scale=1.5 * math.sqrt(2))
     finally:
         for x in bufs + [Bi]:

@@ -163,11 +163,11 @@ def test_mode_setting():
     assert b.get_mode() == L.MODE_TF32
     b.set_mode(L.MODE_3XTF32)
     assert b.get_mode() == L.MODE_3XTF32
-    for mode in (L.MODE_3XF16, L.MODE_F16, L.MODE_3XTF32):
+    for mode in (L.MODE_3XF16, L.MODE_F16, L.MODE_3XMIXED, L.MODE_3XTF32):
         b.set_mode(mode)
         assert b.get_mode() == mode
     with pytest.raises(BackendError):
-        b.set_mode(5)
+        b.set_mode(6)
 
 
 @pytest.mark.parametrize("find,replace", [
