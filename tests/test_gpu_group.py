@@ -18,11 +18,30 @@ from tests import oracle_lib as O
 from tests.gpu_util import CANARY, Dev, dev_from, gemm
 
 pytestmark = pytest.mark.gpu
-MODES = [L.MODE_3XTF32, L.MODE_TF32, L.MODE_3XF16, L.MODE_F16]
+MODES = [L.MODE_3XTF32, L.MODE_TF32, L.MODE_3XF16, L.MODE_F16, L.MODE_3XMIXED]
 
 
 def _tol(mode, K):
-    return (max(1e-5 * math.sqrt(K), 1e-6) if mode in (L.MODE_3XTF32, L.MODE_3XF16) else 2e-3) * 1.5 * math.sqrt(2)
+    return (max(1e-5 * math.sqrt(K), 1e-6) if mode in (L.MODE_3XTF32, L.MODE_3XF16, L.MODE_3XMIXED) else 2e-3) * 1.5 * math.sqrt(2)
+
+
+@pytest.fixture(autouse=True)
+def mixed_mode_on_small_products():
+    """The mixed mode takes products from 2^34 multiply-adds by default; lowered here so that its own kernels run."""
+    L.load().sb200_set_mixed_min_macs(1 << 20)
+    yield
+    L.load().sb200_set_mixed_min_macs(0)
+
+
+def _same(mode, got, want):
+    """Row blocks reproduce the one-launch product bit for bit — except in the mixed mode, whose fp16 panel scales follow
+    the largest magnitude of the rows a call sees and which hands row blocks below its size threshold to 3xTF32: there
+    the forms agree far inside the mode's error bound (1e-5 of the result's rms; TF32 mode would be at 1e-3)."""
+    got, want = np.asarray(got), np.asarray(want)
+    if mode != L.MODE_3XMIXED:
+        return np.array_equal(got, want)
+    rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    return float(np.abs(got.astype(np.float64) - want).max()) <= 1e-5 * max(rms, 1e-30)
 
 
 def _problem(M, N, K, seed):
@@ -80,7 +99,7 @@ def test_group_of_one_host_operands_match_the_oracle(backend, device, mode, pinn
         d2 = np.empty(M * N, np.float32)
         _check(lib.sb200_gemm_f32_host(device.id, mode, M, N, K, a.ctypes.data, K, b.ctypes.data, N, d2.ctypes.data, N, 1.5,
                                        c.ctypes.data, N, 0.5, bias.ctypes.data, 1))
-        assert np.array_equal(np.array(d), d2)
+        assert _same(mode, np.array(d), d2)
     finally:
         grp.close()
         for p in held:
@@ -141,7 +160,7 @@ def test_two_gpu_group_every_form_equals_one_gpu(backend, mode, M):
         kw = dict(alpha=1.5, c_shards=[x.ptr for x in Cs], beta=0.5, bias=Bi.ptr, act=1)
         grp.gemm(mode, M, N, K, [x.ptr for x in A], B.ptr, [x.ptr for x in blocks], **kw)
         for blk, (f, r) in zip(blocks, parts):
-            assert np.array_equal(blk.download().reshape(r, N), want[f:f + r])
+            assert _same(mode, blk.download().reshape(r, N), want[f:f + r])
         for gather in (DeviceGroup.GATHER_FUSED, DeviceGroup.GATHER_NCCL):
             for x in full:
                 x.clear()
@@ -149,7 +168,7 @@ def test_two_gpu_group_every_form_equals_one_gpu(backend, mode, M):
                           b_resident=(gather == DeviceGroup.GATHER_NCCL), **kw)
             assert ms > 0
             for x in full:
-                assert np.array_equal(x.download().reshape(M, N), want)
+                assert _same(mode, x.download().reshape(M, N), want)
         ref = O.gemm(a, b, M, N, K, 1.5, 0.5, c, bias, 1)
         assert O.gemm_rel_error(want, ref) <= _tol(mode, K)
     finally:
@@ -172,7 +191,7 @@ def test_two_gpu_group_host_operands(backend, mode):
         d1gpu = np.empty(M * N, np.float32)
         _check(lib.sb200_gemm_f32_host(d0.id, mode, M, N, K, a.ctypes.data, K, b.ctypes.data, N, d1gpu.ctypes.data, N, 1.5,
                                        c.ctypes.data, N, 0.5, bias.ctypes.data, 1))
-        assert np.array_equal(d, d1gpu)
+        assert _same(mode, d, d1gpu)
         ref = O.gemm(a, b, M, N, K, 1.5, 0.5, c, bias, 1)
         assert O.gemm_rel_error(d.reshape(M, N), ref) <= _tol(mode, K)
     finally:
