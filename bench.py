@@ -434,7 +434,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     # call, which overlaps them with the GEMM by row blocks, then Transfer.to_cpu of the result.  The direct operator on pinned and on
     # pageable buffers (one C-ABI call that overlaps copies and row-block GEMMs) is reported beside it.
     # Several GPUs: the call a single-process host makes, sb200_gemm_sharded_host on a group of all the GPUs — B
-    # crosses PCIe once and reaches the other GPUs by NCCL broadcast, every GPU moves only its own rows — issued by
+    # crosses PCIe once (a band of rows per GPU, all-gathered over NVLink), every GPU moves only its own rows — issued by
     # rank 0 on pageable operands of world x 8192 rows while the other ranks wait at a host-side barrier with
     # nothing running on their GPUs.
     e2e = None

@@ -579,7 +579,15 @@ extern "C" int sb200_gemm_sharded_host(uint64_t group, int mode, int64_t M, int6
   const HostCall hc{mode, M, N, K, A, B, C, bias, D, lda, ldb, ldc, ldd, alpha, beta, act};
   int64_t first[kMaxGroup], rows[kMaxGroup];
   float *dB[kMaxGroup], *dBias[kMaxGroup], *dA[kMaxGroup], *dC[kMaxGroup], *dD[kMaxGroup];
-  const size_t szB = al256(static_cast<size_t>(K) * N * 4), szBias = bias ? al256(static_cast<size_t>(N) * 4) : 0;
+  // B crosses PCIe once: in equal bands of rows, one per GPU and link, assembled on every GPU by an in-place all-gather
+  // over NVLink (SAREK_B200_GROUP_SPLIT_B=0: whole over the first GPU's link, then a broadcast)
+  static const bool split_env = [] {
+    const char* e = getenv("SAREK_B200_GROUP_SPLIT_B");
+    return !(e && e[0] == '0');
+  }();
+  const bool split_b = split_env && n > 1 && K >= n;
+  const int64_t band_rows = (K + n - 1) / n;  // the last band may be shorter; the buffer holds n whole bands
+  const size_t szB = al256(static_cast<size_t>(split_b ? band_rows * n : K) * N * 4), szBias = bias ? al256(static_cast<size_t>(N) * 4) : 0;
   for (int i = 0; i < n; ++i) {
     split(M, n, i, &first[i], &rows[i]);
     const size_t szA = al256(static_cast<size_t>(rows[i]) * K * 4), szC = C ? al256(static_cast<size_t>(rows[i]) * N * 4) : 0,
@@ -598,14 +606,29 @@ extern "C" int sb200_gemm_sharded_host(uint64_t group, int mode, int64_t M, int6
   GCU_TRY(cudaSetDevice(g->dev[0]));
   GCU_TRY(cudaEventRecord(g->ev0[0], g->s_main[0]));
   const bool staged_b = sb200::staged_copy_enabled() && K > 0 && sb200::host_memory_is_pageable(B);
-  int rc = K > 0 ? copy_in(g->dev[0], g->s_main[0], dB[0], B, K, N, ldb, staged_b) : SB200_OK;
+  int rc = SB200_OK;
+  if (split_b) {
+    for (int i = 0; i < n && !rc; ++i) {
+      const int64_t k0 = i * band_rows, kr = std::min<int64_t>(band_rows, K - k0);
+      if (kr <= 0) continue;
+      GCU_TRY(cudaSetDevice(g->dev[i]));
+      rc = copy_in(g->dev[i], g->s_main[i], dB[i] + k0 * N, B + k0 * ldb, kr, N, ldb, staged_b);
+    }
+    GCU_TRY(cudaSetDevice(g->dev[0]));
+  } else if (K > 0) {
+    rc = copy_in(g->dev[0], g->s_main[0], dB[0], B, K, N, ldb, staged_b);
+  }
   if (!rc && bias) GCU_TRY(cudaMemcpyAsync(dBias[0], bias, static_cast<size_t>(N) * 4, cudaMemcpyHostToDevice, g->s_main[0]));
   if (rc) return rc;
   if (n > 1) {
     NCCL_TRY(g_nccl.GroupStart());
     ncclResult_t r = ncclSuccess;
     for (int i = 0; i < n && r == ncclSuccess; ++i) {
-      if (K > 0) r = g_nccl.Broadcast(dB[i], dB[i], static_cast<size_t>(K) * N, ncclFloat, 0, g->comm[i], g->s_main[i]);
+      if (split_b)
+        r = g_nccl.AllGather(dB[i] + static_cast<size_t>(i) * band_rows * N, dB[i], static_cast<size_t>(band_rows) * N, ncclFloat,
+                             g->comm[i], g->s_main[i]);
+      else if (K > 0)
+        r = g_nccl.Broadcast(dB[i], dB[i], static_cast<size_t>(K) * N, ncclFloat, 0, g->comm[i], g->s_main[i]);
       if (bias && r == ncclSuccess) r = g_nccl.Broadcast(dBias[i], dBias[i], static_cast<size_t>(N), ncclFloat, 0, g->comm[i], g->s_main[i]);
     }
     ncclResult_t r2 = g_nccl.GroupEnd();

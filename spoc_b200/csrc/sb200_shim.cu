@@ -2605,7 +2605,9 @@ extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int6
       } else if (mode == SB200_MODE_3XMIXED && gemm_mix_applies(rows, N, K, operands_addressable(dA + r0 * K, K, dB, N))) {
         rc = launch_gemm_mix(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp);
       } else if (mode == SB200_MODE_3XTF32 || mode == SB200_MODE_3XMIXED) {
-        rc = launch_gemm_mode<3>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);
+        // a block the mixed mode leaves to 3xTF32 finds the scratch holding fp16 panels: B's low parts are made anew
+        rc = launch_gemm_mode<3>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows,
+                                 mode == SB200_MODE_3XTF32 && i > 0);
       } else {
         rc = launch_gemm_mode<1>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);
       }
@@ -2692,7 +2694,8 @@ extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int6
     } else if (mode == SB200_MODE_3XMIXED && gemm_mix_applies(rows, N, K, operands_addressable(dA + r0 * K, K, dB, N))) {
       rc = launch_gemm_mix(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp);
     } else if (mode == SB200_MODE_3XTF32 || mode == SB200_MODE_3XMIXED) {
-      rc = launch_gemm_mode<3>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);
+      rc = launch_gemm_mode<3>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows,
+                               mode == SB200_MODE_3XTF32 && i > 0);
     } else {
       rc = launch_gemm_mode<1>(*d, d->pipe_compute, rows, N, K, dA + r0 * K, K, dB, N, gp, block_rows, i > 0);
     }
