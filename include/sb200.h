@@ -347,8 +347,9 @@ SB200_API int sb200_gemm_sharded(uint64_t group, int mode, int64_t M, int64_t N,
                                  const uint64_t *d, int64_t ldd, float alpha,
                                  const uint64_t *c_shards, int64_t ldc, float beta, uint64_t bias, int act, int flags);
 SB200_API int sb200_group_last_ms(uint64_t group, float *ms);
-/* The same on HOST operands, the multi-GPU form of sb200_gemm_f32_host below: B and the bias cross PCIe once, to
- * the first GPU, and reach the others over NVLink (ncclBroadcast); each GPU pulls only its own rows of A and C
+/* The same on HOST operands, the multi-GPU form of sb200_gemm_f32_host below: B crosses PCIe once, a band of
+ * rows over each GPU's link, and is assembled on every GPU over NVLink (ncclAllGather in place; the bias goes to the
+ * first GPU and is broadcast); each GPU pulls only its own rows of A and C
  * and pushes only its own rows of D over its own PCIe link, driven by a host thread of its own, in row chunks so
  * that copies in, GEMM and copies out overlap.  Pinned memory is copied asynchronously, contiguous pageable
  * memory through the staged copier.  Returns when D is complete in host memory.  Replaces, for several devices,

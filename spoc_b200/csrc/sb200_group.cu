@@ -427,8 +427,8 @@ extern "C" int sb200_gemm_sharded(uint64_t group, int mode, int64_t M, int64_t N
 // ---------------------------------------------------------------------------------------------------
 // Row-sharded GEMM on host operands
 // ---------------------------------------------------------------------------------------------------
-// What a single-process host with its data in host memory calls: B and the bias cross PCIe once, to the
-// first GPU, and reach the others over NVLink (ncclBroadcast); every GPU pulls only its own rows of A and C
+// What a single-process host with its data in host memory calls: B crosses PCIe once, a band of rows
+// over each GPU's link, and is assembled everywhere over NVLink (ncclAllGather); every GPU pulls only its own rows of A and C
 // and pushes only its own rows of D, over its own PCIe link, driven by a host thread of its own.  Within a
 // GPU the rows move in a few chunks so that the copy in of one chunk, the GEMM of the one before and the
 // copy out of the one before that overlap.  Pinned host memory (sb200_host_alloc) is copied asynchronously;
