@@ -1319,7 +1319,12 @@ int gemm_upload_pipeline(DeviceState& d, cudaStream_t st, int mode, long long M,
   std::lock_guard<std::mutex> host_call_lock(d.host_call_mu);  // the inbound stream is shared with the host-operand calls
   int src = ensure_pipe_streams(d);
   if (src) return src;
-  long long block_rows = (M + 7) / 8;
+  static const int nblocks = [] {  // row blocks per product (SAREK_B200_PIPE_BLOCKS, 2..64)
+    const char* e = getenv("SAREK_B200_PIPE_BLOCKS");
+    const int v = e ? atoi(e) : 0;
+    return v >= 2 && v <= 64 ? v : 8;
+  }();
+  long long block_rows = (M + nblocks - 1) / nblocks;
   block_rows = (block_rows + 255) / 256 * 256;
   if (block_rows > M) block_rows = M;
   std::vector<cudaEvent_t> events;
