@@ -411,6 +411,10 @@ SB200_API int sb200_set_gemm_tile_n(int tile_n);
 /* SB200_MODE_3XMIXED hands products of fewer than this many multiply-adds (M*N*K) to 3xTF32, whose two launches cost
  * less than the mixed mode's seven on small problems; 0 restores the default (2^34).  A tuning and test knob. */
 SB200_API int sb200_set_mixed_min_macs(int64_t macs);
+/* The plan SB200_MODE_3XMIXED makes on the device from the largest magnitudes of A and B (no GPU needed): out[0] = 1
+ * when the mixed kernel takes the operands (0: the 3xTF32 kernels behind it do), out[1] = rescale stages, out[2] = the
+ * first main-term MMA's scale, out[3], out[4] = the binary exponents the fp16 panels of A and B are scaled by. */
+SB200_API int sb200_mixed_plan(float max_a, float max_b, int32_t out[5]);
 
 /* L2 eviction policies the GEMM kernels attach to their memory instructions (a per-instruction cache hint;
  * no device setting is touched): three 2-bit fields, each 0 = normal, 1 = evict first, 2 = evict last —

@@ -114,6 +114,7 @@ SIGNATURES = {
     "sb200_set_gemm_variant": ([i32], i32),
     "sb200_set_gemm_tile_n": ([i32], i32),
     "sb200_set_mixed_min_macs": ([i64], i32),
+    "sb200_mixed_plan": ([f32, f32, p(C.c_int32)], i32),
     "sb200_set_l2_policy": ([i32], i32),
     "sb200_gemm_describe": ([i32, i64, i64, i64, i32, i32, C.c_char_p, i32], i32),
     "sb200_fill_f32": ([i32, u64, u64, i64, u64, u64, i32, f64, i64], i32),

@@ -725,7 +725,7 @@ __global__ void prep_b_f16_kernel(const float* __restrict__ B, long long ldb, __
 // in the worst case (flushed to zero) its products keep TF32 accuracy, 2^-11 relative.  Every other product carries
 // the error of 3xTF32 mode.  Magnitudes for which no such scaling exists (product of the two maxima above 2^39 or
 // below 2^-60, non-finite values) clear `ok`, and the plain 3xTF32 kernels that follow do the work.
-__device__ __forceinline__ MixCtl mix_plan(unsigned int max_a, unsigned int max_b) {
+__host__ __device__ __forceinline__ MixCtl mix_plan(unsigned int max_a, unsigned int max_b) {
   MixCtl c;
   c.max_a = max_a;
   c.max_b = max_b;

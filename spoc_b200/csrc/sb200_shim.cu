@@ -2153,6 +2153,20 @@ int sb200_set_mode(int mode) {
   return SB200_OK;
 }
 
+int sb200_mixed_plan(float max_a, float max_b, int32_t out[5]) {
+  if (!out) return fail(SB200_ERR_INVALID_VALUE, "null output");
+  uint32_t ua, ub;
+  memcpy(&ua, &max_a, 4);
+  memcpy(&ub, &max_b, 4);
+  const MixCtl c = mix_plan(ua & 0x7fffffffu, ub & 0x7fffffffu);
+  out[0] = c.ok;
+  out[1] = c.rescale_stages;
+  out[2] = c.first_scale;
+  out[3] = c.shift_a;
+  out[4] = c.shift_b;
+  return SB200_OK;
+}
+
 int sb200_set_mixed_min_macs(int64_t macs) {
   if (macs < 0) return fail(SB200_ERR_INVALID_VALUE, "negative threshold");
   g_mix_min_macs.store(macs);
