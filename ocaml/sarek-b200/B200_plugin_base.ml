@@ -209,7 +209,8 @@ module B200 = struct
       | _ -> ()) ;
       match Hashtbl.find_opt Deferred.results (Deferred.key src.dptr) with
       | Some (_, host, true) when host = raw_address_of_ptr p && bytes = src.elems * src.elem_size ->
-          ()  (* the launch that wrote src has already sent it back to this very array *)
+          (* the launch that wrote src has already sent it back to this very array; good for one read *)
+          Hashtbl.remove Deferred.results (Deferred.key src.dptr)
       | _ ->
           if Lazy.force Deferred.enabled && Hashtbl.mem registered (raw_address_of_ptr p) then
             Hashtbl.replace Deferred.host_copy (Deferred.key src.dptr) p ;
