@@ -1372,8 +1372,28 @@ int gemm_upload_pipeline(DeviceState& d, cudaStream_t st, int mode, long long M,
     if (cudaMemcpyAsync(as_ptr<void>(bias->ptr), bias->host, static_cast<size_t>(N) * 4, cudaMemcpyHostToDevice, d.pipe_in) != cudaSuccess)
       return done(cuda_fail(cudaGetLastError(), "upload of the bias"));
   if ((rc = mark())) return done(rc);
-  for (long long r0 = 0; r0 < M && !rc; r0 += block_rows) {
-    const long long rows = std::min(block_rows, M - r0);
+  // The last block's GEMM and download cannot hide behind any upload, so the final stretch is cut finer: whole blocks
+  // while more than one block remains, then half of what is left, a quarter, a quarter (multiples of 256 rows).
+  std::vector<long long> cuts;  // first row of every block, then M
+  {
+    long long r = 0;
+    while (M - r > block_rows) {
+      cuts.push_back(r);
+      r += block_rows;
+    }
+    static const bool taper = [] {
+      const char* e = getenv("SAREK_B200_PIPE_TAPER");
+      return !(e && e[0] == '0');
+    }();
+    for (int split = 0; split < 2 && taper && M - r >= 512; ++split) {
+      cuts.push_back(r);
+      r += ((M - r) / 2 + 255) / 256 * 256;
+    }
+    if (r < M) cuts.push_back(r);
+    cuts.push_back(M);
+  }
+  for (size_t bi = 0; bi + 1 < cuts.size() && !rc; ++bi) {
+    const long long r0 = cuts[bi], rows = cuts[bi + 1] - r0;
     if (a.host && K > 0 &&
         cudaMemcpyAsync(as_ptr<float>(a.ptr) + r0 * K, static_cast<const float*>(a.host) + r0 * K, static_cast<size_t>(rows) * K * 4,
                         cudaMemcpyHostToDevice, d.pipe_in) != cudaSuccess)
