@@ -486,9 +486,31 @@ void member_main(Group* g, int i, const HostCall* hc, int64_t first, int64_t row
   const bool staged_a = sb200::staged_copy_enabled() && c.K > 0 && sb200::host_memory_is_pageable(c.A);
   const bool staged_c = sb200::staged_copy_enabled() && c.C && sb200::host_memory_is_pageable(c.C);
   const bool staged_d = sb200::staged_copy_enabled() && sb200::host_memory_is_pageable(c.D) && c.ldd == c.N;
-  int64_t chunk = (rows + kHostChunks - 1) / kHostChunks;
+  // Row chunks: four when anything goes through the staged copier (it wants large pieces); from page-locked memory
+  // eight, and the last of them cut again into a half and two quarters, because the last chunk's GEMM and copy out
+  // hide behind nothing (SAREK_B200_PIPE_TAPER=0: four equal chunks always).
+  static const bool taper = [] {
+    const char* e = getenv("SAREK_B200_PIPE_TAPER");
+    return !(e && e[0] == '0');
+  }();
+  const bool fine = taper && !(staged_a || staged_c || staged_d);
+  int64_t chunk = (rows + (fine ? 2 * kHostChunks : kHostChunks) - 1) / (fine ? 2 * kHostChunks : kHostChunks);
   chunk = (chunk + 255) / 256 * 256;  // chunk edges on tile edges
   if (chunk <= 0) chunk = 256;
+  std::vector<int64_t> cuts;  // first row of every chunk, then `rows`
+  {
+    int64_t r = 0;
+    while (rows - r > chunk) {
+      cuts.push_back(r);
+      r += chunk;
+    }
+    for (int split = 0; split < 2 && fine && rows - r >= 512; ++split) {
+      cuts.push_back(r);
+      r += ((rows - r) / 2 + 255) / 256 * 256;
+    }
+    if (r < rows) cuts.push_back(r);
+    cuts.push_back(rows);
+  }
   std::vector<cudaEvent_t> ev_in, ev_done;
   auto cleanup = [&] {
     cudaStreamSynchronize(g->s_in[i]);
@@ -516,8 +538,8 @@ void member_main(Group* g, int i, const HostCall* hc, int64_t first, int64_t row
   };
   int64_t prev_r0 = -1, prev_nr = 0;
   cudaEvent_t prev_done = nullptr;
-  for (int64_t r0 = 0; r0 < rows && !rc; r0 += chunk) {
-    const int64_t nr = std::min(chunk, rows - r0);
+  for (size_t ci = 0; ci + 1 < cuts.size() && !rc; ++ci) {
+    const int64_t r0 = cuts[ci], nr = cuts[ci + 1] - r0;
     cudaEvent_t in = nullptr, done = nullptr;
     if (cudaEventCreateWithFlags(&in, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&done, cudaEventDisableTiming) != cudaSuccess) {
