@@ -1227,10 +1227,11 @@ int gemm_upload_pipeline(DeviceState& d, cudaStream_t st, int mode, long long M,
                          const Slot& b, const Slot* c, const Slot* bias, const Slot& dd, float alpha, float beta, int act, void* d_host);
 
 int ensure_pipe_streams(DeviceState& d) {
-  if (!d.pipe_in) {
-    CU_TRY(cudaStreamCreateWithFlags(&d.pipe_in, cudaStreamNonBlocking));
-    CU_TRY(cudaStreamCreateWithFlags(&d.pipe_compute, cudaStreamNonBlocking));
-    CU_TRY(cudaStreamCreateWithFlags(&d.pipe_out, cudaStreamNonBlocking));
+  std::lock_guard<std::mutex> lock(d.mu);  // callers on several host threads may get here at once
+  if (!d.pipe_out) {
+    if (!d.pipe_in) CU_TRY(cudaStreamCreateWithFlags(&d.pipe_in, cudaStreamNonBlocking));
+    if (!d.pipe_compute) CU_TRY(cudaStreamCreateWithFlags(&d.pipe_compute, cudaStreamNonBlocking));
+    CU_TRY(cudaStreamCreateWithFlags(&d.pipe_out, cudaStreamNonBlocking));  // last: its presence says all three exist
   }
   return SB200_OK;
 }
@@ -2518,11 +2519,7 @@ extern "C" int sb200_gemm_f32_host(int dev, int mode, int64_t M, int64_t N, int6
   int rc = device_ready(dev, &d);
   if (rc) return rc;
   std::lock_guard<std::mutex> host_call_lock(d->host_call_mu);
-  if (!d->pipe_in) {
-    CU_TRY(cudaStreamCreateWithFlags(&d->pipe_in, cudaStreamNonBlocking));
-    CU_TRY(cudaStreamCreateWithFlags(&d->pipe_compute, cudaStreamNonBlocking));
-    CU_TRY(cudaStreamCreateWithFlags(&d->pipe_out, cudaStreamNonBlocking));
-  }
+  if ((rc = ensure_pipe_streams(*d))) return rc;
   // device mirrors, packed: A[M x K], B[K x N], C[M x N] (if any), D[M x N], bias[N]
   auto al = [](size_t b) { return (b + 255) / 256 * 256; };
   const size_t szA = al(size_t(M) * K * 4), szB = al(size_t(K) * N * 4), szC = C ? al(size_t(M) * N * 4) : 0,
