@@ -482,6 +482,12 @@ class Vector:
                 self._pinned = True
 
     def __del__(self):
+        if getattr(self, "_prefetch_dev", None) is not None:   # a result still on its way into the array that is going away
+            try:
+                L.load().sb200_prefetch_wait(self._prefetch_dev)
+            except Exception:
+                pass
+            self._prefetch_dev = None
         if getattr(self, "_pinned", False):     # never leave a registration behind memory that is being released
             try:
                 L.load().sb200_host_unregister(self.host.ctypes.data_as(C.c_void_p))
