@@ -197,3 +197,50 @@ def test_two_gpu_group_host_operands(backend, mode):
     finally:
         grp.close()
         backend.Device.set_current(d0)
+
+
+@pytest.mark.parametrize("gpus", [1, 2])
+@pytest.mark.parametrize("pinned", [False, True])
+def test_group_host_operands_with_row_strides(backend, gpus, pinned):
+    """Host matrices that are windows of wider arrays (lda > K, ldb > N, ldc, ldd > N): every copy is two-dimensional,
+    B's bands over the GPUs' links included; K = 137 is odd so the last band is shorter; what lies outside the windows
+    is not touched."""
+    if backend.Device.count() < gpus:
+        pytest.skip("needs two GPUs")
+    lib = L.load()
+    M, N, K = 1033, 260, 137
+    lda, ldb, ldc, ldd = K + 5, N + 12, N + 4, N + 8
+    rng = np.random.default_rng(17)
+    held = []
+
+    def host(rows, ld):
+        x = rng.standard_normal(rows * ld).astype(np.float32)
+        if not pinned:
+            return x
+        p = C.c_void_p()
+        _check(lib.sb200_host_alloc(x.nbytes, C.byref(p)))
+        held.append(p)
+        v = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(x.size,))
+        v[:] = x
+        return v
+
+    a, b, c, d = host(M, lda), host(K, ldb), host(M, ldc), host(M, ldd)
+    d[:] = CANARY
+    bias = rng.standard_normal(N).astype(np.float32)
+    devs = [backend.Device.get(i).id for i in range(gpus)]
+    grp = DeviceGroup(devs)
+    try:
+        _check(lib.sb200_gemm_sharded_host(grp.handle, L.MODE_3XTF32, M, N, K, a.ctypes.data, lda, b.ctypes.data, ldb, d.ctypes.data,
+                                           ldd, 1.5, c.ctypes.data, ldc, 0.5, bias.ctypes.data, 1))
+        dv = np.array(d).reshape(M, ldd)
+        assert np.all(dv[:, N:] == CANARY)
+        av = np.ascontiguousarray(np.array(a).reshape(M, lda)[:, :K]).ravel()
+        bv = np.ascontiguousarray(np.array(b).reshape(K, ldb)[:, :N]).ravel()
+        cv = np.ascontiguousarray(np.array(c).reshape(M, ldc)[:, :N]).ravel()
+        ref = O.gemm(av, bv, M, N, K, 1.5, 0.5, cv, bias, 1)
+        assert O.gemm_rel_error(dv[:, :N], ref) <= _tol(L.MODE_3XTF32, K)
+    finally:
+        grp.close()
+        for p in held:
+            _check(lib.sb200_host_free(p))
+        backend.Device.set_current(backend.Device.get(0))
