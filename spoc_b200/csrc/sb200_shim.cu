@@ -1409,6 +1409,9 @@ int gemm_upload_pipeline(DeviceState& d, cudaStream_t st, int mode, long long M,
     if (!rc && d_host)
       rc = download_behind(d, st, static_cast<float*>(d_host) + r0 * N, D + static_cast<uint64_t>(r0) * N * 4, static_cast<size_t>(rows) * N * 4);
   }
+  // what D's vector holds beyond the product goes back too: the caller is told that the whole host copy is current
+  if (!rc && d_host && dd.len > M * N)
+    rc = download_behind(d, st, static_cast<float*>(d_host) + M * N, D + static_cast<uint64_t>(M) * N * 4, static_cast<size_t>(dd.len - M * N) * 4);
   return done(rc);
 }
 

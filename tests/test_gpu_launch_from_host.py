@@ -195,7 +195,7 @@ def test_run_vectors_repeated_with_large_vectors(backend, device):
 
 
 @pytest.mark.parametrize("shape,whole", [((1024, 512, 256), True), ((2304, 256, 128), True), ((700, 300, 64), False)])
-@pytest.mark.parametrize("from_host", [True, False])
+@pytest.mark.parametrize("from_host", ["all", "operands", "none"])
 def test_longer_vectors_and_the_result_sent_back_behind_the_kernel(backend, device, shape, whole, from_host):
     """Vectors longer than the product needs arrive whole (tails and the old contents of D's vector included), and the
     result is on the host after sb200_prefetch_wait without a download call — on the pipelined route (whole launch,
@@ -217,10 +217,12 @@ def test_longer_vectors_and_the_result_sent_back_behind_the_kernel(backend, devi
         want = _download(backend, device, ref_bufs[4])
         assert np.array_equal(want[covered:], d0[covered:])
         host = [pin.array(x) for x in (a, b, c, bias, d0)]
-        if not from_host:
-            for buf, x in zip(new_bufs, (a, b, c, bias, d0)):
-                backend.Memory.host_to_device(src=x, dst=buf)
-        coming = _launch(backend, device, ir, shape, new_bufs, host if from_host else [None] * 5, grid, block,
+        resident = {"all": [], "operands": [4], "none": [0, 1, 2, 3, 4]}[from_host]
+        for i in resident:
+            backend.Memory.host_to_device(src=(a, b, c, bias, d0)[i], dst=new_bufs[i])
+        if 4 in resident:
+            host[4][:] = -1.0          # the host copy of D is stale everywhere, beyond the product too
+        coming = _launch(backend, device, ir, shape, new_bufs, [None if i in resident else host[i] for i in range(5)], grid, block,
                          copies=[None, None, None, None, host[4]])
         assert coming == {8}                       # the fifth vector's buffer argument
         _check(L.load().sb200_prefetch_wait(device.id))
