@@ -1249,6 +1249,74 @@ int download_behind(DeviceState& d, cudaStream_t st, void* host, uint64_t dev_pt
   return ce == cudaSuccess ? SB200_OK : cuda_fail(ce, "download of a result behind its kernel");
 }
 
+// The element-wise operators by chunks: the inputs of a chunk come over on the inbound stream, the kernel of the chunk
+// follows them on `st`, and the outputs of the chunk go back on the outbound stream to the page-locked arrays the caller
+// named for them (out_host[0], out_host[1]; null: stay on the device).  Every element depends on its own index only, so
+// the chunks compute what the one launch computes.  Vectors longer than the launch covers travel whole, as after
+// Transfer.to_device.  Returns when every upload has completed.
+int map_upload_pipeline(DeviceState& d, cudaStream_t st, const KernelPlan& plan, const std::vector<Slot>& s, long long n,
+                        void* const out_host[2]) {
+  std::lock_guard<std::mutex> host_call_lock(d.host_call_mu);
+  int rc = ensure_pipe_streams(d);
+  if (rc) return rc;
+  const MapPlan& m = plan.map;
+  std::vector<cudaEvent_t> events;
+  auto done = [&](int r) {
+    cudaStreamSynchronize(d.pipe_in);
+    for (auto e : events) cudaEventDestroy(e);
+    cudaGetLastError();
+    return r;
+  };
+  auto order = [&](cudaStream_t from, cudaStream_t to) -> int {  // `to` continues behind what `from` holds so far
+    cudaEvent_t e = nullptr;
+    cudaError_t ce = cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
+    if (ce == cudaSuccess) {
+      events.push_back(e);
+      ce = cudaEventRecord(e, from);
+    }
+    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(to, e, 0);
+    return ce == cudaSuccess ? SB200_OK : cuda_fail(ce, "ordering a chunk behind its upload");
+  };
+  if ((rc = order(st, d.pipe_in))) return done(rc);  // not before work that still uses these buffers on `st`
+  const int vecs[4] = {m.in0, m.in1, m.out0, m.out1};
+  auto seen_before = [&](int idx) {  // the same buffer bound to several parameters moves once
+    for (int j = 0; j < idx; ++j)
+      if (vecs[j] >= 0 && vecs[idx] >= 0 && s[vecs[j]].ptr == s[vecs[idx]].ptr) return true;
+    return false;
+  };
+  auto upload = [&](const Slot& v, long long first, long long count) -> bool {
+    if (!v.host || count <= 0) return true;
+    return cudaMemcpyAsync(as_ptr<float>(v.ptr) + first, static_cast<const float*>(v.host) + first, static_cast<size_t>(count) * 4,
+                           cudaMemcpyHostToDevice, d.pipe_in) == cudaSuccess;
+  };
+  // beyond the launch: whole tails of every vector; of the outputs also nothing below n (the kernel writes all of it)
+  for (int j = 0; j < 4; ++j)
+    if (vecs[j] >= 0 && !seen_before(j) && !upload(s[vecs[j]], n, s[vecs[j]].len - n))
+      return done(cuda_fail(cudaGetLastError(), "upload of a vector's tail"));
+  long long chunk = (n + 15) / 16;
+  chunk = (chunk + 1023) / 1024 * 1024;  // keeps every chunk 16-byte aligned for the vector loads
+  for (long long e0 = 0; e0 < n && !rc; e0 += chunk) {
+    const long long cnt = std::min(chunk, n - e0);
+    for (int j = 0; j < 2; ++j)  // inputs (an output that is also an input is one of them)
+      if (vecs[j] >= 0 && !seen_before(j) && !upload(s[vecs[j]], e0, cnt))
+        return done(cuda_fail(cudaGetLastError(), "upload of a chunk"));
+    if ((rc = order(d.pipe_in, st))) break;
+    const uint64_t off = static_cast<uint64_t>(e0) * 4;
+    rc = run_map(d, st, m.op, s[m.out0].ptr + off, m.out1 >= 0 ? s[m.out1].ptr + off : 0, s[m.in0].ptr + off, s[m.in1].ptr + off,
+                 coef_value(m.scalar, s), cnt);
+    if (!rc && out_host[0]) rc = download_behind(d, st, static_cast<float*>(out_host[0]) + e0, s[m.out0].ptr + off, static_cast<size_t>(cnt) * 4);
+    if (!rc && out_host[1] && m.out1 >= 0)
+      rc = download_behind(d, st, static_cast<float*>(out_host[1]) + e0, s[m.out1].ptr + off, static_cast<size_t>(cnt) * 4);
+  }
+  for (int j = 0; j < 2 && !rc; ++j) {  // the outputs' tails complete the host copies
+    const int v = j == 0 ? m.out0 : m.out1;
+    if (v >= 0 && out_host[j] && s[v].len > n)
+      rc = download_behind(d, st, static_cast<float*>(out_host[j]) + n, s[v].ptr + static_cast<uint64_t>(n) * 4,
+                           static_cast<size_t>(s[v].len - n) * 4);
+  }
+  return done(rc);
+}
+
 // pipeline_uploads: some operands are still in (pinned) host memory; when the launch covers the whole product they are
 // moved by row blocks with the GEMM of each block behind its rows.  *pipelined tells the caller whether that happened.
 // d_host: page-locked host memory the result is to be brought back to behind the kernel (null: leave it on the device).
@@ -1851,6 +1919,30 @@ static int kernel_launch_impl(uint64_t kernel, const sb200_arg* args, int nargs,
     if (out.host_out && out.len > 0 && !host_memory_is_pageable(out.host_out)) {
       d_host = out.host_out;
       d_arg = out.arg;
+    }
+  }
+  // the element-wise operators by chunks, when the vectors are large and the launch indexes by the global thread id
+  if (k->plan.kind == KIND_MAP && k->plan.map.op != OP_GENERIC && k->plan.map.index_kind == IDX_GLOBAL && all_pinned) {
+    const MapPlan& m = k->plan.map;
+    long long n = static_cast<long long>(grid[0]) * block[0];
+    if (m.n_param >= 0 && slots[m.n_param].i < n) n = slots[m.n_param].i;
+    void* out_host[2] = {nullptr, nullptr};
+    int out_arg[2] = {-1, -1};
+    for (int j = 0; j < 2 && prefetched; ++j) {
+      const int v = j == 0 ? m.out0 : m.out1;
+      if (v >= 0 && slots[v].host_out && slots[v].len > 0 && !host_memory_is_pageable(slots[v].host_out)) {
+        out_host[j] = slots[v].host_out;
+        out_arg[j] = slots[v].arg;
+      }
+    }
+    bool fits = n > 0;
+    for (int v : {m.out0, m.out1, m.in0, m.in1})
+      if (v >= 0 && slots[v].len < n) fits = false;  // the plain launch reports it
+    if (fits && static_cast<size_t>(n) * 4 >= kStagedCopyMinBytes && (any_host || out_host[0] || out_host[1])) {
+      rc = map_upload_pipeline(*d, st, k->plan, slots, n, out_host);
+      for (int j = 0; j < 2 && !rc; ++j)
+        if (out_arg[j] >= 0) prefetched[out_arg[j]] = 1;
+      return rc;
     }
   }
   if (any_host) {

@@ -264,3 +264,98 @@ def test_null_table_and_short_vectors_are_refused(backend, device):
     assert lib.sb200_kernel_launch_from_host(k.handle, arr, 1, None, None, None, g, b, 0, 0) == L.ERR_INVALID_VALUE
     hp, pre = (C.c_void_p * 1)(), (C.c_int32 * 1)()
     assert lib.sb200_kernel_launch_from_host(k.handle, arr, 1, hp, None, pre, g, b, 0, 0) == L.ERR_INVALID_VALUE
+
+
+# ---- element-wise operators by chunks -----------------------------------------------------------------------------
+N_MAP = (8 << 20) + 12345          # 32 MiB per vector and a ragged end
+
+
+def _map_launch(backend, device, ir, bufs, hosts, copies, scalars, n):
+    args = []
+    for buf, host, copy in zip(bufs, hosts, copies):
+        args += [RSA_Buffer(buf, buf.size, host, copy), RSA_Int32(buf.size)]
+    args += scalars
+    return backend.run_source(source=ir, lang=backend.supported_source_langs[0], kernel_name="sarek_kern", block=dims1d(256),
+                              grid=dims1d((n + 255) // 256), shared_mem=0, args=args)
+
+
+@pytest.mark.parametrize("kernel", ["vector_add", "stream_triad", "chain"])
+@pytest.mark.parametrize("extra", [0, 777])
+def test_map_from_pinned_host_arrays_by_chunks(backend, device, kernel, extra):
+    """Large vectors from page-locked arrays: uploaded, computed and sent back chunk by chunk; the same bits as upload,
+    one launch, download; vectors longer than the launch covers arrive whole and come back whole."""
+    from spoc_b200.plugin import RSA_Float32
+    n, length = N_MAP, N_MAP + extra
+    x, y, z0 = O.fill(length, 31, 1), O.fill(length, 31, 2), O.fill(length, 31, 3)
+    if kernel == "vector_add":       # a, b -> c
+        ir, order, out, scalars = sarek_ir.vector_add_ir(), (x, y, z0), 2, [RSA_Int32(n)]
+    elif kernel == "stream_triad":   # a <- b + c * s
+        ir, order, out, scalars = sarek_ir.stream_triad_ir(), (z0, x, y), 0, [RSA_Float32(3.0), RSA_Int32(n)]
+    else:                            # d <- (b + 3c)^2 + b, unguarded: the launch covers whole blocks of 256
+        n = N_MAP // 256 * 256
+        ir, order, out, scalars = sarek_ir.chain_fused_ir(3.0), (z0, x, y), 0, []
+    pin = _Pinned()
+    ref_bufs = [backend.Memory.alloc(device, length, np.float32) for _ in range(3)]
+    new_bufs = [backend.Memory.alloc(device, length, np.float32) for _ in range(3)]
+    try:
+        for buf, v in zip(ref_bufs, order):
+            backend.Memory.host_to_device(src=v, dst=buf)
+        assert _map_launch(backend, device, ir, ref_bufs, [None] * 3, [None] * 3, scalars, n) == set()
+        want = _download(backend, device, ref_bufs[out])
+        assert np.array_equal(want[n:], order[out][n:])             # beyond the launch: untouched
+        host = [pin.array(v) for v in order]
+        coming = _map_launch(backend, device, ir, new_bufs, host, [host[i] if i == out else None for i in range(3)], scalars, n)
+        assert coming == {2 * out}
+        _check(L.load().sb200_prefetch_wait(device.id))
+        assert np.array_equal(host[out].view(np.uint32), want.view(np.uint32))
+        for i in range(3):
+            assert np.array_equal(_download(backend, device, new_bufs[i]), want if i == out else order[i])
+    finally:
+        for buf in ref_bufs + new_bufs:
+            backend.Memory.free(buf)
+        pin.release()
+
+
+def test_map_in_place_from_the_host(backend, device):
+    """stream_triad with its output bound to the buffer of its first input: a <- a + c * s."""
+    from spoc_b200.plugin import RSA_Float32
+    n = N_MAP
+    a, c = O.fill(n, 32, 1), O.fill(n, 32, 2)
+    pin = _Pinned()
+    A, Cb = backend.Memory.alloc(device, n, np.float32), backend.Memory.alloc(device, n, np.float32)
+    try:
+        ha, hc = pin.array(a), pin.array(c)
+        coming = _map_launch(backend, device, sarek_ir.stream_triad_ir(), [A, A, Cb], [ha, ha, hc], [ha, None, None],
+                             [RSA_Float32(0.5), RSA_Int32(n)], n)
+        assert coming == {0}
+        _check(L.load().sb200_prefetch_wait(device.id))
+        want = (a.astype(np.float64) + c.astype(np.float64) * 0.5).astype(np.float32)
+        assert np.array_equal(np.array(ha), want)
+        assert np.array_equal(_download(backend, device, A), want)
+    finally:
+        backend.Memory.free(A)
+        backend.Memory.free(Cb)
+        pin.release()
+
+
+def test_run_vectors_on_large_map_vectors(backend, device):
+    """Through Vector / run_vectors: pageable on the first launch, pinned in place later, chunked from then on."""
+    n = N_MAP
+    b, c = O.fill(n, 33, 1), O.fill(n, 33, 2)
+    vb, vc, vd = Vector(backend, b.copy()), Vector(backend, c.copy()), Vector(backend, np.zeros(n, dtype=np.float32))
+    want = (b.astype(np.float64) + c.astype(np.float64)).astype(np.float32)
+    try:
+        for rep in range(4):
+            vb.location = vc.location = Vector.CPU
+            run_vectors(backend, device=device, ir=sarek_ir.vector_add_ir(), args=[vb, vc, vd, ("int32", n)], block=dims1d(256),
+                        grid=dims1d((n + 255) // 256))
+            got = vd.to_array()
+            assert np.array_equal(got, want), rep
+            vd.host[:] = -1.0
+            vd.location = Vector.STALE_CPU if rep % 2 else Vector.BOTH   # sometimes the host copy is declared current
+            if vd.location == Vector.BOTH:
+                vd.host[:] = want
+        assert vb._pinned and vd._pinned
+    finally:
+        for v in (vb, vc, vd):
+            v.free()
