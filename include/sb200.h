@@ -190,8 +190,9 @@ SB200_API int sb200_kernel_launch(uint64_t kernel, const sb200_arg *args, int na
  * Transfer.to_device of each argument followed by the launch (sarek/sarek/Execute.ml:520-543,
  * sarek/core/Transfer.ml:229-268) in one call, which lets the library overlap the two: when the kernel is a recognised
  * matmul whose launch covers the whole product and the host arrays are pinned or registered, B and the bias go first and
- * A and C follow in row blocks, each block's GEMM starting when its rows have arrived; otherwise the vectors are
- * copied whole (staged when pageable and large) and the kernel is launched behind them.  The call returns when every
+ * A and C follow in row blocks, each block's GEMM starting when its rows have arrived; the ahead-of-time element-wise
+ * operators on vectors of 16 MiB or more go chunk by chunk the same way; otherwise the vectors are copied whole (staged
+ * when pageable and large) and the kernel is launched behind them.  The call returns when every
  * upload has completed, so the host arrays may be changed at once; the kernel may still be running on `stream`. */
 SB200_API int sb200_kernel_launch_from_host(uint64_t kernel, const sb200_arg *args, int nargs,
                                             const void *const *host_ptrs, void *const *host_out,
@@ -201,8 +202,9 @@ SB200_API int sb200_kernel_launch_from_host(uint64_t kernel, const sb200_arg *ar
  * host_out entry of a buffer argument names the host array the caller keeps that vector's host copy in.  The reference
  * marks every vector argument stale on the host after a launch (sarek/sarek/Execute.ml:546-553) and downloads it when
  * the host next reads it (sarek/core/Transfer.ml:272-322); a stale host copy may therefore be overwritten early.  For
- * the vector a recognised matmul writes, when that array is pinned or registered, the library sends the result back
- * behind the kernel (row block by row block on the pipelined route) and sets prefetched[i] = 1; every other entry is
+ * the vector a recognised matmul writes (or the outputs of an element-wise operator that runs by chunks), when that
+ * array is pinned or registered, the library sends the result back behind the kernel (block by block on the
+ * pipelined routes) and sets prefetched[i] = 1; every other entry is
  * set to 0 and the caller downloads as before.  The host copy is complete once sb200_prefetch_wait has returned. */
 SB200_API int sb200_prefetch_wait(int dev);
 
