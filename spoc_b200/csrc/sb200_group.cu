@@ -494,7 +494,13 @@ void member_main(Group* g, int i, const HostCall* hc, int64_t first, int64_t row
     return !(e && e[0] == '0');
   }();
   const bool fine = taper && !(staged_a || staged_c || staged_d);
-  int64_t chunk = (rows + (fine ? 2 * kHostChunks : kHostChunks) - 1) / (fine ? 2 * kHostChunks : kHostChunks);
+  static const int fine_chunks = [] {  // SAREK_B200_GROUP_CHUNKS: chunks per GPU from page-locked memory (4..64)
+    const char* e = getenv("SAREK_B200_GROUP_CHUNKS");
+    const int v = e ? atoi(e) : 0;
+    return v >= 4 && v <= 64 ? v : 2 * kHostChunks;
+  }();
+  const int nchunks = fine ? fine_chunks : kHostChunks;
+  int64_t chunk = (rows + nchunks - 1) / nchunks;
   chunk = (chunk + 255) / 256 * 256;  // chunk edges on tile edges
   if (chunk <= 0) chunk = 256;
   std::vector<int64_t> cuts;  // first row of every chunk, then `rows`
