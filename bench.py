@@ -858,14 +858,15 @@ def run_case(args) -> None:
         return run_tiles_case(lib, dev)
     if args.case in ("gemm3", "gemm1", "gemm4", "gemm5"):
         mode = {"gemm3": L.MODE_3XTF32, "gemm1": L.MODE_TF32, "gemm4": L.MODE_3XF16, "gemm5": L.MODE_3XMIXED}[args.case]
-        bufs = [torch.empty(S * S, dtype=torch.float32, device=tdev) for _ in range(4)]
+        Mr = args.rows or S        # --rows: a row block of the square problem (what one GPU of a group computes)
+        bufs = [torch.empty(n, dtype=torch.float32, device=tdev) for n in (Mr * S, S * S, Mr * S, Mr * S)]
         bias = torch.empty(S, dtype=torch.float32, device=tdev)
         for i, t in enumerate(bufs[:3]):
             _check(lib.sb200_fill_f32(dev.id, stream, t.data_ptr(), t.numel(), SEED, i + 1, 0, 1.0, 0))
         _check(lib.sb200_fill_f32(dev.id, stream, bias.data_ptr(), S, SEED, 4, 1, 1.0, 0))
-        fn = lambda: _check(lib.sb200_gemm_f32(dev.id, stream, mode, S, S, S, bufs[0].data_ptr(), S, bufs[1].data_ptr(), S,
+        fn = lambda: _check(lib.sb200_gemm_f32(dev.id, stream, mode, Mr, S, S, bufs[0].data_ptr(), S, bufs[1].data_ptr(), S,
                                                bufs[3].data_ptr(), S, 1.5, bufs[2].data_ptr(), S, 0.5, bias.data_ptr(), 1))
-        work, unit = 2.0 * S ** 3 / 1e12, "TFLOP/s"
+        work, unit = 2.0 * Mr * S * S / 1e12, "TFLOP/s"
     else:
         n = S * S
         bufs = [torch.empty(n, dtype=torch.float32, device=tdev) for _ in range(3)]
@@ -884,7 +885,7 @@ def run_case(args) -> None:
     torch.cuda.synchronize()
     _check(lib.sb200_device_synchronize(dev.id))
     ms = e0.elapsed_time(e1) / 2
-    print(json.dumps({"case": args.case, "size": S, "ms_per_call": ms, "rate": work / (ms * 1e-3), "unit": unit}), flush=True)
+    print(json.dumps({"case": args.case, "size": S, "rows": getattr(args, "rows", 0) or S, "ms_per_call": ms, "rate": work / (ms * 1e-3), "unit": unit}), flush=True)
 
 
 class Ctx:
@@ -1192,6 +1193,7 @@ def main() -> None:
     ap.add_argument("--case", default=None, choices=["gemm3", "gemm1", "gemm4", "gemm5", "map", "transfer", "tiles"],
                     help="profiler-sized single-operator run (square size --size; map uses size^2 elements)")
     ap.add_argument("--size", type=int, default=4096)
+    ap.add_argument("--rows", type=int, default=0, help="--case gemm*: M (default: --size); N = K = --size")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
