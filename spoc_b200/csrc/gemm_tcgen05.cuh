@@ -89,6 +89,11 @@ struct GemmParams {
   int gate_value;
   // Mixed mode: the control words its preparation wrote (MixCtl below).
   const int* mix_ctl;
+  // Soft lockstep for long k-loops (CTA-pair kernel; null: off): 64 epoch counters in global memory, zero before the
+  // launch.  Every 64 stages the TMA lane of each pair's leader counts itself into its epoch's counter and waits a few
+  // microseconds at most for the other pairs, so that the pairs of a wave, which share rows of A and columns of B
+  // through L2, stay within L2's reach of one another.  A hint: nothing depends on the wait.
+  unsigned int* epoch_ctr;
 };
 
 // Control words of the mixed mode, in device memory: the preparation kernels fill them, the GEMM reads them.

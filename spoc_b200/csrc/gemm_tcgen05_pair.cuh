@@ -41,6 +41,19 @@ struct PairCfg {
   static constexpr uint32_t kSmemBytes = kStages * kStageBytes + GEMM_EPI_BUF_BYTES + GEMM_CTRL_BYTES + 1024;
 };
 
+constexpr int PAIR_EPOCH_STAGES = 64;  // soft lockstep: stages between two epochs
+constexpr int PAIR_EPOCH_RING = 64;    // epoch counters (a pair far ahead wraps onto an old counter: harmless, a hint)
+
+// Count this pair into epoch e and wait, for wait_ns at most, until all `pairs` pairs of the launch have reached it.
+__device__ __forceinline__ void pair_soft_epoch(unsigned int* ctr, unsigned int e, unsigned int pairs, uint64_t wait_ns) {
+  unsigned int* slot = ctr + (e % PAIR_EPOCH_RING);
+  const unsigned int target = pairs * (e / PAIR_EPOCH_RING + 1);
+  atomicAdd(slot, 1u);
+  const uint64_t t0 = global_timer_ns();
+  while (*reinterpret_cast<volatile unsigned int*>(slot) < target && global_timer_ns() - t0 < wait_ns) {
+  }
+}
+
 __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
   const int band_tiles = group_m * tiles_n;
   const int band = tile / band_tiles;
@@ -158,13 +171,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       uint32_t phase = 0;
       bool ok = true;
       const uint64_t pol_a = l2_policy(p.l2_policy & 3), pol_b = l2_policy((p.l2_policy >> 2) & 3);
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+      const bool lockstep = p.epoch_ctr != nullptr && rank == 0;
+      const int epochs_per_tile = (stages_per_tile + PAIR_EPOCH_STAGES - 1) / PAIR_EPOCH_STAGES;
+      int my_tiles = 0;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++my_tiles) {
         int tm, tn;
         pair_tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const int m0 = tm * PAIR_BM + static_cast<int>(rank) * 128;  // this block's rows of A
         const int n0 = tn * BN + static_cast<int>(rank) * HALF_N;    // this block's half of B's N-rows
         for (int it = 0; it < stages_per_tile; ++it) {
           const int kb = MIXED ? (it < p.num_k_blocks + mix_rescale ? it : it - p.num_k_blocks - mix_rescale) : it;
+          if (lockstep && (it % PAIR_EPOCH_STAGES) == 0)
+            pair_soft_epoch(p.epoch_ctr, static_cast<unsigned int>(my_tiles * epochs_per_tile + it / PAIR_EPOCH_STAGES),
+                            static_cast<unsigned int>(num_pairs), 4000);
           if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
             atomicCAS(p.status, 0, 0x1100 | (rank << 4) | stage);
             ok = false;
@@ -223,6 +242,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             phase ^= 1u;
           }
         }
+      }
+      if (lockstep) {
+        // a pair with fewer tiles than the others counts itself into the epochs it will not reach
+        const int most_tiles = (num_tiles + num_pairs - 1) / num_pairs;
+        for (int e = my_tiles * epochs_per_tile; e < most_tiles * epochs_per_tile; ++e)
+          atomicAdd(p.epoch_ctr + (e % PAIR_EPOCH_RING), 1u);
       }
       if (!ok) {
         const uint64_t t0 = global_timer_ns();
