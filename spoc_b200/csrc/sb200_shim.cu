@@ -362,6 +362,13 @@ unsigned int* next_epoch_ring(DeviceState& d, cudaStream_t st, long long stages_
   if (setting == 0 || (setting < 0 && stages_per_tile < 128)) return nullptr;
   constexpr int kRings = 8, kRingWords = 64;
   if (!d.epoch_rings) {
+    // never allocate while the stream is being captured into a graph (it would invalidate the capture): such a
+    // launch simply runs without the hint
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+      cudaGetLastError();
+      return nullptr;
+    }
     std::lock_guard<std::mutex> lock(d.mu);
     if (!d.epoch_rings && cudaMalloc(&d.epoch_rings, kRings * kRingWords * sizeof(unsigned int)) != cudaSuccess) {
       cudaGetLastError();
@@ -742,6 +749,7 @@ int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, l
     std::lock_guard<std::mutex> lock(d.mu);
     if (d.ws_in_use && d.ws_last_stream != st) CU_TRY(cudaStreamWaitEvent(st, d.ws_event, 0));
   }
+  unsigned int* epoch_ring = next_epoch_ring(d, st, kp / 64);
   const bool prof = g_profiling.load() != 0;
   DeviceState::ProfRec rec{nullptr, nullptr, nullptr};
   if (prof) {
@@ -808,6 +816,7 @@ int launch_gemm_f16(DeviceState& d, cudaStream_t st, long long M, long long N, l
   gp.num_k_blocks = static_cast<int>(kp / 64);
   gp.status = d.status;
   d.status_armed.store(true);
+  gp.epoch_ctr = epoch_ring;
   derive_params(&gp);
   gp.row_scale = row_scale;
   gp.col_scale = col_scale;
