@@ -94,6 +94,8 @@ struct GemmParams {
   // microseconds at most for the other pairs, so that the pairs of a wave, which share rows of A and columns of B
   // through L2, stay within L2's reach of one another.  A hint: nothing depends on the wait.
   unsigned int* epoch_ctr;
+  int epoch_stages;   // stages between two epochs (64 unless SAREK_B200_LOCKSTEP_STAGES says otherwise)
+  int epoch_wait_ns;  // longest wait at an epoch (4000)
 };
 
 // Control words of the mixed mode, in device memory: the preparation kernels fill them, the GEMM reads them.

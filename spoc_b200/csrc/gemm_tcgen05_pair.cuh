@@ -41,7 +41,6 @@ struct PairCfg {
   static constexpr uint32_t kSmemBytes = kStages * kStageBytes + GEMM_EPI_BUF_BYTES + GEMM_CTRL_BYTES + 1024;
 };
 
-constexpr int PAIR_EPOCH_STAGES = 64;  // soft lockstep: stages between two epochs
 constexpr int PAIR_EPOCH_RING = 64;    // epoch counters (a pair far ahead wraps onto an old counter: harmless, a hint)
 
 // Count this pair into epoch e and wait, for wait_ns at most, until all `pairs` pairs of the launch have reached it.
@@ -172,7 +171,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       bool ok = true;
       const uint64_t pol_a = l2_policy(p.l2_policy & 3), pol_b = l2_policy((p.l2_policy >> 2) & 3);
       const bool lockstep = p.epoch_ctr != nullptr && rank == 0;
-      const int epochs_per_tile = (stages_per_tile + PAIR_EPOCH_STAGES - 1) / PAIR_EPOCH_STAGES;
+      const int epoch_stages = p.epoch_stages > 0 ? p.epoch_stages : 64;
+      const int epochs_per_tile = (stages_per_tile + epoch_stages - 1) / epoch_stages;
       int my_tiles = 0;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++my_tiles) {
         int tm, tn;
@@ -181,9 +181,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         const int n0 = tn * BN + static_cast<int>(rank) * HALF_N;    // this block's half of B's N-rows
         for (int it = 0; it < stages_per_tile; ++it) {
           const int kb = MIXED ? (it < p.num_k_blocks + mix_rescale ? it : it - p.num_k_blocks - mix_rescale) : it;
-          if (lockstep && (it % PAIR_EPOCH_STAGES) == 0)
-            pair_soft_epoch(p.epoch_ctr, static_cast<unsigned int>(my_tiles * epochs_per_tile + it / PAIR_EPOCH_STAGES),
-                            static_cast<unsigned int>(num_pairs), 4000);
+          if (lockstep && (it % epoch_stages) == 0)
+            pair_soft_epoch(p.epoch_ctr, static_cast<unsigned int>(my_tiles * epochs_per_tile + it / epoch_stages),
+                            static_cast<unsigned int>(num_pairs), static_cast<uint64_t>(p.epoch_wait_ns));
           if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
             atomicCAS(p.status, 0, 0x1100 | (rank << 4) | stage);
             ok = false;

@@ -340,7 +340,17 @@ int l2_policy_setting() {
 
 // Fields of GemmParams that follow from the others: whether the epilogue may move 128-bit vectors, and the
 // eviction policies.
+int env_int(const char* name, int fallback, int lo, int hi) {
+  const char* e = getenv(name);
+  const int v = e ? atoi(e) : fallback;
+  return v >= lo && v <= hi ? v : fallback;
+}
+
 void derive_params(GemmParams* gp) {
+  static const int epoch_stages = env_int("SAREK_B200_LOCKSTEP_STAGES", 64, 4, 4096);
+  static const int epoch_wait_ns = env_int("SAREK_B200_LOCKSTEP_WAIT_NS", 4000, 0, 1000000);
+  gp->epoch_stages = epoch_stages;
+  gp->epoch_wait_ns = epoch_wait_ns;
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   bool vec = (gp->N & 3) == 0 && al16(gp->D) && (gp->ldd & 3) == 0 && (!gp->C || (al16(gp->C) && (gp->ldc & 3) == 0)) &&
              (!gp->bias || al16(gp->bias));
