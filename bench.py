@@ -355,9 +355,10 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         "frac": achieved / tf32_peak,
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, taken from an
         # ncu capture of this same kernel and size (a profiler figure, not measured in this run)
-        "traffic": 6.956e9 + 0.258e9,
-        "traffic_unit": "bytes per launch (ncu capture of this kernel at this size, profiles/gemm_pair_kernel_8192cubed_modes_and_l2_policies_ncu.md; "
-                        "box to box the figure varies by about 30 %)",
+        "traffic": 4.832e9 + 0.256e9,
+        "traffic_unit": "bytes per launch (ncu capture of this kernel at this size with the soft lockstep on, "
+                        "profiles/gemm_pair_kernel_4096x32768x32768_ncu.md; 6.63e9 + 0.26e9 with SAREK_B200_LOCKSTEP=0; algorithmic "
+                        "bytes 1.28e9: A, B, their low-part panels, C in, D out)",
         "peak_source": (f"{peaks['source']}: bf16 sustained {peaks['bf16_tflops_sustained']} TF/s / 2 = dense TF32 under the power cap "
                         "(the timed steps follow a pre-load)" if sustained else
                         f"{peaks['source']}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 = dense TF32"),
