@@ -410,6 +410,12 @@ SB200_API int sb200_set_gemm_variant(int variant);
 /* tile columns of the CTA-pair kernel: 0 = automatic (256, or 128 / 64 for problems with too few 256-column
  * tiles to occupy the SMs), else 64, 128 or 256.  Also SAREK_B200_TILE_N.  Results do not depend on it. */
 SB200_API int sb200_set_gemm_tile_n(int tile_n);
+/* The soft lockstep of the CTA-pair kernel: every 64 stages of the k-loop each pair counts itself into an epoch counter
+ * in global memory and waits, 4 us at most and then regardless, for the other pairs of the launch, so that the pairs of a
+ * wave, which share rows of A and columns of B through L2, stay within L2's reach of one another (DRAM reads of the
+ * 8192^3 launch 4.8 GB instead of 6.6 GB; 35 instead of 131 GB at K = 32768).  A hint: results do not depend on it.
+ * -1 = on for k-loops of 128 stages or more (default), 0 = off, 1 = always.  Also SAREK_B200_LOCKSTEP=0|1. */
+SB200_API int sb200_set_lockstep(int setting);
 /* SB200_MODE_3XMIXED hands products of fewer than this many multiply-adds (M*N*K) to 3xTF32, whose two launches cost
  * less than the mixed mode's seven on small problems; 0 restores the default (2^34).  A tuning and test knob. */
 SB200_API int sb200_set_mixed_min_macs(int64_t macs);

@@ -79,6 +79,7 @@ let sb200_kernel_launch_from_host =
 let sb200_prefetch_wait = fn "sb200_prefetch_wait" (int @-> returning int)
 let sb200_enable_profiling = fn "sb200_enable_profiling" (int @-> returning int)
 let sb200_set_mode = fn "sb200_set_mode" (int @-> returning int)
+let sb200_set_lockstep = fn "sb200_set_lockstep" (int @-> returning int)
 (* fusion on IR text; kind 5 = the backend's guarded fusion of `if tid < n then ..` kernels,
    which Sarek_fusion leaves unfused (sarek/sarek/Sarek_fusion.ml:370-375) *)
 let sb200_ir_fuse_as =

@@ -113,6 +113,7 @@ SIGNATURES = {
     "sb200_get_mode": ([p(i32)], i32),
     "sb200_set_gemm_variant": ([i32], i32),
     "sb200_set_gemm_tile_n": ([i32], i32),
+    "sb200_set_lockstep": ([i32], i32),
     "sb200_set_mixed_min_macs": ([i64], i32),
     "sb200_mixed_plan": ([f32, f32, p(C.c_int32)], i32),
     "sb200_set_l2_policy": ([i32], i32),

@@ -364,11 +364,15 @@ void derive_params(GemmParams* gp) {
 // rings.  Measured in the sustained loop at 8192^3: 245 against 221-227 TFLOP/s in alternating runs on one box, the SM
 // clock under the power cap 1400 against 1267-1305 MHz, because the pairs that stay together re-read less from DRAM.  Eight rings are handed out in turn so that launches in flight on several streams rarely share one
 // (sharing only blunts the hint).
+std::atomic<int> g_lockstep{-2};  // -2 = not yet read from the environment; -1 by k-loop length, 0 off, 1 always
+
 unsigned int* next_epoch_ring(DeviceState& d, cudaStream_t st, long long stages_per_tile) {
-  static const int setting = [] {
+  int setting = g_lockstep.load();
+  if (setting == -2) {
     const char* e = getenv("SAREK_B200_LOCKSTEP");
-    return e ? atoi(e) : -1;  // -1: by k-loop length
-  }();
+    setting = e ? (atoi(e) != 0 ? 1 : 0) : -1;
+    g_lockstep.store(setting);
+  }
   if (setting == 0 || (setting < 0 && stages_per_tile < 128)) return nullptr;
   constexpr int kRings = 8, kRingWords = 64;
   if (!d.epoch_rings) {
@@ -2334,6 +2338,12 @@ int sb200_mixed_plan(float max_a, float max_b, int32_t out[5]) {
   out[2] = c.first_scale;
   out[3] = c.shift_a;
   out[4] = c.shift_b;
+  return SB200_OK;
+}
+
+int sb200_set_lockstep(int setting) {
+  if (setting < -1 || setting > 1) return fail(SB200_ERR_INVALID_VALUE, "lockstep setting must be -1 (by k-loop length), 0 or 1");
+  g_lockstep.store(setting);
   return SB200_OK;
 }
 

@@ -1025,3 +1025,33 @@ def test_f16_modes_scale_every_row_of_a_and_column_of_b_on_its_own(backend, devi
     finally:
         for x in bufs + [D0, D1]:
             x.free()
+
+
+@pytest.mark.parametrize("mode", [L.MODE_3XTF32, L.MODE_TF32, L.MODE_3XF16, L.MODE_3XMIXED])
+def test_soft_lockstep_changes_no_bit(backend, device, mode):
+    """The epoch waits that keep the CTA pairs of a wave together over a long k-loop are a hint: the same bits with the
+    lockstep off, on by k-loop length (K = 8192: 256 stages) and forced on for a short loop."""
+    lib = L.load()
+    outs = []
+    try:
+        lib.sb200_set_mixed_min_macs(1 << 20)
+        for (M, N, K), settings in (((1024, 1280, 8192), (0, -1, 1)), ((1024, 1024, 512), (0, 1))):
+            a, b = O.fill(M * K, 91, 1), O.fill(K * N, 91, 2)
+            A, B, D = dev_from(backend, device, a), dev_from(backend, device, b), Dev(backend, device, M * N)
+            try:
+                got = []
+                for setting in settings:
+                    assert lib.sb200_set_lockstep(setting) == 0
+                    D.clear()
+                    gemm(backend, device, mode, M, N, K, A, B, D)
+                    got.append(D.download())
+                for g in got[1:]:
+                    assert np.array_equal(g, got[0])
+                outs.append(got[0])
+            finally:
+                for x in (A, B, D):
+                    x.free()
+        assert lib.sb200_set_lockstep(2) == L.ERR_INVALID_VALUE
+    finally:
+        lib.sb200_set_lockstep(-1)
+        lib.sb200_set_mixed_min_macs(0)
