@@ -1186,7 +1186,17 @@ def run_skinny(args, rank: int, local_rank: int, world: int) -> None:
         ctx.dist.destroy_process_group()
 
 
+def _keep_stdout_for_the_result_line() -> None:
+    """Libraries that write to file descriptor 1 themselves (NCCL prints its version there) must not add lines to the
+    one-line result: descriptor 1 is pointed at stderr for them, and Python's stdout keeps the real one."""
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(saved, "w", buffering=1)
+
+
 def main() -> None:
+    _keep_stdout_for_the_result_line()
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="gemm8192", choices=["gemm8192", "gather", "skinny"],
                     help="gemm8192: the headline run; gather: large square GEMM with the result gathered on every GPU; "
