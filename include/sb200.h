@@ -414,7 +414,8 @@ SB200_API int sb200_set_gemm_tile_n(int tile_n);
  * in global memory and waits, 4 us at most and then regardless, for the other pairs of the launch, so that the pairs of a
  * wave, which share rows of A and columns of B through L2, stay within L2's reach of one another (DRAM reads of the
  * 8192^3 launch 4.8 GB instead of 6.6 GB; 35 instead of 131 GB at K = 32768).  A hint: results do not depend on it.
- * -1 = on for k-loops of 128 stages or more (default), 0 = off, 1 = always.  Also SAREK_B200_LOCKSTEP=0|1. */
+ * -1 = on for k-loops of 128 stages or more except in TF32 mode, whose short stages make the waits weigh more than the
+ * traffic they save (default), 0 = off, 1 = always.  Also SAREK_B200_LOCKSTEP=0|1. */
 SB200_API int sb200_set_lockstep(int setting);
 /* SB200_MODE_3XMIXED hands products of fewer than this many multiply-adds (M*N*K) to 3xTF32, whose two launches cost
  * less than the mixed mode's seven on small problems; 0 restores the default (2^34).  A tuning and test knob. */

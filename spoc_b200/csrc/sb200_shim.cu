@@ -366,14 +366,17 @@ void derive_params(GemmParams* gp) {
 // (sharing only blunts the hint).
 std::atomic<int> g_lockstep{-2};  // -2 = not yet read from the environment; -1 by k-loop length, 0 off, 1 always
 
-unsigned int* next_epoch_ring(DeviceState& d, cudaStream_t st, long long stages_per_tile) {
+unsigned int* next_epoch_ring(DeviceState& d, cudaStream_t st, long long stages_per_tile, bool by_default = true) {
   int setting = g_lockstep.load();
   if (setting == -2) {
     const char* e = getenv("SAREK_B200_LOCKSTEP");
     setting = e ? (atoi(e) != 0 ? 1 : 0) : -1;
     g_lockstep.store(setting);
   }
-  if (setting == 0 || (setting < 0 && stages_per_tile < 128)) return nullptr;
+  // by_default = false: TF32 mode.  Its stages are a third as long as 3xTF32's, so an epoch's wait weighs three times as
+  // much, and alternating runs gave 474-476 TFLOP/s with the lockstep against 593-606 without on one box (573 against 535
+  // on another): off unless forced.
+  if (setting == 0 || (setting < 0 && (stages_per_tile < 128 || !by_default))) return nullptr;
   constexpr int kRings = 8, kRingWords = 64;
   if (!d.epoch_rings) {
     // never allocate while the stream is being captured into a graph (it would invalidate the capture): such a
@@ -606,7 +609,7 @@ int launch_gemm_mode(DeviceState& d, cudaStream_t st, long long M, long long N, 
       if (d.ws_in_use && d.ws_last_stream != st) CU_TRY(cudaStreamWaitEvent(st, d.ws_event, 0));
     }
   }
-  unsigned int* epoch_ring = pair ? next_epoch_ring(d, st, kp / GEMM_BK) : nullptr;  // zeroed ahead of the preparation launch
+  unsigned int* epoch_ring = pair ? next_epoch_ring(d, st, kp / GEMM_BK, MODE == 3) : nullptr;  // zeroed ahead of the preparation launch
   const bool prof = g_profiling.load() != 0;
   DeviceState::ProfRec rec{nullptr, nullptr, nullptr};
   if (prof) {
